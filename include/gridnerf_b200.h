@@ -1,0 +1,171 @@
+/*
+ * gridnerf_b200 -- C ABI of the B200 (sm_100a) GridNeRF render path.
+ *
+ * This is the boundary a host binds instead of the reference's per-chunk ``_forward``
+ * callable (dist_render/ddp_infer/inferer_impl.py:36,60-61,107-119) and instead of the
+ * pybind kernel modules that its kernel-fusion path chains
+ * (dist_render/kernel/cuda_render_extend.py:4-22,350-526).
+ *
+ * Conventions
+ *  - plain C types only; every pointer is a DEVICE pointer unless its name ends in ``_h``;
+ *  - every call that enqueues work takes the CUDA stream (``void*`` = ``cudaStream_t``) and
+ *    never synchronises it, except the ``*_host`` calls, which return finished host buffers;
+ *  - return value 0 = ok, negative = error detected on the host before anything was
+ *    enqueued (``gnr_last_error`` gives the text).  Conditions only the device can see
+ *    (a compacted list larger than its capacity) are written into the 8-word status block
+ *    at the start of the workspace and read back with ``gnr_read_status``;
+ *  - nothing here falls back to the CPU.
+ */
+#ifndef GRIDNERF_B200_H
+#define GRIDNERF_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct GnrModel GnrModel;
+
+/* Scalar description of one field.  The float members are passed as the exact fp32 values
+ * the reference computes with torch (update_stepSize, app/models/gridnerf_sequential.py:149-164;
+ * AlphaGridMask.__init__, app/models/alpha_mask.py:16-26) so that sampling is bit-exact. */
+typedef struct GnrConfig {
+  float aabb[6];            /* min x,y,z then max x,y,z                        (:91)      */
+  float inv_aabb_size[3];   /* 2 / (max - min)                                 (:159)     */
+  int32_t grid[3];          /* gridSize x,y,z                                  (:160)     */
+  float near_t, far_t;      /* near_far                                        (:101)     */
+  float step_size;          /* mean(units) * step_ratio                        (:162)     */
+  float distance_scale;     /*                                                  (:97)      */
+  float density_shift;      /*                                                  (:95)      */
+  int32_t density_act;      /* 0 = softplus(x + shift), 1 = relu(x)            (:386-399) */
+  float ray_weight_thres;   /* rayMarch_weight_thres: app_mask = w > thres     (:479)     */
+  float alpha_filter_thres; /* alpha_mask_filter_thre                          (:462)     */
+  int32_t n_pairs;          /* plane/line pairs per kind = ndims * len(resMode) (:106-110) */
+  int32_t n_density;        /* channels of every density plane/line            (:88)      */
+  int32_t n_app;            /* channels of every appearance plane/line         (:89)      */
+  int32_t app_dim;          /* basis_mat output width (27)                     (:678)     */
+  int32_t fea_pe, view_pe;  /* positional-encoding octaves (mlp_render_fea.py:20-27)      */
+  int32_t hidden;           /* featureC (128)                                             */
+  int32_t has_bias;         /* bias_enable                                                */
+  int32_t mlp_mode;         /* 0 = fp32 CUDA-core MLP, 1 = tcgen05 split-precision MLP (fp32-grade),
+                               2 = tcgen05 single bf16 MLP (fast)                         */
+  int32_t reserved[8];
+} GnrConfig;
+
+/* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */
+enum {
+  GNR_ST_OVERFLOW_VALID = 0, /* 1 if #valid samples exceeded max_valid                    */
+  GNR_ST_OVERFLOW_APP = 1,   /* 1 if #appearance samples exceeded max_app                 */
+  GNR_ST_NUM_VALID = 2,      /* #samples passing the box + occupancy test                 */
+  GNR_ST_NUM_APP = 3,        /* #samples with weight > ray_weight_thres                   */
+  GNR_ST_WAIT_EXPIRED = 4,   /* a bounded device-side wait gave up (tensor-core MLP)      */
+  GNR_ST_WORDS = 8
+};
+
+const char* gnr_last_error(void);
+int gnr_version(void);
+
+/* Model lifetime.  Replaces GridNeRF(**kwargs) + .load(ckpt)
+ * (dist_render/ddp_infer/inferer_impl.py:134-142).  ``device`` is the CUDA ordinal. */
+int gnr_create(const GnrConfig* cfg_h, int device, GnrModel** out_h);
+int gnr_destroy(GnrModel* m);
+
+/* Parameter upload: the source is the reference's checkpoint layout, converted on the
+ * device to this library's layout (channel-last planes ``[H][W][C]``, lines ``[L][C]``,
+ * channels zero-padded to a multiple of 16).  kind 0 = density, 1 = appearance; ``idx`` is
+ * the position in the reference's ParameterList (plane ``idx`` belongs to dimension
+ * ``idx / len(resMode)``).  ``axis_x``/``axis_y`` are matMode[dim] (the xyz components that
+ * index the plane's W and H) and ``axis`` is vecMode[dim].
+ * Replaces load_state_dict of density_plane/app_plane ``[1,C,H,W]`` and
+ * density_line/app_line ``[1,C,L,1]`` (app/models/gridnerf_sequential.py:106-107,676-677,703-718). */
+int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src_chw, int C, int H, int W, int axis_x,
+                     int axis_y, void* stream);
+int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src_cl, int C, int L, int axis, void* stream);
+/* Occupancy volume ``[D][H][W]`` of 0/1 bytes, bit-packed on the device; ``aabb_h`` and
+ * ``inv_size_h`` are AlphaGridMask.aabb and .invgridSize (app/models/alpha_mask.py:20-22).
+ * Passing ``vol = NULL`` removes the mask (alphaMask is None, gridnerf_sequential.py:460). */
+int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, const float* aabb_h,
+                          const float* inv_size_h, void* stream);
+/* basis_mat.weight ``[app_dim][sum n_app]`` and renderModule.mlp.{0,2,4}.{weight,bias}
+ * (row-major ``[out][in]``; bias pointers may be NULL).  app/models/mlp_render_fea.py:29-42. */
+int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const float* b1, const float* w2,
+                   const float* b2, const float* w3, const float* b3, void* stream);
+
+/* Ray generation from a pose.  Replaces generate_rays (dist_render/dataset/utils.py:92-113):
+ * ``dir_x[W]`` and ``dir_y[H]`` are the two torch.arange tables of
+ * get_ray_directions_blender_faster (:57-70); ``pose_h`` is the row-major ``[3][4]`` c2w.
+ * Ray ``r`` of the output is pixel ``pixel_ids[r]`` (row-major y*W+x), or pixel
+ * ``first_pixel + r`` if ``pixel_ids`` is NULL.  Output ``rays[n][6]`` = origin, direction. */
+int gnr_generate_rays(const float* pose_h, const float* dir_x, const float* dir_y, int H, int W,
+                      const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays, void* stream);
+
+/* Scratch memory for one chunk.  The caller allocates ``bytes`` (256-byte aligned) and
+ * passes it to the calls below; contents carry no state between chunks. */
+int gnr_workspace_bytes(const GnrModel* m, int64_t n_rays, int n_samples, int64_t max_valid,
+                        int64_t max_app, size_t* bytes_h);
+
+/* The whole per-chunk forward: GridBaseSequential.forward, dense-sampling branch
+ * (app/models/gridnerf_sequential.py:448-504) = sample_ray (:244-281) + alphaMask filter
+ * (:460-465) + compute_densityfeature (:779-827) + feature2density (:386-399) + raw2alpha
+ * (app/tools/utils.py:51-64) + compute_appfeature (:829-871) + MLPRender_Fea.forward
+ * (app/models/mlp_render_fea.py:44-68) + compositing (:493-501).
+ * ``rays[n][6]`` -> ``rgb_map[n][3]``, ``depth_map[n]`` (either output may be NULL). */
+int gnr_render_chunk(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, int white_bg,
+                     void* workspace, size_t workspace_bytes, int64_t max_valid, int64_t max_app,
+                     float* rgb_map, float* depth_map, void* stream);
+
+/* Same forward with HOST buffers: copies ``rays_h`` to the device in chunks of
+ * ``chunk_rays``, renders, copies rgb/depth back, synchronises, and returns the status block.
+ * This is the renderer_fn chunk loop (dist_render/ddp_infer/inferer_impl.py:95-120) with its
+ * host<->device traffic included.  ``rays_h``/``rgb_h``/``depth_h`` should be pinned. */
+int gnr_render_host(GnrModel* m, const float* rays_h, int64_t n_rays, int n_samples, int white_bg,
+                    int64_t chunk_rays, int64_t max_valid, int64_t max_app, float* rgb_h, float* depth_h,
+                    int32_t* status_h);
+
+/* ---- stage-wise entries (each kernel is parity-testable alone) ---------------------------- */
+
+/* Stage 1: sample_ray + alphaMask filter + compaction.  Outputs (any may be NULL except
+ * inside the workspace, where they are always produced): per-ray ``t_min[n]``, per-ray valid
+ * ``counts[n]``, exclusive ``offsets[n+1]``, the validity bit words ``mask_words[n][ceil(S/32)]``
+ * and the compacted ``ids`` (ray << kbits | sample, kbits = gnr_sample_bits(S)) in the order
+ * of ``xyz_sampled[ray_valid]`` (ray-major).  gridnerf_sequential.py:244-281,460-465. */
+int gnr_sample(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+               size_t workspace_bytes, int64_t max_valid, float* t_min, int32_t* counts, int32_t* offsets,
+               uint32_t* mask_words, uint32_t* ids, void* stream);
+int gnr_sample_bits(int n_samples);
+
+/* Stage 2: density for the compacted samples of the last gnr_sample on this workspace:
+ * ``sigma[i] = feature2density(compute_densityfeature(xyz_i))``; also the raw feature.
+ * gridnerf_sequential.py:471-475,779-827,386-399. */
+int gnr_density(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+                size_t workspace_bytes, int64_t max_valid, float* sigma_feature, float* sigma, void* stream);
+
+/* Stage 3: raw2alpha + app_mask + second compaction (app/tools/utils.py:51-64,
+ * gridnerf_sequential.py:477-479,493,501).  ``weights[i]`` per valid sample, ``acc[n]``,
+ * ``depth[n]``, ``app_counts[n]``, ``app_offsets[n+1]``, ``app_index[j]`` = position in the
+ * valid list of appearance sample j. */
+int gnr_weights(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+                size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* weights, float* acc,
+                float* depth, int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream);
+
+/* Stage 4: compute_appfeature (gather + basis_mat) and MLPRender_Fea for the appearance
+ * samples: ``app_features[j][app_dim]`` and ``rgb[j][3]``.  gridnerf_sequential.py:829-871,
+ * app/models/mlp_render_fea.py:44-68. */
+int gnr_appearance(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+                   size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* app_features,
+                   float* rgb, void* stream);
+
+/* Stage 5: rgb_map = sum w * rgb (+ 1 - acc), clamp; depth_map.  gridnerf_sequential.py:493-501. */
+int gnr_composite(GnrModel* m, int64_t n_rays, int white_bg, void* workspace, size_t workspace_bytes,
+                  int64_t max_valid, int64_t max_app, int n_samples, float* rgb_map, float* depth_map,
+                  void* stream);
+
+/* Copy the 8-word status block of a workspace to the host (synchronises the stream). */
+int gnr_read_status(const void* workspace, int32_t* status_h, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRIDNERF_B200_H */

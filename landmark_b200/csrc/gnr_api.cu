@@ -1,0 +1,681 @@
+// C-ABI entry points: model lifetime, parameter upload / layout conversion, workspace layout,
+// the per-chunk forward and its stage-wise pieces.
+#include <stdarg.h>
+#include <string.h>
+
+#include <new>
+
+#include "gnr_internal.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------------------------
+static thread_local char g_error[512] = "";
+
+void gnr_set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+extern "C" const char* gnr_last_error(void) { return g_error; }
+extern "C" int gnr_version(void) { return 100; }
+
+namespace {
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct DeviceGuard {
+  int prev;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+  }
+  ~DeviceGuard() { cudaSetDevice(prev); }
+};
+
+// ---- layout conversion kernels -------------------------------------------------------------
+// [C][P] (P = H*W or L) -> [P][Cp], zero padded channels.  A 32x32 tile goes through shared
+// memory so that both the read and the write are coalesced.
+__global__ void to_channel_last_kernel(const float* __restrict__ src, float* __restrict__ dst, int C, int Cp, long long P) {
+  __shared__ float tile[32][33];
+  const long long p0 = (long long)blockIdx.x * 32;
+  const int c0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r;
+    const long long p = p0 + threadIdx.x;
+    tile[r][threadIdx.x] = (c < C && p < P) ? src[(long long)c * P + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const long long p = p0 + r;
+    const int c = c0 + threadIdx.x;
+    if (p < P && c < Cp) dst[p * Cp + c] = tile[threadIdx.x][r];
+  }
+}
+
+__global__ void pack_bits_kernel(const uint8_t* __restrict__ vol, uint32_t* __restrict__ bits, long long n_vox, long long n_words) {
+  long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  uint32_t v = 0;
+  for (int b = 0; b < 32; ++b) {
+    long long i = w * 32 + b;
+    if (i < n_vox && vol[i]) v |= (1u << b);
+  }
+  bits[w] = v;
+}
+
+__global__ void transpose_pad_kernel(const float* __restrict__ w, float* __restrict__ wt, int out_f, int in_f, int in_pad) {
+  // w [out_f][in_f] -> wt [in_pad][out_f]
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= in_pad * out_f) return;
+  int k = i / out_f, n = i - k * out_f;
+  wt[i] = (k < in_f) ? w[n * in_f + k] : 0.0f;
+}
+
+__global__ void copy_or_zero_kernel(const float* __restrict__ src, float* __restrict__ dst, int n_src, int n_dst) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_dst) dst[i] = (src && i < n_src) ? src[i] : 0.0f;
+}
+
+// basis_mat.weight [app_dim][n_pairs * C] -> blocked [pair][c4][t = 4 j + e][28] (+8 pad per block)
+__global__ void block_basis_kernel(const float* __restrict__ w, float* __restrict__ dst, int app_dim, int n_pairs, int C, int J) {
+  const int blk = 4 * J * 28 + 8;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_pairs * 4 * blk) return;
+  int pc = i / blk, r = i - pc * blk;
+  int pair = pc >> 2, c4 = pc & 3;
+  float v = 0.0f;
+  if (r < 4 * J * 28) {
+    int t = r / 28, o = r - t * 28;
+    int j = t >> 2, e = t & 3;
+    int c = 16 * j + 4 * c4 + e;
+    if (o < app_dim && c < C) v = w[(long long)o * (n_pairs * C) + pair * C + c];
+  }
+  dst[i] = v;
+}
+
+int free_dev(void* p) {
+  if (p) cudaFree(p);
+  return 0;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+// lifetime
+// ---------------------------------------------------------------------------------------------
+extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
+  if (!cfg || !out) {
+    gnr_set_error("gnr_create: null argument");
+    return -1;
+  }
+  if (cfg->n_pairs < 1 || cfg->n_pairs > GNR_MAX_PLANES) {
+    gnr_set_error("gnr_create: n_pairs %d outside [1, %d]", cfg->n_pairs, GNR_MAX_PLANES);
+    return -1;
+  }
+  if (cfg->app_dim < 1 || cfg->app_dim > 28) {
+    gnr_set_error("gnr_create: app_dim %d outside [1, 28]", cfg->app_dim);
+    return -1;
+  }
+  if (cfg->n_density < 1 || cfg->n_density > 64 || cfg->n_app < 1 || cfg->n_app > 64) {
+    gnr_set_error("gnr_create: channels per plane must be in [1, 64] (density %d, appearance %d)", cfg->n_density, cfg->n_app);
+    return -1;
+  }
+  if (cfg->fea_pe < 0 || cfg->fea_pe > 8 || cfg->view_pe < 0 || cfg->view_pe > 8) {
+    gnr_set_error("gnr_create: fea_pe %d / view_pe %d outside [0, 8]", cfg->fea_pe, cfg->view_pe);
+    return -1;
+  }
+  int n_dev = 0;
+  GNR_CUDA_OK(cudaGetDeviceCount(&n_dev));
+  if (device < 0 || device >= n_dev) {
+    gnr_set_error("gnr_create: device %d not present (%d devices)", device, n_dev);
+    return -1;
+  }
+  cudaDeviceProp prop;
+  GNR_CUDA_OK(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    gnr_set_error("gnr_create: device %d is sm_%d%d; this library contains sm_100a code only", device, prop.major, prop.minor);
+    return -1;
+  }
+  GnrModel* m = new (std::nothrow) GnrModel();
+  if (!m) {
+    gnr_set_error("gnr_create: out of host memory");
+    return -1;
+  }
+  memset(m, 0, sizeof(*m));
+  m->cfg = *cfg;
+  m->device = device;
+  m->sm_count = prop.multiProcessorCount > 0 ? prop.multiProcessorCount : GNR_SM_COUNT_FALLBACK;
+  const int A = cfg->app_dim, V = cfg->view_pe > 0 ? cfg->view_pe : 0;
+  m->mlp.in_dim = A + 3 + 2 * cfg->fea_pe * A + 2 * V * 3;
+  m->mlp.k1_pad = (m->mlp.in_dim + 7) / 8 * 8;
+  *out = m;
+  return 0;
+}
+
+extern "C" int gnr_destroy(GnrModel* m) {
+  if (!m) return 0;
+  DeviceGuard g(m->device);
+  cudaDeviceSynchronize();
+  for (int i = 0; i < GNR_MAX_PLANES; ++i) {
+    free_dev(m->den_plane_buf[i]);
+    free_dev(m->den_line_buf[i]);
+    free_dev(m->app_plane_buf[i]);
+    free_dev(m->app_line_buf[i]);
+  }
+  free_dev(m->alpha_bits);
+  free_dev(m->mlp.basis_blocked);
+  free_dev(m->mlp.w1t);
+  free_dev(m->mlp.w2t);
+  free_dev(m->mlp.w3);
+  free_dev(m->mlp.b1);
+  free_dev(m->mlp.b2);
+  free_dev(m->mlp.b3);
+  free_dev(m->mlp.tc_image);
+  free_dev(m->host_ws);
+  free_dev(m->host_rays);
+  free_dev(m->host_rgb);
+  free_dev(m->host_depth);
+  if (m->host_status) cudaFreeHost(m->host_status);
+  for (int i = 0; i < 2; ++i) {
+    if (m->host_streams[i]) cudaStreamDestroy(m->host_streams[i]);
+    if (m->host_events[i]) cudaEventDestroy(m->host_events[i]);
+  }
+  delete m;
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// uploads
+// ---------------------------------------------------------------------------------------------
+static int padded_channels(int C) { return (C + 15) / 16 * 16; }
+
+extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src, int C, int H, int W, int axis_x,
+                                int axis_y, void* stream) {
+  if (!m || !src || kind < 0 || kind > 1 || idx < 0 || idx >= m->cfg.n_pairs || H < 1 || W < 1 ||
+      axis_x < 0 || axis_x > 2 || axis_y < 0 || axis_y > 2) {
+    gnr_set_error("gnr_upload_plane: bad argument (kind %d idx %d C %d H %d W %d)", kind, idx, C, H, W);
+    return -1;
+  }
+  const int expect = kind == 0 ? m->cfg.n_density : m->cfg.n_app;
+  if (C != expect) {
+    gnr_set_error("gnr_upload_plane: plane %d of kind %d has %d channels, config says %d", idx, kind, C, expect);
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  const int Cp = padded_channels(C);
+  float** buf = kind == 0 ? &m->den_plane_buf[idx] : &m->app_plane_buf[idx];
+  GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
+  free_dev(*buf);
+  *buf = nullptr;
+  const long long P = (long long)H * W;
+  GNR_CUDA_OK(cudaMalloc(buf, (size_t)P * Cp * sizeof(float)));
+  dim3 grid((unsigned)((P + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
+  to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, P);
+  GNR_CUDA_OK(cudaGetLastError());
+  pl->plane = *buf;
+  pl->H = H;
+  pl->W = W;
+  pl->C = Cp;
+  pl->mat0 = axis_x;
+  pl->mat1 = axis_y;
+  return 0;
+}
+
+extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src, int C, int Ln, int axis, void* stream) {
+  if (!m || !src || kind < 0 || kind > 1 || idx < 0 || idx >= m->cfg.n_pairs || Ln < 1 || axis < 0 || axis > 2) {
+    gnr_set_error("gnr_upload_line: bad argument (kind %d idx %d C %d L %d)", kind, idx, C, Ln);
+    return -1;
+  }
+  const int expect = kind == 0 ? m->cfg.n_density : m->cfg.n_app;
+  if (C != expect) {
+    gnr_set_error("gnr_upload_line: line %d of kind %d has %d channels, config says %d", idx, kind, C, expect);
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  const int Cp = padded_channels(C);
+  float** buf = kind == 0 ? &m->den_line_buf[idx] : &m->app_line_buf[idx];
+  GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
+  free_dev(*buf);
+  *buf = nullptr;
+  GNR_CUDA_OK(cudaMalloc(buf, (size_t)Ln * Cp * sizeof(float)));
+  dim3 grid((unsigned)((Ln + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
+  to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, (long long)Ln);
+  GNR_CUDA_OK(cudaGetLastError());
+  pl->line = *buf;
+  pl->L = Ln;
+  pl->vec = axis;
+  return 0;
+}
+
+extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, const float* aabb_h,
+                                     const float* inv_size_h, void* stream) {
+  if (!m) {
+    gnr_set_error("gnr_upload_alpha_mask: null model");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  free_dev(m->alpha_bits);
+  m->alpha_bits = nullptr;
+  m->aD = m->aH = m->aW = 0;
+  if (!vol) return 0;
+  if (D < 1 || H < 1 || W < 1 || !aabb_h || !inv_size_h || (long long)D * H * W > 0xffffffffLL) {
+    gnr_set_error("gnr_upload_alpha_mask: bad volume %dx%dx%d", D, H, W);
+    return -1;
+  }
+  const long long n_vox = (long long)D * H * W, n_words = (n_vox + 31) / 32;
+  GNR_CUDA_OK(cudaMalloc(&m->alpha_bits, (size_t)n_words * sizeof(uint32_t)));
+  pack_bits_kernel<<<(unsigned)((n_words + 255) / 256), 256, 0, (cudaStream_t)stream>>>(vol, m->alpha_bits, n_vox, n_words);
+  GNR_CUDA_OK(cudaGetLastError());
+  m->aD = D;
+  m->aH = H;
+  m->aW = W;
+  for (int a = 0; a < 3; ++a) {
+    m->a_lo[a] = aabb_h[a];
+    m->a_inv[a] = inv_size_h[a];
+  }
+  return 0;
+}
+
+extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const float* b1, const float* w2,
+                              const float* b2, const float* w3, const float* b3, void* stream) {
+  if (!m || !basis_w || !w1 || !w2 || !w3) {
+    gnr_set_error("gnr_upload_mlp: null weight pointer");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  GnrMlp& q = m->mlp;
+  const int Hd = m->cfg.hidden, J = padded_channels(m->cfg.n_app) / 16;
+  const int n_basis = m->cfg.n_pairs * 4 * (4 * J * 28 + 8);
+  free_dev(q.basis_blocked);
+  free_dev(q.w1t);
+  free_dev(q.w2t);
+  free_dev(q.w3);
+  free_dev(q.b1);
+  free_dev(q.b2);
+  free_dev(q.b3);
+  q.basis_blocked = q.w1t = q.w2t = q.w3 = q.b1 = q.b2 = q.b3 = nullptr;
+  GNR_CUDA_OK(cudaMalloc(&q.basis_blocked, (size_t)n_basis * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.w1t, (size_t)q.k1_pad * Hd * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.w2t, (size_t)Hd * Hd * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.w3, (size_t)3 * Hd * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.b1, (size_t)Hd * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.b2, (size_t)Hd * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&q.b3, 4 * sizeof(float)));
+  block_basis_kernel<<<(n_basis + 255) / 256, 256, 0, st>>>(basis_w, q.basis_blocked, m->cfg.app_dim, m->cfg.n_pairs,
+                                                           m->cfg.n_app, J);
+  transpose_pad_kernel<<<(q.k1_pad * Hd + 255) / 256, 256, 0, st>>>(w1, q.w1t, Hd, q.in_dim, q.k1_pad);
+  transpose_pad_kernel<<<(Hd * Hd + 255) / 256, 256, 0, st>>>(w2, q.w2t, Hd, Hd, Hd);
+  copy_or_zero_kernel<<<(3 * Hd + 255) / 256, 256, 0, st>>>(w3, q.w3, 3 * Hd, 3 * Hd);
+  copy_or_zero_kernel<<<(Hd + 255) / 256, 256, 0, st>>>(b1, q.b1, Hd, Hd);
+  copy_or_zero_kernel<<<(Hd + 255) / 256, 256, 0, st>>>(b2, q.b2, Hd, Hd);
+  copy_or_zero_kernel<<<1, 32, 0, st>>>(b3, q.b3, 3, 4);
+  GNR_CUDA_OK(cudaGetLastError());
+  q.n_prod = m->cfg.n_pairs * padded_channels(m->cfg.n_app);
+  if (m->cfg.mlp_mode != 0) return gnr_mlp_tc_prepare(m, w1, b1, w2, b2, w3, b3, st);
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// workspace
+// ---------------------------------------------------------------------------------------------
+extern "C" int gnr_sample_bits(int n_samples) {
+  int b = 1;
+  while ((1 << b) < n_samples) ++b;
+  return b;
+}
+
+GnrWs gnr_ws_layout(const GnrModel* m, int64_t n, int S, int64_t max_valid, int64_t max_app) {
+  GnrWs L;
+  memset(&L, 0, sizeof(L));
+  const size_t words = (size_t)(S + 31) / 32;
+  const size_t n_blocks = (size_t)(n + 1023) / 1024 + 1;
+  L.feat_stride = (m->cfg.app_dim + 3) / 4 * 4;
+  L.max_valid = max_valid;
+  L.max_app = max_app;
+  L.n_rays = n;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    size_t at = off;
+    off = align_up(off + bytes, 256);
+    return at;
+  };
+  L.status = take(GNR_ST_WORDS * sizeof(int32_t));
+  L.t_min = take((size_t)n * 4);
+  L.words = take((size_t)n * words * 4);
+  L.counts = take((size_t)n * 4);
+  L.offsets = take((size_t)(n + 1) * 4);
+  L.block_sums = take(n_blocks * 4);
+  L.ids = take((size_t)max_valid * 4);
+  L.sigma_feat = take((size_t)max_valid * 4);
+  L.sigma = take((size_t)max_valid * 4);
+  L.weight = take((size_t)max_valid * 4);
+  L.acc = take((size_t)n * 4);
+  L.depth = take((size_t)n * 4);
+  L.app_counts = take((size_t)n * 4);
+  L.app_offsets = take((size_t)(n + 1) * 4);
+  L.app_index = take((size_t)max_app * 4);
+  L.app_feat = take((size_t)max_app * L.feat_stride * 4);
+  L.app_rgb = take((size_t)max_app * 3 * 4);
+  L.total = off;
+  return L;
+}
+
+GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
+  GnrSampleParams p;
+  memset(&p, 0, sizeof(p));
+  for (int a = 0; a < 3; ++a) {
+    p.lo[a] = m->cfg.aabb[a];
+    p.hi[a] = m->cfg.aabb[3 + a];
+    p.inv[a] = m->cfg.inv_aabb_size[a];
+    p.a_lo[a] = m->a_lo[a];
+    p.a_inv[a] = m->a_inv[a];
+  }
+  p.near_t = m->cfg.near_t;
+  p.far_t = m->cfg.far_t;
+  p.step = m->cfg.step_size;
+  p.a_thres = m->cfg.alpha_filter_thres;
+  p.aD = m->aD;
+  p.aH = m->aH;
+  p.aW = m->aW;
+  p.has_mask = m->alpha_bits != nullptr;
+  p.a_bits = m->alpha_bits;
+  p.S = S;
+  p.words = (S + 31) / 32;
+  p.kbits = gnr_sample_bits(S);
+  return p;
+}
+
+int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int64_t max_app, const void* ws,
+                    size_t ws_bytes) {
+  if (!m) {
+    gnr_set_error("null model");
+    return -1;
+  }
+  if (n < 0 || S < 1 || max_valid < 0 || max_app < 0) {
+    gnr_set_error("bad chunk arguments: n_rays %lld n_samples %d max_valid %lld max_app %lld", (long long)n, S,
+                  (long long)max_valid, (long long)max_app);
+    return -1;
+  }
+  const int kbits = gnr_sample_bits(S);
+  if (kbits > 20 || n > ((int64_t)1 << (32 - kbits))) {
+    gnr_set_error("chunk of %lld rays x %d samples does not fit the 32-bit sample ids (max %lld rays at this sample count)",
+                  (long long)n, S, (long long)((int64_t)1 << (32 - kbits)));
+    return -1;
+  }
+  if (n * (int64_t)S > 0x7fffffffLL || max_valid > 0x7fffffffLL || max_app > 0x7fffffffLL) {
+    gnr_set_error("chunk too large: n_rays * n_samples and the capacities must stay below 2^31");
+    return -1;
+  }
+  for (int i = 0; i < m->cfg.n_pairs; ++i) {
+    if (!m->den[i].plane || !m->den[i].line || !m->app[i].plane || !m->app[i].line) {
+      gnr_set_error("plane/line pair %d has not been uploaded", i);
+      return -1;
+    }
+  }
+  if (!m->mlp.w1t) {
+    gnr_set_error("MLP weights have not been uploaded");
+    return -1;
+  }
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  if (!ws || ws_bytes < L.total) {
+    gnr_set_error("workspace too small: have %zu bytes, need %zu", ws_bytes, L.total);
+    return -1;
+  }
+  if (((uintptr_t)ws & 255) != 0) {
+    gnr_set_error("workspace must be 256-byte aligned");
+    return -1;
+  }
+  return 0;
+}
+
+extern "C" int gnr_workspace_bytes(const GnrModel* m, int64_t n_rays, int n_samples, int64_t max_valid, int64_t max_app,
+                                   size_t* bytes_h) {
+  if (!m || !bytes_h || n_rays < 0 || n_samples < 1 || max_valid < 0 || max_app < 0) {
+    gnr_set_error("gnr_workspace_bytes: bad argument");
+    return -1;
+  }
+  *bytes_h = gnr_ws_layout(m, n_rays, n_samples, max_valid, max_app).total;
+  return 0;
+}
+
+extern "C" int gnr_read_status(const void* workspace, int32_t* status_h, void* stream) {
+  if (!workspace || !status_h) {
+    gnr_set_error("gnr_read_status: null argument");
+    return -1;
+  }
+  GNR_CUDA_OK(cudaMemcpyAsync(status_h, workspace, GNR_ST_WORDS * sizeof(int32_t), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  GNR_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// stages
+// ---------------------------------------------------------------------------------------------
+#define GNR_LAUNCH_OK(call)                                                                  \
+  do {                                                                                       \
+    int _e = (call);                                                                         \
+    if (_e > 0) {                                                                            \
+      gnr_set_error("%s: %s", #call, cudaGetErrorString((cudaError_t)_e));                   \
+      return -2;                                                                             \
+    }                                                                                        \
+    if (_e < 0) return _e;                                                                   \
+  } while (0)
+
+static int copy_out(void* dst, const void* src, size_t bytes, cudaStream_t st) {
+  if (!dst || bytes == 0) return 0;
+  GNR_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
+static int run_appearance(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
+                          int64_t max_valid, int64_t max_app, cudaStream_t st) {
+  GNR_LAUNCH_OK(launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
+  if (m->cfg.mlp_mode == 0) {
+    GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
+  } else {
+    GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, st));
+  }
+  return 0;
+}
+
+extern "C" int gnr_sample(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                          int64_t max_valid, float* t_min, int32_t* counts, int32_t* offsets, uint32_t* mask_words,
+                          uint32_t* ids, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, 0, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays && n > 0) {
+    gnr_set_error("gnr_sample: null rays");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, 0);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_CUDA_OK(cudaMemsetAsync(ws + L.status, 0, GNR_ST_WORDS * sizeof(int32_t), st));
+  GNR_LAUNCH_OK(launch_sample(m, p, rays, n, ws, L, max_valid, st));
+  if (copy_out(t_min, ws + L.t_min, (size_t)n * 4, st)) return -2;
+  if (copy_out(counts, ws + L.counts, (size_t)n * 4, st)) return -2;
+  if (copy_out(offsets, ws + L.offsets, (size_t)(n + 1) * 4, st)) return -2;
+  if (copy_out(mask_words, ws + L.words, (size_t)n * p.words * 4, st)) return -2;
+  if (copy_out(ids, ws + L.ids, (size_t)max_valid * 4, st)) return -2;
+  return 0;
+}
+
+extern "C" int gnr_density(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                           int64_t max_valid, float* sigma_feature, float* sigma, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, 0, workspace, ws_bytes);
+  if (rc) return rc;
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, 0);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
+  if (copy_out(sigma_feature, ws + L.sigma_feat, (size_t)max_valid * 4, st)) return -2;
+  if (copy_out(sigma, ws + L.sigma, (size_t)max_valid * 4, st)) return -2;
+  return 0;
+}
+
+extern "C" int gnr_weights(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                           int64_t max_valid, int64_t max_app, float* weights, float* acc, float* depth,
+                           int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream) {
+  (void)rays;
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_weights(m, p, n, ws, L, max_valid, max_app, st));
+  if (copy_out(weights, ws + L.weight, (size_t)max_valid * 4, st)) return -2;
+  if (copy_out(acc, ws + L.acc, (size_t)n * 4, st)) return -2;
+  if (copy_out(depth, ws + L.depth, (size_t)n * 4, st)) return -2;
+  if (copy_out(app_counts, ws + L.app_counts, (size_t)n * 4, st)) return -2;
+  if (copy_out(app_offsets, ws + L.app_offsets, (size_t)(n + 1) * 4, st)) return -2;
+  if (copy_out(app_index, ws + L.app_index, (size_t)max_app * 4, st)) return -2;
+  return 0;
+}
+
+extern "C" int gnr_appearance(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                              int64_t max_valid, int64_t max_app, float* app_features, float* rgb, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  rc = run_appearance(m, p, rays, n, ws, L, max_valid, max_app, st);
+  if (rc) return rc;
+  if (app_features) {
+    GNR_CUDA_OK(cudaMemcpy2DAsync(app_features, (size_t)m->cfg.app_dim * 4, ws + L.app_feat, (size_t)L.feat_stride * 4,
+                                  (size_t)m->cfg.app_dim * 4, (size_t)max_app, cudaMemcpyDeviceToDevice, st));
+  }
+  if (copy_out(rgb, ws + L.app_rgb, (size_t)max_app * 12, st)) return -2;
+  return 0;
+}
+
+extern "C" int gnr_composite(GnrModel* m, int64_t n, int white_bg, void* workspace, size_t ws_bytes, int64_t max_valid,
+                             int64_t max_app, int S, float* rgb_map, float* depth_map, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  DeviceGuard g(m->device);
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GNR_LAUNCH_OK(launch_composite(m, n, white_bg, ws, L, rgb_map, depth_map, (cudaStream_t)stream));
+  return 0;
+}
+
+static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, int white_bg, char* ws,
+                             int64_t max_valid, int64_t max_app, float* rgb_map, float* depth_map, cudaStream_t st) {
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_CUDA_OK(cudaMemsetAsync(ws + L.status, 0, GNR_ST_WORDS * sizeof(int32_t), st));
+  GNR_LAUNCH_OK(launch_sample(m, p, rays, n, ws, L, max_valid, st));
+  GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
+  GNR_LAUNCH_OK(launch_weights(m, p, n, ws, L, max_valid, max_app, st));
+  int rc = run_appearance(m, p, rays, n, ws, L, max_valid, max_app, st);
+  if (rc) return rc;
+  GNR_LAUNCH_OK(launch_composite(m, n, white_bg, ws, L, rgb_map, depth_map, st));
+  return 0;
+}
+
+extern "C" int gnr_render_chunk(GnrModel* m, const float* rays, int64_t n, int S, int white_bg, void* workspace,
+                                size_t ws_bytes, int64_t max_valid, int64_t max_app, float* rgb_map, float* depth_map,
+                                void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!rays) {
+    gnr_set_error("gnr_render_chunk: null rays");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  return render_chunk_impl(m, rays, n, S, white_bg, (char*)workspace, max_valid, max_app, rgb_map, depth_map,
+                           (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-buffer forward: two chunks in flight on two streams so that the copies of one chunk
+// overlap the kernels of the other.
+// ---------------------------------------------------------------------------------------------
+extern "C" int gnr_render_host(GnrModel* m, const float* rays_h, int64_t n_rays, int S, int white_bg, int64_t chunk,
+                               int64_t max_valid, int64_t max_app, float* rgb_h, float* depth_h, int32_t* status_h) {
+  if (!m || !rays_h || n_rays < 0 || chunk < 1 || (!rgb_h && !depth_h)) {
+    gnr_set_error("gnr_render_host: bad argument");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  if (chunk > n_rays && n_rays > 0) chunk = n_rays;
+  GnrWs L = gnr_ws_layout(m, chunk, S, max_valid, max_app);
+  const size_t ws_one = align_up(L.total, 256);
+  if (m->host_chunk != chunk || m->host_ws_bytes < 2 * ws_one) {
+    cudaDeviceSynchronize();
+    free_dev(m->host_ws);
+    free_dev(m->host_rays);
+    free_dev(m->host_rgb);
+    free_dev(m->host_depth);
+    m->host_ws = nullptr;
+    m->host_rays = m->host_rgb = m->host_depth = nullptr;
+    m->host_ws_bytes = 0;
+    m->host_chunk = 0;
+    GNR_CUDA_OK(cudaMalloc(&m->host_ws, 2 * ws_one));
+    GNR_CUDA_OK(cudaMalloc(&m->host_rays, 2 * (size_t)chunk * 6 * 4));
+    GNR_CUDA_OK(cudaMalloc(&m->host_rgb, 2 * (size_t)chunk * 3 * 4));
+    GNR_CUDA_OK(cudaMalloc(&m->host_depth, 2 * (size_t)chunk * 4));
+    m->host_ws_bytes = 2 * ws_one;
+    m->host_chunk = chunk;
+  }
+  for (int i = 0; i < 2; ++i) {
+    if (!m->host_streams[i]) GNR_CUDA_OK(cudaStreamCreateWithFlags(&m->host_streams[i], cudaStreamNonBlocking));
+  }
+  int rc = gnr_check_chunk(m, chunk, S, max_valid, max_app, m->host_ws, ws_one);
+  if (rc) return rc;
+  const int64_t n_chunks = (n_rays + chunk - 1) / chunk;
+  if (n_chunks > m->host_status_slots) {
+    if (m->host_status) cudaFreeHost(m->host_status);
+    m->host_status = nullptr;
+    m->host_status_slots = 0;
+    GNR_CUDA_OK(cudaMallocHost(&m->host_status, (size_t)n_chunks * GNR_ST_WORDS * sizeof(int32_t)));
+    m->host_status_slots = n_chunks;
+  }
+  int32_t* st_all = m->host_status;  // pinned, so the status copies stay asynchronous
+  for (int64_t c = 0; c < n_chunks; ++c) {
+    const int b = (int)(c & 1);
+    cudaStream_t st = m->host_streams[b];
+    const int64_t first = c * chunk, n = (first + chunk <= n_rays) ? chunk : n_rays - first;
+    char* ws = (char*)m->host_ws + b * ws_one;
+    float* d_rays = m->host_rays + (size_t)b * chunk * 6;
+    float* d_rgb = m->host_rgb + (size_t)b * chunk * 3;
+    float* d_depth = m->host_depth + (size_t)b * chunk;
+    GNR_CUDA_OK(cudaMemcpyAsync(d_rays, rays_h + first * 6, (size_t)n * 24, cudaMemcpyHostToDevice, st));
+    rc = render_chunk_impl(m, d_rays, n, S, white_bg, ws, max_valid, max_app, d_rgb, d_depth, st);
+    if (rc) return rc;
+    if (rgb_h) GNR_CUDA_OK(cudaMemcpyAsync(rgb_h + first * 3, d_rgb, (size_t)n * 12, cudaMemcpyDeviceToHost, st));
+    if (depth_h) GNR_CUDA_OK(cudaMemcpyAsync(depth_h + first, d_depth, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    GNR_CUDA_OK(cudaMemcpyAsync(&st_all[(size_t)c * GNR_ST_WORDS], ws, GNR_ST_WORDS * 4, cudaMemcpyDeviceToHost, st));
+  }
+  GNR_CUDA_OK(cudaStreamSynchronize(m->host_streams[0]));
+  GNR_CUDA_OK(cudaStreamSynchronize(m->host_streams[1]));
+  if (status_h) {
+    for (int i = 0; i < GNR_ST_WORDS; ++i) status_h[i] = 0;
+    for (int64_t c = 0; c < n_chunks; ++c) {
+      const int32_t* s = &st_all[(size_t)c * GNR_ST_WORDS];
+      status_h[GNR_ST_OVERFLOW_VALID] |= s[GNR_ST_OVERFLOW_VALID];
+      status_h[GNR_ST_OVERFLOW_APP] |= s[GNR_ST_OVERFLOW_APP];
+      status_h[GNR_ST_WAIT_EXPIRED] |= s[GNR_ST_WAIT_EXPIRED];
+      // totals saturate instead of wrapping
+      long long v = (long long)status_h[GNR_ST_NUM_VALID] + s[GNR_ST_NUM_VALID];
+      long long a = (long long)status_h[GNR_ST_NUM_APP] + s[GNR_ST_NUM_APP];
+      status_h[GNR_ST_NUM_VALID] = v > 0x7fffffffLL ? 0x7fffffff : (int32_t)v;
+      status_h[GNR_ST_NUM_APP] = a > 0x7fffffffLL ? 0x7fffffff : (int32_t)a;
+    }
+  }
+  return 0;
+}

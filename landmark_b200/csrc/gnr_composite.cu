@@ -1,0 +1,174 @@
+// Transmittance / weights (raw2alpha), appearance-sample compaction, final compositing.
+//
+// raw2alpha (app/tools/utils.py:51-64): alpha = 1 - exp(-sigma * dist),
+// T = cumprod([1, 1 - alpha + 1e-10]), w = alpha * T[:-1].  Samples that failed the validity
+// test have sigma = 0, hence alpha = 0 and a factor of exactly 1.0f, so the product over a
+// ray's compacted samples equals the product over all of its samples.  One warp walks one
+// ray's segment of the compacted list, 32 samples per step, with a warp multiply-scan and a
+// running carry.  Once the carry is <= the appearance threshold no later sample can satisfy
+// w > threshold (w <= T), which is the early termination of the appearance work.
+#include "gnr_internal.cuh"
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float* __restrict__ t_min_arr,
+               const uint32_t* __restrict__ ids, const float* __restrict__ sigma, const int32_t* __restrict__ offsets,
+               int64_t n_rays, long long capacity, float* __restrict__ weight, float* __restrict__ acc_out,
+               float* __restrict__ depth_out, int32_t* __restrict__ app_counts) {
+  const int lane = threadIdx.x & 31;
+  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+  float acc = 0.0f, dep = 0.0f;
+  int n_app = 0;
+  if (beg < end) {
+    const float t_min = t_min_arr[ray];
+    const uint32_t kmask = (1u << p.kbits) - 1u;
+    float carry = 1.0f;  // transmittance before the first sample of this step
+    for (long long base = beg; base < end; base += 32) {
+      const long long i = base + lane;
+      const bool active = i < end;
+      float alpha = 0.0f, f = 1.0f, t = 0.0f;
+      if (active) {
+        const int k = (int)(__ldg(ids + i) & kmask);
+        t = gnr_sample_t(t_min, p.step, k);
+        // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
+        const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(t_min, p.step, k + 1), t);
+        const float x = __fmul_rn(-__ldg(sigma + i), __fmul_rn(dist, distance_scale));
+        alpha = __fsub_rn(1.0f, expf(x));
+        f = __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
+      }
+      // inclusive multiply-scan of the factors
+      float incl = f;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl *= up;
+      }
+      float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+      if (lane == 0) excl = 1.0f;
+      const float T = carry * excl;
+      const float w = alpha * T;
+      if (active) {
+        weight[i] = w;
+        acc += w;
+        dep = fmaf(w, t, dep);
+      }
+      n_app += __popc(__ballot_sync(0xffffffffu, active && (w > thres)));
+      carry *= __shfl_sync(0xffffffffu, incl, 31);
+    }
+    acc = warp_sum(acc);
+    dep = warp_sum(dep);
+  }
+  if (lane == 0) {
+    acc_out[ray] = acc;
+    depth_out[ray] = dep;
+    app_counts[ray] = n_app;
+  }
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+expand_app_kernel(const float* __restrict__ weight, float thres, const int32_t* __restrict__ offsets,
+                  const int32_t* __restrict__ app_offsets, int64_t n_rays, long long capacity, long long app_capacity,
+                  int32_t* __restrict__ app_index) {
+  const int lane = threadIdx.x & 31;
+  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  long long pos = app_offsets[ray], pend = app_offsets[ray + 1];
+  if (pos == pend) return;
+  long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+  for (long long base = beg; base < end && pos < pend; base += 32) {
+    const long long i = base + lane;
+    const bool flag = (i < end) && (__ldg(weight + i) > thres);
+    const uint32_t bits = __ballot_sync(0xffffffffu, flag);
+    if (flag) {
+      const long long at = pos + __popc(bits & ((1u << lane) - 1u));
+      if (at < app_capacity) app_index[at] = (int32_t)i;
+    }
+    pos += __popc(bits);
+  }
+}
+
+// rgb_map = sum_j w_j rgb_j (+ 1 - acc), clamp to [0,1]; depth_map = sum w t
+// (app/models/gridnerf_sequential.py:493-501)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ app_offsets,
+                 const int32_t* __restrict__ app_index, const float* __restrict__ app_rgb, const float* __restrict__ acc,
+                 const float* __restrict__ depth, int64_t n_rays, long long app_capacity, int white_bg,
+                 float* __restrict__ rgb_map, float* __restrict__ depth_map) {
+  const int lane = threadIdx.x & 31;
+  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  long long beg = app_offsets[ray], end = min((long long)app_offsets[ray + 1], app_capacity);
+  float r = 0.0f, g = 0.0f, b = 0.0f;
+  for (long long j = beg + lane; j < end; j += 32) {
+    const float w = __ldg(weight + __ldg(app_index + j));
+    const float* c = app_rgb + (size_t)j * 3;
+    r = fmaf(w, __ldg(c + 0), r);
+    g = fmaf(w, __ldg(c + 1), g);
+    b = fmaf(w, __ldg(c + 2), b);
+  }
+  if (beg < end) {
+    r = warp_sum(r);
+    g = warp_sum(g);
+    b = warp_sum(b);
+  }
+  if (lane == 0) {
+    if (rgb_map) {
+      const float bg = white_bg ? (1.0f - acc[ray]) : 0.0f;
+      rgb_map[ray * 3 + 0] = fminf(fmaxf(r + bg, 0.0f), 1.0f);
+      rgb_map[ray * 3 + 1] = fminf(fmaxf(g + bg, 0.0f), 1.0f);
+      rgb_map[ray * 3 + 2] = fminf(fmaxf(b + bg, 0.0f), 1.0f);
+    }
+    if (depth_map) depth_map[ray] = depth[ray];
+  }
+}
+
+}  // namespace
+
+int launch_weights(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                   int64_t max_valid, int64_t max_app, cudaStream_t st) {
+  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const float* t_min = (const float*)(ws + L.t_min);
+  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
+  const float* sigma = (const float*)(ws + L.sigma);
+  const int32_t* offsets = (const int32_t*)(ws + L.offsets);
+  float* weight = (float*)(ws + L.weight);
+  float* acc = (float*)(ws + L.acc);
+  float* depth = (float*)(ws + L.depth);
+  int32_t* app_counts = (int32_t*)(ws + L.app_counts);
+  int32_t* app_offsets = (int32_t*)(ws + L.app_offsets);
+  int32_t* app_index = (int32_t*)(ws + L.app_index);
+  int32_t* block_sums = (int32_t*)(ws + L.block_sums);
+  int32_t* status = (int32_t*)(ws + L.status);
+  weights_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, m->cfg.distance_scale, m->cfg.ray_weight_thres, t_min, ids,
+                                                        sigma, offsets, n, (long long)max_valid, weight, acc, depth,
+                                                        app_counts);
+  int e = launch_exclusive_scan(app_counts, app_offsets, block_sums, n, status, GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP,
+                                max_app, st);
+  if (e) return e;
+  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(weight, m->cfg.ray_weight_thres, offsets, app_offsets, n,
+                                                           (long long)max_valid, (long long)max_app, app_index);
+  return (int)cudaGetLastError();
+}
+
+int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
+                     float* depth_map, cudaStream_t st) {
+  (void)m;
+  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  long long app_capacity = L.max_app;
+  composite_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+      (const float*)(ws + L.weight), (const int32_t*)(ws + L.app_offsets), (const int32_t*)(ws + L.app_index),
+      (const float*)(ws + L.app_rgb), (const float*)(ws + L.acc), (const float*)(ws + L.depth), n, app_capacity,
+      white_bg, rgb_map, depth_map);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,255 @@
+// VM feature gather: bilinear plane x linear line, channel-last, 128-bit loads.
+//
+// Four lanes share one sample; lane c4 owns channels {16 j + 4 c4 .. +3 : j < J}, so one load
+// instruction of a warp reads 8 samples x 64 contiguous bytes.  Interpolation follows
+// F.grid_sample(mode="bilinear", padding_mode="zeros", align_corners=True) as called by
+// compute_densityfeature / compute_appfeature (app/models/gridnerf_sequential.py:779-871):
+// index = ((x + 1) / 2) * (size - 1); the weight of a corner is the product of the distances
+// to the opposite corner; taps outside the grid contribute zero.
+#include "gnr_internal.cuh"
+
+namespace {
+
+constexpr int kBlock = 256;
+constexpr int kFeat = 28;  // accumulators per sample for the basis projection (app_dim <= 28)
+
+struct PlaneSet {
+  GnrPlane p[GNR_MAX_PLANES];
+  int n;
+};
+
+__device__ __forceinline__ float pick(float x, float y, float z, int a) { return a == 0 ? x : (a == 1 ? y : z); }
+
+__device__ __forceinline__ float4 f4_scale(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float4 f4_fma(float4 a, float s, float4 c) {
+  return make_float4(fmaf(a.x, s, c.x), fmaf(a.y, s, c.y), fmaf(a.z, s, c.z), fmaf(a.w, s, c.w));
+}
+__device__ __forceinline__ float4 f4_mul(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+
+// Products plane(x, y) * line(l) for the 4 J channels this lane owns.
+template <int J>
+__device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float y, float z, int c4, float4 (&prod)[J]) {
+  const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+  const float ix = (u + 1.0f) * 0.5f * (float)(pl.W - 1);
+  const float iy = (v + 1.0f) * 0.5f * (float)(pl.H - 1);
+  const float il = (l + 1.0f) * 0.5f * (float)(pl.L - 1);
+  const float fx = floorf(ix), fy = floorf(iy), fl = floorf(il);
+  const int x0 = (int)fx, y0 = (int)fy, l0 = (int)fl;
+  const bool x0ok = (unsigned)x0 < (unsigned)pl.W, x1ok = (unsigned)(x0 + 1) < (unsigned)pl.W;
+  const bool y0ok = (unsigned)y0 < (unsigned)pl.H, y1ok = (unsigned)(y0 + 1) < (unsigned)pl.H;
+  const bool l0ok = (unsigned)l0 < (unsigned)pl.L, l1ok = (unsigned)(l0 + 1) < (unsigned)pl.L;
+  const float ax1 = ix - fx, ax0 = (fx + 1.0f) - ix;
+  const float ay1 = iy - fy, ay0 = (fy + 1.0f) - iy;
+  const float w_nw = (x0ok && y0ok) ? ax0 * ay0 : 0.0f, w_ne = (x1ok && y0ok) ? ax1 * ay0 : 0.0f;
+  const float w_sw = (x0ok && y1ok) ? ax0 * ay1 : 0.0f, w_se = (x1ok && y1ok) ? ax1 * ay1 : 0.0f;
+  const float w_l0 = l0ok ? (fl + 1.0f) - il : 0.0f, w_l1 = l1ok ? il - fl : 0.0f;
+  const int xc0 = min(max(x0, 0), pl.W - 1), xc1 = min(max(x0 + 1, 0), pl.W - 1);
+  const int yc0 = min(max(y0, 0), pl.H - 1), yc1 = min(max(y0 + 1, 0), pl.H - 1);
+  const int lc0 = min(max(l0, 0), pl.L - 1), lc1 = min(max(l0 + 1, 0), pl.L - 1);
+  const int c4n = pl.C >> 2;
+  const float4* pb = reinterpret_cast<const float4*>(pl.plane);
+  const float4* lb = reinterpret_cast<const float4*>(pl.line);
+  const size_t nw = ((size_t)yc0 * pl.W + xc0) * c4n, ne = ((size_t)yc0 * pl.W + xc1) * c4n;
+  const size_t sw = ((size_t)yc1 * pl.W + xc0) * c4n, se = ((size_t)yc1 * pl.W + xc1) * c4n;
+  float4 v_nw[J], v_ne[J], v_sw[J], v_se[J], v_l0[J], v_l1[J];
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    const int q = j * 4 + c4;
+    v_nw[j] = __ldg(pb + nw + q);
+    v_ne[j] = __ldg(pb + ne + q);
+    v_sw[j] = __ldg(pb + sw + q);
+    v_se[j] = __ldg(pb + se + q);
+    v_l0[j] = __ldg(lb + (size_t)lc0 * c4n + q);
+    v_l1[j] = __ldg(lb + (size_t)lc1 * c4n + q);
+  }
+#pragma unroll
+  for (int j = 0; j < J; ++j) {
+    float4 pv = f4_scale(v_nw[j], w_nw);
+    pv = f4_fma(v_ne[j], w_ne, pv);
+    pv = f4_fma(v_sw[j], w_sw, pv);
+    pv = f4_fma(v_se[j], w_se, pv);
+    float4 lv = f4_fma(v_l1[j], w_l1, f4_scale(v_l0[j], w_l0));
+    prod[j] = f4_mul(pv, lv);
+  }
+}
+
+// Position of one compacted sample, recomputed exactly as the sampler computed it, then
+// normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
+__device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const float* __restrict__ rays,
+                                           const float* __restrict__ t_min, uint32_t id, float& x, float& y, float& z) {
+  const uint32_t ray = id >> p.kbits;
+  const int k = (int)(id & ((1u << p.kbits) - 1u));
+  const float* r = rays + (size_t)ray * 6;
+  const float t = gnr_sample_t(__ldg(t_min + ray), p.step, k);
+  x = gnr_normalize(gnr_point(__ldg(r + 0), __ldg(r + 3), t), p.lo[0], p.inv[0]);
+  y = gnr_normalize(gnr_point(__ldg(r + 1), __ldg(r + 4), t), p.lo[1], p.inv[1]);
+  z = gnr_normalize(gnr_point(__ldg(r + 2), __ldg(r + 5), t), p.lo[2], p.inv[2]);
+}
+
+__device__ __forceinline__ float density_activation(float f, float shift, int act) {
+  if (act == 1) return fmaxf(f, 0.0f);
+  const float x = f + shift;  // F.softplus: beta 1, threshold 20
+  return x > 20.0f ? x : log1pf(expf(x));
+}
+
+template <int J>
+__global__ void __launch_bounds__(kBlock)
+density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
+               const uint32_t* __restrict__ ids, const int32_t* __restrict__ total_ptr, long long capacity,
+               float shift, int act, float* __restrict__ sigma_feat, float* __restrict__ sigma) {
+  const int c4 = threadIdx.x & 3;
+  long long total = min((long long)*total_ptr, capacity);
+  const long long stride = (long long)gridDim.x * (kBlock / 4);
+  // whole warps iterate together so that the quad shuffles below are always convergent
+  for (long long base = (long long)blockIdx.x * (kBlock / 4) + (threadIdx.x >> 5) * 8; base < total; base += stride) {
+    const long long i = base + ((threadIdx.x & 31) >> 2);
+    const bool active = i < total;
+    float acc = 0.0f;
+    if (active) {
+      float x, y, z;
+      sample_xyz(p, rays, t_min, __ldg(ids + i), x, y, z);
+      for (int pi = 0; pi < planes.n; ++pi) {
+        float4 prod[J];
+        pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
+        acc += s;
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    if (active && c4 == 0) {
+      sigma_feat[i] = acc;
+      sigma[i] = density_activation(acc, shift, act);
+    }
+  }
+}
+
+// Appearance gather + basis projection.  The basis weights sit in shared memory, blocked per
+// (pair, lane-in-quad): row t = 4 j + e of block (pair, c4) holds the `app_dim` weights of
+// channel 16 j + 4 c4 + e of that pair, padded to kFeat floats; blocks are padded by 8 floats
+// so that the four lanes of a quad read disjoint banks.
+template <int J>
+__global__ void __launch_bounds__(kBlock)
+app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
+                  const uint32_t* __restrict__ ids, const int32_t* __restrict__ app_index,
+                  const int32_t* __restrict__ total_ptr, long long capacity, const float* __restrict__ basis_blocked,
+                  int feat_stride, float* __restrict__ feat_out) {
+  extern __shared__ float4 smem_f4[];
+  float* wsm = reinterpret_cast<float*>(smem_f4);
+  constexpr int kBlk = 4 * J * kFeat + 8;
+  const int n_w = planes.n * 4 * kBlk;
+  for (int i = threadIdx.x; i < n_w; i += kBlock) wsm[i] = basis_blocked[i];
+  __syncthreads();
+
+  const int c4 = threadIdx.x & 3;
+  long long total = min((long long)*total_ptr, capacity);
+  const long long stride = (long long)gridDim.x * (kBlock / 4);
+  for (long long base = (long long)blockIdx.x * (kBlock / 4) + (threadIdx.x >> 5) * 8; base < total; base += stride) {
+    const long long j_app = base + ((threadIdx.x & 31) >> 2);
+    const bool active = j_app < total;
+    float acc[kFeat];
+#pragma unroll
+    for (int o = 0; o < kFeat; ++o) acc[o] = 0.0f;
+    if (active) {
+      float x, y, z;
+      sample_xyz(p, rays, t_min, __ldg(ids + __ldg(app_index + j_app)), x, y, z);
+      for (int pi = 0; pi < planes.n; ++pi) {
+        float4 prod[J];
+        pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+        const float* wb = wsm + (pi * 4 + c4) * kBlk;
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+          const float pv[4] = {prod[j].x, prod[j].y, prod[j].z, prod[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float4* wrow = reinterpret_cast<const float4*>(wb + (j * 4 + e) * kFeat);
+#pragma unroll
+            for (int q = 0; q < kFeat / 4; ++q) {
+              const float4 w = wrow[q];
+              acc[4 * q + 0] = fmaf(pv[e], w.x, acc[4 * q + 0]);
+              acc[4 * q + 1] = fmaf(pv[e], w.y, acc[4 * q + 1]);
+              acc[4 * q + 2] = fmaf(pv[e], w.z, acc[4 * q + 2]);
+              acc[4 * q + 3] = fmaf(pv[e], w.w, acc[4 * q + 3]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int o = 0; o < kFeat; ++o) {
+      acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], 1);
+      acc[o] += __shfl_xor_sync(0xffffffffu, acc[o], 2);
+    }
+    if (active && c4 == 0) {
+      float4* out = reinterpret_cast<float4*>(feat_out + (size_t)j_app * feat_stride);
+#pragma unroll
+      for (int q = 0; q < kFeat / 4; ++q)
+        if (4 * q < feat_stride) out[q] = make_float4(acc[4 * q], acc[4 * q + 1], acc[4 * q + 2], acc[4 * q + 3]);
+    }
+  }
+}
+
+PlaneSet make_set(const GnrPlane* src, int n) {
+  PlaneSet s;
+  s.n = n;
+  for (int i = 0; i < n; ++i) s.p[i] = src[i];
+  return s;
+}
+
+}  // namespace
+
+int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                   const GnrWs& L, int64_t max_valid, cudaStream_t st) {
+  (void)n;
+  PlaneSet set = make_set(m->den, m->cfg.n_pairs);
+  const int J = m->den[0].C / 16;
+  const int grid = m->sm_count * 8;
+  const float* t_min = (const float*)(ws + L.t_min);
+  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
+  const int32_t* total = (const int32_t*)(ws + L.offsets) + n;
+  float* sf = (float*)(ws + L.sigma_feat);
+  float* sg = (float*)(ws + L.sigma);
+#define GNR_DEN(JJ)                                                                                          \
+  density_kernel<JJ><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,         \
+                                              m->cfg.density_shift, m->cfg.density_act, sf, sg)
+  switch (J) {
+    case 1: GNR_DEN(1); break;
+    case 2: GNR_DEN(2); break;
+    case 3: GNR_DEN(3); break;
+    case 4: GNR_DEN(4); break;
+    default: gnr_set_error("density channels (padded) %d not supported (16..64)", m->den[0].C); return -1;
+  }
+#undef GNR_DEN
+  return (int)cudaGetLastError();
+}
+
+int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                      const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st) {
+  (void)max_valid;
+  PlaneSet set = make_set(m->app, m->cfg.n_pairs);
+  const int J = m->app[0].C / 16;
+  const int grid = m->sm_count * 4;
+  const float* t_min = (const float*)(ws + L.t_min);
+  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
+  const int32_t* app_index = (const int32_t*)(ws + L.app_index);
+  const int32_t* total = (const int32_t*)(ws + L.app_offsets) + n;
+  float* feat = (float*)(ws + L.app_feat);
+  size_t smem = (size_t)m->cfg.n_pairs * 4 * (4 * J * kFeat + 8) * sizeof(float);
+#define GNR_APP(JJ)                                                                                            \
+  do {                                                                                                         \
+    cudaFuncSetAttribute(app_gather_kernel<JJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    app_gather_kernel<JJ><<<grid, kBlock, smem, st>>>(p, set, rays, t_min, ids, app_index, total,              \
+                                                      (long long)max_app, m->mlp.basis_blocked, L.feat_stride, feat); \
+  } while (0)
+  switch (J) {
+    case 1: GNR_APP(1); break;
+    case 2: GNR_APP(2); break;
+    case 3: GNR_APP(3); break;
+    case 4: GNR_APP(4); break;
+    default: gnr_set_error("appearance channels (padded) %d not supported (16..64)", m->app[0].C); return -1;
+  }
+#undef GNR_APP
+  return (int)cudaGetLastError();
+}

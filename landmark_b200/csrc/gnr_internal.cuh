@@ -1,0 +1,133 @@
+// Internal declarations shared by the translation units of libgridnerf_b200.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "gridnerf_b200.h"
+
+#define GNR_MAX_PLANES 9
+#define GNR_SM_COUNT_FALLBACK 148
+
+// One plane/line pair in device layout: plane [H][W][C] channel-last, line [L][C];
+// C is the padded channel count (multiple of 16, extra channels are zero).
+struct GnrPlane {
+  const float* plane;
+  const float* line;
+  int H, W, L, C;
+  int mat0, mat1, vec;  // coordinate axes: plane x <- xyz[mat0], plane y <- xyz[mat1], line <- xyz[vec]
+};
+
+struct GnrMlp {
+  // fp32 images for the CUDA-core kernels
+  float* basis_blocked;  // [4 lanes][36(+pad)][28] blocked basis weights for the gather kernel
+  float* w1t;            // [K1p][hidden]  (transposed, K padded)
+  float* w2t;            // [hidden][hidden]
+  float* w3;             // [3][hidden]
+  float* b1;             // [hidden] (zeros if no bias)
+  float* b2;
+  float* b3;             // [4]
+  // tensor-core images (pre-tiled, see gnr_mlp_tc.cu)
+  void* tc_image;
+  size_t tc_image_bytes;
+  int in_dim;   // 150
+  int k1_pad;   // in_dim rounded up to 8
+  int n_prod;   // sum of padded appearance channels (144)
+};
+
+struct GnrModel {
+  GnrConfig cfg;
+  int device;
+  int sm_count;
+  GnrPlane den[GNR_MAX_PLANES];
+  GnrPlane app[GNR_MAX_PLANES];
+  float* den_plane_buf[GNR_MAX_PLANES];
+  float* den_line_buf[GNR_MAX_PLANES];
+  float* app_plane_buf[GNR_MAX_PLANES];
+  float* app_line_buf[GNR_MAX_PLANES];
+  // occupancy bits
+  uint32_t* alpha_bits;
+  int aD, aH, aW;
+  float a_lo[3], a_inv[3];
+  GnrMlp mlp;
+  // staging for gnr_render_host
+  void* host_ws;
+  size_t host_ws_bytes;
+  float* host_rays;
+  float* host_rgb;
+  float* host_depth;
+  int64_t host_chunk;
+  int32_t* host_status;  // pinned
+  int64_t host_status_slots;
+  cudaStream_t host_streams[2];
+  cudaEvent_t host_events[2];
+};
+
+// Scalar parameters every sampling-dependent kernel needs (passed by value).
+struct GnrSampleParams {
+  float lo[3], hi[3], inv[3];
+  float near_t, far_t, step;
+  float a_lo[3], a_inv[3];
+  float a_thres;
+  int aD, aH, aW;
+  int has_mask;
+  const uint32_t* a_bits;
+  int S, words, kbits;
+};
+
+// Workspace layout (byte offsets), identical for every stage call with the same arguments.
+struct GnrWs {
+  size_t status, t_min, words, counts, offsets, block_sums, ids, sigma_feat, sigma, weight, acc, depth,
+      app_counts, app_offsets, app_index, app_feat, app_rgb, total;
+  int feat_stride;  // floats per appearance feature row (app_dim rounded up to 4)
+  long long max_valid, max_app;  // capacities of the two compacted lists
+  long long n_rays;
+};
+
+void gnr_set_error(const char* fmt, ...);
+GnrWs gnr_ws_layout(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app);
+GnrSampleParams gnr_sample_params(const GnrModel* m, int S);
+int gnr_check_chunk(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app,
+                    const void* ws, size_t ws_bytes);
+
+// launchers (each enqueues on `st`, returns cudaGetLastError as int)
+int launch_sample(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                  const GnrWs& L, int64_t max_valid, cudaStream_t st);
+int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                   const GnrWs& L, int64_t max_valid, cudaStream_t st);
+int launch_weights(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                   int64_t max_valid, int64_t max_app, cudaStream_t st);
+int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                      const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st);
+int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
+                    int64_t max_app, cudaStream_t st);
+int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
+                  int64_t max_app, cudaStream_t st);
+int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
+                     float* depth_map, cudaStream_t st);
+int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,
+                          int32_t* status, int total_slot, int overflow_slot, int64_t capacity,
+                          cudaStream_t st);
+int gnr_mlp_tc_prepare(GnrModel* m, const float* w1, const float* b1, const float* w2, const float* b2,
+                       const float* w3, const float* b3, cudaStream_t st);
+
+#define GNR_CUDA_OK(expr)                                                              \
+  do {                                                                                 \
+    cudaError_t _e = (expr);                                                           \
+    if (_e != cudaSuccess) {                                                           \
+      gnr_set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+      return -2;                                                                       \
+    }                                                                                  \
+  } while (0)
+
+// ---- device helpers shared by the sampling-dependent kernels ---------------------------------
+// Every operation is individually rounded (no FMA contraction): these reproduce the values
+// torch computes with separate elementwise kernels.
+__device__ __forceinline__ float gnr_sample_t(float t_min, float step, int k) {
+  return __fadd_rn(t_min, __fmul_rn(step, (float)k));
+}
+__device__ __forceinline__ float gnr_point(float o, float d, float t) { return __fadd_rn(o, __fmul_rn(d, t)); }
+__device__ __forceinline__ float gnr_normalize(float p, float lo, float inv) {
+  return __fsub_rn(__fmul_rn(__fsub_rn(p, lo), inv), 1.0f);
+}

@@ -1,0 +1,281 @@
+// Ray generation, sampling + occupancy test, exclusive scan, compaction.
+//
+// Bit-exactness contract of the sampler: the set of valid (ray, sample) pairs equals what
+// the torch renderer selects (sample_ray, app/models/gridnerf_sequential.py:260-281, then the
+// alphaMask filter :460-465 with AlphaGridMask.sample_alpha, app/models/alpha_mask.py:35-59).
+// Every floating-point operation below is therefore a single correctly rounded IEEE
+// operation (__fadd_rn/__fmul_rn/__fdiv_rn are never contracted into FMAs), in the order
+// in which torch's separate elementwise kernels apply them.
+#include "gnr_internal.cuh"
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+// ---------------------------------------------------------------------------------------------
+// ray generation: d = (dir_x[i], dir_y[j], -1) @ R^T, o = c2w[:, 3]
+// (dist_render/dataset/utils.py:57-89)
+// ---------------------------------------------------------------------------------------------
+struct Pose {
+  float m[12];
+};
+
+__global__ void raygen_kernel(Pose pose, const float* __restrict__ dir_x, const float* __restrict__ dir_y,
+                              int W, const int32_t* __restrict__ pixel_ids, int64_t first_pixel, int64_t n,
+                              float* __restrict__ rays) {
+  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  int64_t pix = pixel_ids ? (int64_t)pixel_ids[r] : first_pixel + r;
+  int j = (int)(pix / W), i = (int)(pix - (int64_t)j * W);
+  float dx = dir_x[i], dy = dir_y[j], dz = -1.0f;
+  float* out = rays + r * 6;
+  out[0] = pose.m[3];
+  out[1] = pose.m[7];
+  out[2] = pose.m[11];
+#pragma unroll
+  for (int a = 0; a < 3; ++a)
+    out[3 + a] = fmaf(dz, pose.m[a * 4 + 2], fmaf(dy, pose.m[a * 4 + 1], dx * pose.m[a * 4 + 0]));
+}
+
+// ---------------------------------------------------------------------------------------------
+// sampling: one warp per ray, 32 samples per step, validity bits kept in registers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float px, float py, float pz) {
+  // q = (p - aabb0) * invgridSize - 1 ; index = ((q + 1) / 2) * (size - 1)
+  float ix = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(px, p.a_lo[0], p.a_inv[0]), 1.0f), 0.5f), (float)(p.aW - 1));
+  float iy = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(py, p.a_lo[1], p.a_inv[1]), 1.0f), 0.5f), (float)(p.aH - 1));
+  float iz = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(pz, p.a_lo[2], p.a_inv[2]), 1.0f), 0.5f), (float)(p.aD - 1));
+  float fx0 = floorf(ix), fy0 = floorf(iy), fz0 = floorf(iz);
+  float fx1 = __fadd_rn(fx0, 1.0f), fy1 = __fadd_rn(fy0, 1.0f), fz1 = __fadd_rn(fz0, 1.0f);
+  float wx[2] = {__fsub_rn(fx1, ix), __fsub_rn(ix, fx0)};
+  float wy[2] = {__fsub_rn(fy1, iy), __fsub_rn(iy, fy0)};
+  float wz[2] = {__fsub_rn(fz1, iz), __fsub_rn(iz, fz0)};
+  // corners outside the volume contribute zero (padding_mode="zeros"); indices that do not
+  // fit an int (only possible for samples far outside the mask box) are outside too.
+  bool okx = (ix >= -1.0f) && (ix < (float)p.aW), oky = (iy >= -1.0f) && (iy < (float)p.aH),
+       okz = (iz >= -1.0f) && (iz < (float)p.aD);
+  if (!(okx && oky && okz)) return 0.0f > p.a_thres;
+  int x0 = (int)fx0, y0 = (int)fy0, z0 = (int)fz0;
+  float out = 0.0f;
+#pragma unroll
+  for (int cz = 0; cz < 2; ++cz) {
+#pragma unroll
+    for (int cy = 0; cy < 2; ++cy) {
+#pragma unroll
+      for (int cx = 0; cx < 2; ++cx) {
+        int x = x0 + cx, y = y0 + cy, z = z0 + cz;
+        if ((unsigned)x < (unsigned)p.aW && (unsigned)y < (unsigned)p.aH && (unsigned)z < (unsigned)p.aD) {
+          uint32_t bit = (uint32_t)((z * p.aH + y) * p.aW + x);
+          if ((__ldg(p.a_bits + (bit >> 5)) >> (bit & 31)) & 1u) {
+            float w = __fmul_rn(__fmul_rn(wx[cx], wy[cy]), wz[cz]);
+            out = __fadd_rn(out, w);  // tap is exactly 1, so tap * w == w
+          }
+        }
+      }
+    }
+  }
+  return out > p.a_thres;
+}
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_rays, float* __restrict__ t_min_out,
+                   uint32_t* __restrict__ words_out, int32_t* __restrict__ counts_out) {
+  const int lane = threadIdx.x & 31;
+  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  const float* r = rays + ray * 6;
+  float o[3] = {__ldg(r), __ldg(r + 1), __ldg(r + 2)};
+  float d[3] = {__ldg(r + 3), __ldg(r + 4), __ldg(r + 5)};
+  // slab entry: max over axes of min(rate_a, rate_b), clamped to [near, far]
+  float t_min = -INFINITY;
+#pragma unroll
+  for (int a = 0; a < 3; ++a) {
+    float vec = (d[a] == 0.0f) ? 1e-6f : d[a];
+    float ra = __fdiv_rn(__fsub_rn(p.hi[a], o[a]), vec);
+    float rb = __fdiv_rn(__fsub_rn(p.lo[a], o[a]), vec);
+    t_min = fmaxf(t_min, fminf(ra, rb));
+  }
+  t_min = fminf(fmaxf(t_min, p.near_t), p.far_t);
+  if (lane == 0) t_min_out[ray] = t_min;
+
+  int count = 0;
+  uint32_t* wrow = words_out + ray * p.words;
+  // fl(o + fl(d * fl(t_min + fl(step * k)))) is monotone in k, so once a sample has left the
+  // box through the far side of an axis every later sample is outside as well.
+  bool done = false;
+  for (int base = 0; base < p.words; base += 32) {
+    uint32_t my_word = 0;  // lane w keeps word base + w
+    int nw = min(32, p.words - base);
+    for (int w = 0; w < nw; ++w) {
+      uint32_t bits = 0;
+      if (!done) {
+        int k = (base + w) * 32 + lane;
+        float t = gnr_sample_t(t_min, p.step, k);
+        float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
+        bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
+        bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
+        bool inside = !(lo_out | hi_out) && (k < p.S);
+        bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
+                      ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
+                      ((d[2] > 0.0f) & (pz > p.hi[2])) | ((d[2] < 0.0f) & (p.lo[2] > pz)) |
+                      ((d[0] == 0.0f) & ((p.lo[0] > px) | (px > p.hi[0]))) |
+                      ((d[1] == 0.0f) & ((p.lo[1] > py) | (py > p.hi[1]))) |
+                      ((d[2] == 0.0f) & ((p.lo[2] > pz) | (pz > p.hi[2])));
+        bool valid = inside;
+        if (valid && p.has_mask) valid = occupancy_test(p, px, py, pz);
+        bits = __ballot_sync(0xffffffffu, valid);
+        done = __any_sync(0xffffffffu, exited);
+        count += __popc(bits);
+      }
+      if (lane == w) my_word = bits;
+    }
+    if (lane < nw) wrow[base + lane] = my_word;
+  }
+  if (lane == 0) counts_out[ray] = count;
+}
+
+// ---------------------------------------------------------------------------------------------
+// exclusive scan of int32 (three small kernels, no inter-block waits)
+// ---------------------------------------------------------------------------------------------
+constexpr int kScanBlock = 1024;
+
+__device__ __forceinline__ int block_exclusive_scan(int v, int* total) {
+  __shared__ int warp_sums[32];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[wid] = incl;
+  __syncthreads();
+  if (wid == 0) {
+    int s = warp_sums[lane];
+    int si = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int t = __shfl_up_sync(0xffffffffu, si, o);
+      if (lane >= o) si += t;
+    }
+    warp_sums[lane] = si - s;  // exclusive warp base
+    if (lane == 31) *total = si;
+  }
+  __syncthreads();
+  int res = warp_sums[wid] + incl - v;
+  __syncthreads();
+  return res;
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+scan_local_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out, int32_t* __restrict__ block_sums, int64_t n) {
+  __shared__ int total;
+  int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+  int v = (i < n) ? in[i] : 0;
+  int ex = block_exclusive_scan(v, &total);
+  if (i < n) out[i] = ex;
+  if (threadIdx.x == 0) block_sums[blockIdx.x] = total;
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+scan_sums_kernel(int32_t* __restrict__ block_sums, int n_blocks, int32_t* __restrict__ out_total,
+                 int32_t* __restrict__ status, int total_slot, int overflow_slot, long long capacity) {
+  __shared__ int total;
+  long long carry = 0;
+  for (int base = 0; base < n_blocks; base += kScanBlock) {
+    int i = base + threadIdx.x;
+    int v = (i < n_blocks) ? block_sums[i] : 0;
+    int ex = block_exclusive_scan(v, &total);
+    if (i < n_blocks) block_sums[i] = (int)(carry + ex);
+    carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    *out_total = (int)carry;
+    status[total_slot] = (int)carry;
+    status[overflow_slot] = (carry > capacity) ? 1 : 0;
+  }
+}
+
+__global__ void __launch_bounds__(kScanBlock)
+scan_add_kernel(int32_t* __restrict__ out, const int32_t* __restrict__ block_sums, int64_t n) {
+  int64_t i = (int64_t)blockIdx.x * kScanBlock + threadIdx.x;
+  if (i < n) out[i] += block_sums[blockIdx.x];
+}
+
+// ---------------------------------------------------------------------------------------------
+// compaction: ids[offsets[ray] + rank of sample among the ray's valid ones] = ray << kbits | k
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+expand_ids_kernel(const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, int64_t n_rays, int n_words,
+                  int kbits, long long capacity, uint32_t* __restrict__ ids) {
+  const int lane = threadIdx.x & 31;
+  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  long long pos = offsets[ray];
+  long long end = offsets[ray + 1];
+  if (pos == end) return;
+  const uint32_t* wrow = words + ray * n_words;
+  for (int w = 0; w < n_words && pos < end; ++w) {
+    uint32_t bits = __ldg(wrow + w);
+    if ((bits >> lane) & 1u) {
+      long long at = pos + __popc(bits & ((1u << lane) - 1u));
+      if (at < capacity) ids[at] = ((uint32_t)ray << kbits) | (uint32_t)(w * 32 + lane);
+    }
+    pos += __popc(bits);
+  }
+}
+
+}  // namespace
+
+int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,
+                          int32_t* status, int total_slot, int overflow_slot, int64_t capacity,
+                          cudaStream_t st) {
+  int n_blocks = (int)((n + kScanBlock - 1) / kScanBlock);
+  if (n_blocks < 1) n_blocks = 1;
+  scan_local_kernel<<<n_blocks, kScanBlock, 0, st>>>(counts, offsets, block_sums, n);
+  scan_sums_kernel<<<1, kScanBlock, 0, st>>>(block_sums, n_blocks, offsets + n, status, total_slot, overflow_slot,
+                                             (long long)capacity);
+  scan_add_kernel<<<n_blocks, kScanBlock, 0, st>>>(offsets, block_sums, n);
+  return (int)cudaGetLastError();
+}
+
+int launch_sample(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                  const GnrWs& L, int64_t max_valid, cudaStream_t st) {
+  (void)m;
+  float* t_min = (float*)(ws + L.t_min);
+  uint32_t* words = (uint32_t*)(ws + L.words);
+  int32_t* counts = (int32_t*)(ws + L.counts);
+  int32_t* offsets = (int32_t*)(ws + L.offsets);
+  int32_t* block_sums = (int32_t*)(ws + L.block_sums);
+  int32_t* status = (int32_t*)(ws + L.status);
+  uint32_t* ids = (uint32_t*)(ws + L.ids);
+  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n, t_min, words, counts);
+  int e = launch_exclusive_scan(counts, offsets, block_sums, n, status, GNR_ST_NUM_VALID, GNR_ST_OVERFLOW_VALID,
+                                max_valid, st);
+  if (e) return e;
+  expand_ids_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(words, offsets, n, p.words, p.kbits, (long long)max_valid, ids);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int gnr_generate_rays(const float* pose_h, const float* dir_x, const float* dir_y, int H, int W,
+                                 const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays,
+                                 void* stream) {
+  if (!pose_h || !dir_x || !dir_y || !rays || H <= 0 || W <= 0 || n < 0) {
+    gnr_set_error("gnr_generate_rays: bad argument");
+    return -1;
+  }
+  if (!pixel_ids && (first_pixel < 0 || first_pixel + n > (int64_t)H * W)) {
+    gnr_set_error("gnr_generate_rays: pixel range [%lld, %lld) outside the %dx%d image", (long long)first_pixel,
+                  (long long)(first_pixel + n), W, H);
+    return -1;
+  }
+  if (n == 0) return 0;
+  Pose p;
+  for (int i = 0; i < 12; ++i) p.m[i] = pose_h[i];
+  raygen_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p, dir_x, dir_y, W, pixel_ids,
+                                                                              first_pixel, n, rays);
+  GNR_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -1,0 +1,468 @@
+"""``B200GridNeRF``: the reference's ``GridNeRF`` model API on top of ``libgridnerf_b200.so``.
+
+Same constructor arguments, state-dict keys, checkpoint format, ``load`` and ``forward``
+signature as ``app/models/gridnerf_sequential.py`` (``GridBaseSequential.__init__`` :46-132,
+``save``/``load`` :209-242, ``forward`` :439-658, ``GridNeRF`` :661-747), so that
+``GridNeRF(**ckpt["kwargs"], device=..., args=..., is_train=False); model.load(ckpt)`` and the
+``renderer_fn`` chunk loops (app/tools/render_utils.py:15-63,
+dist_render/ddp_infer/inferer_impl.py:95-120) work unchanged.  All device work of ``forward``
+happens in the CUDA library; torch only owns the tensors.
+
+Rendering only: ``is_train=True``, the NeRF refinement branch (``run_nerf``), the appearance
+latent (``encode_app``) and the hull sampler (``sampling_opt``) raise ``NotImplementedError``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import GnrConfig, check, lib
+
+MAT_MODE = [[0, 1], [0, 2], [1, 2]]
+VEC_MODE = [2, 1, 0]
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return C.c_void_p(t.data_ptr()) if t is not None else C.c_void_p(0)
+
+
+def _stream():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class AlphaGridMask(torch.nn.Module):
+    """Occupancy volume holder with the attributes of app/models/alpha_mask.py:16-26."""
+
+    def __init__(self, device, aabb, alpha_volume):
+        super().__init__()
+        self.device = device
+        self.aabb = aabb.to(device)
+        self.aabbSize = self.aabb[1] - self.aabb[0]
+        self.invgridSize = 1.0 / self.aabbSize * 2
+        self.alpha_volume = alpha_volume.view(1, 1, *alpha_volume.shape[-3:])
+        self.gridSize = torch.LongTensor(
+            [alpha_volume.shape[-1], alpha_volume.shape[-2], alpha_volume.shape[-3]]
+        ).to(device)
+
+
+class _MLPRenderFea(torch.nn.Module):
+    """Parameter holder with the layout of app/models/mlp_render_fea.py:20-42."""
+
+    def __init__(self, in_chanel, viewpe, feape, feature_c, bias_enable):
+        super().__init__()
+        self.in_mlpC = 2 * max(viewpe, 0) * 3 + 2 * feape * in_chanel + 3 * (viewpe > -1) + in_chanel
+        self.viewpe, self.feape = viewpe, feape
+        self.mlp = torch.nn.Sequential(
+            torch.nn.Linear(self.in_mlpC, feature_c, bias=bool(bias_enable)),
+            torch.nn.ReLU(inplace=True),
+            torch.nn.Linear(feature_c, feature_c, bias=bool(bias_enable)),
+            torch.nn.ReLU(inplace=True),
+            torch.nn.Linear(feature_c, 3, bias=bool(bias_enable)),
+        )
+        if bias_enable:
+            torch.nn.init.constant_(self.mlp[-1].bias, 0)
+
+
+class B200GridNeRF(torch.nn.Module):
+    # MLP precision modes of the library (GnrConfig.mlp_mode)
+    MLP_FP32, MLP_TC_SPLIT, MLP_TC_BF16 = 0, 1, 2
+
+    def __init__(  # noqa: PLR0913 -- the reference's signature
+        self,
+        aabb,
+        gridSize,
+        device,
+        density_n_comp=8,
+        appearance_n_comp=24,
+        app_dim=27,
+        alphaMask=None,
+        near_far=(2.0, 6.0),
+        density_shift=-10,
+        alphaMask_thres=0.001,
+        distance_scale=25,
+        rayMarch_weight_thres=0.001,
+        pos_pe=6,
+        view_pe=6,
+        fea_pe=6,
+        featureC=128,
+        step_ratio=2.0,
+        fea2denseAct="softplus",
+        use_plane_split=True,
+        args=None,
+        group=None,
+        is_train=False,
+        mlp_mode: int = 0,
+        **_ignored,
+    ):
+        super().__init__()
+        if args is None:
+            raise ValueError("args namespace required (same attributes as the reference's ArgsConfig)")
+        if is_train:
+            raise NotImplementedError("B200GridNeRF renders only; training stays with the reference model")
+        if getattr(args, "run_nerf", False):
+            raise NotImplementedError("run_nerf (NeRF refinement branch) is not part of the render path")
+        if getattr(args, "encode_app", False):
+            raise NotImplementedError("encode_app (appearance latent) is not supported yet")
+        if getattr(args, "nonlinear_density", False):
+            raise NotImplementedError("nonlinear_density is not supported")
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("B200GridNeRF needs a CUDA device (sm_100a); there is no CPU path")
+        self.device = dev
+        self.args = args
+        self.ndims = int(getattr(args, "ndims", 3))
+        self.resMode = list(args.resMode) if getattr(args, "resMode", None) is not None else [1]
+        if isinstance(density_n_comp, int):
+            density_n_comp = [density_n_comp] * 3
+        if isinstance(appearance_n_comp, int):
+            appearance_n_comp = [appearance_n_comp] * 3
+        self.density_n_comp = list(density_n_comp)[: self.ndims]
+        self.app_n_comp = list(appearance_n_comp)[: self.ndims]
+        if len(set(self.density_n_comp)) != 1 or len(set(self.app_n_comp)) != 1:
+            raise NotImplementedError("planes of one kind must share a channel count")
+        self.app_dim = app_dim
+        self.aabb = torch.as_tensor(aabb, dtype=torch.float32).to(dev)
+        self.alphaMask = alphaMask
+        self.density_shift = density_shift
+        self.alphaMask_thres = alphaMask_thres
+        self.distance_scale = distance_scale
+        self.rayMarch_weight_thres = rayMarch_weight_thres
+        self.fea2denseAct = fea2denseAct
+        self.near_far = list(near_far)
+        self.step_ratio = step_ratio
+        self.pos_pe, self.view_pe, self.fea_pe, self.featureC = pos_pe, view_pe, fea_pe, featureC
+        self.matMode = MAT_MODE[: self.ndims]
+        self.vecMode = VEC_MODE[: self.ndims]
+        self.sampling_opt = getattr(args, "sampling_opt", 0)
+        self.n_importance = getattr(args, "n_importance", 128)
+        self.alpha_mask_filter_thre = getattr(args, "alpha_mask_filter_thre", 0.0) or 0.0
+        self.mlp_mode = int(mlp_mode)
+        self.update_stepSize(gridSize)
+
+        # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
+        g = [int(v) for v in self.gridSize.tolist()]
+        dp, dl, ap, al = [], [], [], []
+        for i in range(len(self.vecMode)):
+            m0, m1 = self.matMode[i]
+            for j in self.resMode:
+                dp.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[m1] * j, g[m0] * j)), requires_grad=False))
+                dl.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[self.vecMode[i]] * j, 1)), requires_grad=False))
+                ap.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[m1] * j, g[m0] * j)), requires_grad=False))
+                al.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[self.vecMode[i]] * j, 1)), requires_grad=False))
+        self.density_plane = torch.nn.ParameterList(dp).to(dev)
+        self.density_line = torch.nn.ParameterList(dl).to(dev)
+        self.app_plane = torch.nn.ParameterList(ap).to(dev)
+        self.app_line = torch.nn.ParameterList(al).to(dev)
+        self.basis_mat = torch.nn.Linear(sum(self.app_n_comp) * len(self.resMode), self.app_dim, bias=False).to(dev)
+        self.renderModule = _MLPRenderFea(self.app_dim, view_pe, fea_pe, featureC, getattr(args, "bias_enable", 0)).to(dev)
+        for p in self.parameters():
+            p.requires_grad_(False)
+
+        self._handle = C.c_void_p(0)
+        self._committed = False
+        self._ws: Dict[tuple, torch.Tensor] = {}
+        # capacities of the two compacted sample lists, per ray of a chunk
+        self.valid_capacity_per_ray: Optional[int] = None  # None = n_samples (can never overflow)
+        self.app_capacity_per_ray = 192
+        self.check_status_every_call = True
+        self.last_status: Optional[np.ndarray] = None
+
+    # -- geometry scalars, computed with torch exactly as the reference does (:149-164) ----------
+    def update_stepSize(self, gridSize):
+        self.aabbSize = self.aabb[1] - self.aabb[0]
+        self.invaabbSize = 2.0 / self.aabbSize
+        self.gridSize = torch.tensor(gridSize, device=self.aabbSize.device)
+        self.units = self.aabbSize / (self.gridSize - 1)
+        self.stepSize = torch.mean(self.units) * self.step_ratio
+        self.aabbDiag = torch.sqrt(torch.sum(torch.square(self.aabbSize)))
+        self.nSamples = int((self.aabbDiag / self.stepSize).item()) + 1
+
+    def get_kwargs(self):
+        return {
+            "aabb": self.aabb,
+            "gridSize": self.gridSize.tolist(),
+            "density_n_comp": self.density_n_comp,
+            "appearance_n_comp": self.app_n_comp,
+            "app_dim": self.app_dim,
+            "density_shift": self.density_shift,
+            "alphaMask_thres": self.alphaMask_thres,
+            "distance_scale": self.distance_scale,
+            "rayMarch_weight_thres": self.rayMarch_weight_thres,
+            "fea2denseAct": self.fea2denseAct,
+            "near_far": self.near_far,
+            "step_ratio": self.step_ratio,
+            "pos_pe": self.pos_pe,
+            "view_pe": self.view_pe,
+            "fea_pe": self.fea_pe,
+            "featureC": self.featureC,
+        }
+
+    def normalize_coord(self, xyz_sampled):
+        return (xyz_sampled - self.aabb[0]) * self.invaabbSize - 1
+
+    # -- checkpoint I/O (:209-242) -----------------------------------------------------------------
+    def save(self, path):
+        ckpt = {"kwargs": self.get_kwargs(), "state_dict": self.state_dict()}
+        if self.alphaMask is not None:
+            alpha_volume = self.alphaMask.alpha_volume.bool().cpu().numpy()
+            ckpt.update({"alphaMask.shape": alpha_volume.shape})
+            ckpt.update({"alphaMask.mask": np.packbits(alpha_volume.reshape(-1))})
+            ckpt.update({"alphaMask.aabb": self.alphaMask.aabb.cpu()})
+        torch.save(ckpt, path)
+
+    def load(self, ckpt):
+        if "alphaMask.aabb" in ckpt.keys():
+            length = int(np.prod(ckpt["alphaMask.shape"]))
+            alpha_volume = torch.from_numpy(
+                np.unpackbits(ckpt["alphaMask.mask"])[:length].reshape(ckpt["alphaMask.shape"])
+            )
+            self.alphaMask = AlphaGridMask(self.device, ckpt["alphaMask.aabb"].to(self.device),
+                                           alpha_volume.float().to(self.device))
+        self.load_state_dict(ckpt["state_dict"], strict=False)
+        self.commit()
+
+    # -- library handle ----------------------------------------------------------------------------
+    def _config(self) -> GnrConfig:
+        cfg = GnrConfig()
+        aabb = self.aabb.detach().cpu().numpy().astype(np.float32)
+        inv = self.invaabbSize.detach().cpu().numpy().astype(np.float32)
+        for a in range(3):
+            cfg.aabb[a] = float(aabb[0, a])
+            cfg.aabb[3 + a] = float(aabb[1, a])
+            cfg.inv_aabb_size[a] = float(inv[a])
+            cfg.grid[a] = int(self.gridSize[a])
+        cfg.near_t, cfg.far_t = float(self.near_far[0]), float(self.near_far[1])
+        cfg.step_size = float(self.stepSize.item())
+        cfg.distance_scale = float(self.distance_scale)
+        cfg.density_shift = float(self.density_shift)
+        if self.fea2denseAct not in ("softplus", "relu"):
+            raise ValueError(f"fea2denseAct {self.fea2denseAct!r} (softplus|relu)")
+        cfg.density_act = 0 if self.fea2denseAct == "softplus" else 1
+        cfg.ray_weight_thres = float(self.rayMarch_weight_thres)
+        cfg.alpha_filter_thres = float(self.alpha_mask_filter_thre)
+        cfg.n_pairs = len(self.density_plane)
+        cfg.n_density = int(self.density_n_comp[0])
+        cfg.n_app = int(self.app_n_comp[0])
+        cfg.app_dim = int(self.app_dim)
+        cfg.fea_pe, cfg.view_pe = int(self.fea_pe), int(self.view_pe)
+        cfg.hidden = int(self.featureC)
+        cfg.has_bias = int(self.renderModule.mlp[0].bias is not None)
+        cfg.mlp_mode = self.mlp_mode
+        return cfg
+
+    def commit(self, release_torch_planes: bool = False):
+        """(Re)create the library model from the current parameters: converts planes and
+        lines to channel-last, bit-packs the occupancy volume, re-tiles the MLP weights."""
+        self._release()
+        dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        cfg = self._config()
+        h = C.c_void_p(0)
+        check(lib.gnr_create(C.byref(cfg), dev_index, C.byref(h)), "gnr_create")
+        self._handle = h
+        st = _stream()
+        n_res = len(self.resMode)
+        with torch.cuda.device(self.device):
+            for kind, planes, lines in ((0, self.density_plane, self.density_line), (1, self.app_plane, self.app_line)):
+                for idx in range(len(planes)):
+                    dim = idx // n_res
+                    p = planes[idx].detach().float().contiguous()
+                    l_ = lines[idx].detach().float().contiguous()
+                    check(lib.gnr_upload_plane(h, kind, idx, _ptr(p), p.shape[1], p.shape[2], p.shape[3],
+                                               self.matMode[dim][0], self.matMode[dim][1], st), "gnr_upload_plane")
+                    check(lib.gnr_upload_line(h, kind, idx, _ptr(l_), l_.shape[1], l_.shape[2], self.vecMode[dim], st),
+                          "gnr_upload_line")
+            if self.alphaMask is not None:
+                vol = (self.alphaMask.alpha_volume[0, 0] > 0).to(torch.uint8).contiguous().to(self.device)
+                d_, h_, w_ = vol.shape
+                a = self.alphaMask.aabb.detach().cpu().numpy().astype(np.float32)
+                inv = self.alphaMask.invgridSize.detach().cpu().numpy().astype(np.float32)
+                a_c = (C.c_float * 6)(*[float(v) for v in a.reshape(-1)])
+                i_c = (C.c_float * 3)(*[float(v) for v in inv])
+                check(lib.gnr_upload_alpha_mask(h, _ptr(vol), d_, h_, w_, a_c, i_c, st), "gnr_upload_alpha_mask")
+            mlp = self.renderModule.mlp
+            ws = [mlp[i].weight.detach().float().contiguous() for i in (0, 2, 4)]
+            bs = [mlp[i].bias.detach().float().contiguous() if mlp[i].bias is not None else None for i in (0, 2, 4)]
+            bw = self.basis_mat.weight.detach().float().contiguous()
+            check(lib.gnr_upload_mlp(h, _ptr(bw), _ptr(ws[0]), _ptr(bs[0]), _ptr(ws[1]), _ptr(bs[1]), _ptr(ws[2]),
+                                     _ptr(bs[2]), st), "gnr_upload_mlp")
+            torch.cuda.current_stream().synchronize()
+        self._committed = True
+        if release_torch_planes:
+            for plist in (self.density_plane, self.app_plane):
+                for p in plist:
+                    p.data = torch.empty(0, device=self.device)
+
+    def _release(self):
+        if getattr(self, "_handle", None) is not None and self._handle.value:
+            lib.gnr_destroy(self._handle)
+        self._handle = C.c_void_p(0)
+        self._committed = False
+
+    def __del__(self):
+        try:
+            self._release()
+        except Exception:
+            pass
+
+    # -- chunk plumbing ----------------------------------------------------------------------------
+    def capacities(self, n_rays: int, n_samples: int):
+        per_valid = n_samples if self.valid_capacity_per_ray is None else min(n_samples, self.valid_capacity_per_ray)
+        per_app = min(n_samples, self.app_capacity_per_ray)
+        return max(1, n_rays * per_valid), max(1, n_rays * per_app)
+
+    def workspace(self, n_rays: int, n_samples: int):
+        max_valid, max_app = self.capacities(n_rays, n_samples)
+        key = (n_rays, n_samples, max_valid, max_app)
+        buf = self._ws.get(key)
+        if buf is None:
+            nbytes = C.c_size_t(0)
+            check(lib.gnr_workspace_bytes(self._handle, n_rays, n_samples, max_valid, max_app, C.byref(nbytes)),
+                  "gnr_workspace_bytes")
+            if len(self._ws) > 4:
+                self._ws.clear()
+            buf = torch.empty(nbytes.value + 256, dtype=torch.uint8, device=self.device)
+            self._ws[key] = buf
+        off = (-buf.data_ptr()) % 256
+        return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off, max_valid, max_app
+
+    def _samples(self, N_samples: int) -> int:
+        return int(N_samples) if N_samples > 0 else self.nSamples
+
+    def _prepare(self, rays_chunk):
+        if not self._committed:
+            raise RuntimeError("model parameters were never committed: call load(ckpt) or commit()")
+        if rays_chunk.device != self.device and rays_chunk.device.type != "cuda":
+            raise RuntimeError("rays must live on the model's CUDA device")
+        return rays_chunk.detach().to(torch.float32).contiguous()
+
+    def read_status(self, ws_ptr) -> np.ndarray:
+        st = (C.c_int32 * _lib.ST_WORDS)()
+        check(lib.gnr_read_status(ws_ptr, st, _stream()), "gnr_read_status")
+        self.last_status = np.array(list(st), dtype=np.int64)
+        return self.last_status
+
+    def raise_on_status(self, status):
+        if status[_lib.ST_OVERFLOW_VALID]:
+            raise RuntimeError(f"valid-sample list overflow ({status[_lib.ST_NUM_VALID]} samples): "
+                               "raise valid_capacity_per_ray (None = worst case)")
+        if status[_lib.ST_OVERFLOW_APP]:
+            raise RuntimeError(f"appearance-sample list overflow ({status[_lib.ST_NUM_APP]} samples): "
+                               "raise app_capacity_per_ray")
+        if status[_lib.ST_WAIT_EXPIRED]:
+            raise RuntimeError("a bounded device-side wait expired in the tensor-core MLP kernel")
+
+    # -- the reference's forward (:439-658), rendering branch ---------------------------------------
+    def forward(self, rays_chunk, app_code=None, white_bg=True, is_train=False, N_samples=-1, idxs_chunk=None):
+        if is_train:
+            raise NotImplementedError("is_train=True: training is not part of this package")
+        if self.sampling_opt:
+            raise NotImplementedError("sampling_opt=1 (sample_ray_within_hull) is not supported yet")
+        rays = self._prepare(rays_chunk)
+        n = rays.shape[0]
+        s = self._samples(N_samples)
+        rgb = torch.empty((n, 3), dtype=torch.float32, device=self.device)
+        depth = torch.empty((n,), dtype=torch.float32, device=self.device)
+        if n == 0:
+            return {"rgb_map": rgb, "depth_map": depth}, {}
+        with torch.cuda.device(self.device):
+            keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(n, s)
+            check(lib.gnr_render_chunk(self._handle, _ptr(rays), n, s, int(bool(white_bg)), ws_ptr, ws_bytes,
+                                       max_valid, max_app, _ptr(rgb), _ptr(depth), _stream()), "gnr_render_chunk")
+            if self.check_status_every_call:
+                self.raise_on_status(self.read_status(ws_ptr))
+        return {"rgb_map": rgb, "depth_map": depth}, {}
+
+    # -- stage-wise access for parity tests and profiling --------------------------------------------
+    @torch.no_grad()
+    def run_stages(self, rays_chunk, N_samples=-1, white_bg=True, upto: str = "composite"):
+        """Run the chunk stage by stage through the stage-wise C entry points and return every
+        intermediate as torch tensors (lists are trimmed to their true lengths)."""
+        order = ["sample", "density", "weights", "appearance", "composite"]
+        stop = order.index(upto)
+        rays = self._prepare(rays_chunk)
+        n, s = rays.shape[0], self._samples(N_samples)
+        dev = self.device
+        out = {}
+        with torch.cuda.device(dev):
+            keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(n, s)
+            words = (s + 31) // 32
+            t_min = torch.empty(n, dtype=torch.float32, device=dev)
+            counts = torch.empty(n, dtype=torch.int32, device=dev)
+            offsets = torch.empty(n + 1, dtype=torch.int32, device=dev)
+            mask_words = torch.empty((n, words), dtype=torch.int32, device=dev)
+            ids = torch.empty(max_valid, dtype=torch.int32, device=dev)
+            st = _stream()
+            check(lib.gnr_sample(self._handle, _ptr(rays), n, s, ws_ptr, ws_bytes, max_valid, _ptr(t_min), _ptr(counts),
+                                 _ptr(offsets), _ptr(mask_words), _ptr(ids), st), "gnr_sample")
+            status = self.read_status(ws_ptr)
+            self.raise_on_status(status)
+            m_v = int(offsets[-1].item())
+            kbits = lib.gnr_sample_bits(s)
+            ids64 = ids[:m_v].to(torch.int64) & 0xFFFFFFFF
+            out.update({"t_min": t_min, "counts": counts, "offsets": offsets, "mask_words": mask_words,
+                        "ray_index": ids64 >> kbits, "sample_index": ids64 & ((1 << kbits) - 1), "num_valid": m_v})
+            if stop >= 1:
+                sf = torch.empty(max_valid, dtype=torch.float32, device=dev)
+                sg = torch.empty(max_valid, dtype=torch.float32, device=dev)
+                check(lib.gnr_density(self._handle, _ptr(rays), n, s, ws_ptr, ws_bytes, max_valid, _ptr(sf), _ptr(sg), st),
+                      "gnr_density")
+                out.update({"sigma_feature": sf[:m_v], "sigma": sg[:m_v]})
+            if stop >= 2:
+                w = torch.empty(max_valid, dtype=torch.float32, device=dev)
+                acc = torch.empty(n, dtype=torch.float32, device=dev)
+                dep = torch.empty(n, dtype=torch.float32, device=dev)
+                ac = torch.empty(n, dtype=torch.int32, device=dev)
+                ao = torch.empty(n + 1, dtype=torch.int32, device=dev)
+                ai = torch.empty(max_app, dtype=torch.int32, device=dev)
+                check(lib.gnr_weights(self._handle, _ptr(rays), n, s, ws_ptr, ws_bytes, max_valid, max_app, _ptr(w),
+                                      _ptr(acc), _ptr(dep), _ptr(ac), _ptr(ao), _ptr(ai), st), "gnr_weights")
+                self.raise_on_status(self.read_status(ws_ptr))
+                m_a = int(ao[-1].item())
+                out.update({"weight": w[:m_v], "acc": acc, "depth": dep, "app_counts": ac, "app_offsets": ao,
+                            "app_index": ai[:m_a].to(torch.int64), "num_app": m_a})
+            if stop >= 3:
+                feat = torch.empty((max_app, self.app_dim), dtype=torch.float32, device=dev)
+                rgb_s = torch.empty((max_app, 3), dtype=torch.float32, device=dev)
+                check(lib.gnr_appearance(self._handle, _ptr(rays), n, s, ws_ptr, ws_bytes, max_valid, max_app, _ptr(feat),
+                                         _ptr(rgb_s), st), "gnr_appearance")
+                out.update({"app_features": feat[: out["num_app"]], "rgb_samples": rgb_s[: out["num_app"]]})
+            if stop >= 4:
+                rgb = torch.empty((n, 3), dtype=torch.float32, device=dev)
+                depth = torch.empty(n, dtype=torch.float32, device=dev)
+                check(lib.gnr_composite(self._handle, n, int(bool(white_bg)), ws_ptr, ws_bytes, max_valid, max_app, s,
+                                        _ptr(rgb), _ptr(depth), st), "gnr_composite")
+                self.raise_on_status(self.read_status(ws_ptr))
+                out.update({"rgb_map": rgb, "depth_map": depth})
+            torch.cuda.current_stream().synchronize()
+        return out
+
+    @torch.no_grad()
+    def render_host(self, rays_host: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,
+                    rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None):
+        """Whole chunk loop with HOST buffers (pinned recommended): rays are copied to the
+        device chunk by chunk and rgb/depth copied back, all inside the library call."""
+        if rays_host.device.type != "cpu" or rays_host.dtype != torch.float32 or not rays_host.is_contiguous():
+            raise ValueError("rays_host must be a contiguous float32 CPU tensor [N, 6]")
+        n, s = rays_host.shape[0], self._samples(N_samples)
+        if rgb_out is None:
+            rgb_out = torch.empty((n, 3), dtype=torch.float32).pin_memory()
+        if depth_out is None:
+            depth_out = torch.empty((n,), dtype=torch.float32).pin_memory()
+        chunk = min(chunk, max(n, 1))
+        max_valid, max_app = self.capacities(chunk, s)
+        st = (C.c_int32 * _lib.ST_WORDS)()
+        check(lib.gnr_render_host(self._handle, _ptr(rays_host), n, s, int(bool(white_bg)), chunk, max_valid, max_app,
+                                  _ptr(rgb_out), _ptr(depth_out), st), "gnr_render_host")
+        self.last_status = np.array(list(st), dtype=np.int64)
+        self.raise_on_status(self.last_status)
+        return rgb_out, depth_out
+
+
+# The reference's class name, so that ``eval(args.model_name)(**kwargs)``-style construction
+# (app/tools/render_utils.py:452-462) can be pointed at this module.
+GridNeRF = B200GridNeRF

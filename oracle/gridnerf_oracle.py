@@ -1,0 +1,249 @@
+"""CPU oracle for the GridNeRF render path.  TEST INFRASTRUCTURE, NOT PRODUCT CODE.
+
+Only the test-suite, the smoke check and the benchmark's CPU-baseline leg may import this
+module; the package itself never does.
+
+This is a functional restatement (no ``nn.Module``, no checkpoint classes) of what the
+reference's torch renderer computes for one chunk of rays, written with the same torch
+operators in the same order so that on the same torch build it reproduces the reference
+bit for bit on CPU.  Each function names the reference lines it follows.  The arithmetic of
+``F.grid_sample``, ``cumprod``, ``softplus``, ``sin``/``cos``, ``sigmoid`` and ``linear`` lives in
+torch itself (ATen, here torch 2.11.0; the reference pins 1.13.1), which is why a second,
+torch-free restatement of the integer-valued part (which samples are valid) is kept next
+to it in ``sampling_numpy.py``.
+
+Pinning: the reference's own tests hold no golden vectors for this path (they compare PSNR
+against photographs on a cluster), so the oracle is pinned against the reference itself:
+``tests/golden/make_golden.py`` imports the reference model, loads the same seeded scene,
+asserts that every stage below equals the reference's tensors exactly, and writes the
+fixtures under ``tests/golden/``.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.nn.functional as F
+
+MAT_MODE = ((0, 1), (0, 2), (1, 2))
+VEC_MODE = (2, 1, 0)
+
+
+class Field:
+    """Plain container of one scene's tensors in the reference's native layout."""
+
+    def __init__(self, state_dict: Dict[str, torch.Tensor], kwargs: Dict[str, object],
+                 alpha_volume: Optional[torch.Tensor], alpha_aabb: Optional[torch.Tensor],
+                 alpha_filter_thres: float = 0.0):
+        sd = state_dict
+        self.density_plane = [sd[f"density_plane.{i}"].float() for i in range(3)]
+        self.density_line = [sd[f"density_line.{i}"].float() for i in range(3)]
+        self.app_plane = [sd[f"app_plane.{i}"].float() for i in range(3)]
+        self.app_line = [sd[f"app_line.{i}"].float() for i in range(3)]
+        self.basis_w = sd["basis_mat.weight"].float()
+        self.mlp_w = [sd[f"renderModule.mlp.{j}.weight"].float() for j in (0, 2, 4)]
+        self.mlp_b = [sd.get(f"renderModule.mlp.{j}.bias") for j in (0, 2, 4)]
+        self.aabb = torch.as_tensor(kwargs["aabb"], dtype=torch.float32)
+        self.near, self.far = [float(v) for v in kwargs["near_far"]]
+        self.density_shift = float(kwargs["density_shift"])
+        self.distance_scale = float(kwargs["distance_scale"])
+        self.ray_weight_thres = float(kwargs["rayMarch_weight_thres"])
+        self.act = kwargs.get("fea2denseAct", "softplus")
+        self.view_pe = int(kwargs["view_pe"])
+        self.fea_pe = int(kwargs["fea_pe"])
+        self.alpha_filter_thres = float(alpha_filter_thres)
+        # update_stepSize, app/models/gridnerf_sequential.py:149-164
+        self.aabb_size = self.aabb[1] - self.aabb[0]
+        self.inv_aabb_size = 2.0 / self.aabb_size
+        grid = torch.tensor(kwargs["gridSize"])
+        units = self.aabb_size / (grid - 1)
+        self.step_size = torch.mean(units) * float(kwargs["step_ratio"])
+        diag = torch.sqrt(torch.sum(torch.square(self.aabb_size)))
+        self.n_samples_default = int((diag / self.step_size).item()) + 1
+        if alpha_volume is not None:
+            # AlphaGridMask.__init__, app/models/alpha_mask.py:16-26
+            self.alpha_aabb = torch.as_tensor(alpha_aabb, dtype=torch.float32)
+            self.alpha_inv = 1.0 / (self.alpha_aabb[1] - self.alpha_aabb[0]) * 2
+            self.alpha_volume = alpha_volume.float().view(1, 1, *alpha_volume.shape[-3:])
+        else:
+            self.alpha_volume = None
+
+
+def generate_rays(pose: torch.Tensor, height: int, width: int, focal: float) -> torch.Tensor:
+    """Pinhole rays ``[H*W, 6]`` (origin, un-normalised direction) for a ``[3, 4]`` pose.
+    Follows dist_render/dataset/utils.py:57-70 (direction tables by ``torch.arange``),
+    :73-89 (rotate by the pose) and :92-113 (concatenate)."""
+    cx, cy = width / 2, height / 2
+    d = torch.empty((3, height, width), dtype=torch.float32)
+    d[0] = torch.arange(-cx / focal, (width - cx - 1e-5) / focal, 1 / focal, dtype=torch.float32).view(1, width)
+    d[1] = torch.arange(cy / focal, (cy - height + 1e-5) / focal, -1 / focal, dtype=torch.float32).view(height, 1)
+    d[2] = -1
+    d = d.permute(1, 2, 0)
+    pose = torch.as_tensor(pose, dtype=torch.float32)
+    rays_d = (d @ pose[:3, :3].T).reshape(-1, 3)
+    rays_o = pose[:3, 3].expand(rays_d.shape)
+    return torch.cat([rays_o, rays_d], 1)
+
+
+def sample_ray(f: Field, rays_o, rays_d, n_samples: int):
+    """Uniform samples from the slab entry point.  app/models/gridnerf_sequential.py:260-281
+    (``is_train=False`` branch)."""
+    vec = torch.where(rays_d == 0, torch.full_like(rays_d, 1e-6), rays_d)
+    rate_a = (f.aabb[1] - rays_o) / vec
+    rate_b = (f.aabb[0] - rays_o) / vec
+    t_min = torch.minimum(rate_a, rate_b).amax(-1).clamp(min=f.near, max=f.far)
+    rng = torch.arange(n_samples)[None].float()
+    step = f.step_size * rng
+    interpx = t_min[..., None] + step
+    pts = rays_o[..., None, :] + rays_d[..., None, :] * interpx[..., None]
+    outside = ((f.aabb[0] > pts) | (pts > f.aabb[1])).any(dim=-1)
+    return pts, interpx, ~outside, t_min
+
+
+def sample_alpha(f: Field, pts):
+    """Trilinear occupancy lookup.  app/models/alpha_mask.py:35-59."""
+    q = (pts - f.alpha_aabb[0]) * f.alpha_inv - 1
+    return F.grid_sample(f.alpha_volume, q.view(1, -1, 1, 1, 3), align_corners=True).view(-1)
+
+
+def _coords(xyz):
+    plane = torch.stack([xyz[..., list(MAT_MODE[i])] for i in range(3)]).view(3, -1, 1, 2)
+    line = torch.stack([xyz[..., VEC_MODE[i]] for i in range(3)])
+    line = torch.stack((torch.zeros_like(line), line), dim=-1).view(3, -1, 1, 2)
+    return plane, line
+
+
+def density_feature(f: Field, xyz):
+    """Sum over planes and channels of plane x line.  app/models/gridnerf_sequential.py:779-827."""
+    cp, cl = _coords(xyz)
+    sigma = torch.zeros((xyz.shape[0],))
+    for i in range(3):
+        p = F.grid_sample(f.density_plane[i], cp[[i]], align_corners=True).view(-1, xyz.shape[0])
+        l = F.grid_sample(f.density_line[i], cl[[i]], align_corners=True).view(-1, xyz.shape[0])
+        sigma = sigma + torch.sum(p * l, dim=0)
+    return sigma
+
+
+def feature2density(f: Field, feat):
+    """app/models/gridnerf_sequential.py:386-399."""
+    if f.act == "softplus":
+        return F.softplus(feat + f.density_shift)
+    return F.relu(feat)
+
+
+def app_feature(f: Field, xyz):
+    """Plane x line products, concatenated and projected by ``basis_mat``.
+    app/models/gridnerf_sequential.py:829-871."""
+    cp, cl = _coords(xyz)
+    ps, ls = [], []
+    for i in range(3):
+        ps.append(F.grid_sample(f.app_plane[i], cp[[i]], align_corners=True).view(-1, xyz.shape[0]))
+        ls.append(F.grid_sample(f.app_line[i], cl[[i]], align_corners=True).view(-1, xyz.shape[0]))
+    prod = (torch.cat(ps) * torch.cat(ls)).T
+    return F.linear(prod, f.basis_w)
+
+
+def positional_encoding(x, freqs: int):
+    """app/tools/utils.py:42-48."""
+    bands = 2 ** torch.arange(freqs, dtype=torch.float)
+    pts = (x[..., None] * bands).reshape(x.shape[:-1] + (freqs * x.shape[-1],))
+    return torch.cat([torch.sin(pts), torch.cos(pts)], dim=-1)
+
+
+def mlp_render(f: Field, viewdirs, feats):
+    """Appearance MLP.  app/models/mlp_render_fea.py:44-68 (no appearance latent)."""
+    parts = [feats]
+    if f.view_pe > -1:
+        parts.append(viewdirs)
+    if f.fea_pe > 0:
+        parts.append(positional_encoding(feats, f.fea_pe))
+    if f.view_pe > 0:
+        parts.append(positional_encoding(viewdirs, f.view_pe))
+    x = torch.cat(parts, dim=-1)
+    x = torch.relu(F.linear(x, f.mlp_w[0], f.mlp_b[0]))
+    x = torch.relu(F.linear(x, f.mlp_w[1], f.mlp_b[1]))
+    return torch.sigmoid(F.linear(x, f.mlp_w[2], f.mlp_b[2]))
+
+
+def raw2alpha(sigma, dist):
+    """app/tools/utils.py:51-64."""
+    alpha = 1.0 - torch.exp(-sigma * dist)
+    trans = torch.cumprod(torch.cat([torch.ones(alpha.shape[0], 1), 1.0 - alpha + 1e-10], -1), -1)
+    return alpha, alpha * trans[:, :-1], trans[:, -1:]
+
+
+@torch.no_grad()
+def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bool = True,
+                 keep_stages: bool = False):
+    """One chunk through the dense-sampling branch of ``GridBaseSequential.forward``
+    (app/models/gridnerf_sequential.py:448-504).  Returns ``rgb_map [N,3]``, ``depth_map [N]``
+    and, with ``keep_stages``, every intermediate the parity tests compare."""
+    rays = rays.float()
+    rays_o, viewdirs = rays[:, :3], rays[:, 3:6]
+    n_samples = n_samples if n_samples > 0 else f.n_samples_default
+    pts, z_vals, ray_valid, t_min = sample_ray(f, rays_o, viewdirs, n_samples)
+    in_box = ray_valid.clone()
+    dists = torch.cat((z_vals[:, 1:] - z_vals[:, :-1], torch.zeros_like(z_vals[:, :1])), dim=-1)
+    view_exp = viewdirs.view(-1, 1, 3).expand(pts.shape)
+    if f.alpha_volume is not None:
+        alphas = sample_alpha(f, pts[ray_valid])
+        alpha_mask = alphas > f.alpha_filter_thres
+        ray_invalid = ~ray_valid
+        ray_invalid[ray_valid] |= ~alpha_mask
+        ray_valid = ~ray_invalid
+    sigma = torch.zeros(pts.shape[:-1])
+    rgb = torch.zeros((*pts.shape[:2], 3))
+    xyz = pts
+    sigma_feat = None
+    if ray_valid.any():
+        xyz = (pts - f.aabb[0]) * f.inv_aabb_size - 1
+        sigma_feat = density_feature(f, xyz[ray_valid])
+        sigma[ray_valid] = feature2density(f, sigma_feat)
+    _, weight, _ = raw2alpha(sigma, dists * f.distance_scale)
+    app_mask = weight > f.ray_weight_thres
+    feats = None
+    if app_mask.any():
+        feats = app_feature(f, xyz[app_mask])
+        rgb[app_mask] = mlp_render(f, view_exp[app_mask], feats)
+    acc = torch.sum(weight, -1)
+    rgb_map = torch.sum(weight[..., None] * rgb, -2)
+    if white_bg:
+        rgb_map = rgb_map + (1.0 - acc[..., None])
+    rgb_map = rgb_map.clamp(0, 1)
+    depth_map = torch.sum(weight * z_vals, -1)
+    out = {"rgb_map": rgb_map, "depth_map": depth_map}
+    if keep_stages:
+        out.update({
+            "t_min": t_min, "in_box": in_box, "ray_valid": ray_valid, "sigma": sigma,
+            "sigma_feature": sigma_feat, "weight": weight, "app_mask": app_mask,
+            "app_features": feats, "rgb": rgb, "acc": acc, "z_vals": z_vals,
+        })
+    return out
+
+
+@torch.no_grad()
+def render_rays(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bool = True,
+                chunk: int = 8192):
+    """Host chunk loop.  dist_render/ddp_infer/inferer_impl.py:95-120."""
+    rgbs, depths = [], []
+    for s in range(0, rays.shape[0], chunk):
+        o = render_chunk(f, rays[s:s + chunk], n_samples, white_bg)
+        rgbs.append(o["rgb_map"])
+        depths.append(o["depth_map"])
+    return torch.cat(rgbs, 0), torch.cat(depths, 0)
+
+
+def field_from_checkpoint(ckpt: Dict[str, object], alpha_filter_thres: float = 0.0) -> Field:
+    """Unpack a checkpoint dict the way ``GridBaseSequential.load`` does
+    (app/models/gridnerf_sequential.py:225-242)."""
+    import numpy as np
+
+    vol = aabb = None
+    if "alphaMask.aabb" in ckpt:
+        shape = tuple(ckpt["alphaMask.shape"])
+        n = int(np.prod(shape))
+        vol = torch.from_numpy(np.unpackbits(ckpt["alphaMask.mask"])[:n].reshape(shape))
+        aabb = ckpt["alphaMask.aabb"]
+    sd = {k: v.detach().cpu() for k, v in ckpt["state_dict"].items()}
+    return Field(sd, ckpt["kwargs"], vol, aabb, alpha_filter_thres)

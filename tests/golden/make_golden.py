@@ -1,0 +1,203 @@
+"""Pin the oracle against the reference and write the golden fixtures.
+
+Run once, in a container that has the reference checked out (it is NOT needed to run the
+tests): ``python tests/golden/make_golden.py --reference /path/to/LandMark``.
+
+What it does, per scene:
+  1. builds the seeded synthetic scene (``landmark_b200.scenes``) as a reference-format
+     checkpoint and loads it into the reference's own ``GridNeRF`` on CPU;
+  2. runs the reference's own methods stage by stage (``sample_ray``, ``sample_alpha``,
+     ``compute_densityfeature``, ``feature2density``, ``raw2alpha``, ``compute_appfeature``,
+     ``renderModule``) and its ``forward``;
+  3. asserts that the torch oracle (``oracle/gridnerf_oracle.py``) reproduces every stage
+     EXACTLY (``torch.equal``) and that the numpy sampler (``oracle/sampling_numpy.py``)
+     reproduces the valid-sample set exactly;
+  4. writes compact ``.npz`` fixtures (bit-packed masks, per-ray counts, images, strided
+     subsets of per-sample values) that the tests compare the oracle and the CUDA path with.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+
+from landmark_b200 import scenes  # noqa: E402
+from oracle import gridnerf_oracle as orc  # noqa: E402
+from oracle import sampling_numpy as snp  # noqa: E402
+
+SUBSET_STRIDE = 97
+
+
+def import_reference(path):
+    """The reference imports two packages this image lacks for training-only symbols."""
+    sys.path.insert(0, path)
+    m = types.ModuleType("torch_efficient_distloss")
+    m.eff_distloss = lambda *a, **k: None
+    sys.modules["torch_efficient_distloss"] = m
+    k = types.ModuleType("kornia")
+    k.create_meshgrid = lambda *a, **kw: None
+    sys.modules["kornia"] = k
+    from app.models.gridnerf_sequential import GridNeRF
+    from app.tools.utils import raw2alpha
+    from dist_render.dataset import utils as ray_utils
+
+    return GridNeRF, raw2alpha, ray_utils
+
+
+def reference_model(GridNeRF, spec, ckpt):
+    args = scenes.model_args(spec)
+    kwargs = dict(ckpt["kwargs"])
+    kwargs.update({"device": "cpu", "args": args, "is_train": False})
+    model = GridNeRF(**kwargs)
+    model.load(ckpt)
+    return model
+
+
+def reference_stages(model, raw2alpha, rays, n_samples):
+    """Re-trace app/models/gridnerf_sequential.py:448-504 with the model's own methods."""
+    rays_o, viewdirs = rays[:, :3], rays[:, 3:6]
+    pts, _, z_vals, ray_valid = model.sample_ray(rays_o, viewdirs, is_train=False, N_samples=n_samples)
+    in_box = ray_valid.clone()
+    dists = torch.cat((z_vals[:, 1:] - z_vals[:, :-1], torch.zeros_like(z_vals[:, :1])), dim=-1)
+    alphas = model.alphaMask.sample_alpha(pts[ray_valid])
+    alpha_mask = alphas > model.alpha_mask_filter_thre
+    ray_invalid = ~ray_valid
+    ray_invalid[ray_valid] |= ~alpha_mask
+    ray_valid = ~ray_invalid
+    sigma = torch.zeros(pts.shape[:-1])
+    xyz = model.normalize_coord(pts)
+    sigma_feat = model.compute_densityfeature(xyz[ray_valid])
+    sigma[ray_valid] = model.feature2density(sigma_feat)
+    _, weight, _ = raw2alpha(sigma, dists * model.distance_scale)
+    app_mask = weight > model.rayMarch_weight_thres
+    feats = rgb_s = None
+    if app_mask.any():
+        feats = model.compute_appfeature(xyz[app_mask])
+        view_exp = viewdirs.view(-1, 1, 3).expand(pts.shape)
+        rgb_s = model.renderModule(view_exp[app_mask], feats, None)
+    return {"in_box": in_box, "ray_valid": ray_valid, "sigma_feature": sigma_feat, "sigma": sigma,
+            "weight": weight, "app_mask": app_mask, "app_features": feats, "rgb_samples": rgb_s,
+            "z_vals": z_vals}
+
+
+def check_equal(name, a, b):
+    if a is None and b is None:
+        return
+    assert torch.equal(a, b), f"oracle != reference at stage {name}: max diff {(a.float() - b.float()).abs().max()}"
+
+
+def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples, note):
+    ckpt = scenes.make_checkpoint(spec)
+    digest = scenes.state_dict_digest(ckpt["state_dict"])
+    with torch.no_grad():
+        model = reference_model(GridNeRF, spec, ckpt)
+        ref = reference_stages(model, raw2alpha, rays, n_samples)
+        ref_out, _ = model(rays, white_bg=True, is_train=False, N_samples=n_samples)
+    field = orc.field_from_checkpoint(ckpt, spec.alpha_filter_thres)
+    assert torch.equal(field.step_size, model.stepSize)
+    assert field.n_samples_default == model.nSamples
+    mine = orc.render_chunk(field, rays, n_samples, True, keep_stages=True)
+    for k in ("in_box", "ray_valid", "sigma_feature", "sigma", "weight", "app_mask", "app_features", "z_vals"):
+        check_equal(k, mine[k], ref[k])
+    if ref["rgb_samples"] is not None:
+        check_equal("rgb_samples", mine["rgb"][mine["app_mask"]], ref["rgb_samples"])
+    check_equal("rgb_map", mine["rgb_map"], ref_out["rgb_map"])
+    check_equal("depth_map", mine["depth_map"], ref_out["depth_map"])
+    # torch-free sampler against the reference
+    vol = field.alpha_volume[0, 0].numpy()
+    v_np, t_np = snp.valid_mask(rays.numpy(), field.aabb.numpy(), field.near, field.far,
+                                field.step_size.item(), n_samples, vol, field.alpha_aabb.numpy(),
+                                spec.alpha_filter_thres)
+    assert np.array_equal(v_np, ref["ray_valid"].numpy()), "numpy sampler != reference ray_valid"
+    assert np.array_equal(t_np, mine["t_min"].numpy())
+
+    valid = ref["ray_valid"].numpy()
+    app = ref["app_mask"].numpy()
+    sub = slice(0, None, SUBSET_STRIDE)
+    fx = {
+        "note": np.array(note),
+        "scene": np.array(spec.name),
+        "state_dict_digest": np.array(digest),
+        "torch_version": np.array(torch.__version__),
+        "n_samples": np.array(n_samples),
+        "rays": rays.numpy(),
+        "step_size": np.array(field.step_size.item(), dtype=np.float32),
+        "t_min": mine["t_min"].numpy(),
+        "valid_bits": np.packbits(valid, axis=1),
+        "valid_counts": valid.sum(1).astype(np.int32),
+        "in_box_counts": ref["in_box"].numpy().sum(1).astype(np.int32),
+        "app_bits": np.packbits(app, axis=1),
+        "app_counts": app.sum(1).astype(np.int32),
+        "sigma_feature_sub": ref["sigma_feature"].numpy()[sub],
+        "weight_sub": ref["weight"].numpy()[valid][sub],
+        "acc": ref["weight"].sum(-1).numpy(),
+        "rgb_map": ref_out["rgb_map"].numpy(),
+        "depth_map": ref_out["depth_map"].numpy(),
+        "subset_stride": np.array(SUBSET_STRIDE),
+    }
+    if ref["app_features"] is not None:
+        fx["app_features_sub"] = ref["app_features"].numpy()[sub]
+        fx["rgb_samples_sub"] = ref["rgb_samples"].numpy()[sub]
+    path = os.path.join(HERE, out_name)
+    np.savez_compressed(path, **fx)
+    print(f"{out_name}: rays {rays.shape[0]} valid {int(valid.sum())} app {int(app.sum())} "
+          f"rgb_mean {float(ref_out['rgb_map'].mean()):.4f} digest {digest} "
+          f"size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--skip-city", action="store_true")
+    a = ap.parse_args()
+    GridNeRF, raw2alpha, ray_utils = import_reference(a.reference)
+    torch.set_num_threads(os.cpu_count())
+
+    # ray generation: the reference's two device-agnostic helpers vs the oracle's restatement
+    for spec in (scenes.tiny_spec(), scenes.city_spec()):
+        pose = torch.from_numpy(scenes.make_pose(spec, scenes.make_alpha_volume(spec)))
+        dirs = ray_utils.get_ray_directions_blender_faster(spec.height, spec.width, spec.focal, device="cpu")
+        ro, rd = ray_utils.get_rays_with_directions(dirs, pose)
+        ref_rays = torch.cat([ro, rd], 1)
+        assert torch.equal(ref_rays, orc.generate_rays(pose, spec.height, spec.width, spec.focal))
+        print(f"generate_rays pinned for {spec.name}: {tuple(ref_rays.shape)}")
+
+    tiny = scenes.tiny_spec()
+    pose = torch.from_numpy(scenes.make_pose(tiny))
+    rays = orc.generate_rays(pose, tiny.height, tiny.width, tiny.focal)
+    pin_and_dump(GridNeRF, raw2alpha, ray_utils, tiny, rays, "tiny_literal.npz", tiny.n_samples,
+                 "config[0], density_shift=-10 (no appearance samples)")
+    pin_and_dump(GridNeRF, raw2alpha, ray_utils, tiny.lit(), rays, "tiny_lit.npz", tiny.n_samples,
+                 "config[0] with density_shift=0 (appearance path active)")
+    # a threshold > 0 exercises the trilinear sum rather than the any-corner test
+    thr = scenes.tiny_spec().lit()
+    thr.name = "tiny_lit_thr05"
+    thr.alpha_filter_thres = 0.5
+    pin_and_dump(GridNeRF, raw2alpha, ray_utils, thr, rays[::7].contiguous(), "tiny_lit_thr05.npz",
+                 thr.n_samples, "config[0] lit, alpha_mask_filter_thre=0.5, every 7th ray")
+
+    if not a.skip_city:
+        city = scenes.city_spec().lit()
+        vol = scenes.make_alpha_volume(city)
+        pose = torch.from_numpy(scenes.make_pose(city, vol))
+        rays = orc.generate_rays(pose, city.height, city.width, city.focal)
+        # 64-ray slices: image rows 100, 540 and 1000, columns spread over the row
+        pick = torch.cat([torch.arange(r * city.width + 7, (r + 1) * city.width, 30)[:64] for r in (100, 540, 1000)])
+        pin_and_dump(GridNeRF, raw2alpha, ray_utils, city, rays[pick].contiguous(), "city_lit_slices.npz",
+                     city.n_samples, "config[1] lit, 3 x 64 rays from rows 100/540/1000; ray ids in 'pick'")
+        d = dict(np.load(os.path.join(HERE, "city_lit_slices.npz")))
+        d["pick"] = pick.numpy()
+        np.savez_compressed(os.path.join(HERE, "city_lit_slices.npz"), **d)
+
+
+if __name__ == "__main__":
+    main()
