@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the GridNeRF render path: Mrays/s and ms per 1080p frame.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One *step* renders one 1920x1080 frame of the city-block scene (AABB [-8,8]^2x[-1,1], grid
+2048x2048x256, 16/48-channel VM planes, 512x512x64 occupancy heightfield, 512 samples per
+ray, 150->128->128->3 MLP).  The fields are seeded synthetic tensors with the shapes and
+value distribution of a reference checkpoint (no trained checkpoint is redistributable).
+Two variants of the scene exist; the headline is ``city_lit`` (``density_shift = 0``), in which
+the appearance gather and the MLP actually run; with the literal ``density_shift = -10`` every
+weight stays below the appearance threshold and only sampling, density and compositing run
+(``--workload city`` measures that).
+
+With N > 1 (launched by torchrun, one rank per GPU) the frame is split into 64x64 pixel
+tiles dealt round-robin to the ranks (replicated model), each rank renders its tiles and
+the colours are all-gathered over NCCL; ``value`` is the whole frame's rays divided by the
+slowest rank's device time (strong scaling).
+
+``--impl reference`` times the reference's CPU torch path (the oracle port of it) on a
+bounded sample of the same frame with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+TILE = 64
+DENSITY_BYTES_PER_SAMPLE = 784      # 3 planes x 4 corners x 16 ch x 4 B + 12 B coordinate + 4 B sigma
+APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B coordinate
+MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
+BASIS_FLOP_PER_SAMPLE = 7776        # 2 * 144 * 27 (done inside the appearance gather kernel)
+CPU_SAMPLE_RAYS = 8192
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            p = json.load(fh)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
+
+
+def tile_pixel_ids(H, W, rank, world):
+    """Pixel ids (row-major y*W+x) of the tiles owned by ``rank``: tile k -> rank k % world,
+    pixels inside a tile in row-major order, tiles clipped at the image border."""
+    tx, ty = (W + TILE - 1) // TILE, (H + TILE - 1) // TILE
+    ids = []
+    for k in range(rank, tx * ty, world):
+        y0, x0 = (k // tx) * TILE, (k % tx) * TILE
+        ys = np.arange(y0, min(y0 + TILE, H))
+        xs = np.arange(x0, min(x0 + TILE, W))
+        ids.append((ys[:, None] * W + xs[None, :]).reshape(-1))
+    return np.concatenate(ids).astype(np.int32) if ids else np.zeros((0,), np.int32)
+
+
+class ClockSampler:
+    """nvidia-smi clocks/throttle reasons of one GPU, sampled every 200 ms in the background."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(names, r[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_scene(workload, device):
+    from landmark_b200 import scenes
+
+    spec = scenes.city_spec()
+    if workload == "city_lit":
+        spec = spec.lit()
+    vol = scenes.make_alpha_volume(spec)
+    sd = scenes.make_state_dict(spec, device=device)  # CUDA generator: fast, seeded
+    ckpt = {"kwargs": scenes.model_kwargs(spec), "state_dict": sd, "alphaMask.shape": tuple(vol.shape),
+            "alphaMask.mask": np.packbits(vol.numpy().reshape(-1)),
+            "alphaMask.aabb": torch.tensor(spec.aabb, dtype=torch.float32)}
+    pose = scenes.make_pose(spec, vol)
+    return spec, ckpt, pose
+
+
+def run_reference(a):
+    """CPU arm: the oracle port of the reference's torch path, all host threads, one bounded
+    sample (8192 rays = image rows 536..540 of the same frame) per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from landmark_b200 import scenes
+    from oracle import gridnerf_oracle as orc
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    spec = scenes.city_spec()
+    if a.workload == "city_lit":
+        spec = spec.lit()
+    vol = scenes.make_alpha_volume(spec)
+    ckpt = scenes.make_checkpoint(spec)
+    field = orc.field_from_checkpoint(ckpt)
+    pose = torch.from_numpy(scenes.make_pose(spec, vol))
+    rays = orc.generate_rays(pose, spec.height, spec.width, spec.focal)
+    first = 536 * spec.width
+    sample = rays[first:first + CPU_SAMPLE_RAYS].contiguous()
+    for _ in range(min(a.warmup, 1)):
+        orc.render_chunk(field, sample, spec.n_samples, True)
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        orc.render_chunk(field, sample, spec.n_samples, True)
+    dt = (time.perf_counter() - t0) / a.steps
+    value = CPU_SAMPLE_RAYS / dt / 1e6
+    line = {
+        "impl": "reference", "metric": "Mrays/s", "value": value, "unit": "Mrays/s", "n_gpus": a.gpus,
+        "steps": a.steps, "warmup": min(a.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": value, "unit": "Mrays/s", "cores": cores, "kind": "port",
+                         "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-540) per step, torch {torch.__version__} CPU"},
+        "e2e": {"value": value, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "ms_per_frame_extrapolated": dt * 1e3 * spec.height * spec.width / CPU_SAMPLE_RAYS,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="city_lit", choices=["city_lit", "city"])
+    ap.add_argument("--chunk", type=int, default=131072, help="rays per library call")
+    ap.add_argument("--mlp-mode", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the render path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    device = f"cuda:{local_rank}"
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(device))
+    from landmark_b200 import scenes
+    from landmark_b200.gridnerf import B200GridNeRF
+    from landmark_b200.rays import generate_rays
+
+    spec, ckpt, pose = build_scene(a.workload, device)
+    kwargs = dict(ckpt["kwargs"])
+    kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
+    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode)
+    model.load(ckpt)
+    cpu_sd = None
+    if rank == 0 and world == 1 and not a.no_cpu_baseline:
+        cpu_sd = {k: v.cpu() for k, v in ckpt["state_dict"].items()}
+    model.release_torch_planes()
+    del ckpt["state_dict"]
+    torch.cuda.empty_cache()
+
+    H, W, S = spec.height, spec.width, spec.n_samples
+    if world == 1 and a.order == "rows":
+        ids_np = np.arange(H * W, dtype=np.int32)
+    else:
+        ids_np = tile_pixel_ids(H, W, rank, world)
+    n_local = int(ids_np.shape[0])
+    n_pad = n_local
+    if world > 1:
+        cnt = torch.tensor([n_local], device=device)
+        dist.all_reduce(cnt, op=dist.ReduceOp.MAX)
+        n_pad = int(cnt.item())
+    pix = torch.from_numpy(ids_np).to(device)
+    rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=pix)
+    rgb = torch.zeros((n_pad, 3), dtype=torch.float32, device=device)
+    depth = torch.zeros((n_pad,), dtype=torch.float32, device=device)
+    gathered = torch.empty((world * n_pad, 3), dtype=torch.float32, device=device) if world > 1 else None
+    image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
+    if world > 1:
+        pix_pad = torch.full((n_pad,), -1, dtype=torch.int64, device=device)
+        pix_pad[:n_local] = pix.to(torch.int64)
+        all_pix = torch.empty((world * n_pad,), dtype=torch.int64, device=device)
+        dist.all_gather_into_tensor(all_pix, pix_pad)
+        keep = all_pix >= 0
+        all_pix_keep = all_pix[keep]
+
+    def step():
+        model.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb[:n_local], depth_out=depth[:n_local])
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, rgb)
+            if rank == 0:
+                image[all_pix_keep] = gathered[keep]
+        else:
+            image[pix.to(torch.int64)] = rgb
+
+    for _ in range(max(a.warmup, 3)):
+        step()
+    model.check_pending_status()
+    torch.cuda.synchronize()
+    stats = model.last_status.copy()
+
+    # ---- timed region: device-resident inputs -----------------------------------------------
+    model.profile_enable(True)
+    model.profile_collect()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    stage_ms, stage_launches = model.profile_collect()
+    model.profile_enable(False)
+    t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / a.steps
+    model.check_pending_status()
+
+    # ---- end to end: host rays in, host rgb/depth out, through the C ABI ---------------------
+    rays_h = rays.cpu().pin_memory()
+    rgb_h = torch.empty((n_local, 3), dtype=torch.float32).pin_memory()
+    depth_h = torch.empty((n_local,), dtype=torch.float32).pin_memory()
+    for _ in range(2):
+        model.render_host(rays_h, S, True, chunk=a.chunk, rgb_out=rgb_h, depth_out=depth_h)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        model.render_host(rays_h, S, True, chunk=a.chunk, rgb_out=rgb_h, depth_out=depth_h)
+    e2e_s = (time.perf_counter() - t0) / a.steps
+    t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    same = bool(torch.equal(rgb_h, rgb[:n_local].cpu()))
+
+    tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local)], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tot)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    n_valid, n_app = float(stats[2]), float(stats[3])  # this rank's samples per frame
+    per_launch = {k: (stage_ms[k] / a.steps) for k in stage_ms}  # ms per frame per stage (all chunks)
+    roof = {}
+    if per_launch["density"] > 0:
+        ach = n_valid * DENSITY_BYTES_PER_SAMPLE / (per_launch["density"] * 1e-3) / 1e9
+        roof["density_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                  "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"]}
+    if per_launch["app_gather"] > 0 and n_app > 0:
+        ach = n_app * APP_BYTES_PER_SAMPLE / (per_launch["app_gather"] * 1e-3) / 1e9
+        roof["app_gather_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                     "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["app_gather"]}
+    if per_launch["mlp"] > 0 and n_app > 0:
+        ach = n_app * MLP_FLOP_PER_SAMPLE / (per_launch["mlp"] * 1e-3) / 1e12
+        roof["mlp_kernel"] = {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
+                              "frac": ach / pk["bf16_tflops"], "ms_per_frame": per_launch["mlp"],
+                              "note": "fp32 CUDA-core kernel" if a.mlp_mode == 0 else "tcgen05 kernel"}
+    dominant = max(roof, key=lambda k: roof[k]["ms_per_frame"]) if roof else None
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if dominant and os.path.exists(tpath):
+        with open(tpath) as fh:
+            tj = json.load(fh)
+        if dominant in tj:
+            units = n_valid if dominant == "density_kernel" else n_app
+            traffic = tj[dominant]["dram_bytes_per_sample"] * units
+    roofline = None
+    if dominant:
+        roofline = dict(roof[dominant])
+        roofline["kernel"] = dominant
+        roofline["peak_source"] = f"of {pk['source']}"
+        roofline["traffic"] = traffic
+        roofline["per"] = "frame (sum over the chunk launches of this kernel)"
+
+    line = {
+        "metric": "Mrays/s", "value": H * W / (ms_step * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": world,
+        "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
+                   "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
+                   "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode,
+                   "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
+        "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
+        "e2e": {"value": H * W / e2e_s / 1e6, "unit": "Mrays/s", "ms_per_frame": e2e_s * 1e3,
+                "h2d_bytes_per_step": int(n_local * 24), "d2h_bytes_per_step": int(n_local * 16),
+                "matches_device_path": same},
+        "gpu_launches": int(sum(stage_launches.values())),
+        "clocks": clocks,
+        "roofline": roofline,
+        "roofline_all": roof,
+        "stage_ms_per_frame": per_launch,
+        "samples_per_frame": {"valid": float(tot[0].item()), "appearance": float(tot[1].item()),
+                              "rays": float(tot[2].item())},
+    }
+    if cpu_sd is not None:
+        from oracle import gridnerf_oracle as orc
+
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        vol = scenes.make_alpha_volume(spec)
+        field = orc.Field(cpu_sd, scenes.model_kwargs(spec), vol, torch.tensor(spec.aabb), 0.0)
+        first = 536 * W
+        sample = generate_rays(pose, H, W, spec.focal, device=device, first_pixel=first, n=CPU_SAMPLE_RAYS).cpu()
+        t0 = time.perf_counter()
+        ref = orc.render_chunk(field, sample, S, True)
+        dt = time.perf_counter() - t0
+        got, _ = model(sample.to(device), N_samples=S)
+        err = (got["rgb_map"].cpu() - ref["rgb_map"]).abs().max(dim=1).values
+        line["cpu_baseline"] = {"value": CPU_SAMPLE_RAYS / dt / 1e6, "unit": "Mrays/s", "cores": cores, "kind": "port",
+                                "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-540), one pass, torch {torch.__version__} CPU",
+                                "rays_above_1e-4_vs_gpu": int((err > 1e-4).sum()), "max_abs_rgb_diff": float(err.max())}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -162,6 +162,25 @@ int gnr_composite(GnrModel* m, int64_t n_rays, int white_bg, void* workspace, si
                   int64_t max_valid, int64_t max_app, int n_samples, float* rgb_map, float* depth_map,
                   void* stream);
 
+/* Per-stage timing with CUDA events recorded on the launching stream around every stage of
+ * gnr_render_chunk / gnr_render_host (the counterpart of the reference's PipeStagesProfiler,
+ * dist_render/comm/profiler.py:18-69, at kernel granularity).  gnr_profile_collect waits for
+ * the recorded events, adds the elapsed milliseconds per stage into ``stage_ms_h[GNR_STAGE_COUNT]``
+ * and the number of kernel launches per stage into ``launches_h[GNR_STAGE_COUNT]``, then clears. */
+enum {
+  GNR_STAGE_SAMPLE = 0,     /* sampling + occupancy test (mask words, counts)             */
+  GNR_STAGE_COMPACT = 1,    /* scan + compaction of the valid samples                     */
+  GNR_STAGE_DENSITY = 2,    /* density feature gather                                     */
+  GNR_STAGE_WEIGHTS = 3,    /* transmittance / weights                                    */
+  GNR_STAGE_COMPACT_APP = 4,/* scan + compaction of the appearance samples                */
+  GNR_STAGE_APP_GATHER = 5, /* appearance gather + basis projection                       */
+  GNR_STAGE_MLP = 6,        /* appearance MLP                                             */
+  GNR_STAGE_COMPOSITE = 7,  /* final compositing                                          */
+  GNR_STAGE_COUNT = 8
+};
+int gnr_profile_enable(GnrModel* m, int on);
+int gnr_profile_collect(GnrModel* m, float* stage_ms_h, int64_t* launches_h);
+
 /* Copy the 8-word status block of a workspace to the host (synchronises the stream). */
 int gnr_read_status(const void* workspace, int32_t* status_h, void* stream);
 

@@ -12,6 +12,7 @@ import os
 _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libgridnerf_b200.so")
 
+STAGE_NAMES = ("sample", "compact", "density", "weights", "compact_app", "app_gather", "mlp", "composite")
 ST_OVERFLOW_VALID, ST_OVERFLOW_APP, ST_NUM_VALID, ST_NUM_APP, ST_WAIT_EXPIRED, ST_WORDS = 0, 1, 2, 3, 4, 8
 
 
@@ -66,6 +67,8 @@ SIGNATURES = {
     "gnr_weights": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _I64, _P, _P, _P, _P, _P, _P, _P]),
     "gnr_appearance": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _I64, _P, _P, _P]),
     "gnr_composite": (_INT, [_P, _I64, _INT, _P, _SZ, _I64, _I64, _INT, _P, _P, _P]),
+    "gnr_profile_enable": (_INT, [_P, _INT]),
+    "gnr_profile_collect": (_INT, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
     "gnr_read_status": (_INT, [_P, C.POINTER(C.c_int32), _P]),
 }
 

@@ -4,6 +4,7 @@
 #include <string.h>
 
 #include <new>
+#include <vector>
 
 #include "gnr_internal.cuh"
 
@@ -22,7 +23,52 @@ void gnr_set_error(const char* fmt, ...) {
 extern "C" const char* gnr_last_error(void) { return g_error; }
 extern "C" int gnr_version(void) { return 100; }
 
+// Event-pair profiler: one span per stage per chunk, summed at collect time.
+struct GnrProfiler {
+  struct Span {
+    int stage;
+    int launches;
+    cudaEvent_t a, b;
+  };
+  std::vector<Span> spans;
+  std::vector<cudaEvent_t> pool;
+  cudaEvent_t get() {
+    if (!pool.empty()) {
+      cudaEvent_t e = pool.back();
+      pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e;
+    cudaEventCreate(&e);
+    return e;
+  }
+  void begin(int stage, int launches, cudaStream_t st) {
+    Span s{stage, launches, get(), get()};
+    cudaEventRecord(s.a, st);
+    spans.push_back(s);
+  }
+  void end(cudaStream_t st) { cudaEventRecord(spans.back().b, st); }
+  ~GnrProfiler() {
+    for (auto& s : spans) {
+      cudaEventDestroy(s.a);
+      cudaEventDestroy(s.b);
+    }
+    for (auto e : pool) cudaEventDestroy(e);
+  }
+};
+
 namespace {
+
+struct StageScope {
+  GnrProfiler* p;
+  cudaStream_t st;
+  StageScope(GnrModel* m, int stage, int launches, cudaStream_t s) : p(m->prof), st(s) {
+    if (p) p->begin(stage, launches, st);
+  }
+  ~StageScope() {
+    if (p) p->end(st);
+  }
+};
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -179,6 +225,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
   free_dev(m->host_rgb);
   free_dev(m->host_depth);
   if (m->host_status) cudaFreeHost(m->host_status);
+  delete m->prof;
   for (int i = 0; i < 2; ++i) {
     if (m->host_streams[i]) cudaStreamDestroy(m->host_streams[i]);
     if (m->host_events[i]) cudaEventDestroy(m->host_events[i]);
@@ -465,6 +512,20 @@ extern "C" int gnr_read_status(const void* workspace, int32_t* status_h, void* s
     if (_e < 0) return _e;                                                                   \
   } while (0)
 
+static int launch_sample(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
+                         int64_t max_valid, cudaStream_t st) {
+  int e = launch_sample_mask(m, p, rays, n, ws, L, st);
+  if (e) return e;
+  return launch_sample_compact(m, p, n, ws, L, max_valid, st);
+}
+
+static int launch_weights(GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L, int64_t max_valid,
+                          int64_t max_app, cudaStream_t st) {
+  int e = launch_weights_only(m, p, n, ws, L, max_valid, st);
+  if (e) return e;
+  return launch_app_compact(m, p, n, ws, L, max_valid, max_app, st);
+}
+
 static int copy_out(void* dst, const void* src, size_t bytes, cudaStream_t st) {
   if (!dst || bytes == 0) return 0;
   GNR_CUDA_OK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, st));
@@ -577,12 +638,80 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
   GnrSampleParams p = gnr_sample_params(m, S);
   GNR_CUDA_OK(cudaMemsetAsync(ws + L.status, 0, GNR_ST_WORDS * sizeof(int32_t), st));
-  GNR_LAUNCH_OK(launch_sample(m, p, rays, n, ws, L, max_valid, st));
-  GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
-  GNR_LAUNCH_OK(launch_weights(m, p, n, ws, L, max_valid, max_app, st));
-  int rc = run_appearance(m, p, rays, n, ws, L, max_valid, max_app, st);
-  if (rc) return rc;
-  GNR_LAUNCH_OK(launch_composite(m, n, white_bg, ws, L, rgb_map, depth_map, st));
+  {
+    StageScope sc(m, GNR_STAGE_SAMPLE, 1, st);
+    GNR_LAUNCH_OK(launch_sample_mask(m, p, rays, n, ws, L, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_COMPACT, 4, st);
+    GNR_LAUNCH_OK(launch_sample_compact(m, p, n, ws, L, max_valid, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
+    GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_WEIGHTS, 1, st);
+    GNR_LAUNCH_OK(launch_weights_only(m, p, n, ws, L, max_valid, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_COMPACT_APP, 4, st);
+    GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_APP_GATHER, 1, st);
+    GNR_LAUNCH_OK(launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
+  }
+  {
+    StageScope sc(m, GNR_STAGE_MLP, 1, st);
+    if (m->cfg.mlp_mode == 0) {
+      GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
+    } else {
+      GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, st));
+    }
+  }
+  {
+    StageScope sc(m, GNR_STAGE_COMPOSITE, 1, st);
+    GNR_LAUNCH_OK(launch_composite(m, n, white_bg, ws, L, rgb_map, depth_map, st));
+  }
+  return 0;
+}
+
+extern "C" int gnr_profile_enable(GnrModel* m, int on) {
+  if (!m) {
+    gnr_set_error("gnr_profile_enable: null model");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  if (on && !m->prof) m->prof = new (std::nothrow) GnrProfiler();
+  if (!on && m->prof) {
+    cudaDeviceSynchronize();
+    delete m->prof;
+    m->prof = nullptr;
+  }
+  return 0;
+}
+
+extern "C" int gnr_profile_collect(GnrModel* m, float* stage_ms_h, int64_t* launches_h) {
+  if (!m || !stage_ms_h || !launches_h) {
+    gnr_set_error("gnr_profile_collect: null argument");
+    return -1;
+  }
+  if (!m->prof) {
+    gnr_set_error("gnr_profile_collect: profiling is not enabled");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  for (auto& s : m->prof->spans) {
+    GNR_CUDA_OK(cudaEventSynchronize(s.b));
+    float ms = 0.0f;
+    GNR_CUDA_OK(cudaEventElapsedTime(&ms, s.a, s.b));
+    stage_ms_h[s.stage] += ms;
+    launches_h[s.stage] += s.launches;
+    m->prof->pool.push_back(s.a);
+    m->prof->pool.push_back(s.b);
+  }
+  m->prof->spans.clear();
   return 0;
 }
 

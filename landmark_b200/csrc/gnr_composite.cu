@@ -135,29 +135,28 @@ composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ a
 
 }  // namespace
 
-int launch_weights(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                   int64_t max_valid, int64_t max_app, cudaStream_t st) {
+int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                        int64_t max_valid, cudaStream_t st) {
   unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  const float* t_min = (const float*)(ws + L.t_min);
-  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
-  const float* sigma = (const float*)(ws + L.sigma);
-  const int32_t* offsets = (const int32_t*)(ws + L.offsets);
-  float* weight = (float*)(ws + L.weight);
-  float* acc = (float*)(ws + L.acc);
-  float* depth = (float*)(ws + L.depth);
-  int32_t* app_counts = (int32_t*)(ws + L.app_counts);
+  weights_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+      p, m->cfg.distance_scale, m->cfg.ray_weight_thres, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids),
+      (const float*)(ws + L.sigma), (const int32_t*)(ws + L.offsets), n, (long long)max_valid, (float*)(ws + L.weight),
+      (float*)(ws + L.acc), (float*)(ws + L.depth), (int32_t*)(ws + L.app_counts));
+  return (int)cudaGetLastError();
+}
+
+int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                       int64_t max_valid, int64_t max_app, cudaStream_t st) {
+  (void)p;
   int32_t* app_offsets = (int32_t*)(ws + L.app_offsets);
-  int32_t* app_index = (int32_t*)(ws + L.app_index);
-  int32_t* block_sums = (int32_t*)(ws + L.block_sums);
-  int32_t* status = (int32_t*)(ws + L.status);
-  weights_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, m->cfg.distance_scale, m->cfg.ray_weight_thres, t_min, ids,
-                                                        sigma, offsets, n, (long long)max_valid, weight, acc, depth,
-                                                        app_counts);
-  int e = launch_exclusive_scan(app_counts, app_offsets, block_sums, n, status, GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP,
-                                max_app, st);
+  int e = launch_exclusive_scan((const int32_t*)(ws + L.app_counts), app_offsets, (int32_t*)(ws + L.block_sums), n,
+                                (int32_t*)(ws + L.status), GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP, max_app, st);
   if (e) return e;
-  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(weight, m->cfg.ray_weight_thres, offsets, app_offsets, n,
-                                                           (long long)max_valid, (long long)max_app, app_index);
+  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), m->cfg.ray_weight_thres,
+                                                           (const int32_t*)(ws + L.offsets), app_offsets, n,
+                                                           (long long)max_valid, (long long)max_app,
+                                                           (int32_t*)(ws + L.app_index));
   return (int)cudaGetLastError();
 }
 

@@ -36,8 +36,11 @@ struct GnrMlp {
   int n_prod;   // sum of padded appearance channels (144)
 };
 
+struct GnrProfiler;
+
 struct GnrModel {
   GnrConfig cfg;
+  GnrProfiler* prof;  // null unless profiling is enabled
   int device;
   int sm_count;
   GnrPlane den[GNR_MAX_PLANES];
@@ -92,12 +95,16 @@ int gnr_check_chunk(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid,
                     const void* ws, size_t ws_bytes);
 
 // launchers (each enqueues on `st`, returns cudaGetLastError as int)
-int launch_sample(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                  const GnrWs& L, int64_t max_valid, cudaStream_t st);
+int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                       const GnrWs& L, cudaStream_t st);
+int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                          int64_t max_valid, cudaStream_t st);
 int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
                    const GnrWs& L, int64_t max_valid, cudaStream_t st);
-int launch_weights(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                   int64_t max_valid, int64_t max_app, cudaStream_t st);
+int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                        int64_t max_valid, cudaStream_t st);
+int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                       int64_t max_valid, int64_t max_app, cudaStream_t st);
 int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
                       const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st);
 int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,

@@ -240,22 +240,25 @@ int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* bloc
   return (int)cudaGetLastError();
 }
 
-int launch_sample(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                  const GnrWs& L, int64_t max_valid, cudaStream_t st) {
+int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                       const GnrWs& L, cudaStream_t st) {
   (void)m;
-  float* t_min = (float*)(ws + L.t_min);
-  uint32_t* words = (uint32_t*)(ws + L.words);
-  int32_t* counts = (int32_t*)(ws + L.counts);
-  int32_t* offsets = (int32_t*)(ws + L.offsets);
-  int32_t* block_sums = (int32_t*)(ws + L.block_sums);
-  int32_t* status = (int32_t*)(ws + L.status);
-  uint32_t* ids = (uint32_t*)(ws + L.ids);
   unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n, t_min, words, counts);
-  int e = launch_exclusive_scan(counts, offsets, block_sums, n, status, GNR_ST_NUM_VALID, GNR_ST_OVERFLOW_VALID,
-                                max_valid, st);
+  sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n, (float*)(ws + L.t_min), (uint32_t*)(ws + L.words),
+                                                            (int32_t*)(ws + L.counts));
+  return (int)cudaGetLastError();
+}
+
+int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
+                          int64_t max_valid, cudaStream_t st) {
+  (void)m;
+  int32_t* offsets = (int32_t*)(ws + L.offsets);
+  int e = launch_exclusive_scan((const int32_t*)(ws + L.counts), offsets, (int32_t*)(ws + L.block_sums), n,
+                                (int32_t*)(ws + L.status), GNR_ST_NUM_VALID, GNR_ST_OVERFLOW_VALID, max_valid, st);
   if (e) return e;
-  expand_ids_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(words, offsets, n, p.words, p.kbits, (long long)max_valid, ids);
+  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  expand_ids_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const uint32_t*)(ws + L.words), offsets, n, p.words, p.kbits,
+                                                           (long long)max_valid, (uint32_t*)(ws + L.ids));
   return (int)cudaGetLastError();
 }
 

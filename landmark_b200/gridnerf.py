@@ -150,14 +150,14 @@ class B200GridNeRF(torch.nn.Module):
         for i in range(len(self.vecMode)):
             m0, m1 = self.matMode[i]
             for j in self.resMode:
-                dp.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[m1] * j, g[m0] * j)), requires_grad=False))
-                dl.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[self.vecMode[i]] * j, 1)), requires_grad=False))
-                ap.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[m1] * j, g[m0] * j)), requires_grad=False))
-                al.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[self.vecMode[i]] * j, 1)), requires_grad=False))
-        self.density_plane = torch.nn.ParameterList(dp).to(dev)
-        self.density_line = torch.nn.ParameterList(dl).to(dev)
-        self.app_plane = torch.nn.ParameterList(ap).to(dev)
-        self.app_line = torch.nn.ParameterList(al).to(dev)
+                dp.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[m1] * j, g[m0] * j), device=dev), requires_grad=False))
+                dl.append(torch.nn.Parameter(torch.zeros((1, self.density_n_comp[i], g[self.vecMode[i]] * j, 1), device=dev), requires_grad=False))
+                ap.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[m1] * j, g[m0] * j), device=dev), requires_grad=False))
+                al.append(torch.nn.Parameter(torch.zeros((1, self.app_n_comp[i], g[self.vecMode[i]] * j, 1), device=dev), requires_grad=False))
+        self.density_plane = torch.nn.ParameterList(dp)
+        self.density_line = torch.nn.ParameterList(dl)
+        self.app_plane = torch.nn.ParameterList(ap)
+        self.app_line = torch.nn.ParameterList(al)
         self.basis_mat = torch.nn.Linear(sum(self.app_n_comp) * len(self.resMode), self.app_dim, bias=False).to(dev)
         self.renderModule = _MLPRenderFea(self.app_dim, view_pe, fea_pe, featureC, getattr(args, "bias_enable", 0)).to(dev)
         for p in self.parameters():
@@ -293,9 +293,14 @@ class B200GridNeRF(torch.nn.Module):
             torch.cuda.current_stream().synchronize()
         self._committed = True
         if release_torch_planes:
-            for plist in (self.density_plane, self.app_plane):
-                for p in plist:
-                    p.data = torch.empty(0, device=self.device)
+            self.release_torch_planes()
+
+    def release_torch_planes(self):
+        """Drop the torch (NCHW) copies of the planes once the library holds its own
+        channel-last copies; ``state_dict()`` no longer contains them afterwards."""
+        for plist in (self.density_plane, self.app_plane):
+            for p in plist:
+                p.data = torch.empty(0, device=self.device)
 
     def _release(self):
         if getattr(self, "_handle", None) is not None and self._handle.value:
@@ -440,6 +445,57 @@ class B200GridNeRF(torch.nn.Module):
                 out.update({"rgb_map": rgb, "depth_map": depth})
             torch.cuda.current_stream().synchronize()
         return out
+
+    def profile_enable(self, on: bool = True):
+        check(lib.gnr_profile_enable(self._handle, int(on)), "gnr_profile_enable")
+
+    def profile_collect(self):
+        """Milliseconds and kernel launches per stage since the last collect."""
+        ms = (C.c_float * len(_lib.STAGE_NAMES))()
+        launches = (C.c_int64 * len(_lib.STAGE_NAMES))()
+        check(lib.gnr_profile_collect(self._handle, ms, launches), "gnr_profile_collect")
+        return ({k: float(v) for k, v in zip(_lib.STAGE_NAMES, ms)},
+                {k: int(v) for k, v in zip(_lib.STAGE_NAMES, launches)})
+
+    @torch.no_grad()
+    def render_rays(self, rays: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,
+                    rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None):
+        """Device-resident chunk loop: ``rays [N, 6]`` on the GPU -> ``rgb [N, 3]``, ``depth [N]``
+        written in place, one status check at the end instead of one per chunk."""
+        rays = self._prepare(rays)
+        n, s = rays.shape[0], self._samples(N_samples)
+        if rgb_out is None:
+            rgb_out = torch.empty((n, 3), dtype=torch.float32, device=self.device)
+        if depth_out is None:
+            depth_out = torch.empty((n,), dtype=torch.float32, device=self.device)
+        chunk = max(1, min(chunk, n))
+        status = torch.zeros((max(1, (n + chunk - 1) // chunk), _lib.ST_WORDS), dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            st = _stream()
+            for ci, first in enumerate(range(0, n, chunk)):
+                m = min(chunk, n - first)
+                keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(chunk, s)
+                check(lib.gnr_render_chunk(self._handle, C.c_void_p(rays.data_ptr() + first * 24), m, s,
+                                           int(bool(white_bg)), ws_ptr, ws_bytes, max_valid, max_app,
+                                           C.c_void_p(rgb_out.data_ptr() + first * 12),
+                                           C.c_void_p(depth_out.data_ptr() + first * 4), st), "gnr_render_chunk")
+                status[ci].copy_(keep[(-keep.data_ptr()) % 256:][: 4 * _lib.ST_WORDS].view(torch.int32))
+        self._pending_status = status
+        return rgb_out, depth_out
+
+    def check_pending_status(self):
+        """Synchronise and raise if any chunk of the last ``render_rays`` overflowed a list."""
+        st = getattr(self, "_pending_status", None)
+        if st is None:
+            return None
+        h = st.cpu().numpy().astype(np.int64)
+        agg = np.zeros(_lib.ST_WORDS, dtype=np.int64)
+        agg[[0, 1, 4]] = h[:, [0, 1, 4]].max(0)
+        agg[[2, 3]] = h[:, [2, 3]].sum(0)
+        self.last_status = agg
+        self._pending_status = None
+        self.raise_on_status(agg)
+        return agg
 
     @torch.no_grad()
     def render_host(self, rays_host: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,

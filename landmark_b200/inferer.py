@@ -1,0 +1,102 @@
+"""Per-process inferer implementation: the ``dist_render`` seam for a model forward.
+
+Mirrors ``AbstractDDPInfererImpl`` / ``TorchNerfDDPInfererImpl``
+(dist_render/ddp_infer/inferer_impl.py:27-145): ``load_model(H, W)`` builds the model from a
+checkpoint's ``kwargs`` and installs its forward with ``set_forward_func``; ``renderer_fn``
+walks the rays in chunks of ``render_batch_size`` and concatenates ``rgb_map``.  The forward
+installed here is ``B200GridNeRF``, i.e. the CUDA library.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from .gridnerf import B200GridNeRF
+
+
+def renderer_fn(forward: Callable, rays: torch.Tensor, chunk_size: int, **kwargs) -> torch.Tensor:
+    """The chunk loop of inferer_impl.py:95-120, including its handling of the two return
+    shapes a forward may have and its error for a result without ``rgb_map``."""
+    all_ret = []
+    n_all = rays.shape[0]
+    for chunk_idx in range(n_all // chunk_size + int(n_all % chunk_size > 0)):
+        rays_chunk = rays[chunk_idx * chunk_size:(chunk_idx + 1) * chunk_size]
+        with torch.inference_mode():
+            ret = forward(rays_chunk, **kwargs)
+        if isinstance(ret, tuple) and "rgb_map" in ret[0]:
+            all_ret.append(ret[0]["rgb_map"])
+        elif "rgb_map" in ret:
+            all_ret.append(ret["rgb_map"])
+        else:
+            raise Exception("cannot find correct key for ret")
+    if not all_ret:
+        return rays.new_zeros((0, 3))
+    return torch.cat(all_ret, 0)
+
+
+class B200NerfDDPInfererImpl:
+    """Drop-in for ``TorchNerfDDPInfererImpl``: same constructor argument (a context with
+    ``args_nerf`` and ``model_path``), same methods and properties."""
+
+    def __init__(self, context, profile_stages: bool = False, mlp_mode: int = 0) -> None:
+        self._chunk_size = context.args_nerf.render_batch_size
+        self._args = context.args_nerf
+        self._tensor_parallel = False
+        self._forward: Optional[Callable] = None
+        self._profile_stages = profile_stages
+        self._model = None
+        self._model_path = getattr(context, "model_path", None)
+        self._ckpt = getattr(context, "checkpoint", None)  # an already loaded checkpoint dict
+        self._mlp_mode = mlp_mode
+
+    @property
+    def args(self):
+        return self._args
+
+    @property
+    def tensor_parallel(self):
+        return self._tensor_parallel
+
+    @property
+    def model(self):
+        return self._model
+
+    def set_pose(self, pose):
+        pass
+
+    def edit_model(self, edit_mode):
+        pass
+
+    def set_forward_func(self, func):
+        self._forward = func
+
+    def remove_old_kwargs(self, kwargs):
+        kwargs.pop("shadingMode", None)
+        return kwargs
+
+    def set_distributed_args(self, data_parallel_local_rank, rank, data_parallel_group_world_size):
+        self._args.local_rank = data_parallel_local_rank
+        self._args.rank = rank
+        self._args.world_size = data_parallel_group_world_size
+        self._args.distributed = data_parallel_group_world_size > 1
+
+    def load_model(self, H, W):
+        if self._model is not None:
+            return
+        ckpt = self._ckpt if self._ckpt is not None else torch.load(self._model_path, map_location="cpu", weights_only=False)
+        device = getattr(self._args, "device", "cuda")
+        if device == "cuda":
+            device = f"cuda:{torch.cuda.current_device()}"
+        kwargs = dict(ckpt["kwargs"])
+        kwargs.update({"device": device, "args": self._args, "is_train": False})
+        kwargs = self.remove_old_kwargs(kwargs)
+        self._model = B200GridNeRF(**kwargs, mlp_mode=self._mlp_mode)
+        self._model.load(ckpt)
+        self.set_forward_func(self._model)
+
+    def renderer_fn(self, rays, N_samples=-1, white_bg=True, is_train=False, app_code=None):
+        if self._forward is None:
+            raise RuntimeError("load_model() has not been called")
+        return renderer_fn(self._forward, rays, self._chunk_size, N_samples=N_samples, white_bg=white_bg, is_train=is_train)
