@@ -279,3 +279,35 @@ def test_multires_single_plane_layout():
     assert (got["sigma_feature"].cpu() - sig).abs().max().item() <= 2e-6
     feats = F.linear(torch.cat(prods).T, sd["basis_mat.weight"])
     assert (got["app_features"].cpu() - feats[got["app_index"].cpu()]).abs().max().item() <= 5e-6
+
+
+@pytest.mark.parametrize("mlp_mode,tol", [(1, 5e-5), (2, 1e-4)])
+def test_tensor_core_mlp_modes(tiny, mlp_mode, tol):
+    """tcgen05 MLP: mode 1 = fp16 activations as hi + lo (two MMAs per K-step), mode 2 = single
+    fp16.  Both must stay inside the 1e-4 rgb bar of the fp32 path; sampling is unaffected."""
+    spec, field, model, rays, ref, got = tiny
+    m = cuda_model(spec, scenes.make_checkpoint(spec), mlp_mode=mlp_mode)
+    out = m.run_stages(rays.cuda(), spec.n_samples, True)
+    assert m.last_status[4] == 0, "a bounded wait expired in the tensor-core kernel"
+    assert torch.equal(out["counts"], got["counts"]) and torch.equal(out["app_index"], got["app_index"])
+    assert torch.equal(out["app_features"], got["app_features"])
+    d = (out["rgb_samples"] - got["rgb_samples"]).abs().max().item()
+    assert d <= tol, f"per-sample rgb differs from the fp32 kernel by {d:.3e}"
+    fx = load_golden("tiny_lit.npz")
+    err = (out["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+    # ragged tail: a sample count that is not a multiple of the 128-row tile
+    few = rays[4990:5003].cuda()
+    a = m.run_stages(few, spec.n_samples, True)
+    b = model.run_stages(few, spec.n_samples, True)
+    assert a["num_app"] == b["num_app"] and a["num_app"] % 128 != 0
+    assert (a["rgb_samples"] - b["rgb_samples"]).abs().max().item() <= tol
+
+
+def test_tensor_core_mlp_rejects_other_shapes():
+    spec = scenes.tiny_spec(grid=32).lit()
+    spec.fea_pe = 3
+    from landmark_b200._lib import GnrError
+
+    with pytest.raises(GnrError, match="tensor-core MLP supports"):
+        cuda_model(spec, mlp_mode=2)
