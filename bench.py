@@ -42,7 +42,7 @@ DENSITY_BYTES_PER_SAMPLE = 784      # 3 planes x 4 corners x 16 ch x 4 B + 12 B 
 APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B coordinate
 MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
 BASIS_FLOP_PER_SAMPLE = 7776        # 2 * 144 * 27 (done inside the appearance gather kernel)
-CPU_SAMPLE_RAYS = 8192
+CPU_SAMPLE_RAYS = 65536
 
 
 def peaks():
@@ -131,7 +131,7 @@ def build_scene(workload, device):
 
 def run_reference(a):
     """CPU arm: the oracle port of the reference's torch path, all host threads, one bounded
-    sample (8192 rays = image rows 536..540 of the same frame) per step."""
+    sample (CPU_SAMPLE_RAYS rays starting at image row 536 of the same frame) per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -163,7 +163,7 @@ def run_reference(a):
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": value, "unit": "Mrays/s", "cores": cores, "kind": "port",
-                         "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-540) per step, torch {torch.__version__} CPU"},
+                         "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-570) per step, torch {torch.__version__} CPU"},
         "e2e": {"value": value, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "ms_per_frame_extrapolated": dt * 1e3 * spec.height * spec.width / CPU_SAMPLE_RAYS,
     }
@@ -181,6 +181,9 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
+    ap.add_argument("--profile-case", type=int, default=0, metavar="RAYS",
+                    help="render one chunk of RAYS rays from the middle of the frame twice and exit "
+                         "(a small, self-terminating case for ncu captures)")
     a = ap.parse_args()
     if a.impl == "reference":
         run_reference(a)
@@ -214,6 +217,17 @@ def main():
     torch.cuda.empty_cache()
 
     H, W, S = spec.height, spec.width, spec.n_samples
+    if a.profile_case:
+        ids_np = tile_pixel_ids(H, W, 0, 1)
+        mid = (ids_np.shape[0] // 2 // (TILE * TILE)) * TILE * TILE
+        pix = torch.from_numpy(ids_np[mid:mid + a.profile_case]).to(device)
+        rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=pix)
+        for _ in range(2):
+            model.render_rays(rays, S, True, chunk=a.profile_case)
+            st = model.check_pending_status()
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_case_rays": int(rays.shape[0]), "valid": int(st[2]), "appearance": int(st[3])}))
+        return
     if world == 1 and a.order == "rows":
         ids_np = np.arange(H * W, dtype=np.int32)
     else:
@@ -374,7 +388,7 @@ def main():
         got, _ = model(sample.to(device), N_samples=S)
         err = (got["rgb_map"].cpu() - ref["rgb_map"]).abs().max(dim=1).values
         line["cpu_baseline"] = {"value": CPU_SAMPLE_RAYS / dt / 1e6, "unit": "Mrays/s", "cores": cores, "kind": "port",
-                                "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-540), one pass, torch {torch.__version__} CPU",
+                                "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-570), one pass, torch {torch.__version__} CPU",
                                 "rays_above_1e-4_vs_gpu": int((err > 1e-4).sum()), "max_abs_rgb_diff": float(err.max())}
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -197,6 +197,7 @@ extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
   const int A = cfg->app_dim, V = cfg->view_pe > 0 ? cfg->view_pe : 0;
   m->mlp.in_dim = A + 3 + 2 * cfg->fea_pe * A + 2 * V * 3;
   m->mlp.k1_pad = (m->mlp.in_dim + 7) / 8 * 8;
+  m->mlp.n_prod = cfg->n_pairs * ((cfg->n_app + 15) / 16 * 16);
   *out = m;
   return 0;
 }
@@ -246,6 +247,10 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
     gnr_set_error("gnr_upload_plane: bad argument (kind %d idx %d C %d H %d W %d)", kind, idx, C, H, W);
     return -1;
   }
+  if (H < 2 || W < 2 || (long long)H * W * ((C + 15) / 16 * 4) > 0x7fffffffLL) {
+    gnr_set_error("gnr_upload_plane: plane %dx%d must be at least 2x2 and fit 32-bit texel offsets", W, H);
+    return -1;
+  }
   const int expect = kind == 0 ? m->cfg.n_density : m->cfg.n_app;
   if (C != expect) {
     gnr_set_error("gnr_upload_plane: plane %d of kind %d has %d channels, config says %d", idx, kind, C, expect);
@@ -265,6 +270,8 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
   pl->plane = *buf;
   pl->H = H;
   pl->W = W;
+  pl->fw = (float)(W - 1);
+  pl->fh = (float)(H - 1);
   pl->C = Cp;
   pl->mat0 = axis_x;
   pl->mat1 = axis_y;
@@ -274,6 +281,10 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
 extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src, int C, int Ln, int axis, void* stream) {
   if (!m || !src || kind < 0 || kind > 1 || idx < 0 || idx >= m->cfg.n_pairs || Ln < 1 || axis < 0 || axis > 2) {
     gnr_set_error("gnr_upload_line: bad argument (kind %d idx %d C %d L %d)", kind, idx, C, Ln);
+    return -1;
+  }
+  if (Ln < 2) {
+    gnr_set_error("gnr_upload_line: a line needs at least 2 entries");
     return -1;
   }
   const int expect = kind == 0 ? m->cfg.n_density : m->cfg.n_app;
@@ -293,6 +304,7 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   GNR_CUDA_OK(cudaGetLastError());
   pl->line = *buf;
   pl->L = Ln;
+  pl->fl = (float)(Ln - 1);
   pl->vec = axis;
   return 0;
 }
@@ -361,8 +373,7 @@ extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1
   copy_or_zero_kernel<<<(Hd + 255) / 256, 256, 0, st>>>(b2, q.b2, Hd, Hd);
   copy_or_zero_kernel<<<1, 32, 0, st>>>(b3, q.b3, 3, 4);
   GNR_CUDA_OK(cudaGetLastError());
-  q.n_prod = m->cfg.n_pairs * padded_channels(m->cfg.n_app);
-  if (m->cfg.mlp_mode != 0) return gnr_mlp_tc_prepare(m, w1, b1, w2, b2, w3, b3, st);
+  if (m->cfg.mlp_mode != 0) return gnr_mlp_tc_prepare(m, basis_w, w1, w2, st);
   return 0;
 }
 
@@ -407,6 +418,13 @@ GnrWs gnr_ws_layout(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
   L.app_index = take((size_t)max_app * 4);
   L.app_feat = take((size_t)max_app * L.feat_stride * 4);
   L.app_rgb = take((size_t)max_app * 3 * 4);
+  if (gnr_tc_basis_fused(m)) {
+    const int terms = m->cfg.mlp_mode == 1 ? 2 : 1;
+    const size_t tiles = (size_t)(max_app + 127) / 128;
+    L.app_prod_tile = (m->mlp.n_prod / 8) * 2048;
+    L.app_prod_image = align_up(tiles * (size_t)L.app_prod_tile, 256);
+    L.app_prod = take(L.app_prod_image * terms);
+  }
   L.total = off;
   return L;
 }
@@ -532,13 +550,19 @@ static int copy_out(void* dst, const void* src, size_t bytes, cudaStream_t st) {
   return 0;
 }
 
+static int run_app_gather(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
+                          int64_t max_valid, int64_t max_app, cudaStream_t st) {
+  if (gnr_tc_basis_fused(m)) return launch_app_products(m, p, rays, n, ws, L, max_app, m->cfg.mlp_mode == 1 ? 2 : 1, st);
+  return launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st);
+}
+
 static int run_appearance(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, int64_t max_app, cudaStream_t st) {
-  GNR_LAUNCH_OK(launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
+  GNR_LAUNCH_OK(run_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
   if (m->cfg.mlp_mode == 0) {
     GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
   } else {
-    GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, st));
+    GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, /*write_features=*/1, st));
   }
   return 0;
 }
@@ -660,14 +684,14 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   }
   {
     StageScope sc(m, GNR_STAGE_APP_GATHER, 1, st);
-    GNR_LAUNCH_OK(launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
+    GNR_LAUNCH_OK(run_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
   }
   {
     StageScope sc(m, GNR_STAGE_MLP, 1, st);
     if (m->cfg.mlp_mode == 0) {
       GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
     } else {
-      GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, st));
+      GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, /*write_features=*/0, st));
     }
   }
   {

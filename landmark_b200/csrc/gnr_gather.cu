@@ -6,6 +6,8 @@
 // compute_densityfeature / compute_appfeature (app/models/gridnerf_sequential.py:779-871):
 // index = ((x + 1) / 2) * (size - 1); the weight of a corner is the product of the distances
 // to the opposite corner; taps outside the grid contribute zero.
+#include <cuda_fp16.h>
+
 #include "gnr_internal.cuh"
 
 namespace {
@@ -27,40 +29,35 @@ __device__ __forceinline__ float4 f4_fma(float4 a, float s, float4 c) {
 __device__ __forceinline__ float4 f4_mul(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
 
 // Products plane(x, y) * line(l) for the 4 J channels this lane owns.
+// Valid samples lie inside the closed box, so the continuous index is clamped to the grid
+// and the lower corner to size - 2: no tap can fall outside and no bounds test is needed (a
+// point exactly on the upper face then takes the last texel with weight 1, which is what
+// zero padding gives as well).  All offsets are 32-bit float4 indices.
 template <int J>
 __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float y, float z, int c4, float4 (&prod)[J]) {
   const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-  const float ix = (u + 1.0f) * 0.5f * (float)(pl.W - 1);
-  const float iy = (v + 1.0f) * 0.5f * (float)(pl.H - 1);
-  const float il = (l + 1.0f) * 0.5f * (float)(pl.L - 1);
-  const float fx = floorf(ix), fy = floorf(iy), fl = floorf(il);
-  const int x0 = (int)fx, y0 = (int)fy, l0 = (int)fl;
-  const bool x0ok = (unsigned)x0 < (unsigned)pl.W, x1ok = (unsigned)(x0 + 1) < (unsigned)pl.W;
-  const bool y0ok = (unsigned)y0 < (unsigned)pl.H, y1ok = (unsigned)(y0 + 1) < (unsigned)pl.H;
-  const bool l0ok = (unsigned)l0 < (unsigned)pl.L, l1ok = (unsigned)(l0 + 1) < (unsigned)pl.L;
-  const float ax1 = ix - fx, ax0 = (fx + 1.0f) - ix;
-  const float ay1 = iy - fy, ay0 = (fy + 1.0f) - iy;
-  const float w_nw = (x0ok && y0ok) ? ax0 * ay0 : 0.0f, w_ne = (x1ok && y0ok) ? ax1 * ay0 : 0.0f;
-  const float w_sw = (x0ok && y1ok) ? ax0 * ay1 : 0.0f, w_se = (x1ok && y1ok) ? ax1 * ay1 : 0.0f;
-  const float w_l0 = l0ok ? (fl + 1.0f) - il : 0.0f, w_l1 = l1ok ? il - fl : 0.0f;
-  const int xc0 = min(max(x0, 0), pl.W - 1), xc1 = min(max(x0 + 1, 0), pl.W - 1);
-  const int yc0 = min(max(y0, 0), pl.H - 1), yc1 = min(max(y0 + 1, 0), pl.H - 1);
-  const int lc0 = min(max(l0, 0), pl.L - 1), lc1 = min(max(l0 + 1, 0), pl.L - 1);
-  const int c4n = pl.C >> 2;
+  const float ix = fminf(fmaxf((u + 1.0f) * 0.5f * pl.fw, 0.0f), pl.fw);
+  const float iy = fminf(fmaxf((v + 1.0f) * 0.5f * pl.fh, 0.0f), pl.fh);
+  const float il = fminf(fmaxf((l + 1.0f) * 0.5f * pl.fl, 0.0f), pl.fl);
+  const int x0 = min((int)ix, pl.W - 2), y0 = min((int)iy, pl.H - 2), l0 = min((int)il, pl.L - 2);
+  const float ax1 = ix - (float)x0, ay1 = iy - (float)y0, al1 = il - (float)l0;
+  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
+  const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
+  const uint32_t c4n = (uint32_t)pl.C >> 2;
+  const uint32_t nw = ((uint32_t)y0 * (uint32_t)pl.W + (uint32_t)x0) * c4n + (uint32_t)c4;
+  const uint32_t sw = nw + (uint32_t)pl.W * c4n;
+  const uint32_t ln = (uint32_t)l0 * c4n + (uint32_t)c4;
   const float4* pb = reinterpret_cast<const float4*>(pl.plane);
   const float4* lb = reinterpret_cast<const float4*>(pl.line);
-  const size_t nw = ((size_t)yc0 * pl.W + xc0) * c4n, ne = ((size_t)yc0 * pl.W + xc1) * c4n;
-  const size_t sw = ((size_t)yc1 * pl.W + xc0) * c4n, se = ((size_t)yc1 * pl.W + xc1) * c4n;
   float4 v_nw[J], v_ne[J], v_sw[J], v_se[J], v_l0[J], v_l1[J];
 #pragma unroll
   for (int j = 0; j < J; ++j) {
-    const int q = j * 4 + c4;
-    v_nw[j] = __ldg(pb + nw + q);
-    v_ne[j] = __ldg(pb + ne + q);
-    v_sw[j] = __ldg(pb + sw + q);
-    v_se[j] = __ldg(pb + se + q);
-    v_l0[j] = __ldg(lb + (size_t)lc0 * c4n + q);
-    v_l1[j] = __ldg(lb + (size_t)lc1 * c4n + q);
+    v_nw[j] = __ldg(pb + nw + 4 * j);
+    v_ne[j] = __ldg(pb + nw + c4n + 4 * j);
+    v_sw[j] = __ldg(pb + sw + 4 * j);
+    v_se[j] = __ldg(pb + sw + c4n + 4 * j);
+    v_l0[j] = __ldg(lb + ln + 4 * j);
+    v_l1[j] = __ldg(lb + ln + c4n + 4 * j);
   }
 #pragma unroll
   for (int j = 0; j < J; ++j) {
@@ -68,7 +65,7 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
     pv = f4_fma(v_ne[j], w_ne, pv);
     pv = f4_fma(v_sw[j], w_sw, pv);
     pv = f4_fma(v_se[j], w_se, pv);
-    float4 lv = f4_fma(v_l1[j], w_l1, f4_scale(v_l0[j], w_l0));
+    float4 lv = f4_fma(v_l1[j], al1, f4_scale(v_l0[j], al0));
     prod[j] = f4_mul(pv, lv);
   }
 }
@@ -92,23 +89,38 @@ __device__ __forceinline__ float density_activation(float f, float shift, int ac
   return x > 20.0f ? x : log1pf(expf(x));
 }
 
-template <int J>
+// Contiguous share of [0, total) for this CTA, in units of the kBlock / 4 samples one CTA
+// iteration covers.
+__device__ __forceinline__ void cta_range(long long total, long long& beg, long long& end) {
+  constexpr long long kStep = kBlock / 4;
+  const long long steps = (total + kStep - 1) / kStep;
+  const long long per = (steps + gridDim.x - 1) / gridDim.x;
+  beg = min(total, (long long)blockIdx.x * per * kStep);
+  end = min(total, beg + per * kStep);
+}
+
+template <int J, int NP>
 __global__ void __launch_bounds__(kBlock)
 density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
                const uint32_t* __restrict__ ids, const int32_t* __restrict__ total_ptr, long long capacity,
                float shift, int act, float* __restrict__ sigma_feat, float* __restrict__ sigma) {
   const int c4 = threadIdx.x & 3;
-  long long total = min((long long)*total_ptr, capacity);
-  const long long stride = (long long)gridDim.x * (kBlock / 4);
+  const long long total = min((long long)*total_ptr, capacity);
+  // Each CTA walks one contiguous range of the (ray-major) list, so that the texels a ray
+  // touches are still in this SM's L1 when the next samples and the neighbouring ray need them.
+  long long range_beg, range_end;
+  cta_range(total, range_beg, range_end);
   // whole warps iterate together so that the quad shuffles below are always convergent
-  for (long long base = (long long)blockIdx.x * (kBlock / 4) + (threadIdx.x >> 5) * 8; base < total; base += stride) {
+  for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
     const long long i = base + ((threadIdx.x & 31) >> 2);
-    const bool active = i < total;
+    const bool active = i < range_end;
     float acc = 0.0f;
     if (active) {
       float x, y, z;
       sample_xyz(p, rays, t_min, __ldg(ids + i), x, y, z);
-      for (int pi = 0; pi < planes.n; ++pi) {
+      const int n_planes = NP > 0 ? NP : planes.n;
+#pragma unroll
+      for (int pi = 0; pi < n_planes; ++pi) {
         float4 prod[J];
         pair_products<J>(planes.p[pi], x, y, z, c4, prod);
         float s = 0.0f;
@@ -144,11 +156,12 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ 
   __syncthreads();
 
   const int c4 = threadIdx.x & 3;
-  long long total = min((long long)*total_ptr, capacity);
-  const long long stride = (long long)gridDim.x * (kBlock / 4);
-  for (long long base = (long long)blockIdx.x * (kBlock / 4) + (threadIdx.x >> 5) * 8; base < total; base += stride) {
+  const long long total = min((long long)*total_ptr, capacity);
+  long long range_beg, range_end;
+  cta_range(total, range_beg, range_end);
+  for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
     const long long j_app = base + ((threadIdx.x & 31) >> 2);
-    const bool active = j_app < total;
+    const bool active = j_app < range_end;
     float acc[kFeat];
 #pragma unroll
     for (int o = 0; o < kFeat; ++o) acc[o] = 0.0f;
@@ -191,6 +204,56 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ 
   }
 }
 
+// Appearance gather for the tensor-core path: the plane x line products themselves are the
+// K dimension of the basis projection, so they are written as fp16 straight into the MMA
+// operand layout of their 128-sample tile: element (row r, k) of tile t at byte
+//   t * tile_bytes + (k / 8) * 2048 + r * 16 + (k % 8) * 2,     k = pair * C + channel.
+// With TA == 2 the fp16 rounding residual goes to a second image of the same shape.
+template <int J, int NP, int TA>
+__global__ void __launch_bounds__(kBlock)
+app_products_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
+                    const uint32_t* __restrict__ ids, const int32_t* __restrict__ app_index,
+                    const int32_t* __restrict__ total_ptr, long long capacity, unsigned char* __restrict__ prod_hi,
+                    unsigned char* __restrict__ prod_lo, int tile_bytes) {
+  const int c4 = threadIdx.x & 3;
+  const long long total = min((long long)*total_ptr, capacity);
+  long long range_beg, range_end;
+  cta_range(total, range_beg, range_end);
+  for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
+    const long long j_app = base + ((threadIdx.x & 31) >> 2);
+    if (j_app >= range_end) continue;
+    float x, y, z;
+    sample_xyz(p, rays, t_min, __ldg(ids + __ldg(app_index + j_app)), x, y, z);
+    const long long tile = j_app >> 7;
+    const int row = (int)(j_app & 127);
+    const size_t out0 = (size_t)tile * tile_bytes + (size_t)row * 16 + (size_t)(c4 & 1) * 8;
+    const int n_planes = NP > 0 ? NP : planes.n;
+#pragma unroll
+    for (int pi = 0; pi < n_planes; ++pi) {
+      float4 prod[J];
+      pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+#pragma unroll
+      for (int j = 0; j < J; ++j) {
+        const size_t at = out0 + (size_t)(pi * 2 * J + 2 * j + (c4 >> 1)) * 2048;
+        const __half2 h0 = __floats2half2_rn(prod[j].x, prod[j].y), h1 = __floats2half2_rn(prod[j].z, prod[j].w);
+        uint2 hv;
+        hv.x = *reinterpret_cast<const uint32_t*>(&h0);
+        hv.y = *reinterpret_cast<const uint32_t*>(&h1);
+        *reinterpret_cast<uint2*>(prod_hi + at) = hv;
+        if (TA == 2) {
+          const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+          const __half2 l0 = __floats2half2_rn(prod[j].x - f0.x, prod[j].y - f0.y);
+          const __half2 l1 = __floats2half2_rn(prod[j].z - f1.x, prod[j].w - f1.y);
+          uint2 lv;
+          lv.x = *reinterpret_cast<const uint32_t*>(&l0);
+          lv.y = *reinterpret_cast<const uint32_t*>(&l1);
+          *reinterpret_cast<uint2*>(prod_lo + at) = lv;
+        }
+      }
+    }
+  }
+}
+
 PlaneSet make_set(const GnrPlane* src, int n) {
   PlaneSet s;
   s.n = n;
@@ -205,15 +268,21 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* ray
   (void)n;
   PlaneSet set = make_set(m->den, m->cfg.n_pairs);
   const int J = m->den[0].C / 16;
-  const int grid = m->sm_count * 8;
+  const int grid = m->sm_count * 4;
   const float* t_min = (const float*)(ws + L.t_min);
   const uint32_t* ids = (const uint32_t*)(ws + L.ids);
   const int32_t* total = (const int32_t*)(ws + L.offsets) + n;
   float* sf = (float*)(ws + L.sigma_feat);
   float* sg = (float*)(ws + L.sigma);
-#define GNR_DEN(JJ)                                                                                          \
-  density_kernel<JJ><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,         \
-                                              m->cfg.density_shift, m->cfg.density_act, sf, sg)
+#define GNR_DEN(JJ)                                                                                               \
+  do {                                                                                                            \
+    if (set.n == 3)                                                                                               \
+      density_kernel<JJ, 3><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,       \
+                                                     m->cfg.density_shift, m->cfg.density_act, sf, sg);           \
+    else                                                                                                          \
+      density_kernel<JJ, 0><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,       \
+                                                     m->cfg.density_shift, m->cfg.density_act, sf, sg);           \
+  } while (0)
   switch (J) {
     case 1: GNR_DEN(1); break;
     case 2: GNR_DEN(2); break;
@@ -251,5 +320,36 @@ int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* 
     default: gnr_set_error("appearance channels (padded) %d not supported (16..64)", m->app[0].C); return -1;
   }
 #undef GNR_APP
+  return (int)cudaGetLastError();
+}
+
+int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                        const GnrWs& L, int64_t max_app, int terms, cudaStream_t st) {
+  PlaneSet set = make_set(m->app, m->cfg.n_pairs);
+  const int J = m->app[0].C / 16;
+  const int grid = m->sm_count * 4;
+  const float* t_min = (const float*)(ws + L.t_min);
+  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
+  const int32_t* app_index = (const int32_t*)(ws + L.app_index);
+  const int32_t* total = (const int32_t*)(ws + L.app_offsets) + n;
+  unsigned char* hi = (unsigned char*)(ws + L.app_prod);
+  unsigned char* lo = hi + L.app_prod_image;
+  const int tile_bytes = L.app_prod_tile;
+#define GNR_PRD(JJ, NPP, TT)                                                                                     \
+  app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, app_index, total,          \
+                                                            (long long)max_app, hi, lo, tile_bytes)
+  if (J == 3 && set.n == 3) {
+    if (terms == 2) GNR_PRD(3, 3, 2); else GNR_PRD(3, 3, 1);
+  } else if (J == 1) {
+    if (terms == 2) GNR_PRD(1, 0, 2); else GNR_PRD(1, 0, 1);
+  } else if (J == 2) {
+    if (terms == 2) GNR_PRD(2, 0, 2); else GNR_PRD(2, 0, 1);
+  } else if (J == 3) {
+    if (terms == 2) GNR_PRD(3, 0, 2); else GNR_PRD(3, 0, 1);
+  } else {
+    gnr_set_error("appearance channels (padded) %d not supported by the tensor-core path", m->app[0].C);
+    return -1;
+  }
+#undef GNR_PRD
   return (int)cudaGetLastError();
 }

@@ -16,6 +16,7 @@ struct GnrPlane {
   const float* plane;
   const float* line;
   int H, W, L, C;
+  float fw, fh, fl;  // (float)(W - 1), (H - 1), (L - 1)
   int mat0, mat1, vec;  // coordinate axes: plane x <- xyz[mat0], plane y <- xyz[mat1], line <- xyz[vec]
 };
 
@@ -82,7 +83,9 @@ struct GnrSampleParams {
 // Workspace layout (byte offsets), identical for every stage call with the same arguments.
 struct GnrWs {
   size_t status, t_min, words, counts, offsets, block_sums, ids, sigma_feat, sigma, weight, acc, depth,
-      app_counts, app_offsets, app_index, app_feat, app_rgb, total;
+      app_counts, app_offsets, app_index, app_feat, app_rgb, app_prod, total;
+  size_t app_prod_image;  // bytes of one fp16 product image (hi), 0 if the tensor-core path is off
+  int app_prod_tile;      // bytes of one 128-sample tile of that image
   int feat_stride;  // floats per appearance feature row (app_dim rounded up to 4)
   long long max_valid, max_app;  // capacities of the two compacted lists
   long long n_rays;
@@ -107,17 +110,19 @@ int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, c
                        int64_t max_valid, int64_t max_app, cudaStream_t st);
 int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
                       const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st);
+int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
+                        const GnrWs& L, int64_t max_app, int terms, cudaStream_t st);
+int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
                     int64_t max_app, cudaStream_t st);
 int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                  int64_t max_app, cudaStream_t st);
+                  int64_t max_app, int write_features, cudaStream_t st);
 int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
                      float* depth_map, cudaStream_t st);
 int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,
                           int32_t* status, int total_slot, int overflow_slot, int64_t capacity,
                           cudaStream_t st);
-int gnr_mlp_tc_prepare(GnrModel* m, const float* w1, const float* b1, const float* w2, const float* b2,
-                       const float* w3, const float* b3, cudaStream_t st);
+int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, cudaStream_t st);
 
 #define GNR_CUDA_OK(expr)                                                              \
   do {                                                                                 \

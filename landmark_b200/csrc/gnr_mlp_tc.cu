@@ -1,27 +1,33 @@
-// Appearance MLP on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM).
+// Basis projection + appearance MLP on the 5th-generation tensor cores (tcgen05.mma with
+// accumulators in tensor memory), one kernel.
 //
-// MLPRender_Fea.forward (app/models/mlp_render_fea.py:44-68): 150 -> 128 -> 128 -> 3.  One
-// persistent CTA per SM keeps W1 and W2 in shared memory as fp16 in the tensor core's
-// K-major "interleaved" (no-swizzle) operand layout and walks tiles of 128 appearance samples.
-// A CTA has NSLOT groups of 128 threads; each group owns one tile at a time (thread = sample
-// row = TMEM lane) and its own 128 TMEM columns, so that while one group runs its CUDA-core
-// phases (positional encoding, bias + ReLU, the 128 -> 3 layer, sigmoid) the other group's
-// MMAs occupy the tensor pipe.
+// compute_appfeature's Linear(144 -> 27) (app/models/gridnerf_sequential.py:678,864-871) and
+// MLPRender_Fea.forward (app/models/mlp_render_fea.py:44-68): 150 -> 128 -> 128 -> 3, sigmoid.
 //
-//   per tile:  build A1[128 x 160] (fp16, optionally hi + lo)      -> smem
-//              D = A1 * W1^T   (10 K-steps of tcgen05.mma M128 N128 K16, fp32 accumulate)
-//              A2 = relu(D + b1) (fp16, optionally hi + lo)         TMEM -> registers -> smem
-//              D = A2 * W2^T   (8 K-steps)
-//              rgb = sigmoid(W3 * relu(D + b2) + b3)                TMEM -> registers, fp32
+// One persistent CTA per SM keeps the basis matrix, W1 and W2 in shared memory as fp16 in the
+// tensor core's K-major "interleaved" (no-swizzle) operand layout and walks tiles of 128
+// appearance samples.  A CTA has NSLOT groups of 128 threads; a group owns one tile at a time
+// (thread = sample row = TMEM lane), its own operand buffer and its own 160 TMEM columns, so
+// while one group runs its CUDA-core phases another group's MMAs occupy the tensor pipe.
 //
-// Operand layout (both A and B): element (row r, k) lives at byte  (k / 8) * 2048 + r * 16 +
-// (k % 8) * 2; i.e. 8 rows x 16 B form one contiguous 128 B core matrix, row groups are 128 B
-// apart (stride byte offset) and the two K halves of one MMA are 2048 B apart (leading byte
-// offset).  TA = 2 adds the fp16 rounding residual of the activations as a second MMA per
-// K-step (activations then carry ~22 mantissa bits; weights stay single fp16).
+//   per tile:  A0[128 x 144] fp16 plane x line products, written by the gather kernel in
+//              operand layout, arrive by one bulk async copy (cp.async.bulk -> mbarrier)
+//              F  = A0 * Wb^T           (9 K-steps of tcgen05.mma M128 N32 K16, fp32 accumulate)
+//              A1 = [F, view, sin/cos(F 2^f), sin/cos(view 2^f)]      TMEM -> registers -> smem
+//              D  = A1 * W1^T           (10 K-steps, M128 N128 K16)
+//              A2 = relu(D + b1)                                      TMEM -> registers -> smem
+//              D  = A2 * W2^T           (8 K-steps)
+//              rgb = sigmoid(W3 relu(D + b2) + b3)                    TMEM -> registers, fp32
 //
-// Every wait on an mbarrier is bounded; when it expires the kernel raises
-// status[GNR_ST_WAIT_EXPIRED], stops taking tiles, frees its TMEM and returns.
+// Operand layout (A and B alike): element (row r, k) at byte (k / 8) * LBO + r * 16 + (k % 8) * 2:
+// 8 rows x 16 B form one contiguous 128 B core matrix, row groups are 128 B apart (stride byte
+// offset), the two K halves of one MMA are LBO = rows * 16 bytes apart (leading byte offset).
+// TA = 2 carries the fp16 rounding residual of every activation (and product) as a second
+// operand and a second MMA per K-step (activations then hold ~22 mantissa bits; weights stay
+// single fp16).
+//
+// Every wait on an mbarrier is bounded; when one expires the group raises
+// status[GNR_ST_WAIT_EXPIRED], stops taking tiles, and the CTA frees its TMEM and returns.
 #include <cuda_fp16.h>
 
 #include "gnr_internal.cuh"
@@ -35,28 +41,34 @@ constexpr int K1 = 160, K2 = 128;                              // padded to the 
 constexpr int KG1 = K1 / 8, KG2 = K2 / 8;                      // 16-byte K groups
 constexpr int ROWS = 128;
 constexpr int KG_BYTES = ROWS * 16;                            // 2048: one K group of all rows
+constexpr int NB = 32;                                         // basis outputs padded to the MMA N
+constexpr int KGB_BYTES = NB * 16;                             // 512: one K group of the basis operand
+constexpr int MAX_K0 = 160;                                    // products per sample the A buffer can hold
 constexpr int W1_BYTES = KG1 * KG_BYTES, W2_BYTES = KG2 * KG_BYTES, A_BYTES = KG1 * KG_BYTES;
+constexpr int WB_BYTES = (MAX_K0 / 8) * KGB_BYTES;
 constexpr int FEAT_STRIDE = 28;
+constexpr int COLS_PER_SLOT = HID + NB;  // D (128) + F (32)
 constexpr uint32_t kWaitLimit = 1u << 20;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-  // K-major, no swizzle: start address, leading byte offset 2048, stride byte offset 128 (all >> 4), version 1
-  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(KG_BYTES >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) |
+// K-major, no swizzle: start address, leading byte offset, stride byte offset 128 (all >> 4), version 1
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(128 >> 4) << 32) |
          ((uint64_t)1 << 46);
 }
 
-// fp16 x fp16 -> fp32, A and B K-major, M = 128, N = 128
-constexpr uint32_t kIdesc = (1u << 4) | ((uint32_t)(HID >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+// fp16 x fp16 -> fp32, A and B K-major, M = 128
+constexpr uint32_t kIdescHid = (1u << 4) | ((uint32_t)(HID >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr uint32_t kIdescBasis = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t"
       ".reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -101,6 +113,16 @@ __device__ __forceinline__ bool group_wait(uint32_t mbar, uint32_t parity, int b
   return ok;
 }
 
+// Bulk async copy global -> shared, completion counted in bytes on an mbarrier.
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t mbar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+               "l"(src), "r"(bytes), "r"(mbar)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32"
@@ -112,6 +134,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr));
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// sin and cos for operands that are about to be rounded to fp16: two-constant reduction by
+// 2 pi, then the hardware approximations (absolute error ~5e-7 on the reduced range).
+__device__ __forceinline__ void sincos_reduced(float x, float& s, float& c) {
+  const float k = rintf(x * 0.15915494309189535f);
+  float r = fmaf(-k, 6.2831854820251465f, x);
+  r = fmaf(-k, -1.7484555e-07f, r);
+  s = __sinf(r);
+  c = __cosf(r);
 }
 
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
@@ -152,8 +184,13 @@ struct TcArgs {
   const int32_t* app_index;
   const int32_t* total_ptr;
   long long capacity;
-  const float* feat;
-  const unsigned char* w_image;  // [W1 fp16 operand image][W2 fp16 operand image]
+  const float* feat_in;           // BASIS == false: features from the CUDA-core gather
+  float* feat_out;                // BASIS == true: optional copy of the projected features
+  const unsigned char* prod_hi;   // BASIS == true: fp16 product tiles in operand layout
+  const unsigned char* prod_lo;
+  int tile_bytes;                 // bytes of one product tile (k0 / 8 * 2048)
+  int k0;                         // products per sample
+  const unsigned char* w_image;   // [basis fp16 operand image (WB_BYTES)][W1 image][W2 image]
   const float* w3;
   const float* b1;
   const float* b2;
@@ -163,28 +200,30 @@ struct TcArgs {
   int kbits;
 };
 
-template <int TA, int NSLOT>
+template <int TA, int NSLOT, bool BASIS>
 __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
-  unsigned char* s_w1 = smem;
+  unsigned char* s_wb = smem;
+  unsigned char* s_w1 = s_wb + WB_BYTES;
   unsigned char* s_w2 = s_w1 + W1_BYTES;
   unsigned char* s_a = s_w2 + W2_BYTES;  // [NSLOT][TA][A_BYTES]
   float* s_w3 = reinterpret_cast<float*>(s_a + NSLOT * TA * A_BYTES);
   float* s_b1 = s_w3 + 3 * HID;
   float* s_b2 = s_b1 + HID;
   float* s_b3 = s_b2 + HID;
-  uint64_t* s_mbar = reinterpret_cast<uint64_t*>(s_b3 + 4);
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_mbar + NSLOT);
+  uint64_t* s_mbar = reinterpret_cast<uint64_t*>(s_b3 + 4);  // [NSLOT][2]: MMA completion, bulk-copy completion
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_mbar + 2 * NSLOT);
   volatile uint32_t* s_flag = s_tmem + 1 + (threadIdx.x >> 7);  // per-group outcome of the last wait
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr uint32_t kTmemCols = (NSLOT * COLS_PER_SLOT <= 256) ? 256u : 512u;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int slot = tid >> 7, row = tid & 127;
 
   // ---- one-time set-up: weights -> smem, mbarriers, TMEM ---------------------------------------
   {
     const uint4* src = reinterpret_cast<const uint4*>(a.w_image);
-    uint4* dst = reinterpret_cast<uint4*>(s_w1);
-    for (int i = tid; i < (W1_BYTES + W2_BYTES) / 16; i += NSLOT * 128) dst[i] = src[i];
+    uint4* dst = reinterpret_cast<uint4*>(s_wb);
+    for (int i = tid; i < (WB_BYTES + W1_BYTES + W2_BYTES) / 16; i += NSLOT * 128) dst[i] = src[i];
     for (int i = tid; i < 3 * HID; i += NSLOT * 128) s_w3[i] = a.w3[i];
     for (int i = tid; i < HID; i += NSLOT * 128) {
       s_b1[i] = a.b1[i];
@@ -192,13 +231,13 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     }
     if (tid < 4) s_b3[tid] = a.b3[tid];
     if (tid == 0) {
-      for (int s = 0; s < NSLOT; ++s)
+      for (int s = 0; s < 2 * NSLOT; ++s)
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_mbar[s])));
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
-                   "r"((uint32_t)(NSLOT * HID < 32 ? 32 : NSLOT * HID)));
+                   "r"(kTmemCols));
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     proxy_fence();
@@ -207,29 +246,76 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     tc_fence_after();
   }
   const uint32_t tmem_base = *s_tmem;
-  const uint32_t d_tmem = tmem_base + (uint32_t)(slot * HID);                        // this group's accumulator
-  const uint32_t my_taddr = d_tmem + ((uint32_t)((warp & 3) * 32) << 16);            // this warp's lane quarter
+  const uint32_t d_tmem = tmem_base + (uint32_t)(slot * COLS_PER_SLOT);     // this group's D accumulator
+  const uint32_t f_tmem = d_tmem + HID;                                     // this group's feature accumulator
+  const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;              // this warp's TMEM lane quarter
   unsigned char* a_hi = s_a + (slot * TA) * A_BYTES;
   unsigned char* a_lo = a_hi + (TA == 2 ? A_BYTES : 0);
   const uint32_t a_hi_addr = smem_u32(a_hi), a_lo_addr = smem_u32(a_lo);
-  const uint32_t w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2);
-  const uint32_t mbar = smem_u32(&s_mbar[slot]);
+  const uint32_t wb_addr = smem_u32(s_wb), w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2);
+  const uint32_t mbar = smem_u32(&s_mbar[2 * slot]), tbar = smem_u32(&s_mbar[2 * slot + 1]);
   const int bar_id = 1 + slot;  // named barrier of this group (0 is __syncthreads)
-  uint32_t parity = 0;
+  uint32_t parity = 0, tparity = 0;
+  bool copy_pending = false;
 
   const long long total = min((long long)*a.total_ptr, a.capacity);
   const long long n_tiles = (total + ROWS - 1) / ROWS;
+  const long long tile_stride = (long long)gridDim.x * NSLOT;
+  const uint32_t copy_bytes = (uint32_t)a.tile_bytes;
 
-  for (long long tile = (long long)blockIdx.x * NSLOT + slot; tile < n_tiles; tile += (long long)gridDim.x * NSLOT) {
+  auto start_copy = [&](long long t) {
+    // one thread: announce the bytes, then start the copies of the tile's operand image(s)
+    mbar_expect_tx(tbar, copy_bytes * TA);
+    bulk_load(a_hi_addr, a.prod_hi + (size_t)t * copy_bytes, copy_bytes, tbar);
+    if (TA == 2) bulk_load(a_lo_addr, a.prod_lo + (size_t)t * copy_bytes, copy_bytes, tbar);
+  };
+
+  long long tile = (long long)blockIdx.x * NSLOT + slot;
+  if (BASIS && tile < n_tiles) {
+    if (row == 0) start_copy(tile);
+    copy_pending = true;
+  }
+
+  for (; tile < n_tiles; tile += tile_stride) {
     const long long j = tile * ROWS + row;
     const bool live = j < total;
+    float f[32];
 
-    // ---- phase 1: this row of the layer-1 input ---------------------------------------------
-    {
-      float f[FEAT_STRIDE];
-      float view[3] = {0.0f, 0.0f, 0.0f};
+    if (BASIS) {
+      // ---- phase 0: F = A0 * Wb^T ---------------------------------------------------------------
+      const bool arrived = group_wait(tbar, tparity, bar_id, row, s_flag);
+      if (!arrived) {
+        if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
+        break;
+      }
+      copy_pending = false;
+      tparity ^= 1;
+      if (row == 0) {
+        const int ksteps = a.k0 >> 4;
+        for (int ks = 0; ks < ksteps; ++ks) {
+          const uint64_t bd = make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES);
+          mma_f16(f_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, ks > 0 ? 1u : 0u);
+          if (TA == 2) mma_f16(f_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, 1u);
+        }
+        mma_commit(mbar);
+      }
+      if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
+        if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
+        break;
+      }
+      parity ^= 1;
+      uint32_t v[32];
+      tmem_ld32(f_tmem + lane_off, v);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+      if (a.feat_out != nullptr && live) {
+        float4* fo = reinterpret_cast<float4*>(a.feat_out + (size_t)j * FEAT_STRIDE);
+#pragma unroll
+        for (int q = 0; q < FEAT_STRIDE / 4; ++q) fo[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      }
+    } else {
       if (live) {
-        const float4* fr = reinterpret_cast<const float4*>(a.feat + (size_t)j * FEAT_STRIDE);
+        const float4* fr = reinterpret_cast<const float4*>(a.feat_in + (size_t)j * FEAT_STRIDE);
 #pragma unroll
         for (int q = 0; q < FEAT_STRIDE / 4; ++q) {
           const float4 v = __ldg(fr + q);
@@ -238,24 +324,31 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
           f[4 * q + 2] = v.z;
           f[4 * q + 3] = v.w;
         }
+      } else {
+#pragma unroll
+        for (int q = 0; q < FEAT_STRIDE; ++q) f[q] = 0.0f;
+      }
+    }
+
+    // ---- phase 1: this row of the layer-1 input ---------------------------------------------
+    {
+      float view[3] = {0.0f, 0.0f, 0.0f};
+      if (live) {
         const uint32_t ray = __ldg(a.ids + __ldg(a.app_index + j)) >> a.kbits;
         view[0] = __ldg(a.rays + (size_t)ray * 6 + 3);
         view[1] = __ldg(a.rays + (size_t)ray * 6 + 4);
         view[2] = __ldg(a.rays + (size_t)ray * 6 + 5);
-      } else {
-#pragma unroll
-        for (int q = 0; q < FEAT_STRIDE; ++q) f[q] = 0.0f;
       }
       float x[K1];
 #pragma unroll
       for (int i = 0; i < APP; ++i) x[i] = f[i];
 #pragma unroll
       for (int i = 0; i < 3; ++i) x[APP + i] = view[i];
-      // sin/cos of v and 2 v: one accurate sincos, then the double-angle identities
+      // sin/cos of v and 2 v: one sincos, then the double-angle identities
 #pragma unroll
       for (int i = 0; i < APP; ++i) {
         float s, c;
-        sincosf(f[i], &s, &c);
+        sincos_reduced(f[i], s, c);
         x[APP + 3 + 2 * i] = s;
         x[APP + 3 + 2 * i + 1] = 2.0f * s * c;
         x[APP + 3 + 2 * APP + 2 * i] = c;
@@ -264,7 +357,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
         float s, c;
-        sincosf(view[i], &s, &c);
+        sincos_reduced(view[i], s, c);
         x[APP + 3 + 4 * APP + 2 * i] = s;
         x[APP + 3 + 4 * APP + 2 * i + 1] = 2.0f * s * c;
         x[APP + 3 + 4 * APP + 6 + 2 * i] = c;
@@ -280,6 +373,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
         store_group<TA>(a_hi, a_lo, kg, row, g);
       }
     }
+    tc_fence_before();
     proxy_fence();
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 
@@ -288,9 +382,9 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < K1 / 16; ++ks) {
-        const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES);
-        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES), bd, ks > 0 ? 1u : 0u);
-        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES), bd, 1u);
+        const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES);
+        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
+        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
       }
       mma_commit(mbar);
     }
@@ -304,7 +398,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
 #pragma unroll
     for (int cb = 0; cb < HID / 32; ++cb) {
       uint32_t v[32];
-      tmem_ld32(my_taddr + cb * 32, v);
+      tmem_ld32(d_tmem + lane_off + cb * 32, v);
 #pragma unroll
       for (int g8 = 0; g8 < 4; ++g8) {
         float g[8];
@@ -322,9 +416,9 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       tc_fence_after();
 #pragma unroll
       for (int ks = 0; ks < K2 / 16; ++ks) {
-        const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES);
-        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES), bd, ks > 0 ? 1u : 0u);
-        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES), bd, 1u);
+        const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES, KG_BYTES);
+        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
+        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
       }
       mma_commit(mbar);
     }
@@ -333,20 +427,32 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       break;
     }
     parity ^= 1;
+    // the operand buffer is free again: fetch the next tile's products while phase 3 runs
+    if (BASIS && tile + tile_stride < n_tiles) {
+      if (row == 0) start_copy(tile + tile_stride);
+      copy_pending = true;
+    }
 
     // ---- phase 3: rgb = sigmoid(W3 relu(D + b2) + b3), fp32 on the CUDA cores ------------------
     float o0 = s_b3[0], o1 = s_b3[1], o2 = s_b3[2];
 #pragma unroll
     for (int cb = 0; cb < HID / 32; ++cb) {
       uint32_t v[32];
-      tmem_ld32(my_taddr + cb * 32, v);
+      tmem_ld32(d_tmem + lane_off + cb * 32, v);
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        const int c = cb * 32 + e;
-        const float h = fmaxf(__uint_as_float(v[e]) + s_b2[c], 0.0f);
-        o0 = fmaf(h, s_w3[c], o0);
-        o1 = fmaf(h, s_w3[HID + c], o1);
-        o2 = fmaf(h, s_w3[2 * HID + c], o2);
+      for (int e4 = 0; e4 < 8; ++e4) {
+        const int c = cb * 32 + e4 * 4;
+        const float4 bb = *reinterpret_cast<const float4*>(s_b2 + c);
+        const float4 wr = *reinterpret_cast<const float4*>(s_w3 + c);
+        const float4 wg = *reinterpret_cast<const float4*>(s_w3 + HID + c);
+        const float4 wb = *reinterpret_cast<const float4*>(s_w3 + 2 * HID + c);
+        const float h0 = fmaxf(__uint_as_float(v[e4 * 4 + 0]) + bb.x, 0.0f);
+        const float h1 = fmaxf(__uint_as_float(v[e4 * 4 + 1]) + bb.y, 0.0f);
+        const float h2 = fmaxf(__uint_as_float(v[e4 * 4 + 2]) + bb.z, 0.0f);
+        const float h3 = fmaxf(__uint_as_float(v[e4 * 4 + 3]) + bb.w, 0.0f);
+        o0 = fmaf(h3, wr.w, fmaf(h2, wr.z, fmaf(h1, wr.y, fmaf(h0, wr.x, o0))));
+        o1 = fmaf(h3, wg.w, fmaf(h2, wg.z, fmaf(h1, wg.y, fmaf(h0, wg.x, o1))));
+        o2 = fmaf(h3, wb.w, fmaf(h2, wb.z, fmaf(h1, wb.y, fmaf(h0, wb.x, o2))));
       }
     }
     if (live) {
@@ -355,54 +461,68 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       out[1] = 1.0f / (1.0f + expf(-o1));
       out[2] = 1.0f / (1.0f + expf(-o2));
     }
-    // the next tile's phase 1 overwrites A and its MMAs overwrite D: order this group's TMEM
-    // reads before them
+    // the next tile's MMAs overwrite F and D: order this group's TMEM reads before the syncs
+    // that precede them
     tc_fence_before();
-    asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+    if (!BASIS) asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
   }
 
   // ---- teardown -----------------------------------------------------------------------------------
+  if (copy_pending) {
+    // a group that stopped early still has a bulk copy in flight into its operand buffer
+    group_wait(tbar, tparity, bar_id, row, s_flag);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
-                 "r"((uint32_t)(NSLOT * HID < 32 ? 32 : NSLOT * HID)));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols));
   }
-  (void)lane;
 }
 
-// W [n_out = 128][k_real] fp32 -> fp16 operand image [k_groups][128][8]
-__global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __restrict__ img, int k_real, int k_groups) {
+// W [n_out][k_real] fp32 -> fp16 operand image [k_groups][n_rows][8]; rows >= n_out and
+// columns >= k_real are zero.  `k_map_c`/`k_map_cp` translate a padded product index
+// (pair * cp + c) into the column of the unpadded matrix; pass 0 for a plain matrix.
+__global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __restrict__ img, int n_out, int n_rows,
+                                         int k_real, int k_groups, int k_map_c, int k_map_cp) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (kg, n)
-  if (i >= k_groups * HID) return;
-  int kg = i / HID, n = i - kg * HID;
+  if (i >= k_groups * n_rows) return;
+  int kg = i / n_rows, n = i - kg * n_rows;
   __half* dst = img + (size_t)i * 8;
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     int k = kg * 8 + e;
-    dst[e] = __float2half_rn(k < k_real ? w[(size_t)n * k_real + k] : 0.0f);
+    float v = 0.0f;
+    if (n < n_out) {
+      if (k_map_cp > 0) {
+        int pair = k / k_map_cp, c = k - pair * k_map_cp;
+        int col = pair * k_map_c + c;
+        if (c < k_map_c && col < k_real) v = w[(size_t)n * k_real + col];
+      } else if (k < k_real) {
+        v = w[(size_t)n * k_real + k];
+      }
+    }
+    dst[e] = __float2half_rn(v);
   }
 }
 
-template <int TA, int NSLOT>
+template <int TA, int NSLOT, bool BASIS>
 int launch_variant(const GnrModel* m, const TcArgs& args, cudaStream_t st) {
-  const size_t smem = (size_t)W1_BYTES + W2_BYTES + (size_t)NSLOT * TA * A_BYTES + (3 * HID + 2 * HID + 4) * sizeof(float) +
-                      NSLOT * sizeof(uint64_t) + 32;
-  cudaError_t e = cudaFuncSetAttribute(mlp_tc_kernel<TA, NSLOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + (size_t)NSLOT * TA * A_BYTES +
+                      (3 * HID + 2 * HID + 4) * sizeof(float) + 2 * NSLOT * sizeof(uint64_t) + 32;
+  cudaError_t e = cudaFuncSetAttribute(mlp_tc_kernel<TA, NSLOT, BASIS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
-  mlp_tc_kernel<TA, NSLOT><<<m->sm_count, NSLOT * 128, smem, st>>>(args);
+  mlp_tc_kernel<TA, NSLOT, BASIS><<<m->sm_count, NSLOT * 128, smem, st>>>(args);
   return (int)cudaGetLastError();
 }
 
 }  // namespace
 
-int gnr_mlp_tc_prepare(GnrModel* m, const float* w1, const float* b1, const float* w2, const float* b2, const float* w3,
-                       const float* b3, cudaStream_t st) {
-  (void)b1;
-  (void)b2;
-  (void)w3;
-  (void)b3;
+int gnr_tc_basis_fused(const GnrModel* m) {
+  return m->cfg.mlp_mode != 0 && m->mlp.n_prod % 16 == 0 && m->mlp.n_prod <= MAX_K0 && m->cfg.app_dim <= NB;
+}
+
+int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, cudaStream_t st) {
   const GnrConfig& c = m->cfg;
   if (c.app_dim != APP || c.fea_pe != FPE || c.view_pe != VPE || c.hidden != HID) {
     gnr_set_error("tensor-core MLP supports app_dim 27, fea_pe 2, view_pe 2, featureC 128 (got %d, %d, %d, %d); use mlp_mode 0",
@@ -411,17 +531,24 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* w1, const float* b1, const floa
   }
   if (m->mlp.tc_image) cudaFree(m->mlp.tc_image);
   m->mlp.tc_image = nullptr;
-  m->mlp.tc_image_bytes = (size_t)W1_BYTES + W2_BYTES;
+  m->mlp.tc_image_bytes = (size_t)WB_BYTES + W1_BYTES + W2_BYTES;
   GNR_CUDA_OK(cudaMalloc(&m->mlp.tc_image, m->mlp.tc_image_bytes));
+  GNR_CUDA_OK(cudaMemsetAsync(m->mlp.tc_image, 0, m->mlp.tc_image_bytes, st));
   __half* img = reinterpret_cast<__half*>(m->mlp.tc_image);
-  pack_weight_image_kernel<<<(KG1 * HID + 255) / 256, 256, 0, st>>>(w1, img, IN_DIM, KG1);
-  pack_weight_image_kernel<<<(KG2 * HID + 255) / 256, 256, 0, st>>>(w2, img + W1_BYTES / 2, HID, KG2);
+  if (gnr_tc_basis_fused(m)) {
+    const int cp = (c.n_app + 15) / 16 * 16, kgb = m->mlp.n_prod / 8;
+    pack_weight_image_kernel<<<(kgb * NB + 255) / 256, 256, 0, st>>>(basis_w, img, c.app_dim, NB, c.n_pairs * c.n_app, kgb,
+                                                                    c.n_app, cp);
+  }
+  pack_weight_image_kernel<<<(KG1 * HID + 255) / 256, 256, 0, st>>>(w1, img + WB_BYTES / 2, HID, HID, IN_DIM, KG1, 0, 0);
+  pack_weight_image_kernel<<<(KG2 * HID + 255) / 256, 256, 0, st>>>(w2, img + (WB_BYTES + W1_BYTES) / 2, HID, HID, HID, KG2,
+                                                                   0, 0);
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                  int64_t max_app, cudaStream_t st) {
+                  int64_t max_app, int write_features, cudaStream_t st) {
   if (!m->mlp.tc_image) {
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
@@ -430,13 +557,19 @@ int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays
     gnr_set_error("tensor-core MLP expects a feature stride of %d floats", FEAT_STRIDE);
     return -1;
   }
+  const bool fused = gnr_tc_basis_fused(m) != 0;
   TcArgs a;
   a.rays = rays;
   a.ids = (const uint32_t*)(ws + L.ids);
   a.app_index = (const int32_t*)(ws + L.app_index);
   a.total_ptr = (const int32_t*)(ws + L.app_offsets) + L.n_rays;
   a.capacity = (long long)max_app;
-  a.feat = (const float*)(ws + L.app_feat);
+  a.feat_in = (const float*)(ws + L.app_feat);
+  a.feat_out = (fused && write_features) ? (float*)(ws + L.app_feat) : nullptr;
+  a.prod_hi = fused ? (const unsigned char*)(ws + L.app_prod) : nullptr;
+  a.prod_lo = fused ? a.prod_hi + L.app_prod_image : nullptr;
+  a.tile_bytes = L.app_prod_tile;
+  a.k0 = m->mlp.n_prod;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
   a.w3 = m->mlp.w3;
   a.b1 = m->mlp.b1;
@@ -445,8 +578,8 @@ int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays
   a.rgb_out = (float*)(ws + L.app_rgb);
   a.status = (int32_t*)(ws + L.status);
   a.kbits = p.kbits;
-  if (m->cfg.mlp_mode == 1) return launch_variant<2, 1>(m, a, st);  // activations hi + lo
-  if (m->cfg.mlp_mode == 2) return launch_variant<1, 2>(m, a, st);  // single fp16, two tiles in flight
+  if (m->cfg.mlp_mode == 1) return fused ? launch_variant<2, 1, true>(m, a, st) : launch_variant<2, 1, false>(m, a, st);
+  if (m->cfg.mlp_mode == 2) return fused ? launch_variant<1, 3, true>(m, a, st) : launch_variant<1, 3, false>(m, a, st);
   gnr_set_error("unknown mlp_mode %d", m->cfg.mlp_mode);
   return -1;
 }

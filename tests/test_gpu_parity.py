@@ -290,7 +290,9 @@ def test_tensor_core_mlp_modes(tiny, mlp_mode, tol):
     out = m.run_stages(rays.cuda(), spec.n_samples, True)
     assert m.last_status[4] == 0, "a bounded wait expired in the tensor-core kernel"
     assert torch.equal(out["counts"], got["counts"]) and torch.equal(out["app_index"], got["app_index"])
-    assert torch.equal(out["app_features"], got["app_features"])
+    # the basis projection runs on the tensor cores too: fp16 products x fp16 weights, fp32 accumulate
+    df = (out["app_features"] - got["app_features"]).abs().max().item()
+    assert df <= 3e-5, f"projected features differ from the fp32 kernel by {df:.3e}"
     d = (out["rgb_samples"] - got["rgb_samples"]).abs().max().item()
     assert d <= tol, f"per-sample rgb differs from the fp32 kernel by {d:.3e}"
     fx = load_golden("tiny_lit.npz")
