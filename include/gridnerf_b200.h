@@ -136,6 +136,31 @@ int gnr_sample(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, vo
                uint32_t* mask_words, uint32_t* ids, void* stream);
 int gnr_sample_bits(int n_samples);
 
+/* Stage 1 again, for callers that must not allocate.  (This entry has no counterpart in the
+ * reference.)  The frame loop of an online renderer is such a caller: a cudaMalloc there
+ * synchronises the whole device and stalls the other pipeline stages' streams, and a host
+ * that has given all of its device memory to the field's planes has nothing left to hand out
+ * as a workspace.  gnr_sample_static therefore takes no workspace: its scratch (the validity
+ * bit words and the scan's block sums) lives in one fixed array of
+ * GNR_SAMPLE_STATIC_SCRATCH_BYTES inside the library, which every GPU that loads the library
+ * holds until the process exits.  The call allocates and frees nothing.
+ *
+ *  - Limit: 4 * n_rays * ceil(n_samples / 32) + 4 * (n_rays / 1024 + 2), each part rounded up to
+ *    256 bytes, must not exceed GNR_SAMPLE_STATIC_SCRATCH_BYTES (e.g. 65536 rays x 512 samples);
+ *    larger chunks are refused with an error, nothing is enqueued.
+ *  - All five outputs are required device buffers owned by the caller: ``t_min[n]``, ``counts[n]``,
+ *    ``offsets[n+1]``, ``ids[max_valid]`` and an 8-word ``status`` block (GNR_ST_* indices) that
+ *    the call clears first and that reports an ``ids`` overflow.  Results equal gnr_sample's.
+ *  - The first call on a device looks up the array's device address (with that device
+ *    current); make that first call outside any stream capture.
+ *  - All calls on one GPU share the array and it keeps the previous call's contents; the call
+ *    rewrites every word it reads, so nothing stale leaks in, but two calls that overlap on
+ *    the GPU (different streams, no dependency) race on it.  Serialise them. */
+#define GNR_SAMPLE_STATIC_SCRATCH_BYTES (4u << 20)
+int gnr_sample_static(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, int64_t max_valid,
+                      float* t_min, int32_t* counts, int32_t* offsets, uint32_t* ids, int32_t* status,
+                      void* stream);
+
 /* Stage 2: density for the compacted samples of the last gnr_sample on this workspace:
  * ``sigma[i] = feature2density(compute_densityfeature(xyz_i))``; also the raw feature.
  * gridnerf_sequential.py:471-475,779-827,386-399. */

@@ -13,6 +13,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libgridnerf_b200.so")
 
 STAGE_NAMES = ("sample", "compact", "density", "weights", "compact_app", "app_gather", "mlp", "composite")
+SAMPLE_STATIC_SCRATCH_BYTES = 4 << 20
 ST_OVERFLOW_VALID, ST_OVERFLOW_APP, ST_NUM_VALID, ST_NUM_APP, ST_WAIT_EXPIRED, ST_WORDS = 0, 1, 2, 3, 4, 8
 
 
@@ -63,6 +64,7 @@ SIGNATURES = {
     "gnr_render_host": (_INT, [_P, _P, _I64, _INT, _INT, _I64, _I64, _I64, _P, _P, C.POINTER(C.c_int32)]),
     "gnr_sample": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _P, _P, _P, _P, _P, _P]),
     "gnr_sample_bits": (_INT, [_INT]),
+    "gnr_sample_static": (_INT, [_P, _P, _I64, _INT, _I64, _P, _P, _P, _P, _P, _P]),
     "gnr_density": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _P, _P, _P]),
     "gnr_weights": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _I64, _P, _P, _P, _P, _P, _P, _P]),
     "gnr_appearance": (_INT, [_P, _P, _I64, _INT, _P, _SZ, _I64, _I64, _P, _P, _P]),

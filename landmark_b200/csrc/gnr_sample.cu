@@ -282,3 +282,106 @@ extern "C" int gnr_generate_rays(const float* pose_h, const float* dir_x, const 
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free sampling: same kernels, scratch in a fixed device array of this library.
+// ---------------------------------------------------------------------------------------------
+// Scratch of gnr_sample_static: [validity bit words][scan block sums].  One copy per GPU that
+// loads the library, shared by every call on that GPU.
+static __device__ __align__(256) unsigned char g_sample_static_scratch[GNR_SAMPLE_STATIC_SCRATCH_BYTES];
+
+#include <mutex>
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+unsigned char* g_static_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array on `device`.  The array's name is only a host-side
+// handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once per
+// device with that device current.
+int static_scratch_for(int device, unsigned char** out) {
+  if (device < 0 || device >= kMaxDevices) {
+    gnr_set_error("gnr_sample_static: device ordinal %d outside [0, %d)", device, kMaxDevices);
+    return -1;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[device]) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_sample_static_scratch);
+    if (e != cudaSuccess || !p) {
+      gnr_set_error("gnr_sample_static: cudaGetSymbolAddress failed on device %d: %s", device, cudaGetErrorString(e));
+      return -2;
+    }
+    g_static_ptr[device] = (unsigned char*)p;
+  }
+  *out = g_static_ptr[device];
+  return 0;
+}
+
+inline size_t round256(size_t v) { return (v + 255) / 256 * 256; }
+}  // namespace
+
+extern "C" int gnr_sample_static(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, int64_t max_valid,
+                                 float* t_min, int32_t* counts, int32_t* offsets, uint32_t* ids, int32_t* status,
+                                 void* stream) {
+  if (!m) {
+    gnr_set_error("gnr_sample_static: null model");
+    return -1;
+  }
+  if (!rays || !t_min || !counts || !offsets || !ids || !status) {
+    gnr_set_error("gnr_sample_static: rays and all five output buffers are required");
+    return -1;
+  }
+  if (n_rays < 1 || n_samples < 1 || max_valid < 1) {
+    gnr_set_error("gnr_sample_static: bad sizes (n_rays %lld, n_samples %d, max_valid %lld)", (long long)n_rays, n_samples,
+                  (long long)max_valid);
+    return -1;
+  }
+  const int kbits = gnr_sample_bits(n_samples);
+  if (kbits > 20 || n_rays > ((int64_t)1 << (32 - kbits)) || n_rays * (int64_t)n_samples > 0x7fffffffLL ||
+      max_valid > 0x7fffffffLL) {
+    gnr_set_error("gnr_sample_static: %lld rays x %d samples does not fit the 32-bit sample ids", (long long)n_rays, n_samples);
+    return -1;
+  }
+  const size_t words = (size_t)(n_samples + 31) / 32;
+  const size_t words_bytes = round256((size_t)n_rays * words * 4);
+  const size_t sums_bytes = round256(((size_t)n_rays / 1024 + 2) * 4);
+  if (words_bytes + sums_bytes > (size_t)GNR_SAMPLE_STATIC_SCRATCH_BYTES) {
+    gnr_set_error("gnr_sample_static: %lld rays x %d samples need %zu bytes of scratch, the built-in array holds %u; "
+                  "split the chunk or use gnr_sample with a workspace",
+                  (long long)n_rays, n_samples, words_bytes + sums_bytes, (unsigned)GNR_SAMPLE_STATIC_SCRATCH_BYTES);
+    return -1;
+  }
+  int prev = 0;
+  cudaGetDevice(&prev);
+  if (prev != m->device) cudaSetDevice(m->device);
+  unsigned char* scratch = nullptr;
+  int rc = static_scratch_for(m->device, &scratch);
+  if (rc == 0) {
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t* mask_words = (uint32_t*)scratch;
+    int32_t* block_sums = (int32_t*)(scratch + words_bytes);
+    GnrSampleParams p = gnr_sample_params(m, n_samples);
+    const unsigned blocks = (unsigned)((n_rays + kWarpsPerBlock - 1) / kWarpsPerBlock);
+    cudaError_t e = cudaMemsetAsync(status, 0, GNR_ST_WORDS * sizeof(int32_t), st);  // the overflow flag starts at zero
+    if (e == cudaSuccess) {
+      // every word of mask_words and block_sums that is read below is written first by these
+      // launches, so what an earlier call left in the array is never seen
+      sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n_rays, t_min, mask_words, counts);
+      e = (cudaError_t)launch_exclusive_scan(counts, offsets, block_sums, n_rays, status, GNR_ST_NUM_VALID,
+                                             GNR_ST_OVERFLOW_VALID, max_valid, st);
+    }
+    if (e == cudaSuccess) {
+      expand_ids_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(mask_words, offsets, n_rays, p.words, p.kbits,
+                                                               (long long)max_valid, ids);
+      e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+      gnr_set_error("gnr_sample_static: launch failed: %s", cudaGetErrorString(e));
+      rc = -2;
+    }
+  }
+  if (prev != m->device) cudaSetDevice(prev);
+  return rc;
+}
