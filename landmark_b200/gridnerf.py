@@ -41,9 +41,11 @@ class AlphaGridMask(torch.nn.Module):
     def __init__(self, device, aabb, alpha_volume):
         super().__init__()
         self.device = device
-        self.aabb = aabb.to(device)
-        self.aabbSize = self.aabb[1] - self.aabb[0]
-        self.invgridSize = 1.0 / self.aabbSize * 2
+        aabb_cpu = aabb.detach().cpu().float()
+        size_cpu = aabb_cpu[1] - aabb_cpu[0]
+        self.aabb = aabb_cpu.to(device)
+        self.aabbSize = size_cpu.to(device)
+        self.invgridSize = (1.0 / size_cpu * 2).to(device)  # evaluated on the CPU, see update_stepSize
         self.alpha_volume = alpha_volume.view(1, 1, *alpha_volume.shape[-3:])
         self.gridSize = torch.LongTensor(
             [alpha_volume.shape[-1], alpha_volume.shape[-2], alpha_volume.shape[-3]]
@@ -172,15 +174,26 @@ class B200GridNeRF(torch.nn.Module):
         self.check_status_every_call = True
         self.last_status: Optional[np.ndarray] = None
 
-    # -- geometry scalars, computed with torch exactly as the reference does (:149-164) ----------
+    # -- geometry scalars (:149-164) -------------------------------------------------------------
     def update_stepSize(self, gridSize):
-        self.aabbSize = self.aabb[1] - self.aabb[0]
-        self.invaabbSize = 2.0 / self.aabbSize
-        self.gridSize = torch.tensor(gridSize, device=self.aabbSize.device)
-        self.units = self.aabbSize / (self.gridSize - 1)
-        self.stepSize = torch.mean(self.units) * self.step_ratio
-        self.aabbDiag = torch.sqrt(torch.sum(torch.square(self.aabbSize)))
-        self.nSamples = int((self.aabbDiag / self.stepSize).item()) + 1
+        """Same expressions as the reference, evaluated on CPU tensors: torch's CUDA ``mean``
+        multiplies by 1/N where the CPU divides by N, which moves ``stepSize`` by one ulp for
+        anisotropic grids and with it every sample position.  The CPU values are the ones the
+        sampler's bit-exactness is defined against; device copies are kept for API parity."""
+        aabb = self.aabb.detach().cpu()
+        aabb_size = aabb[1] - aabb[0]
+        grid = torch.tensor(gridSize)
+        units = aabb_size / (grid - 1)
+        step = torch.mean(units) * self.step_ratio
+        diag = torch.sqrt(torch.sum(torch.square(aabb_size)))
+        dev = self.aabb.device
+        self.aabbSize = aabb_size.to(dev)
+        self.invaabbSize = (2.0 / aabb_size).to(dev)
+        self.gridSize = grid.to(dev)
+        self.units = units.to(dev)
+        self.stepSize = step.to(dev)
+        self.aabbDiag = diag.to(dev)
+        self.nSamples = int((diag / step).item()) + 1
 
     def get_kwargs(self):
         return {

@@ -1,0 +1,120 @@
+"""GPU parity at the benchmark's full size: the city-block scene (grid 2048x2048x256, 16/48
+channels, 512x512x64 occupancy heightfield, 512 samples per ray).
+
+* the 3 x 64-ray slices the reference itself rendered (tests/golden/city_lit_slices.npz):
+  valid-sample sets bit-exact, rgb within 1e-4;
+* a random 4096-ray subset of the 1920x1080 frame against the CPU oracle;
+* size-independent properties on the whole frame: chunking and ray order do not change a
+  single bit of any pixel, counts add up, white minus black background equals 1 - acc.
+"""
+import numpy as np
+import pytest
+import torch
+
+from landmark_b200 import scenes
+from oracle import gridnerf_oracle as orc
+from tests._util import cuda_model, load_golden, valid_bits_from_words
+
+pytestmark = pytest.mark.gpu
+
+RGB_TOL = 1e-4
+FLIP_RGB_TOL = 2.5e-3
+
+
+@pytest.fixture(scope="module")
+def city():
+    spec = scenes.city_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)  # CPU generator: same bits as the fixture's scene
+    fx = load_golden("city_lit_slices.npz")
+    assert scenes.state_dict_digest(ckpt["state_dict"]) == str(fx["state_dict_digest"])
+    field = orc.field_from_checkpoint(ckpt)
+    model = cuda_model(spec, ckpt, mlp_mode=0)
+    model.release_torch_planes()
+    vol = scenes.make_alpha_volume(spec)
+    pose = scenes.make_pose(spec, vol)
+    rays = orc.generate_rays(torch.from_numpy(pose), spec.height, spec.width, spec.focal)
+    return spec, field, model, rays, fx
+
+
+def test_reference_slices_exact_indices_and_rgb(city):
+    spec, field, model, rays, fx = city
+    pick = torch.from_numpy(fx["pick"])
+    assert np.array_equal(rays[pick].numpy(), fx["rays"])
+    got = model.run_stages(torch.from_numpy(fx["rays"]).cuda(), spec.n_samples, True)
+    bits = valid_bits_from_words(got["mask_words"], spec.n_samples)
+    assert np.array_equal(np.packbits(bits, axis=1), fx["valid_bits"])
+    assert np.array_equal(got["counts"].cpu().numpy(), fx["valid_counts"])
+    assert np.array_equal(got["t_min"].cpu().numpy(), fx["t_min"])
+    stride = int(fx["subset_stride"])
+    assert (got["sigma_feature"].cpu().numpy()[::stride] - fx["sigma_feature_sub"]).__abs__().max() <= 3e-5
+    assert abs(got["num_app"] - int(fx["app_counts"].sum())) <= 2
+    err = (got["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+    assert (got["depth_map"].cpu() - torch.from_numpy(fx["depth_map"])).abs().max().item() <= 1e-4
+
+
+@pytest.mark.parametrize("mlp_mode", [0, 2])
+def test_random_frame_subset_vs_oracle(city, mlp_mode):
+    spec, field, model, rays, fx = city
+    g = torch.Generator().manual_seed(1234)
+    pick = torch.randperm(rays.shape[0], generator=g)[:4096].sort().values
+    sub = rays[pick].contiguous()
+    ref = orc.render_chunk(field, sub, spec.n_samples, True, keep_stages=True)
+    m = model
+    if mlp_mode != 0:
+        m = _second_model(city, mlp_mode)
+    got = m.run_stages(sub.cuda(), spec.n_samples, True)
+    assert np.array_equal(valid_bits_from_words(got["mask_words"], spec.n_samples), ref["ray_valid"].numpy())
+    err = (got["rgb_map"].cpu() - ref["rgb_map"]).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 3, f"{int((err > RGB_TOL).sum())} rays above 1e-4 (max {err.max():.2e})"
+    assert err.max().item() <= FLIP_RGB_TOL
+    assert (got["depth_map"].cpu() - ref["depth_map"]).abs().max().item() <= 2e-4
+
+
+_models = {}
+
+
+def _second_model(city, mlp_mode):
+    """A tensor-core-mode model over the same scene (shares nothing with the fp32 one)."""
+    spec, field, model, rays, fx = city
+    if mlp_mode not in _models:
+        ckpt = scenes.make_checkpoint(spec)
+        m = cuda_model(spec, ckpt, mlp_mode=mlp_mode)
+        m.release_torch_planes()
+        _models[mlp_mode] = m
+    return _models[mlp_mode]
+
+
+def test_full_frame_properties(city):
+    spec, field, model, rays, fx = city
+    m = _second_model(city, 2)
+    n = rays.shape[0]
+    r = rays.cuda()
+    rgb_w, depth = m.render_rays(r, spec.n_samples, True, chunk=131072)
+    st = m.check_pending_status()
+    rgb_w, depth = rgb_w.clone(), depth.clone()
+    assert st[2] > 4e8 and st[3] > 1e8  # the frame really has ~463 M valid / ~125 M appearance samples
+    assert torch.isfinite(rgb_w).all() and float(rgb_w.min()) >= 0.0 and float(rgb_w.max()) <= 1.0
+    assert float(depth.min()) >= 0.0
+    # other chunking: not one bit changes
+    rgb2, depth2 = m.render_rays(r, spec.n_samples, True, chunk=50000)
+    st2 = m.check_pending_status()
+    assert torch.equal(rgb2, rgb_w) and torch.equal(depth2, depth)
+    assert st2[2] == st[2] and st2[3] == st[3]
+    # other ray order (a fixed permutation): every pixel keeps its bits
+    g = torch.Generator().manual_seed(7)
+    perm = torch.randperm(n, generator=g).cuda()
+    rgb3, depth3 = m.render_rays(r[perm].contiguous(), spec.n_samples, True, chunk=131072)
+    m.check_pending_status()
+    assert torch.equal(rgb3, rgb_w[perm]) and torch.equal(depth3, depth[perm])
+    # white minus black background is 1 - acc, where nothing clamps
+    rgb_b, _ = m.render_rays(r, spec.n_samples, False, chunk=131072)
+    m.check_pending_status()
+    sub = r[::997].contiguous()
+    acc = m.run_stages(sub, spec.n_samples, True, upto="weights")["acc"]
+    inner = (rgb_w[::997] < 1.0).all(dim=1)
+    diff = (rgb_w[::997] - rgb_b[::997])[inner]
+    assert (diff - (1.0 - acc[inner])[:, None]).abs().max().item() <= 1e-6
+    # host-buffer path: same bits
+    rgb_h, depth_h = m.render_host(rays.pin_memory(), spec.n_samples, True, chunk=131072)
+    assert torch.equal(rgb_h, rgb_w.cpu()) and torch.equal(depth_h, depth.cpu())
