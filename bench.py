@@ -37,7 +37,6 @@ if ROOT not in sys.path:
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
-TILE = 64
 DENSITY_BYTES_PER_SAMPLE = 784      # 3 planes x 4 corners x 16 ch x 4 B + 12 B coordinate + 4 B sigma
 APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B coordinate
 MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
@@ -53,19 +52,6 @@ def peaks():
         return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
                 "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1400.0, "source": "fallback"}
-
-
-def tile_pixel_ids(H, W, rank, world):
-    """Pixel ids (row-major y*W+x) of the tiles owned by ``rank``: tile k -> rank k % world,
-    pixels inside a tile in row-major order, tiles clipped at the image border."""
-    tx, ty = (W + TILE - 1) // TILE, (H + TILE - 1) // TILE
-    ids = []
-    for k in range(rank, tx * ty, world):
-        y0, x0 = (k // tx) * TILE, (k % tx) * TILE
-        ys = np.arange(y0, min(y0 + TILE, H))
-        xs = np.arange(x0, min(x0 + TILE, W))
-        ids.append((ys[:, None] * W + xs[None, :]).reshape(-1))
-    return np.concatenate(ids).astype(np.int32) if ids else np.zeros((0,), np.int32)
 
 
 class ClockSampler:
@@ -178,7 +164,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="city_lit", choices=["city_lit", "city"])
     ap.add_argument("--chunk", type=int, default=131072, help="rays per library call")
-    ap.add_argument("--mlp-mode", type=int, default=0)
+    ap.add_argument("--mlp-mode", type=int, default=2,
+                    help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
     ap.add_argument("--profile-case", type=int, default=0, metavar="RAYS",
@@ -202,6 +189,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(device))
     from landmark_b200 import scenes
     from landmark_b200.gridnerf import B200GridNeRF
+    from landmark_b200.parallel import TILE, TileSharding, tile_pixel_ids
     from landmark_b200.rays import generate_rays
 
     spec, ckpt, pose = build_scene(a.workload, device)
@@ -229,37 +217,18 @@ def main():
         print(json.dumps({"profile_case_rays": int(rays.shape[0]), "valid": int(st[2]), "appearance": int(st[3])}))
         return
     if world == 1 and a.order == "rows":
-        ids_np = np.arange(H * W, dtype=np.int32)
+        shard = TileSharding(H, W, 0, 1, device, tile=max(H, W))  # one tile = the whole image, row-major
     else:
-        ids_np = tile_pixel_ids(H, W, rank, world)
-    n_local = int(ids_np.shape[0])
-    n_pad = n_local
-    if world > 1:
-        cnt = torch.tensor([n_local], device=device)
-        dist.all_reduce(cnt, op=dist.ReduceOp.MAX)
-        n_pad = int(cnt.item())
-    pix = torch.from_numpy(ids_np).to(device)
+        shard = TileSharding(H, W, rank, world, device)
+    n_local, n_pad, pix = shard.n_local, shard.n_pad, shard.pixel_ids
     rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=pix)
     rgb = torch.zeros((n_pad, 3), dtype=torch.float32, device=device)
     depth = torch.zeros((n_pad,), dtype=torch.float32, device=device)
-    gathered = torch.empty((world * n_pad, 3), dtype=torch.float32, device=device) if world > 1 else None
     image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
-    if world > 1:
-        pix_pad = torch.full((n_pad,), -1, dtype=torch.int64, device=device)
-        pix_pad[:n_local] = pix.to(torch.int64)
-        all_pix = torch.empty((world * n_pad,), dtype=torch.int64, device=device)
-        dist.all_gather_into_tensor(all_pix, pix_pad)
-        keep = all_pix >= 0
-        all_pix_keep = all_pix[keep]
 
     def step():
         model.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb[:n_local], depth_out=depth[:n_local])
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, rgb)
-            if rank == 0:
-                image[all_pix_keep] = gathered[keep]
-        else:
-            image[pix.to(torch.int64)] = rgb
+        shard.assemble(rgb, image)
 
     for _ in range(max(a.warmup, 3)):
         step()
@@ -356,7 +325,7 @@ def main():
     line = {
         "metric": "Mrays/s", "value": H * W / (ms_step * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 (gathers, compositing) + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode,

@@ -1,0 +1,79 @@
+"""Image-tile data parallelism for a replicated model.
+
+The reference splits a frame's rays into contiguous ranges, scatters them from rank 0 and
+gathers the colours back (dist_render/ddp_infer/nerf_inferer.py:58-72,300-305,337-339; offline:
+app/tools/render_utils.py:126-170).  Here every rank derives its own rays from the pose, so
+nothing is scattered: the frame is cut into ``tile x tile`` pixel tiles, tile ``k`` belongs to
+rank ``k % world`` (round-robin balances empty sky against dense ground), and one
+``all_gather_into_tensor`` of the per-rank colour buffers (padded to a common length) brings
+the frame together.  Works with any ``torch.distributed`` backend (NCCL on GPUs, gloo in tests).
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import numpy as np
+import torch
+
+TILE = 64
+
+
+def tile_pixel_ids(H: int, W: int, rank: int, world: int, tile: int = TILE) -> np.ndarray:
+    """Pixel ids (row-major ``y * W + x``) of the tiles owned by ``rank``; pixels inside a tile
+    in row-major order, tiles clipped at the image border."""
+    tx, ty = (W + tile - 1) // tile, (H + tile - 1) // tile
+    ids = []
+    for k in range(rank, tx * ty, world):
+        y0, x0 = (k // tx) * tile, (k % tx) * tile
+        ys = np.arange(y0, min(y0 + tile, H))
+        xs = np.arange(x0, min(x0 + tile, W))
+        ids.append((ys[:, None] * W + xs[None, :]).reshape(-1))
+    return np.concatenate(ids).astype(np.int32) if ids else np.zeros((0,), np.int32)
+
+
+class TileSharding:
+    """Per-rank pixel list plus what rank 0 needs to put the gathered colours back in place."""
+
+    def __init__(self, H: int, W: int, rank: int, world: int, device, tile: int = TILE, group=None):
+        import torch.distributed as dist
+
+        self.H, self.W, self.rank, self.world, self.group = H, W, rank, world, group
+        ids = tile_pixel_ids(H, W, rank, world, tile)
+        self.n_local = int(ids.shape[0])
+        self.pixel_ids = torch.from_numpy(ids).to(device)
+        self.n_pad = self.n_local
+        if world > 1:
+            cnt = torch.tensor([self.n_local], device=device, dtype=torch.int64)
+            dist.all_reduce(cnt, op=dist.ReduceOp.MAX, group=group)
+            self.n_pad = int(cnt.item())
+            pad = torch.full((self.n_pad,), -1, dtype=torch.int64, device=device)
+            pad[: self.n_local] = self.pixel_ids.to(torch.int64)
+            all_pix = torch.empty((world * self.n_pad,), dtype=torch.int64, device=device)
+            dist.all_gather_into_tensor(all_pix, pad, group=group)
+            self.keep = all_pix >= 0
+            self.all_pixels = all_pix[self.keep]
+            self.gathered = torch.empty((world * self.n_pad, 3), dtype=torch.float32, device=device)
+        else:
+            self.keep = None
+            self.all_pixels = self.pixel_ids.to(torch.int64)
+            self.gathered = None
+
+    def assemble(self, rgb_padded: torch.Tensor, image: torch.Tensor) -> torch.Tensor:
+        """``rgb_padded [n_pad, 3]`` of this rank -> ``image [H*W, 3]`` (complete on every rank
+        after the all-gather; callers usually only read it on rank 0)."""
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, rgb_padded, group=self.group)
+            image[self.all_pixels] = self.gathered[self.keep]
+        else:
+            image[self.all_pixels] = rgb_padded[: self.n_local]
+        return image
+
+
+def split_contiguous(n_rays: int, world: int) -> Tuple[int, int]:
+    """The reference's split: ``ceil(n / world)`` rays per rank and the padding that makes the
+    total divisible (nerf_inferer.py:58-72)."""
+    per = -(-n_rays // world)
+    return per, per * world - n_rays
