@@ -307,7 +307,7 @@ def main():
                               "note": "fp32 CUDA-core kernel" if a.mlp_mode == 0 else "tcgen05 kernel"}
     dominant = max(roof, key=lambda k: roof[k]["ms_per_frame"]) if roof else None
     traffic = None
-    tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.txt")
     if dominant and os.path.exists(tpath):
         with open(tpath) as fh:
             tj = json.load(fh)
