@@ -101,6 +101,12 @@ int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const flo
 int gnr_generate_rays(const float* pose_h, const float* dir_x, const float* dir_y, int H, int W,
                       const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays, void* stream);
 
+/* Frame post-process on the device: ``out[i] = (uint8)(rgb[i] * 255)`` (truncation, what
+ * ``.byte()`` does) with alpha 255, i.e. the ``result * 255`` / ``torch.cat(..., 255)`` / ``.byte()``
+ * steps of model_infer_postprocess (dist_render/ddp_infer/nerf_inferer.py:366-370).
+ * ``rgb[n][3]`` fp32 -> ``rgba[n][4]`` uint8. */
+int gnr_rgba8(const float* rgb, int64_t n, uint8_t* rgba, void* stream);
+
 /* Scratch memory for one chunk.  The caller allocates ``bytes`` (256-byte aligned) and
  * passes it to the calls below; contents carry no state between chunks. */
 int gnr_workspace_bytes(const GnrModel* m, int64_t n_rays, int n_samples, int64_t max_valid,

@@ -59,6 +59,7 @@ SIGNATURES = {
     "gnr_upload_alpha_mask": (_INT, [_P, _P, _INT, _INT, _INT, C.POINTER(C.c_float), C.POINTER(C.c_float), _P]),
     "gnr_upload_mlp": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "gnr_generate_rays": (_INT, [C.POINTER(C.c_float), _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),
+    "gnr_rgba8": (_INT, [_P, _I64, _P, _P]),
     "gnr_workspace_bytes": (_INT, [_P, _I64, _INT, _I64, _I64, C.POINTER(_SZ)]),
     "gnr_render_chunk": (_INT, [_P, _P, _I64, _INT, _INT, _P, _SZ, _I64, _I64, _P, _P, _P]),
     "gnr_render_host": (_INT, [_P, _P, _I64, _INT, _INT, _I64, _I64, _I64, _P, _P, C.POINTER(C.c_int32)]),

@@ -171,3 +171,25 @@ int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const
       white_bg, rgb_map, depth_map);
   return (int)cudaGetLastError();
 }
+
+namespace {
+__global__ void rgba8_kernel(const float* __restrict__ rgb, long long n, uchar4* __restrict__ out) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float r = rgb[i * 3 + 0] * 255.0f, g = rgb[i * 3 + 1] * 255.0f, b = rgb[i * 3 + 2] * 255.0f;
+  out[i] = make_uchar4((unsigned char)__float2uint_rz(fminf(fmaxf(r, 0.0f), 255.0f)),
+                       (unsigned char)__float2uint_rz(fminf(fmaxf(g, 0.0f), 255.0f)),
+                       (unsigned char)__float2uint_rz(fminf(fmaxf(b, 0.0f), 255.0f)), 255);
+}
+}  // namespace
+
+extern "C" int gnr_rgba8(const float* rgb, int64_t n, uint8_t* rgba, void* stream) {
+  if (!rgb || !rgba || n < 0) {
+    gnr_set_error("gnr_rgba8: bad argument");
+    return -1;
+  }
+  if (n == 0) return 0;
+  rgba8_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(rgb, (long long)n, reinterpret_cast<uchar4*>(rgba));
+  GNR_CUDA_OK(cudaGetLastError());
+  return 0;
+}

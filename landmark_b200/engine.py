@@ -1,0 +1,193 @@
+"""Runner and engines of the online renderer: pose in, ``uint8 [H, W, 4]`` image out.
+
+Mirrors the entry points of the reference's ``dist_render``:
+
+* ``NerfDDPRunner.run_batch(pose)`` (dist_render/runner/ddp_runner/nerf_ddp_runner.py) =
+  ``model_infer_preprocess`` (pose -> rays, dist_render/ddp_infer/nerf_inferer.py:393-410) +
+  ``infer`` (:267-341) + ``model_infer_postprocess`` (:345-378: x255, alpha 255, ``.byte()``, pinned
+  device->host copy, numpy image);
+* ``MainRankDDPRenderEngine.start / submit / warm_up / run_for_latency``
+  (dist_render/engine/ddp_engine.py:18-75) on rank 0;
+* ``OtherRankRenderEngine.start`` (dist_render/engine/render_engine.py:99-120): the loop the
+  other ranks sit in (``render_other_rank``, nerf_inferer.py:126-193).
+
+Differences in mechanism, not in interface: rank 0 broadcasts the pose (12 floats + focal +
+a stop flag) instead of scattering H*W rays, every rank generates the rays of its own 64x64
+tiles and the colours come together with one all-gather (``landmark_b200.parallel``).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import time
+from typing import Callable, List, Optional
+
+import numpy as np
+import torch
+
+from .parallel import TileSharding
+
+RENDER_1080P = (1080, 1920, 1483.6378)  # H, W, focal of the online renderer (nerf_inferer.py:385-404)
+
+
+class FrameRenderer:
+    """Renders the pixels a rank owns.  The default implementation drives ``B200GridNeRF``; tests
+    substitute a CPU fake with the same two methods to exercise the multi-rank protocol."""
+
+    def __init__(self, model, n_samples: int = -1, white_bg: bool = True, chunk: int = 131072):
+        self.model, self.n_samples, self.white_bg, self.chunk = model, n_samples, white_bg, chunk
+        self.device = model.device
+
+    def render_pixels(self, pose: np.ndarray, H: int, W: int, focal: float, pixel_ids: torch.Tensor,
+                      rgb_out: torch.Tensor) -> None:
+        from .rays import generate_rays
+
+        rays = generate_rays(pose, H, W, focal, device=self.device, pixel_ids=pixel_ids)
+        self.model.render_rays(rays, self.n_samples, self.white_bg, chunk=self.chunk, rgb_out=rgb_out)
+
+    def finish(self):
+        self.model.check_pending_status()
+
+    def to_rgba8(self, image: torch.Tensor, out: torch.Tensor) -> None:
+        from ._lib import check, lib
+
+        with torch.cuda.device(self.device):
+            check(lib.gnr_rgba8(C.c_void_p(image.data_ptr()), image.shape[0], C.c_void_p(out.data_ptr()),
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gnr_rgba8")
+
+
+class NerfDDPRunner:
+    """``run_batch(single_pose) -> numpy uint8 [H, W, 4]``.  ``single_pose`` is ``[3, 4]`` or ``[3, 5]``
+    (focal in the last column); without a focal column the ``focal`` given here is used."""
+
+    def __init__(self, renderer, H: int = RENDER_1080P[0], W: int = RENDER_1080P[1], focal: Optional[float] = RENDER_1080P[2],
+                 rank: int = 0, world: int = 1, group=None):
+        self.renderer, self.H, self.W, self.focal = renderer, int(H), int(W), focal
+        self.rank, self.world, self.group = rank, world, group
+        dev = renderer.device
+        self.shard = TileSharding(self.H, self.W, rank, world, dev, group=group)
+        self.rgb = torch.zeros((self.shard.n_pad, 3), dtype=torch.float32, device=dev)
+        self.image = torch.zeros((self.H * self.W, 3), dtype=torch.float32, device=dev)
+        self.rgba = torch.zeros((self.H * self.W, 4), dtype=torch.uint8, device=dev)
+        self.img_cpu = torch.zeros((self.H, self.W, 4), dtype=torch.uint8)
+        if torch.device(dev).type == "cuda":
+            self.img_cpu = self.img_cpu.pin_memory()
+        self._msg = torch.zeros(14, dtype=torch.float32, device=dev)  # pose (12), focal, stop flag
+
+    # -- rank 0 <-> other ranks -------------------------------------------------------------------
+    def _broadcast(self, pose: Optional[np.ndarray], focal: float, stop: bool):
+        import torch.distributed as dist
+
+        if self.world == 1:
+            return pose, focal, stop
+        if self.rank == 0:
+            m = np.zeros(14, dtype=np.float32)
+            if pose is not None:
+                m[:12] = np.asarray(pose, dtype=np.float32)[:3, :4].reshape(-1)
+            m[12], m[13] = focal, 1.0 if stop else 0.0
+            self._msg.copy_(torch.from_numpy(m))
+        dist.broadcast(self._msg, src=0, group=self.group)
+        m = self._msg.cpu().numpy()
+        return m[:12].reshape(3, 4).copy(), float(m[12]), bool(m[13] > 0.5)
+
+    def _focal_of(self, pose) -> float:
+        pose = np.asarray(pose)
+        if pose.shape[-1] >= 5 and self.focal is None:
+            return float(pose[-1, -1])
+        if self.focal is None:
+            raise ValueError("no focal length: pass focal= or a [3, 5] pose")
+        return float(self.focal)
+
+    def _render_and_gather(self, pose, focal):
+        self.renderer.render_pixels(pose, self.H, self.W, focal, self.shard.pixel_ids, self.rgb[: self.shard.n_local])
+        self.shard.assemble(self.rgb, self.image)
+        self.renderer.finish()
+
+    def run_batch(self, single_pose) -> np.ndarray:
+        if self.rank != 0:
+            raise RuntimeError("run_batch is the main rank's call; other ranks run serve()")
+        pose = np.asarray(single_pose.cpu() if isinstance(single_pose, torch.Tensor) else single_pose, dtype=np.float32)
+        focal = self._focal_of(pose)
+        pose, focal, _ = self._broadcast(pose[:3, :4], focal, False)
+        self._render_and_gather(pose, focal)
+        # postprocess (nerf_inferer.py:345-378)
+        self.renderer.to_rgba8(self.image, self.rgba)
+        self.img_cpu.copy_(self.rgba.view(self.H, self.W, 4), non_blocking=True)
+        if torch.device(self.renderer.device).type == "cuda":
+            torch.cuda.current_stream(self.renderer.device).synchronize()
+        return self.img_cpu.numpy().copy()
+
+    def serve(self, max_frames: int = -1) -> int:
+        """Loop of a non-main rank: render every broadcast pose until the stop message (or
+        ``max_frames``, the role of the reference's CI_TEST_PICTURES).  Returns frames rendered."""
+        n = 0
+        while max_frames < 0 or n < max_frames:
+            pose, focal, stop = self._broadcast(None, 0.0, False)
+            if stop:
+                break
+            self._render_and_gather(pose, focal)
+            n += 1
+        return n
+
+    def stop(self):
+        """Main rank: release the other ranks from ``serve``."""
+        if self.rank == 0 and self.world > 1:
+            self._broadcast(None, 0.0, True)
+
+
+class MainRankDDPRenderEngine:
+    """Rank-0 engine around a runner (dist_render/engine/ddp_engine.py:18-75)."""
+
+    def __init__(self, runner_factory: Callable[[], NerfDDPRunner], poses: Optional[List[np.ndarray]] = None,
+                 save_png: bool = False, save_path: str = ".", pose_num: int = -1):
+        self._factory, self.runner = runner_factory, None
+        self.poses, self.save_png, self.save_path, self.pose_num = poses, save_png, save_path, pose_num
+        self.latency: List[float] = []
+
+    def start(self, test: bool = False):
+        self.runner = self._factory()
+        if test:
+            self.run_test()
+
+    def warm_up(self, pose_num: int = 60):
+        for pose in (self.poses or [])[:pose_num]:
+            self.runner.run_batch(pose)
+
+    def run_for_latency(self):
+        self.latency = []
+        for i, pose in enumerate(self.poses or []):
+            t0 = time.time()
+            out = self.runner.run_batch(pose)
+            self.latency.append(time.time() - t0)
+            if self.save_png:
+                from PIL import Image
+
+                Image.fromarray(out).save(f"{self.save_path}/{i}.png")
+        if self.latency:
+            avg = sum(self.latency) / len(self.latency)
+            print("Latency:", avg, flush=True)
+            print("Throughput:", 1 / avg, flush=True)
+
+    def run_test(self):
+        if self.pose_num > 0 and self.poses:
+            self.poses = self.poses[: self.pose_num]
+        self.warm_up()
+        self.run_for_latency()
+
+    def submit(self, pose):
+        return self.runner.run_batch(pose)
+
+    def stop(self):
+        if self.runner is not None:
+            self.runner.stop()
+
+
+class OtherRankRenderEngine:
+    """Engine of ranks > 0 (dist_render/engine/render_engine.py:99-120)."""
+
+    def __init__(self, runner_factory: Callable[[], NerfDDPRunner], max_frames: int = -1):
+        self._factory, self.max_frames, self.frames = runner_factory, max_frames, 0
+
+    def start(self, test: bool = False):
+        runner = self._factory()
+        self.frames = runner.serve(self.max_frames)

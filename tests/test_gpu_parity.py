@@ -313,3 +313,27 @@ def test_tensor_core_mlp_rejects_other_shapes():
 
     with pytest.raises(GnrError, match="tensor-core MLP supports"):
         cuda_model(spec, mlp_mode=2)
+
+
+def test_runner_pose_to_uint8_image(tiny):
+    """The online entry point: pose -> rays -> render -> x255 / alpha / .byte() -> host image
+    (NerfDDPRunner.run_batch), against the oracle pushed through the reference's post-process
+    (dist_render/ddp_infer/nerf_inferer.py:366-370)."""
+    spec, field, model, rays, ref, got = tiny
+    from landmark_b200.engine import FrameRenderer, MainRankDDPRenderEngine, NerfDDPRunner
+
+    pose = scenes.make_pose(spec)
+    eng = MainRankDDPRenderEngine(lambda: NerfDDPRunner(FrameRenderer(model, spec.n_samples, True, chunk=4096),
+                                                        spec.height, spec.width, focal=spec.focal))
+    eng.start()
+    img = eng.submit(pose)
+    assert img.shape == (spec.height, spec.width, 4) and img.dtype == np.uint8 and (img[..., 3] == 255).all()
+    want = (ref["rgb_map"].reshape(spec.height, spec.width, 3) * 255).byte().numpy()
+    d = np.abs(img[..., :3].astype(np.int32) - want.astype(np.int32))
+    assert d.max() <= 1 and (d > 0).mean() < 0.01  # truncation can differ by one level where rgb*255 is near an integer
+    # [3, 5] pose with the focal in the last column, as the reference's pose files have it
+    pose5 = np.concatenate([pose, np.full((3, 1), spec.focal, dtype=np.float32)], 1)
+    eng2 = MainRankDDPRenderEngine(lambda: NerfDDPRunner(FrameRenderer(model, spec.n_samples, True), spec.height,
+                                                         spec.width, focal=None))
+    eng2.start()
+    assert np.array_equal(eng2.submit(pose5), img)

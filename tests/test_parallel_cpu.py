@@ -65,3 +65,79 @@ def test_two_rank_gather_over_gloo(tmp_path):
     image = torch.load(out)
     pid = torch.arange(H * W, dtype=torch.float32)
     assert torch.equal(image, torch.stack([pid, pid * 2, pid + 0.5], 1))
+
+
+class _FakeRenderer:
+    """CPU stand-in for FrameRenderer: colour = f(pose, pixel), rgba by torch ops."""
+
+    device = "cpu"
+
+    def render_pixels(self, pose, H, W, focal, pixel_ids, rgb_out):
+        pid = pixel_ids.to(torch.float32)
+        base = float(np.asarray(pose).sum()) + focal
+        rgb_out[:, 0] = (pid % 251) / 251.0
+        rgb_out[:, 1] = ((pid * 7 + base) % 13) / 13.0
+        rgb_out[:, 2] = 0.5
+
+    def finish(self):
+        pass
+
+    def to_rgba8(self, image, out):
+        out[:, :3] = (image * 255).clamp(0, 255).to(torch.uint8)
+        out[:, 3] = 255
+
+
+def _expected(pose, focal, H, W):
+    pid = torch.arange(H * W, dtype=torch.float32)
+    base = float(np.asarray(pose, dtype=np.float32)[:3, :4].sum()) + focal
+    img = torch.stack([(pid % 251) / 251.0, ((pid * 7 + base) % 13) / 13.0, torch.full_like(pid, 0.5)], 1)
+    out = torch.full((H * W, 4), 255, dtype=torch.uint8)
+    out[:, :3] = (img * 255).clamp(0, 255).to(torch.uint8)
+    return out.view(H, W, 4).numpy()
+
+
+def _engine_worker(rank, world, port, H, W, out):
+    from landmark_b200.engine import MainRankDDPRenderEngine, NerfDDPRunner, OtherRankRenderEngine
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        factory = lambda: NerfDDPRunner(_FakeRenderer(), H, W, focal=100.0, rank=rank, world=world)  # noqa: E731
+        poses = [np.eye(4, dtype=np.float32)[:3] * (k + 1) for k in range(3)]
+        if rank == 0:
+            eng = MainRankDDPRenderEngine(factory, poses=poses)
+            eng.start()
+            imgs = [eng.submit(p) for p in poses]
+            eng.stop()
+            torch.save(imgs, out)
+        else:
+            eng = OtherRankRenderEngine(factory)
+            eng.start()
+            assert eng.frames == 3
+    finally:
+        dist.destroy_process_group()
+
+
+def test_engine_protocol_two_ranks_over_gloo(tmp_path):
+    """Main-rank engine submits three poses; the other rank sits in its serve loop, renders its
+    tiles for each broadcast pose and is released by the stop message."""
+    H, W = 40, 72
+    out = str(tmp_path / "imgs.pt")
+    mp.spawn(_engine_worker, args=(2, _free_port(), H, W, out), nprocs=2, join=True)
+    imgs = torch.load(out, weights_only=False)
+    for k, img in enumerate(imgs):
+        pose = np.eye(4, dtype=np.float32)[:3] * (k + 1)
+        assert img.shape == (H, W, 4) and img.dtype == np.uint8
+        assert np.array_equal(img, _expected(pose, 100.0, H, W))
+
+
+def test_engine_single_rank_cpu_fake():
+    from landmark_b200.engine import MainRankDDPRenderEngine, NerfDDPRunner
+
+    eng = MainRankDDPRenderEngine(lambda: NerfDDPRunner(_FakeRenderer(), 30, 50, focal=None),
+                                  poses=[np.concatenate([np.eye(3), np.zeros((3, 1)), np.full((3, 1), 80.0)], 1)])
+    eng.start(test=True)
+    assert len(eng.latency) == 1
+    img = eng.submit(eng.poses[0])
+    assert np.array_equal(img, _expected(eng.poses[0], 80.0, 30, 50))
