@@ -193,6 +193,47 @@ int gnr_composite(GnrModel* m, int64_t n_rays, int white_bg, void* workspace, si
                   int64_t max_valid, int64_t max_app, int n_samples, float* rgb_map, float* depth_map,
                   void* stream);
 
+/* ---- split-stage and point-mode entries ------------------------------------------------------
+ * Building blocks for renderers that spread ONE field over several GPUs and exchange samples or
+ * partial results with collectives: the reference's branch (block) parallel model
+ * (app/models/gridnerf_parallel.py:279-338,765-859) and its tensor (channel) parallel model
+ * (app/models/gridnerf_tensor_parallel.py:198-217,284-330).  The host composes them with
+ * torch.distributed calls (landmark_b200/model_parallel.py). */
+
+/* Normalised coordinates ``xyz[i][3]`` (normalize_coord, gridnerf_sequential.py:203-204) and ray
+ * number of every valid sample of the last gnr_sample on this workspace. */
+int gnr_valid_positions(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+                        size_t workspace_bytes, int64_t max_valid, float* xyz, int32_t* ray_index, void* stream);
+/* compute_densityfeature + feature2density at explicit normalised points (block owner side of
+ * gridnerf_parallel.py:765-790).  ``sigma_feature`` may be NULL. */
+int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_feature, float* sigma, void* stream);
+/* raw2alpha + app_mask + compaction with sigma supplied by the caller (``sigma[max_valid]``, one
+ * value per valid sample, as gathered from the block owners; gridnerf_parallel.py:791-800).
+ * ``app_index[max_app]`` (optional) receives the appearance list. */
+int gnr_weights_from_sigma(GnrModel* m, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
+                           int64_t max_valid, int64_t max_app, const float* sigma, int32_t* app_index, void* stream);
+/* compute_appfeature only (fp32 gather + basis projection) for the appearance list of the
+ * workspace: with a channel slice of the planes and the matching columns of basis_mat these are
+ * the partial sums a tensor-parallel rank contributes (gridnerf_tensor_parallel.py:284-300). */
+int gnr_app_features(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+                     size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* features, void* stream);
+/* Scratch for the two calls below (256-byte aligned, caller-allocated). */
+int gnr_points_scratch_bytes(const GnrModel* m, int64_t n, size_t* bytes_h);
+/* compute_appfeature + MLPRender_Fea at explicit points: ``xyz[n][3]`` normalised, ``view[n][3]``
+ * -> ``rgb[n][3]`` (and optionally ``features[n][app_dim]``).  Block owner side of
+ * gridnerf_parallel.py:801-859. */
+int gnr_appearance_points(GnrModel* m, const float* xyz, const float* view, int64_t n, void* scratch,
+                          size_t scratch_bytes, float* features, float* rgb, void* stream);
+/* MLPRender_Fea alone on explicit ``features[n][app_dim]`` and ``view[n][3]`` (the sample slice a
+ * tensor-parallel rank owns after the reduction, gridnerf_tensor_parallel.py:301-325). */
+int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,
+                     size_t scratch_bytes, float* rgb, void* stream);
+/* Compositing with per-appearance-sample colours supplied by the caller
+ * (``rgb_samples[n_rgb][3]`` in the order of the workspace's appearance list). */
+int gnr_composite_rgb(GnrModel* m, int64_t n_rays, int white_bg, void* workspace, size_t workspace_bytes,
+                      int64_t max_valid, int64_t max_app, int n_samples, const float* rgb_samples, int64_t n_rgb,
+                      float* rgb_map, float* depth_map, void* stream);
+
 /* Per-stage timing with CUDA events recorded on the launching stream around every stage of
  * gnr_render_chunk / gnr_render_host (the counterpart of the reference's PipeStagesProfiler,
  * dist_render/comm/profiler.py:18-69, at kernel granularity).  gnr_profile_collect waits for

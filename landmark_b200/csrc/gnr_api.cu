@@ -552,18 +552,32 @@ static int copy_out(void* dst, const void* src, size_t bytes, cudaStream_t st) {
 
 static int run_app_gather(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, int64_t max_app, cudaStream_t st) {
-  if (gnr_tc_basis_fused(m)) return launch_app_products(m, p, rays, n, ws, L, max_app, m->cfg.mlp_mode == 1 ? 2 : 1, st);
-  return launch_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st);
+  (void)n;
+  (void)max_valid;
+  (void)max_app;
+  const GnrCoords c = gnr_coords_app(rays, ws, L);
+  if (gnr_tc_basis_fused(m)) {
+    unsigned char* hi = (unsigned char*)(ws + L.app_prod);
+    return launch_app_products(m, p, c, hi, hi + L.app_prod_image, L.app_prod_tile, m->cfg.mlp_mode == 1 ? 2 : 1, st);
+  }
+  return launch_app_gather(m, p, c, L.feat_stride, (float*)(ws + L.app_feat), st);
+}
+
+static int run_mlp(GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L, int write_features,
+                   cudaStream_t st) {
+  const GnrCoords c = gnr_coords_app(rays, ws, L);
+  float* feat = (float*)(ws + L.app_feat);
+  float* rgb = (float*)(ws + L.app_rgb);
+  if (m->cfg.mlp_mode == 0) return launch_mlp_simt(m, p, c, L.feat_stride, feat, rgb, st);
+  const unsigned char* hi = (const unsigned char*)(ws + L.app_prod);
+  return launch_mlp_tc(m, p, c, L.feat_stride, feat, write_features ? feat : nullptr, hi, hi + L.app_prod_image,
+                       L.app_prod_tile, rgb, (int32_t*)(ws + L.status), 0, st);
 }
 
 static int run_appearance(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, int64_t max_app, cudaStream_t st) {
   GNR_LAUNCH_OK(run_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
-  if (m->cfg.mlp_mode == 0) {
-    GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
-  } else {
-    GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, /*write_features=*/1, st));
-  }
+  GNR_LAUNCH_OK(run_mlp(m, p, rays, ws, L, /*write_features=*/1, st));
   return 0;
 }
 
@@ -600,7 +614,7 @@ extern "C" int gnr_density(GnrModel* m, const float* rays, int64_t n, int S, voi
   char* ws = (char*)workspace;
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, 0);
   GnrSampleParams p = gnr_sample_params(m, S);
-  GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
+  GNR_LAUNCH_OK(launch_density(m, p, gnr_coords_valid(rays, ws, L), (float*)(ws + L.sigma_feat), (float*)(ws + L.sigma), st));
   if (copy_out(sigma_feature, ws + L.sigma_feat, (size_t)max_valid * 4, st)) return -2;
   if (copy_out(sigma, ws + L.sigma, (size_t)max_valid * 4, st)) return -2;
   return 0;
@@ -672,7 +686,7 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   }
   {
     StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
-    GNR_LAUNCH_OK(launch_density(m, p, rays, n, ws, L, max_valid, st));
+    GNR_LAUNCH_OK(launch_density(m, p, gnr_coords_valid(rays, ws, L), (float*)(ws + L.sigma_feat), (float*)(ws + L.sigma), st));
   }
   {
     StageScope sc(m, GNR_STAGE_WEIGHTS, 1, st);
@@ -688,11 +702,7 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   }
   {
     StageScope sc(m, GNR_STAGE_MLP, 1, st);
-    if (m->cfg.mlp_mode == 0) {
-      GNR_LAUNCH_OK(launch_mlp_simt(m, p, rays, ws, L, max_app, st));
-    } else {
-      GNR_LAUNCH_OK(launch_mlp_tc(m, p, rays, ws, L, max_app, /*write_features=*/0, st));
-    }
+    GNR_LAUNCH_OK(run_mlp(m, p, rays, ws, L, /*write_features=*/0, st));
   }
   {
     StageScope sc(m, GNR_STAGE_COMPOSITE, 1, st);
@@ -752,6 +762,227 @@ extern "C" int gnr_render_chunk(GnrModel* m, const float* rays, int64_t n, int S
   DeviceGuard g(m->device);
   return render_chunk_impl(m, rays, n, S, white_bg, (char*)workspace, max_valid, max_app, rgb_map, depth_map,
                            (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// split-stage and point-mode entries (model-parallel renderers compose these with collectives)
+// ---------------------------------------------------------------------------------------------
+static GnrCoords coords_points(const float* xyz, const float* view, int64_t n) {
+  GnrCoords c;
+  memset(&c, 0, sizeof(c));
+  c.xyz_direct = xyz;
+  c.view_direct = view;
+  c.total_direct = n;
+  c.capacity = n;
+  return c;
+}
+
+struct PointScratch {
+  size_t status, feat, prod, total, prod_image;
+  int tile_bytes, terms;
+};
+
+static PointScratch point_scratch(const GnrModel* m, int64_t n) {
+  PointScratch s;
+  memset(&s, 0, sizeof(s));
+  size_t off = 0;
+  s.status = off;
+  off = align_up(off + GNR_ST_WORDS * 4, 256);
+  s.feat = off;
+  off = align_up(off + (size_t)n * 28 * 4, 256);
+  if (m->cfg.mlp_mode != 0 && gnr_tc_basis_fused(m)) {
+    s.terms = m->cfg.mlp_mode == 1 ? 2 : 1;
+    s.tile_bytes = (m->mlp.n_prod / 8) * 2048;
+    s.prod_image = align_up((size_t)((n + 127) / 128) * s.tile_bytes, 256);
+    s.prod = off;
+    off += s.prod_image * s.terms;
+  }
+  s.total = off;
+  return s;
+}
+
+static int check_points(const GnrModel* m, const char* who, int64_t n, const void* scratch, size_t scratch_bytes) {
+  if (!m) {
+    gnr_set_error("%s: null model", who);
+    return -1;
+  }
+  if (n < 0 || n > 0x7fffffffLL) {
+    gnr_set_error("%s: bad point count %lld", who, (long long)n);
+    return -1;
+  }
+  if (!m->mlp.w1t || !m->app[0].plane || !m->den[0].plane) {
+    gnr_set_error("%s: model parameters have not been uploaded", who);
+    return -1;
+  }
+  if (scratch_bytes != (size_t)-1) {
+    const PointScratch s = point_scratch(m, n);
+    if (!scratch || scratch_bytes < s.total || ((uintptr_t)scratch & 255) != 0) {
+      gnr_set_error("%s: scratch must be 256-byte aligned and hold %zu bytes (got %zu)", who, s.total, scratch_bytes);
+      return -1;
+    }
+  }
+  return 0;
+}
+
+extern "C" int gnr_points_scratch_bytes(const GnrModel* m, int64_t n, size_t* bytes_h) {
+  if (!m || !bytes_h || n < 0) {
+    gnr_set_error("gnr_points_scratch_bytes: bad argument");
+    return -1;
+  }
+  *bytes_h = point_scratch(m, n).total;
+  return 0;
+}
+
+extern "C" int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_feature, float* sigma, void* stream) {
+  int rc = check_points(m, "gnr_density_points", n, nullptr, (size_t)-1);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!xyz || !sigma) {
+    gnr_set_error("gnr_density_points: null xyz or sigma");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  GnrSampleParams p = gnr_sample_params(m, 1);
+  GNR_LAUNCH_OK(launch_density(m, p, coords_points(xyz, nullptr, n), sigma_feature, sigma, (cudaStream_t)stream));
+  return 0;
+}
+
+static int mlp_points(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, char* sc, const PointScratch& S, int fused,
+                      float* feat_copy, float* rgb, cudaStream_t st) {
+  float* feat = (float*)(sc + S.feat);
+  if (m->cfg.mlp_mode == 0) {
+    GNR_LAUNCH_OK(launch_mlp_simt(m, p, c, 28, feat, rgb, st));
+  } else {
+    const unsigned char* hi = (const unsigned char*)(sc + S.prod);
+    GNR_LAUNCH_OK(launch_mlp_tc(m, p, c, 28, feat, (fused && feat_copy) ? feat : nullptr, hi, hi + S.prod_image, S.tile_bytes, rgb,
+                                (int32_t*)(sc + S.status), fused ? 0 : 1, st));
+  }
+  if (feat_copy) {
+    GNR_CUDA_OK(cudaMemcpy2DAsync(feat_copy, (size_t)m->cfg.app_dim * 4, feat, 28 * 4, (size_t)m->cfg.app_dim * 4,
+                                  (size_t)c.total_direct, cudaMemcpyDeviceToDevice, st));
+  }
+  return 0;
+}
+
+extern "C" int gnr_appearance_points(GnrModel* m, const float* xyz, const float* view, int64_t n, void* scratch,
+                                     size_t scratch_bytes, float* features, float* rgb, void* stream) {
+  int rc = check_points(m, "gnr_appearance_points", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!xyz || !view || !rgb) {
+    gnr_set_error("gnr_appearance_points: null xyz, view or rgb");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = (char*)scratch;
+  const PointScratch S = point_scratch(m, n);
+  GnrSampleParams p = gnr_sample_params(m, 1);
+  const GnrCoords c = coords_points(xyz, view, n);
+  GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+  const int fused = m->cfg.mlp_mode != 0 && gnr_tc_basis_fused(m);
+  if (fused) {
+    unsigned char* hi = (unsigned char*)(sc + S.prod);
+    GNR_LAUNCH_OK(launch_app_products(m, p, c, hi, hi + S.prod_image, S.tile_bytes, S.terms, st));
+  } else {
+    GNR_LAUNCH_OK(launch_app_gather(m, p, c, 28, (float*)(sc + S.feat), st));
+  }
+  return mlp_points(m, p, c, sc, S, fused, features, rgb, st);
+}
+
+extern "C" int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,
+                                size_t scratch_bytes, float* rgb, void* stream) {
+  int rc = check_points(m, "gnr_mlp_features", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!features || !view || !rgb) {
+    gnr_set_error("gnr_mlp_features: null features, view or rgb");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = (char*)scratch;
+  const PointScratch S = point_scratch(m, n);
+  GnrSampleParams p = gnr_sample_params(m, 1);
+  GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+  GNR_CUDA_OK(cudaMemsetAsync(sc + S.feat, 0, (size_t)n * 28 * 4, st));
+  GNR_CUDA_OK(cudaMemcpy2DAsync(sc + S.feat, 28 * 4, features, (size_t)m->cfg.app_dim * 4, (size_t)m->cfg.app_dim * 4, (size_t)n,
+                                cudaMemcpyDeviceToDevice, st));
+  return mlp_points(m, p, coords_points(nullptr, view, n), sc, S, /*fused=*/0, nullptr, rgb, st);
+}
+
+extern "C" int gnr_valid_positions(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                                   int64_t max_valid, float* xyz, int32_t* ray_index, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, 0, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays || !xyz) {
+    gnr_set_error("gnr_valid_positions: null rays or xyz");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, 0);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_positions(m, p, gnr_coords_valid(rays, ws, L), xyz, ray_index, (cudaStream_t)stream));
+  return 0;
+}
+
+extern "C" int gnr_weights_from_sigma(GnrModel* m, int64_t n, int S, void* workspace, size_t ws_bytes, int64_t max_valid,
+                                      int64_t max_app, const float* sigma_in, int32_t* app_index, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!sigma_in) {
+    gnr_set_error("gnr_weights_from_sigma: null sigma");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_CUDA_OK(cudaMemcpyAsync(ws + L.sigma, sigma_in, (size_t)max_valid * 4, cudaMemcpyDeviceToDevice, st));
+  GNR_LAUNCH_OK(launch_weights(m, p, n, ws, L, max_valid, max_app, st));
+  if (copy_out(app_index, ws + L.app_index, (size_t)max_app * 4, st)) return -2;
+  return 0;
+}
+
+extern "C" int gnr_app_features(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                                int64_t max_valid, int64_t max_app, float* features, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays || !features) {
+    gnr_set_error("gnr_app_features: null rays or features");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_app_gather(m, p, gnr_coords_app(rays, ws, L), L.feat_stride, (float*)(ws + L.app_feat), st));
+  GNR_CUDA_OK(cudaMemcpy2DAsync(features, (size_t)m->cfg.app_dim * 4, ws + L.app_feat, (size_t)L.feat_stride * 4,
+                                (size_t)m->cfg.app_dim * 4, (size_t)max_app, cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
+extern "C" int gnr_composite_rgb(GnrModel* m, int64_t n, int white_bg, void* workspace, size_t ws_bytes, int64_t max_valid,
+                                 int64_t max_app, int S, const float* rgb_samples, int64_t n_samples_rgb, float* rgb_map,
+                                 float* depth_map, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (n_samples_rgb < 0 || n_samples_rgb > max_app || (!rgb_samples && n_samples_rgb > 0)) {
+    gnr_set_error("gnr_composite_rgb: %lld colours do not fit the appearance list (capacity %lld)", (long long)n_samples_rgb,
+                  (long long)max_app);
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  if (n_samples_rgb > 0)
+    GNR_CUDA_OK(cudaMemcpyAsync(ws + L.app_rgb, rgb_samples, (size_t)n_samples_rgb * 12, cudaMemcpyDeviceToDevice, st));
+  GNR_LAUNCH_OK(launch_composite(m, n, white_bg, ws, L, rgb_map, depth_map, st));
+  return 0;
 }
 
 // ---------------------------------------------------------------------------------------------

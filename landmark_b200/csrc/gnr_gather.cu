@@ -70,17 +70,29 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
   }
 }
 
-// Position of one compacted sample, recomputed exactly as the sampler computed it, then
-// normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
-__device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const float* __restrict__ rays,
-                                           const float* __restrict__ t_min, uint32_t id, float& x, float& y, float& z) {
+// Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
+// computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
+__device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCoords& c, long long i, float& x, float& y,
+                                           float& z) {
+  if (c.xyz_direct) {
+    x = __ldg(c.xyz_direct + i * 3 + 0);
+    y = __ldg(c.xyz_direct + i * 3 + 1);
+    z = __ldg(c.xyz_direct + i * 3 + 2);
+    return;
+  }
+  const uint32_t id = __ldg(c.ids + (c.index ? (long long)__ldg(c.index + i) : i));
   const uint32_t ray = id >> p.kbits;
   const int k = (int)(id & ((1u << p.kbits) - 1u));
-  const float* r = rays + (size_t)ray * 6;
-  const float t = gnr_sample_t(__ldg(t_min + ray), p.step, k);
+  const float* r = c.rays + (size_t)ray * 6;
+  const float t = gnr_sample_t(__ldg(c.t_min + ray), p.step, k);
   x = gnr_normalize(gnr_point(__ldg(r + 0), __ldg(r + 3), t), p.lo[0], p.inv[0]);
   y = gnr_normalize(gnr_point(__ldg(r + 1), __ldg(r + 4), t), p.lo[1], p.inv[1]);
   z = gnr_normalize(gnr_point(__ldg(r + 2), __ldg(r + 5), t), p.lo[2], p.inv[2]);
+}
+
+__device__ __forceinline__ long long coords_total(const GnrCoords& c) {
+  const long long t = c.total_ptr ? (long long)*c.total_ptr : c.total_direct;
+  return min(t, c.capacity);
 }
 
 __device__ __forceinline__ float density_activation(float f, float shift, int act) {
@@ -101,11 +113,10 @@ __device__ __forceinline__ void cta_range(long long total, long long& beg, long 
 
 template <int J, int NP>
 __global__ void __launch_bounds__(kBlock)
-density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
-               const uint32_t* __restrict__ ids, const int32_t* __restrict__ total_ptr, long long capacity,
-               float shift, int act, float* __restrict__ sigma_feat, float* __restrict__ sigma) {
+density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, int act, float* __restrict__ sigma_feat,
+               float* __restrict__ sigma) {
   const int c4 = threadIdx.x & 3;
-  const long long total = min((long long)*total_ptr, capacity);
+  const long long total = coords_total(crd);
   // Each CTA walks one contiguous range of the (ray-major) list, so that the texels a ray
   // touches are still in this SM's L1 when the next samples and the neighbouring ray need them.
   long long range_beg, range_end;
@@ -117,7 +128,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ ray
     float acc = 0.0f;
     if (active) {
       float x, y, z;
-      sample_xyz(p, rays, t_min, __ldg(ids + i), x, y, z);
+      sample_xyz(p, crd, i, x, y, z);
       const int n_planes = NP > 0 ? NP : planes.n;
 #pragma unroll
       for (int pi = 0; pi < n_planes; ++pi) {
@@ -132,7 +143,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ ray
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     if (active && c4 == 0) {
-      sigma_feat[i] = acc;
+      if (sigma_feat) sigma_feat[i] = acc;
       sigma[i] = density_activation(acc, shift, act);
     }
   }
@@ -144,9 +155,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ ray
 // so that the four lanes of a quad read disjoint banks.
 template <int J>
 __global__ void __launch_bounds__(kBlock)
-app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
-                  const uint32_t* __restrict__ ids, const int32_t* __restrict__ app_index,
-                  const int32_t* __restrict__ total_ptr, long long capacity, const float* __restrict__ basis_blocked,
+app_gather_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, const float* __restrict__ basis_blocked,
                   int feat_stride, float* __restrict__ feat_out) {
   extern __shared__ float4 smem_f4[];
   float* wsm = reinterpret_cast<float*>(smem_f4);
@@ -156,7 +165,7 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ 
   __syncthreads();
 
   const int c4 = threadIdx.x & 3;
-  const long long total = min((long long)*total_ptr, capacity);
+  const long long total = coords_total(crd);
   long long range_beg, range_end;
   cta_range(total, range_beg, range_end);
   for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
@@ -167,7 +176,7 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ 
     for (int o = 0; o < kFeat; ++o) acc[o] = 0.0f;
     if (active) {
       float x, y, z;
-      sample_xyz(p, rays, t_min, __ldg(ids + __ldg(app_index + j_app)), x, y, z);
+      sample_xyz(p, crd, j_app, x, y, z);
       for (int pi = 0; pi < planes.n; ++pi) {
         float4 prod[J];
         pair_products<J>(planes.p[pi], x, y, z, c4, prod);
@@ -211,19 +220,17 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ 
 // With TA == 2 the fp16 rounding residual goes to a second image of the same shape.
 template <int J, int NP, int TA>
 __global__ void __launch_bounds__(kBlock)
-app_products_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min,
-                    const uint32_t* __restrict__ ids, const int32_t* __restrict__ app_index,
-                    const int32_t* __restrict__ total_ptr, long long capacity, unsigned char* __restrict__ prod_hi,
+app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
                     unsigned char* __restrict__ prod_lo, int tile_bytes) {
   const int c4 = threadIdx.x & 3;
-  const long long total = min((long long)*total_ptr, capacity);
+  const long long total = coords_total(crd);
   long long range_beg, range_end;
   cta_range(total, range_beg, range_end);
   for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
     const long long j_app = base + ((threadIdx.x & 31) >> 2);
     if (j_app >= range_end) continue;
     float x, y, z;
-    sample_xyz(p, rays, t_min, __ldg(ids + __ldg(app_index + j_app)), x, y, z);
+    sample_xyz(p, crd, j_app, x, y, z);
     const long long tile = j_app >> 7;
     const int row = (int)(j_app & 127);
     const size_t out0 = (size_t)tile * tile_bytes + (size_t)row * 16 + (size_t)(c4 & 1) * 8;
@@ -254,6 +261,20 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict_
   }
 }
 
+// Normalised positions (and ray numbers) of the valid samples, for renderers that route
+// samples to the GPU that owns their part of the field.
+__global__ void positions_kernel(GnrSampleParams p, GnrCoords crd, float* __restrict__ xyz, int32_t* __restrict__ ray_index) {
+  const long long total = coords_total(crd);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    float x, y, z;
+    sample_xyz(p, crd, i, x, y, z);
+    xyz[i * 3 + 0] = x;
+    xyz[i * 3 + 1] = y;
+    xyz[i * 3 + 2] = z;
+    if (ray_index) ray_index[i] = (int32_t)(__ldg(crd.ids + i) >> p.kbits);
+  }
+}
+
 PlaneSet make_set(const GnrPlane* src, int n) {
   PlaneSet s;
   s.n = n;
@@ -263,25 +284,39 @@ PlaneSet make_set(const GnrPlane* src, int n) {
 
 }  // namespace
 
-int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                   const GnrWs& L, int64_t max_valid, cudaStream_t st) {
-  (void)n;
+GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L) {
+  GnrCoords c;
+  c.rays = rays;
+  c.t_min = (const float*)(ws + L.t_min);
+  c.ids = (const uint32_t*)(ws + L.ids);
+  c.index = nullptr;
+  c.xyz_direct = nullptr;
+  c.view_direct = nullptr;
+  c.total_ptr = (const int32_t*)(ws + L.offsets) + L.n_rays;
+  c.total_direct = 0;
+  c.capacity = L.max_valid;
+  return c;
+}
+
+GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L) {
+  GnrCoords c = gnr_coords_valid(rays, ws, L);
+  c.index = (const int32_t*)(ws + L.app_index);
+  c.total_ptr = (const int32_t*)(ws + L.app_offsets) + L.n_rays;
+  c.capacity = L.max_app;
+  return c;
+}
+
+int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,
+                   cudaStream_t st) {
   PlaneSet set = make_set(m->den, m->cfg.n_pairs);
   const int J = m->den[0].C / 16;
   const int grid = m->sm_count * 4;
-  const float* t_min = (const float*)(ws + L.t_min);
-  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
-  const int32_t* total = (const int32_t*)(ws + L.offsets) + n;
-  float* sf = (float*)(ws + L.sigma_feat);
-  float* sg = (float*)(ws + L.sigma);
-#define GNR_DEN(JJ)                                                                                               \
-  do {                                                                                                            \
-    if (set.n == 3)                                                                                               \
-      density_kernel<JJ, 3><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,       \
-                                                     m->cfg.density_shift, m->cfg.density_act, sf, sg);           \
-    else                                                                                                          \
-      density_kernel<JJ, 0><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, total, (long long)max_valid,       \
-                                                     m->cfg.density_shift, m->cfg.density_act, sf, sg);           \
+#define GNR_DEN(JJ)                                                                                                   \
+  do {                                                                                                                \
+    if (set.n == 3)                                                                                                   \
+      density_kernel<JJ, 3><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma); \
+    else                                                                                                              \
+      density_kernel<JJ, 0><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma); \
   } while (0)
   switch (J) {
     case 1: GNR_DEN(1); break;
@@ -294,23 +329,16 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* ray
   return (int)cudaGetLastError();
 }
 
-int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                      const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st) {
-  (void)max_valid;
+int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, float* feat,
+                      cudaStream_t st) {
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
-  const float* t_min = (const float*)(ws + L.t_min);
-  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
-  const int32_t* app_index = (const int32_t*)(ws + L.app_index);
-  const int32_t* total = (const int32_t*)(ws + L.app_offsets) + n;
-  float* feat = (float*)(ws + L.app_feat);
   size_t smem = (size_t)m->cfg.n_pairs * 4 * (4 * J * kFeat + 8) * sizeof(float);
 #define GNR_APP(JJ)                                                                                            \
   do {                                                                                                         \
     cudaFuncSetAttribute(app_gather_kernel<JJ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-    app_gather_kernel<JJ><<<grid, kBlock, smem, st>>>(p, set, rays, t_min, ids, app_index, total,              \
-                                                      (long long)max_app, m->mlp.basis_blocked, L.feat_stride, feat); \
+    app_gather_kernel<JJ><<<grid, kBlock, smem, st>>>(p, set, c, m->mlp.basis_blocked, feat_stride, feat);     \
   } while (0)
   switch (J) {
     case 1: GNR_APP(1); break;
@@ -323,21 +351,12 @@ int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* 
   return (int)cudaGetLastError();
 }
 
-int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                        const GnrWs& L, int64_t max_app, int terms, cudaStream_t st) {
+int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* hi,
+                        unsigned char* lo, int tile_bytes, int terms, cudaStream_t st) {
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
-  const float* t_min = (const float*)(ws + L.t_min);
-  const uint32_t* ids = (const uint32_t*)(ws + L.ids);
-  const int32_t* app_index = (const int32_t*)(ws + L.app_index);
-  const int32_t* total = (const int32_t*)(ws + L.app_offsets) + n;
-  unsigned char* hi = (unsigned char*)(ws + L.app_prod);
-  unsigned char* lo = hi + L.app_prod_image;
-  const int tile_bytes = L.app_prod_tile;
-#define GNR_PRD(JJ, NPP, TT)                                                                                     \
-  app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, rays, t_min, ids, app_index, total,          \
-                                                            (long long)max_app, hi, lo, tile_bytes)
+#define GNR_PRD(JJ, NPP, TT) app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, c, hi, lo, tile_bytes)
   if (J == 3 && set.n == 3) {
     if (terms == 2) GNR_PRD(3, 3, 2); else GNR_PRD(3, 3, 1);
   } else if (J == 1) {
@@ -351,5 +370,11 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const float
     return -1;
   }
 #undef GNR_PRD
+  return (int)cudaGetLastError();
+}
+
+int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
+                     cudaStream_t st) {
+  positions_kernel<<<m->sm_count * 8, 256, 0, st>>>(p, c, xyz, ray_index);
   return (int)cudaGetLastError();
 }

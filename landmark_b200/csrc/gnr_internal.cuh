@@ -91,6 +91,21 @@ struct GnrWs {
   long long n_rays;
 };
 
+// Where a per-sample kernel finds item i: either through the chunk's compacted lists
+// (ids[index ? index[i] : i] -> ray, sample -> position recomputed from the ray) or, in point
+// mode, from explicit arrays of normalised positions / view directions.
+struct GnrCoords {
+  const float* rays;
+  const float* t_min;
+  const uint32_t* ids;
+  const int32_t* index;       // optional indirection (appearance list -> valid list)
+  const float* xyz_direct;    // [n][3] normalised positions (point mode)
+  const float* view_direct;   // [n][3] view directions (point mode)
+  const int32_t* total_ptr;   // device count of items, or null ...
+  long long total_direct;     // ... then this host count
+  long long capacity;
+};
+
 void gnr_set_error(const char* fmt, ...);
 GnrWs gnr_ws_layout(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app);
 GnrSampleParams gnr_sample_params(const GnrModel* m, int S);
@@ -102,21 +117,28 @@ int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float*
                        const GnrWs& L, cudaStream_t st);
 int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, cudaStream_t st);
-int launch_density(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                   const GnrWs& L, int64_t max_valid, cudaStream_t st);
+GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L);
+GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L);
+int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,
+                   cudaStream_t st);
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                         int64_t max_valid, cudaStream_t st);
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                        int64_t max_valid, int64_t max_app, cudaStream_t st);
-int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                      const GnrWs& L, int64_t max_valid, int64_t max_app, cudaStream_t st);
-int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
-                        const GnrWs& L, int64_t max_app, int terms, cudaStream_t st);
+int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, float* feat,
+                      cudaStream_t st);
+int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* prod_hi,
+                        unsigned char* prod_lo, int tile_bytes, int terms, cudaStream_t st);
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
-int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                    int64_t max_app, cudaStream_t st);
-int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                  int64_t max_app, int write_features, cudaStream_t st);
+int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
+                     cudaStream_t st);
+int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat,
+                    float* rgb, cudaStream_t st);
+// feat_in: features for the non-fused variant; feat_out: optional copy of the projected features
+// (fused variant); prod_*: product tiles (fused variant); status: 8-word block for the wait flag.
+int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat_in,
+                  float* feat_out, const unsigned char* prod_hi, const unsigned char* prod_lo, int tile_bytes, float* rgb,
+                  int32_t* status, int force_unfused, cudaStream_t st);
 int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
                      float* depth_map, cudaStream_t st);
 int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,

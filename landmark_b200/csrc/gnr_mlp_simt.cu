@@ -55,9 +55,8 @@ __device__ __forceinline__ void dense_relu(const float* __restrict__ wt, const f
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-mlp_simt_kernel(MlpDims d, int kbits, const float* __restrict__ rays, const uint32_t* __restrict__ ids,
-                const int32_t* __restrict__ app_index, const int32_t* __restrict__ total_ptr, long long capacity,
-                const float* __restrict__ feat, const float* __restrict__ g_w1t, const float* __restrict__ g_w2t,
+mlp_simt_kernel(MlpDims d, int kbits, GnrCoords crd, const float* __restrict__ feat, const float* __restrict__ g_w1t,
+                const float* __restrict__ g_w2t,
                 const float* __restrict__ g_w3, const float* __restrict__ g_b1, const float* __restrict__ g_b2,
                 const float* __restrict__ g_b3, float* __restrict__ rgb_out) {
   extern __shared__ float4 smem_f4[];
@@ -81,7 +80,7 @@ mlp_simt_kernel(MlpDims d, int kbits, const float* __restrict__ rays, const uint
   if (threadIdx.x < 4) b3[threadIdx.x] = g_b3[threadIdx.x];
   __syncthreads();
 
-  const long long total = min((long long)*total_ptr, capacity);
+  const long long total = min(crd.total_ptr ? (long long)*crd.total_ptr : crd.total_direct, crd.capacity);
   const int A = d.app_dim, F = d.fea_pe, V = d.view_pe;
   const int base_s = A + 3, base_c = base_s + A * F, base_vs = base_c + A * F, base_vc = base_vs + 3 * V;
 
@@ -94,10 +93,16 @@ mlp_simt_kernel(MlpDims d, int kbits, const float* __restrict__ rays, const uint
       const float* fr = feat + (size_t)(live ? j : 0) * d.feat_stride;
       float view[3] = {0.0f, 0.0f, 0.0f};
       if (live) {
-        const uint32_t ray = __ldg(ids + __ldg(app_index + j)) >> kbits;
-        view[0] = __ldg(rays + (size_t)ray * 6 + 3);
-        view[1] = __ldg(rays + (size_t)ray * 6 + 4);
-        view[2] = __ldg(rays + (size_t)ray * 6 + 5);
+        const float* vsrc;
+        if (crd.view_direct) {
+          vsrc = crd.view_direct + (size_t)j * 3;
+        } else {
+          const uint32_t ray = __ldg(crd.ids + (crd.index ? (long long)__ldg(crd.index + j) : j)) >> kbits;
+          vsrc = crd.rays + (size_t)ray * 6 + 3;
+        }
+        view[0] = __ldg(vsrc + 0);
+        view[1] = __ldg(vsrc + 1);
+        view[2] = __ldg(vsrc + 2);
       }
       for (int it = q; it < A + 3; it += 4) xa[it * TM + m] = live ? (it < A ? __ldg(fr + it) : view[it - A]) : 0.0f;
       for (int idx = q; idx < A * F; idx += 4) {
@@ -136,8 +141,8 @@ mlp_simt_kernel(MlpDims d, int kbits, const float* __restrict__ rays, const uint
 
 }  // namespace
 
-int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                    int64_t max_app, cudaStream_t st) {
+int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat,
+                    float* rgb, cudaStream_t st) {
   if (m->cfg.hidden != HID) {
     gnr_set_error("fp32 MLP kernel supports featureC == %d (got %d)", HID, m->cfg.hidden);
     return -1;
@@ -148,17 +153,14 @@ int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const float* ra
   d.view_pe = m->cfg.view_pe > 0 ? m->cfg.view_pe : 0;
   d.in_dim = m->mlp.in_dim;
   d.k1_pad = m->mlp.k1_pad;
-  d.feat_stride = L.feat_stride;
+  d.feat_stride = feat_stride;
   size_t smem = ((size_t)d.k1_pad * HID + HID * HID + 3 * HID + 2 * HID + 4 + (size_t)d.k1_pad * TM + HID * TM) * sizeof(float);
   if (smem > 227 * 1024) {
     gnr_set_error("fp32 MLP kernel: input width %d needs %zu bytes of shared memory", d.in_dim, smem);
     return -1;
   }
   cudaFuncSetAttribute(mlp_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  const int32_t* total = (const int32_t*)(ws + L.app_offsets) + L.n_rays;
-  mlp_simt_kernel<<<m->sm_count, kThreads, smem, st>>>(
-      d, p.kbits, rays, (const uint32_t*)(ws + L.ids), (const int32_t*)(ws + L.app_index), total, (long long)max_app,
-      (const float*)(ws + L.app_feat), m->mlp.w1t, m->mlp.w2t, m->mlp.w3, m->mlp.b1, m->mlp.b2, m->mlp.b3,
-      (float*)(ws + L.app_rgb));
+  mlp_simt_kernel<<<m->sm_count, kThreads, smem, st>>>(d, p.kbits, c, feat, m->mlp.w1t, m->mlp.w2t, m->mlp.w3, m->mlp.b1,
+                                                       m->mlp.b2, m->mlp.b3, rgb);
   return (int)cudaGetLastError();
 }

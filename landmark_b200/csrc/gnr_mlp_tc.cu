@@ -179,11 +179,7 @@ __device__ __forceinline__ void store_group(unsigned char* a_hi, unsigned char* 
 }
 
 struct TcArgs {
-  const float* rays;
-  const uint32_t* ids;
-  const int32_t* app_index;
-  const int32_t* total_ptr;
-  long long capacity;
+  GnrCoords crd;
   const float* feat_in;           // BASIS == false: features from the CUDA-core gather
   float* feat_out;                // BASIS == true: optional copy of the projected features
   const unsigned char* prod_hi;   // BASIS == true: fp16 product tiles in operand layout
@@ -258,7 +254,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   uint32_t parity = 0, tparity = 0;
   bool copy_pending = false;
 
-  const long long total = min((long long)*a.total_ptr, a.capacity);
+  const long long total = min(a.crd.total_ptr ? (long long)*a.crd.total_ptr : a.crd.total_direct, a.crd.capacity);
   const long long n_tiles = (total + ROWS - 1) / ROWS;
   const long long tile_stride = (long long)gridDim.x * NSLOT;
   const uint32_t copy_bytes = (uint32_t)a.tile_bytes;
@@ -334,10 +330,16 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     {
       float view[3] = {0.0f, 0.0f, 0.0f};
       if (live) {
-        const uint32_t ray = __ldg(a.ids + __ldg(a.app_index + j)) >> a.kbits;
-        view[0] = __ldg(a.rays + (size_t)ray * 6 + 3);
-        view[1] = __ldg(a.rays + (size_t)ray * 6 + 4);
-        view[2] = __ldg(a.rays + (size_t)ray * 6 + 5);
+        const float* vsrc;
+        if (a.crd.view_direct) {
+          vsrc = a.crd.view_direct + (size_t)j * 3;
+        } else {
+          const uint32_t ray = __ldg(a.crd.ids + (a.crd.index ? (long long)__ldg(a.crd.index + j) : j)) >> a.kbits;
+          vsrc = a.crd.rays + (size_t)ray * 6 + 3;
+        }
+        view[0] = __ldg(vsrc + 0);
+        view[1] = __ldg(vsrc + 1);
+        view[2] = __ldg(vsrc + 2);
       }
       float x[K1];
 #pragma unroll
@@ -547,36 +549,33 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
   return 0;
 }
 
-int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const float* rays, char* ws, const GnrWs& L,
-                  int64_t max_app, int write_features, cudaStream_t st) {
+int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat_in,
+                  float* feat_out, const unsigned char* prod_hi, const unsigned char* prod_lo, int tile_bytes, float* rgb,
+                  int32_t* status, int force_unfused, cudaStream_t st) {
   if (!m->mlp.tc_image) {
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
   }
-  if (L.feat_stride != FEAT_STRIDE) {
+  if (feat_stride != FEAT_STRIDE) {
     gnr_set_error("tensor-core MLP expects a feature stride of %d floats", FEAT_STRIDE);
     return -1;
   }
-  const bool fused = gnr_tc_basis_fused(m) != 0;
+  const bool fused = gnr_tc_basis_fused(m) != 0 && !force_unfused;
   TcArgs a;
-  a.rays = rays;
-  a.ids = (const uint32_t*)(ws + L.ids);
-  a.app_index = (const int32_t*)(ws + L.app_index);
-  a.total_ptr = (const int32_t*)(ws + L.app_offsets) + L.n_rays;
-  a.capacity = (long long)max_app;
-  a.feat_in = (const float*)(ws + L.app_feat);
-  a.feat_out = (fused && write_features) ? (float*)(ws + L.app_feat) : nullptr;
-  a.prod_hi = fused ? (const unsigned char*)(ws + L.app_prod) : nullptr;
-  a.prod_lo = fused ? a.prod_hi + L.app_prod_image : nullptr;
-  a.tile_bytes = L.app_prod_tile;
+  a.crd = c;
+  a.feat_in = feat_in;
+  a.feat_out = fused ? feat_out : nullptr;
+  a.prod_hi = fused ? prod_hi : nullptr;
+  a.prod_lo = fused ? prod_lo : nullptr;
+  a.tile_bytes = tile_bytes;
   a.k0 = m->mlp.n_prod;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
   a.w3 = m->mlp.w3;
   a.b1 = m->mlp.b1;
   a.b2 = m->mlp.b2;
   a.b3 = m->mlp.b3;
-  a.rgb_out = (float*)(ws + L.app_rgb);
-  a.status = (int32_t*)(ws + L.status);
+  a.rgb_out = rgb;
+  a.status = status;
   a.kbits = p.kbits;
   if (m->cfg.mlp_mode == 1) return fused ? launch_variant<2, 1, true>(m, a, st) : launch_variant<2, 1, false>(m, a, st);
   if (m->cfg.mlp_mode == 2) return fused ? launch_variant<1, 3, true>(m, a, st) : launch_variant<1, 3, false>(m, a, st);

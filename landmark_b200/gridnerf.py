@@ -99,6 +99,7 @@ class B200GridNeRF(torch.nn.Module):
         group=None,
         is_train=False,
         mlp_mode: int = 0,
+        field_grid=None,
         **_ignored,
     ):
         super().__init__()
@@ -147,7 +148,9 @@ class B200GridNeRF(torch.nn.Module):
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
-        g = [int(v) for v in self.gridSize.tolist()]
+        # ``field_grid``: resolution of the stored planes when it differs from ``gridSize`` (which
+        # fixes the step size); a model that only samples and composites keeps 2x2 planes.
+        g = [int(v) for v in (field_grid if field_grid is not None else self.gridSize.tolist())]
         dp, dl, ap, al = [], [], [], []
         for i in range(len(self.vecMode)):
             m0, m1 = self.matMode[i]

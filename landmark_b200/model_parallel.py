@@ -1,0 +1,384 @@
+"""Renderers that spread ONE field over several GPUs.
+
+Two layouts of the reference are covered, both composed from the library's split-stage and
+point-mode entries plus ``torch.distributed`` collectives:
+
+* ``ChannelParallelRenderer`` -- tensor (channel) parallel rendering
+  (app/models/gridnerf_tensor_parallel.py:198-217,284-330; dist_render/kernel/cuda_render_extend.py:552-632):
+  every rank holds all density planes and a slice of the appearance channels with the matching
+  columns of ``basis_mat``.  All ranks sample the same rays; each computes its partial
+  ``[M_a, app_dim]`` projection; a reduce-scatter sums them and leaves every rank with the complete
+  features of ``M_a / W`` samples, on which it runs the MLP; an all-gather returns the colours.
+  (The reference all-gathers the products and sums; reduce-scatter moves W times fewer bytes.)
+
+* ``BlockParallelRenderer`` -- branch (block) parallel rendering
+  (app/models/gridnerf_parallel.py:279-338,765-859): the scene is cut into ``Px x Py`` blocks in
+  x-y, rank ``b`` owns the field of block ``b``.  Rays are data-parallel (each rank renders its
+  own rays); every rank samples its rays against the global box and occupancy mask, assigns each
+  valid sample to a block (``assign_blocks_to_samples``), and routes it to the owner with an
+  all-to-all.  Owners evaluate density (then, in a second round trip, colour) at the received
+  block-local points and send the values back; weights and compositing happen at the ray's rank.
+  (The reference replicates the sampling on every rank and all-gathers sigma and rgb.)
+
+Collectives go through a small ``Comm`` interface.  ``DistComm`` is the real thing (one rank per
+process).  ``LoopbackComm`` runs all ranks of a group inside one process in lock step, which is how
+the multi-rank logic is tested on a single GPU.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import check, lib
+from .gridnerf import B200GridNeRF, _ptr, _stream
+
+
+# ----------------------------------------------------------------------------------------------
+# collectives
+# ----------------------------------------------------------------------------------------------
+class DistComm:
+    """One rank per process over ``torch.distributed`` (NCCL on GPUs).  Every method takes and
+    returns a one-element list: the value of the local rank."""
+
+    def __init__(self, group=None):
+        import torch.distributed as dist
+
+        self.dist, self.group = dist, group
+        self.world = dist.get_world_size(group)
+        self.local_ranks = [dist.get_rank(group)]
+
+    def reduce_scatter_rows(self, xs: List[torch.Tensor]) -> List[torch.Tensor]:
+        x = xs[0]
+        out = torch.empty((x.shape[0] // self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        self.dist.reduce_scatter_tensor(out, x.contiguous(), group=self.group)
+        return [out]
+
+    def all_gather_rows(self, xs: List[torch.Tensor]) -> List[torch.Tensor]:
+        x = xs[0]
+        out = torch.empty((x.shape[0] * self.world,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        self.dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+        return [out]
+
+    def all_to_all_rows(self, xs: List[torch.Tensor], send_counts: List[List[int]]):
+        """Rows of ``xs[0]`` are grouped by destination rank (``send_counts[0][d]`` rows for rank d).
+        Returns the received rows (grouped by source rank) and the receive counts."""
+        x, sc = xs[0], send_counts[0]
+        cnt = torch.tensor(sc, dtype=torch.int64, device=x.device)
+        rcnt = torch.empty_like(cnt)
+        self.dist.all_to_all_single(rcnt, cnt, group=self.group)
+        rc = [int(v) for v in rcnt.cpu().tolist()]
+        out = torch.empty((sum(rc),) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+        self.dist.all_to_all_single(out, x.contiguous(), output_split_sizes=rc, input_split_sizes=sc, group=self.group)
+        return [out], [rc]
+
+
+class LoopbackComm:
+    """All ranks of the group live in this process; element ``r`` of every list is rank ``r``'s."""
+
+    def __init__(self, world: int):
+        self.world = world
+        self.local_ranks = list(range(world))
+
+    def reduce_scatter_rows(self, xs):
+        total = xs[0].clone()
+        for x in xs[1:]:
+            total = total + x
+        n = total.shape[0] // self.world
+        return [total[r * n:(r + 1) * n].clone() for r in range(self.world)]
+
+    def all_gather_rows(self, xs):
+        cat = torch.cat(list(xs), 0)
+        return [cat.clone() for _ in range(self.world)]
+
+    def all_to_all_rows(self, xs, send_counts):
+        outs, rcs = [], []
+        starts = [np.concatenate([[0], np.cumsum(sc)]) for sc in send_counts]
+        for d in range(self.world):
+            parts = [xs[s][starts[s][d]:starts[s][d + 1]] for s in range(self.world)]
+            outs.append(torch.cat(parts, 0))
+            rcs.append([int(send_counts[s][d]) for s in range(self.world)])
+        return outs, rcs
+
+
+# ----------------------------------------------------------------------------------------------
+# thin stage wrappers (no output copies, no host syncs except where a count is needed)
+# ----------------------------------------------------------------------------------------------
+class _Chunk:
+    """One model's view of one chunk of rays: workspace + the list sizes read back so far."""
+
+    def __init__(self, model: B200GridNeRF, rays: torch.Tensor, n_samples: int):
+        self.m = model
+        self.rays = model._prepare(rays)
+        self.n = self.rays.shape[0]
+        self.s = model._samples(n_samples)
+        self.keep, self.ws, self.ws_bytes, self.max_valid, self.max_app = model.workspace(self.n, self.s)
+        self.kbits = lib.gnr_sample_bits(self.s)
+        self.num_valid = self.num_app = 0
+        self.ids = self.app_index = None
+
+    def sample(self):
+        self.ids = torch.empty(self.max_valid, dtype=torch.int32, device=self.m.device)
+        check(lib.gnr_sample(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                             None, None, None, None, _ptr(self.ids), _stream()), "gnr_sample")
+        st = self.m.read_status(self.ws)
+        self.m.raise_on_status(st)
+        self.num_valid = int(st[_lib.ST_NUM_VALID])
+
+    def density(self):
+        check(lib.gnr_density(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                              None, None, _stream()), "gnr_density")
+
+    def positions(self):
+        xyz = torch.empty((self.max_valid, 3), dtype=torch.float32, device=self.m.device)
+        ray = torch.empty((self.max_valid,), dtype=torch.int32, device=self.m.device)
+        check(lib.gnr_valid_positions(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes,
+                                      self.max_valid, _ptr(xyz), _ptr(ray), _stream()), "gnr_valid_positions")
+        return xyz[: self.num_valid], ray[: self.num_valid].to(torch.int64)
+
+    def weights(self, sigma: Optional[torch.Tensor] = None):
+        self.app_index = torch.empty(self.max_app, dtype=torch.int32, device=self.m.device)
+        if sigma is None:
+            check(lib.gnr_weights(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                  self.max_app, None, None, None, None, None, _ptr(self.app_index), _stream()),
+                  "gnr_weights")
+        else:
+            full = torch.zeros(self.max_valid, dtype=torch.float32, device=self.m.device)
+            full[: self.num_valid] = sigma
+            check(lib.gnr_weights_from_sigma(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                             self.max_app, _ptr(full), _ptr(self.app_index), _stream()),
+                  "gnr_weights_from_sigma")
+        st = self.m.read_status(self.ws)
+        self.m.raise_on_status(st)
+        self.num_app = int(st[_lib.ST_NUM_APP])
+        self.app_index = self.app_index[: self.num_app].to(torch.int64)
+
+    def app_ray_index(self) -> torch.Tensor:
+        ids = self.ids[: self.num_valid].to(torch.int64) & 0xFFFFFFFF
+        return (ids[self.app_index] >> self.kbits)
+
+    def app_features(self) -> torch.Tensor:
+        feat = torch.empty((self.max_app, self.m.app_dim), dtype=torch.float32, device=self.m.device)
+        check(lib.gnr_app_features(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                   self.max_app, _ptr(feat), _stream()), "gnr_app_features")
+        return feat[: self.num_app]
+
+    def composite(self, rgb_samples: torch.Tensor, white_bg: bool):
+        rgb = torch.empty((self.n, 3), dtype=torch.float32, device=self.m.device)
+        depth = torch.empty((self.n,), dtype=torch.float32, device=self.m.device)
+        rgb_samples = rgb_samples.contiguous()
+        check(lib.gnr_composite_rgb(self.m._handle, self.n, int(bool(white_bg)), self.ws, self.ws_bytes, self.max_valid,
+                                    self.max_app, self.s, _ptr(rgb_samples) if rgb_samples.numel() else None,
+                                    rgb_samples.shape[0], _ptr(rgb), _ptr(depth), _stream()), "gnr_composite_rgb")
+        return rgb, depth
+
+
+def _scratch(model: B200GridNeRF, n: int):
+    nb = C.c_size_t(0)
+    check(lib.gnr_points_scratch_bytes(model._handle, n, C.byref(nb)), "gnr_points_scratch_bytes")
+    buf = torch.empty(nb.value + 256, dtype=torch.uint8, device=model.device)
+    off = (-buf.data_ptr()) % 256
+    return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off
+
+
+def mlp_features(model: B200GridNeRF, feats: torch.Tensor, view: torch.Tensor) -> torch.Tensor:
+    n = feats.shape[0]
+    rgb = torch.empty((n, 3), dtype=torch.float32, device=model.device)
+    if n == 0:
+        return rgb
+    keep, sc, nb = _scratch(model, n)
+    feats, view = feats.contiguous(), view.contiguous()
+    with torch.cuda.device(model.device):
+        check(lib.gnr_mlp_features(model._handle, _ptr(feats), _ptr(view), n, sc, nb, _ptr(rgb), _stream()), "gnr_mlp_features")
+        torch.cuda.current_stream().synchronize()  # `keep` must outlive the kernels
+    return rgb
+
+
+def density_points(model: B200GridNeRF, xyz: torch.Tensor) -> torch.Tensor:
+    n = xyz.shape[0]
+    sigma = torch.empty((n,), dtype=torch.float32, device=model.device)
+    if n:
+        xyz = xyz.contiguous()
+        with torch.cuda.device(model.device):
+            check(lib.gnr_density_points(model._handle, _ptr(xyz), n, None, _ptr(sigma), _stream()), "gnr_density_points")
+    return sigma
+
+
+def appearance_points(model: B200GridNeRF, xyz: torch.Tensor, view: torch.Tensor) -> torch.Tensor:
+    n = xyz.shape[0]
+    rgb = torch.empty((n, 3), dtype=torch.float32, device=model.device)
+    if n == 0:
+        return rgb
+    keep, sc, nb = _scratch(model, n)
+    xyz, view = xyz.contiguous(), view.contiguous()
+    with torch.cuda.device(model.device):
+        check(lib.gnr_appearance_points(model._handle, _ptr(xyz), _ptr(view), n, sc, nb, None, _ptr(rgb), _stream()),
+              "gnr_appearance_points")
+        torch.cuda.current_stream().synchronize()
+    return rgb
+
+
+# ----------------------------------------------------------------------------------------------
+# channel (tensor) parallel
+# ----------------------------------------------------------------------------------------------
+def slice_checkpoint_channels(ckpt: Dict, rank: int, world: int) -> Dict:
+    """The checkpoint of tensor-parallel rank ``rank``: density untouched, appearance planes and
+    lines chunked on the channel dimension (inferer_impl.py:259-261), ``basis_mat.weight`` viewed as
+    ``[app_dim, pairs, C]`` and sliced on ``C`` (cuda_render_extend.py:552-562)."""
+    sd = dict(ckpt["state_dict"])
+    n_pairs = sum(1 for k in sd if k.startswith("app_plane."))
+    c_full = sd["app_plane.0"].shape[1]
+    if c_full % world:
+        raise ValueError(f"{c_full} appearance channels do not split over {world} ranks")
+    c = c_full // world
+    for i in range(n_pairs):
+        sd[f"app_plane.{i}"] = sd[f"app_plane.{i}"][:, rank * c:(rank + 1) * c].contiguous()
+        sd[f"app_line.{i}"] = sd[f"app_line.{i}"][:, rank * c:(rank + 1) * c].contiguous()
+    w = sd["basis_mat.weight"]
+    sd["basis_mat.weight"] = w.view(w.shape[0], n_pairs, c_full)[:, :, rank * c:(rank + 1) * c].reshape(w.shape[0], -1).contiguous()
+    out = dict(ckpt)
+    out["state_dict"] = sd
+    kw = dict(ckpt["kwargs"])
+    kw["appearance_n_comp"] = [c] * len(kw["appearance_n_comp"])
+    out["kwargs"] = kw
+    return out
+
+
+class ChannelParallelRenderer:
+    """``models[i]`` is the channel-sliced model of ``comm.local_ranks[i]``."""
+
+    def __init__(self, models: Sequence[B200GridNeRF], comm):
+        assert len(models) == len(comm.local_ranks)
+        self.models, self.comm = list(models), comm
+
+    @torch.no_grad()
+    def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
+        """``rays[i]``: the same chunk on each local rank's device.  Returns per local rank
+        ``(rgb_map, depth_map)``; all ranks end up with the full result."""
+        W = self.comm.world
+        chunks = []
+        for m, r in zip(self.models, rays):
+            with torch.cuda.device(m.device):
+                ch = _Chunk(m, r, n_samples)
+                ch.sample()
+                ch.density()
+                ch.weights()
+                chunks.append(ch)
+        m_a = chunks[0].num_app
+        if any(ch.num_app != m_a for ch in chunks):
+            raise RuntimeError("tensor-parallel ranks disagree on the appearance list (sampling must be replicated)")
+        per = -(-max(m_a, 1) // W)
+        m_pad = per * W
+        partial, views = [], []
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                f = torch.zeros((m_pad, ch.m.app_dim), dtype=torch.float32, device=ch.m.device)
+                if m_a:
+                    f[:m_a] = ch.app_features()
+                partial.append(f)
+                v = torch.zeros((m_pad, 3), dtype=torch.float32, device=ch.m.device)
+                if m_a:
+                    v[:m_a] = ch.rays[ch.app_ray_index(), 3:6]
+                views.append(v)
+        feats = self.comm.reduce_scatter_rows(partial)  # complete features of this rank's sample slice
+        rgb_slices = []
+        for ch, f, v, rank in zip(chunks, feats, views, self.comm.local_ranks):
+            rgb_slices.append(mlp_features(ch.m, f, v[rank * per:(rank + 1) * per]))
+        rgb_all = self.comm.all_gather_rows(rgb_slices)
+        out = []
+        for ch, rgb in zip(chunks, rgb_all):
+            with torch.cuda.device(ch.m.device):
+                out.append(ch.composite(rgb[:m_a], white_bg))
+        return out
+
+
+# ----------------------------------------------------------------------------------------------
+# block (branch) parallel
+# ----------------------------------------------------------------------------------------------
+def assign_blocks(xyz: torch.Tensor, division: Tuple[int, int]):
+    """Block index and block-local coordinates of normalised samples; the arithmetic of
+    ``assign_blocks_to_samples`` (app/models/gridnerf_parallel.py:296-327) with torch ops in the
+    same order.  A sample exactly on the upper face of the box (x or y == 1) is given to the last
+    block instead of an out-of-range index."""
+    px, py = division
+    pw, ph = 2 / px, 2 / py
+    t = xyz[:, :2] + 1
+    u, v = t[:, 0] / pw, t[:, 1] / ph
+    bx = torch.floor(u).clamp_(0, px - 1)
+    by = torch.floor(v).clamp_(0, py - 1)
+    b = bx * py + by
+    coord_min = torch.stack([-1 + (b // py) * pw, -1 + (b % py) * ph], dim=-1)
+    coord_max = torch.stack([-1 + (b // py + 1) * pw, -1 + (b % py + 1) * ph], dim=-1)
+    local = xyz.clone()
+    local[:, :2] = (xyz[:, :2] - coord_min) * 2 / (coord_max - coord_min) - 1
+    return b.to(torch.int64), local
+
+
+def _route(owner: torch.Tensor, world: int):
+    order = torch.argsort(owner, stable=True)
+    counts = torch.bincount(owner, minlength=world).cpu().tolist()
+    return order, [int(c) for c in counts]
+
+
+class BlockParallelRenderer:
+    """``samplers[i]``: a model carrying the global box, step size and occupancy mask (its planes
+    are never read); ``owners[i]``: the field of the block that ``comm.local_ranks[i]`` owns.
+    Block ``b`` lives on rank ``b``; ``division[0] * division[1]`` must equal the world size."""
+
+    def __init__(self, samplers: Sequence[B200GridNeRF], owners: Sequence[B200GridNeRF], comm, division: Tuple[int, int]):
+        if division[0] * division[1] != comm.world:
+            raise ValueError(f"{division[0]}x{division[1]} blocks need {division[0] * division[1]} ranks, have {comm.world}")
+        self.samplers, self.owners, self.comm, self.division = list(samplers), list(owners), comm, division
+
+    @torch.no_grad()
+    def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
+        """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
+        Returns per local rank ``(rgb_map, depth_map)`` of its own rays."""
+        W = self.comm.world
+        chunks, locals_, rays_idx, orders, counts = [], [], [], [], []
+        # ---- sample globally, assign blocks, route positions to the owners ----------------------
+        for s, r in zip(self.samplers, rays):
+            with torch.cuda.device(s.device):
+                ch = _Chunk(s, r, n_samples)
+                ch.sample()
+                xyz, ray = ch.positions()
+                b, loc = assign_blocks(xyz, self.division)
+                order, cnt = _route(b, W)
+                chunks.append(ch)
+                locals_.append((b, loc))
+                rays_idx.append(ray)
+                orders.append(order)
+                counts.append(cnt)
+        send = [loc[o] for (b, loc), o in zip(locals_, orders)]
+        recv, rcounts = self.comm.all_to_all_rows(send, counts)
+        # ---- owners: density at the received points, values travel back -------------------------
+        sig = [density_points(o, x) for o, x in zip(self.owners, recv)]
+        back, _ = self.comm.all_to_all_rows(sig, rcounts)
+        app_send, app_counts, app_orders = [], [], []
+        for ch, (b, loc), order, ray, sg in zip(chunks, locals_, orders, rays_idx, back):
+            with torch.cuda.device(ch.m.device):
+                sigma = torch.empty_like(sg)
+                sigma[order] = sg
+                ch.weights(sigma)
+                ai = ch.app_index
+                ob = b[ai]
+                o2, c2 = _route(ob, W)
+                payload = torch.cat([loc[ai], ch.rays[ray[ai], 3:6]], dim=1)[o2]
+                app_send.append(payload)
+                app_counts.append(c2)
+                app_orders.append(o2)
+        # ---- owners: colour at the received (position, view) pairs, values travel back ----------
+        arecv, arcounts = self.comm.all_to_all_rows(app_send, app_counts)
+        rgb_o = [appearance_points(o, x[:, :3], x[:, 3:6]) for o, x in zip(self.owners, arecv)]
+        rgb_back, _ = self.comm.all_to_all_rows(rgb_o, arcounts)
+        out = []
+        for ch, o2, rb in zip(chunks, app_orders, rgb_back):
+            with torch.cuda.device(ch.m.device):
+                rgb_s = torch.empty_like(rb)
+                rgb_s[o2] = rb
+                out.append(ch.composite(rgb_s, white_bg))
+        return out

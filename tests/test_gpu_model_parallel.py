@@ -1,0 +1,132 @@
+"""GPU tests of the two model-parallel renderers.  All ranks of a group run inside this one
+process in lock step (LoopbackComm), with the real kernels, against the CPU oracles."""
+import numpy as np
+import pytest
+import torch
+
+from landmark_b200 import scenes
+from oracle import gridnerf_oracle as orc
+from oracle import model_parallel_oracle as mpo
+from tests._util import cuda_model, oracle_field, tiny_rays
+
+pytestmark = pytest.mark.gpu
+RGB_TOL, FLIP_RGB_TOL = 1e-4, 2.5e-3
+
+
+def _check(rgb, depth, ref, max_flips=3):
+    err = (rgb.cpu() - ref["rgb_map"]).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= max_flips, f"{int((err > RGB_TOL).sum())} rays above 1e-4 (max {err.max():.2e})"
+    assert err.max().item() <= FLIP_RGB_TOL
+    assert (depth.cpu() - ref["depth_map"]).abs().max().item() <= 2e-4
+
+
+@pytest.mark.parametrize("world,mlp_mode", [(2, 0), (3, 2), (1, 2)])
+def test_channel_parallel_matches_unsplit_oracle(world, mlp_mode):
+    from landmark_b200.model_parallel import ChannelParallelRenderer, LoopbackComm, slice_checkpoint_channels
+
+    spec = scenes.tiny_spec(grid=64).lit()
+    field, ckpt = oracle_field(spec)
+    rays = tiny_rays(spec)[3000:7000].contiguous()
+    ref = orc.render_chunk(field, rays, spec.n_samples, True)
+    models = []
+    for r in range(world):
+        sl = slice_checkpoint_channels(ckpt, r, world)
+        assert sl["state_dict"]["app_plane.0"].shape[1] == 48 // world
+        sspec = scenes.tiny_spec(grid=64).lit()
+        sspec.app_n_comp = (48 // world,) * 3
+        models.append(cuda_model(sspec, sl, mlp_mode=mlp_mode))
+    ren = ChannelParallelRenderer(models, LoopbackComm(world))
+    outs = ren.render_chunk([rays.cuda()] * world, spec.n_samples, True)
+    assert len(outs) == world
+    for rgb, depth in outs:
+        _check(rgb, depth, ref)
+    for rgb, depth in outs[1:]:
+        assert torch.equal(rgb, outs[0][0])  # every rank ends with the same image
+
+
+def _block_scene(division, grid=32, seed0=100):
+    """Global box split in x-y; every block has its own seeded field of ``grid``^3."""
+    px, py = division
+    gspec = scenes.tiny_spec(grid=grid).lit()
+    gspec.name = "blocks_global"
+    gspec.aabb = ((-1.0 * px, -1.0 * py, -1.0), (1.0 * px, 1.0 * py, 1.0))
+    gspec.grid = (grid * px, grid * py, grid)
+    gspec.mask_shape = (32, 32 * py, 32 * px)
+    gspec.near_far = (0.1, 12.0)
+    gspec.mask_boxes = 40 * px * py
+    blocks = []
+    for b in range(px * py):
+        bs = scenes.tiny_spec(grid=grid).lit()
+        blocks.append((bs, scenes.make_checkpoint(bs, seed=seed0 + b)))
+    gck = scenes.make_checkpoint(gspec)
+    return gspec, gck, blocks
+
+
+@pytest.mark.parametrize("division,mlp_mode", [((2, 1), 0), ((2, 2), 2)])
+def test_block_parallel_matches_oracle(division, mlp_mode):
+    from landmark_b200.gridnerf import B200GridNeRF
+    from landmark_b200.model_parallel import BlockParallelRenderer, LoopbackComm
+
+    world = division[0] * division[1]
+    gspec, gck, blocks = _block_scene(division)
+    gfield = orc.field_from_checkpoint(gck)
+    bfields = [orc.field_from_checkpoint(ck) for _, ck in blocks]
+    # camera above the middle of the scene looking down at an angle, so that rays cross block seams
+    pose = scenes.pitched_pose((0.1, -0.2, 2.5), yaw_deg=20.0, pitch_deg=-65.0)
+    rays = orc.generate_rays(torch.from_numpy(pose), 48, 64, 40.0)
+    ref = mpo.render_chunk_blocks(gfield, bfields, division, rays, 160, True)
+    assert len(torch.unique(ref["block"])) == world and int(ref["app_mask"].sum()) > 2000
+    # samplers: global box / step / mask, planes never read -> keep them 2x2
+    samplers, owners = [], []
+    for r in range(world):
+        kw = dict(gck["kwargs"])
+        kw.update({"device": "cuda:0", "args": scenes.model_args(gspec, "cuda:0"), "is_train": False})
+        s = B200GridNeRF(**kw, mlp_mode=0, field_grid=(2, 2, 2))
+        s.load({k: v for k, v in gck.items() if k != "state_dict"} | {"state_dict": {}})
+        samplers.append(s)
+        owners.append(cuda_model(blocks[r][0], blocks[r][1], mlp_mode=mlp_mode))
+    ren = BlockParallelRenderer(samplers, owners, LoopbackComm(world), division)
+    # data parallel over rays: rank r renders rows r, r + world, ...
+    parts = [torch.arange(r, rays.shape[0], world) for r in range(world)]
+    outs = ren.render_chunk([rays[p].cuda() for p in parts], 160, True)
+    rgb = torch.zeros((rays.shape[0], 3))
+    depth = torch.zeros(rays.shape[0])
+    for p, (c, d) in zip(parts, outs):
+        rgb[p], depth[p] = c.cpu(), d.cpu()
+    _check(rgb, depth, ref)
+
+
+def test_assign_blocks_matches_oracle_restatement():
+    from landmark_b200.model_parallel import assign_blocks
+
+    g = torch.Generator().manual_seed(3)
+    xyz = torch.rand((5000, 3), generator=g) * 2 - 1
+    xyz[0] = torch.tensor([1.0, 1.0, 0.0])   # upper faces
+    xyz[1] = torch.tensor([-1.0, -1.0, 0.0])
+    xyz[2] = torch.tensor([0.0, 0.0, 0.5])   # exactly on a seam
+    for division in ((4, 2), (2, 1), (3, 3)):
+        b0, l0 = mpo.assign_blocks(xyz, division)
+        b1, l1 = assign_blocks(xyz.cuda(), division)
+        assert torch.equal(b0, b1.cpu()) and torch.equal(l0, l1.cpu())
+        assert int(b0.max()) == division[0] * division[1] - 1 and int(b0.min()) == 0
+
+
+def test_point_mode_entries_match_list_mode():
+    """gnr_density_points / gnr_appearance_points on explicit coordinates give what the list-mode
+    stages give for the same samples."""
+    from landmark_b200.model_parallel import _Chunk, appearance_points, density_points
+
+    spec = scenes.tiny_spec(grid=64).lit()
+    for mode in (0, 2):
+        model = cuda_model(spec, mlp_mode=mode)
+        rays = tiny_rays(spec)[4000:6000].cuda()
+        got = model.run_stages(rays, spec.n_samples, True)
+        ch = _Chunk(model, rays, spec.n_samples)
+        ch.sample()
+        xyz, ray = ch.positions()
+        assert torch.equal(ray, got["ray_index"])
+        sig = density_points(model, xyz)
+        assert torch.equal(sig, got["sigma"])
+        ai = got["app_index"]
+        rgb = appearance_points(model, xyz[ai], rays[ray[ai], 3:6])
+        assert torch.equal(rgb, got["rgb_samples"])
