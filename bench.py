@@ -162,7 +162,11 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="city_lit", choices=["city_lit", "city"])
+    ap.add_argument("--workload", default="city_lit", choices=["city_lit", "city", "city_blocks", "city_channels"],
+                    help="city_lit (headline) | city (density_shift=-10) | city_blocks (block-partitioned field, "
+                         "all-to-all routing) | city_channels (channel-parallel appearance, reduce-scatter)")
+    ap.add_argument("--grid-scale", type=int, default=1, help="divide grid and mask resolution (model-parallel workloads)")
+    ap.add_argument("--check", action="store_true", help="city_blocks: compare rank 0 with a single-process render")
     ap.add_argument("--chunk", type=int, default=131072, help="rays per library call")
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
@@ -187,6 +191,27 @@ def main():
 
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(device))
+    if a.workload in ("city_blocks", "city_channels"):
+        from landmark_b200.model_parallel_run import run as run_model_parallel
+
+        sampler = ClockSampler(local_rank) if rank == 0 else None
+        res = run_model_parallel(a.workload, a.steps, max(a.warmup, 3), a.chunk, a.mlp_mode, rank, world, device,
+                                 a.grid_scale, a.check)
+        clocks = sampler.stop() if sampler else None
+        if rank == 0:
+            line = {"metric": "Mrays/s", "value": res["rays"] / (res["ms_per_frame"] * 1e-3) / 1e6, "unit": "Mrays/s",
+                    "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": res["ms_per_frame"],
+                    "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                    "dtype": "f32 + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
+                    "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "parallelism": res["parallelism"],
+                               "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "grid_scale": a.grid_scale,
+                               "l2": "inputs larger than L2"},
+                    "ms_per_frame": res["ms_per_frame"], "clocks": clocks,
+                    "samples_per_frame": {"valid": res["valid"], "appearance": res["appearance"]}, "detail": res}
+            print(json.dumps(line), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     from landmark_b200 import scenes
     from landmark_b200.gridnerf import B200GridNeRF
     from landmark_b200.parallel import TILE, TileSharding, tile_pixel_ids
