@@ -22,11 +22,23 @@ struct PlaneSet {
 
 __device__ __forceinline__ float pick(float x, float y, float z, int a) { return a == 0 ? x : (a == 1 ? y : z); }
 
-__device__ __forceinline__ float4 f4_scale(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
-__device__ __forceinline__ float4 f4_fma(float4 a, float s, float4 c) {
-  return make_float4(fmaf(a.x, s, c.x), fmaf(a.y, s, c.y), fmaf(a.z, s, c.z), fmaf(a.w, s, c.w));
+// float4 arithmetic as two packed fp32x2 instructions each (sm_100 has paired FP32 pipes)
+__device__ __forceinline__ float4 f4_scale(float4 a, float s) {
+  const float2 ss = make_float2(s, s);
+  const float2 lo = __fmul2_rn(make_float2(a.x, a.y), ss), hi = __fmul2_rn(make_float2(a.z, a.w), ss);
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
 }
-__device__ __forceinline__ float4 f4_mul(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 f4_fma(float4 a, float s, float4 c) {
+  const float2 ss = make_float2(s, s);
+  const float2 lo = __ffma2_rn(make_float2(a.x, a.y), ss, make_float2(c.x, c.y));
+  const float2 hi = __ffma2_rn(make_float2(a.z, a.w), ss, make_float2(c.z, c.w));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float4 f4_mul(float4 a, float4 b) {
+  const float2 lo = __fmul2_rn(make_float2(a.x, a.y), make_float2(b.x, b.y));
+  const float2 hi = __fmul2_rn(make_float2(a.z, a.w), make_float2(b.z, b.w));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
 
 // Products plane(x, y) * line(l) for the 4 J channels this lane owns.
 // Valid samples lie inside the closed box, so the continuous index is clamped to the grid
@@ -97,8 +109,12 @@ __device__ __forceinline__ long long coords_total(const GnrCoords& c) {
 
 __device__ __forceinline__ float density_activation(float f, float shift, int act) {
   if (act == 1) return fmaxf(f, 0.0f);
-  const float x = f + shift;  // F.softplus: beta 1, threshold 20
-  return x > 20.0f ? x : log1pf(expf(x));
+  // F.softplus (beta 1, threshold 20): log1p(exp(x)).  exp by the hardware approximation; log1p
+  // by its series while exp(x) is small (where 1 + e would round e away) and by log(1 + e) above.
+  const float x = f + shift;
+  if (x > 20.0f) return x;
+  const float e = __expf(x);
+  return e < 0.01f ? e * (1.0f - e * (0.5f - e * 0.33333334f)) : __logf(1.0f + e);
 }
 
 // Contiguous share of [0, total) for this CTA, in units of the kBlock / 4 samples one CTA

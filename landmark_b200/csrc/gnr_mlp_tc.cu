@@ -133,8 +133,8 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
         "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
         "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // sin and cos for operands that are about to be rounded to fp16: two-constant reduction by
 // 2 pi, then the hardware approximations (absolute error ~5e-7 on the reduced range).
@@ -302,6 +302,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       parity ^= 1;
       uint32_t v[32];
       tmem_ld32(f_tmem + lane_off, v);
+      tmem_ld_wait();
 #pragma unroll
       for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
       if (a.feat_out != nullptr && live) {
@@ -396,17 +397,19 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     }
     parity ^= 1;
 
-    // ---- phase 2: A2 = relu(D + b1) -> smem ----------------------------------------------------
+    // ---- phase 2: A2 = relu(D + b1) -> smem (two TMEM loads in flight per wait) ------------------
 #pragma unroll
-    for (int cb = 0; cb < HID / 32; ++cb) {
-      uint32_t v[32];
-      tmem_ld32(d_tmem + lane_off + cb * 32, v);
+    for (int cb = 0; cb < HID / 64; ++cb) {
+      uint32_t v[64];
+      tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+      tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      tmem_ld_wait();
 #pragma unroll
-      for (int g8 = 0; g8 < 4; ++g8) {
+      for (int g8 = 0; g8 < 8; ++g8) {
         float g[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] = fmaxf(__uint_as_float(v[g8 * 8 + e]) + s_b1[cb * 32 + g8 * 8 + e], 0.0f);
-        store_group<TA>(a_hi, a_lo, cb * 4 + g8, row, g);
+        for (int e = 0; e < 8; ++e) g[e] = fmaxf(__uint_as_float(v[g8 * 8 + e]) + s_b1[cb * 64 + g8 * 8 + e], 0.0f);
+        store_group<TA>(a_hi, a_lo, cb * 8 + g8, row, g);
       }
     }
     tc_fence_before();
@@ -435,28 +438,33 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       copy_pending = true;
     }
 
-    // ---- phase 3: rgb = sigmoid(W3 relu(D + b2) + b3), fp32 on the CUDA cores ------------------
-    float o0 = s_b3[0], o1 = s_b3[1], o2 = s_b3[2];
+    // ---- phase 3: rgb = sigmoid(W3 relu(D + b2) + b3), fp32 on the CUDA cores (packed fp32x2 FMAs)
+    float2 p0 = make_float2(0.0f, 0.0f), p1 = p0, p2 = p0;
 #pragma unroll
-    for (int cb = 0; cb < HID / 32; ++cb) {
-      uint32_t v[32];
-      tmem_ld32(d_tmem + lane_off + cb * 32, v);
+    for (int cb = 0; cb < HID / 64; ++cb) {
+      uint32_t v[64];
+      tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+      tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+      tmem_ld_wait();
 #pragma unroll
-      for (int e4 = 0; e4 < 8; ++e4) {
-        const int c = cb * 32 + e4 * 4;
+      for (int e4 = 0; e4 < 16; ++e4) {
+        const int c = cb * 64 + e4 * 4;
         const float4 bb = *reinterpret_cast<const float4*>(s_b2 + c);
         const float4 wr = *reinterpret_cast<const float4*>(s_w3 + c);
         const float4 wg = *reinterpret_cast<const float4*>(s_w3 + HID + c);
         const float4 wb = *reinterpret_cast<const float4*>(s_w3 + 2 * HID + c);
-        const float h0 = fmaxf(__uint_as_float(v[e4 * 4 + 0]) + bb.x, 0.0f);
-        const float h1 = fmaxf(__uint_as_float(v[e4 * 4 + 1]) + bb.y, 0.0f);
-        const float h2 = fmaxf(__uint_as_float(v[e4 * 4 + 2]) + bb.z, 0.0f);
-        const float h3 = fmaxf(__uint_as_float(v[e4 * 4 + 3]) + bb.w, 0.0f);
-        o0 = fmaf(h3, wr.w, fmaf(h2, wr.z, fmaf(h1, wr.y, fmaf(h0, wr.x, o0))));
-        o1 = fmaf(h3, wg.w, fmaf(h2, wg.z, fmaf(h1, wg.y, fmaf(h0, wg.x, o1))));
-        o2 = fmaf(h3, wb.w, fmaf(h2, wb.z, fmaf(h1, wb.y, fmaf(h0, wb.x, o2))));
+        float2 ha = __fadd2_rn(make_float2(__uint_as_float(v[e4 * 4 + 0]), __uint_as_float(v[e4 * 4 + 1])), make_float2(bb.x, bb.y));
+        float2 hb = __fadd2_rn(make_float2(__uint_as_float(v[e4 * 4 + 2]), __uint_as_float(v[e4 * 4 + 3])), make_float2(bb.z, bb.w));
+        ha.x = fmaxf(ha.x, 0.0f);
+        ha.y = fmaxf(ha.y, 0.0f);
+        hb.x = fmaxf(hb.x, 0.0f);
+        hb.y = fmaxf(hb.y, 0.0f);
+        p0 = __ffma2_rn(hb, make_float2(wr.z, wr.w), __ffma2_rn(ha, make_float2(wr.x, wr.y), p0));
+        p1 = __ffma2_rn(hb, make_float2(wg.z, wg.w), __ffma2_rn(ha, make_float2(wg.x, wg.y), p1));
+        p2 = __ffma2_rn(hb, make_float2(wb.z, wb.w), __ffma2_rn(ha, make_float2(wb.x, wb.y), p2));
       }
     }
+    const float o0 = s_b3[0] + (p0.x + p0.y), o1 = s_b3[1] + (p1.x + p1.y), o2 = s_b3[2] + (p2.x + p2.y);
     if (live) {
       float* out = a.rgb_out + (size_t)j * 3;
       out[0] = 1.0f / (1.0f + expf(-o0));
