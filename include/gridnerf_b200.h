@@ -51,7 +51,9 @@ typedef struct GnrConfig {
   int32_t has_bias;         /* bias_enable                                                */
   int32_t mlp_mode;         /* 0 = fp32 CUDA-core MLP, 1 = tcgen05 split-precision MLP (fp32-grade),
                                2 = tcgen05 single bf16 MLP (fast)                         */
-  int32_t reserved[8];
+  int32_t sampling_mode;    /* 0 = sample_ray (:244-281), 1 = sample_ray_within_hull (:283-319,
+                               args.sampling_opt); mode 1 needs gnr_upload_hull_tables             */
+  int32_t reserved[7];
 } GnrConfig;
 
 /* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */
@@ -92,6 +94,12 @@ int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, 
  * (row-major ``[out][in]``; bias pointers may be NULL).  app/models/mlp_render_fea.py:29-42. */
 int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const float* b1, const float* w2,
                    const float* b2, const float* w3, const float* b3, void* stream);
+
+/* Tables of the hull sampler for ``n_samples`` (= n_importance) samples per ray:
+ * ``u[k] = torch.linspace(0, 1, n_samples)[k]`` and ``near_term[k] = near * (1.0 - u[k])``, both
+ * evaluated by torch on the CPU so that ``z = near_term[k] + far * u[k]`` has the reference's bits
+ * (app/models/gridnerf_sequential.py:303-304).  Device pointers; copied. */
+int gnr_upload_hull_tables(GnrModel* m, int n_samples, const float* near_term, const float* u, void* stream);
 
 /* Ray generation from a pose.  Replaces generate_rays (dist_render/dataset/utils.py:92-113):
  * ``dir_x[W]`` and ``dir_y[H]`` are the two torch.arange tables of

@@ -39,7 +39,8 @@ class GnrConfig(C.Structure):
         ("hidden", C.c_int32),
         ("has_bias", C.c_int32),
         ("mlp_mode", C.c_int32),
-        ("reserved", C.c_int32 * 8),
+        ("sampling_mode", C.c_int32),
+        ("reserved", C.c_int32 * 7),
     ]
 
 
@@ -58,6 +59,7 @@ SIGNATURES = {
     "gnr_upload_line": (_INT, [_P, _INT, _INT, _P, _INT, _INT, _INT, _P]),
     "gnr_upload_alpha_mask": (_INT, [_P, _P, _INT, _INT, _INT, C.POINTER(C.c_float), C.POINTER(C.c_float), _P]),
     "gnr_upload_mlp": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
+    "gnr_upload_hull_tables": (_INT, [_P, _INT, _P, _P, _P]),
     "gnr_generate_rays": (_INT, [C.POINTER(C.c_float), _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),
     "gnr_rgba8": (_INT, [_P, _I64, _P, _P]),
     "gnr_workspace_bytes": (_INT, [_P, _I64, _INT, _I64, _I64, C.POINTER(_SZ)]),

@@ -169,6 +169,10 @@ extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
     gnr_set_error("gnr_create: channels per plane must be in [1, 64] (density %d, appearance %d)", cfg->n_density, cfg->n_app);
     return -1;
   }
+  if (cfg->sampling_mode != 0 && cfg->sampling_mode != 1) {
+    gnr_set_error("gnr_create: sampling_mode %d (0 = dense, 1 = hull)", cfg->sampling_mode);
+    return -1;
+  }
   if (cfg->fea_pe < 0 || cfg->fea_pe > 8 || cfg->view_pe < 0 || cfg->view_pe > 8) {
     gnr_set_error("gnr_create: fea_pe %d / view_pe %d outside [0, 8]", cfg->fea_pe, cfg->view_pe);
     return -1;
@@ -213,6 +217,8 @@ extern "C" int gnr_destroy(GnrModel* m) {
     free_dev(m->app_line_buf[i]);
   }
   free_dev(m->alpha_bits);
+  free_dev(m->hull_near_term);
+  free_dev(m->hull_u);
   free_dev(m->mlp.basis_blocked);
   free_dev(m->mlp.w1t);
   free_dev(m->mlp.w2t);
@@ -338,6 +344,24 @@ extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int
   return 0;
 }
 
+extern "C" int gnr_upload_hull_tables(GnrModel* m, int n_samples, const float* near_term, const float* u, void* stream) {
+  if (!m || n_samples < 1 || !near_term || !u) {
+    gnr_set_error("gnr_upload_hull_tables: bad argument");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  free_dev(m->hull_near_term);
+  free_dev(m->hull_u);
+  m->hull_near_term = m->hull_u = nullptr;
+  m->hull_samples = 0;
+  GNR_CUDA_OK(cudaMalloc(&m->hull_near_term, (size_t)n_samples * 4));
+  GNR_CUDA_OK(cudaMalloc(&m->hull_u, (size_t)n_samples * 4));
+  GNR_CUDA_OK(cudaMemcpyAsync(m->hull_near_term, near_term, (size_t)n_samples * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  GNR_CUDA_OK(cudaMemcpyAsync(m->hull_u, u, (size_t)n_samples * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+  m->hull_samples = n_samples;
+  return 0;
+}
+
 extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const float* b1, const float* w2,
                               const float* b2, const float* w3, const float* b3, void* stream) {
   if (!m || !basis_w || !w1 || !w2 || !w3) {
@@ -451,6 +475,9 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
   p.S = S;
   p.words = (S + 31) / 32;
   p.kbits = gnr_sample_bits(S);
+  p.mode = m->cfg.sampling_mode;
+  p.hull_a = m->hull_near_term;
+  p.hull_u = m->hull_u;
   return p;
 }
 
@@ -483,6 +510,10 @@ int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
   }
   if (!m->mlp.w1t) {
     gnr_set_error("MLP weights have not been uploaded");
+    return -1;
+  }
+  if (m->cfg.sampling_mode == 1 && (m->hull_samples != S || !m->hull_u)) {
+    gnr_set_error("hull sampler: tables for %d samples per ray have not been uploaded (have %d)", S, m->hull_samples);
     return -1;
   }
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);

@@ -40,9 +40,9 @@ weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float
       float alpha = 0.0f, f = 1.0f, t = 0.0f;
       if (active) {
         const int k = (int)(__ldg(ids + i) & kmask);
-        t = gnr_sample_t(t_min, p.step, k);
+        t = gnr_sample_t(p, t_min, k);
         // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
-        const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(t_min, p.step, k + 1), t);
+        const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
         const float x = __fmul_rn(-__ldg(sigma + i), __fmul_rn(dist, distance_scale));
         alpha = __fsub_rn(1.0f, expf(x));
         f = __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);

@@ -96,7 +96,7 @@ __device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCo
   const uint32_t ray = id >> p.kbits;
   const int k = (int)(id & ((1u << p.kbits) - 1u));
   const float* r = c.rays + (size_t)ray * 6;
-  const float t = gnr_sample_t(__ldg(c.t_min + ray), p.step, k);
+  const float t = gnr_sample_t(p, __ldg(c.t_min + ray), k);
   x = gnr_normalize(gnr_point(__ldg(r + 0), __ldg(r + 3), t), p.lo[0], p.inv[0]);
   y = gnr_normalize(gnr_point(__ldg(r + 1), __ldg(r + 4), t), p.lo[1], p.inv[1]);
   z = gnr_normalize(gnr_point(__ldg(r + 2), __ldg(r + 5), t), p.lo[2], p.inv[2]);

@@ -55,6 +55,10 @@ struct GnrModel {
   int aD, aH, aW;
   float a_lo[3], a_inv[3];
   GnrMlp mlp;
+  // hull sampler tables (sampling_mode 1)
+  float* hull_near_term;
+  float* hull_u;
+  int hull_samples;
   // staging for gnr_render_host
   void* host_ws;
   size_t host_ws_bytes;
@@ -78,6 +82,9 @@ struct GnrSampleParams {
   int has_mask;
   const uint32_t* a_bits;
   int S, words, kbits;
+  int mode;                 // 0 dense sampler, 1 hull sampler
+  const float* hull_a;      // near * (1 - u[k])
+  const float* hull_u;      // u[k]
 };
 
 // Workspace layout (byte offsets), identical for every stage call with the same arguments.
@@ -158,8 +165,12 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
 // ---- device helpers shared by the sampling-dependent kernels ---------------------------------
 // Every operation is individually rounded (no FMA contraction): these reproduce the values
 // torch computes with separate elementwise kernels.
-__device__ __forceinline__ float gnr_sample_t(float t_min, float step, int k) {
-  return __fadd_rn(t_min, __fmul_rn(step, (float)k));
+// Distance of sample k along a ray.  Dense sampler: t_min + stepSize * k with the ray's slab
+// entry t_min; hull sampler: near * (1 - u_k) + far * u_k with the ray's own far
+// (app/models/gridnerf_sequential.py:268-273 and :303-304).  `ray_param` is t_min resp. far.
+__device__ __forceinline__ float gnr_sample_t(const GnrSampleParams& p, float ray_param, int k) {
+  if (p.mode == 0) return __fadd_rn(ray_param, __fmul_rn(p.step, (float)k));
+  return __fadd_rn(__ldg(p.hull_a + k), __fmul_rn(ray_param, __ldg(p.hull_u + k)));
 }
 __device__ __forceinline__ float gnr_point(float o, float d, float t) { return __fadd_rn(o, __fmul_rn(d, t)); }
 __device__ __forceinline__ float gnr_normalize(float p, float lo, float inv) {

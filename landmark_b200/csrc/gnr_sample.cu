@@ -96,6 +96,12 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
     t_min = fmaxf(t_min, fminf(ra, rb));
   }
   t_min = fminf(fmaxf(t_min, p.near_t), p.far_t);
+  if (p.mode == 1) {
+    // hull sampler: the per-ray parameter is `far`, the hit with the ground plane z = aabb_min_z
+    // (far = -(o_z - z0) / d_z, replaced by near_far[1] for rays that do not point down)
+    const float far = -__fdiv_rn(__fsub_rn(o[2], p.lo[2]), d[2]);
+    t_min = (d[2] >= 0.0f) ? p.far_t : far;
+  }
   if (lane == 0) t_min_out[ray] = t_min;
 
   int count = 0;
@@ -110,7 +116,7 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
       uint32_t bits = 0;
       if (!done) {
         int k = (base + w) * 32 + lane;
-        float t = gnr_sample_t(t_min, p.step, k);
+        float t = gnr_sample_t(p, t_min, min(k, p.S - 1));
         float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
         bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
         bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
@@ -124,7 +130,9 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
         bool valid = inside;
         if (valid && p.has_mask) valid = occupancy_test(p, px, py, pz);
         bits = __ballot_sync(0xffffffffu, valid);
-        done = __any_sync(0xffffffffu, exited);
+        // (the hull sampler's distances are a sum of a falling and a rising term and need not be
+        // monotone to the last bit, so only the dense sampler stops at the first exit)
+        done = (p.mode == 0) && __any_sync(0xffffffffu, exited);
         count += __popc(bits);
       }
       if (lane == w) my_word = bits;

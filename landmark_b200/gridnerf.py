@@ -9,7 +9,8 @@ dist_render/ddp_infer/inferer_impl.py:95-120) work unchanged.  All device work o
 happens in the CUDA library; torch only owns the tensors.
 
 Rendering only: ``is_train=True``, the NeRF refinement branch (``run_nerf``), the appearance
-latent (``encode_app``) and the hull sampler (``sampling_opt``) raise ``NotImplementedError``.
+latent (``encode_app``) raise ``NotImplementedError``.  Both samplers are supported: the dense
+``sample_ray`` and, with ``args.sampling_opt``, ``sample_ray_within_hull`` with ``n_importance`` samples.
 """
 
 from __future__ import annotations
@@ -170,6 +171,7 @@ class B200GridNeRF(torch.nn.Module):
 
         self._handle = C.c_void_p(0)
         self._committed = False
+        self._hull_tables_for = -1
         self._ws: Dict[tuple, torch.Tensor] = {}
         # capacities of the two compacted sample lists, per ray of a chunk
         self.valid_capacity_per_ray: Optional[int] = None  # None = n_samples (can never overflow)
@@ -269,12 +271,14 @@ class B200GridNeRF(torch.nn.Module):
         cfg.hidden = int(self.featureC)
         cfg.has_bias = int(self.renderModule.mlp[0].bias is not None)
         cfg.mlp_mode = self.mlp_mode
+        cfg.sampling_mode = 1 if self.sampling_opt else 0
         return cfg
 
     def commit(self, release_torch_planes: bool = False):
         """(Re)create the library model from the current parameters: converts planes and
         lines to channel-last, bit-packs the occupancy volume, re-tiles the MLP weights."""
         self._release()
+        self._hull_tables_for = -1
         dev_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
         cfg = self._config()
         h = C.c_void_p(0)
@@ -352,6 +356,18 @@ class B200GridNeRF(torch.nn.Module):
         return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off, max_valid, max_app
 
     def _samples(self, N_samples: int) -> int:
+        if self.sampling_opt:
+            # the hull branch ignores N_samples and takes n_importance samples (:528-530)
+            s = int(self.n_importance)
+            if self._hull_tables_for != s:
+                t_vals = torch.linspace(0.0, 1.0, steps=s)  # CPU: the bits of the CPU reference
+                near_term = (float(self.near_far[0]) * (1.0 - t_vals)).to(self.device)
+                u = t_vals.to(self.device)
+                check(lib.gnr_upload_hull_tables(self._handle, s, _ptr(near_term), _ptr(u), _stream()),
+                      "gnr_upload_hull_tables")
+                torch.cuda.current_stream(self.device).synchronize()
+                self._hull_tables_for = s
+            return s
         return int(N_samples) if N_samples > 0 else self.nSamples
 
     def _prepare(self, rays_chunk):
@@ -381,8 +397,6 @@ class B200GridNeRF(torch.nn.Module):
     def forward(self, rays_chunk, app_code=None, white_bg=True, is_train=False, N_samples=-1, idxs_chunk=None):
         if is_train:
             raise NotImplementedError("is_train=True: training is not part of this package")
-        if self.sampling_opt:
-            raise NotImplementedError("sampling_opt=1 (sample_ray_within_hull) is not supported yet")
         rays = self._prepare(rays_chunk)
         n = rays.shape[0]
         s = self._samples(N_samples)

@@ -101,6 +101,21 @@ def sample_ray(f: Field, rays_o, rays_d, n_samples: int):
     return pts, interpx, ~outside, t_min
 
 
+def sample_ray_within_hull(f: Field, rays_o, rays_d, n_samples: int):
+    """Samples between ``near`` and the ray's hit with the ground plane ``z = aabb_min_z``.
+    app/models/gridnerf_sequential.py:298-319 (``is_train=False`` branch)."""
+    near = f.near
+    o_z = rays_o[:, -1:] - f.aabb[0, 2].item()
+    d_z = rays_d[:, -1:]
+    far = -(o_z / d_z)
+    far[rays_d[:, 2] >= 0] = f.far
+    t_vals = torch.linspace(0.0, 1.0, steps=n_samples)
+    z_vals = near * (1.0 - t_vals) + far * (t_vals)
+    pts = rays_o[..., None, :] + rays_d[..., None, :] * z_vals[..., :, None]
+    outside = ((f.aabb[0] > pts) | (pts > f.aabb[1])).any(dim=-1)
+    return pts, z_vals, ~outside, far[:, 0]
+
+
 def sample_alpha(f: Field, pts):
     """Trilinear occupancy lookup.  app/models/alpha_mask.py:35-59."""
     q = (pts - f.alpha_aabb[0]) * f.alpha_inv - 1
@@ -175,14 +190,18 @@ def raw2alpha(sigma, dist):
 
 @torch.no_grad()
 def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bool = True,
-                 keep_stages: bool = False):
-    """One chunk through the dense-sampling branch of ``GridBaseSequential.forward``
-    (app/models/gridnerf_sequential.py:448-504).  Returns ``rgb_map [N,3]``, ``depth_map [N]``
-    and, with ``keep_stages``, every intermediate the parity tests compare."""
+                 keep_stages: bool = False, sampling_opt: bool = False):
+    """One chunk through ``GridBaseSequential.forward``: the dense-sampling branch
+    (app/models/gridnerf_sequential.py:448-504) or, with ``sampling_opt``, the hull-sampling
+    branch (:522-576, ``n_samples`` playing the role of ``n_importance``).  Returns ``rgb_map [N,3]``,
+    ``depth_map [N]`` and, with ``keep_stages``, every intermediate the parity tests compare."""
     rays = rays.float()
     rays_o, viewdirs = rays[:, :3], rays[:, 3:6]
     n_samples = n_samples if n_samples > 0 else f.n_samples_default
-    pts, z_vals, ray_valid, t_min = sample_ray(f, rays_o, viewdirs, n_samples)
+    if sampling_opt:
+        pts, z_vals, ray_valid, t_min = sample_ray_within_hull(f, rays_o, viewdirs, n_samples)
+    else:
+        pts, z_vals, ray_valid, t_min = sample_ray(f, rays_o, viewdirs, n_samples)
     in_box = ray_valid.clone()
     dists = torch.cat((z_vals[:, 1:] - z_vals[:, :-1], torch.zeros_like(z_vals[:, :1])), dim=-1)
     view_exp = viewdirs.view(-1, 1, 3).expand(pts.shape)

@@ -53,8 +53,11 @@ def import_reference(path):
     return GridNeRF, raw2alpha, ray_utils
 
 
-def reference_model(GridNeRF, spec, ckpt):
+def reference_model(GridNeRF, spec, ckpt, sampling_opt=0, n_importance=None):
     args = scenes.model_args(spec)
+    args.sampling_opt = sampling_opt
+    if n_importance is not None:
+        args.n_importance = n_importance
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": "cpu", "args": args, "is_train": False})
     model = GridNeRF(**kwargs)
@@ -63,9 +66,13 @@ def reference_model(GridNeRF, spec, ckpt):
 
 
 def reference_stages(model, raw2alpha, rays, n_samples):
-    """Re-trace app/models/gridnerf_sequential.py:448-504 with the model's own methods."""
+    """Re-trace app/models/gridnerf_sequential.py:448-504 (or :522-576 when the model was built
+    with sampling_opt) with the model's own methods."""
     rays_o, viewdirs = rays[:, :3], rays[:, 3:6]
-    pts, _, z_vals, ray_valid = model.sample_ray(rays_o, viewdirs, is_train=False, N_samples=n_samples)
+    if model.sampling_opt:
+        pts, _, z_vals, ray_valid = model.sample_ray_within_hull(rays_o, viewdirs, is_train=False, N_samples=n_samples)
+    else:
+        pts, _, z_vals, ray_valid = model.sample_ray(rays_o, viewdirs, is_train=False, N_samples=n_samples)
     in_box = ray_valid.clone()
     dists = torch.cat((z_vals[:, 1:] - z_vals[:, :-1], torch.zeros_like(z_vals[:, :1])), dim=-1)
     alphas = model.alphaMask.sample_alpha(pts[ray_valid])
@@ -95,30 +102,31 @@ def check_equal(name, a, b):
     assert torch.equal(a, b), f"oracle != reference at stage {name}: max diff {(a.float() - b.float()).abs().max()}"
 
 
-def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples, note):
+def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples, note, sampling_opt=0):
     ckpt = scenes.make_checkpoint(spec)
     digest = scenes.state_dict_digest(ckpt["state_dict"])
     with torch.no_grad():
-        model = reference_model(GridNeRF, spec, ckpt)
+        model = reference_model(GridNeRF, spec, ckpt, sampling_opt, n_samples)
         ref = reference_stages(model, raw2alpha, rays, n_samples)
         ref_out, _ = model(rays, white_bg=True, is_train=False, N_samples=n_samples)
     field = orc.field_from_checkpoint(ckpt, spec.alpha_filter_thres)
     assert torch.equal(field.step_size, model.stepSize)
     assert field.n_samples_default == model.nSamples
-    mine = orc.render_chunk(field, rays, n_samples, True, keep_stages=True)
+    mine = orc.render_chunk(field, rays, n_samples, True, keep_stages=True, sampling_opt=bool(sampling_opt))
     for k in ("in_box", "ray_valid", "sigma_feature", "sigma", "weight", "app_mask", "app_features", "z_vals"):
         check_equal(k, mine[k], ref[k])
     if ref["rgb_samples"] is not None:
         check_equal("rgb_samples", mine["rgb"][mine["app_mask"]], ref["rgb_samples"])
     check_equal("rgb_map", mine["rgb_map"], ref_out["rgb_map"])
     check_equal("depth_map", mine["depth_map"], ref_out["depth_map"])
-    # torch-free sampler against the reference
-    vol = field.alpha_volume[0, 0].numpy()
-    v_np, t_np = snp.valid_mask(rays.numpy(), field.aabb.numpy(), field.near, field.far,
-                                field.step_size.item(), n_samples, vol, field.alpha_aabb.numpy(),
-                                spec.alpha_filter_thres)
-    assert np.array_equal(v_np, ref["ray_valid"].numpy()), "numpy sampler != reference ray_valid"
-    assert np.array_equal(t_np, mine["t_min"].numpy())
+    # torch-free sampler against the reference (dense sampler only)
+    if not sampling_opt:
+        vol = field.alpha_volume[0, 0].numpy()
+        v_np, t_np = snp.valid_mask(rays.numpy(), field.aabb.numpy(), field.near, field.far,
+                                    field.step_size.item(), n_samples, vol, field.alpha_aabb.numpy(),
+                                    spec.alpha_filter_thres)
+        assert np.array_equal(v_np, ref["ray_valid"].numpy()), "numpy sampler != reference ray_valid"
+        assert np.array_equal(t_np, mine["t_min"].numpy())
 
     valid = ref["ray_valid"].numpy()
     app = ref["app_mask"].numpy()
@@ -184,6 +192,11 @@ def main():
     thr.alpha_filter_thres = 0.5
     pin_and_dump(GridNeRF, raw2alpha, ray_utils, thr, rays[::7].contiguous(), "tiny_lit_thr05.npz",
                  thr.n_samples, "config[0] lit, alpha_mask_filter_thre=0.5, every 7th ray")
+
+    # the hull sampler of the online renderer (sampling_opt=1, n_importance samples per ray)
+    pin_and_dump(GridNeRF, raw2alpha, ray_utils, tiny.lit(), rays[::3].contiguous(), "tiny_lit_hull.npz", 128,
+                 "config[0] lit, sampling_opt=1 (sample_ray_within_hull), n_importance=128, every 3rd ray",
+                 sampling_opt=1)
 
     if not a.skip_city:
         city = scenes.city_spec().lit()

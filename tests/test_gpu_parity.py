@@ -337,3 +337,33 @@ def test_runner_pose_to_uint8_image(tiny):
                                                          spec.width, focal=None))
     eng2.start()
     assert np.array_equal(eng2.submit(pose5), img)
+
+
+def test_hull_sampler_matches_reference_fixture():
+    """sampling_opt=1: sample_ray_within_hull with n_importance samples (the sampler of the
+    reference's online-render configs), against the fixture the reference itself produced."""
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    spec = scenes.tiny_spec().lit()
+    fx = load_golden("tiny_lit_hull.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    args = scenes.model_args(spec, "cuda:0")
+    args.sampling_opt, args.n_importance = 1, int(fx["n_samples"])
+    kw = dict(ckpt["kwargs"])
+    kw.update({"device": "cuda:0", "args": args, "is_train": False})
+    for mode in (0, 2):
+        model = B200GridNeRF(**kw, mlp_mode=mode)
+        model.load(ckpt)
+        rays = torch.from_numpy(fx["rays"]).cuda()
+        got = model.run_stages(rays, -1, True)
+        bits = valid_bits_from_words(got["mask_words"], int(fx["n_samples"]))
+        assert np.array_equal(np.packbits(bits, axis=1), fx["valid_bits"])
+        assert np.array_equal(got["counts"].cpu().numpy(), fx["valid_counts"])
+        assert np.array_equal(got["t_min"].cpu().numpy(), fx["t_min"])  # the per-ray `far`
+        assert abs(got["num_app"] - int(fx["app_counts"].sum())) <= 2
+        err = (got["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+        assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+        assert (got["depth_map"].cpu() - torch.from_numpy(fx["depth_map"])).abs().max().item() <= 1e-4
+        # the drop-in forward ignores N_samples in this mode, as the reference does
+        out, _ = model(rays, N_samples=77)
+        assert torch.equal(out["rgb_map"], got["rgb_map"])

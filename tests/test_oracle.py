@@ -112,3 +112,16 @@ def test_city_slice_fixture_is_self_consistent():
     assert fx["rays"].shape == (192, 6)
     assert int(fx["valid_counts"].sum()) == 42671 and int(fx["app_counts"].sum()) == 11374
     assert fx["pick"].shape == (192,)
+
+
+def test_hull_sampler_fixture():
+    """sampling_opt=1 (sample_ray_within_hull): the oracle reproduces what the reference gave."""
+    spec = scenes.tiny_spec().lit()
+    field, _ = oracle_field(spec)
+    fx = load_golden("tiny_lit_hull.npz")
+    out = orc.render_chunk(field, torch.from_numpy(fx["rays"]), int(fx["n_samples"]), True, keep_stages=True,
+                           sampling_opt=True)
+    assert np.array_equal(np.packbits(out["ray_valid"].numpy(), axis=1), fx["valid_bits"])
+    assert np.array_equal(out["t_min"].numpy(), fx["t_min"])
+    assert np.array_equal(out["rgb_map"].numpy(), fx["rgb_map"])
+    assert np.array_equal(out["depth_map"].numpy(), fx["depth_map"])
