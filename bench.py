@@ -171,6 +171,10 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ert", type=float, default=5e-5,
+                    help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
+                         "-1 = separate density and weights kernels")
+    ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
     ap.add_argument("--profile-case", type=int, default=0, metavar="RAYS",
                     help="render one chunk of RAYS rays from the middle of the frame twice and exit "
@@ -204,7 +208,8 @@ def main():
                     "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                     "dtype": "f32 + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
                     "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "parallelism": res["parallelism"],
-                               "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "grid_scale": a.grid_scale,
+                               "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": "2 streams" if not a.no_overlap else "none",
+                   "ert_transmittance": a.ert, "grid_scale": a.grid_scale,
                                "l2": "inputs larger than L2"},
                     "ms_per_frame": res["ms_per_frame"], "clocks": clocks,
                     "samples_per_frame": {"valid": res["valid"], "appearance": res["appearance"]}, "detail": res}
@@ -220,7 +225,7 @@ def main():
     spec, ckpt, pose = build_scene(a.workload, device)
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
-    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode)
+    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert)
     model.load(ckpt)
     cpu_sd = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
@@ -251,8 +256,8 @@ def main():
     depth = torch.zeros((n_pad,), dtype=torch.float32, device=device)
     image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
 
-    def step():
-        model.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb[:n_local], depth_out=depth[:n_local])
+    def step(overlap=not a.no_overlap):
+        model.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb[:n_local], depth_out=depth[:n_local], overlap=overlap)
         shard.assemble(rgb, image)
 
     for _ in range(max(a.warmup, 3)):
@@ -262,8 +267,6 @@ def main():
     stats = model.last_status.copy()
 
     # ---- timed region: device-resident inputs -----------------------------------------------
-    model.profile_enable(True)
-    model.profile_collect()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if world > 1:
         dist.barrier()
@@ -278,12 +281,25 @@ def main():
         dist.barrier()
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
-    stage_ms, stage_launches = model.profile_collect()
-    model.profile_enable(False)
     t = torch.tensor([ms_total], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / a.steps
+    model.check_pending_status()
+    # ---- per-kernel times: the same K frames once more on ONE stream, CUDA events around every
+    # stage (chunks of a frame run back to back, so a span times its kernels alone) -------------
+    model.profile_enable(True)
+    model.profile_collect()
+    torch.cuda.synchronize()
+    e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2.record()
+    for _ in range(a.steps):
+        step(overlap=False)
+    e3.record()
+    torch.cuda.synchronize()
+    ms_step_single = e2.elapsed_time(e3) / a.steps
+    stage_ms, stage_launches = model.profile_collect()
+    model.profile_enable(False)
     model.check_pending_status()
 
     # ---- end to end: host rays in, host rgb/depth out, through the C ABI ---------------------
@@ -346,6 +362,7 @@ def main():
         roofline["peak_source"] = f"of {pk['source']}"
         roofline["traffic"] = traffic
         roofline["per"] = "frame (sum over the chunk launches of this kernel)"
+        roofline["timing"] = "CUDA events around the kernel on its stream, single-stream pass of the same K frames"
 
     line = {
         "metric": "Mrays/s", "value": H * W / (ms_step * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": world,
@@ -353,9 +370,11 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (gathers, compositing) + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
-                   "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode,
+                   "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": "2 streams" if not a.no_overlap else "none",
+                   "ert_transmittance": a.ert,
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
+        "ms_per_frame_single_stream": ms_step_single,
         "e2e": {"value": H * W / e2e_s / 1e6, "unit": "Mrays/s", "ms_per_frame": e2e_s * 1e3,
                 "h2d_bytes_per_step": int(n_local * 24), "d2h_bytes_per_step": int(n_local * 16),
                 "matches_device_path": same},

@@ -53,7 +53,12 @@ typedef struct GnrConfig {
                                2 = tcgen05 single bf16 MLP (fast)                         */
   int32_t sampling_mode;    /* 0 = sample_ray (:244-281), 1 = sample_ray_within_hull (:283-319,
                                args.sampling_opt); mode 1 needs gnr_upload_hull_tables             */
-  int32_t reserved[7];
+  float ert_transmittance;  /* early ray termination of the fused density + weights pass: a ray stops
+                               taking density samples once its transmittance falls below this value
+                               (its rgb then differs from the unterminated result by less than the
+                               value).  0 = never terminate (exact); negative = use the separate
+                               density and weights kernels instead of the fused pass.             */
+  int32_t reserved[6];
 } GnrConfig;
 
 /* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */

@@ -40,7 +40,8 @@ class GnrConfig(C.Structure):
         ("has_bias", C.c_int32),
         ("mlp_mode", C.c_int32),
         ("sampling_mode", C.c_int32),
-        ("reserved", C.c_int32 * 7),
+        ("ert_transmittance", C.c_float),
+        ("reserved", C.c_int32 * 6),
     ]
 
 

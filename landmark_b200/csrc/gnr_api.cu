@@ -715,13 +715,19 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
     StageScope sc(m, GNR_STAGE_COMPACT, 4, st);
     GNR_LAUNCH_OK(launch_sample_compact(m, p, n, ws, L, max_valid, st));
   }
-  {
+  if (m->cfg.ert_transmittance >= 0.0f) {
+    // fused density + weights pass (with early ray termination when the threshold is > 0)
     StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
-    GNR_LAUNCH_OK(launch_density(m, p, gnr_coords_valid(rays, ws, L), (float*)(ws + L.sigma_feat), (float*)(ws + L.sigma), st));
-  }
-  {
-    StageScope sc(m, GNR_STAGE_WEIGHTS, 1, st);
-    GNR_LAUNCH_OK(launch_weights_only(m, p, n, ws, L, max_valid, st));
+    GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st));
+  } else {
+    {
+      StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
+      GNR_LAUNCH_OK(launch_density(m, p, gnr_coords_valid(rays, ws, L), (float*)(ws + L.sigma_feat), (float*)(ws + L.sigma), st));
+    }
+    {
+      StageScope sc(m, GNR_STAGE_WEIGHTS, 1, st);
+      GNR_LAUNCH_OK(launch_weights_only(m, p, n, ws, L, max_valid, st));
+    }
   }
   {
     StageScope sc(m, GNR_STAGE_COMPACT_APP, 4, st);

@@ -165,6 +165,118 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
   }
 }
 
+// Fused density + weights pass ("march"): one warp walks one ray's segment of the compacted
+// list, 32 samples per step.  Each step gathers the density of its 32 samples (4 sub-steps of 8
+// samples, 4 lanes per sample as in density_kernel), hands every sample's sigma to the lane of
+// the same index, and continues raw2alpha's transmittance product with the same 32-sample
+// multiply-scan and carry as weights_kernel (so with t_stop == 0 the weights are bit-identical to
+// the two-kernel path).  When the carry falls below t_stop the ray stops: the remaining samples
+// get weight 0 and never touch the planes.  What they would have added to acc (and, with a white
+// background, taken from rgb) is bounded by the transmittance at the stop, i.e. by t_stop.
+template <int J, int NP>
+__global__ void __launch_bounds__(kBlock)
+march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
+             const uint32_t* __restrict__ ids, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
+             float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
+             float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts) {
+  const int lane = threadIdx.x & 31, c4 = lane & 3, quad = lane >> 2;
+  const long long ray = (long long)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
+  if (ray >= n_rays) return;
+  const long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+  float acc = 0.0f, dep = 0.0f;
+  int n_app = 0;
+  if (beg < end) {
+    GnrCoords crd;
+    crd.rays = rays;
+    crd.t_min = t_min_arr;
+    crd.ids = ids;
+    crd.index = nullptr;
+    crd.xyz_direct = nullptr;
+    const float t_min = t_min_arr[ray];
+    const uint32_t kmask = (1u << p.kbits) - 1u;
+    float carry = 1.0f;
+    for (long long base = beg; base < end; base += 32) {
+      float my_sigma = 0.0f;
+      uint32_t my_id = 0;
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub) {
+        const long long i = base + sub * 8 + quad;
+        const bool active = i < end;
+        float f = 0.0f;
+        uint32_t id = 0;
+        if (active) {
+          id = __ldg(ids + i);
+          float x, y, z;
+          sample_xyz(p, crd, i, x, y, z);
+          const int n_planes = NP > 0 ? NP : planes.n;
+#pragma unroll
+          for (int pi = 0; pi < n_planes; ++pi) {
+            float4 prod[J];
+            pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+            float s = 0.0f;
+#pragma unroll
+            for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
+            f += s;
+          }
+        }
+        f += __shfl_xor_sync(0xffffffffu, f, 1);
+        f += __shfl_xor_sync(0xffffffffu, f, 2);
+        const float sg = active ? density_activation(f, shift, act) : 0.0f;
+        // sample base + L is handled in sub-step L >> 3 by quad L & 7
+        const float v = __shfl_sync(0xffffffffu, sg, (lane & 7) * 4);
+        const uint32_t vid = __shfl_sync(0xffffffffu, id, (lane & 7) * 4);
+        if ((lane >> 3) == sub) {
+          my_sigma = v;
+          my_id = vid;
+        }
+      }
+      // ---- raw2alpha for these 32 samples (lane = sample), as in weights_kernel -----------------
+      const long long i = base + lane;
+      const bool active = i < end;
+      float alpha = 0.0f, fct = 1.0f, t = 0.0f;
+      if (active) {
+        const int k = (int)(my_id & kmask);
+        t = gnr_sample_t(p, t_min, k);
+        const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
+        const float xx = __fmul_rn(-my_sigma, __fmul_rn(dist, distance_scale));
+        alpha = __fsub_rn(1.0f, expf(xx));
+        fct = __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
+      }
+      float incl = fct;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const float up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl *= up;
+      }
+      float excl = __shfl_up_sync(0xffffffffu, incl, 1);
+      if (lane == 0) excl = 1.0f;
+      const float T = carry * excl;
+      const float w = alpha * T;
+      if (active) {
+        weight[i] = w;
+        acc += w;
+        dep = fmaf(w, t, dep);
+      }
+      n_app += __popc(__ballot_sync(0xffffffffu, active && (w > thres)));
+      carry *= __shfl_sync(0xffffffffu, incl, 31);
+      if (carry < t_stop) {
+        for (long long r = base + 32 + lane; r < end; r += 32) weight[r] = 0.0f;
+        break;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      dep += __shfl_xor_sync(0xffffffffu, dep, o);
+    }
+  }
+  if (lane == 0) {
+    acc_out[ray] = acc;
+    depth_out[ray] = dep;
+    app_counts[ray] = n_app;
+  }
+}
+
 // Appearance gather + basis projection.  The basis weights sit in shared memory, blocked per
 // (pair, lane-in-quad): row t = 4 j + e of block (pair, c4) holds the `app_dim` weights of
 // channel 16 j + 4 c4 + e of that pair, padded to kFeat floats; blocks are padded by 8 floats
@@ -392,5 +504,30 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
                      cudaStream_t st) {
   positions_kernel<<<m->sm_count * 8, 256, 0, st>>>(p, c, xyz, ray_index);
+  return (int)cudaGetLastError();
+}
+
+int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
+                 cudaStream_t st) {
+  PlaneSet set = make_set(m->den, m->cfg.n_pairs);
+  const int J = m->den[0].C / 16;
+  const unsigned grid = (unsigned)((n + kBlock / 32 - 1) / (kBlock / 32));
+  const float t_stop = m->cfg.ert_transmittance > 0.0f ? m->cfg.ert_transmittance : 0.0f;
+#define GNR_MARCH(JJ, NPP)                                                                                        \
+  march_kernel<JJ, NPP><<<grid, kBlock, 0, st>>>(                                                                 \
+      p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids), (const int32_t*)(ws + L.offsets), \
+      (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
+      m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
+      (int32_t*)(ws + L.app_counts))
+  if (J == 1 && set.n == 3) GNR_MARCH(1, 3);
+  else if (J == 1) GNR_MARCH(1, 0);
+  else if (J == 2) GNR_MARCH(2, 0);
+  else if (J == 3) GNR_MARCH(3, 0);
+  else if (J == 4) GNR_MARCH(4, 0);
+  else {
+    gnr_set_error("density channels (padded) %d not supported (16..64)", m->den[0].C);
+    return -1;
+  }
+#undef GNR_MARCH
   return (int)cudaGetLastError();
 }

@@ -132,6 +132,9 @@ int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, 
                         int64_t max_valid, cudaStream_t st);
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                        int64_t max_valid, int64_t max_app, cudaStream_t st);
+// Fused density gather + transmittance scan + early termination, one warp per ray.
+int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
+                 cudaStream_t st);
 int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, float* feat,
                       cudaStream_t st);
 int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* prod_hi,

@@ -101,6 +101,7 @@ class B200GridNeRF(torch.nn.Module):
         is_train=False,
         mlp_mode: int = 0,
         field_grid=None,
+        ert_transmittance: float = 0.0,
         **_ignored,
     ):
         super().__init__()
@@ -146,6 +147,8 @@ class B200GridNeRF(torch.nn.Module):
         self.n_importance = getattr(args, "n_importance", 128)
         self.alpha_mask_filter_thre = getattr(args, "alpha_mask_filter_thre", 0.0) or 0.0
         self.mlp_mode = int(mlp_mode)
+        # early ray termination of the density pass (see GnrConfig.ert_transmittance); 0 = exact
+        self.ert_transmittance = float(ert_transmittance)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -272,6 +275,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.has_bias = int(self.renderModule.mlp[0].bias is not None)
         cfg.mlp_mode = self.mlp_mode
         cfg.sampling_mode = 1 if self.sampling_opt else 0
+        cfg.ert_transmittance = self.ert_transmittance
         return cfg
 
     def commit(self, release_torch_planes: bool = False):
@@ -340,9 +344,9 @@ class B200GridNeRF(torch.nn.Module):
         per_app = min(n_samples, self.app_capacity_per_ray)
         return max(1, n_rays * per_valid), max(1, n_rays * per_app)
 
-    def workspace(self, n_rays: int, n_samples: int):
+    def workspace(self, n_rays: int, n_samples: int, slot: int = 0):
         max_valid, max_app = self.capacities(n_rays, n_samples)
-        key = (n_rays, n_samples, max_valid, max_app)
+        key = (n_rays, n_samples, max_valid, max_app, slot)
         buf = self._ws.get(key)
         if buf is None:
             nbytes = C.c_size_t(0)
@@ -489,9 +493,12 @@ class B200GridNeRF(torch.nn.Module):
 
     @torch.no_grad()
     def render_rays(self, rays: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,
-                    rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None):
+                    rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None,
+                    overlap: bool = False):
         """Device-resident chunk loop: ``rays [N, 6]`` on the GPU -> ``rgb [N, 3]``, ``depth [N]``
-        written in place, one status check at the end instead of one per chunk."""
+        written in place, one status check at the end instead of one per chunk.  With
+        ``overlap`` consecutive chunks alternate between two side streams (each with its own
+        workspace), so that one chunk's latency-bound kernels run beside the other's."""
         rays = self._prepare(rays)
         n, s = rays.shape[0], self._samples(N_samples)
         if rgb_out is None:
@@ -499,17 +506,31 @@ class B200GridNeRF(torch.nn.Module):
         if depth_out is None:
             depth_out = torch.empty((n,), dtype=torch.float32, device=self.device)
         chunk = max(1, min(chunk, n))
-        status = torch.zeros((max(1, (n + chunk - 1) // chunk), _lib.ST_WORDS), dtype=torch.int32, device=self.device)
+        n_chunks = max(1, (n + chunk - 1) // chunk)
+        status = torch.zeros((n_chunks, _lib.ST_WORDS), dtype=torch.int32, device=self.device)
+        use_side = overlap and n_chunks > 1
         with torch.cuda.device(self.device):
-            st = _stream()
+            main = torch.cuda.current_stream()
+            if use_side:
+                if getattr(self, "_side_streams", None) is None:
+                    self._side_streams = [torch.cuda.Stream(device=self.device) for _ in range(2)]
+                for st_ in self._side_streams:
+                    st_.wait_stream(main)
             for ci, first in enumerate(range(0, n, chunk)):
                 m = min(chunk, n - first)
-                keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(chunk, s)
-                check(lib.gnr_render_chunk(self._handle, C.c_void_p(rays.data_ptr() + first * 24), m, s,
-                                           int(bool(white_bg)), ws_ptr, ws_bytes, max_valid, max_app,
-                                           C.c_void_p(rgb_out.data_ptr() + first * 12),
-                                           C.c_void_p(depth_out.data_ptr() + first * 4), st), "gnr_render_chunk")
-                status[ci].copy_(keep[(-keep.data_ptr()) % 256:][: 4 * _lib.ST_WORDS].view(torch.int32))
+                slot = ci & 1 if use_side else 0
+                keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(chunk, s, slot)
+                stream = self._side_streams[slot] if use_side else main
+                with torch.cuda.stream(stream):
+                    check(lib.gnr_render_chunk(self._handle, C.c_void_p(rays.data_ptr() + first * 24), m, s,
+                                               int(bool(white_bg)), ws_ptr, ws_bytes, max_valid, max_app,
+                                               C.c_void_p(rgb_out.data_ptr() + first * 12),
+                                               C.c_void_p(depth_out.data_ptr() + first * 4),
+                                               C.c_void_p(stream.cuda_stream)), "gnr_render_chunk")
+                    status[ci].copy_(keep[(-keep.data_ptr()) % 256:][: 4 * _lib.ST_WORDS].view(torch.int32))
+            if use_side:
+                for st_ in self._side_streams:
+                    main.wait_stream(st_)
         self._pending_status = status
         return rgb_out, depth_out
 

@@ -367,3 +367,32 @@ def test_hull_sampler_matches_reference_fixture():
         # the drop-in forward ignores N_samples in this mode, as the reference does
         out, _ = model(rays, N_samples=77)
         assert torch.equal(out["rgb_map"], got["rgb_map"])
+
+
+def test_early_ray_termination_stays_inside_the_bar(tiny):
+    """Fused density + weights pass.  Threshold 0: bit-identical to the separate kernels (that is
+    what test_forward_equals_stagewise checks, the stage-wise path uses the separate kernels).
+    Threshold 5e-5: rays stop sampling density once T < 5e-5; every pixel stays within 5e-5 (+ the
+    usual rounding) of the unterminated render and within the 1e-4 bar of the reference."""
+    spec, field, model, rays, ref, got = tiny
+    ckpt = scenes.make_checkpoint(spec)
+    kw = dict(ckpt["kwargs"])
+    kw.update({"device": "cuda:0", "args": scenes.model_args(spec, "cuda:0"), "is_train": False})
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    outs = {}
+    for ert in (-1.0, 0.0, 5e-5, 1e-3):
+        m = B200GridNeRF(**kw, mlp_mode=0, ert_transmittance=ert)
+        m.load(ckpt)
+        outs[ert], _ = m(rays.cuda(), N_samples=spec.n_samples)
+        if ert == 5e-5:
+            n_app_ert = int(m.last_status[3])
+    assert torch.equal(outs[0.0]["rgb_map"], outs[-1.0]["rgb_map"]) and torch.equal(outs[0.0]["depth_map"], outs[-1.0]["depth_map"])
+    d = (outs[5e-5]["rgb_map"] - outs[0.0]["rgb_map"]).abs().max().item()
+    assert d <= 5.1e-5, f"termination at 5e-5 moved a pixel by {d:.2e}"
+    assert n_app_ert == got["num_app"]  # appearance samples all lie before the stop
+    fx = load_golden("tiny_lit.npz")
+    err = (outs[5e-5]["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+    d3 = (outs[1e-3]["rgb_map"] - outs[0.0]["rgb_map"]).abs().max().item()
+    assert 5e-5 < d3 <= 1.01e-3  # a coarser stop is visible but bounded by its threshold
