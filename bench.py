@@ -321,7 +321,7 @@ def main():
     e2e_s = float(t.item())
     same = bool(torch.equal(rgb_h, rgb[:n_local].cpu()))
 
-    tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local)], device=device, dtype=torch.float64)
+    tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local), float(stats[5])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
     if rank != 0:
@@ -331,12 +331,15 @@ def main():
 
     pk = peaks()
     n_valid, n_app = float(stats[2]), float(stats[3])  # this rank's samples per frame
+    n_density = float(stats[5]) if stats[5] > 0 else n_valid  # samples whose density was actually gathered
     per_launch = {k: (stage_ms[k] / a.steps) for k in stage_ms}  # ms per frame per stage (all chunks)
     roof = {}
     if per_launch["density"] > 0:
-        ach = n_valid * DENSITY_BYTES_PER_SAMPLE / (per_launch["density"] * 1e-3) / 1e9
+        ach = n_density * DENSITY_BYTES_PER_SAMPLE / (per_launch["density"] * 1e-3) / 1e9
         roof["density_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                  "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"]}
+                                  "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"],
+                                  "samples_gathered": n_density,
+                                  "note": "fused density gather + transmittance scan (march_kernel)" if a.ert >= 0 else "density_kernel"}
     if per_launch["app_gather"] > 0 and n_app > 0:
         ach = n_app * APP_BYTES_PER_SAMPLE / (per_launch["app_gather"] * 1e-3) / 1e9
         roof["app_gather_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
@@ -353,7 +356,7 @@ def main():
         with open(tpath) as fh:
             tj = json.load(fh)
         if dominant in tj:
-            units = n_valid if dominant == "density_kernel" else n_app
+            units = n_density if dominant == "density_kernel" else n_app
             traffic = tj[dominant]["dram_bytes_per_sample"] * units
     roofline = None
     if dominant:
@@ -384,7 +387,7 @@ def main():
         "roofline_all": roof,
         "stage_ms_per_frame": per_launch,
         "samples_per_frame": {"valid": float(tot[0].item()), "appearance": float(tot[1].item()),
-                              "rays": float(tot[2].item())},
+                              "rays": float(tot[2].item()), "density_evaluated": float(tot[3].item())},
     }
     if cpu_sd is not None:
         from oracle import gridnerf_oracle as orc

@@ -68,6 +68,8 @@ enum {
   GNR_ST_NUM_VALID = 2,      /* #samples passing the box + occupancy test                 */
   GNR_ST_NUM_APP = 3,        /* #samples with weight > ray_weight_thres                   */
   GNR_ST_WAIT_EXPIRED = 4,   /* a bounded device-side wait gave up (tensor-core MLP)      */
+  GNR_ST_NUM_DENSITY = 5,    /* #samples whose density was evaluated (fused pass; < NUM_VALID
+                                when early ray termination is on)                          */
   GNR_ST_WORDS = 8
 };
 

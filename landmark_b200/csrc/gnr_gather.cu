@@ -178,13 +178,18 @@ __global__ void __launch_bounds__(kBlock)
 march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
              const uint32_t* __restrict__ ids, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
-             float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts) {
+             float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts,
+             int32_t* __restrict__ evaluated_total) {
+  __shared__ int s_evaluated;
+  if (threadIdx.x == 0) s_evaluated = 0;
+  __syncthreads();
   const int lane = threadIdx.x & 31, c4 = lane & 3, quad = lane >> 2;
   const long long ray = (long long)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
-  if (ray >= n_rays) return;
-  const long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+  const bool has_ray = ray < n_rays;
+  const long long beg = has_ray ? offsets[ray] : 0, end = has_ray ? min((long long)offsets[ray + 1], capacity) : 0;
   float acc = 0.0f, dep = 0.0f;
   int n_app = 0;
+  long long evaluated = 0;
   if (beg < end) {
     GnrCoords crd;
     crd.rays = rays;
@@ -259,6 +264,7 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
       }
       n_app += __popc(__ballot_sync(0xffffffffu, active && (w > thres)));
       carry *= __shfl_sync(0xffffffffu, incl, 31);
+      evaluated = min(base + 32, end) - beg;
       if (carry < t_stop) {
         for (long long r = base + 32 + lane; r < end; r += 32) weight[r] = 0.0f;
         break;
@@ -270,11 +276,14 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
       dep += __shfl_xor_sync(0xffffffffu, dep, o);
     }
   }
-  if (lane == 0) {
+  if (lane == 0 && has_ray) {
     acc_out[ray] = acc;
     depth_out[ray] = dep;
     app_counts[ray] = n_app;
+    if (evaluated) atomicAdd(&s_evaluated, (int)evaluated);
   }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_evaluated) atomicAdd(evaluated_total, s_evaluated);
 }
 
 // Appearance gather + basis projection.  The basis weights sit in shared memory, blocked per
@@ -518,7 +527,7 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
       p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
-      (int32_t*)(ws + L.app_counts))
+      (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)
   if (J == 1 && set.n == 3) GNR_MARCH(1, 3);
   else if (J == 1) GNR_MARCH(1, 0);
   else if (J == 2) GNR_MARCH(2, 0);

@@ -542,7 +542,7 @@ class B200GridNeRF(torch.nn.Module):
         h = st.cpu().numpy().astype(np.int64)
         agg = np.zeros(_lib.ST_WORDS, dtype=np.int64)
         agg[[0, 1, 4]] = h[:, [0, 1, 4]].max(0)
-        agg[[2, 3]] = h[:, [2, 3]].sum(0)
+        agg[[2, 3, 5]] = h[:, [2, 3, 5]].sum(0)
         self.last_status = agg
         self._pending_status = None
         self.raise_on_status(agg)
