@@ -1094,6 +1094,8 @@ extern "C" int gnr_render_host(GnrModel* m, const float* rays_h, int64_t n_rays,
       // totals saturate instead of wrapping
       long long v = (long long)status_h[GNR_ST_NUM_VALID] + s[GNR_ST_NUM_VALID];
       long long a = (long long)status_h[GNR_ST_NUM_APP] + s[GNR_ST_NUM_APP];
+      long long dn = (long long)status_h[GNR_ST_NUM_DENSITY] + s[GNR_ST_NUM_DENSITY];
+      status_h[GNR_ST_NUM_DENSITY] = dn > 0x7fffffffLL ? 0x7fffffff : (int32_t)dn;
       status_h[GNR_ST_NUM_VALID] = v > 0x7fffffffLL ? 0x7fffffff : (int32_t)v;
       status_h[GNR_ST_NUM_APP] = a > 0x7fffffffLL ? 0x7fffffff : (int32_t)a;
     }
