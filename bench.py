@@ -244,7 +244,8 @@ def main():
             model.render_rays(rays, S, True, chunk=a.profile_case)
             st = model.check_pending_status()
         torch.cuda.synchronize()
-        print(json.dumps({"profile_case_rays": int(rays.shape[0]), "valid": int(st[2]), "appearance": int(st[3])}))
+        print(json.dumps({"profile_case_rays": int(rays.shape[0]), "valid": int(st[2]), "appearance": int(st[3]),
+                          "density_evaluated": int(st[5])}))
         return
     if world == 1 and a.order == "rows":
         shard = TileSharding(H, W, 0, 1, device, tile=max(H, W))  # one tile = the whole image, row-major
