@@ -164,7 +164,7 @@ def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a LandMark checkout")
     ap.add_argument("--skip-city", action="store_true")
     a = ap.parse_args()
     GridNeRF, raw2alpha, ray_utils = import_reference(a.reference)
