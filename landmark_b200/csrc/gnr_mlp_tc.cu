@@ -19,6 +19,10 @@
 //              D  = A2 * W2^T           (8 K-steps)
 //              rgb = sigmoid(W3 relu(D + b2) + b3)                    TMEM -> registers, fp32
 //
+// Biases ride in the MMAs: every layer input carries a constant 1 in its first padding column
+// (column 150 of layer 1, column 128 of layer 2) and the weight image holds the bias there, so
+// the epilogues only apply ReLU, which the fp16 conversion does itself (cvt.rn.relu.f16x2.f32).
+//
 // Operand layout (A and B alike): element (row r, k) at byte (k / 8) * LBO + r * 16 + (k % 8) * 2:
 // 8 rows x 16 B form one contiguous 128 B core matrix, row groups are 128 B apart (stride byte
 // offset), the two K halves of one MMA are LBO = rows * 16 bytes apart (leading byte offset).
@@ -37,7 +41,9 @@ namespace {
 constexpr int HID = 128;
 constexpr int APP = 27, FPE = 2, VPE = 2;
 constexpr int IN_DIM = APP + 3 + 2 * FPE * APP + 2 * VPE * 3;  // 150
-constexpr int K1 = 160, K2 = 128;                              // padded to the MMA K (16)
+constexpr int K1 = 160, K2 = 144;                              // layer inputs + one constant-1 column for the
+                                                               // bias, padded to the MMA K (16)
+constexpr int BIAS_COL1 = IN_DIM, BIAS_COL2 = HID;             // where that column sits
 constexpr int KG1 = K1 / 8, KG2 = K2 / 8;                      // 16-byte K groups
 constexpr int ROWS = 128;
 constexpr int KG_BYTES = ROWS * 16;                            // 2048: one K group of all rows
@@ -149,6 +155,13 @@ __device__ __forceinline__ void sincos_reduced(float x, float& s, float& c) {
 __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// max(x, 0) and the conversion to two fp16 in one instruction; `a` lands in the low half
+__device__ __forceinline__ uint32_t pack_h2_relu(float a, float b) {
+  uint32_t d;
+  asm("cvt.rn.relu.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(b), "f"(a));
+  return d;
 }
 
 // Store 8 consecutive-k values of one row as fp16 (and, with TA == 2, their rounding residuals).
@@ -366,8 +379,9 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
         x[APP + 3 + 4 * APP + 6 + 2 * i] = c;
         x[APP + 3 + 4 * APP + 6 + 2 * i + 1] = 1.0f - 2.0f * s * s;
       }
+      x[BIAS_COL1] = 1.0f;  // multiplies the b1 column of the W1 image
 #pragma unroll
-      for (int i = IN_DIM; i < K1; ++i) x[i] = 0.0f;
+      for (int i = IN_DIM + 1; i < K1; ++i) x[i] = 0.0f;
 #pragma unroll
       for (int kg = 0; kg < KG1; ++kg) {
         float g[8];
@@ -397,7 +411,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     }
     parity ^= 1;
 
-    // ---- phase 2: A2 = relu(D + b1) -> smem (two TMEM loads in flight per wait) ------------------
+    // ---- phase 2: A2 = relu(D) -> smem (D already holds the bias; two TMEM loads per wait) -------
 #pragma unroll
     for (int cb = 0; cb < HID / 64; ++cb) {
       uint32_t v[64];
@@ -406,11 +420,27 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       tmem_ld_wait();
 #pragma unroll
       for (int g8 = 0; g8 < 8; ++g8) {
-        float g[8];
+        if (TA == 1) {
+          uint4 hi;
+          hi.x = pack_h2_relu(__uint_as_float(v[g8 * 8 + 0]), __uint_as_float(v[g8 * 8 + 1]));
+          hi.y = pack_h2_relu(__uint_as_float(v[g8 * 8 + 2]), __uint_as_float(v[g8 * 8 + 3]));
+          hi.z = pack_h2_relu(__uint_as_float(v[g8 * 8 + 4]), __uint_as_float(v[g8 * 8 + 5]));
+          hi.w = pack_h2_relu(__uint_as_float(v[g8 * 8 + 6]), __uint_as_float(v[g8 * 8 + 7]));
+          *reinterpret_cast<uint4*>(a_hi + (cb * 8 + g8) * KG_BYTES + row * 16) = hi;
+        } else {
+          float g[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) g[e] = fmaxf(__uint_as_float(v[g8 * 8 + e]) + s_b1[cb * 64 + g8 * 8 + e], 0.0f);
-        store_group<TA>(a_hi, a_lo, cb * 8 + g8, row, g);
+          for (int e = 0; e < 8; ++e) g[e] = fmaxf(__uint_as_float(v[g8 * 8 + e]), 0.0f);
+          store_group<TA>(a_hi, a_lo, cb * 8 + g8, row, g);
+        }
       }
+    }
+    {
+      // the constant-1 column (input 128) and the padding of the last K-step
+      const float one[8] = {1.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      const float zero[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+      store_group<TA>(a_hi, a_lo, HID / 8, row, one);
+      store_group<TA>(a_hi, a_lo, HID / 8 + 1, row, zero);
     }
     tc_fence_before();
     proxy_fence();
@@ -438,7 +468,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       copy_pending = true;
     }
 
-    // ---- phase 3: rgb = sigmoid(W3 relu(D + b2) + b3), fp32 on the CUDA cores (packed fp32x2 FMAs)
+    // ---- phase 3: rgb = sigmoid(W3 relu(D) + b3), fp32 on the CUDA cores (packed fp32x2 FMAs) ------
     float2 p0 = make_float2(0.0f, 0.0f), p1 = p0, p2 = p0;
 #pragma unroll
     for (int cb = 0; cb < HID / 64; ++cb) {
@@ -449,16 +479,11 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
 #pragma unroll
       for (int e4 = 0; e4 < 16; ++e4) {
         const int c = cb * 64 + e4 * 4;
-        const float4 bb = *reinterpret_cast<const float4*>(s_b2 + c);
         const float4 wr = *reinterpret_cast<const float4*>(s_w3 + c);
         const float4 wg = *reinterpret_cast<const float4*>(s_w3 + HID + c);
         const float4 wb = *reinterpret_cast<const float4*>(s_w3 + 2 * HID + c);
-        float2 ha = __fadd2_rn(make_float2(__uint_as_float(v[e4 * 4 + 0]), __uint_as_float(v[e4 * 4 + 1])), make_float2(bb.x, bb.y));
-        float2 hb = __fadd2_rn(make_float2(__uint_as_float(v[e4 * 4 + 2]), __uint_as_float(v[e4 * 4 + 3])), make_float2(bb.z, bb.w));
-        ha.x = fmaxf(ha.x, 0.0f);
-        ha.y = fmaxf(ha.y, 0.0f);
-        hb.x = fmaxf(hb.x, 0.0f);
-        hb.y = fmaxf(hb.y, 0.0f);
+        const float2 ha = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 0]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 1]), 0.0f));
+        const float2 hb = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 2]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 3]), 0.0f));
         p0 = __ffma2_rn(hb, make_float2(wr.z, wr.w), __ffma2_rn(ha, make_float2(wr.x, wr.y), p0));
         p1 = __ffma2_rn(hb, make_float2(wg.z, wg.w), __ffma2_rn(ha, make_float2(wg.x, wg.y), p1));
         p2 = __ffma2_rn(hb, make_float2(wb.z, wb.w), __ffma2_rn(ha, make_float2(wb.x, wb.y), p2));
@@ -491,10 +516,11 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
 }
 
 // W [n_out][k_real] fp32 -> fp16 operand image [k_groups][n_rows][8]; rows >= n_out and
-// columns >= k_real are zero.  `k_map_c`/`k_map_cp` translate a padded product index
+// columns >= k_real are zero, except column `bias_col`, which takes `bias`.  `k_map_c`/`k_map_cp` translate a padded product index
 // (pair * cp + c) into the column of the unpadded matrix; pass 0 for a plain matrix.
 __global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __restrict__ img, int n_out, int n_rows,
-                                         int k_real, int k_groups, int k_map_c, int k_map_cp) {
+                                         int k_real, int k_groups, int k_map_c, int k_map_cp,
+                                         const float* __restrict__ bias, int bias_col) {
   int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (kg, n)
   if (i >= k_groups * n_rows) return;
   int kg = i / n_rows, n = i - kg * n_rows;
@@ -510,6 +536,8 @@ __global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __
         if (c < k_map_c && col < k_real) v = w[(size_t)n * k_real + col];
       } else if (k < k_real) {
         v = w[(size_t)n * k_real + k];
+      } else if (k == bias_col && bias != nullptr) {
+        v = bias[n];  // multiplied by the constant-1 input column
       }
     }
     dst[e] = __float2half_rn(v);
@@ -548,11 +576,13 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
   if (gnr_tc_basis_fused(m)) {
     const int cp = (c.n_app + 15) / 16 * 16, kgb = m->mlp.n_prod / 8;
     pack_weight_image_kernel<<<(kgb * NB + 255) / 256, 256, 0, st>>>(basis_w, img, c.app_dim, NB, c.n_pairs * c.n_app, kgb,
-                                                                    c.n_app, cp);
+                                                                    c.n_app, cp, nullptr, -1);
   }
-  pack_weight_image_kernel<<<(KG1 * HID + 255) / 256, 256, 0, st>>>(w1, img + WB_BYTES / 2, HID, HID, IN_DIM, KG1, 0, 0);
+  // b1 / b2 in the m->mlp fp32 copies are zeros when the model has no biases
+  pack_weight_image_kernel<<<(KG1 * HID + 255) / 256, 256, 0, st>>>(w1, img + WB_BYTES / 2, HID, HID, IN_DIM, KG1, 0, 0,
+                                                                   m->mlp.b1, BIAS_COL1);
   pack_weight_image_kernel<<<(KG2 * HID + 255) / 256, 256, 0, st>>>(w2, img + (WB_BYTES + W1_BYTES) / 2, HID, HID, HID, KG2,
-                                                                   0, 0);
+                                                                   0, 0, m->mlp.b2, BIAS_COL2);
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }
