@@ -45,20 +45,28 @@ __device__ __forceinline__ float4 f4_mul(float4 a, float4 b) {
 // and the lower corner to size - 2: no tap can fall outside and no bounds test is needed (a
 // point exactly on the upper face then takes the last texel with weight 1, which is what
 // zero padding gives as well).  All offsets are 32-bit float4 indices.
+// Lower grid index and fractional offset of one normalised coordinate on an axis of `size` points.
+struct Tap {
+  int i0;
+  float f1;
+};
+__device__ __forceinline__ Tap make_tap(float u, float fsize, int size) {
+  const float ix = fminf(fmaxf((u + 1.0f) * 0.5f * fsize, 0.0f), fsize);
+  Tap t;
+  t.i0 = min((int)ix, size - 2);
+  t.f1 = ix - (float)t.i0;
+  return t;
+}
+
 template <int J>
-__device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float y, float z, int c4, float4 (&prod)[J]) {
-  const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-  const float ix = fminf(fmaxf((u + 1.0f) * 0.5f * pl.fw, 0.0f), pl.fw);
-  const float iy = fminf(fmaxf((v + 1.0f) * 0.5f * pl.fh, 0.0f), pl.fh);
-  const float il = fminf(fmaxf((l + 1.0f) * 0.5f * pl.fl, 0.0f), pl.fl);
-  const int x0 = min((int)ix, pl.W - 2), y0 = min((int)iy, pl.H - 2), l0 = min((int)il, pl.L - 2);
-  const float ax1 = ix - (float)x0, ay1 = iy - (float)y0, al1 = il - (float)l0;
+__device__ __forceinline__ void pair_products_tap(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, int c4, float4 (&prod)[J]) {
+  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
   const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
   const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
   const uint32_t c4n = (uint32_t)pl.C >> 2;
-  const uint32_t nw = ((uint32_t)y0 * (uint32_t)pl.W + (uint32_t)x0) * c4n + (uint32_t)c4;
+  const uint32_t nw = ((uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0) * c4n + (uint32_t)c4;
   const uint32_t sw = nw + (uint32_t)pl.W * c4n;
-  const uint32_t ln = (uint32_t)l0 * c4n + (uint32_t)c4;
+  const uint32_t ln = (uint32_t)tl.i0 * c4n + (uint32_t)c4;
   const float4* pb = reinterpret_cast<const float4*>(pl.plane);
   const float4* lb = reinterpret_cast<const float4*>(pl.line);
   float4 v_nw[J], v_ne[J], v_sw[J], v_se[J], v_l0[J], v_l1[J];
@@ -79,6 +87,37 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
     pv = f4_fma(v_se[j], w_se, pv);
     float4 lv = f4_fma(v_l1[j], al1, f4_scale(v_l0[j], al0));
     prod[j] = f4_mul(pv, lv);
+  }
+}
+
+template <int J>
+__device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float y, float z, int c4, float4 (&prod)[J]) {
+  const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+  pair_products_tap<J>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), c4, prod);
+}
+
+// The three plane/line pairs of one sample.  NP == 3 is the standard VM layout (pairs
+// (x,y|z), (x,z|y), (y,z|x) on one grid, verified by the host): its nine coordinate lookups
+// collapse into three.  NP == 0 walks planes.n pairs generically.
+template <int J, int NP, class F>
+__device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, float y, float z, int c4, F&& f) {
+  if (NP == 3) {
+    const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+    const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+    const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+    float4 prod[J];
+    pair_products_tap<J>(planes.p[0], tx, ty, tz, c4, prod);
+    f(0, prod);
+    pair_products_tap<J>(planes.p[1], tx, tz, ty, c4, prod);
+    f(1, prod);
+    pair_products_tap<J>(planes.p[2], ty, tz, tx, c4, prod);
+    f(2, prod);
+  } else {
+    for (int pi = 0; pi < planes.n; ++pi) {
+      float4 prod[J];
+      pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+      f(pi, prod);
+    }
   }
 }
 
@@ -145,16 +184,12 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
     if (active) {
       float x, y, z;
       sample_xyz(p, crd, i, x, y, z);
-      const int n_planes = NP > 0 ? NP : planes.n;
-#pragma unroll
-      for (int pi = 0; pi < n_planes; ++pi) {
-        float4 prod[J];
-        pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+      for_each_pair<J, NP>(planes, x, y, z, c4, [&](int, const float4(&prod)[J]) {
         float s = 0.0f;
 #pragma unroll
         for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
         acc += s;
-      }
+      });
     }
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
@@ -213,16 +248,12 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
           id = __ldg(ids + i);
           float x, y, z;
           sample_xyz(p, crd, i, x, y, z);
-          const int n_planes = NP > 0 ? NP : planes.n;
-#pragma unroll
-          for (int pi = 0; pi < n_planes; ++pi) {
-            float4 prod[J];
-            pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+          for_each_pair<J, NP>(planes, x, y, z, c4, [&](int, const float4(&prod)[J]) {
             float s = 0.0f;
 #pragma unroll
             for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
             f += s;
-          }
+          });
         }
         f += __shfl_xor_sync(0xffffffffu, f, 1);
         f += __shfl_xor_sync(0xffffffffu, f, 2);
@@ -371,11 +402,7 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
     const long long tile = j_app >> 7;
     const int row = (int)(j_app & 127);
     const size_t out0 = (size_t)tile * tile_bytes + (size_t)row * 16 + (size_t)(c4 & 1) * 8;
-    const int n_planes = NP > 0 ? NP : planes.n;
-#pragma unroll
-    for (int pi = 0; pi < n_planes; ++pi) {
-      float4 prod[J];
-      pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+    for_each_pair<J, NP>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
 #pragma unroll
       for (int j = 0; j < J; ++j) {
         const size_t at = out0 + (size_t)(pi * 2 * J + 2 * j + (c4 >> 1)) * 2048;
@@ -394,7 +421,7 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
           *reinterpret_cast<uint2*>(prod_lo + at) = lv;
         }
       }
-    }
+    });
   }
 }
 
@@ -410,6 +437,16 @@ __global__ void positions_kernel(GnrSampleParams p, GnrCoords crd, float* __rest
     xyz[i * 3 + 2] = z;
     if (ray_index) ray_index[i] = (int32_t)(__ldg(crd.ids + i) >> p.kbits);
   }
+}
+
+// True if the three pairs are the standard VM layout on one grid: (x,y|z), (x,z|y), (y,z|x).
+bool standard_vm3(const PlaneSet& s) {
+  if (s.n != 3) return false;
+  const GnrPlane &a = s.p[0], &b = s.p[1], &c = s.p[2];
+  const bool modes = a.mat0 == 0 && a.mat1 == 1 && a.vec == 2 && b.mat0 == 0 && b.mat1 == 2 && b.vec == 1 &&
+                     c.mat0 == 1 && c.mat1 == 2 && c.vec == 0;
+  const bool sizes = b.W == a.W && b.H == a.L && b.L == a.H && c.W == a.H && c.H == a.L && c.L == a.W;
+  return modes && sizes;
 }
 
 PlaneSet make_set(const GnrPlane* src, int n) {
@@ -450,7 +487,7 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords&
   const int grid = m->sm_count * 4;
 #define GNR_DEN(JJ)                                                                                                   \
   do {                                                                                                                \
-    if (set.n == 3)                                                                                                   \
+    if (standard_vm3(set))                                                                                            \
       density_kernel<JJ, 3><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma); \
     else                                                                                                              \
       density_kernel<JJ, 0><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma); \
@@ -494,7 +531,7 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
 #define GNR_PRD(JJ, NPP, TT) app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, c, hi, lo, tile_bytes)
-  if (J == 3 && set.n == 3) {
+  if (J == 3 && standard_vm3(set)) {
     if (terms == 2) GNR_PRD(3, 3, 2); else GNR_PRD(3, 3, 1);
   } else if (J == 1) {
     if (terms == 2) GNR_PRD(1, 0, 2); else GNR_PRD(1, 0, 1);
@@ -528,7 +565,7 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
       (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)
-  if (J == 1 && set.n == 3) GNR_MARCH(1, 3);
+  if (J == 1 && standard_vm3(set)) GNR_MARCH(1, 3);
   else if (J == 1) GNR_MARCH(1, 0);
   else if (J == 2) GNR_MARCH(2, 0);
   else if (J == 3) GNR_MARCH(3, 0);
