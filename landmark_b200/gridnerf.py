@@ -8,8 +8,11 @@ signature as ``app/models/gridnerf_sequential.py`` (``GridBaseSequential.__init_
 dist_render/ddp_infer/inferer_impl.py:95-120) work unchanged.  All device work of ``forward``
 happens in the CUDA library; torch only owns the tensors.
 
-Rendering only: ``is_train=True``, the NeRF refinement branch (``run_nerf``), the appearance
-latent (``encode_app``) raise ``NotImplementedError``.  Both samplers are supported: the dense
+Rendering only: ``is_train=True`` and the NeRF refinement branch (``run_nerf``) raise
+``NotImplementedError``.  With ``args.encode_app`` the 48-d appearance latent of ``app_code``
+(``embedding_app``, gridnerf_sequential.py:429-437,681-682) is the same for every sample of a call, so
+its layer-1 contribution ``W1[:, 27:75] @ latent`` is folded into the layer-1 bias when ``app_code``
+changes; the kernels keep their 150-wide input.  Both samplers are supported: the dense
 ``sample_ray`` and, with ``args.sampling_opt``, ``sample_ray_within_hull`` with ``n_importance`` samples.
 """
 
@@ -56,9 +59,11 @@ class AlphaGridMask(torch.nn.Module):
 class _MLPRenderFea(torch.nn.Module):
     """Parameter holder with the layout of app/models/mlp_render_fea.py:20-42."""
 
-    def __init__(self, in_chanel, viewpe, feape, feature_c, bias_enable):
+    def __init__(self, in_chanel, viewpe, feape, feature_c, bias_enable, encode_app=False):
         super().__init__()
-        self.in_mlpC = 2 * max(viewpe, 0) * 3 + 2 * feape * in_chanel + 3 * (viewpe > -1) + in_chanel
+        self.encode_app = bool(encode_app)
+        self.in_mlpC = (2 * max(viewpe, 0) * 3 + 2 * feape * in_chanel + 3 * (viewpe > -1) + in_chanel
+                        + (48 if self.encode_app else 0))
         self.viewpe, self.feape = viewpe, feape
         self.mlp = torch.nn.Sequential(
             torch.nn.Linear(self.in_mlpC, feature_c, bias=bool(bias_enable)),
@@ -111,8 +116,6 @@ class B200GridNeRF(torch.nn.Module):
             raise NotImplementedError("B200GridNeRF renders only; training stays with the reference model")
         if getattr(args, "run_nerf", False):
             raise NotImplementedError("run_nerf (NeRF refinement branch) is not part of the render path")
-        if getattr(args, "encode_app", False):
-            raise NotImplementedError("encode_app (appearance latent) is not supported yet")
         if getattr(args, "nonlinear_density", False):
             raise NotImplementedError("nonlinear_density is not supported")
         dev = torch.device(device)
@@ -168,7 +171,12 @@ class B200GridNeRF(torch.nn.Module):
         self.app_plane = torch.nn.ParameterList(ap)
         self.app_line = torch.nn.ParameterList(al)
         self.basis_mat = torch.nn.Linear(sum(self.app_n_comp) * len(self.resMode), self.app_dim, bias=False).to(dev)
-        self.renderModule = _MLPRenderFea(self.app_dim, view_pe, fea_pe, featureC, getattr(args, "bias_enable", 0)).to(dev)
+        self.encode_app = bool(getattr(args, "encode_app", False))
+        if self.encode_app:
+            self.embedding_app = torch.nn.Embedding(11500, 48).to(dev)
+        self._app_code = None  # the appearance code whose latent is currently folded into the uploaded bias
+        self.renderModule = _MLPRenderFea(self.app_dim, view_pe, fea_pe, featureC, getattr(args, "bias_enable", 0),
+                                          self.encode_app).to(dev)
         for p in self.parameters():
             p.requires_grad_(False)
 
@@ -272,7 +280,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.app_dim = int(self.app_dim)
         cfg.fea_pe, cfg.view_pe = int(self.fea_pe), int(self.view_pe)
         cfg.hidden = int(self.featureC)
-        cfg.has_bias = int(self.renderModule.mlp[0].bias is not None)
+        cfg.has_bias = int(self.renderModule.mlp[0].bias is not None or self.encode_app)
         cfg.mlp_mode = self.mlp_mode
         cfg.sampling_mode = 1 if self.sampling_opt else 0
         cfg.ert_transmittance = self.ert_transmittance
@@ -308,16 +316,43 @@ class B200GridNeRF(torch.nn.Module):
                 a_c = (C.c_float * 6)(*[float(v) for v in a.reshape(-1)])
                 i_c = (C.c_float * 3)(*[float(v) for v in inv])
                 check(lib.gnr_upload_alpha_mask(h, _ptr(vol), d_, h_, w_, a_c, i_c, st), "gnr_upload_alpha_mask")
-            mlp = self.renderModule.mlp
-            ws = [mlp[i].weight.detach().float().contiguous() for i in (0, 2, 4)]
-            bs = [mlp[i].bias.detach().float().contiguous() if mlp[i].bias is not None else None for i in (0, 2, 4)]
-            bw = self.basis_mat.weight.detach().float().contiguous()
-            check(lib.gnr_upload_mlp(h, _ptr(bw), _ptr(ws[0]), _ptr(bs[0]), _ptr(ws[1]), _ptr(bs[1]), _ptr(ws[2]),
-                                     _ptr(bs[2]), st), "gnr_upload_mlp")
+            self._upload_mlp(st)
             torch.cuda.current_stream().synchronize()
         self._committed = True
         if release_torch_planes:
             self.release_torch_planes()
+
+    def _upload_mlp(self, st=None):
+        """basis_mat and the three MLP layers -> library.  With encode_app the latent columns
+        (27..74) of layer 1 are removed and their product with the current latent joins the bias."""
+        mlp = self.renderModule.mlp
+        ws = [mlp[i].weight.detach().float().contiguous() for i in (0, 2, 4)]
+        bs = [mlp[i].bias.detach().float().contiguous() if mlp[i].bias is not None else None for i in (0, 2, 4)]
+        if self.encode_app:
+            a = self.app_dim
+            w1 = ws[0]
+            b1 = bs[0] if bs[0] is not None else torch.zeros(w1.shape[0], device=self.device)
+            if self._app_code is not None:
+                latent = self.embedding_app.weight.detach()[int(self._app_code)].float()
+                b1 = b1 + w1[:, a:a + 48] @ latent
+            ws[0] = torch.cat([w1[:, :a], w1[:, a + 48:]], dim=1).contiguous()
+            bs[0] = b1.contiguous()
+        bw = self.basis_mat.weight.detach().float().contiguous()
+        check(lib.gnr_upload_mlp(self._handle, _ptr(bw), _ptr(ws[0]), _ptr(bs[0]), _ptr(ws[1]), _ptr(bs[1]), _ptr(ws[2]),
+                                 _ptr(bs[2]), st if st is not None else _stream()), "gnr_upload_mlp")
+        torch.cuda.current_stream(self.device).synchronize()  # the temporaries above must outlive the copy kernels
+
+    def set_app_code(self, app_code):
+        """Select the appearance embedding row used by the following renders (encode_app models)."""
+        if not self.encode_app:
+            return
+        if app_code is None:
+            raise ValueError("this model was built with encode_app: forward needs an app_code")
+        code = int(app_code.item()) if isinstance(app_code, torch.Tensor) else int(app_code)
+        if code != self._app_code:
+            self._app_code = code
+            with torch.cuda.device(self.device):
+                self._upload_mlp()
 
     def release_torch_planes(self):
         """Drop the torch (NCHW) copies of the planes once the library holds its own
@@ -402,6 +437,7 @@ class B200GridNeRF(torch.nn.Module):
         if is_train:
             raise NotImplementedError("is_train=True: training is not part of this package")
         rays = self._prepare(rays_chunk)
+        self.set_app_code(app_code)
         n = rays.shape[0]
         s = self._samples(N_samples)
         rgb = torch.empty((n, 3), dtype=torch.float32, device=self.device)

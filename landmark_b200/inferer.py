@@ -99,4 +99,9 @@ class B200NerfDDPInfererImpl:
     def renderer_fn(self, rays, N_samples=-1, white_bg=True, is_train=False, app_code=None):
         if self._forward is None:
             raise RuntimeError("load_model() has not been called")
-        return renderer_fn(self._forward, rays, self._chunk_size, N_samples=N_samples, white_bg=white_bg, is_train=is_train)
+        kw = {"N_samples": N_samples, "white_bg": white_bg, "is_train": is_train}
+        if getattr(self._model, "encode_app", False):
+            # the reference's single-block inferer drops app_code (inferer_impl.py:144-145), which fails
+            # for an encode_app checkpoint; here it reaches the model
+            kw["app_code"] = app_code
+        return renderer_fn(self._forward, rays, self._chunk_size, **kw)

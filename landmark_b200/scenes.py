@@ -59,6 +59,7 @@ class SceneSpec:
     ray_weight_thres: float = 1e-3
     alpha_filter_thres: float = 0.0
     bias_enable: bool = True
+    encode_app: bool = False  # 48-d appearance latent per image (embedding_app), gridnerf_sequential.py:681-682
     fea2dense_act: str = "softplus"
     mask_kind: str = "boxes"  # "boxes" (free 3-D boxes) | "heightfield" (columns from z=0)
     mask_boxes: int = 60
@@ -134,7 +135,8 @@ def _linear(gen: torch.Generator, out_f: int, in_f: int, bias: bool):
 
 def mlp_in_dim(spec: SceneSpec) -> int:
     """Width of the appearance MLP input (app/models/mlp_render_fea.py:24-26, encode_app off)."""
-    return 2 * max(spec.view_pe, 0) * 3 + 2 * spec.fea_pe * spec.app_dim + 3 * (spec.view_pe > -1) + spec.app_dim
+    return (2 * max(spec.view_pe, 0) * 3 + 2 * spec.fea_pe * spec.app_dim + 3 * (spec.view_pe > -1) + spec.app_dim
+            + (48 if spec.encode_app else 0))
 
 
 def make_state_dict(spec: SceneSpec, seed: int = FIELD_SEED, device: str = "cpu") -> Dict[str, torch.Tensor]:
@@ -171,6 +173,8 @@ def make_state_dict(spec: SceneSpec, seed: int = FIELD_SEED, device: str = "cpu"
             sd[f"renderModule.mlp.{layer}.bias"] = b
     if spec.bias_enable:
         sd["renderModule.mlp.4.bias"].zero_()  # app/models/mlp_render_fea.py:41-42
+    if spec.encode_app:
+        sd["embedding_app.weight"] = torch.randn((11500, 48), generator=gen_w, dtype=torch.float32)
     if device != "cpu":
         sd = {k: v.to(device) for k, v in sd.items()}
     return sd
@@ -237,7 +241,7 @@ def model_args(spec: SceneSpec, device: str = "cpu"):
         resMode=[1],
         sampling_opt=0,
         bias_enable=int(spec.bias_enable),
-        encode_app=False,
+        encode_app=bool(spec.encode_app),
         n_importance=spec.n_samples,
         alpha_mask_filter_thre=spec.alpha_filter_thres,
         ckpt=None,

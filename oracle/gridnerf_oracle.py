@@ -44,6 +44,7 @@ class Field:
         self.basis_w = sd["basis_mat.weight"].float()
         self.mlp_w = [sd[f"renderModule.mlp.{j}.weight"].float() for j in (0, 2, 4)]
         self.mlp_b = [sd.get(f"renderModule.mlp.{j}.bias") for j in (0, 2, 4)]
+        self.embedding_app = sd.get("embedding_app.weight")  # present iff encode_app
         self.aabb = torch.as_tensor(kwargs["aabb"], dtype=torch.float32)
         self.near, self.far = [float(v) for v in kwargs["near_far"]]
         self.density_shift = float(kwargs["density_shift"])
@@ -166,9 +167,10 @@ def positional_encoding(x, freqs: int):
     return torch.cat([torch.sin(pts), torch.cos(pts)], dim=-1)
 
 
-def mlp_render(f: Field, viewdirs, feats):
-    """Appearance MLP.  app/models/mlp_render_fea.py:44-68 (no appearance latent)."""
-    parts = [feats]
+def mlp_render(f: Field, viewdirs, feats, latent=None):
+    """Appearance MLP.  app/models/mlp_render_fea.py:44-68; ``latent [M, 48]`` is the appearance
+    embedding when the model was built with encode_app."""
+    parts = [feats] if latent is None else [feats, latent]
     if f.view_pe > -1:
         parts.append(viewdirs)
     if f.fea_pe > 0:
@@ -190,7 +192,7 @@ def raw2alpha(sigma, dist):
 
 @torch.no_grad()
 def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bool = True,
-                 keep_stages: bool = False, sampling_opt: bool = False):
+                 keep_stages: bool = False, sampling_opt: bool = False, app_code=None):
     """One chunk through ``GridBaseSequential.forward``: the dense-sampling branch
     (app/models/gridnerf_sequential.py:448-504) or, with ``sampling_opt``, the hull-sampling
     branch (:522-576, ``n_samples`` playing the role of ``n_importance``).  Returns ``rgb_map [N,3]``,
@@ -224,7 +226,12 @@ def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bo
     feats = None
     if app_mask.any():
         feats = app_feature(f, xyz[app_mask])
-        rgb[app_mask] = mlp_render(f, view_exp[app_mask], feats)
+        latent = None
+        if f.embedding_app is not None:
+            # compute_app_latent, app/models/gridnerf_sequential.py:429-437: the same row for every sample
+            idx = torch.ones(pts.shape[:-1], dtype=torch.long) * torch.as_tensor(app_code).long()
+            latent = F.embedding(idx[app_mask], f.embedding_app)
+        rgb[app_mask] = mlp_render(f, view_exp[app_mask], feats, latent)
     acc = torch.sum(weight, -1)
     rgb_map = torch.sum(weight[..., None] * rgb, -2)
     if white_bg:

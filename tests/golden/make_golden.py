@@ -65,7 +65,7 @@ def reference_model(GridNeRF, spec, ckpt, sampling_opt=0, n_importance=None):
     return model
 
 
-def reference_stages(model, raw2alpha, rays, n_samples):
+def reference_stages(model, raw2alpha, rays, n_samples, app_code=None):
     """Re-trace app/models/gridnerf_sequential.py:448-504 (or :522-576 when the model was built
     with sampling_opt) with the model's own methods."""
     rays_o, viewdirs = rays[:, :3], rays[:, 3:6]
@@ -90,7 +90,8 @@ def reference_stages(model, raw2alpha, rays, n_samples):
     if app_mask.any():
         feats = model.compute_appfeature(xyz[app_mask])
         view_exp = viewdirs.view(-1, 1, 3).expand(pts.shape)
-        rgb_s = model.renderModule(view_exp[app_mask], feats, None)
+        latent = model.compute_app_latent(xyz, app_mask, app_code) if model.args.encode_app else None
+        rgb_s = model.renderModule(view_exp[app_mask], feats, latent)
     return {"in_box": in_box, "ray_valid": ray_valid, "sigma_feature": sigma_feat, "sigma": sigma,
             "weight": weight, "app_mask": app_mask, "app_features": feats, "rgb_samples": rgb_s,
             "z_vals": z_vals}
@@ -102,17 +103,17 @@ def check_equal(name, a, b):
     assert torch.equal(a, b), f"oracle != reference at stage {name}: max diff {(a.float() - b.float()).abs().max()}"
 
 
-def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples, note, sampling_opt=0):
+def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples, note, sampling_opt=0, app_code=None):
     ckpt = scenes.make_checkpoint(spec)
     digest = scenes.state_dict_digest(ckpt["state_dict"])
     with torch.no_grad():
         model = reference_model(GridNeRF, spec, ckpt, sampling_opt, n_samples)
-        ref = reference_stages(model, raw2alpha, rays, n_samples)
-        ref_out, _ = model(rays, white_bg=True, is_train=False, N_samples=n_samples)
+        ref = reference_stages(model, raw2alpha, rays, n_samples, app_code)
+        ref_out, _ = model(rays, app_code=app_code, white_bg=True, is_train=False, N_samples=n_samples)
     field = orc.field_from_checkpoint(ckpt, spec.alpha_filter_thres)
     assert torch.equal(field.step_size, model.stepSize)
     assert field.n_samples_default == model.nSamples
-    mine = orc.render_chunk(field, rays, n_samples, True, keep_stages=True, sampling_opt=bool(sampling_opt))
+    mine = orc.render_chunk(field, rays, n_samples, True, keep_stages=True, sampling_opt=bool(sampling_opt), app_code=app_code)
     for k in ("in_box", "ray_valid", "sigma_feature", "sigma", "weight", "app_mask", "app_features", "z_vals"):
         check_equal(k, mine[k], ref[k])
     if ref["rgb_samples"] is not None:
@@ -151,6 +152,7 @@ def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples
         "rgb_map": ref_out["rgb_map"].numpy(),
         "depth_map": ref_out["depth_map"].numpy(),
         "subset_stride": np.array(SUBSET_STRIDE),
+        "app_code": np.array(-1 if app_code is None else int(app_code)),
     }
     if ref["app_features"] is not None:
         fx["app_features_sub"] = ref["app_features"].numpy()[sub]
@@ -197,6 +199,12 @@ def main():
     pin_and_dump(GridNeRF, raw2alpha, ray_utils, tiny.lit(), rays[::3].contiguous(), "tiny_lit_hull.npz", 128,
                  "config[0] lit, sampling_opt=1 (sample_ray_within_hull), n_importance=128, every 3rd ray",
                  sampling_opt=1)
+
+    # appearance latent (encode_app=1): embedding row `app_code` appended to the MLP input
+    enc = scenes.tiny_spec().lit()
+    enc.name, enc.encode_app = "tiny_lit_encode_app", True
+    pin_and_dump(GridNeRF, raw2alpha, ray_utils, enc, rays[::5].contiguous(), "tiny_lit_encode_app.npz", enc.n_samples,
+                 "config[0] lit, encode_app=1, app_code=1234, every 5th ray", app_code=torch.tensor(1234))
 
     if not a.skip_city:
         city = scenes.city_spec().lit()

@@ -396,3 +396,26 @@ def test_early_ray_termination_stays_inside_the_bar(tiny):
     assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
     d3 = (outs[1e-3]["rgb_map"] - outs[0.0]["rgb_map"]).abs().max().item()
     assert 5e-5 < d3 <= 1.01e-3  # a coarser stop is visible but bounded by its threshold
+
+
+def test_encode_app_latent_matches_reference_fixture():
+    """encode_app=1: the 48-d appearance latent of ``app_code`` (folded into the layer-1 bias here)
+    against the fixture rendered by the reference with the latent concatenated to the MLP input."""
+    spec = scenes.tiny_spec().lit()
+    spec.encode_app = True
+    fx = load_golden("tiny_lit_encode_app.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    assert scenes.state_dict_digest(ckpt["state_dict"]) == str(fx["state_dict_digest"])
+    rays = torch.from_numpy(fx["rays"]).cuda()
+    code = int(fx["app_code"])
+    for mode in (0, 2):
+        model = cuda_model(spec, ckpt, mlp_mode=mode)
+        with pytest.raises(ValueError, match="app_code"):
+            model(rays, N_samples=spec.n_samples)
+        out, _ = model(rays, app_code=torch.tensor(code), N_samples=spec.n_samples)
+        err = (out["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+        assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+        other, _ = model(rays, app_code=7, N_samples=spec.n_samples)  # another code gives another image ...
+        assert (other["rgb_map"] - out["rgb_map"]).abs().max().item() > 1e-2
+        again, _ = model(rays, app_code=code, N_samples=spec.n_samples)  # ... and switching back restores it
+        assert torch.equal(again["rgb_map"], out["rgb_map"])

@@ -125,3 +125,12 @@ def test_hull_sampler_fixture():
     assert np.array_equal(out["t_min"].numpy(), fx["t_min"])
     assert np.array_equal(out["rgb_map"].numpy(), fx["rgb_map"])
     assert np.array_equal(out["depth_map"].numpy(), fx["depth_map"])
+
+
+def test_encode_app_fixture():
+    spec = scenes.tiny_spec().lit()
+    spec.encode_app = True
+    field, _ = oracle_field(spec)
+    fx = load_golden("tiny_lit_encode_app.npz")
+    out = orc.render_chunk(field, torch.from_numpy(fx["rays"]), int(fx["n_samples"]), True, app_code=int(fx["app_code"]))
+    assert np.array_equal(out["rgb_map"].numpy(), fx["rgb_map"])
