@@ -397,7 +397,7 @@ extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1
   copy_or_zero_kernel<<<(Hd + 255) / 256, 256, 0, st>>>(b2, q.b2, Hd, Hd);
   copy_or_zero_kernel<<<1, 32, 0, st>>>(b3, q.b3, 3, 4);
   GNR_CUDA_OK(cudaGetLastError());
-  if (m->cfg.mlp_mode != 0) return gnr_mlp_tc_prepare(m, basis_w, w1, w2, st);
+  if (m->cfg.mlp_mode != 0) return gnr_mlp_tc_prepare(m, basis_w, w1, w2, w3, st);
   return 0;
 }
 
@@ -445,7 +445,7 @@ GnrWs gnr_ws_layout(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
   if (gnr_tc_basis_fused(m)) {
     const int terms = m->cfg.mlp_mode == 1 ? 2 : 1;
     const size_t tiles = (size_t)(max_app + 127) / 128;
-    L.app_prod_tile = (m->mlp.n_prod / 8) * 2048;
+    L.app_prod_tile = gnr_tc_tile_bytes(m);
     L.app_prod_image = align_up(tiles * (size_t)L.app_prod_tile, 256);
     L.app_prod = take(L.app_prod_image * terms);
   }
@@ -829,7 +829,7 @@ static PointScratch point_scratch(const GnrModel* m, int64_t n) {
   off = align_up(off + (size_t)n * 28 * 4, 256);
   if (m->cfg.mlp_mode != 0 && gnr_tc_basis_fused(m)) {
     s.terms = m->cfg.mlp_mode == 1 ? 2 : 1;
-    s.tile_bytes = (m->mlp.n_prod / 8) * 2048;
+    s.tile_bytes = gnr_tc_tile_bytes(m);
     s.prod_image = align_up((size_t)((n + 127) / 128) * s.tile_bytes, 256);
     s.prod = off;
     off += s.prod_image * s.terms;

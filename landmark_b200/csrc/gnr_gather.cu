@@ -123,12 +123,17 @@ __device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, f
 
 // Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
 // computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
+// `view` (optional) receives the ray direction of the sample.
 __device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCoords& c, long long i, float& x, float& y,
-                                           float& z) {
+                                           float& z, float* view = nullptr) {
   if (c.xyz_direct) {
     x = __ldg(c.xyz_direct + i * 3 + 0);
     y = __ldg(c.xyz_direct + i * 3 + 1);
     z = __ldg(c.xyz_direct + i * 3 + 2);
+    if (view) {
+#pragma unroll
+      for (int a = 0; a < 3; ++a) view[a] = c.view_direct ? __ldg(c.view_direct + i * 3 + a) : 0.0f;
+    }
     return;
   }
   const uint32_t id = __ldg(c.ids + (c.index ? (long long)__ldg(c.index + i) : i));
@@ -136,9 +141,15 @@ __device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCo
   const int k = (int)(id & ((1u << p.kbits) - 1u));
   const float* r = c.rays + (size_t)ray * 6;
   const float t = gnr_sample_t(p, __ldg(c.t_min + ray), k);
-  x = gnr_normalize(gnr_point(__ldg(r + 0), __ldg(r + 3), t), p.lo[0], p.inv[0]);
-  y = gnr_normalize(gnr_point(__ldg(r + 1), __ldg(r + 4), t), p.lo[1], p.inv[1]);
-  z = gnr_normalize(gnr_point(__ldg(r + 2), __ldg(r + 5), t), p.lo[2], p.inv[2]);
+  const float dx = __ldg(r + 3), dy = __ldg(r + 4), dz = __ldg(r + 5);
+  x = gnr_normalize(gnr_point(__ldg(r + 0), dx, t), p.lo[0], p.inv[0]);
+  y = gnr_normalize(gnr_point(__ldg(r + 1), dy, t), p.lo[1], p.inv[1]);
+  z = gnr_normalize(gnr_point(__ldg(r + 2), dz, t), p.lo[2], p.inv[2]);
+  if (view) {
+    view[0] = dx;
+    view[1] = dy;
+    view[2] = dz;
+  }
 }
 
 __device__ __forceinline__ long long coords_total(const GnrCoords& c) {
@@ -386,10 +397,13 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, const float
 // operand layout of their 128-sample tile: element (row r, k) of tile t at byte
 //   t * tile_bytes + (k / 8) * 2048 + r * 16 + (k % 8) * 2,     k = pair * C + channel.
 // With TA == 2 the fp16 rounding residual goes to a second image of the same shape.
+// One more 16-byte group per row, after the products (k group `view_group`), carries the
+// sample's view direction for the MLP kernel as fp16 pairs {hi x, hi y, hi z, lo x, lo y, lo z}:
+// hi + lo restores the fp32 value to about 2^-22, and the MLP kernel needs no list lookups.
 template <int J, int NP, int TA>
 __global__ void __launch_bounds__(kBlock)
 app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
-                    unsigned char* __restrict__ prod_lo, int tile_bytes) {
+                    unsigned char* __restrict__ prod_lo, int tile_bytes, int view_group) {
   const int c4 = threadIdx.x & 3;
   const long long total = coords_total(crd);
   long long range_beg, range_end;
@@ -397,11 +411,23 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
   for (long long base = range_beg + (threadIdx.x >> 5) * 8; base < range_end; base += kBlock / 4) {
     const long long j_app = base + ((threadIdx.x & 31) >> 2);
     if (j_app >= range_end) continue;
-    float x, y, z;
-    sample_xyz(p, crd, j_app, x, y, z);
+    float x, y, z, view[3];
+    sample_xyz(p, crd, j_app, x, y, z, view);
     const long long tile = j_app >> 7;
     const int row = (int)(j_app & 127);
     const size_t out0 = (size_t)tile * tile_bytes + (size_t)row * 16 + (size_t)(c4 & 1) * 8;
+    if (c4 == 0) {
+      const __half hx = __float2half_rn(view[0]), hy = __float2half_rn(view[1]), hz = __float2half_rn(view[2]);
+      const __half2 a = __halves2half2(hx, hy);
+      const __half2 b = __halves2half2(hz, __float2half_rn(view[0] - __half2float(hx)));
+      const __half2 c = __floats2half2_rn(view[1] - __half2float(hy), view[2] - __half2float(hz));
+      uint4 vv;
+      vv.x = *reinterpret_cast<const uint32_t*>(&a);
+      vv.y = *reinterpret_cast<const uint32_t*>(&b);
+      vv.z = *reinterpret_cast<const uint32_t*>(&c);
+      vv.w = 0u;
+      *reinterpret_cast<uint4*>(prod_hi + (size_t)tile * tile_bytes + (size_t)view_group * 2048 + (size_t)row * 16) = vv;
+    }
     for_each_pair<J, NP>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
 #pragma unroll
       for (int j = 0; j < J; ++j) {
@@ -530,7 +556,7 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
-#define GNR_PRD(JJ, NPP, TT) app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, c, hi, lo, tile_bytes)
+#define GNR_PRD(JJ, NPP, TT) app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, c, hi, lo, tile_bytes, m->mlp.n_prod / 8)
   if (J == 3 && standard_vm3(set)) {
     if (terms == 2) GNR_PRD(3, 3, 2); else GNR_PRD(3, 3, 1);
   } else if (J == 1) {

@@ -140,6 +140,7 @@ int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoor
 int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* prod_hi,
                         unsigned char* prod_lo, int tile_bytes, int terms, cudaStream_t st);
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
+int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
                      cudaStream_t st);
 int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat,
@@ -154,7 +155,8 @@ int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const
 int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,
                           int32_t* status, int total_slot, int overflow_slot, int64_t capacity,
                           cudaStream_t st);
-int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, cudaStream_t st);
+int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, const float* w3,
+                       cudaStream_t st);
 
 #define GNR_CUDA_OK(expr)                                                              \
   do {                                                                                 \

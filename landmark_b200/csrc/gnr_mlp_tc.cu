@@ -52,6 +52,9 @@ constexpr int KGB_BYTES = NB * 16;                             // 512: one K gro
 constexpr int MAX_K0 = 160;                                    // products per sample the A buffer can hold
 constexpr int W1_BYTES = KG1 * KG_BYTES, W2_BYTES = KG2 * KG_BYTES, A_BYTES = KG1 * KG_BYTES;
 constexpr int WB_BYTES = (MAX_K0 / 8) * KGB_BYTES;
+constexpr int N3 = 16;                                         // layer-3 outputs padded to the smallest MMA N
+constexpr int KG3_BYTES = N3 * 16;                             // 256: one K group of the layer-3 operand
+constexpr int W3_BYTES = (HID / 8) * KG3_BYTES;                // 4096
 constexpr int FEAT_STRIDE = 28;
 constexpr int COLS_PER_SLOT = HID + NB;  // D (128) + F (32)
 constexpr uint32_t kWaitLimit = 1u << 20;
@@ -67,6 +70,7 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 // fp16 x fp16 -> fp32, A and B K-major, M = 128
 constexpr uint32_t kIdescHid = (1u << 4) | ((uint32_t)(HID >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 constexpr uint32_t kIdescBasis = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+constexpr uint32_t kIdescOut = (1u << 4) | ((uint32_t)(N3 >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 
 __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -75,6 +79,17 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
       "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Same, with the A operand in tensor memory: lane = row, one 32-bit column = two consecutive k (fp16).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 
@@ -141,6 +156,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&v)[4]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3])
+               : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0],"
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16,"
+      " %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+      "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+      "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]),
+      "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]),
+      "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // sin and cos for operands that are about to be rounded to fp16 (relative step 4.9e-4): the
 // hardware approximations, which reduce the argument themselves (absolute error about 1e-6 for
@@ -194,7 +226,7 @@ struct TcArgs {
   const unsigned char* prod_lo;
   int tile_bytes;                 // bytes of one product tile (k0 / 8 * 2048)
   int k0;                         // products per sample
-  const unsigned char* w_image;   // [basis fp16 operand image (WB_BYTES)][W1 image][W2 image]
+  const unsigned char* w_image;   // [basis fp16 operand image (WB_BYTES)][W1 image][W2 image][W3 image]
   const float* w3;
   const float* b1;
   const float* b2;
@@ -210,7 +242,8 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   unsigned char* s_wb = smem;
   unsigned char* s_w1 = s_wb + WB_BYTES;
   unsigned char* s_w2 = s_w1 + W1_BYTES;
-  unsigned char* s_a = s_w2 + W2_BYTES;  // [NSLOT][TA][A_BYTES]
+  unsigned char* s_w3h = s_w2 + W2_BYTES;  // layer 3 as an fp16 operand (used when L3TC)
+  unsigned char* s_a = s_w3h + W3_BYTES;   // [NSLOT][TA][A_BYTES]
   float* s_w3 = reinterpret_cast<float*>(s_a + NSLOT * TA * A_BYTES);
   float* s_b1 = s_w3 + 3 * HID;
   float* s_b2 = s_b1 + HID;
@@ -227,7 +260,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   {
     const uint4* src = reinterpret_cast<const uint4*>(a.w_image);
     uint4* dst = reinterpret_cast<uint4*>(s_wb);
-    for (int i = tid; i < (WB_BYTES + W1_BYTES + W2_BYTES) / 16; i += NSLOT * 128) dst[i] = src[i];
+    for (int i = tid; i < (WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES) / 16; i += NSLOT * 128) dst[i] = src[i];
     for (int i = tid; i < 3 * HID; i += NSLOT * 128) s_w3[i] = a.w3[i];
     for (int i = tid; i < HID; i += NSLOT * 128) {
       s_b1[i] = a.b1[i];
@@ -256,7 +289,8 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   unsigned char* a_hi = s_a + (slot * TA) * A_BYTES;
   unsigned char* a_lo = a_hi + (TA == 2 ? A_BYTES : 0);
   const uint32_t a_hi_addr = smem_u32(a_hi), a_lo_addr = smem_u32(a_lo);
-  const uint32_t wb_addr = smem_u32(s_wb), w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2);
+  const uint32_t wb_addr = smem_u32(s_wb), w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2), w3_addr = smem_u32(s_w3h);
+  constexpr bool L3TC = (TA == 1);  // layer 3 on the tensor cores too (fp16 operands); TA == 2 keeps it in fp32
   const uint32_t mbar = smem_u32(&s_mbar[2 * slot]), tbar = smem_u32(&s_mbar[2 * slot + 1]);
   const int bar_id = 1 + slot;  // named barrier of this group (0 is __syncthreads)
   uint32_t parity = 0, tparity = 0;
@@ -338,7 +372,18 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     // ---- phase 1: this row of the layer-1 input ---------------------------------------------
     {
       float view[3] = {0.0f, 0.0f, 0.0f};
-      if (live) {
+      if (BASIS) {
+        // the gather kernel left the view direction in the k group after the products (hi + lo fp16)
+        const uint4 vv = *reinterpret_cast<const uint4*>(a_hi + (a.k0 >> 3) * KG_BYTES + row * 16);
+        const float2 p0 = __half22float2(*reinterpret_cast<const __half2*>(&vv.x));
+        const float2 p1 = __half22float2(*reinterpret_cast<const __half2*>(&vv.y));
+        const float2 p2 = __half22float2(*reinterpret_cast<const __half2*>(&vv.z));
+        if (live) {
+          view[0] = p0.x + p1.y;
+          view[1] = p0.y + p2.x;
+          view[2] = p1.x + p2.y;
+        }
+      } else if (live) {
         const float* vsrc;
         if (a.crd.view_direct) {
           vsrc = a.crd.view_direct + (size_t)j * 3;
@@ -463,28 +508,69 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       copy_pending = true;
     }
 
-    // ---- phase 3: rgb = sigmoid(W3 relu(D) + b3), fp32 on the CUDA cores (packed fp32x2 FMAs) ------
-    float2 p0 = make_float2(0.0f, 0.0f), p1 = p0, p2 = p0;
+    float o0, o1, o2;
+    if (L3TC) {
+      // ---- phase 3 (tensor cores): relu(D) goes back into tensor memory as packed fp16 pairs, over the
+      // columns of D this thread has already read (64 columns hold k = 0..127), and is the A operand
+      // of 8 more MMAs (N = 16, 3 real outputs) whose accumulator reuses the feature columns.
 #pragma unroll
-    for (int cb = 0; cb < HID / 64; ++cb) {
-      uint32_t v[64];
-      tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-      tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-      tmem_ld_wait();
+      for (int cb = 0; cb < HID / 64; ++cb) {
+        uint32_t v[64];
+        tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_ld_wait();
+        uint32_t h[32];
 #pragma unroll
-      for (int e4 = 0; e4 < 16; ++e4) {
-        const int c = cb * 64 + e4 * 4;
-        const float4 wr = *reinterpret_cast<const float4*>(s_w3 + c);
-        const float4 wg = *reinterpret_cast<const float4*>(s_w3 + HID + c);
-        const float4 wb = *reinterpret_cast<const float4*>(s_w3 + 2 * HID + c);
-        const float2 ha = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 0]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 1]), 0.0f));
-        const float2 hb = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 2]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 3]), 0.0f));
-        p0 = __ffma2_rn(hb, make_float2(wr.z, wr.w), __ffma2_rn(ha, make_float2(wr.x, wr.y), p0));
-        p1 = __ffma2_rn(hb, make_float2(wg.z, wg.w), __ffma2_rn(ha, make_float2(wg.x, wg.y), p1));
-        p2 = __ffma2_rn(hb, make_float2(wb.z, wb.w), __ffma2_rn(ha, make_float2(wb.x, wb.y), p2));
+        for (int e = 0; e < 32; ++e) h[e] = pack_h2_relu(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+        tmem_st32(d_tmem + lane_off + cb * 32, h);
       }
+      tmem_st_wait();
+      tc_fence_before();
+      asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+      if (row == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int ks = 0; ks < HID / 16; ++ks)
+          mma_f16_ts(f_tmem, d_tmem + ks * 8, make_desc(w3_addr + ks * 2 * KG3_BYTES, KG3_BYTES), kIdescOut, ks > 0 ? 1u : 0u);
+        mma_commit(mbar);
+      }
+      if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
+        if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
+        break;
+      }
+      parity ^= 1;
+      uint32_t r[4];
+      tmem_ld4(f_tmem + lane_off, r);
+      tmem_ld_wait();
+      o0 = s_b3[0] + __uint_as_float(r[0]);
+      o1 = s_b3[1] + __uint_as_float(r[1]);
+      o2 = s_b3[2] + __uint_as_float(r[2]);
+    } else {
+      // ---- phase 3 (CUDA cores): rgb = sigmoid(W3 relu(D) + b3) in fp32, packed fp32x2 FMAs ----------
+      float2 p0 = make_float2(0.0f, 0.0f), p1 = p0, p2 = p0;
+#pragma unroll
+      for (int cb = 0; cb < HID / 64; ++cb) {
+        uint32_t v[64];
+        tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+        tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+        tmem_ld_wait();
+#pragma unroll
+        for (int e4 = 0; e4 < 16; ++e4) {
+          const int c = cb * 64 + e4 * 4;
+          const float4 wr = *reinterpret_cast<const float4*>(s_w3 + c);
+          const float4 wg = *reinterpret_cast<const float4*>(s_w3 + HID + c);
+          const float4 wb = *reinterpret_cast<const float4*>(s_w3 + 2 * HID + c);
+          const float2 ha = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 0]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 1]), 0.0f));
+          const float2 hb = make_float2(fmaxf(__uint_as_float(v[e4 * 4 + 2]), 0.0f), fmaxf(__uint_as_float(v[e4 * 4 + 3]), 0.0f));
+          p0 = __ffma2_rn(hb, make_float2(wr.z, wr.w), __ffma2_rn(ha, make_float2(wr.x, wr.y), p0));
+          p1 = __ffma2_rn(hb, make_float2(wg.z, wg.w), __ffma2_rn(ha, make_float2(wg.x, wg.y), p1));
+          p2 = __ffma2_rn(hb, make_float2(wb.z, wb.w), __ffma2_rn(ha, make_float2(wb.x, wb.y), p2));
+        }
+      }
+      o0 = s_b3[0] + (p0.x + p0.y);
+      o1 = s_b3[1] + (p1.x + p1.y);
+      o2 = s_b3[2] + (p2.x + p2.y);
     }
-    const float o0 = s_b3[0] + (p0.x + p0.y), o1 = s_b3[1] + (p1.x + p1.y), o2 = s_b3[2] + (p2.x + p2.y);
     if (live) {
       float* out = a.rgb_out + (size_t)j * 3;
       out[0] = 1.0f / (1.0f + expf(-o0));
@@ -541,7 +627,7 @@ __global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __
 
 template <int TA, int NSLOT, bool BASIS>
 int launch_variant(const GnrModel* m, const TcArgs& args, cudaStream_t st) {
-  const size_t smem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + (size_t)NSLOT * TA * A_BYTES +
+  const size_t smem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES + (size_t)NSLOT * TA * A_BYTES +
                       (3 * HID + 2 * HID + 4) * sizeof(float) + 2 * NSLOT * sizeof(uint64_t) + 32;
   cudaError_t e = cudaFuncSetAttribute(mlp_tc_kernel<TA, NSLOT, BASIS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
@@ -552,10 +638,13 @@ int launch_variant(const GnrModel* m, const TcArgs& args, cudaStream_t st) {
 }  // namespace
 
 int gnr_tc_basis_fused(const GnrModel* m) {
-  return m->cfg.mlp_mode != 0 && m->mlp.n_prod % 16 == 0 && m->mlp.n_prod <= MAX_K0 && m->cfg.app_dim <= NB;
+  // the operand buffer holds the products and one more k group (the view direction)
+  return m->cfg.mlp_mode != 0 && m->mlp.n_prod % 16 == 0 && m->mlp.n_prod + 8 <= MAX_K0 && m->cfg.app_dim <= NB;
 }
 
-int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, cudaStream_t st) {
+int gnr_tc_tile_bytes(const GnrModel* m) { return (m->mlp.n_prod / 8 + 1) * KG_BYTES; }
+
+int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const float* w2, const float* w3, cudaStream_t st) {
   const GnrConfig& c = m->cfg;
   if (c.app_dim != APP || c.fea_pe != FPE || c.view_pe != VPE || c.hidden != HID) {
     gnr_set_error("tensor-core MLP supports app_dim 27, fea_pe 2, view_pe 2, featureC 128 (got %d, %d, %d, %d); use mlp_mode 0",
@@ -564,7 +653,7 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
   }
   if (m->mlp.tc_image) cudaFree(m->mlp.tc_image);
   m->mlp.tc_image = nullptr;
-  m->mlp.tc_image_bytes = (size_t)WB_BYTES + W1_BYTES + W2_BYTES;
+  m->mlp.tc_image_bytes = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES;
   GNR_CUDA_OK(cudaMalloc(&m->mlp.tc_image, m->mlp.tc_image_bytes));
   GNR_CUDA_OK(cudaMemsetAsync(m->mlp.tc_image, 0, m->mlp.tc_image_bytes, st));
   __half* img = reinterpret_cast<__half*>(m->mlp.tc_image);
@@ -578,6 +667,8 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
                                                                    m->mlp.b1, BIAS_COL1);
   pack_weight_image_kernel<<<(KG2 * HID + 255) / 256, 256, 0, st>>>(w2, img + (WB_BYTES + W1_BYTES) / 2, HID, HID, HID, KG2,
                                                                    0, 0, m->mlp.b2, BIAS_COL2);
+  pack_weight_image_kernel<<<((HID / 8) * N3 + 255) / 256, 256, 0, st>>>(w3, img + (WB_BYTES + W1_BYTES + W2_BYTES) / 2, 3, N3,
+                                                                        HID, HID / 8, 0, 0, nullptr, -1);
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }
