@@ -3,10 +3,8 @@
 // raw2alpha (app/tools/utils.py:51-64): alpha = 1 - exp(-sigma * dist),
 // T = cumprod([1, 1 - alpha + 1e-10]), w = alpha * T[:-1].  Samples that failed the validity
 // test have sigma = 0, hence alpha = 0 and a factor of exactly 1.0f, so the product over a
-// ray's compacted samples equals the product over all of its samples.  One warp walks one
-// ray's segment of the compacted list, 32 samples per step, with a warp multiply-scan and a
-// running carry.  Once the carry is <= the appearance threshold no later sample can satisfy
-// w > threshold (w <= T), which is the early termination of the appearance work.
+// ray's compacted samples equals the product over all of its samples, taken in sample order as
+// torch.cumprod does on the CPU.
 #include "gnr_internal.cuh"
 
 namespace {
@@ -19,61 +17,39 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+// One thread per ray, samples in order: the same operations in the same order as the fused
+// march kernel, so both give the same bits.
+__global__ void __launch_bounds__(128)
 weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float* __restrict__ t_min_arr,
                const uint32_t* __restrict__ ids, const float* __restrict__ sigma, const int32_t* __restrict__ offsets,
                int64_t n_rays, long long capacity, float* __restrict__ weight, float* __restrict__ acc_out,
                float* __restrict__ depth_out, int32_t* __restrict__ app_counts) {
-  const int lane = threadIdx.x & 31;
-  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t ray = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (ray >= n_rays) return;
-  long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+  const long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
   float acc = 0.0f, dep = 0.0f;
   int n_app = 0;
   if (beg < end) {
     const float t_min = t_min_arr[ray];
     const uint32_t kmask = (1u << p.kbits) - 1u;
-    float carry = 1.0f;  // transmittance before the first sample of this step
-    for (long long base = beg; base < end; base += 32) {
-      const long long i = base + lane;
-      const bool active = i < end;
-      float alpha = 0.0f, f = 1.0f, t = 0.0f;
-      if (active) {
-        const int k = (int)(__ldg(ids + i) & kmask);
-        t = gnr_sample_t(p, t_min, k);
-        // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
-        const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
-        const float x = __fmul_rn(-__ldg(sigma + i), __fmul_rn(dist, distance_scale));
-        alpha = __fsub_rn(1.0f, expf(x));
-        f = __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
-      }
-      // inclusive multiply-scan of the factors
-      float incl = f;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl *= up;
-      }
-      float excl = __shfl_up_sync(0xffffffffu, incl, 1);
-      if (lane == 0) excl = 1.0f;
-      const float T = carry * excl;
+    float T = 1.0f;  // transmittance before the current sample
+    for (long long i = beg; i < end; ++i) {
+      const int k = (int)(__ldg(ids + i) & kmask);
+      const float t = gnr_sample_t(p, t_min, k);
+      // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
+      const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
+      const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-__ldg(sigma + i), __fmul_rn(dist, distance_scale))));
       const float w = alpha * T;
-      if (active) {
-        weight[i] = w;
-        acc += w;
-        dep = fmaf(w, t, dep);
-      }
-      n_app += __popc(__ballot_sync(0xffffffffu, active && (w > thres)));
-      carry *= __shfl_sync(0xffffffffu, incl, 31);
+      weight[i] = w;
+      acc += w;
+      dep = fmaf(w, t, dep);
+      n_app += (w > thres) ? 1 : 0;
+      T *= __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
     }
-    acc = warp_sum(acc);
-    dep = warp_sum(dep);
   }
-  if (lane == 0) {
-    acc_out[ray] = acc;
-    depth_out[ray] = dep;
-    app_counts[ray] = n_app;
-  }
+  acc_out[ray] = acc;
+  depth_out[ray] = dep;
+  app_counts[ray] = n_app;
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -137,8 +113,8 @@ composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ a
 
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                         int64_t max_valid, cudaStream_t st) {
-  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  weights_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+  unsigned blocks = (unsigned)((n + 127) / 128);
+  weights_kernel<<<blocks, 128, 0, st>>>(
       p, m->cfg.distance_scale, m->cfg.ray_weight_thres, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids),
       (const float*)(ws + L.sigma), (const int32_t*)(ws + L.offsets), n, (long long)max_valid, (float*)(ws + L.weight),
       (float*)(ws + L.acc), (float*)(ws + L.depth), (int32_t*)(ws + L.app_counts));

@@ -121,6 +121,74 @@ __device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, f
   }
 }
 
+// ---- one thread, one sample: all channels of a pair with 256-bit loads ----------------------------
+struct __align__(32) F8 {
+  float4 lo, hi;
+};
+__device__ __forceinline__ F8 ldg8(const float* ptr) {
+  F8 r;
+  asm("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=f"(r.lo.x), "=f"(r.lo.y), "=f"(r.lo.z), "=f"(r.lo.w), "=f"(r.hi.x), "=f"(r.hi.y), "=f"(r.hi.z), "=f"(r.hi.w)
+      : "l"(ptr));
+  return r;
+}
+
+// Adds to part[c] (c = 0..3) the sum over j of the plane x line products of channels
+// 16 j + 4 c .. 16 j + 4 c + 3, with the operations and the order the four lanes of a quad use in
+// pair_products_tap / density_kernel, so that a sample's density feature has the same bits
+// whichever kernel computes it.
+template <int J>
+__device__ __forceinline__ void pair_sums_thread(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, float (&part)[4]) {
+  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
+  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
+  const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
+  constexpr uint32_t C = 16u * J;
+  const float* pn = pl.plane + ((uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0) * C;
+  const float* ps = pn + (uint32_t)pl.W * C;
+  const float* ln = pl.line + (uint32_t)tl.i0 * C;
+  float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int h = 0; h < 2 * J; ++h) {  // 8 channels per round: quarters 2 (h & 1) and 2 (h & 1) + 1 of group j = h >> 1
+    const F8 v_nw = ldg8(pn + 8 * h), v_ne = ldg8(pn + C + 8 * h), v_sw = ldg8(ps + 8 * h), v_se = ldg8(ps + C + 8 * h);
+    const F8 v_l0 = ldg8(ln + 8 * h), v_l1 = ldg8(ln + C + 8 * h);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float4 nw = q ? v_nw.hi : v_nw.lo, ne = q ? v_ne.hi : v_ne.lo, sw = q ? v_sw.hi : v_sw.lo, se = q ? v_se.hi : v_se.lo;
+      const float4 l0 = q ? v_l0.hi : v_l0.lo, l1 = q ? v_l1.hi : v_l1.lo;
+      float4 pv = f4_scale(nw, w_nw);
+      pv = f4_fma(ne, w_ne, pv);
+      pv = f4_fma(sw, w_sw, pv);
+      pv = f4_fma(se, w_se, pv);
+      const float4 lv = f4_fma(l1, al1, f4_scale(l0, al0));
+      const float4 prod = f4_mul(pv, lv);
+      s[2 * (h & 1) + q] += (prod.x + prod.y) + (prod.z + prod.w);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) part[c] += s[c];
+}
+
+// Density feature of one sample, computed by one thread.
+template <int J, int NP>
+__device__ __forceinline__ float density_thread(const PlaneSet& planes, float x, float y, float z) {
+  float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  if (NP == 3) {
+    const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+    const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+    const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+    pair_sums_thread<J>(planes.p[0], tx, ty, tz, part);
+    pair_sums_thread<J>(planes.p[1], tx, tz, ty, part);
+    pair_sums_thread<J>(planes.p[2], ty, tz, tx, part);
+  } else {
+    for (int pi = 0; pi < planes.n; ++pi) {
+      const GnrPlane& pl = planes.p[pi];
+      const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+      pair_sums_thread<J>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), part);
+    }
+  }
+  return (part[0] + part[1]) + (part[2] + part[3]);
+}
+
 // Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
 // computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
 // `view` (optional) receives the ray direction of the sample.
@@ -167,10 +235,11 @@ __device__ __forceinline__ float density_activation(float f, float shift, int ac
   return e < 0.01f ? e * (1.0f - e * (0.5f - e * 0.33333334f)) : __logf(1.0f + e);
 }
 
-// Contiguous share of [0, total) for this CTA, in units of the kBlock / 4 samples one CTA
-// iteration covers.
+// Contiguous share of [0, total) for this CTA, in units of the kBlock / LANES samples one CTA
+// iteration covers (LANES lanes share a sample).
+template <int LANES = 4>
 __device__ __forceinline__ void cta_range(long long total, long long& beg, long long& end) {
-  constexpr long long kStep = kBlock / 4;
+  constexpr long long kStep = kBlock / LANES;
   const long long steps = (total + kStep - 1) / kStep;
   const long long per = (steps + gridDim.x - 1) / gridDim.x;
   beg = min(total, (long long)blockIdx.x * per * kStep);
@@ -211,16 +280,21 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
   }
 }
 
-// Fused density + weights pass ("march"): one warp walks one ray's segment of the compacted
-// list, 32 samples per step.  Each step gathers the density of its 32 samples (4 sub-steps of 8
-// samples, 4 lanes per sample as in density_kernel), hands every sample's sigma to the lane of
-// the same index, and continues raw2alpha's transmittance product with the same 32-sample
-// multiply-scan and carry as weights_kernel (so with t_stop == 0 the weights are bit-identical to
-// the two-kernel path).  When the carry falls below t_stop the ray stops: the remaining samples
-// get weight 0 and never touch the planes.  What they would have added to acc (and, with a white
-// background, taken from rgb) is bounded by the transmittance at the stop, i.e. by t_stop.
+// Fused density + weights pass ("march"): one thread walks one ray's segment of the compacted
+// list, sample by sample: density feature (density_thread), activation, raw2alpha's alpha, the
+// running transmittance product in sample order (as torch.cumprod computes it on the CPU), weight,
+// and the ray's accumulated opacity and depth.  The 32 rays of a warp are consecutive rays of the
+// chunk; when those are neighbouring pixels (tile order) their samples of equal rank lie within a
+// few voxels of each other, so the lanes of one load instruction read a handful of texels and the
+// L1 serves them as broadcasts.  When the transmittance falls below t_stop the ray stops: the
+// remaining samples get weight 0 and never touch the planes.  What they would have added to acc
+// (and, with a white background, taken from rgb) is bounded by the transmittance at the stop,
+// i.e. by t_stop.  With t_stop == 0 the weights are bit-identical to density_kernel followed by
+// weights_kernel.
+constexpr int kMarchBlock = 128;
+
 template <int J, int NP>
-__global__ void __launch_bounds__(kBlock)
+__global__ void __launch_bounds__(kMarchBlock)
 march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
              const uint32_t* __restrict__ ids, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
@@ -229,101 +303,47 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
   __shared__ int s_evaluated;
   if (threadIdx.x == 0) s_evaluated = 0;
   __syncthreads();
-  const int lane = threadIdx.x & 31, c4 = lane & 3, quad = lane >> 2;
-  const long long ray = (long long)blockIdx.x * (kBlock / 32) + (threadIdx.x >> 5);
-  const bool has_ray = ray < n_rays;
-  const long long beg = has_ray ? offsets[ray] : 0, end = has_ray ? min((long long)offsets[ray + 1], capacity) : 0;
-  float acc = 0.0f, dep = 0.0f;
-  int n_app = 0;
-  long long evaluated = 0;
-  if (beg < end) {
-    GnrCoords crd;
-    crd.rays = rays;
-    crd.t_min = t_min_arr;
-    crd.ids = ids;
-    crd.index = nullptr;
-    crd.xyz_direct = nullptr;
-    const float t_min = t_min_arr[ray];
-    const uint32_t kmask = (1u << p.kbits) - 1u;
-    float carry = 1.0f;
-    for (long long base = beg; base < end; base += 32) {
-      float my_sigma = 0.0f;
-      uint32_t my_id = 0;
-#pragma unroll
-      for (int sub = 0; sub < 4; ++sub) {
-        const long long i = base + sub * 8 + quad;
-        const bool active = i < end;
-        float f = 0.0f;
-        uint32_t id = 0;
-        if (active) {
-          id = __ldg(ids + i);
-          float x, y, z;
-          sample_xyz(p, crd, i, x, y, z);
-          for_each_pair<J, NP>(planes, x, y, z, c4, [&](int, const float4(&prod)[J]) {
-            float s = 0.0f;
-#pragma unroll
-            for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
-            f += s;
-          });
-        }
-        f += __shfl_xor_sync(0xffffffffu, f, 1);
-        f += __shfl_xor_sync(0xffffffffu, f, 2);
-        const float sg = active ? density_activation(f, shift, act) : 0.0f;
-        // sample base + L is handled in sub-step L >> 3 by quad L & 7
-        const float v = __shfl_sync(0xffffffffu, sg, (lane & 7) * 4);
-        const uint32_t vid = __shfl_sync(0xffffffffu, id, (lane & 7) * 4);
-        if ((lane >> 3) == sub) {
-          my_sigma = v;
-          my_id = vid;
-        }
-      }
-      // ---- raw2alpha for these 32 samples (lane = sample), as in weights_kernel -----------------
-      const long long i = base + lane;
-      const bool active = i < end;
-      float alpha = 0.0f, fct = 1.0f, t = 0.0f;
-      if (active) {
-        const int k = (int)(my_id & kmask);
-        t = gnr_sample_t(p, t_min, k);
+  const long long ray = (long long)blockIdx.x * kMarchBlock + threadIdx.x;
+  int evaluated = 0;
+  if (ray < n_rays) {
+    const long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
+    float acc = 0.0f, dep = 0.0f;
+    int n_app = 0;
+    if (beg < end) {
+      const float* r = rays + (size_t)ray * 6;
+      const float ox = __ldg(r + 0), oy = __ldg(r + 1), oz = __ldg(r + 2);
+      const float dx = __ldg(r + 3), dy = __ldg(r + 4), dz = __ldg(r + 5);
+      const float t_min = t_min_arr[ray];
+      const uint32_t kmask = (1u << p.kbits) - 1u;
+      float T = 1.0f;
+      long long i = beg;
+      while (i < end) {
+        const int k = (int)(__ldg(ids + i) & kmask);
+        const float t = gnr_sample_t(p, t_min, k);
+        const float x = gnr_normalize(gnr_point(ox, dx, t), p.lo[0], p.inv[0]);
+        const float y = gnr_normalize(gnr_point(oy, dy, t), p.lo[1], p.inv[1]);
+        const float z = gnr_normalize(gnr_point(oz, dz, t), p.lo[2], p.inv[2]);
+        const float sg = density_activation(density_thread<J, NP>(planes, x, y, z), shift, act);
         const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
-        const float xx = __fmul_rn(-my_sigma, __fmul_rn(dist, distance_scale));
-        alpha = __fsub_rn(1.0f, expf(xx));
-        fct = __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
-      }
-      float incl = fct;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const float up = __shfl_up_sync(0xffffffffu, incl, o);
-        if (lane >= o) incl *= up;
-      }
-      float excl = __shfl_up_sync(0xffffffffu, incl, 1);
-      if (lane == 0) excl = 1.0f;
-      const float T = carry * excl;
-      const float w = alpha * T;
-      if (active) {
+        const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-sg, __fmul_rn(dist, distance_scale))));
+        const float w = alpha * T;
         weight[i] = w;
         acc += w;
         dep = fmaf(w, t, dep);
+        n_app += (w > thres) ? 1 : 0;
+        T *= __fadd_rn(__fsub_rn(1.0f, alpha), 1e-10f);
+        ++i;
+        if (T < t_stop) break;
       }
-      n_app += __popc(__ballot_sync(0xffffffffu, active && (w > thres)));
-      carry *= __shfl_sync(0xffffffffu, incl, 31);
-      evaluated = min(base + 32, end) - beg;
-      if (carry < t_stop) {
-        for (long long r = base + 32 + lane; r < end; r += 32) weight[r] = 0.0f;
-        break;
-      }
+      evaluated = (int)(i - beg);
+      for (; i < end; ++i) weight[i] = 0.0f;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      dep += __shfl_xor_sync(0xffffffffu, dep, o);
-    }
-  }
-  if (lane == 0 && has_ray) {
     acc_out[ray] = acc;
     depth_out[ray] = dep;
     app_counts[ray] = n_app;
-    if (evaluated) atomicAdd(&s_evaluated, (int)evaluated);
   }
+  evaluated = __reduce_add_sync(0xffffffffu, evaluated);
+  if ((threadIdx.x & 31) == 0 && evaluated) atomicAdd(&s_evaluated, evaluated);
   __syncthreads();
   if (threadIdx.x == 0 && s_evaluated) atomicAdd(evaluated_total, s_evaluated);
 }
@@ -583,10 +603,10 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
                  cudaStream_t st) {
   PlaneSet set = make_set(m->den, m->cfg.n_pairs);
   const int J = m->den[0].C / 16;
-  const unsigned grid = (unsigned)((n + kBlock / 32 - 1) / (kBlock / 32));
+  const unsigned grid = (unsigned)((n + kMarchBlock - 1) / kMarchBlock);
   const float t_stop = m->cfg.ert_transmittance > 0.0f ? m->cfg.ert_transmittance : 0.0f;
 #define GNR_MARCH(JJ, NPP)                                                                                        \
-  march_kernel<JJ, NPP><<<grid, kBlock, 0, st>>>(                                                                 \
+  march_kernel<JJ, NPP><<<grid, kMarchBlock, 0, st>>>(                                                            \
       p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
