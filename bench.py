@@ -171,6 +171,8 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--app-fp16", type=int, default=0, choices=(0, 1),
+                    help="hold the appearance planes as fp16 in HBM (mlp_mode 2 only)")
     ap.add_argument("--ert", type=float, default=5e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
@@ -225,7 +227,7 @@ def main():
     spec, ckpt, pose = build_scene(a.workload, device)
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
-    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert)
+    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16))
     model.load(ckpt)
     cpu_sd = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
@@ -375,7 +377,7 @@ def main():
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": "2 streams" if not a.no_overlap else "none",
-                   "ert_transmittance": a.ert,
+                   "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,

@@ -50,7 +50,7 @@ typedef struct GnrConfig {
   int32_t hidden;           /* featureC (128)                                             */
   int32_t has_bias;         /* bias_enable                                                */
   int32_t mlp_mode;         /* 0 = fp32 CUDA-core MLP, 1 = tcgen05 split-precision MLP (fp32-grade),
-                               2 = tcgen05 single bf16 MLP (fast)                         */
+                               2 = tcgen05 MLP with single fp16 operands, fp32 accumulate (fast) */
   int32_t sampling_mode;    /* 0 = sample_ray (:244-281), 1 = sample_ray_within_hull (:283-319,
                                args.sampling_opt); mode 1 needs gnr_upload_hull_tables             */
   float ert_transmittance;  /* early ray termination of the fused density + weights pass: a ray stops
@@ -58,7 +58,10 @@ typedef struct GnrConfig {
                                (its rgb then differs from the unterminated result by less than the
                                value).  0 = never terminate (exact); negative = use the separate
                                density and weights kernels instead of the fused pass.             */
-  int32_t reserved[6];
+  int32_t app_storage;      /* 0 = appearance planes and lines held as fp32; 1 = held as fp16 (half the
+                               gather traffic; the products they feed are rounded to fp16 for the
+                               tensor cores anyway).  1 needs mlp_mode 2 and 33..48 appearance channels. */
+  int32_t reserved[5];
 } GnrConfig;
 
 /* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */

@@ -41,7 +41,8 @@ class GnrConfig(C.Structure):
         ("mlp_mode", C.c_int32),
         ("sampling_mode", C.c_int32),
         ("ert_transmittance", C.c_float),
-        ("reserved", C.c_int32 * 6),
+        ("app_storage", C.c_int32),
+        ("reserved", C.c_int32 * 5),
     ]
 
 

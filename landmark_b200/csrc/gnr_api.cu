@@ -1,5 +1,6 @@
 // C-ABI entry points: model lifetime, parameter upload / layout conversion, workspace layout,
 // the per-chunk forward and its stage-wise pieces.
+#include <cuda_fp16.h>
 #include <stdarg.h>
 #include <string.h>
 
@@ -101,6 +102,24 @@ __global__ void to_channel_last_kernel(const float* __restrict__ src, float* __r
   }
 }
 
+// Same, to fp16 (appearance planes with GnrConfig.app_storage == 1).
+__global__ void to_channel_last_half_kernel(const float* __restrict__ src, __half* __restrict__ dst, int C, int Cp, long long P) {
+  __shared__ float tile[32][33];
+  const long long p0 = (long long)blockIdx.x * 32;
+  const int c0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r;
+    const long long p = p0 + threadIdx.x;
+    tile[r][threadIdx.x] = (c < C && p < P) ? src[(long long)c * P + p] : 0.0f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const long long p = p0 + r;
+    const int c = c0 + threadIdx.x;
+    if (p < P && c < Cp) dst[p * Cp + c] = __float2half_rn(tile[threadIdx.x][r]);
+  }
+}
+
 __global__ void pack_bits_kernel(const uint8_t* __restrict__ vol, uint32_t* __restrict__ bits, long long n_vox, long long n_words) {
   long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (w >= n_words) return;
@@ -171,6 +190,12 @@ extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
   }
   if (cfg->sampling_mode != 0 && cfg->sampling_mode != 1) {
     gnr_set_error("gnr_create: sampling_mode %d (0 = dense, 1 = hull)", cfg->sampling_mode);
+    return -1;
+  }
+  if (cfg->app_storage != 0 &&
+      (cfg->app_storage != 1 || cfg->mlp_mode != 2 || cfg->n_app <= 32 || cfg->n_app > 48 || cfg->app_dim > 27)) {
+    gnr_set_error("gnr_create: app_storage %d: fp16 appearance planes need mlp_mode 2 (got %d) and 33..48 appearance channels (got %d)",
+                  cfg->app_storage, cfg->mlp_mode, cfg->n_app);
     return -1;
   }
   if (cfg->fea_pe < 0 || cfg->fea_pe > 8 || cfg->view_pe < 0 || cfg->view_pe > 8) {
@@ -269,9 +294,13 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
   free_dev(*buf);
   *buf = nullptr;
   const long long P = (long long)H * W;
-  GNR_CUDA_OK(cudaMalloc(buf, (size_t)P * Cp * sizeof(float)));
+  const bool half = kind == 1 && m->cfg.app_storage == 1;
+  GNR_CUDA_OK(cudaMalloc(buf, (size_t)P * Cp * (half ? sizeof(__half) : sizeof(float))));
   dim3 grid((unsigned)((P + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
-  to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, P);
+  if (half)
+    to_channel_last_half_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, reinterpret_cast<__half*>(*buf), C, Cp, P);
+  else
+    to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, P);
   GNR_CUDA_OK(cudaGetLastError());
   pl->plane = *buf;
   pl->H = H;
@@ -304,9 +333,14 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
   free_dev(*buf);
   *buf = nullptr;
-  GNR_CUDA_OK(cudaMalloc(buf, (size_t)Ln * Cp * sizeof(float)));
+  const bool half = kind == 1 && m->cfg.app_storage == 1;
+  GNR_CUDA_OK(cudaMalloc(buf, (size_t)Ln * Cp * (half ? sizeof(__half) : sizeof(float))));
   dim3 grid((unsigned)((Ln + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
-  to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, (long long)Ln);
+  if (half)
+    to_channel_last_half_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, reinterpret_cast<__half*>(*buf), C, Cp,
+                                                                          (long long)Ln);
+  else
+    to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, (long long)Ln);
   GNR_CUDA_OK(cudaGetLastError());
   pl->line = *buf;
   pl->L = Ln;

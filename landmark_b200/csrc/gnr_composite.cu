@@ -11,12 +11,6 @@ namespace {
 
 constexpr int kWarpsPerBlock = 8;
 
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-
 // One thread per ray, samples in order: the same operations in the same order as the fused
 // march kernel, so both give the same bits.
 __global__ void __launch_bounds__(128)
@@ -52,53 +46,80 @@ weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float
   app_counts[ray] = n_app;
 }
 
+// Order of the appearance list.  Rays are taken in groups of 32 consecutive rays (one warp, lane =
+// ray).  Group g owns positions app_offsets[32 g] .. app_offsets[32 g + 32) of the list (the
+// exclusive scan of the per-ray counts); inside the group the samples are ordered by rank first
+// and ray second: all first appearance samples of the group's rays, then all second ones, ...
+// With rays in tile order the 32 entries a warp of the gather or MLP kernel touches together are
+// then samples of neighbouring pixels at about the same depth, which read the same texels, and
+// their rows in the product tiles are consecutive.  app_group_walk yields, for rank j, the list
+// position of this lane's sample; both kernels below and nothing else define the order.
+struct AppGroupWalk {
+  long long pos;  // position of rank j of the group's first active ray
+  __device__ __forceinline__ bool step(int lane, bool has, long long& at) {
+    const uint32_t mask = __ballot_sync(0xffffffffu, has);
+    if (mask == 0u) return false;
+    at = pos + __popc(mask & ((1u << lane) - 1u));
+    pos += __popc(mask);
+    return true;
+  }
+};
+
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 expand_app_kernel(const float* __restrict__ weight, float thres, const int32_t* __restrict__ offsets,
-                  const int32_t* __restrict__ app_offsets, int64_t n_rays, long long capacity, long long app_capacity,
-                  int32_t* __restrict__ app_index) {
+                  const int32_t* __restrict__ app_counts, const int32_t* __restrict__ app_offsets, int64_t n_rays,
+                  long long capacity, long long app_capacity, int32_t* __restrict__ app_index) {
   const int lane = threadIdx.x & 31;
-  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (ray >= n_rays) return;
-  long long pos = app_offsets[ray], pend = app_offsets[ray + 1];
-  if (pos == pend) return;
-  long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
-  for (long long base = beg; base < end && pos < pend; base += 32) {
-    const long long i = base + lane;
-    const bool flag = (i < end) && (__ldg(weight + i) > thres);
-    const uint32_t bits = __ballot_sync(0xffffffffu, flag);
-    if (flag) {
-      const long long at = pos + __popc(bits & ((1u << lane) - 1u));
-      if (at < app_capacity) app_index[at] = (int32_t)i;
+  const int64_t group = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (group * 32 >= n_rays) return;
+  const int64_t ray = group * 32 + lane;
+  const bool has_ray = ray < n_rays;
+  int left = has_ray ? app_counts[ray] : 0;  // appearance samples this ray still has to place
+  long long i = has_ray ? offsets[ray] : 0;
+  const long long end = has_ray ? min((long long)offsets[ray + 1], capacity) : 0;
+  AppGroupWalk walk;
+  walk.pos = app_offsets[group * 32];
+  long long at;
+  while (walk.step(lane, left > 0, at)) {
+    if (left > 0) {
+      while (i < end && !(__ldg(weight + i) > thres)) ++i;  // the next sample with w > thres
+      if (i < end && at < app_capacity) app_index[at] = (int32_t)i;
+      ++i;
+      --left;
     }
-    pos += __popc(bits);
   }
 }
 
 // rgb_map = sum_j w_j rgb_j (+ 1 - acc), clamp to [0,1]; depth_map = sum w t
-// (app/models/gridnerf_sequential.py:493-501)
+// (app/models/gridnerf_sequential.py:493-501).  One thread per ray, ranks in order.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ app_offsets,
-                 const int32_t* __restrict__ app_index, const float* __restrict__ app_rgb, const float* __restrict__ acc,
-                 const float* __restrict__ depth, int64_t n_rays, long long app_capacity, int white_bg,
-                 float* __restrict__ rgb_map, float* __restrict__ depth_map) {
+composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ app_counts,
+                 const int32_t* __restrict__ app_offsets, const int32_t* __restrict__ app_index,
+                 const float* __restrict__ app_rgb, const float* __restrict__ acc, const float* __restrict__ depth,
+                 int64_t n_rays, long long app_capacity, int white_bg, float* __restrict__ rgb_map,
+                 float* __restrict__ depth_map) {
   const int lane = threadIdx.x & 31;
-  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
-  if (ray >= n_rays) return;
-  long long beg = app_offsets[ray], end = min((long long)app_offsets[ray + 1], app_capacity);
+  const int64_t group = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (group * 32 >= n_rays) return;
+  const int64_t ray = group * 32 + lane;
+  const bool has_ray = ray < n_rays;
+  int left = has_ray ? app_counts[ray] : 0;
   float r = 0.0f, g = 0.0f, b = 0.0f;
-  for (long long j = beg + lane; j < end; j += 32) {
-    const float w = __ldg(weight + __ldg(app_index + j));
-    const float* c = app_rgb + (size_t)j * 3;
-    r = fmaf(w, __ldg(c + 0), r);
-    g = fmaf(w, __ldg(c + 1), g);
-    b = fmaf(w, __ldg(c + 2), b);
+  AppGroupWalk walk;
+  walk.pos = app_offsets[group * 32];
+  long long at;
+  while (walk.step(lane, left > 0, at)) {
+    if (left > 0) {
+      if (at < app_capacity) {
+        const float w = __ldg(weight + __ldg(app_index + at));
+        r = fmaf(w, __ldg(app_rgb + at * 3 + 0), r);
+        g = fmaf(w, __ldg(app_rgb + at * 3 + 1), g);
+        b = fmaf(w, __ldg(app_rgb + at * 3 + 2), b);
+      }
+      --left;
+    }
   }
-  if (beg < end) {
-    r = warp_sum(r);
-    g = warp_sum(g);
-    b = warp_sum(b);
-  }
-  if (lane == 0) {
+  if (has_ray) {
     if (rgb_map) {
       const float bg = white_bg ? (1.0f - acc[ray]) : 0.0f;
       rgb_map[ray * 3 + 0] = fminf(fmaxf(r + bg, 0.0f), 1.0f);
@@ -128,9 +149,11 @@ int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, c
   int e = launch_exclusive_scan((const int32_t*)(ws + L.app_counts), app_offsets, (int32_t*)(ws + L.block_sums), n,
                                 (int32_t*)(ws + L.status), GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP, max_app, st);
   if (e) return e;
-  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const int64_t groups = (n + 31) / 32;
+  unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
   expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), m->cfg.ray_weight_thres,
-                                                           (const int32_t*)(ws + L.offsets), app_offsets, n,
+                                                           (const int32_t*)(ws + L.offsets),
+                                                           (const int32_t*)(ws + L.app_counts), app_offsets, n,
                                                            (long long)max_valid, (long long)max_app,
                                                            (int32_t*)(ws + L.app_index));
   return (int)cudaGetLastError();
@@ -139,10 +162,12 @@ int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, c
 int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
                      float* depth_map, cudaStream_t st) {
   (void)m;
-  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const int64_t groups = (n + 31) / 32;
+  unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
   long long app_capacity = L.max_app;
   composite_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
-      (const float*)(ws + L.weight), (const int32_t*)(ws + L.app_offsets), (const int32_t*)(ws + L.app_index),
+      (const float*)(ws + L.weight), (const int32_t*)(ws + L.app_counts), (const int32_t*)(ws + L.app_offsets),
+      (const int32_t*)(ws + L.app_index),
       (const float*)(ws + L.app_rgb), (const float*)(ws + L.acc), (const float*)(ws + L.depth), n, app_capacity,
       white_bg, rgb_map, depth_map);
   return (int)cudaGetLastError();

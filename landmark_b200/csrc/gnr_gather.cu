@@ -96,26 +96,73 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
   pair_products_tap<J>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), c4, prod);
 }
 
+// fp16 storage (48 channels, 96-byte texels): lane c4 owns channels 8 c4 .. 8 c4 + 7 (one 16-byte
+// load) and 32 + 4 c4 .. 32 + 4 c4 + 3 (one 8-byte load); prod[0], prod[1] are the first eight,
+// prod[2] the last four.  Interpolation and product are in fp32 as in pair_products_tap.
+__device__ __forceinline__ void load_texel_h48(const unsigned char* base, uint32_t texel, int c4, float4 (&v)[3]) {
+  const unsigned char* t = base + (size_t)texel * 96u;
+  const uint4 a = __ldg(reinterpret_cast<const uint4*>(t) + c4);
+  const uint2 b = __ldg(reinterpret_cast<const uint2*>(t + 64) + c4);
+  const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+  const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&a.z)), a3 = __half22float2(*reinterpret_cast<const __half2*>(&a.w));
+  const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x)), b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
+  v[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
+  v[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
+  v[2] = make_float4(b0.x, b0.y, b1.x, b1.y);
+}
+
+__device__ __forceinline__ void pair_products_tap_h48(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, int c4, float4 (&prod)[3]) {
+  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
+  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
+  const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
+  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0;
+  const unsigned char* pb = reinterpret_cast<const unsigned char*>(pl.plane);
+  const unsigned char* lb = reinterpret_cast<const unsigned char*>(pl.line);
+  float4 v_nw[3], v_ne[3], v_sw[3], v_se[3], v_l0[3], v_l1[3];
+  load_texel_h48(pb, nw, c4, v_nw);
+  load_texel_h48(pb, nw + 1u, c4, v_ne);
+  load_texel_h48(pb, nw + (uint32_t)pl.W, c4, v_sw);
+  load_texel_h48(pb, nw + (uint32_t)pl.W + 1u, c4, v_se);
+  load_texel_h48(lb, (uint32_t)tl.i0, c4, v_l0);
+  load_texel_h48(lb, (uint32_t)tl.i0 + 1u, c4, v_l1);
+#pragma unroll
+  for (int j = 0; j < 3; ++j) {
+    float4 pv = f4_scale(v_nw[j], w_nw);
+    pv = f4_fma(v_ne[j], w_ne, pv);
+    pv = f4_fma(v_sw[j], w_sw, pv);
+    pv = f4_fma(v_se[j], w_se, pv);
+    const float4 lv = f4_fma(v_l1[j], al1, f4_scale(v_l0[j], al0));
+    prod[j] = f4_mul(pv, lv);
+  }
+}
+
 // The three plane/line pairs of one sample.  NP == 3 is the standard VM layout (pairs
 // (x,y|z), (x,z|y), (y,z|x) on one grid, verified by the host): its nine coordinate lookups
 // collapse into three.  NP == 0 walks planes.n pairs generically.
-template <int J, int NP, class F>
+template <int J, int NP, bool HALF = false, class F>
 __device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, float y, float z, int c4, F&& f) {
+  static_assert(!HALF || J == 3, "fp16 storage is implemented for 48 channels");
+  auto one = [&](const GnrPlane& pl, Tap ta, Tap tb, Tap tl, float4(&prod)[J]) {
+    if constexpr (HALF) pair_products_tap_h48(pl, ta, tb, tl, c4, prod);
+    else pair_products_tap<J>(pl, ta, tb, tl, c4, prod);
+  };
   if (NP == 3) {
     const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
     const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
     const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
     float4 prod[J];
-    pair_products_tap<J>(planes.p[0], tx, ty, tz, c4, prod);
+    one(planes.p[0], tx, ty, tz, prod);
     f(0, prod);
-    pair_products_tap<J>(planes.p[1], tx, tz, ty, c4, prod);
+    one(planes.p[1], tx, tz, ty, prod);
     f(1, prod);
-    pair_products_tap<J>(planes.p[2], ty, tz, tx, c4, prod);
+    one(planes.p[2], ty, tz, tx, prod);
     f(2, prod);
   } else {
     for (int pi = 0; pi < planes.n; ++pi) {
+      const GnrPlane& pl = planes.p[pi];
+      const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
       float4 prod[J];
-      pair_products<J>(planes.p[pi], x, y, z, c4, prod);
+      one(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), prod);
       f(pi, prod);
     }
   }
@@ -291,7 +338,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
 // (and, with a white background, taken from rgb) is bounded by the transmittance at the stop,
 // i.e. by t_stop.  With t_stop == 0 the weights are bit-identical to density_kernel followed by
 // weights_kernel.
-constexpr int kMarchBlock = 128;
+constexpr int kMarchBlock = 32;  // one warp per CTA: a finished warp frees its slot at once
 
 template <int J, int NP>
 __global__ void __launch_bounds__(kMarchBlock)
@@ -420,7 +467,9 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, const float
 // One more 16-byte group per row, after the products (k group `view_group`), carries the
 // sample's view direction for the MLP kernel as fp16 pairs {hi x, hi y, hi z, lo x, lo y, lo z}:
 // hi + lo restores the fp32 value to about 2^-22, and the MLP kernel needs no list lookups.
-template <int J, int NP, int TA>
+// HALF: the planes are held as fp16 (load_texel_h48) and the lane's twelve channels are
+// 8 c4 .. 8 c4 + 7 and 32 + 4 c4 .. + 3: one 16-byte and one 8-byte store per pair.
+template <int J, int NP, int TA, bool HALF = false>
 __global__ void __launch_bounds__(kBlock)
 app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
                     unsigned char* __restrict__ prod_lo, int tile_bytes, int view_group) {
@@ -448,7 +497,24 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
       vv.w = 0u;
       *reinterpret_cast<uint4*>(prod_hi + (size_t)tile * tile_bytes + (size_t)view_group * 2048 + (size_t)row * 16) = vv;
     }
-    for_each_pair<J, NP>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
+    for_each_pair<J, NP, HALF>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
+      if constexpr (HALF) {
+        unsigned char* row_base = prod_hi + (size_t)tile * tile_bytes + (size_t)row * 16;
+        const __half2 h0 = __floats2half2_rn(prod[0].x, prod[0].y), h1 = __floats2half2_rn(prod[0].z, prod[0].w);
+        const __half2 h2 = __floats2half2_rn(prod[1].x, prod[1].y), h3 = __floats2half2_rn(prod[1].z, prod[1].w);
+        const __half2 h4 = __floats2half2_rn(prod[2].x, prod[2].y), h5 = __floats2half2_rn(prod[2].z, prod[2].w);
+        uint4 va;
+        va.x = *reinterpret_cast<const uint32_t*>(&h0);
+        va.y = *reinterpret_cast<const uint32_t*>(&h1);
+        va.z = *reinterpret_cast<const uint32_t*>(&h2);
+        va.w = *reinterpret_cast<const uint32_t*>(&h3);
+        uint2 vb;
+        vb.x = *reinterpret_cast<const uint32_t*>(&h4);
+        vb.y = *reinterpret_cast<const uint32_t*>(&h5);
+        *reinterpret_cast<uint4*>(row_base + (size_t)(pi * 6 + c4) * 2048) = va;
+        *reinterpret_cast<uint2*>(row_base + (size_t)(pi * 6 + 4 + (c4 >> 1)) * 2048 + (size_t)(c4 & 1) * 8) = vb;
+        return;
+      }
 #pragma unroll
       for (int j = 0; j < J; ++j) {
         const size_t at = out0 + (size_t)(pi * 2 * J + 2 * j + (c4 >> 1)) * 2048;
@@ -468,6 +534,109 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
         }
       }
     });
+  }
+}
+
+// The same for 48 channels with one thread per sample.  Consecutive list entries are samples of
+// neighbouring rays at the same rank (see the order of the appearance list), so the 32 lanes of a
+// load read a few texels between them, and their rows in the tile are consecutive: every store
+// instruction writes 512 contiguous bytes.  A thread takes the 48 channels of a pair in six rounds
+// of 8: six 256-bit loads (128-bit with fp16 storage), the fp32 interpolation and product of
+// pair_products_tap, and one 16-byte store, which is exactly one k group of its row.
+constexpr int kThreadBlock = 128;
+
+template <bool HALF>
+__device__ __forceinline__ void load8(const void* base, uint32_t texel, int h, float4& lo, float4& hi) {
+  if constexpr (HALF) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned char*>(base) + (size_t)texel * 96u) + h);
+    const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+    const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&a.z)), a3 = __half22float2(*reinterpret_cast<const __half2*>(&a.w));
+    lo = make_float4(a0.x, a0.y, a1.x, a1.y);
+    hi = make_float4(a2.x, a2.y, a3.x, a3.y);
+  } else {
+    const F8 v = ldg8(reinterpret_cast<const float*>(base) + (size_t)texel * 48u + 8 * h);
+    lo = v.lo;
+    hi = v.hi;
+  }
+}
+
+template <bool HALF>
+__device__ __forceinline__ void pair_products_thread48(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, unsigned char* out) {
+  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
+  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
+  const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
+  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0, sw = nw + (uint32_t)pl.W;
+  const uint32_t seg = (uint32_t)tl.i0;
+#pragma unroll
+  for (int h = 0; h < 6; ++h) {
+    float4 nwl, nwh, nel, neh, swl, swh, sel, seh, l0l, l0h, l1l, l1h;
+    load8<HALF>(pl.plane, nw, h, nwl, nwh);
+    load8<HALF>(pl.plane, nw + 1u, h, nel, neh);
+    load8<HALF>(pl.plane, sw, h, swl, swh);
+    load8<HALF>(pl.plane, sw + 1u, h, sel, seh);
+    load8<HALF>(pl.line, seg, h, l0l, l0h);
+    load8<HALF>(pl.line, seg + 1u, h, l1l, l1h);
+    float4 pa = f4_scale(nwl, w_nw), pb = f4_scale(nwh, w_nw);
+    pa = f4_fma(nel, w_ne, pa);
+    pb = f4_fma(neh, w_ne, pb);
+    pa = f4_fma(swl, w_sw, pa);
+    pb = f4_fma(swh, w_sw, pb);
+    pa = f4_fma(sel, w_se, pa);
+    pb = f4_fma(seh, w_se, pb);
+    const float4 la = f4_fma(l1l, al1, f4_scale(l0l, al0)), lb = f4_fma(l1h, al1, f4_scale(l0h, al0));
+    const float4 qa = f4_mul(pa, la), qb = f4_mul(pb, lb);
+    const __half2 h0 = __floats2half2_rn(qa.x, qa.y), h1 = __floats2half2_rn(qa.z, qa.w);
+    const __half2 h2 = __floats2half2_rn(qb.x, qb.y), h3 = __floats2half2_rn(qb.z, qb.w);
+    uint4 v;
+    v.x = *reinterpret_cast<const uint32_t*>(&h0);
+    v.y = *reinterpret_cast<const uint32_t*>(&h1);
+    v.z = *reinterpret_cast<const uint32_t*>(&h2);
+    v.w = *reinterpret_cast<const uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(out + (size_t)h * 2048) = v;
+  }
+}
+
+template <int NP, bool HALF>
+__global__ void __launch_bounds__(kThreadBlock)
+app_products_thread_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
+                           int tile_bytes, int view_group) {
+  const long long total = coords_total(crd);
+  // contiguous share of the list per CTA, in steps of kThreadBlock entries
+  const long long steps = (total + kThreadBlock - 1) / kThreadBlock;
+  const long long per = (steps + gridDim.x - 1) / gridDim.x;
+  const long long range_beg = min(total, (long long)blockIdx.x * per * kThreadBlock);
+  const long long range_end = min(total, range_beg + per * kThreadBlock);
+  for (long long j = range_beg + threadIdx.x; j < range_end; j += kThreadBlock) {
+    float x, y, z, view[3];
+    sample_xyz(p, crd, j, x, y, z, view);
+    unsigned char* row = prod_hi + (size_t)(j >> 7) * tile_bytes + (size_t)(j & 127) * 16;
+    {
+      const __half hx = __float2half_rn(view[0]), hy = __float2half_rn(view[1]), hz = __float2half_rn(view[2]);
+      const __half2 a = __halves2half2(hx, hy);
+      const __half2 b = __halves2half2(hz, __float2half_rn(view[0] - __half2float(hx)));
+      const __half2 c = __floats2half2_rn(view[1] - __half2float(hy), view[2] - __half2float(hz));
+      uint4 vv;
+      vv.x = *reinterpret_cast<const uint32_t*>(&a);
+      vv.y = *reinterpret_cast<const uint32_t*>(&b);
+      vv.z = *reinterpret_cast<const uint32_t*>(&c);
+      vv.w = 0u;
+      *reinterpret_cast<uint4*>(row + (size_t)view_group * 2048) = vv;
+    }
+    if (NP == 3) {
+      const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+      const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+      const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+      pair_products_thread48<HALF>(planes.p[0], tx, ty, tz, row);
+      pair_products_thread48<HALF>(planes.p[1], tx, tz, ty, row + 6 * 2048);
+      pair_products_thread48<HALF>(planes.p[2], ty, tz, tx, row + 12 * 2048);
+    } else {
+      for (int pi = 0; pi < planes.n; ++pi) {
+        const GnrPlane& pl = planes.p[pi];
+        const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+        pair_products_thread48<HALF>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L),
+                                     row + (size_t)pi * 6 * 2048);
+      }
+    }
   }
 }
 
@@ -551,6 +720,10 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords&
 
 int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, float* feat,
                       cudaStream_t st) {
+  if (m->cfg.app_storage != 0) {
+    gnr_set_error("the CUDA-core appearance gather reads fp32 planes; this model holds them as fp16 (app_storage 1)");
+    return -1;
+  }
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
@@ -577,7 +750,23 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
   const int J = m->app[0].C / 16;
   const int grid = m->sm_count * 4;
 #define GNR_PRD(JJ, NPP, TT) app_products_kernel<JJ, NPP, TT><<<grid, kBlock, 0, st>>>(p, set, c, hi, lo, tile_bytes, m->mlp.n_prod / 8)
-  if (J == 3 && standard_vm3(set)) {
+  if (m->cfg.app_storage == 1 && (J != 3 || terms != 1)) {
+    gnr_set_error("fp16 appearance planes need 48 (padded) channels and mlp_mode 2");
+    return -1;
+  }
+  if (J == 3 && terms == 1 && m->cfg.app_storage == 1) {
+    // fp16 storage: one thread per sample; fp32 storage below: four lanes per sample, which the L1
+    // serves better when every load instruction moves 16 bytes per lane
+    const int tgrid = m->sm_count * 8;
+    const bool vm3 = standard_vm3(set), half = m->cfg.app_storage == 1;
+#define GNR_PRT(NPP, HH) \
+  app_products_thread_kernel<NPP, HH><<<tgrid, kThreadBlock, 0, st>>>(p, set, c, hi, tile_bytes, m->mlp.n_prod / 8)
+    if (vm3 && half) GNR_PRT(3, true);
+    else if (vm3) GNR_PRT(3, false);
+    else if (half) GNR_PRT(0, true);
+    else GNR_PRT(0, false);
+#undef GNR_PRT
+  } else if (J == 3 && standard_vm3(set)) {
     if (terms == 2) GNR_PRD(3, 3, 2); else GNR_PRD(3, 3, 1);
   } else if (J == 1) {
     if (terms == 2) GNR_PRD(1, 0, 2); else GNR_PRD(1, 0, 1);

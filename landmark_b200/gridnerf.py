@@ -107,6 +107,7 @@ class B200GridNeRF(torch.nn.Module):
         mlp_mode: int = 0,
         field_grid=None,
         ert_transmittance: float = 0.0,
+        app_plane_fp16: bool = False,
         **_ignored,
     ):
         super().__init__()
@@ -152,6 +153,8 @@ class B200GridNeRF(torch.nn.Module):
         self.mlp_mode = int(mlp_mode)
         # early ray termination of the density pass (see GnrConfig.ert_transmittance); 0 = exact
         self.ert_transmittance = float(ert_transmittance)
+        # appearance planes and lines held as fp16 in the library (GnrConfig.app_storage); mlp_mode 2 only
+        self.app_plane_fp16 = bool(app_plane_fp16)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -284,6 +287,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.mlp_mode = self.mlp_mode
         cfg.sampling_mode = 1 if self.sampling_opt else 0
         cfg.ert_transmittance = self.ert_transmittance
+        cfg.app_storage = 1 if self.app_plane_fp16 else 0
         return cfg
 
     def commit(self, release_torch_planes: bool = False):

@@ -19,13 +19,13 @@ def oracle_field(spec, ckpt=None):
     return orc.field_from_checkpoint(ckpt, spec.alpha_filter_thres), ckpt
 
 
-def cuda_model(spec, ckpt=None, mlp_mode=0, device="cuda:0"):
+def cuda_model(spec, ckpt=None, mlp_mode=0, device="cuda:0", **extra):
     from landmark_b200.gridnerf import B200GridNeRF
 
     ckpt = ckpt or scenes.make_checkpoint(spec)
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
-    model = B200GridNeRF(**kwargs, mlp_mode=mlp_mode)
+    model = B200GridNeRF(**kwargs, mlp_mode=mlp_mode, **extra)
     model.load(ckpt)
     return model
 

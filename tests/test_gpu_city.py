@@ -53,7 +53,7 @@ def test_reference_slices_exact_indices_and_rgb(city):
     assert (got["depth_map"].cpu() - torch.from_numpy(fx["depth_map"])).abs().max().item() <= 1e-4
 
 
-@pytest.mark.parametrize("mlp_mode", [0, 2])
+@pytest.mark.parametrize("mlp_mode", [0, 2, "2+fp16 planes"])
 def test_random_frame_subset_vs_oracle(city, mlp_mode):
     spec, field, model, rays, fx = city
     g = torch.Generator().manual_seed(1234)
@@ -79,7 +79,10 @@ def _second_model(city, mlp_mode):
     spec, field, model, rays, fx = city
     if mlp_mode not in _models:
         ckpt = scenes.make_checkpoint(spec)
-        m = cuda_model(spec, ckpt, mlp_mode=mlp_mode)
+        if mlp_mode == "2+fp16 planes":  # appearance planes held as fp16 in HBM
+            m = cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True)
+        else:
+            m = cuda_model(spec, ckpt, mlp_mode=mlp_mode)
         m.release_torch_planes()
         _models[mlp_mode] = m
     return _models[mlp_mode]

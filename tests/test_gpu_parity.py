@@ -419,3 +419,24 @@ def test_encode_app_latent_matches_reference_fixture():
         assert (other["rgb_map"] - out["rgb_map"]).abs().max().item() > 1e-2
         again, _ = model(rays, app_code=code, N_samples=spec.n_samples)  # ... and switching back restores it
         assert torch.equal(again["rgb_map"], out["rgb_map"])
+
+
+def test_fp16_appearance_planes_stay_inside_the_bar():
+    """app_plane_fp16: the appearance planes and lines are rounded to fp16 once at upload (mlp_mode 2,
+    whose tensor-core operands are fp16 anyway).  Indices do not change; rgb stays within 1e-4 of
+    the reference fixture and within 5e-5 of the fp32-plane render of the same mode."""
+    spec = scenes.tiny_spec().lit()
+    fx = load_golden("tiny_lit.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    rays = torch.from_numpy(fx["rays"]).cuda()
+    full = cuda_model(spec, ckpt, mlp_mode=2)
+    half = cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True)
+    a, _ = full(rays, N_samples=spec.n_samples)
+    b, _ = half(rays, N_samples=spec.n_samples)
+    assert int(half.last_status[2]) == int(full.last_status[2]) and int(half.last_status[3]) == int(full.last_status[3])
+    assert torch.equal(a["depth_map"], b["depth_map"])
+    assert 0.0 < (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 5e-5
+    err = (b["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+    with pytest.raises(RuntimeError, match="mlp_mode 2"):
+        cuda_model(spec, ckpt, mlp_mode=0, app_plane_fp16=True)
