@@ -177,6 +177,7 @@ def main():
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
+    ap.add_argument("--streams", type=int, default=2, help="streams the chunks of a frame rotate over")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
     ap.add_argument("--profile-case", type=int, default=0, metavar="RAYS",
                     help="render one chunk of RAYS rays from the middle of the frame twice and exit "
@@ -210,7 +211,7 @@ def main():
                     "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                     "dtype": "f32 + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
                     "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "parallelism": res["parallelism"],
-                               "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": "2 streams" if not a.no_overlap else "none",
+                               "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "grid_scale": a.grid_scale,
                                "l2": "inputs larger than L2"},
                     "ms_per_frame": res["ms_per_frame"], "clocks": clocks,
@@ -259,7 +260,7 @@ def main():
     depth = torch.zeros((n_pad,), dtype=torch.float32, device=device)
     image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
 
-    def step(overlap=not a.no_overlap):
+    def step(overlap=(0 if a.no_overlap else a.streams)):
         model.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb[:n_local], depth_out=depth[:n_local], overlap=overlap)
         shard.assemble(rgb, image)
 
@@ -376,7 +377,7 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (gathers, compositing) + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
-                   "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": "2 streams" if not a.no_overlap else "none",
+                   "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,

@@ -242,6 +242,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
     free_dev(m->app_line_buf[i]);
   }
   free_dev(m->alpha_bits);
+  free_dev(m->alpha_coarse);
   free_dev(m->hull_near_term);
   free_dev(m->hull_u);
   free_dev(m->mlp.basis_blocked);
@@ -349,6 +350,30 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   return 0;
 }
 
+// Coarse occupancy: block (bx, by, bz) covers mask cells [4 b, 4 b + 4] on each axis (its own 4 and
+// the first cell of the next block: a trilinear test whose lower corner lies in the block reads
+// those).  A clear bit therefore proves that the fine test of any such sample sums to zero.
+__global__ void coarse_bits_kernel(const uint32_t* __restrict__ bits, int D, int H, int W, int cD, int cH, int cW,
+                                   uint32_t* __restrict__ coarse) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const bool in_range = c < (long long)cD * cH * cW;
+  bool any = false;
+  if (in_range) {
+    const int bx = (int)(c % cW), by = (int)((c / cW) % cH), bz = (int)(c / ((long long)cW * cH));
+    for (int z = 4 * bz; z <= 4 * bz + 4 && z < D && !any; ++z)
+      for (int y = 4 * by; y <= 4 * by + 4 && y < H && !any; ++y)
+        for (int x = 4 * bx; x <= 4 * bx + 4 && x < W; ++x) {
+          const uint32_t bit = (uint32_t)(((long long)z * H + y) * W + x);
+          if ((bits[bit >> 5] >> (bit & 31)) & 1u) {
+            any = true;
+            break;
+          }
+        }
+  }
+  const uint32_t word = __ballot_sync(0xffffffffu, any);  // 32 consecutive blocks = one word
+  if ((threadIdx.x & 31) == 0 && c < (((long long)cD * cH * cW + 31) / 32) * 32) coarse[c >> 5] = word;
+}
+
 extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, const float* aabb_h,
                                      const float* inv_size_h, void* stream) {
   if (!m) {
@@ -357,7 +382,8 @@ extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int
   }
   DeviceGuard g(m->device);
   free_dev(m->alpha_bits);
-  m->alpha_bits = nullptr;
+  free_dev(m->alpha_coarse);
+  m->alpha_bits = m->alpha_coarse = nullptr;
   m->aD = m->aH = m->aW = 0;
   if (!vol) return 0;
   if (D < 1 || H < 1 || W < 1 || !aabb_h || !inv_size_h || (long long)D * H * W > 0xffffffffLL) {
@@ -368,6 +394,14 @@ extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int
   GNR_CUDA_OK(cudaMalloc(&m->alpha_bits, (size_t)n_words * sizeof(uint32_t)));
   pack_bits_kernel<<<(unsigned)((n_words + 255) / 256), 256, 0, (cudaStream_t)stream>>>(vol, m->alpha_bits, n_vox, n_words);
   GNR_CUDA_OK(cudaGetLastError());
+  {
+    const int cD = (D + 3) / 4, cH = (H + 3) / 4, cW = (W + 3) / 4;
+    const long long n_blocks = (long long)cD * cH * cW, n_cwords = (n_blocks + 31) / 32;
+    GNR_CUDA_OK(cudaMalloc(&m->alpha_coarse, (size_t)n_cwords * sizeof(uint32_t)));
+    coarse_bits_kernel<<<(unsigned)((n_cwords * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(m->alpha_bits, D, H, W, cD, cH,
+                                                                                            cW, m->alpha_coarse);
+    GNR_CUDA_OK(cudaGetLastError());
+  }
   m->aD = D;
   m->aH = H;
   m->aW = W;
@@ -506,6 +540,10 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
   p.aW = m->aW;
   p.has_mask = m->alpha_bits != nullptr;
   p.a_bits = m->alpha_bits;
+  p.a_coarse = m->alpha_coarse;
+  p.cD = (m->aD + 3) / 4;
+  p.cH = (m->aH + 3) / 4;
+  p.cW = (m->aW + 3) / 4;
   p.S = S;
   p.words = (S + 31) / 32;
   p.kbits = gnr_sample_bits(S);

@@ -52,6 +52,7 @@ struct GnrModel {
   float* app_line_buf[GNR_MAX_PLANES];
   // occupancy bits
   uint32_t* alpha_bits;
+  uint32_t* alpha_coarse;  // one bit per 4x4x4 block of mask cells (see coarse_bits_kernel)
   int aD, aH, aW;
   float a_lo[3], a_inv[3];
   GnrMlp mlp;
@@ -81,6 +82,8 @@ struct GnrSampleParams {
   int aD, aH, aW;
   int has_mask;
   const uint32_t* a_bits;
+  const uint32_t* a_coarse;  // null, or 1 bit per 4x4x4 block: set if any cell of the block or of its +1 border is set
+  int cD, cH, cW;
   int S, words, kbits;
   int mode;                 // 0 dense sampler, 1 hull sampler
   const float* hull_a;      // near * (1 - u[k])

@@ -38,37 +38,52 @@ __global__ void raygen_kernel(Pose pose, const float* __restrict__ dir_x, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// sampling: one warp per ray, 32 samples per step, validity bits kept in registers
+// sampling: one thread per ray, samples in order, 32 validity bits per register word
 // ---------------------------------------------------------------------------------------------
+// AlphaGridMask.sample_alpha (app/models/alpha_mask.py:35-59): trilinear interpolation of the 0/1
+// volume with zero padding, then `> threshold`.  The sum runs over the corners in grid_sample's
+// order with individually rounded operations.  Two exact shortcuts come first: a clear bit of the
+// coarse grid proves that all eight corners are empty (threshold >= 0 then fails), and with a
+// threshold of exactly zero the sum of non-negative weights is positive as soon as one occupied
+// corner has a positive weight, so the loop can stop there.
 __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float px, float py, float pz) {
   // q = (p - aabb0) * invgridSize - 1 ; index = ((q + 1) / 2) * (size - 1)
-  float ix = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(px, p.a_lo[0], p.a_inv[0]), 1.0f), 0.5f), (float)(p.aW - 1));
-  float iy = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(py, p.a_lo[1], p.a_inv[1]), 1.0f), 0.5f), (float)(p.aH - 1));
-  float iz = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(pz, p.a_lo[2], p.a_inv[2]), 1.0f), 0.5f), (float)(p.aD - 1));
-  float fx0 = floorf(ix), fy0 = floorf(iy), fz0 = floorf(iz);
-  float fx1 = __fadd_rn(fx0, 1.0f), fy1 = __fadd_rn(fy0, 1.0f), fz1 = __fadd_rn(fz0, 1.0f);
-  float wx[2] = {__fsub_rn(fx1, ix), __fsub_rn(ix, fx0)};
-  float wy[2] = {__fsub_rn(fy1, iy), __fsub_rn(iy, fy0)};
-  float wz[2] = {__fsub_rn(fz1, iz), __fsub_rn(iz, fz0)};
+  const float ix = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(px, p.a_lo[0], p.a_inv[0]), 1.0f), 0.5f), (float)(p.aW - 1));
+  const float iy = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(py, p.a_lo[1], p.a_inv[1]), 1.0f), 0.5f), (float)(p.aH - 1));
+  const float iz = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(pz, p.a_lo[2], p.a_inv[2]), 1.0f), 0.5f), (float)(p.aD - 1));
   // corners outside the volume contribute zero (padding_mode="zeros"); indices that do not
   // fit an int (only possible for samples far outside the mask box) are outside too.
-  bool okx = (ix >= -1.0f) && (ix < (float)p.aW), oky = (iy >= -1.0f) && (iy < (float)p.aH),
-       okz = (iz >= -1.0f) && (iz < (float)p.aD);
+  const bool okx = (ix >= -1.0f) && (ix < (float)p.aW), oky = (iy >= -1.0f) && (iy < (float)p.aH),
+             okz = (iz >= -1.0f) && (iz < (float)p.aD);
   if (!(okx && oky && okz)) return 0.0f > p.a_thres;
-  int x0 = (int)fx0, y0 = (int)fy0, z0 = (int)fz0;
+  const float fx0 = floorf(ix), fy0 = floorf(iy), fz0 = floorf(iz);
+  const int x0 = (int)fx0, y0 = (int)fy0, z0 = (int)fz0;
+  if (p.a_coarse != nullptr && p.a_thres >= 0.0f && x0 >= 0 && y0 >= 0 && z0 >= 0) {
+    const uint32_t cb = (uint32_t)(((z0 >> 2) * p.cH + (y0 >> 2)) * p.cW + (x0 >> 2));
+    if (!((__ldg(p.a_coarse + (cb >> 5)) >> (cb & 31)) & 1u)) return false;
+  }
+  const float fx1 = __fadd_rn(fx0, 1.0f), fy1 = __fadd_rn(fy0, 1.0f), fz1 = __fadd_rn(fz0, 1.0f);
+  const float wx[2] = {__fsub_rn(fx1, ix), __fsub_rn(ix, fx0)};
+  const float wy[2] = {__fsub_rn(fy1, iy), __fsub_rn(iy, fy0)};
+  const float wz[2] = {__fsub_rn(fz1, iz), __fsub_rn(iz, fz0)};
+  const bool stop_at_first = p.a_thres == 0.0f;
   float out = 0.0f;
 #pragma unroll
   for (int cz = 0; cz < 2; ++cz) {
 #pragma unroll
     for (int cy = 0; cy < 2; ++cy) {
+      const int y = y0 + cy, z = z0 + cz;
+      if ((unsigned)y >= (unsigned)p.aH || (unsigned)z >= (unsigned)p.aD) continue;
+      const uint32_t row = (uint32_t)((z * p.aH + y) * p.aW);
 #pragma unroll
       for (int cx = 0; cx < 2; ++cx) {
-        int x = x0 + cx, y = y0 + cy, z = z0 + cz;
-        if ((unsigned)x < (unsigned)p.aW && (unsigned)y < (unsigned)p.aH && (unsigned)z < (unsigned)p.aD) {
-          uint32_t bit = (uint32_t)((z * p.aH + y) * p.aW + x);
+        const int x = x0 + cx;
+        if ((unsigned)x < (unsigned)p.aW) {
+          const uint32_t bit = row + (uint32_t)x;
           if ((__ldg(p.a_bits + (bit >> 5)) >> (bit & 31)) & 1u) {
-            float w = __fmul_rn(__fmul_rn(wx[cx], wy[cy]), wz[cz]);
+            const float w = __fmul_rn(__fmul_rn(wx[cx], wy[cy]), wz[cz]);
             out = __fadd_rn(out, w);  // tap is exactly 1, so tap * w == w
+            if (stop_at_first && w > 0.0f) return true;
           }
         }
       }
@@ -77,22 +92,23 @@ __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float p
   return out > p.a_thres;
 }
 
-__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+constexpr int kSampleBlock = 128;
+
+__global__ void __launch_bounds__(kSampleBlock)
 sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_rays, float* __restrict__ t_min_out,
                    uint32_t* __restrict__ words_out, int32_t* __restrict__ counts_out) {
-  const int lane = threadIdx.x & 31;
-  int64_t ray = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  const int64_t ray = (int64_t)blockIdx.x * kSampleBlock + threadIdx.x;
   if (ray >= n_rays) return;
   const float* r = rays + ray * 6;
-  float o[3] = {__ldg(r), __ldg(r + 1), __ldg(r + 2)};
-  float d[3] = {__ldg(r + 3), __ldg(r + 4), __ldg(r + 5)};
+  const float o[3] = {__ldg(r), __ldg(r + 1), __ldg(r + 2)};
+  const float d[3] = {__ldg(r + 3), __ldg(r + 4), __ldg(r + 5)};
   // slab entry: max over axes of min(rate_a, rate_b), clamped to [near, far]
   float t_min = -INFINITY;
 #pragma unroll
   for (int a = 0; a < 3; ++a) {
-    float vec = (d[a] == 0.0f) ? 1e-6f : d[a];
-    float ra = __fdiv_rn(__fsub_rn(p.hi[a], o[a]), vec);
-    float rb = __fdiv_rn(__fsub_rn(p.lo[a], o[a]), vec);
+    const float vec = (d[a] == 0.0f) ? 1e-6f : d[a];
+    const float ra = __fdiv_rn(__fsub_rn(p.hi[a], o[a]), vec);
+    const float rb = __fdiv_rn(__fsub_rn(p.lo[a], o[a]), vec);
     t_min = fmaxf(t_min, fminf(ra, rb));
   }
   t_min = fminf(fmaxf(t_min, p.near_t), p.far_t);
@@ -102,44 +118,44 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
     const float far = -__fdiv_rn(__fsub_rn(o[2], p.lo[2]), d[2]);
     t_min = (d[2] >= 0.0f) ? p.far_t : far;
   }
-  if (lane == 0) t_min_out[ray] = t_min;
+  t_min_out[ray] = t_min;
 
   int count = 0;
   uint32_t* wrow = words_out + ray * p.words;
   // fl(o + fl(d * fl(t_min + fl(step * k)))) is monotone in k, so once a sample has left the
   // box through the far side of an axis every later sample is outside as well.
+  // (The hull sampler's distances are a sum of a falling and a rising term and need not be
+  // monotone to the last bit, so only the dense sampler stops at the first exit.)
   bool done = false;
-  for (int base = 0; base < p.words; base += 32) {
-    uint32_t my_word = 0;  // lane w keeps word base + w
-    int nw = min(32, p.words - base);
-    for (int w = 0; w < nw; ++w) {
-      uint32_t bits = 0;
-      if (!done) {
-        int k = (base + w) * 32 + lane;
-        float t = gnr_sample_t(p, t_min, min(k, p.S - 1));
-        float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
-        bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
-        bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
-        bool inside = !(lo_out | hi_out) && (k < p.S);
-        bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
-                      ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
-                      ((d[2] > 0.0f) & (pz > p.hi[2])) | ((d[2] < 0.0f) & (p.lo[2] > pz)) |
-                      ((d[0] == 0.0f) & ((p.lo[0] > px) | (px > p.hi[0]))) |
-                      ((d[1] == 0.0f) & ((p.lo[1] > py) | (py > p.hi[1]))) |
-                      ((d[2] == 0.0f) & ((p.lo[2] > pz) | (pz > p.hi[2])));
-        bool valid = inside;
-        if (valid && p.has_mask) valid = occupancy_test(p, px, py, pz);
-        bits = __ballot_sync(0xffffffffu, valid);
-        // (the hull sampler's distances are a sum of a falling and a rising term and need not be
-        // monotone to the last bit, so only the dense sampler stops at the first exit)
-        done = (p.mode == 0) && __any_sync(0xffffffffu, exited);
-        count += __popc(bits);
+  for (int w = 0; w < p.words; ++w) {
+    uint32_t bits = 0;
+    if (!done) {
+      const int k_end = min(32, p.S - w * 32);
+      for (int b = 0; b < k_end; ++b) {
+        const float t = gnr_sample_t(p, t_min, w * 32 + b);
+        const float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
+        const bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
+        const bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
+        if (!(lo_out | hi_out)) {
+          if (!p.has_mask || occupancy_test(p, px, py, pz)) bits |= 1u << b;
+        } else if (p.mode == 0) {
+          const bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
+                              ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
+                              ((d[2] > 0.0f) & (pz > p.hi[2])) | ((d[2] < 0.0f) & (p.lo[2] > pz)) |
+                              ((d[0] == 0.0f) & ((p.lo[0] > px) | (px > p.hi[0]))) |
+                              ((d[1] == 0.0f) & ((p.lo[1] > py) | (py > p.hi[1]))) |
+                              ((d[2] == 0.0f) & ((p.lo[2] > pz) | (pz > p.hi[2])));
+          if (exited) {
+            done = true;
+            break;
+          }
+        }
       }
-      if (lane == w) my_word = bits;
+      count += __popc(bits);
     }
-    if (lane < nw) wrow[base + lane] = my_word;
+    wrow[w] = bits;
   }
-  if (lane == 0) counts_out[ray] = count;
+  counts_out[ray] = count;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -251,8 +267,8 @@ int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* bloc
 int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
                        const GnrWs& L, cudaStream_t st) {
   (void)m;
-  unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n, (float*)(ws + L.t_min), (uint32_t*)(ws + L.words),
+  unsigned blocks = (unsigned)((n + kSampleBlock - 1) / kSampleBlock);
+  sample_mask_kernel<<<blocks, kSampleBlock, 0, st>>>(p, rays, n, (float*)(ws + L.t_min), (uint32_t*)(ws + L.words),
                                                             (int32_t*)(ws + L.counts));
   return (int)cudaGetLastError();
 }
@@ -376,7 +392,8 @@ extern "C" int gnr_sample_static(GnrModel* m, const float* rays, int64_t n_rays,
     if (e == cudaSuccess) {
       // every word of mask_words and block_sums that is read below is written first by these
       // launches, so what an earlier call left in the array is never seen
-      sample_mask_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(p, rays, n_rays, t_min, mask_words, counts);
+      sample_mask_kernel<<<(unsigned)((n_rays + kSampleBlock - 1) / kSampleBlock), kSampleBlock, 0, st>>>(p, rays, n_rays, t_min,
+                                                                                                  mask_words, counts);
       e = (cudaError_t)launch_exclusive_scan(counts, offsets, block_sums, n_rays, status, GNR_ST_NUM_VALID,
                                              GNR_ST_OVERFLOW_VALID, max_valid, st);
     }

@@ -391,7 +391,7 @@ class B200GridNeRF(torch.nn.Module):
             nbytes = C.c_size_t(0)
             check(lib.gnr_workspace_bytes(self._handle, n_rays, n_samples, max_valid, max_app, C.byref(nbytes)),
                   "gnr_workspace_bytes")
-            if len(self._ws) > 4:
+            if len(self._ws) > 6:
                 self._ws.clear()
             buf = torch.empty(nbytes.value + 256, dtype=torch.uint8, device=self.device)
             self._ws[key] = buf
@@ -534,11 +534,12 @@ class B200GridNeRF(torch.nn.Module):
     @torch.no_grad()
     def render_rays(self, rays: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,
                     rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None,
-                    overlap: bool = False):
+                    overlap=False):
         """Device-resident chunk loop: ``rays [N, 6]`` on the GPU -> ``rgb [N, 3]``, ``depth [N]``
         written in place, one status check at the end instead of one per chunk.  With
-        ``overlap`` consecutive chunks alternate between two side streams (each with its own
-        workspace), so that one chunk's latency-bound kernels run beside the other's."""
+        With ``overlap`` consecutive chunks rotate over that many side streams (``True`` = 2), each
+        with its own workspace, so that one chunk's kernels run beside the other's: the stages are
+        bound by different units (issue slots, L1, tensor pipe)."""
         rays = self._prepare(rays)
         n, s = rays.shape[0], self._samples(N_samples)
         if rgb_out is None:
@@ -548,17 +549,18 @@ class B200GridNeRF(torch.nn.Module):
         chunk = max(1, min(chunk, n))
         n_chunks = max(1, (n + chunk - 1) // chunk)
         status = torch.zeros((n_chunks, _lib.ST_WORDS), dtype=torch.int32, device=self.device)
-        use_side = overlap and n_chunks > 1
+        n_side = 2 if overlap is True else int(overlap or 0)
+        use_side = n_side > 1 and n_chunks > 1
         with torch.cuda.device(self.device):
             main = torch.cuda.current_stream()
             if use_side:
-                if getattr(self, "_side_streams", None) is None:
-                    self._side_streams = [torch.cuda.Stream(device=self.device) for _ in range(2)]
-                for st_ in self._side_streams:
+                if len(getattr(self, "_side_streams", None) or ()) < n_side:
+                    self._side_streams = [torch.cuda.Stream(device=self.device) for _ in range(n_side)]
+                for st_ in self._side_streams[:n_side]:
                     st_.wait_stream(main)
             for ci, first in enumerate(range(0, n, chunk)):
                 m = min(chunk, n - first)
-                slot = ci & 1 if use_side else 0
+                slot = ci % n_side if use_side else 0
                 keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(chunk, s, slot)
                 stream = self._side_streams[slot] if use_side else main
                 with torch.cuda.stream(stream):
@@ -569,7 +571,7 @@ class B200GridNeRF(torch.nn.Module):
                                                C.c_void_p(stream.cuda_stream)), "gnr_render_chunk")
                     status[ci].copy_(keep[(-keep.data_ptr()) % 256:][: 4 * _lib.ST_WORDS].view(torch.int32))
             if use_side:
-                for st_ in self._side_streams:
+                for st_ in self._side_streams[:n_side]:
                     main.wait_stream(st_)
         self._pending_status = status
         return rgb_out, depth_out
