@@ -38,7 +38,13 @@ import numpy as np  # noqa: E402
 import torch  # noqa: E402
 
 DENSITY_BYTES_PER_SAMPLE = 784      # 3 planes x 4 corners x 16 ch x 4 B + 12 B coordinate + 4 B sigma
-APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B coordinate
+APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B coordinate (fp16 storage: 1164)
+# What actually bounds the two gathers: every tap of a sample is delivered from L1 into registers
+# (the texels themselves are cache-resident, a frame oversamples the grid), and an SM's L1 hands
+# 128 B per clock to its register files.
+DENSITY_L1_BYTES_PER_SAMPLE = 18 * 16 * 4   # (4 plane + 2 line taps) x 3 pairs x 16 ch x 4 B
+APP_L1_BYTES_PER_SAMPLE = 18 * 48 * 4       # halved by fp16 storage
+L1_BYTES_PER_CLOCK_PER_SM = 128
 MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
 BASIS_FLOP_PER_SAMPLE = 7776        # 2 * 144 * 27 (done inside the appearance gather kernel)
 CPU_SAMPLE_RAYS = 65536
@@ -171,9 +177,11 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--app-fp16", type=int, default=0, choices=(0, 1),
+    ap.add_argument("--no-strict", action="store_true",
+                    help="skip the second measurement with every approximation off (fp32 MLP, fp32 planes, no termination)")
+    ap.add_argument("--app-fp16", type=int, default=1, choices=(0, 1),
                     help="hold the appearance planes as fp16 in HBM (mlp_mode 2 only)")
-    ap.add_argument("--ert", type=float, default=5e-5,
+    ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
@@ -325,6 +333,43 @@ def main():
     e2e_s = float(t.item())
     same = bool(torch.equal(rgb_h, rgb[:n_local].cpu()))
 
+    # ---- the same frame with every approximation off: fp32 CUDA-core MLP, fp32 planes, no early
+    # termination.  Its image is the full-frame check of the fast configuration. -----------------
+    strict = None
+    if world == 1 and not a.no_strict:
+        _, ckpt2, _ = build_scene(a.workload, device)
+        m2 = B200GridNeRF(**kwargs, mlp_mode=0, ert_transmittance=0.0, app_plane_fp16=False)
+        m2.load(ckpt2)
+        m2.release_torch_planes()
+        del ckpt2
+        torch.cuda.empty_cache()
+        rgb2, depth2 = torch.zeros_like(rgb), torch.zeros_like(depth)
+
+        def step2():
+            m2.render_rays(rays, S, True, chunk=a.chunk, rgb_out=rgb2[:n_local], depth_out=depth2[:n_local],
+                           overlap=(0 if a.no_overlap else a.streams))
+
+        for _ in range(3):
+            step2()
+        m2.check_pending_status()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(a.steps):
+            step2()
+        s1.record()
+        torch.cuda.synchronize()
+        st2 = m2.check_pending_status()
+        ms2 = s0.elapsed_time(s1) / a.steps
+        err2 = (rgb2[:n_local] - rgb[:n_local]).abs().max(dim=1).values
+        strict = {"value": H * W / (ms2 * 1e-3) / 1e6, "unit": "Mrays/s", "ms_per_step": ms2,
+                  "config": "mlp_mode 0 (fp32 CUDA-core MLP), fp32 planes, ert_transmittance 0",
+                  "density_evaluated": float(st2[5]),
+                  "fast_vs_strict_max_abs_rgb_diff": float(err2.max()), "fast_vs_strict_rays_above_1e-4": int((err2 > 1e-4).sum()),
+                  "rays_compared": int(n_local)}
+        del m2, rgb2, depth2
+        torch.cuda.empty_cache()
+
     tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local), float(stats[5])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
@@ -338,16 +383,28 @@ def main():
     n_density = float(stats[5]) if stats[5] > 0 else n_valid  # samples whose density was actually gathered
     per_launch = {k: (stage_ms[k] / a.steps) for k in stage_ms}  # ms per frame per stage (all chunks)
     roof = {}
+    sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)
+    l1_peak = L1_BYTES_PER_CLOCK_PER_SM * torch.cuda.get_device_properties(device).multi_processor_count * sm_mhz * 1e6 / 1e9
+
+    def l1_roof(bytes_per_sample, samples, ms):
+        ach_l1 = samples * bytes_per_sample / (ms * 1e-3) / 1e9
+        return {"achieved": ach_l1, "peak": l1_peak, "unit": "GB/s", "frac": ach_l1 / l1_peak,
+                "peak_is": "128 B/clk/SM x SMs x median SM clock (nominal L1 width, not measured)"}
+
+    app_bytes = APP_BYTES_PER_SAMPLE if not a.app_fp16 else 1164
+    app_l1_bytes = APP_L1_BYTES_PER_SAMPLE // (2 if a.app_fp16 else 1)
     if per_launch["density"] > 0:
         ach = n_density * DENSITY_BYTES_PER_SAMPLE / (per_launch["density"] * 1e-3) / 1e9
         roof["density_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                   "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"],
                                   "samples_gathered": n_density,
-                                  "note": "fused density gather + transmittance scan (march_kernel)" if a.ert >= 0 else "density_kernel"}
+                                  "l1_to_register": l1_roof(DENSITY_L1_BYTES_PER_SAMPLE, n_density, per_launch["density"]),
+                                  "note": "fused density gather + transmittance product (march_kernel)" if a.ert >= 0 else "density_kernel"}
     if per_launch["app_gather"] > 0 and n_app > 0:
-        ach = n_app * APP_BYTES_PER_SAMPLE / (per_launch["app_gather"] * 1e-3) / 1e9
+        ach = n_app * app_bytes / (per_launch["app_gather"] * 1e-3) / 1e9
         roof["app_gather_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                     "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["app_gather"]}
+                                     "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["app_gather"],
+                                     "l1_to_register": l1_roof(app_l1_bytes, n_app, per_launch["app_gather"])}
     if per_launch["mlp"] > 0 and n_app > 0:
         ach = n_app * MLP_FLOP_PER_SAMPLE / (per_launch["mlp"] * 1e-3) / 1e12
         roof["mlp_kernel"] = {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
@@ -393,6 +450,8 @@ def main():
         "samples_per_frame": {"valid": float(tot[0].item()), "appearance": float(tot[1].item()),
                               "rays": float(tot[2].item()), "density_evaluated": float(tot[3].item())},
     }
+    if strict is not None:
+        line["strict_fp32"] = strict
     if cpu_sd is not None:
         from oracle import gridnerf_oracle as orc
 
