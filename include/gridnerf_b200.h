@@ -193,8 +193,11 @@ int gnr_density(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, v
 
 /* Stage 3: raw2alpha + app_mask + second compaction (app/tools/utils.py:51-64,
  * gridnerf_sequential.py:477-479,493,501).  ``weights[i]`` per valid sample, ``acc[n]``,
- * ``depth[n]``, ``app_counts[n]``, ``app_offsets[n+1]``, ``app_index[j]`` = position in the
- * valid list of appearance sample j. */
+ * ``depth[n]``, ``app_counts[n]``, ``app_offsets[n+1]`` (exclusive scan of app_counts),
+ * ``app_index[j]`` = position in the valid list of appearance sample j.  The appearance list is
+ * ordered inside groups of 32 consecutive rays: group g owns entries app_offsets[32 g] ..
+ * app_offsets[min(32 g + 32, n)), first the first appearance sample of each of its rays (in ray
+ * order), then the second ones, and so on; a ray's samples keep their order along the ray. */
 int gnr_weights(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
                 size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* weights, float* acc,
                 float* depth, int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream);
