@@ -260,6 +260,39 @@ def render_rays(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: boo
     return torch.cat(rgbs, 0), torch.cat(depths, 0)
 
 
+def compute_alpha(f: Field, xyz_locs, length):
+    """alpha of free points over a segment of ``length``.  app/models/gridnerf_sequential.py:401-427."""
+    if f.alpha_volume is not None:
+        alpha_mask = sample_alpha(f, xyz_locs) > 0
+    else:
+        alpha_mask = torch.ones_like(xyz_locs[:, 0], dtype=torch.bool)
+    sigma = torch.zeros(xyz_locs.shape[:-1])
+    if alpha_mask.any():
+        xyz = (xyz_locs[alpha_mask] - f.aabb[0]) * f.inv_aabb_size - 1
+        sigma[alpha_mask] = feature2density(f, density_feature(f, xyz))
+    return 1 - torch.exp(-sigma * length)
+
+
+def update_alpha_mask(f: Field, grid_size, alpha_mask_thres: float = 1e-3, increase_alpha_thresh: int = 0):
+    """getDenseAlpha + updateAlphaMask, app/models/gridnerf_sequential.py:321-384: alpha on a dense
+    lattice of the box, 3x3x3 max pooling, threshold.  Returns the new 0/1 volume ``[D, H, W]`` and
+    the bounding box of its occupied lattice points."""
+    gx, gy, gz = [int(g) for g in grid_size]
+    samples = torch.stack(torch.meshgrid(torch.linspace(0, 1, gx), torch.linspace(0, 1, gy), torch.linspace(0, 1, gz),
+                                         indexing="ij"), -1)
+    dense_xyz = f.aabb[0] * (1 - samples) + f.aabb[1] * samples
+    alpha = torch.zeros_like(dense_xyz[..., 0])
+    for i in range(gx):
+        alpha[i] = compute_alpha(f, dense_xyz[i].view(-1, 3), f.step_size).view(gy, gz)
+    dense_xyz = dense_xyz.transpose(0, 2).contiguous()
+    alpha = alpha.clamp(0, 1).transpose(0, 2).contiguous()[None, None]
+    alpha = F.max_pool3d(alpha, kernel_size=3, padding=1, stride=1).view(gz, gy, gx)
+    thres = alpha_mask_thres * (10 ** increase_alpha_thresh)
+    volume = alpha >= thres
+    valid_xyz = dense_xyz[volume]
+    return volume, torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
+
+
 def field_from_checkpoint(ckpt: Dict[str, object], alpha_filter_thres: float = 0.0) -> Field:
     """Unpack a checkpoint dict the way ``GridBaseSequential.load`` does
     (app/models/gridnerf_sequential.py:225-242)."""

@@ -134,3 +134,20 @@ def test_encode_app_fixture():
     fx = load_golden("tiny_lit_encode_app.npz")
     out = orc.render_chunk(field, torch.from_numpy(fx["rays"]), int(fx["n_samples"]), True, app_code=int(fx["app_code"]))
     assert np.array_equal(out["rgb_map"].numpy(), fx["rgb_map"])
+
+
+def test_update_alpha_mask_fixture():
+    """updateAlphaMask: the oracle against what the reference produced (existing mask kept, no mask,
+    and a threshold in the middle of the scene's alpha values)."""
+    spec = scenes.tiny_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)
+    fx = load_golden("tiny_lit_update_mask.npz")
+    grid = tuple(int(g) for g in fx["grid"])
+    n = int(np.prod(grid))
+    bare = {k: v for k, v in ckpt.items() if not k.startswith("alphaMask")}
+    for tag, ck, thres in (("masked", ckpt, 1e-3), ("threshold", bare, float(fx["threshold_value"]))):
+        vol, box = orc.update_alpha_mask(orc.field_from_checkpoint(ck), grid, alpha_mask_thres=thres)
+        assert vol.shape == grid[::-1]
+        assert np.array_equal(np.packbits(vol.numpy().reshape(-1)), fx[f"{tag}_volume_bits"])
+        assert np.array_equal(box.numpy(), fx[f"{tag}_aabb"])
+        assert 0 < int(vol.sum()) == int(fx[f"{tag}_occupied"]) < n
