@@ -177,6 +177,7 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay measurement")
     ap.add_argument("--no-strict", action="store_true",
                     help="skip the second measurement with every approximation off (fp32 MLP, fp32 planes, no termination)")
     ap.add_argument("--app-fp16", type=int, default=1, choices=(0, 1),
@@ -333,6 +334,32 @@ def main():
     e2e_s = float(t.item())
     same = bool(torch.equal(rgb_h, rgb[:n_local].cpu()))
 
+    # ---- the frame as one replayed CUDA graph: pose in, RGBA8 pixels out (device) -----------------
+    graphed = None
+    if world == 1 and not a.no_graph:
+        from landmark_b200.engine import GraphedFrameRenderer
+
+        gr = GraphedFrameRenderer(model, H, W, spec.focal, pixel_ids=pix, n_samples=S, chunk=a.chunk,
+                                  streams=(1 if a.no_overlap else a.streams)).capture(pose)
+        for _ in range(2):
+            gr.render(pose)
+        torch.cuda.synchronize()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        g0.record()
+        for _ in range(a.steps):
+            gr.render(pose)
+        host_ms = (time.perf_counter() - t0) * 1e3 / a.steps  # host time to submit a frame
+        g1.record()
+        torch.cuda.synchronize()
+        gr.finish()
+        ms_g = g0.elapsed_time(g1) / a.steps
+        graphed = {"value": H * W / (ms_g * 1e-3) / 1e6, "unit": "Mrays/s", "ms_per_frame": ms_g,
+                   "host_submit_ms_per_frame": host_ms, "same_pixels_as_eager": bool(torch.equal(gr.rgb, rgb[:n_local])),
+                   "what": "pose upload + ray generation + chunk loop + RGBA8 as one CUDA graph replay per frame"}
+        del gr
+        torch.cuda.empty_cache()
+
     # ---- the same frame with every approximation off: fp32 CUDA-core MLP, fp32 planes, no early
     # termination.  Its image is the full-frame check of the fast configuration. -----------------
     strict = None
@@ -450,6 +477,8 @@ def main():
         "samples_per_frame": {"valid": float(tot[0].item()), "appearance": float(tot[1].item()),
                               "rays": float(tot[2].item()), "density_evaluated": float(tot[3].item())},
     }
+    if graphed is not None:
+        line["graph_replay"] = graphed
     if strict is not None:
         line["strict_fp32"] = strict
     if cpu_sd is not None:

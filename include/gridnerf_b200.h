@@ -119,6 +119,12 @@ int gnr_upload_hull_tables(GnrModel* m, int n_samples, const float* near_term, c
 int gnr_generate_rays(const float* pose_h, const float* dir_x, const float* dir_y, int H, int W,
                       const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays, void* stream);
 
+/* gnr_generate_rays with the pose (12 floats, row-major [3][4]) in DEVICE memory, read when the
+ * kernel runs: a frame captured as a CUDA graph is replayed for a new pose by rewriting the pose
+ * buffer (the role of the per-frame pose broadcast, dist_render/ddp_infer/nerf_inferer.py:150-171). */
+int gnr_generate_rays_dev(const float* pose_dev, const float* dir_x, const float* dir_y, int H, int W,
+                          const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays, void* stream);
+
 /* Frame post-process on the device: ``out[i] = (uint8)(rgb[i] * 255)`` (truncation, what
  * ``.byte()`` does) with alpha 255, i.e. the ``result * 255`` / ``torch.cat(..., 255)`` / ``.byte()``
  * steps of model_infer_postprocess (dist_render/ddp_infer/nerf_inferer.py:366-370).

@@ -63,6 +63,7 @@ SIGNATURES = {
     "gnr_upload_mlp": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "gnr_upload_hull_tables": (_INT, [_P, _INT, _P, _P, _P]),
     "gnr_generate_rays": (_INT, [C.POINTER(C.c_float), _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),
+    "gnr_generate_rays_dev": (_INT, [_P, _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),
     "gnr_rgba8": (_INT, [_P, _I64, _P, _P]),
     "gnr_workspace_bytes": (_INT, [_P, _I64, _INT, _I64, _I64, C.POINTER(_SZ)]),
     "gnr_render_chunk": (_INT, [_P, _P, _I64, _INT, _INT, _P, _SZ, _I64, _I64, _P, _P, _P]),

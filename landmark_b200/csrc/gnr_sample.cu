@@ -37,6 +37,27 @@ __global__ void raygen_kernel(Pose pose, const float* __restrict__ dir_x, const 
     out[3 + a] = fmaf(dz, pose.m[a * 4 + 2], fmaf(dy, pose.m[a * 4 + 1], dx * pose.m[a * 4 + 0]));
 }
 
+// Same, with the pose read from device memory: a captured CUDA graph replays this launch for a new
+// pose by rewriting those 12 floats.
+__global__ void raygen_dev_kernel(const float* __restrict__ pose_dev, const float* __restrict__ dir_x,
+                                  const float* __restrict__ dir_y, int W, const int32_t* __restrict__ pixel_ids,
+                                  int64_t first_pixel, int64_t n, float* __restrict__ rays) {
+  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= n) return;
+  float m[12];
+#pragma unroll
+  for (int i = 0; i < 12; ++i) m[i] = __ldg(pose_dev + i);
+  int64_t pix = pixel_ids ? (int64_t)pixel_ids[r] : first_pixel + r;
+  int j = (int)(pix / W), i = (int)(pix - (int64_t)j * W);
+  float dx = dir_x[i], dy = dir_y[j], dz = -1.0f;
+  float* out = rays + r * 6;
+  out[0] = m[3];
+  out[1] = m[7];
+  out[2] = m[11];
+#pragma unroll
+  for (int a = 0; a < 3; ++a) out[3 + a] = fmaf(dz, m[a * 4 + 2], fmaf(dy, m[a * 4 + 1], dx * m[a * 4 + 0]));
+}
+
 // ---------------------------------------------------------------------------------------------
 // sampling: one thread per ray, samples in order, 32 validity bits per register word
 // ---------------------------------------------------------------------------------------------
@@ -303,6 +324,25 @@ extern "C" int gnr_generate_rays(const float* pose_h, const float* dir_x, const 
   for (int i = 0; i < 12; ++i) p.m[i] = pose_h[i];
   raygen_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p, dir_x, dir_y, W, pixel_ids,
                                                                               first_pixel, n, rays);
+  GNR_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int gnr_generate_rays_dev(const float* pose_dev, const float* dir_x, const float* dir_y, int H, int W,
+                                     const int32_t* pixel_ids, int64_t first_pixel, int64_t n, float* rays,
+                                     void* stream) {
+  if (!pose_dev || !dir_x || !dir_y || !rays || H <= 0 || W <= 0 || n < 0) {
+    gnr_set_error("gnr_generate_rays_dev: bad argument");
+    return -1;
+  }
+  if (!pixel_ids && (first_pixel < 0 || first_pixel + n > (int64_t)H * W)) {
+    gnr_set_error("gnr_generate_rays_dev: pixel range [%lld, %lld) outside the %dx%d image", (long long)first_pixel,
+                  (long long)(first_pixel + n), W, H);
+    return -1;
+  }
+  if (n == 0) return 0;
+  raygen_dev_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(pose_dev, dir_x, dir_y, W, pixel_ids,
+                                                                                  first_pixel, n, rays);
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -56,6 +56,89 @@ class FrameRenderer:
                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gnr_rgba8")
 
 
+class GraphedFrameRenderer:
+    """One frame of a fixed shape as a replayable CUDA graph.
+
+    Pose upload, ray generation for this rank's pixels, the chunk loop of ``render_rays`` on its
+    streams, and the RGBA8 conversion are captured once; ``render(pose)`` writes the 12 pose floats
+    into a pinned host buffer and replays the graph, so a frame costs one launch on the host instead
+    of some 400 (the three-stage overlap of dist_render/runner/pipe_runner/nerf_pipe_runner.py:102-140
+    then needs no host thread per stage).  Every buffer the graph touches is allocated before the
+    capture and kept alive here.  List overflow / expired waits are read from the status blocks
+    with ``finish()``.
+    """
+
+    def __init__(self, model, H: int, W: int, focal: float, pixel_ids: Optional[torch.Tensor] = None,
+                 n_samples: int = -1, white_bg: bool = True, chunk: int = 131072, streams: int = 2):
+        from .rays import direction_tables
+
+        self.model, self.H, self.W, self.focal = model, int(H), int(W), float(focal)
+        self.n_samples, self.white_bg, self.chunk, self.streams = n_samples, white_bg, chunk, streams
+        dev = self.device = model.device
+        self.pixel_ids = None if pixel_ids is None else pixel_ids.to(device=dev, dtype=torch.int32).contiguous()
+        n = self.n = self.H * self.W if pixel_ids is None else int(self.pixel_ids.numel())
+        dx, dy = direction_tables(self.H, self.W, self.focal)
+        self.dir_x, self.dir_y = dx.to(dev), dy.to(dev)
+        self.pose_host = torch.zeros(12, dtype=torch.float32).pin_memory()
+        self.pose_dev = torch.zeros(12, dtype=torch.float32, device=dev)
+        self.rays = torch.empty((n, 6), dtype=torch.float32, device=dev)
+        self.rgb = torch.empty((n, 3), dtype=torch.float32, device=dev)
+        self.depth = torch.empty((n,), dtype=torch.float32, device=dev)
+        self.rgba = torch.empty((n, 4), dtype=torch.uint8, device=dev)
+        self.graph = None
+
+    def _enqueue(self):
+        from ._lib import check, lib
+
+        with torch.cuda.device(self.device):
+            st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+            self.pose_dev.copy_(self.pose_host, non_blocking=True)
+            check(lib.gnr_generate_rays_dev(C.c_void_p(self.pose_dev.data_ptr()), C.c_void_p(self.dir_x.data_ptr()),
+                                            C.c_void_p(self.dir_y.data_ptr()), self.H, self.W,
+                                            C.c_void_p(self.pixel_ids.data_ptr() if self.pixel_ids is not None else 0),
+                                            0, self.n, C.c_void_p(self.rays.data_ptr()), st), "gnr_generate_rays_dev")
+            self.model.render_rays(self.rays, self.n_samples, self.white_bg, chunk=self.chunk, rgb_out=self.rgb,
+                                   depth_out=self.depth, overlap=self.streams)
+            self._status = self.model._pending_status
+            check(lib.gnr_rgba8(C.c_void_p(self.rgb.data_ptr()), self.n, C.c_void_p(self.rgba.data_ptr()),
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gnr_rgba8")
+
+    def capture(self, pose: np.ndarray):
+        """Warm up (creates workspaces and side streams) and capture the frame."""
+        self._set_pose(pose)
+        with torch.cuda.device(self.device):
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._enqueue()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            self.model.check_pending_status()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._enqueue()
+            self.graph = g
+        return self
+
+    def _set_pose(self, pose):
+        p = np.asarray(pose.cpu() if isinstance(pose, torch.Tensor) else pose, dtype=np.float32)[:3, :4].reshape(-1)
+        self.pose_host.copy_(torch.from_numpy(np.ascontiguousarray(p)))
+
+    def render(self, pose) -> torch.Tensor:
+        """Replay for ``pose``; returns the RGBA8 pixels ``[n, 4]`` (device, valid after the stream
+        work completes; the same buffer every frame)."""
+        if self.graph is None:
+            raise RuntimeError("capture() has not been called")
+        self._set_pose(pose)
+        self.graph.replay()
+        return self.rgba
+
+    def finish(self):
+        self.model._pending_status = self._status
+        return self.model.check_pending_status()
+
+
 class NerfDDPRunner:
     """``run_batch(single_pose) -> numpy uint8 [H, W, 4]``.  ``single_pose`` is ``[3, 4]`` or ``[3, 5]``
     (focal in the last column); without a focal column the ``focal`` given here is used."""

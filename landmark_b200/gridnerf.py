@@ -312,19 +312,27 @@ class B200GridNeRF(torch.nn.Module):
                                                self.matMode[dim][0], self.matMode[dim][1], st), "gnr_upload_plane")
                     check(lib.gnr_upload_line(h, kind, idx, _ptr(l_), l_.shape[1], l_.shape[2], self.vecMode[dim], st),
                           "gnr_upload_line")
-            if self.alphaMask is not None:
-                vol = (self.alphaMask.alpha_volume[0, 0] > 0).to(torch.uint8).contiguous().to(self.device)
-                d_, h_, w_ = vol.shape
-                a = self.alphaMask.aabb.detach().cpu().numpy().astype(np.float32)
-                inv = self.alphaMask.invgridSize.detach().cpu().numpy().astype(np.float32)
-                a_c = (C.c_float * 6)(*[float(v) for v in a.reshape(-1)])
-                i_c = (C.c_float * 3)(*[float(v) for v in inv])
-                check(lib.gnr_upload_alpha_mask(h, _ptr(vol), d_, h_, w_, a_c, i_c, st), "gnr_upload_alpha_mask")
+            self._upload_alpha_mask(st)
             self._upload_mlp(st)
             torch.cuda.current_stream().synchronize()
         self._committed = True
         if release_torch_planes:
             self.release_torch_planes()
+
+    def _upload_alpha_mask(self, st=None):
+        """Occupancy volume -> library (bit-packed there, with its coarse grid)."""
+        if self.alphaMask is None:
+            return
+        with torch.cuda.device(self.device):
+            vol = (self.alphaMask.alpha_volume[0, 0] > 0).to(torch.uint8).contiguous().to(self.device)
+            d_, h_, w_ = vol.shape
+            a = self.alphaMask.aabb.detach().cpu().numpy().astype(np.float32)
+            inv = self.alphaMask.invgridSize.detach().cpu().numpy().astype(np.float32)
+            a_c = (C.c_float * 6)(*[float(v) for v in a.reshape(-1)])
+            i_c = (C.c_float * 3)(*[float(v) for v in inv])
+            check(lib.gnr_upload_alpha_mask(self._handle, _ptr(vol), d_, h_, w_, a_c, i_c, st if st is not None else _stream()),
+                  "gnr_upload_alpha_mask")
+            torch.cuda.current_stream(self.device).synchronize()  # `vol` must outlive the packing kernels
 
     def _upload_mlp(self, st=None):
         """basis_mat and the three MLP layers -> library.  With encode_app the latent columns
@@ -357,6 +365,47 @@ class B200GridNeRF(torch.nn.Module):
             self._app_code = code
             with torch.cuda.device(self.device):
                 self._upload_mlp()
+
+    @torch.no_grad()
+    def updateAlphaMask(self, gridSize=(200, 200, 200), increase_alpha_thresh=0):
+        """Regenerate the occupancy mask from the current density field, as
+        app/models/gridnerf_sequential.py:321-384 does: alpha over one step at the points of a dense
+        lattice of the box (points the current mask already rules out keep alpha 0), 3x3x3 max
+        pooling, threshold ``alphaMask_thres * 10**increase_alpha_thresh``.  The density of the
+        lattice points comes from the library's point-mode entry; the new mask is uploaded to the
+        library.  Returns the bounding box of the occupied lattice points."""
+        if not self._committed:
+            self.commit()
+        from .model_parallel import density_points  # point-mode wrapper over gnr_density_points
+
+        gx, gy, gz = [int(g) for g in gridSize]
+        dev = self.device
+        samples = torch.stack(torch.meshgrid(torch.linspace(0, 1, gx), torch.linspace(0, 1, gy), torch.linspace(0, 1, gz),
+                                             indexing="ij"), -1).to(dev)
+        dense_xyz = self.aabb[0] * (1 - samples) + self.aabb[1] * samples
+        alpha = torch.zeros_like(dense_xyz[..., 0])
+        for i in range(gx):
+            pts = dense_xyz[i].view(-1, 3)
+            if self.alphaMask is not None:
+                q = (pts - self.alphaMask.aabb[0]) * self.alphaMask.invgridSize - 1
+                keep = torch.nn.functional.grid_sample(self.alphaMask.alpha_volume, q.view(1, -1, 1, 1, 3),
+                                                       align_corners=True).view(-1) > 0
+            else:
+                keep = torch.ones(pts.shape[0], dtype=torch.bool, device=dev)
+            sigma = torch.zeros(pts.shape[0], device=dev)
+            if bool(keep.any()):
+                xyz = ((pts[keep] - self.aabb[0]) * self.invaabbSize - 1).contiguous()
+                sigma[keep] = density_points(self, xyz)
+            alpha[i] = (1 - torch.exp(-sigma * self.stepSize)).view(gy, gz)
+        dense_xyz = dense_xyz.transpose(0, 2).contiguous()
+        alpha = alpha.clamp(0, 1).transpose(0, 2).contiguous()[None, None]
+        alpha = torch.nn.functional.max_pool3d(alpha, kernel_size=3, padding=1, stride=1).view(gz, gy, gx)
+        thres = self.alphaMask_thres * (10 ** increase_alpha_thresh)
+        volume = (alpha >= thres).float()
+        self.alphaMask = AlphaGridMask(dev, self.aabb, volume)
+        self._upload_alpha_mask()
+        valid_xyz = dense_xyz[volume > 0.5]
+        return torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
 
     def release_torch_planes(self):
         """Drop the torch (NCHW) copies of the planes once the library holds its own

@@ -164,6 +164,81 @@ def pin_and_dump(GridNeRF, raw2alpha, ray_utils, spec, rays, out_name, n_samples
           f"size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
 
 
+def block_checkpoints(n_blocks=2, grid=8):
+    """Seeded per-block checkpoints (what the branch-parallel trainer saves as <exp>-sub<b>.th)."""
+    spec = scenes.tiny_spec(grid=grid).lit()
+    return [scenes.make_checkpoint(spec, seed=500 + b) for b in range(n_blocks)]
+
+
+def pin_merged_stack():
+    """Run the reference's merge_ckpts (gridnerf_branch_parallel.py:465-546) on two small block
+    checkpoints and keep what it stacked, as the pin of landmark_b200.checkpoints."""
+    import tempfile
+
+    from app.models.gridnerf_branch_parallel import GridNeRFBranchParallel
+    from landmark_b200 import checkpoints
+
+    blocks = block_checkpoints()
+    orig_load = torch.load
+    torch.load = lambda *x, **k: orig_load(*x, **{**k, "weights_only": False})  # our own files; torch>=2.6 default differs
+    try:
+        with tempfile.TemporaryDirectory() as d:
+            for b, ck in enumerate(blocks):
+                torch.save(ck, f"{d}/exp-sub{b}.th")
+            fake = types.SimpleNamespace(args=types.SimpleNamespace(rank=0, expname="exp", model_parallel_degree=len(blocks),
+                                                                    plane_division=[len(blocks), 1], device="cpu"))
+            GridNeRFBranchParallel.merge_ckpts(fake, d)
+            ref = torch.load(f"{d}/exp-merged-stack.th", map_location="cpu")
+            wo = torch.load(f"{d}/exp-merged-stack-wo_plane.th", map_location="cpu")
+    finally:
+        torch.load = orig_load
+    mine = checkpoints.merge_stack(blocks)
+    assert set(ref["state_dict"]) == set(mine["state_dict"])
+    for k, v in ref["state_dict"].items():
+        assert torch.equal(v, mine["state_dict"][k]), k
+    assert list(ref["kwargs"]["gridSize"]) == list(mine["kwargs"]["gridSize"])
+    assert {k: tuple(v) for k, v in ref["gridShape"].items()} == {k: tuple(v) for k, v in mine["gridShape"].items()}
+    assert set(wo["state_dict"]) == set(checkpoints.without_planes(mine)["state_dict"])
+    fx = {"grid_size": np.array(ref["kwargs"]["gridSize"], dtype=np.int64), "n_blocks": np.int64(len(blocks))}
+    for k, v in ref["state_dict"].items():
+        if any(n in k for n in checkpoints.PLANE_NAMES + checkpoints.LINE_NAMES):
+            fx["sd." + k] = v.numpy()
+    path = os.path.join(HERE, "merged_stack_tiny.npz")
+    np.savez_compressed(path, **fx)
+    print(f"merged_stack_tiny.npz: merge_ckpts of {len(blocks)} blocks pinned, size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
+
+
+def pin_update_alpha_mask(GridNeRF, grid=(40, 36, 28)):
+    """updateAlphaMask of the reference (gridnerf_sequential.py:321-384) on the tiny lit scene, with
+    and without an existing mask; the oracle's restatement must give the same volume and box."""
+    spec = scenes.tiny_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)
+    fx = {"grid": np.array(grid, dtype=np.int64), "state_dict_digest": scenes.state_dict_digest(ckpt["state_dict"])}
+    # "threshold": no mask, and a threshold in the middle of the scene's alpha values, so that the
+    # outcome depends on the density itself
+    for tag, with_mask, thres in (("masked", True, None), ("unmasked", False, None), ("threshold", False, 0.00575)):
+        ck = ckpt if with_mask else {k: v for k, v in ckpt.items() if not k.startswith("alphaMask")}
+        if thres is not None:
+            ck = dict(ck)
+            ck["kwargs"] = dict(ck["kwargs"], alphaMask_thres=thres)
+        model = reference_model(GridNeRF, spec, ck)
+        new_aabb = model.updateAlphaMask(tuple(grid))
+        ref_vol = model.alphaMask.alpha_volume[0, 0] > 0.5
+        field = orc.field_from_checkpoint(ck)
+        vol, box = orc.update_alpha_mask(field, grid, alpha_mask_thres=model.alphaMask_thres)
+        assert torch.equal(vol, ref_vol), tag
+        assert torch.equal(box, new_aabb), tag
+        fx[f"{tag}_volume_bits"] = np.packbits(ref_vol.numpy().reshape(-1))
+        fx[f"{tag}_aabb"] = new_aabb.numpy()
+        fx[f"{tag}_occupied"] = np.int64(int(ref_vol.sum()))
+    fx["threshold_value"] = np.float64(0.00575)
+    path = os.path.join(HERE, "tiny_lit_update_mask.npz")
+    np.savez_compressed(path, **fx)
+    print(f"tiny_lit_update_mask.npz: updateAlphaMask{tuple(grid)} pinned, occupied masked/unmasked/threshold "
+          f"{int(fx['masked_occupied'])}/{int(fx['unmasked_occupied'])}/{int(fx['threshold_occupied'])} of {int(np.prod(grid))}",
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a LandMark checkout")
@@ -205,6 +280,9 @@ def main():
     enc.name, enc.encode_app = "tiny_lit_encode_app", True
     pin_and_dump(GridNeRF, raw2alpha, ray_utils, enc, rays[::5].contiguous(), "tiny_lit_encode_app.npz", enc.n_samples,
                  "config[0] lit, encode_app=1, app_code=1234, every 5th ray", app_code=torch.tensor(1234))
+
+    pin_merged_stack()
+    pin_update_alpha_mask(GridNeRF)
 
     if not a.skip_city:
         city = scenes.city_spec().lit()

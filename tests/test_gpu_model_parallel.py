@@ -130,3 +130,42 @@ def test_point_mode_entries_match_list_mode():
         ai = got["app_index"]
         rgb = appearance_points(model, xyz[ai], rays[ray[ai], 3:6])
         assert torch.equal(rgb, got["rgb_samples"])
+
+
+def test_block_renderer_from_merged_stack_checkpoint():
+    """Blocks split out of a merged-stack checkpoint (the reference's single-file export of a
+    branch-parallel model) render exactly what the per-block checkpoints render."""
+    from landmark_b200 import checkpoints
+    from landmark_b200.gridnerf import B200GridNeRF
+    from landmark_b200.model_parallel import BlockParallelRenderer, LoopbackComm
+
+    division = (2, 1)
+    gspec, gck, blocks = _block_scene(division)
+    # the trainer keeps basis_mat and the MLP identical across blocks; the merged file holds block 0's
+    shared = {k: v for k, v in blocks[0][1]["state_dict"].items()
+              if not any(n in k for n in checkpoints.PLANE_NAMES + checkpoints.LINE_NAMES)}
+    for _, ck in blocks[1:]:
+        ck["state_dict"].update(shared)
+    merged = checkpoints.merge_stack([ck for _, ck in blocks])
+    merged.update({k: gck[k] for k in checkpoints.MASK_KEYS})
+    parts = checkpoints.split_merged_stack(merged)
+    pose = scenes.pitched_pose((0.1, -0.2, 2.5), yaw_deg=20.0, pitch_deg=-65.0)
+    rays = orc.generate_rays(torch.from_numpy(pose), 32, 48, 30.0).cuda()
+
+    def renderer(block_ckpts):
+        samplers, owners = [], []
+        for r in range(2):
+            kw = dict(gck["kwargs"])
+            kw.update({"device": "cuda:0", "args": scenes.model_args(gspec, "cuda:0"), "is_train": False})
+            s = B200GridNeRF(**kw, mlp_mode=0, field_grid=(2, 2, 2))
+            s.load({k: v for k, v in gck.items() if k != "state_dict"} | {"state_dict": {}})
+            samplers.append(s)
+            owners.append(cuda_model(blocks[r][0], block_ckpts[r], mlp_mode=2))
+        return BlockParallelRenderer(samplers, owners, LoopbackComm(2), division)
+
+    halves = [rays[0::2].contiguous(), rays[1::2].contiguous()]
+    a = renderer([ck for _, ck in blocks]).render_chunk(halves, 160, True)
+    b = renderer(parts).render_chunk(halves, 160, True)
+    for (rgb_a, dep_a), (rgb_b, dep_b) in zip(a, b):
+        assert torch.equal(rgb_a, rgb_b) and torch.equal(dep_a, dep_b)
+    assert float(a[0][0].std()) > 0.05

@@ -440,3 +440,69 @@ def test_fp16_appearance_planes_stay_inside_the_bar():
     assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
     with pytest.raises(RuntimeError, match="mlp_mode 2"):
         cuda_model(spec, ckpt, mlp_mode=0, app_plane_fp16=True)
+
+
+def test_update_alpha_mask_matches_reference_fixture():
+    """B200GridNeRF.updateAlphaMask (density of the lattice points from the library) against the
+    volume the reference produced.  With the existing mask the result is exact; with a threshold in
+    the middle of the alpha values a lattice point whose alpha sits within rounding of the
+    threshold may flip (the density sums 48 products in another order): at most 0.1 % of the voxels."""
+    spec = scenes.tiny_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)
+    fx = load_golden("tiny_lit_update_mask.npz")
+    grid = tuple(int(g) for g in fx["grid"])
+    n = int(np.prod(grid))
+    model = cuda_model(spec, ckpt, mlp_mode=0)
+    box = model.updateAlphaMask(grid)
+    vol = (model.alphaMask.alpha_volume[0, 0] > 0.5).cpu().numpy()
+    assert vol.shape == grid[::-1]
+    ref = np.unpackbits(fx["masked_volume_bits"])[:n].reshape(vol.shape).astype(bool)
+    assert np.array_equal(vol, ref)
+    assert np.array_equal(box.cpu().numpy(), fx["masked_aabb"])
+    # the new mask is live in the library: a render uses it (fewer or equal valid samples than before)
+    rays = torch.from_numpy(load_golden("tiny_lit.npz")["rays"]).cuda()
+    before = int(load_golden("tiny_lit.npz")["valid_counts"].sum())
+    model(rays, N_samples=spec.n_samples)
+    assert 0 < int(model.last_status[2]) != before
+
+    bare = {k: v for k, v in ckpt.items() if not k.startswith("alphaMask")}
+    bare["kwargs"] = dict(bare["kwargs"], alphaMask_thres=float(fx["threshold_value"]))
+    m2 = cuda_model(spec, bare, mlp_mode=0)
+    assert m2.alphaMask is None
+    m2.updateAlphaMask(grid)
+    vol2 = (m2.alphaMask.alpha_volume[0, 0] > 0.5).cpu().numpy()
+    ref2 = np.unpackbits(fx["threshold_volume_bits"])[:n].reshape(vol2.shape).astype(bool)
+    flips = int((vol2 != ref2).sum())
+    assert flips <= n // 1000, f"{flips} of {n} voxels differ"
+    assert abs(int(vol2.sum()) - int(fx["threshold_occupied"])) <= n // 1000
+
+
+def test_graph_captured_frame_equals_eager_frames():
+    """A frame captured once as a CUDA graph (pose upload, ray generation, chunk loop on two streams,
+    RGBA8) replays for other poses with exactly the pixels of the eager path."""
+    from landmark_b200.engine import GraphedFrameRenderer
+    from landmark_b200.rays import generate_rays
+
+    spec = scenes.tiny_spec().lit()
+    model = cuda_model(spec, mlp_mode=2)
+    pose0 = scenes.make_pose(spec)
+    ren = GraphedFrameRenderer(model, spec.height, spec.width, spec.focal, n_samples=spec.n_samples, chunk=3000,
+                               streams=2).capture(pose0)
+    for k in range(3):
+        pose = pose0.copy()
+        pose[:, 3] += np.array([0.05 * k, -0.03 * k, 0.02 * k], dtype=pose.dtype)  # move the camera
+        rgba = ren.render(pose)
+        torch.cuda.synchronize()
+        st = ren.finish()
+        rays = generate_rays(pose, spec.height, spec.width, spec.focal, device="cuda:0")
+        assert torch.equal(rays, ren.rays)
+        rgb, depth = model.render_rays(rays, spec.n_samples, True, chunk=3000, overlap=2)
+        st2 = model.check_pending_status()
+        assert torch.equal(rgb, ren.rgb) and torch.equal(depth, ren.depth)
+        assert int(st[2]) == int(st2[2]) and int(st[3]) == int(st2[3]) and int(st[2]) > 0
+        expect = (rgb * 255.0).clamp(0, 255).to(torch.uint8)
+        assert torch.equal(rgba[:, :3], expect) and bool((rgba[:, 3] == 255).all())
+        if k:
+            assert not torch.equal(rgba, first)  # another pose, another picture
+        else:
+            first = rgba.clone()
