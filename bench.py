@@ -177,6 +177,8 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reload-test", action="store_true",
+                    help="time the refill of one resident block from pinned host memory (dynamic block window) and exit")
     ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay measurement")
     ap.add_argument("--no-strict", action="store_true",
                     help="skip the second measurement with every approximation off (fp32 MLP, fp32 planes, no termination)")
@@ -239,6 +241,26 @@ def main():
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
     model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16))
     model.load(ckpt)
+    if a.reload_test:
+        from landmark_b200.dynamic import pin_block
+
+        host = pin_block(ckpt)
+        nbytes = sum(t.numel() * 4 for t in host.values())
+        load_stream = torch.cuda.Stream(device=device)
+        times = []
+        for _ in range(4):
+            torch.cuda.synchronize()
+            r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            r0.record(load_stream)
+            model.reload_field_async(host, load_stream)
+            r1.record(load_stream)
+            torch.cuda.synchronize()
+            times.append(r0.elapsed_time(r1))
+        ms = sorted(times[1:])[1]
+        print(json.dumps({"reload_block": {"bytes_from_host": nbytes, "ms": ms, "gb_per_s": nbytes / ms / 1e6,
+                                           "what": "pinned host planes/lines -> device staging -> channel-last (fp16 for appearance) "
+                                                   "on a copy stream, no allocation, median of 3"}}))
+        return
     cpu_sd = None
     if rank == 0 and world == 1 and not a.no_cpu_baseline:
         cpu_sd = {k: v.cpu() for k, v in ckpt["state_dict"].items()}

@@ -292,11 +292,16 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
   const int Cp = padded_channels(C);
   float** buf = kind == 0 ? &m->den_plane_buf[idx] : &m->app_plane_buf[idx];
   GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
-  free_dev(*buf);
-  *buf = nullptr;
   const long long P = (long long)H * W;
   const bool half = kind == 1 && m->cfg.app_storage == 1;
-  GNR_CUDA_OK(cudaMalloc(buf, (size_t)P * Cp * (half ? sizeof(__half) : sizeof(float))));
+  const size_t need = (size_t)P * Cp * (half ? sizeof(__half) : sizeof(float));
+  if (*buf == nullptr || m->plane_bytes[kind][idx] != need) {
+    free_dev(*buf);
+    *buf = nullptr;
+    m->plane_bytes[kind][idx] = 0;
+    GNR_CUDA_OK(cudaMalloc(buf, need));
+    m->plane_bytes[kind][idx] = need;
+  }
   dim3 grid((unsigned)((P + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
   if (half)
     to_channel_last_half_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, reinterpret_cast<__half*>(*buf), C, Cp, P);
@@ -332,10 +337,15 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   const int Cp = padded_channels(C);
   float** buf = kind == 0 ? &m->den_line_buf[idx] : &m->app_line_buf[idx];
   GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
-  free_dev(*buf);
-  *buf = nullptr;
   const bool half = kind == 1 && m->cfg.app_storage == 1;
-  GNR_CUDA_OK(cudaMalloc(buf, (size_t)Ln * Cp * (half ? sizeof(__half) : sizeof(float))));
+  const size_t need = (size_t)Ln * Cp * (half ? sizeof(__half) : sizeof(float));
+  if (*buf == nullptr || m->line_bytes[kind][idx] != need) {
+    free_dev(*buf);
+    *buf = nullptr;
+    m->line_bytes[kind][idx] = 0;
+    GNR_CUDA_OK(cudaMalloc(buf, need));
+    m->line_bytes[kind][idx] = need;
+  }
   dim3 grid((unsigned)((Ln + 31) / 32), (unsigned)((Cp + 31) / 32)), block(32, 8);
   if (half)
     to_channel_last_half_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, reinterpret_cast<__half*>(*buf), C, Cp,

@@ -50,6 +50,8 @@ struct GnrModel {
   float* den_line_buf[GNR_MAX_PLANES];
   float* app_plane_buf[GNR_MAX_PLANES];
   float* app_line_buf[GNR_MAX_PLANES];
+  size_t plane_bytes[2][GNR_MAX_PLANES];  // current size of every plane / line buffer: an upload of the
+  size_t line_bytes[2][GNR_MAX_PLANES];   // same size reuses it (no cudaFree, hence no device-wide sync)
   // occupancy bits
   uint32_t* alpha_bits;
   uint32_t* alpha_coarse;  // one bit per 4x4x4 block of mask cells (see coarse_bits_kernel)

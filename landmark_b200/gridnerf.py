@@ -407,6 +407,36 @@ class B200GridNeRF(torch.nn.Module):
         valid_xyz = dense_xyz[volume > 0.5]
         return torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
 
+    @torch.no_grad()
+    def reload_field_async(self, state_dict, stream=None):
+        """Replace the planes and lines by those of ``state_dict`` (same shapes; pinned host or device
+        tensors), everything enqueued on ``stream``: no allocation, no host or device-wide
+        synchronisation, so that a copy stream can refill a spare model while another one renders.
+        The torch parameters serve as the staging copy, so they must not have been released.
+        The caller orders later use after this work (event / wait_stream)."""
+        if not self._committed:
+            raise RuntimeError("reload_field_async needs a committed model (load a first block with load())")
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        n_res = len(self.resMode)
+        with torch.cuda.device(self.device), torch.cuda.stream(st):
+            raw = C.c_void_p(st.cuda_stream)
+            for kind, planes, lines, pn, ln in ((0, self.density_plane, self.density_line, "density_plane", "density_line"),
+                                                (1, self.app_plane, self.app_line, "app_plane", "app_line")):
+                for idx in range(len(planes)):
+                    p, l_ = planes[idx].data, lines[idx].data
+                    if p.numel() == 0 or p.dtype != torch.float32 or not p.is_contiguous():
+                        raise RuntimeError("the torch planes were released or are not plain fp32 tensors")
+                    src_p, src_l = state_dict[f"{pn}.{idx}"], state_dict[f"{ln}.{idx}"]
+                    if tuple(src_p.shape) != tuple(p.shape) or tuple(src_l.shape) != tuple(l_.shape):
+                        raise ValueError(f"{pn}.{idx}: block shape {tuple(src_p.shape)} does not fit this model's {tuple(p.shape)}")
+                    p.copy_(src_p, non_blocking=True)
+                    l_.copy_(src_l, non_blocking=True)
+                    dim = idx // n_res
+                    check(lib.gnr_upload_plane(self._handle, kind, idx, _ptr(p), p.shape[1], p.shape[2], p.shape[3],
+                                               self.matMode[dim][0], self.matMode[dim][1], raw), "gnr_upload_plane")
+                    check(lib.gnr_upload_line(self._handle, kind, idx, _ptr(l_), l_.shape[1], l_.shape[2], self.vecMode[dim], raw),
+                          "gnr_upload_line")
+
     def release_torch_planes(self):
         """Drop the torch (NCHW) copies of the planes once the library holds its own
         channel-last copies; ``state_dict()`` no longer contains them afterwards."""

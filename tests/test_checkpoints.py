@@ -59,3 +59,13 @@ def test_sidecar_without_planes():
     bad["state_dict"]["density_line.0"] = bad["state_dict"]["density_line.0"][..., :1]
     with pytest.raises(ValueError, match="stacked line"):
         checkpoints.split_merged_stack(bad)
+
+
+def test_dynamic_window_blocks():
+    from landmark_b200.dynamic import window_blocks
+
+    assert window_blocks(0, (4, 2), 1) == [0, 1, 2, 3]
+    assert window_blocks(5, (4, 2), 1) == [2, 3, 4, 5, 6, 7]
+    assert window_blocks(5, (4, 2), 0) == [5]
+    assert window_blocks(12, (5, 5), 1) == [6, 7, 8, 11, 12, 13, 16, 17, 18]
+    assert window_blocks(3, (4, 2), 9) == list(range(8))

@@ -169,3 +169,79 @@ def test_block_renderer_from_merged_stack_checkpoint():
     for (rgb_a, dep_a), (rgb_b, dep_b) in zip(a, b):
         assert torch.equal(rgb_a, rgb_b) and torch.equal(dep_a, dep_b)
     assert float(a[0][0].std()) > 0.05
+
+
+def test_dynamic_block_window_follows_the_camera():
+    """Blocks wait in pinned host memory; a 3x3 window around the camera is resident.  While the
+    camera stays inside the window's reach the windowed render equals the render with every block
+    resident, bit for bit; a move into another block starts an asynchronous load into spare slots,
+    frames keep coming from the old window, and after the switch the pictures agree again."""
+    from landmark_b200.dynamic import DynamicBlockRenderer, LoadStatus, pin_block, window_blocks
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    division = (4, 2)
+    gspec, gck, blocks = _block_scene(division, grid=16)
+    kw = dict(gck["kwargs"])
+    kw.update({"device": "cuda:0", "args": scenes.model_args(gspec, "cuda:0"), "is_train": False})
+    sampler = B200GridNeRF(**kw, mlp_mode=0, field_grid=(2, 2, 2))
+    sampler.load({k: v for k, v in gck.items() if k != "state_dict"} | {"state_dict": {}})
+    host = [pin_block(ck) for _, ck in blocks]
+    assert all(t.is_pinned() for t in host[0].values())
+
+    def factory(b):
+        return cuda_model(blocks[b][0], blocks[b][1], mlp_mode=2)
+
+    # basis_mat and the MLP are per model here; give every block the same ones, as a trained scene has
+    shared = {k: v for k, v in blocks[0][1]["state_dict"].items() if "plane" not in k and "line" not in k}
+    for _, ck in blocks[1:]:
+        ck["state_dict"].update(shared)
+
+    def frame_rays(x, y):
+        pose = scenes.pitched_pose((x, y, 1.6), yaw_deg=10.0, pitch_deg=-88.0)  # looking almost straight down
+        return orc.generate_rays(torch.from_numpy(pose), 40, 40, 60.0).cuda()
+
+    everything = DynamicBlockRenderer(sampler, host, division, factory, radius=4).start((-3.0, -1.0, 1.6))
+    assert sorted(everything.block_to_slot) == list(range(8))
+    windowed = DynamicBlockRenderer(sampler, host, division, factory, radius=1).start((-3.0, -1.0, 1.6))
+    assert sorted(windowed.block_to_slot) == window_blocks(0, division, 1) == [0, 1, 2, 3]
+    assert windowed.n_slots == 8 and windowed.loads == 0
+
+    rays = frame_rays(-3.0, -1.0)
+    a, da = everything.render_rays(rays, 160, True, chunk=700)
+    b, db = windowed.render_rays(rays, 160, True, chunk=700)
+    assert torch.equal(a, b) and torch.equal(da, db) and float(a.std()) > 0.002
+    assert windowed.update((-3.2, -0.8, 1.6)) is LoadStatus.IDLE  # same block: nothing to do
+
+    # the camera flies to block 5 (x in [0, 2), y in [0, 2)): its window is blocks 2..7
+    assert windowed.update((1.0, 1.0, 1.6)) is LoadStatus.LOADING
+    assert sorted(windowed.block_to_slot) == [0, 1, 2, 3]  # frames still see the old window
+    b_old, _ = windowed.render_rays(rays, 160, True, chunk=700)
+    assert torch.equal(b_old, b)
+    windowed.wait_loaded()
+    assert windowed.update((1.0, 1.0, 1.6)) is LoadStatus.IDLE
+    assert sorted(windowed.block_to_slot) == window_blocks(5, division, 1) == [2, 3, 4, 5, 6, 7]
+    # blocks 4..7 had been parked in the spare slots at start-up, so nothing came from the host yet
+    rays2 = frame_rays(1.0, 1.0)
+    a2, da2 = everything.render_rays(rays2, 160, True, chunk=700)
+    b2, db2 = windowed.render_rays(rays2, 160, True, chunk=700)
+    assert torch.equal(a2, b2) and torch.equal(da2, db2)
+    assert not torch.equal(a2, a)
+
+    # a one-block window with three slots: the block under the camera really comes from the host
+    small = DynamicBlockRenderer(sampler, host, division, factory, radius=0, n_slots=3).start((1.0, 1.0, 1.6))
+    assert sorted(small.block_to_slot) == [5] and small.slot_block == [5, 0, 1] and small.loads == 0
+    assert small.update((-1.0, 1.0, 1.6)) is LoadStatus.LOADING  # block 3
+    assert sorted(small.block_to_slot) == [5]
+    small.wait_loaded()
+    assert small.update((-1.0, 1.0, 1.6)) is LoadStatus.IDLE
+    assert sorted(small.block_to_slot) == [3] and small.loads == 1
+    rays3 = frame_rays(-1.0, 1.0)  # straight down on the middle of block 3: no ray leaves the block
+    c, dc = small.render_rays(rays3, 160, True, chunk=700)
+    a3, da3 = everything.render_rays(rays3, 160, True, chunk=700)
+    assert torch.equal(c, a3) and torch.equal(dc, da3)
+    # an oblique view through the one-block window lacks the other blocks
+    far = scenes.pitched_pose((-3.0, -1.0, 2.5), yaw_deg=0.0, pitch_deg=-30.0)
+    rays4 = orc.generate_rays(torch.from_numpy(far), 32, 48, 30.0).cuda()
+    full4, _ = everything.render_rays(rays4, 200, True)
+    part4, _ = small.render_rays(rays4, 200, True)
+    assert not torch.equal(full4, part4)
