@@ -19,16 +19,39 @@ import torch
 TILE = 64
 
 
-def tile_pixel_ids(H: int, W: int, rank: int, world: int, tile: int = TILE) -> np.ndarray:
-    """Pixel ids (row-major ``y * W + x``) of the tiles owned by ``rank``; pixels inside a tile
-    in row-major order, tiles clipped at the image border."""
+PATCH = (8, 4)  # pixels of one warp: 8 wide, 4 high
+
+
+def _patch_order(ys: np.ndarray, xs: np.ndarray, W: int, patch) -> np.ndarray:
+    """Pixel ids of the region ys x xs, in patches of ``patch`` = (width, height) pixels: patches
+    row-major over the region, pixels row-major inside a patch."""
+    pw, ph = patch
+    grid = ys[:, None] * W + xs[None, :]
+    h, w = grid.shape
+    if h % ph == 0 and w % pw == 0:
+        return grid.reshape(h // ph, ph, w // pw, pw).transpose(0, 2, 1, 3).reshape(-1)
+    out = []
+    for y0 in range(0, h, ph):
+        for x0 in range(0, w, pw):
+            out.append(grid[y0:y0 + ph, x0:x0 + pw].reshape(-1))
+    return np.concatenate(out)
+
+
+def tile_pixel_ids(H: int, W: int, rank: int, world: int, tile: int = TILE, patch=PATCH) -> np.ndarray:
+    """Pixel ids (row-major ``y * W + x``) of the tiles owned by ``rank``, tiles clipped at the image
+    border.  Inside a tile the pixels come in 8 x 4 patches (``patch``; ``None`` = plain row-major):
+    the render kernels give 32 consecutive rays to one warp, and the rays of a compact patch stay
+    within a voxel of each other, so the lanes of a load read the same few texels."""
     tx, ty = (W + tile - 1) // tile, (H + tile - 1) // tile
     ids = []
     for k in range(rank, tx * ty, world):
         y0, x0 = (k // tx) * tile, (k % tx) * tile
         ys = np.arange(y0, min(y0 + tile, H))
         xs = np.arange(x0, min(x0 + tile, W))
-        ids.append((ys[:, None] * W + xs[None, :]).reshape(-1))
+        if patch is None:
+            ids.append((ys[:, None] * W + xs[None, :]).reshape(-1))
+        else:
+            ids.append(_patch_order(ys, xs, W, patch))
     return np.concatenate(ids).astype(np.int32) if ids else np.zeros((0,), np.int32)
 
 

@@ -22,8 +22,10 @@ def test_tiles_partition_the_frame():
     # a ragged image: tiles clipped at both borders
     parts = [tile_pixel_ids(70, 130, r, 4) for r in range(4)]
     assert np.array_equal(np.sort(np.concatenate(parts)), np.arange(70 * 130))
-    first = tile_pixel_ids(70, 130, 0, 4)
-    assert list(first[:3]) == [0, 1, 2] and first[64] == 130  # row-major inside a tile
+    first = tile_pixel_ids(70, 130, 0, 4, patch=None)
+    assert list(first[:3]) == [0, 1, 2] and first[64] == 130  # plain row-major inside a tile
+    first = tile_pixel_ids(70, 130, 0, 4)  # default: 8 x 4 patches, one warp's rays each
+    assert list(first[:9]) == [0, 1, 2, 3, 4, 5, 6, 7, 130] and first[32] == 8 and first[8 * 32] == 4 * 130
 
 
 def test_reference_contiguous_split():
