@@ -518,6 +518,8 @@ GnrWs gnr_ws_layout(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
   L.app_counts = take((size_t)n * 4);
   L.app_offsets = take((size_t)(n + 1) * 4);
   L.app_index = take((size_t)max_app * 4);
+  L.app_ids = take((size_t)max_app * 4);     // ray << kbits | sample of every appearance entry
+  L.app_weight = take((size_t)max_app * 4);  // its compositing weight
   L.app_feat = take((size_t)max_app * L.feat_stride * 4);
   L.app_rgb = take((size_t)max_app * 3 * 4);
   if (gnr_tc_basis_fused(m)) {

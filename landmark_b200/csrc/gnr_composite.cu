@@ -66,9 +66,10 @@ struct AppGroupWalk {
 };
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-expand_app_kernel(const float* __restrict__ weight, float thres, const int32_t* __restrict__ offsets,
-                  const int32_t* __restrict__ app_counts, const int32_t* __restrict__ app_offsets, int64_t n_rays,
-                  long long capacity, long long app_capacity, int32_t* __restrict__ app_index) {
+expand_app_kernel(const float* __restrict__ weight, const uint32_t* __restrict__ ids, float thres,
+                  const int32_t* __restrict__ offsets, const int32_t* __restrict__ app_counts,
+                  const int32_t* __restrict__ app_offsets, int64_t n_rays, long long capacity, long long app_capacity,
+                  int32_t* __restrict__ app_index, uint32_t* __restrict__ app_ids, float* __restrict__ app_weight) {
   const int lane = threadIdx.x & 31;
   const int64_t group = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (group * 32 >= n_rays) return;
@@ -82,8 +83,13 @@ expand_app_kernel(const float* __restrict__ weight, float thres, const int32_t* 
   long long at;
   while (walk.step(lane, left > 0, at)) {
     if (left > 0) {
-      while (i < end && !(__ldg(weight + i) > thres)) ++i;  // the next sample with w > thres
-      if (i < end && at < app_capacity) app_index[at] = (int32_t)i;
+      float w = 0.0f;
+      while (i < end && !((w = __ldg(weight + i)) > thres)) ++i;  // the next sample with w > thres
+      if (i < end && at < app_capacity) {
+        app_index[at] = (int32_t)i;
+        app_ids[at] = __ldg(ids + i);  // the gather and MLP kernels find ray and sample here
+        app_weight[at] = w;            // the compositing reads its weights in list order
+      }
       ++i;
       --left;
     }
@@ -93,9 +99,8 @@ expand_app_kernel(const float* __restrict__ weight, float thres, const int32_t* 
 // rgb_map = sum_j w_j rgb_j (+ 1 - acc), clamp to [0,1]; depth_map = sum w t
 // (app/models/gridnerf_sequential.py:493-501).  One thread per ray, ranks in order.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ app_counts,
-                 const int32_t* __restrict__ app_offsets, const int32_t* __restrict__ app_index,
-                 const float* __restrict__ app_rgb, const float* __restrict__ acc, const float* __restrict__ depth,
+composite_kernel(const float* __restrict__ app_weight, const int32_t* __restrict__ app_counts,
+                 const int32_t* __restrict__ app_offsets, const float* __restrict__ app_rgb, const float* __restrict__ acc, const float* __restrict__ depth,
                  int64_t n_rays, long long app_capacity, int white_bg, float* __restrict__ rgb_map,
                  float* __restrict__ depth_map) {
   const int lane = threadIdx.x & 31;
@@ -111,7 +116,7 @@ composite_kernel(const float* __restrict__ weight, const int32_t* __restrict__ a
   while (walk.step(lane, left > 0, at)) {
     if (left > 0) {
       if (at < app_capacity) {
-        const float w = __ldg(weight + __ldg(app_index + at));
+        const float w = __ldg(app_weight + at);
         r = fmaf(w, __ldg(app_rgb + at * 3 + 0), r);
         g = fmaf(w, __ldg(app_rgb + at * 3 + 1), g);
         b = fmaf(w, __ldg(app_rgb + at * 3 + 2), b);
@@ -151,11 +156,12 @@ int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, c
   if (e) return e;
   const int64_t groups = (n + 31) / 32;
   unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), m->cfg.ray_weight_thres,
-                                                           (const int32_t*)(ws + L.offsets),
+  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), (const uint32_t*)(ws + L.ids),
+                                                           m->cfg.ray_weight_thres, (const int32_t*)(ws + L.offsets),
                                                            (const int32_t*)(ws + L.app_counts), app_offsets, n,
                                                            (long long)max_valid, (long long)max_app,
-                                                           (int32_t*)(ws + L.app_index));
+                                                           (int32_t*)(ws + L.app_index), (uint32_t*)(ws + L.app_ids),
+                                                           (float*)(ws + L.app_weight));
   return (int)cudaGetLastError();
 }
 
@@ -166,8 +172,7 @@ int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const
   unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
   long long app_capacity = L.max_app;
   composite_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
-      (const float*)(ws + L.weight), (const int32_t*)(ws + L.app_counts), (const int32_t*)(ws + L.app_offsets),
-      (const int32_t*)(ws + L.app_index),
+      (const float*)(ws + L.app_weight), (const int32_t*)(ws + L.app_counts), (const int32_t*)(ws + L.app_offsets),
       (const float*)(ws + L.app_rgb), (const float*)(ws + L.acc), (const float*)(ws + L.depth), n, app_capacity,
       white_bg, rgb_map, depth_map);
   return (int)cudaGetLastError();

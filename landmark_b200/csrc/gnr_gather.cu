@@ -689,7 +689,7 @@ GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L) {
 
 GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L) {
   GnrCoords c = gnr_coords_valid(rays, ws, L);
-  c.index = (const int32_t*)(ws + L.app_index);
+  c.ids = (const uint32_t*)(ws + L.app_ids);  // written by expand_app_kernel in list order
   c.total_ptr = (const int32_t*)(ws + L.app_offsets) + L.n_rays;
   c.capacity = L.max_app;
   return c;

@@ -95,7 +95,7 @@ struct GnrSampleParams {
 // Workspace layout (byte offsets), identical for every stage call with the same arguments.
 struct GnrWs {
   size_t status, t_min, words, counts, offsets, block_sums, ids, sigma_feat, sigma, weight, acc, depth,
-      app_counts, app_offsets, app_index, app_feat, app_rgb, app_prod, total;
+      app_counts, app_offsets, app_index, app_ids, app_weight, app_feat, app_rgb, app_prod, total;
   size_t app_prod_image;  // bytes of one fp16 product image (hi), 0 if the tensor-core path is off
   int app_prod_tile;      // bytes of one 128-sample tile of that image
   int feat_stride;  // floats per appearance feature row (app_dim rounded up to 4)
