@@ -649,7 +649,7 @@ static int launch_sample(GnrModel* m, const GnrSampleParams& p, const float* ray
                          int64_t max_valid, cudaStream_t st) {
   int e = launch_sample_mask(m, p, rays, n, ws, L, st);
   if (e) return e;
-  return launch_sample_compact(m, p, n, ws, L, max_valid, st);
+  return launch_sample_compact(m, p, n, ws, L, max_valid, 1, st);
 }
 
 static int launch_weights(GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L, int64_t max_valid,
@@ -796,8 +796,9 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
     GNR_LAUNCH_OK(launch_sample_mask(m, p, rays, n, ws, L, st));
   }
   {
-    StageScope sc(m, GNR_STAGE_COMPACT, 4, st);
-    GNR_LAUNCH_OK(launch_sample_compact(m, p, n, ws, L, max_valid, st));
+    const int fused = m->cfg.ert_transmittance >= 0.0f;
+    StageScope sc(m, GNR_STAGE_COMPACT, fused ? 3 : 4, st);
+    GNR_LAUNCH_OK(launch_sample_compact(m, p, n, ws, L, max_valid, fused ? 0 : 1, st));
   }
   if (m->cfg.ert_transmittance >= 0.0f) {
     // fused density + weights pass (with early ray termination when the threshold is > 0)

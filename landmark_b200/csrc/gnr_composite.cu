@@ -66,8 +66,8 @@ struct AppGroupWalk {
 };
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
-expand_app_kernel(const float* __restrict__ weight, const uint32_t* __restrict__ ids, float thres,
-                  const int32_t* __restrict__ offsets, const int32_t* __restrict__ app_counts,
+expand_app_kernel(const float* __restrict__ weight, const uint32_t* __restrict__ words, int n_words, int kbits,
+                  float thres, const int32_t* __restrict__ offsets, const int32_t* __restrict__ app_counts,
                   const int32_t* __restrict__ app_offsets, int64_t n_rays, long long capacity, long long app_capacity,
                   int32_t* __restrict__ app_index, uint32_t* __restrict__ app_ids, float* __restrict__ app_weight) {
   const int lane = threadIdx.x & 31;
@@ -78,17 +78,30 @@ expand_app_kernel(const float* __restrict__ weight, const uint32_t* __restrict__
   int left = has_ray ? app_counts[ray] : 0;  // appearance samples this ray still has to place
   long long i = has_ray ? offsets[ray] : 0;
   const long long end = has_ray ? min((long long)offsets[ray + 1], capacity) : 0;
+  // entry i of the valid list is the (i - offsets[ray])-th set bit of the ray's validity words
+  const uint32_t* wrow = words + (size_t)(has_ray ? ray : 0) * n_words;
+  int word = 0;
+  uint32_t bits = has_ray ? __ldg(wrow) : 0u;
   AppGroupWalk walk;
   walk.pos = app_offsets[group * 32];
   long long at;
   while (walk.step(lane, left > 0, at)) {
     if (left > 0) {
       float w = 0.0f;
-      while (i < end && !((w = __ldg(weight + i)) > thres)) ++i;  // the next sample with w > thres
-      if (i < end && at < app_capacity) {
+      int k = 0;
+      bool found = false;
+      while (i < end && !found) {  // the next sample with w > thres
+        while (bits == 0u && word + 1 < n_words) bits = __ldg(wrow + ++word);
+        k = word * 32 + (__ffs(bits) - 1);
+        bits &= bits - 1u;
+        w = __ldg(weight + i);
+        found = w > thres;
+        if (!found) ++i;
+      }
+      if (found && at < app_capacity) {
         app_index[at] = (int32_t)i;
-        app_ids[at] = __ldg(ids + i);  // the gather and MLP kernels find ray and sample here
-        app_weight[at] = w;            // the compositing reads its weights in list order
+        app_ids[at] = ((uint32_t)ray << kbits) | (uint32_t)k;  // the gather and MLP kernels find ray and sample here
+        app_weight[at] = w;                                     // the compositing reads its weights in list order
       }
       ++i;
       --left;
@@ -149,15 +162,15 @@ int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, 
 
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                        int64_t max_valid, int64_t max_app, cudaStream_t st) {
-  (void)p;
   int32_t* app_offsets = (int32_t*)(ws + L.app_offsets);
   int e = launch_exclusive_scan((const int32_t*)(ws + L.app_counts), app_offsets, (int32_t*)(ws + L.block_sums), n,
                                 (int32_t*)(ws + L.status), GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP, max_app, st);
   if (e) return e;
   const int64_t groups = (n + 31) / 32;
   unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), (const uint32_t*)(ws + L.ids),
-                                                           m->cfg.ray_weight_thres, (const int32_t*)(ws + L.offsets),
+  expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), (const uint32_t*)(ws + L.words),
+                                                           p.words, p.kbits, m->cfg.ray_weight_thres,
+                                                           (const int32_t*)(ws + L.offsets),
                                                            (const int32_t*)(ws + L.app_counts), app_offsets, n,
                                                            (long long)max_valid, (long long)max_app,
                                                            (int32_t*)(ws + L.app_index), (uint32_t*)(ws + L.app_ids),

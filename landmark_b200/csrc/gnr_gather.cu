@@ -327,8 +327,8 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
   }
 }
 
-// Fused density + weights pass ("march"): one thread walks one ray's segment of the compacted
-// list, sample by sample: density feature (density_thread), activation, raw2alpha's alpha, the
+// Fused density + weights pass ("march"): one thread walks one ray's valid samples (the set bits of
+// its validity words; sample j of the ray owns entry offsets[ray] + j of the per-sample arrays): density feature (density_thread), activation, raw2alpha's alpha, the
 // running transmittance product in sample order (as torch.cumprod computes it on the CPU), weight,
 // and the ray's accumulated opacity and depth.  The 32 rays of a warp are consecutive rays of the
 // chunk; when those are neighbouring pixels (tile order) their samples of equal rank lie within a
@@ -343,7 +343,7 @@ constexpr int kMarchBlock = 32;  // one warp per CTA: a finished warp frees its 
 template <int J, int NP>
 __global__ void __launch_bounds__(kMarchBlock)
 march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
-             const uint32_t* __restrict__ ids, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
+             const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
              float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts,
              int32_t* __restrict__ evaluated_total) {
@@ -361,11 +361,17 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
       const float ox = __ldg(r + 0), oy = __ldg(r + 1), oz = __ldg(r + 2);
       const float dx = __ldg(r + 3), dy = __ldg(r + 4), dz = __ldg(r + 5);
       const float t_min = t_min_arr[ray];
-      const uint32_t kmask = (1u << p.kbits) - 1u;
       float T = 1.0f;
       long long i = beg;
+      // the ray's valid samples are the set bits of its validity words, in order
+      const uint32_t* wrow = words + (size_t)ray * p.words;
+      int word = 0;
+      uint32_t bits = __ldg(wrow);
       while (i < end) {
-        const int k = (int)(__ldg(ids + i) & kmask);
+        while (bits == 0u && word + 1 < p.words) bits = __ldg(wrow + ++word);
+        if (bits == 0u) break;  // (cannot happen: offsets count exactly the set bits)
+        const int k = word * 32 + (__ffs(bits) - 1);
+        bits &= bits - 1u;
         const float t = gnr_sample_t(p, t_min, k);
         const float x = gnr_normalize(gnr_point(ox, dx, t), p.lo[0], p.inv[0]);
         const float y = gnr_normalize(gnr_point(oy, dy, t), p.lo[1], p.inv[1]);
@@ -796,7 +802,7 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
   const float t_stop = m->cfg.ert_transmittance > 0.0f ? m->cfg.ert_transmittance : 0.0f;
 #define GNR_MARCH(JJ, NPP)                                                                                        \
   march_kernel<JJ, NPP><<<grid, kMarchBlock, 0, st>>>(                                                            \
-      p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids), (const int32_t*)(ws + L.offsets), \
+      p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
       (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)

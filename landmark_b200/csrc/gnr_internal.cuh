@@ -127,8 +127,9 @@ int gnr_check_chunk(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid,
 // launchers (each enqueues on `st`, returns cudaGetLastError as int)
 int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws,
                        const GnrWs& L, cudaStream_t st);
+// with_ids == 0: offsets only (the compacted id list is needed by the list-based density kernel and the stage API)
 int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                          int64_t max_valid, cudaStream_t st);
+                          int64_t max_valid, int with_ids, cudaStream_t st);
 GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L);
 GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L);
 int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,

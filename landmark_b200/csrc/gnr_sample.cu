@@ -295,12 +295,12 @@ int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float*
 }
 
 int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                          int64_t max_valid, cudaStream_t st) {
+                          int64_t max_valid, int with_ids, cudaStream_t st) {
   (void)m;
   int32_t* offsets = (int32_t*)(ws + L.offsets);
   int e = launch_exclusive_scan((const int32_t*)(ws + L.counts), offsets, (int32_t*)(ws + L.block_sums), n,
                                 (int32_t*)(ws + L.status), GNR_ST_NUM_VALID, GNR_ST_OVERFLOW_VALID, max_valid, st);
-  if (e) return e;
+  if (e || !with_ids) return e;  // the fused march pass and the appearance compaction read the words themselves
   unsigned blocks = (unsigned)((n + kWarpsPerBlock - 1) / kWarpsPerBlock);
   expand_ids_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const uint32_t*)(ws + L.words), offsets, n, p.words, p.kbits,
                                                            (long long)max_valid, (uint32_t*)(ws + L.ids));
