@@ -93,6 +93,22 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
       : "memory");
 }
 
+// One lane of a converged warp.  The MMAs are issued from warp-uniform control flow (a whole warp
+// enters, one elected lane issues) with operands derived from warp-uniform values, so that the
+// descriptors live in uniform registers; issued from a divergent `if (thread == 0)` every MMA
+// first moves its operands there, which costs about 100 cycles per instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 __device__ __forceinline__ void mma_commit(uint32_t mbar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
@@ -250,11 +266,13 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   float* s_b3 = s_b2 + HID;
   uint64_t* s_mbar = reinterpret_cast<uint64_t*>(s_b3 + 4);  // [NSLOT][2]: MMA completion, bulk-copy completion
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_mbar + 2 * NSLOT);
-  volatile uint32_t* s_flag = s_tmem + 1 + (threadIdx.x >> 7);  // per-group outcome of the last wait
+  volatile uint32_t* s_flag = s_tmem + 1;  // [NSLOT] per-group outcome of the last wait (indexed below)
 
   constexpr uint32_t kTmemCols = (NSLOT * COLS_PER_SLOT <= 256) ? 256u : 512u;
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int slot = tid >> 7, row = tid & 127;
+  const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same number, known to be warp-uniform
+  const int slot = warp_u >> 2, row = tid & 127;
+  const bool lead_warp = (warp_u & 3) == 0;                  // the warp of a group that issues its MMAs
 
   // ---- one-time set-up: weights -> smem, mbarriers, TMEM ---------------------------------------
   {
@@ -282,7 +300,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     __syncthreads();
     tc_fence_after();
   }
-  const uint32_t tmem_base = *s_tmem;
+  const uint32_t tmem_base = __shfl_sync(0xffffffffu, *s_tmem, 0);  // (broadcast: warp-uniform for the compiler)
   const uint32_t d_tmem = tmem_base + (uint32_t)(slot * COLS_PER_SLOT);     // this group's D accumulator
   const uint32_t f_tmem = d_tmem + HID;                                     // this group's feature accumulator
   const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;              // this warp's TMEM lane quarter
@@ -293,6 +311,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
   constexpr bool L3TC = (TA == 1);  // layer 3 on the tensor cores too (fp16 operands); TA == 2 keeps it in fp32
   const uint32_t mbar = smem_u32(&s_mbar[2 * slot]), tbar = smem_u32(&s_mbar[2 * slot + 1]);
   const int bar_id = 1 + slot;  // named barrier of this group (0 is __syncthreads)
+  s_flag += slot;
   uint32_t parity = 0, tparity = 0;
   bool copy_pending = false;
 
@@ -328,14 +347,20 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       }
       copy_pending = false;
       tparity ^= 1;
-      if (row == 0) {
-        const int ksteps = a.k0 >> 4;
-        for (int ks = 0; ks < ksteps; ++ks) {
-          const uint64_t bd = make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES);
-          mma_f16(f_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, ks > 0 ? 1u : 0u);
-          if (TA == 2) mma_f16(f_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, 1u);
+      if (lead_warp) {
+        if (elect_one()) {
+          const int ksteps = a.k0 >> 4;
+#pragma unroll
+          for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
+            if (ks < ksteps) {
+              const uint64_t bd = make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES);
+              mma_f16(f_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, ks > 0 ? 1u : 0u);
+              if (TA == 2) mma_f16(f_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, 1u);
+            }
+          }
+          mma_commit(mbar);
         }
-        mma_commit(mbar);
+        __syncwarp();
       }
       if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
         if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
@@ -435,15 +460,18 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 
     // ---- layer 1 MMAs (one thread of the group) ----------------------------------------------
-    if (row == 0) {
+    if (lead_warp) {
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int ks = 0; ks < K1 / 16; ++ks) {
-        const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES);
-        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
-        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
+        for (int ks = 0; ks < K1 / 16; ++ks) {
+          const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES);
+          mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
+          if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
+        }
+        mma_commit(mbar);
       }
-      mma_commit(mbar);
+      __syncwarp();
     }
     if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
       if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
@@ -487,15 +515,18 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
 
     // ---- layer 2 MMAs ---------------------------------------------------------------------------
-    if (row == 0) {
+    if (lead_warp) {
       tc_fence_after();
+      if (elect_one()) {
 #pragma unroll
-      for (int ks = 0; ks < K2 / 16; ++ks) {
-        const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES, KG_BYTES);
-        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
-        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
+        for (int ks = 0; ks < K2 / 16; ++ks) {
+          const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES, KG_BYTES);
+          mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
+          if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
+        }
+        mma_commit(mbar);
       }
-      mma_commit(mbar);
+      __syncwarp();
     }
     if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
       if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
@@ -527,12 +558,15 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       tmem_st_wait();
       tc_fence_before();
       asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
-      if (row == 0) {
+      if (lead_warp) {
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < HID / 16; ++ks)
-          mma_f16_ts(f_tmem, d_tmem + ks * 8, make_desc(w3_addr + ks * 2 * KG3_BYTES, KG3_BYTES), kIdescOut, ks > 0 ? 1u : 0u);
-        mma_commit(mbar);
+          for (int ks = 0; ks < HID / 16; ++ks)
+            mma_f16_ts(f_tmem, d_tmem + ks * 8, make_desc(w3_addr + ks * 2 * KG3_BYTES, KG3_BYTES), kIdescOut, ks > 0 ? 1u : 0u);
+          mma_commit(mbar);
+        }
+        __syncwarp();
       }
       if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
         if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);
