@@ -72,24 +72,30 @@ constexpr uint32_t kIdescHid = (1u << 4) | ((uint32_t)(HID >> 3) << 17) | ((uint
 constexpr uint32_t kIdescBasis = (1u << 4) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 constexpr uint32_t kIdescOut = (1u << 4) | ((uint32_t)(N3 >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 
-__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// `issue` != 0 in exactly one lane (elect_one): the whole warp runs the surrounding loop, so the
+// descriptors are computed in warp-uniform code, and the instruction itself is predicated.
+__device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                        uint32_t issue) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
 
 // Same, with the A operand in tensor memory: lane = row, one 32-bit column = two consecutive k (fp16).
-__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                           uint32_t issue) {
   asm volatile(
       "{\n\t"
-      ".reg .pred p;\n\t"
+      ".reg .pred p, q;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
-      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      "setp.ne.b32 q, %5, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(issue)
       : "memory");
 }
 
@@ -97,7 +103,7 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 // enters, one elected lane issues) with operands derived from warp-uniform values, so that the
 // descriptors live in uniform registers; issued from a divergent `if (thread == 0)` every MMA
 // first moves its operands there, which costs about 100 cycles per instruction.
-__device__ __forceinline__ bool elect_one() {
+__device__ __forceinline__ uint32_t elect_one() {
   uint32_t pred;
   asm volatile(
       "{\n\t"
@@ -106,11 +112,17 @@ __device__ __forceinline__ bool elect_one() {
       "selp.u32 %0, 1, 0, p;\n\t"
       "}"
       : "=r"(pred));
-  return pred != 0;
+  return pred;
 }
 
-__device__ __forceinline__ void mma_commit(uint32_t mbar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+__device__ __forceinline__ void mma_commit(uint32_t mbar, uint32_t issue) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}\n" ::"r"(mbar), "r"(issue)
+      : "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -348,18 +360,17 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       copy_pending = false;
       tparity ^= 1;
       if (lead_warp) {
-        if (elect_one()) {
-          const int ksteps = a.k0 >> 4;
+        const uint32_t leader = elect_one();
+        const int ksteps = a.k0 >> 4;
 #pragma unroll
-          for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
-            if (ks < ksteps) {
-              const uint64_t bd = make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES);
-              mma_f16(f_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, ks > 0 ? 1u : 0u);
-              if (TA == 2) mma_f16(f_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, 1u);
-            }
+        for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
+          if (ks < ksteps) {
+            const uint64_t bd = make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES);
+            mma_f16(f_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, ks > 0 ? 1u : 0u, leader);
+            if (TA == 2) mma_f16(f_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescBasis, 1u, leader);
           }
-          mma_commit(mbar);
         }
+        mma_commit(mbar, leader);
         __syncwarp();
       }
       if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
@@ -462,15 +473,14 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     // ---- layer 1 MMAs (one thread of the group) ----------------------------------------------
     if (lead_warp) {
       tc_fence_after();
-      if (elect_one()) {
+      const uint32_t leader = elect_one();
 #pragma unroll
-        for (int ks = 0; ks < K1 / 16; ++ks) {
-          const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES);
-          mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
-          if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
-        }
-        mma_commit(mbar);
+      for (int ks = 0; ks < K1 / 16; ++ks) {
+        const uint64_t bd = make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES);
+        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u, leader);
+        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u, leader);
       }
+      mma_commit(mbar, leader);
       __syncwarp();
     }
     if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
@@ -517,15 +527,14 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
     // ---- layer 2 MMAs ---------------------------------------------------------------------------
     if (lead_warp) {
       tc_fence_after();
-      if (elect_one()) {
+      const uint32_t leader = elect_one();
 #pragma unroll
-        for (int ks = 0; ks < K2 / 16; ++ks) {
-          const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES, KG_BYTES);
-          mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u);
-          if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u);
-        }
-        mma_commit(mbar);
+      for (int ks = 0; ks < K2 / 16; ++ks) {
+        const uint64_t bd = make_desc(w2_addr + ks * 2 * KG_BYTES, KG_BYTES);
+        mma_f16(d_tmem, make_desc(a_hi_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, ks > 0 ? 1u : 0u, leader);
+        if (TA == 2) mma_f16(d_tmem, make_desc(a_lo_addr + ks * 2 * KG_BYTES, KG_BYTES), bd, kIdescHid, 1u, leader);
       }
+      mma_commit(mbar, leader);
       __syncwarp();
     }
     if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
@@ -560,12 +569,11 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
       if (lead_warp) {
         tc_fence_after();
-        if (elect_one()) {
+        const uint32_t leader = elect_one();
 #pragma unroll
-          for (int ks = 0; ks < HID / 16; ++ks)
-            mma_f16_ts(f_tmem, d_tmem + ks * 8, make_desc(w3_addr + ks * 2 * KG3_BYTES, KG3_BYTES), kIdescOut, ks > 0 ? 1u : 0u);
-          mma_commit(mbar);
-        }
+        for (int ks = 0; ks < HID / 16; ++ks)
+          mma_f16_ts(f_tmem, d_tmem + ks * 8, make_desc(w3_addr + ks * 2 * KG3_BYTES, KG3_BYTES), kIdescOut, ks > 0 ? 1u : 0u, leader);
+        mma_commit(mbar, leader);
         __syncwarp();
       }
       if (!group_wait(mbar, parity, bar_id, row, s_flag)) {
