@@ -67,7 +67,12 @@ __global__ void raygen_dev_kernel(const float* __restrict__ pose_dev, const floa
 // coarse grid proves that all eight corners are empty (threshold >= 0 then fails), and with a
 // threshold of exactly zero the sum of non-negative weights is positive as soon as one occupied
 // corner has a positive weight, so the loop can stop there.
-__device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float px, float py, float pz) {
+// `skip` (optional): when the coarse grid rules the sample out, the number of FOLLOWING samples
+// that provably lie in the same empty coarse block, given the index-space step `di` per sample
+// (dense sampler: positions advance by d * stepSize).  The bound keeps 1/100 of a mask cell away
+// from the block's faces, far more than the rounding of the index arithmetic (a few 1e-4).
+__device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float px, float py, float pz,
+                                               const float* di = nullptr, int* skip = nullptr) {
   // q = (p - aabb0) * invgridSize - 1 ; index = ((q + 1) / 2) * (size - 1)
   const float ix = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(px, p.a_lo[0], p.a_inv[0]), 1.0f), 0.5f), (float)(p.aW - 1));
   const float iy = __fmul_rn(__fmul_rn(__fadd_rn(gnr_normalize(py, p.a_lo[1], p.a_inv[1]), 1.0f), 0.5f), (float)(p.aH - 1));
@@ -81,7 +86,21 @@ __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float p
   const int x0 = (int)fx0, y0 = (int)fy0, z0 = (int)fz0;
   if (p.a_coarse != nullptr && p.a_thres >= 0.0f && x0 >= 0 && y0 >= 0 && z0 >= 0) {
     const uint32_t cb = (uint32_t)(((z0 >> 2) * p.cH + (y0 >> 2)) * p.cW + (x0 >> 2));
-    if (!((__ldg(p.a_coarse + (cb >> 5)) >> (cb & 31)) & 1u)) return false;
+    if (!((__ldg(p.a_coarse + (cb >> 5)) >> (cb & 31)) & 1u)) {
+      if (skip) {
+        const float idx[3] = {ix, iy, iz};
+        const int lo[3] = {x0 & ~3, y0 & ~3, z0 & ~3};
+        float n = 64.0f;
+#pragma unroll
+        for (int a = 0; a < 3; ++a) {
+          const float room = di[a] > 0.0f ? ((float)(lo[a] + 4) - idx[a] - 0.01f) : (idx[a] - (float)lo[a] - 0.01f);
+          const float speed = fabsf(di[a]);
+          if (speed > 0.0f) n = fminf(n, room / speed);
+        }
+        *skip = n > 0.0f ? (int)n : 0;
+      }
+      return false;
+    }
   }
   const float fx1 = __fadd_rn(fx0, 1.0f), fy1 = __fadd_rn(fy0, 1.0f), fz1 = __fadd_rn(fz0, 1.0f);
   const float wx[2] = {__fsub_rn(fx1, ix), __fsub_rn(ix, fx0)};
@@ -118,8 +137,9 @@ constexpr int kSampleBlock = 128;
 __global__ void __launch_bounds__(kSampleBlock)
 sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_rays, float* __restrict__ t_min_out,
                    uint32_t* __restrict__ words_out, int32_t* __restrict__ counts_out) {
-  const int64_t ray = (int64_t)blockIdx.x * kSampleBlock + threadIdx.x;
-  if (ray >= n_rays) return;
+  const int64_t ray_raw = (int64_t)blockIdx.x * kSampleBlock + threadIdx.x;
+  const bool live = ray_raw < n_rays;  // lanes past the end keep their warp company (warp votes below) and write nothing
+  const int64_t ray = live ? ray_raw : n_rays - 1;
   const float* r = rays + ray * 6;
   const float o[3] = {__ldg(r), __ldg(r + 1), __ldg(r + 2)};
   const float d[3] = {__ldg(r + 3), __ldg(r + 4), __ldg(r + 5)};
@@ -139,44 +159,64 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
     const float far = -__fdiv_rn(__fsub_rn(o[2], p.lo[2]), d[2]);
     t_min = (d[2] >= 0.0f) ? p.far_t : far;
   }
-  t_min_out[ray] = t_min;
+  if (live) t_min_out[ray] = t_min;
 
   int count = 0;
   uint32_t* wrow = words_out + ray * p.words;
   // fl(o + fl(d * fl(t_min + fl(step * k)))) is monotone in k, so once a sample has left the
   // box through the far side of an axis every later sample is outside as well.
   // (The hull sampler's distances are a sum of a falling and a rising term and need not be
-  // monotone to the last bit, so only the dense sampler stops at the first exit.)
-  bool done = false;
-  for (int w = 0; w < p.words; ++w) {
-    uint32_t bits = 0;
+  // monotone to the last bit, so only the dense sampler stops at the first exit and skips.)
+  // The 32 rays of a warp walk the sample index k together.  When every ray of the warp stands in
+  // an empty coarse block (or has left the box) the warp jumps over the samples that all of them
+  // can rule out; jumping together keeps neighbouring rays, which see the same occupancy, in step.
+  const float di[3] = {d[0] * p.step * p.a_inv[0] * 0.5f * (float)(p.aW - 1), d[1] * p.step * p.a_inv[1] * 0.5f * (float)(p.aH - 1),
+                       d[2] * p.step * p.a_inv[2] * 0.5f * (float)(p.aD - 1)};
+  const bool can_skip = p.mode == 0 && p.has_mask;
+  constexpr int kMaxSkip = 64;
+  bool done = !live;
+  uint32_t bits = 0;
+  int word = 0, k = 0;
+  while (k < p.S) {
+    const int w = k >> 5;
+    while (word < w) {  // words completed since the last sample (all of them when samples were skipped)
+      if (live) wrow[word] = bits;
+      ++word;
+      count += __popc(bits);
+      bits = 0;
+    }
+    int skip = kMaxSkip;  // a finished ray never holds the warp back
     if (!done) {
-      const int k_end = min(32, p.S - w * 32);
-      for (int b = 0; b < k_end; ++b) {
-        const float t = gnr_sample_t(p, t_min, w * 32 + b);
-        const float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
-        const bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
-        const bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
-        if (!(lo_out | hi_out)) {
-          if (!p.has_mask || occupancy_test(p, px, py, pz)) bits |= 1u << b;
-        } else if (p.mode == 0) {
-          const bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
-                              ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
-                              ((d[2] > 0.0f) & (pz > p.hi[2])) | ((d[2] < 0.0f) & (p.lo[2] > pz)) |
-                              ((d[0] == 0.0f) & ((p.lo[0] > px) | (px > p.hi[0]))) |
-                              ((d[1] == 0.0f) & ((p.lo[1] > py) | (py > p.hi[1]))) |
-                              ((d[2] == 0.0f) & ((p.lo[2] > pz) | (pz > p.hi[2])));
-          if (exited) {
-            done = true;
-            break;
-          }
+      skip = 0;
+      const float t = gnr_sample_t(p, t_min, k);
+      const float px = gnr_point(o[0], d[0], t), py = gnr_point(o[1], d[1], t), pz = gnr_point(o[2], d[2], t);
+      const bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
+      const bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
+      if (!(lo_out | hi_out)) {
+        if (!p.has_mask || occupancy_test(p, px, py, pz, di, can_skip ? &skip : nullptr)) bits |= 1u << (k & 31);
+      } else if (p.mode == 0) {
+        const bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
+                            ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
+                            ((d[2] > 0.0f) & (pz > p.hi[2])) | ((d[2] < 0.0f) & (p.lo[2] > pz)) |
+                            ((d[0] == 0.0f) & ((p.lo[0] > px) | (px > p.hi[0]))) |
+                            ((d[1] == 0.0f) & ((p.lo[1] > py) | (py > p.hi[1]))) |
+                            ((d[2] == 0.0f) & ((p.lo[2] > pz) | (pz > p.hi[2])));
+        if (exited) {
+          done = true;
+          skip = kMaxSkip;
         }
       }
-      count += __popc(bits);
     }
-    wrow[w] = bits;
+    if (__all_sync(0xffffffffu, done)) break;
+    k += 1 + __reduce_min_sync(0xffffffffu, min(skip, kMaxSkip));
   }
-  counts_out[ray] = count;
+  while (word < p.words) {
+    if (live) wrow[word] = bits;
+    ++word;
+    count += __popc(bits);
+    bits = 0;
+  }
+  if (live) counts_out[ray] = count;
 }
 
 // ---------------------------------------------------------------------------------------------
