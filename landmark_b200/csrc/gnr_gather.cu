@@ -341,7 +341,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
 constexpr int kMarchBlock = 32;  // one warp per CTA: a finished warp frees its slot at once
 
 template <int J, int NP>
-__global__ void __launch_bounds__(kMarchBlock)
+__global__ void __launch_bounds__(kMarchBlock, 16)
 march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
              const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
@@ -603,7 +603,7 @@ __device__ __forceinline__ void pair_products_thread48(const GnrPlane& pl, Tap t
 }
 
 template <int NP, bool HALF>
-__global__ void __launch_bounds__(kThreadBlock)
+__global__ void __launch_bounds__(kThreadBlock, 4)
 app_products_thread_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
                            int tile_bytes, int view_group) {
   const long long total = coords_total(crd);
