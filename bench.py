@@ -173,7 +173,8 @@ def main():
                          "all-to-all routing) | city_channels (channel-parallel appearance, reduce-scatter)")
     ap.add_argument("--grid-scale", type=int, default=1, help="divide grid and mask resolution (model-parallel workloads)")
     ap.add_argument("--check", action="store_true", help="city_blocks: compare rank 0 with a single-process render")
-    ap.add_argument("--chunk", type=int, default=131072, help="rays per library call")
+    ap.add_argument("--chunk", type=int, default=262144,
+                    help="rays per library call (lowered so that every stream of a rank has a chunk)")
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -287,6 +288,10 @@ def main():
         shard = TileSharding(H, W, rank, world, device)
     n_local, n_pad, pix = shard.n_local, shard.n_pad, shard.pixel_ids
     rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=pix)
+    if not a.no_overlap and a.streams > 1:
+        # at least one chunk per stream: a rank of an 8-GPU run owns ~259 k rays
+        per_stream = -(-n_local // a.streams)
+        a.chunk = max(4096, min(a.chunk, -(-per_stream // 4096) * 4096))
     rgb = torch.zeros((n_pad, 3), dtype=torch.float32, device=device)
     depth = torch.zeros((n_pad,), dtype=torch.float32, device=device)
     image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
