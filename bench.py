@@ -106,10 +106,13 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_scene(workload, device):
+FRAMES = {"1080p": (1080, 1920), "4k": (2160, 3840)}
+
+
+def build_scene(workload, device, frame="1080p"):
     from landmark_b200 import scenes
 
-    spec = scenes.city_spec()
+    spec = scenes.city_spec(*FRAMES[frame])
     if workload == "city_lit":
         spec = spec.lit()
     vol = scenes.make_alpha_volume(spec)
@@ -178,6 +181,8 @@ def main():
     ap.add_argument("--mlp-mode", type=int, default=2,
                     help="0 fp32 CUDA cores, 1 tcgen05 fp16 hi+lo activations, 2 tcgen05 fp16 (default)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--frame", choices=sorted(FRAMES), default="1080p",
+                    help="frame size (the focal length scales with the width); 4k is the tile-parallel configuration's frame")
     ap.add_argument("--reload-test", action="store_true",
                     help="time the refill of one resident block from pinned host memory (dynamic block window) and exit")
     ap.add_argument("--no-graph", action="store_true", help="skip the CUDA-graph replay measurement")
@@ -237,7 +242,7 @@ def main():
     from landmark_b200.parallel import TILE, TileSharding, tile_pixel_ids
     from landmark_b200.rays import generate_rays
 
-    spec, ckpt, pose = build_scene(a.workload, device)
+    spec, ckpt, pose = build_scene(a.workload, device, a.frame)
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
     model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16))
@@ -391,7 +396,7 @@ def main():
     # termination.  Its image is the full-frame check of the fast configuration. -----------------
     strict = None
     if world == 1 and not a.no_strict:
-        _, ckpt2, _ = build_scene(a.workload, device)
+        _, ckpt2, _ = build_scene(a.workload, device, a.frame)
         m2 = B200GridNeRF(**kwargs, mlp_mode=0, ert_transmittance=0.0, app_plane_fp16=False)
         m2.load(ckpt2)
         m2.release_torch_planes()
@@ -486,7 +491,7 @@ def main():
         "metric": "Mrays/s", "value": H * W / (ms_step * 1e-3) / 1e6, "unit": "Mrays/s", "n_gpus": world,
         "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 (gathers, compositing) + f16 operands / f32 accumulate (tcgen05 MLP)" if a.mlp_mode else "f32", "data": "synthetic",
-        "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
+        "config": {"workload": f"{a.workload}: {W}x{H} frame, 512 samples/ray, grid 2048x2048x256, 16/48 ch",
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
