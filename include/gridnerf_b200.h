@@ -208,6 +208,14 @@ int gnr_weights(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, v
                 size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* weights, float* acc,
                 float* depth, int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream);
 
+/* Stages 2 + 3 in one pass (what gnr_render_chunk runs): density of the valid samples of the
+ * last gnr_sample on this workspace, raw2alpha with the transmittance product in sample order,
+ * early ray termination at GnrConfig.ert_transmittance (0 = none), and the appearance compaction.
+ * Outputs as gnr_weights (samples after a ray's termination have weight 0); no sigma is kept. */
+int gnr_march(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
+              size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* weights, float* acc,
+              float* depth, int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream);
+
 /* Stage 4: compute_appfeature (gather + basis_mat) and MLPRender_Fea for the appearance
  * samples: ``app_features[j][app_dim]`` and ``rgb[j][3]``.  gridnerf_sequential.py:829-871,
  * app/models/mlp_render_fea.py:44-68. */
@@ -239,11 +247,15 @@ int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_fe
  * ``app_index[max_app]`` (optional) receives the appearance list. */
 int gnr_weights_from_sigma(GnrModel* m, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
                            int64_t max_valid, int64_t max_app, const float* sigma, int32_t* app_index, void* stream);
-/* compute_appfeature only (fp32 gather + basis projection) for the appearance list of the
- * workspace: with a channel slice of the planes and the matching columns of basis_mat these are
- * the partial sums a tensor-parallel rank contributes (gridnerf_tensor_parallel.py:284-300). */
+/* compute_appfeature only (gather + basis projection; on the tensor cores with mlp_mode 1/2, in fp32
+ * on the CUDA cores with mode 0) for the appearance list of the workspace: with a channel slice of
+ * the planes and the matching columns of basis_mat these are the partial sums a tensor-parallel
+ * rank contributes (gridnerf_tensor_parallel.py:284-300).  ``features[n_features][app_dim]``
+ * receives the first n_features rows of the list (the caller read the list length from the status
+ * block; negative = max_app rows). */
 int gnr_app_features(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
-                     size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* features, void* stream);
+                     size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* features, int64_t n_features,
+                     void* stream);
 /* Scratch for the two calls below (256-byte aligned, caller-allocated). */
 int gnr_points_scratch_bytes(const GnrModel* m, int64_t n, size_t* bytes_h);
 /* compute_appfeature + MLPRender_Fea at explicit points: ``xyz[n][3]`` normalised, ``view[n][3]``

@@ -735,6 +735,31 @@ extern "C" int gnr_density(GnrModel* m, const float* rays, int64_t n, int S, voi
   return 0;
 }
 
+extern "C" int gnr_march(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                         int64_t max_valid, int64_t max_app, float* weights, float* acc, float* depth,
+                         int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays) {
+    gnr_set_error("gnr_march: null rays");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st));
+  GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st));
+  if (copy_out(weights, ws + L.weight, (size_t)max_valid * 4, st)) return -2;
+  if (copy_out(acc, ws + L.acc, (size_t)n * 4, st)) return -2;
+  if (copy_out(depth, ws + L.depth, (size_t)n * 4, st)) return -2;
+  if (copy_out(app_counts, ws + L.app_counts, (size_t)n * 4, st)) return -2;
+  if (copy_out(app_offsets, ws + L.app_offsets, (size_t)(n + 1) * 4, st)) return -2;
+  if (copy_out(app_index, ws + L.app_index, (size_t)max_app * 4, st)) return -2;
+  return 0;
+}
+
 extern "C" int gnr_weights(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
                            int64_t max_valid, int64_t max_app, float* weights, float* acc, float* depth,
                            int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream) {
@@ -1069,21 +1094,32 @@ extern "C" int gnr_weights_from_sigma(GnrModel* m, int64_t n, int S, void* works
 }
 
 extern "C" int gnr_app_features(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
-                                int64_t max_valid, int64_t max_app, float* features, void* stream) {
+                                int64_t max_valid, int64_t max_app, float* features, int64_t n_features, void* stream) {
   int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
   if (rc) return rc;
-  if (!rays || !features) {
-    gnr_set_error("gnr_app_features: null rays or features");
+  if (!rays || !features || n_features > max_app) {
+    gnr_set_error("gnr_app_features: null rays or features, or more rows asked for than the list can hold");
     return -1;
   }
+  const int64_t rows = n_features < 0 ? max_app : n_features;
+  if (rows == 0) return 0;
   DeviceGuard g(m->device);
   cudaStream_t st = (cudaStream_t)stream;
   char* ws = (char*)workspace;
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
   GnrSampleParams p = gnr_sample_params(m, S);
-  GNR_LAUNCH_OK(launch_app_gather(m, p, gnr_coords_app(rays, ws, L), L.feat_stride, (float*)(ws + L.app_feat), st));
+  const GnrCoords c = gnr_coords_app(rays, ws, L);
+  if (gnr_tc_basis_fused(m)) {
+    // tensor-core path: fp16 product tiles, then the projection alone (tcgen05, fp32 accumulate)
+    unsigned char* hi = (unsigned char*)(ws + L.app_prod);
+    GNR_LAUNCH_OK(launch_app_products(m, p, c, hi, hi + L.app_prod_image, L.app_prod_tile, m->cfg.mlp_mode == 1 ? 2 : 1, st));
+    GNR_LAUNCH_OK(launch_mlp_tc(m, p, c, L.feat_stride, nullptr, (float*)(ws + L.app_feat), hi, hi + L.app_prod_image,
+                                L.app_prod_tile, (float*)(ws + L.app_rgb), (int32_t*)(ws + L.status), 0, st, /*basis_only=*/1));
+  } else {
+    GNR_LAUNCH_OK(launch_app_gather(m, p, c, L.feat_stride, (float*)(ws + L.app_feat), st));
+  }
   GNR_CUDA_OK(cudaMemcpy2DAsync(features, (size_t)m->cfg.app_dim * 4, ws + L.app_feat, (size_t)L.feat_stride * 4,
-                                (size_t)m->cfg.app_dim * 4, (size_t)max_app, cudaMemcpyDeviceToDevice, st));
+                                (size_t)m->cfg.app_dim * 4, (size_t)rows, cudaMemcpyDeviceToDevice, st));
   return 0;
 }
 

@@ -155,7 +155,7 @@ int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords
 // (fused variant); prod_*: product tiles (fused variant); status: 8-word block for the wait flag.
 int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat_in,
                   float* feat_out, const unsigned char* prod_hi, const unsigned char* prod_lo, int tile_bytes, float* rgb,
-                  int32_t* status, int force_unfused, cudaStream_t st);
+                  int32_t* status, int force_unfused, cudaStream_t st, int basis_only = 0);
 int launch_composite(const GnrModel* m, int64_t n, int white_bg, char* ws, const GnrWs& L, float* rgb_map,
                      float* depth_map, cudaStream_t st);
 int launch_exclusive_scan(const int32_t* counts, int32_t* offsets, int32_t* block_sums, int64_t n,

@@ -262,6 +262,7 @@ struct TcArgs {
   float* rgb_out;
   int32_t* status;
   int kbits;
+  int basis_only;                 // stop after the projection: feat_out receives F and nothing else runs
 };
 
 template <int TA, int NSLOT, bool BASIS>
@@ -387,6 +388,16 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
         float4* fo = reinterpret_cast<float4*>(a.feat_out + (size_t)j * FEAT_STRIDE);
 #pragma unroll
         for (int q = 0; q < FEAT_STRIDE / 4; ++q) fo[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      }
+      if (a.basis_only) {
+        // partial projection for channel-parallel rendering: the operand buffer is free as soon as
+        // the basis MMAs have completed, so the next tile's products can come in right away
+        if (tile + tile_stride < n_tiles) {
+          if (row == 0) start_copy(tile + tile_stride);
+          copy_pending = true;
+        }
+        tc_fence_before();  // F was read from tensor memory; the next tile's MMAs overwrite it
+        continue;
       }
     } else {
       if (live) {
@@ -717,7 +728,7 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
 
 int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat_in,
                   float* feat_out, const unsigned char* prod_hi, const unsigned char* prod_lo, int tile_bytes, float* rgb,
-                  int32_t* status, int force_unfused, cudaStream_t st) {
+                  int32_t* status, int force_unfused, cudaStream_t st, int basis_only) {
   if (!m->mlp.tc_image) {
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
@@ -743,6 +754,11 @@ int launch_mlp_tc(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& 
   a.rgb_out = rgb;
   a.status = status;
   a.kbits = p.kbits;
+  a.basis_only = (basis_only && fused) ? 1 : 0;
+  if (basis_only && !fused) {
+    gnr_set_error("the projection-only launch needs the fused tensor-core path");
+    return -1;
+  }
   if (m->cfg.mlp_mode == 1) return fused ? launch_variant<2, 1, true>(m, a, st) : launch_variant<2, 1, false>(m, a, st);
   if (m->cfg.mlp_mode == 2) return fused ? launch_variant<1, 3, true>(m, a, st) : launch_variant<1, 3, false>(m, a, st);
   gnr_set_error("unknown mlp_mode %d", m->cfg.mlp_mode);

@@ -133,6 +133,16 @@ class _Chunk:
         check(lib.gnr_density(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
                               None, None, _stream()), "gnr_density")
 
+    def march(self):
+        """Density + weights + appearance compaction in the fused pass (a field held whole by this model)."""
+        self.app_index = torch.empty(self.max_app, dtype=torch.int32, device=self.m.device)
+        check(lib.gnr_march(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                            self.max_app, None, None, None, None, None, _ptr(self.app_index), _stream()), "gnr_march")
+        st = self.m.read_status(self.ws)
+        self.m.raise_on_status(st)
+        self.num_app = int(st[_lib.ST_NUM_APP])
+        self.app_index = self.app_index[: self.num_app].to(torch.int64)
+
     def positions(self):
         xyz = torch.empty((self.max_valid, 3), dtype=torch.float32, device=self.m.device)
         ray = torch.empty((self.max_valid,), dtype=torch.int32, device=self.m.device)
@@ -162,10 +172,11 @@ class _Chunk:
         return (ids[self.app_index] >> self.kbits)
 
     def app_features(self) -> torch.Tensor:
-        feat = torch.empty((self.max_app, self.m.app_dim), dtype=torch.float32, device=self.m.device)
-        check(lib.gnr_app_features(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
-                                   self.max_app, _ptr(feat), _stream()), "gnr_app_features")
-        return feat[: self.num_app]
+        feat = torch.empty((self.num_app, self.m.app_dim), dtype=torch.float32, device=self.m.device)
+        if self.num_app:
+            check(lib.gnr_app_features(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes,
+                                       self.max_valid, self.max_app, _ptr(feat), self.num_app, _stream()), "gnr_app_features")
+        return feat
 
     def composite(self, rgb_samples: torch.Tensor, white_bg: bool):
         rgb = torch.empty((self.n, 3), dtype=torch.float32, device=self.m.device)
@@ -265,8 +276,11 @@ class ChannelParallelRenderer:
             with torch.cuda.device(m.device):
                 ch = _Chunk(m, r, n_samples)
                 ch.sample()
-                ch.density()
-                ch.weights()
+                if m.ert_transmittance >= 0.0:
+                    ch.march()  # density is replicated: the fused pass of the single-GPU renderer
+                else:
+                    ch.density()
+                    ch.weights()
                 chunks.append(ch)
         m_a = chunks[0].num_app
         if any(ch.num_app != m_a for ch in chunks):

@@ -38,7 +38,7 @@ def _model(spec, ckpt, device, mlp_mode, **extra):
     return m
 
 
-def build_blocks(world: int, rank_list, device: str, mlp_mode: int, grid_scale: int = 1):
+def build_blocks(world: int, rank_list, device: str, mlp_mode: int, grid_scale: int = 1, **model_extra):
     """Sampler (global box + mask) and the owned block fields for the ranks in ``rank_list``."""
     px, py = DIVISIONS[world]
     block = scenes.city_spec(scale=grid_scale).lit()
@@ -55,14 +55,14 @@ def build_blocks(world: int, rank_list, device: str, mlp_mode: int, grid_scale: 
     for r in rank_list:
         samplers.append(_model(gspec, gck, device, 0, field_grid=(2, 2, 2)))
         sd = scenes.make_state_dict(block, seed=scenes.FIELD_SEED + 1000 * (r + 1), device=device)
-        owners.append(_model(block, {"kwargs": scenes.model_kwargs(block), "state_dict": sd}, device, mlp_mode))
+        owners.append(_model(block, {"kwargs": scenes.model_kwargs(block), "state_dict": sd}, device, mlp_mode, **model_extra))
         del sd
         torch.cuda.empty_cache()
     pose = scenes.make_pose(gspec, vol)
     return gspec, pose, samplers, owners, (px, py)
 
 
-def build_channels(world: int, rank_list, device: str, mlp_mode: int, grid_scale: int = 1):
+def build_channels(world: int, rank_list, device: str, mlp_mode: int, grid_scale: int = 1, **model_extra):
     """Channel-sliced models (48 appearance channels each) for the ranks in ``rank_list``."""
     spec = scenes.city_spec(scale=grid_scale).lit()
     vol = scenes.make_alpha_volume(spec)
@@ -80,27 +80,29 @@ def build_channels(world: int, rank_list, device: str, mlp_mode: int, grid_scale
         sd["basis_mat.weight"] = ((torch.rand((spec.app_dim, 3 * 48), generator=gw) * 2 - 1) * bound).to(device)
         ck = {"kwargs": scenes.model_kwargs(spec), "state_dict": sd, "alphaMask.shape": tuple(vol.shape),
               "alphaMask.mask": np.packbits(vol.numpy().reshape(-1)), "alphaMask.aabb": torch.tensor(spec.aabb)}
-        models.append(_model(spec, ck, device, mlp_mode))
+        models.append(_model(spec, ck, device, mlp_mode, **model_extra))
         del sd
         torch.cuda.empty_cache()
     return spec, scenes.make_pose(spec, vol), models
 
 
 def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank: int, world: int, device: str,
-        grid_scale: int = 1, check: bool = False) -> Dict:
+        grid_scale: int = 1, check: bool = False, ert: float = 0.0, app_fp16: bool = False) -> Dict:
     """Render ``steps`` frames; returns timing and sample statistics (rank 0's view)."""
     import torch.distributed as dist
 
     comm = DistComm() if world > 1 else LoopbackComm(1)
     H, W = 1080, 1920
     if workload == "city_blocks":
-        spec, pose, samplers, owners, division = build_blocks(world, [rank], device, mlp_mode, grid_scale)
+        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2)}
+        spec, pose, samplers, owners, division = build_blocks(world, [rank], device, mlp_mode, grid_scale, **extra)
         ren = BlockParallelRenderer(samplers, owners, comm, division)
         shard = TileSharding(H, W, rank, world, device)
         rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=shard.pixel_ids)
         parallelism = f"blocks {division[0]}x{division[1]} (all-to-all sample routing) + ray tiles x{world}"
     elif workload == "city_channels":
-        spec, pose, models = build_channels(world, [rank], device, mlp_mode, grid_scale)
+        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2), "ert_transmittance": float(ert)}
+        spec, pose, models = build_channels(world, [rank], device, mlp_mode, grid_scale, **extra)
         ren = ChannelParallelRenderer(models, comm)
         shard = TileSharding(H, W, 0, 1, device)  # every rank walks the whole frame
         rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=shard.pixel_ids)
@@ -160,7 +162,7 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
            "image_mean": float(image.mean().item()), "rays": H * W}
     if check and workload == "city_blocks" and rank == 0 and world > 1:
         # rank 0 re-renders its own rays with every block held locally (loopback); the bits must agree
-        _, _, s_all, o_all, division = build_blocks(world, list(range(world)), device, mlp_mode, grid_scale)
+        _, _, s_all, o_all, division = build_blocks(world, list(range(world)), device, mlp_mode, grid_scale, **extra)
         lb = BlockParallelRenderer(s_all, o_all, LoopbackComm(world), division)
         sub = rays[: min(n_local, 20000)]
         parts = [sub] + [sub[:1]] * (world - 1)
