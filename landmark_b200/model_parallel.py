@@ -333,9 +333,14 @@ def assign_blocks(xyz: torch.Tensor, division: Tuple[int, int]):
 
 
 def _route(owner: torch.Tensor, world: int):
-    order = torch.argsort(owner, stable=True)
-    counts = torch.bincount(owner, minlength=world).cpu().tolist()
-    return order, [int(c) for c in counts]
+    """Stable grouping of the samples by owner: ``order`` lists the sample indices owner by owner,
+    ``counts[d]`` how many go to rank ``d``.  A handful of owners: one compaction per owner beats a
+    radix sort plus an atomics histogram (one bin takes most samples when a camera looks at one block)."""
+    if world > 16:
+        order = torch.argsort(owner, stable=True)
+        return order, [int(c) for c in torch.bincount(owner, minlength=world).cpu().tolist()]
+    parts = [(owner == d).nonzero(as_tuple=True)[0] for d in range(world)]
+    return (torch.cat(parts) if world > 1 else parts[0]), [int(p.numel()) for p in parts]
 
 
 class BlockParallelRenderer:
