@@ -1,7 +1,12 @@
-// VM feature gather: bilinear plane x linear line, channel-last, 128-bit loads.
+// VM feature gather: bilinear plane x linear line, channel-last planes.
 //
-// Four lanes share one sample; lane c4 owns channels {16 j + 4 c4 .. +3 : j < J}, so one load
-// instruction of a warp reads 8 samples x 64 contiguous bytes.  Interpolation follows
+// Two families of kernels.  The general ones (density_kernel, app_gather_kernel,
+// app_products_kernel; any channel count, list or point mode) let four lanes share one sample:
+// lane c4 owns channels {16 j + 4 c4 .. +3 : j < J}, so one 128-bit load instruction of a warp reads
+// 8 samples x 64 contiguous bytes.  The ones the frame loop runs (march_kernel,
+// app_products_thread_kernel) give a whole sample to one thread and neighbouring rays to the lanes
+// of a warp, with 256-bit loads; per sample they perform the same operations in the same order as
+// the four-lane kernels, so both families give the same bits.  Interpolation follows
 // F.grid_sample(mode="bilinear", padding_mode="zeros", align_corners=True) as called by
 // compute_densityfeature / compute_appfeature (app/models/gridnerf_sequential.py:779-871):
 // index = ((x + 1) / 2) * (size - 1); the weight of a corner is the product of the distances
