@@ -101,55 +101,13 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
   pair_products_tap<J>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), c4, prod);
 }
 
-// fp16 storage (48 channels, 96-byte texels): lane c4 owns channels 8 c4 .. 8 c4 + 7 (one 16-byte
-// load) and 32 + 4 c4 .. 32 + 4 c4 + 3 (one 8-byte load); prod[0], prod[1] are the first eight,
-// prod[2] the last four.  Interpolation and product are in fp32 as in pair_products_tap.
-__device__ __forceinline__ void load_texel_h48(const unsigned char* base, uint32_t texel, int c4, float4 (&v)[3]) {
-  const unsigned char* t = base + (size_t)texel * 96u;
-  const uint4 a = __ldg(reinterpret_cast<const uint4*>(t) + c4);
-  const uint2 b = __ldg(reinterpret_cast<const uint2*>(t + 64) + c4);
-  const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
-  const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&a.z)), a3 = __half22float2(*reinterpret_cast<const __half2*>(&a.w));
-  const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x)), b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
-  v[0] = make_float4(a0.x, a0.y, a1.x, a1.y);
-  v[1] = make_float4(a2.x, a2.y, a3.x, a3.y);
-  v[2] = make_float4(b0.x, b0.y, b1.x, b1.y);
-}
-
-__device__ __forceinline__ void pair_products_tap_h48(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, int c4, float4 (&prod)[3]) {
-  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
-  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
-  const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
-  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0;
-  const unsigned char* pb = reinterpret_cast<const unsigned char*>(pl.plane);
-  const unsigned char* lb = reinterpret_cast<const unsigned char*>(pl.line);
-  float4 v_nw[3], v_ne[3], v_sw[3], v_se[3], v_l0[3], v_l1[3];
-  load_texel_h48(pb, nw, c4, v_nw);
-  load_texel_h48(pb, nw + 1u, c4, v_ne);
-  load_texel_h48(pb, nw + (uint32_t)pl.W, c4, v_sw);
-  load_texel_h48(pb, nw + (uint32_t)pl.W + 1u, c4, v_se);
-  load_texel_h48(lb, (uint32_t)tl.i0, c4, v_l0);
-  load_texel_h48(lb, (uint32_t)tl.i0 + 1u, c4, v_l1);
-#pragma unroll
-  for (int j = 0; j < 3; ++j) {
-    float4 pv = f4_scale(v_nw[j], w_nw);
-    pv = f4_fma(v_ne[j], w_ne, pv);
-    pv = f4_fma(v_sw[j], w_sw, pv);
-    pv = f4_fma(v_se[j], w_se, pv);
-    const float4 lv = f4_fma(v_l1[j], al1, f4_scale(v_l0[j], al0));
-    prod[j] = f4_mul(pv, lv);
-  }
-}
-
 // The three plane/line pairs of one sample.  NP == 3 is the standard VM layout (pairs
 // (x,y|z), (x,z|y), (y,z|x) on one grid, verified by the host): its nine coordinate lookups
 // collapse into three.  NP == 0 walks planes.n pairs generically.
-template <int J, int NP, bool HALF = false, class F>
+template <int J, int NP, class F>
 __device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, float y, float z, int c4, F&& f) {
-  static_assert(!HALF || J == 3, "fp16 storage is implemented for 48 channels");
   auto one = [&](const GnrPlane& pl, Tap ta, Tap tb, Tap tl, float4(&prod)[J]) {
-    if constexpr (HALF) pair_products_tap_h48(pl, ta, tb, tl, c4, prod);
-    else pair_products_tap<J>(pl, ta, tb, tl, c4, prod);
+    pair_products_tap<J>(pl, ta, tb, tl, c4, prod);
   };
   if (NP == 3) {
     const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
@@ -478,9 +436,8 @@ app_gather_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, const float
 // One more 16-byte group per row, after the products (k group `view_group`), carries the
 // sample's view direction for the MLP kernel as fp16 pairs {hi x, hi y, hi z, lo x, lo y, lo z}:
 // hi + lo restores the fp32 value to about 2^-22, and the MLP kernel needs no list lookups.
-// HALF: the planes are held as fp16 (load_texel_h48) and the lane's twelve channels are
-// 8 c4 .. 8 c4 + 7 and 32 + 4 c4 .. + 3: one 16-byte and one 8-byte store per pair.
-template <int J, int NP, int TA, bool HALF = false>
+// (fp32 planes only; fp16 storage goes through app_products_thread_kernel.)
+template <int J, int NP, int TA>
 __global__ void __launch_bounds__(kBlock)
 app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
                     unsigned char* __restrict__ prod_lo, int tile_bytes, int view_group) {
@@ -508,24 +465,7 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
       vv.w = 0u;
       *reinterpret_cast<uint4*>(prod_hi + (size_t)tile * tile_bytes + (size_t)view_group * 2048 + (size_t)row * 16) = vv;
     }
-    for_each_pair<J, NP, HALF>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
-      if constexpr (HALF) {
-        unsigned char* row_base = prod_hi + (size_t)tile * tile_bytes + (size_t)row * 16;
-        const __half2 h0 = __floats2half2_rn(prod[0].x, prod[0].y), h1 = __floats2half2_rn(prod[0].z, prod[0].w);
-        const __half2 h2 = __floats2half2_rn(prod[1].x, prod[1].y), h3 = __floats2half2_rn(prod[1].z, prod[1].w);
-        const __half2 h4 = __floats2half2_rn(prod[2].x, prod[2].y), h5 = __floats2half2_rn(prod[2].z, prod[2].w);
-        uint4 va;
-        va.x = *reinterpret_cast<const uint32_t*>(&h0);
-        va.y = *reinterpret_cast<const uint32_t*>(&h1);
-        va.z = *reinterpret_cast<const uint32_t*>(&h2);
-        va.w = *reinterpret_cast<const uint32_t*>(&h3);
-        uint2 vb;
-        vb.x = *reinterpret_cast<const uint32_t*>(&h4);
-        vb.y = *reinterpret_cast<const uint32_t*>(&h5);
-        *reinterpret_cast<uint4*>(row_base + (size_t)(pi * 6 + c4) * 2048) = va;
-        *reinterpret_cast<uint2*>(row_base + (size_t)(pi * 6 + 4 + (c4 >> 1)) * 2048 + (size_t)(c4 & 1) * 8) = vb;
-        return;
-      }
+    for_each_pair<J, NP>(planes, x, y, z, c4, [&](int pi, const float4(&prod)[J]) {
 #pragma unroll
       for (int j = 0; j < J; ++j) {
         const size_t at = out0 + (size_t)(pi * 2 * J + 2 * j + (c4 >> 1)) * 2048;
