@@ -60,7 +60,11 @@ typedef struct GnrConfig {
                                density and weights kernels instead of the fused pass.             */
   int32_t app_storage;      /* 0 = appearance planes and lines held as fp32; 1 = held as fp16 (half the
                                gather traffic; the products they feed are rounded to fp16 for the
-                               tensor cores anyway).  1 needs mlp_mode 2 and 33..48 appearance channels. */
+                               tensor cores anyway).  The reference's half_precision_param does this to
+                               the planes of its tensor-parallel model
+                               (dist_render/ddp_infer/inferer_impl.py:263-267; there the density planes
+                               too, here they stay fp32).  1 needs mlp_mode 2 and 33..48 appearance
+                               channels. */
   int32_t reserved[5];
 } GnrConfig;
 

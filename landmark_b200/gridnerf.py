@@ -153,8 +153,10 @@ class B200GridNeRF(torch.nn.Module):
         self.mlp_mode = int(mlp_mode)
         # early ray termination of the density pass (see GnrConfig.ert_transmittance); 0 = exact
         self.ert_transmittance = float(ert_transmittance)
-        # appearance planes and lines held as fp16 in the library (GnrConfig.app_storage); mlp_mode 2 only
-        self.app_plane_fp16 = bool(app_plane_fp16)
+        # appearance planes and lines held as fp16 in the library (GnrConfig.app_storage); mlp_mode 2 only.
+        # args.half_precision_param is the reference's switch for half planes (inferer_impl.py:263-267).
+        self.app_plane_fp16 = bool(app_plane_fp16) or (bool(getattr(args, "half_precision_param", False))
+                                                       and int(mlp_mode) == 2)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
