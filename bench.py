@@ -190,6 +190,8 @@ def main():
                     help="skip the second measurement with every approximation off (fp32 MLP, fp32 planes, no termination)")
     ap.add_argument("--app-fp16", type=int, default=1, choices=(0, 1),
                     help="hold the appearance planes as fp16 in HBM (mlp_mode 2 only)")
+    ap.add_argument("--den-fp16", type=int, default=0, choices=(0, 1),
+                    help="hold the density planes and lines as fp16 in HBM as well")
     ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
@@ -245,7 +247,8 @@ def main():
     spec, ckpt, pose = build_scene(a.workload, device, a.frame)
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
-    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16))
+    model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16),
+                         density_plane_fp16=bool(a.den_fp16))
     model.load(ckpt)
     if a.reload_test:
         from landmark_b200.dynamic import pin_block
@@ -397,7 +400,7 @@ def main():
     strict = None
     if world == 1 and not a.no_strict:
         _, ckpt2, _ = build_scene(a.workload, device, a.frame)
-        m2 = B200GridNeRF(**kwargs, mlp_mode=0, ert_transmittance=0.0, app_plane_fp16=False)
+        m2 = B200GridNeRF(**kwargs, mlp_mode=0, ert_transmittance=0.0, app_plane_fp16=False, density_plane_fp16=False)
         m2.load(ckpt2)
         m2.release_torch_planes()
         del ckpt2
@@ -453,11 +456,12 @@ def main():
     app_bytes = APP_BYTES_PER_SAMPLE if not a.app_fp16 else 1164
     app_l1_bytes = APP_L1_BYTES_PER_SAMPLE // (2 if a.app_fp16 else 1)
     if per_launch["density"] > 0:
-        ach = n_density * DENSITY_BYTES_PER_SAMPLE / (per_launch["density"] * 1e-3) / 1e9
+        den_bytes = DENSITY_BYTES_PER_SAMPLE if not a.den_fp16 else 400  # 3 x 4 x 16 ch x 2 B + 12 B + 4 B
+        ach = n_density * den_bytes / (per_launch["density"] * 1e-3) / 1e9
         roof["density_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                   "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"],
                                   "samples_gathered": n_density,
-                                  "l1_to_register": l1_roof(DENSITY_L1_BYTES_PER_SAMPLE, n_density, per_launch["density"]),
+                                  "l1_to_register": l1_roof(DENSITY_L1_BYTES_PER_SAMPLE // (2 if a.den_fp16 else 1), n_density, per_launch["density"]),
                                   "note": "fused density gather + transmittance product (march_kernel)" if a.ert >= 0 else "density_kernel"}
     if per_launch["app_gather"] > 0 and n_app > 0:
         ach = n_app * app_bytes / (per_launch["app_gather"] * 1e-3) / 1e9
@@ -495,6 +499,7 @@ def main():
                    "parallelism": f"tiles{TILE}x{TILE} round-robin x{world}" if world > 1 or a.order == "tiles" else "rows",
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
+                   "density_plane_storage": "fp16" if a.den_fp16 else "fp32",
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,

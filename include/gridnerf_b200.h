@@ -65,7 +65,10 @@ typedef struct GnrConfig {
                                (dist_render/ddp_infer/inferer_impl.py:263-267; there the density planes
                                too, here they stay fp32).  1 needs mlp_mode 2 and 33..48 appearance
                                channels. */
-  int32_t reserved[5];
+  int32_t den_storage;      /* the same for the density planes and lines (the other half of the
+                               reference's half_precision_param); any mlp_mode; 16 (padded) density
+                               channels.  Sample sets do not depend on it; rgb moves by a few 1e-6. */
+  int32_t reserved[4];
 } GnrConfig;
 
 /* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */

@@ -42,7 +42,8 @@ class GnrConfig(C.Structure):
         ("sampling_mode", C.c_int32),
         ("ert_transmittance", C.c_float),
         ("app_storage", C.c_int32),
-        ("reserved", C.c_int32 * 5),
+        ("den_storage", C.c_int32),
+        ("reserved", C.c_int32 * 4),
     ]
 
 

@@ -198,6 +198,11 @@ extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
                   cfg->app_storage, cfg->mlp_mode, cfg->n_app);
     return -1;
   }
+  if (cfg->den_storage != 0 && (cfg->den_storage != 1 || cfg->n_density > 16)) {
+    gnr_set_error("gnr_create: den_storage %d: fp16 density planes are implemented for up to 16 channels (got %d)",
+                  cfg->den_storage, cfg->n_density);
+    return -1;
+  }
   if (cfg->fea_pe < 0 || cfg->fea_pe > 8 || cfg->view_pe < 0 || cfg->view_pe > 8) {
     gnr_set_error("gnr_create: fea_pe %d / view_pe %d outside [0, 8]", cfg->fea_pe, cfg->view_pe);
     return -1;
@@ -293,7 +298,7 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
   float** buf = kind == 0 ? &m->den_plane_buf[idx] : &m->app_plane_buf[idx];
   GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
   const long long P = (long long)H * W;
-  const bool half = kind == 1 && m->cfg.app_storage == 1;
+  const bool half = (kind == 1 && m->cfg.app_storage == 1) || (kind == 0 && m->cfg.den_storage == 1);
   const size_t need = (size_t)P * Cp * (half ? sizeof(__half) : sizeof(float));
   if (*buf == nullptr || m->plane_bytes[kind][idx] != need) {
     free_dev(*buf);
@@ -337,7 +342,7 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   const int Cp = padded_channels(C);
   float** buf = kind == 0 ? &m->den_line_buf[idx] : &m->app_line_buf[idx];
   GnrPlane* pl = kind == 0 ? &m->den[idx] : &m->app[idx];
-  const bool half = kind == 1 && m->cfg.app_storage == 1;
+  const bool half = (kind == 1 && m->cfg.app_storage == 1) || (kind == 0 && m->cfg.den_storage == 1);
   const size_t need = (size_t)Ln * Cp * (half ? sizeof(__half) : sizeof(float));
   if (*buf == nullptr || m->line_bytes[kind][idx] != need) {
     free_dev(*buf);

@@ -63,26 +63,36 @@ __device__ __forceinline__ Tap make_tap(float u, float fsize, int size) {
   return t;
 }
 
-template <int J>
+// The four channels 16 j + 4 c4 .. + 3 of texel `texel` (C channels per texel) from an fp32 or an
+// fp16 array.
+template <bool HALF>
+__device__ __forceinline__ float4 load4(const float* base, uint32_t texel, uint32_t C, int c4, int j) {
+  if constexpr (HALF) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(base) + ((texel * C) >> 2) + c4 + 4 * j);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  } else {
+    return __ldg(reinterpret_cast<const float4*>(base) + ((texel * C) >> 2) + c4 + 4 * j);
+  }
+}
+
+template <int J, bool HALF = false>
 __device__ __forceinline__ void pair_products_tap(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, int c4, float4 (&prod)[J]) {
   const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
   const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
   const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
-  const uint32_t c4n = (uint32_t)pl.C >> 2;
-  const uint32_t nw = ((uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0) * c4n + (uint32_t)c4;
-  const uint32_t sw = nw + (uint32_t)pl.W * c4n;
-  const uint32_t ln = (uint32_t)tl.i0 * c4n + (uint32_t)c4;
-  const float4* pb = reinterpret_cast<const float4*>(pl.plane);
-  const float4* lb = reinterpret_cast<const float4*>(pl.line);
+  const uint32_t C = (uint32_t)pl.C;
+  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0, sw = nw + (uint32_t)pl.W;
+  const uint32_t ln = (uint32_t)tl.i0;
   float4 v_nw[J], v_ne[J], v_sw[J], v_se[J], v_l0[J], v_l1[J];
 #pragma unroll
   for (int j = 0; j < J; ++j) {
-    v_nw[j] = __ldg(pb + nw + 4 * j);
-    v_ne[j] = __ldg(pb + nw + c4n + 4 * j);
-    v_sw[j] = __ldg(pb + sw + 4 * j);
-    v_se[j] = __ldg(pb + sw + c4n + 4 * j);
-    v_l0[j] = __ldg(lb + ln + 4 * j);
-    v_l1[j] = __ldg(lb + ln + c4n + 4 * j);
+    v_nw[j] = load4<HALF>(pl.plane, nw, C, c4, j);
+    v_ne[j] = load4<HALF>(pl.plane, nw + 1u, C, c4, j);
+    v_sw[j] = load4<HALF>(pl.plane, sw, C, c4, j);
+    v_se[j] = load4<HALF>(pl.plane, sw + 1u, C, c4, j);
+    v_l0[j] = load4<HALF>(pl.line, ln, C, c4, j);
+    v_l1[j] = load4<HALF>(pl.line, ln + 1u, C, c4, j);
   }
 #pragma unroll
   for (int j = 0; j < J; ++j) {
@@ -104,10 +114,10 @@ __device__ __forceinline__ void pair_products(const GnrPlane& pl, float x, float
 // The three plane/line pairs of one sample.  NP == 3 is the standard VM layout (pairs
 // (x,y|z), (x,z|y), (y,z|x) on one grid, verified by the host): its nine coordinate lookups
 // collapse into three.  NP == 0 walks planes.n pairs generically.
-template <int J, int NP, class F>
+template <int J, int NP, bool HALF = false, class F>
 __device__ __forceinline__ void for_each_pair(const PlaneSet& planes, float x, float y, float z, int c4, F&& f) {
   auto one = [&](const GnrPlane& pl, Tap ta, Tap tb, Tap tl, float4(&prod)[J]) {
-    pair_products_tap<J>(pl, ta, tb, tl, c4, prod);
+    pair_products_tap<J, HALF>(pl, ta, tb, tl, c4, prod);
   };
   if (NP == 3) {
     const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
@@ -147,20 +157,37 @@ __device__ __forceinline__ F8 ldg8(const float* ptr) {
 // 16 j + 4 c .. 16 j + 4 c + 3, with the operations and the order the four lanes of a quad use in
 // pair_products_tap / density_kernel, so that a sample's density feature has the same bits
 // whichever kernel computes it.
-template <int J>
+// Eight consecutive channels starting at channel 8 h of a texel, fp32 (one 256-bit load) or fp16 (one
+// 128-bit load).
+template <bool HALF>
+__device__ __forceinline__ F8 load8c(const float* base, uint32_t texel, uint32_t C, int h) {
+  if constexpr (HALF) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(base) + ((texel * C) >> 3) + h);
+    const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+    const float2 a2 = __half22float2(*reinterpret_cast<const __half2*>(&a.z)), a3 = __half22float2(*reinterpret_cast<const __half2*>(&a.w));
+    F8 r;
+    r.lo = make_float4(a0.x, a0.y, a1.x, a1.y);
+    r.hi = make_float4(a2.x, a2.y, a3.x, a3.y);
+    return r;
+  } else {
+    return ldg8(base + (size_t)texel * C + 8 * h);
+  }
+}
+
+template <int J, bool HALF = false>
 __device__ __forceinline__ void pair_sums_thread(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, float (&part)[4]) {
   const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
   const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
   const float w_nw = ax0 * ay0, w_ne = ax1 * ay0, w_sw = ax0 * ay1, w_se = ax1 * ay1;
   constexpr uint32_t C = 16u * J;
-  const float* pn = pl.plane + ((uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0) * C;
-  const float* ps = pn + (uint32_t)pl.W * C;
-  const float* ln = pl.line + (uint32_t)tl.i0 * C;
+  const uint32_t nw_t = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0, sw_t = nw_t + (uint32_t)pl.W;
+  const uint32_t l_t = (uint32_t)tl.i0;
   float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
   for (int h = 0; h < 2 * J; ++h) {  // 8 channels per round: quarters 2 (h & 1) and 2 (h & 1) + 1 of group j = h >> 1
-    const F8 v_nw = ldg8(pn + 8 * h), v_ne = ldg8(pn + C + 8 * h), v_sw = ldg8(ps + 8 * h), v_se = ldg8(ps + C + 8 * h);
-    const F8 v_l0 = ldg8(ln + 8 * h), v_l1 = ldg8(ln + C + 8 * h);
+    const F8 v_nw = load8c<HALF>(pl.plane, nw_t, C, h), v_ne = load8c<HALF>(pl.plane, nw_t + 1u, C, h);
+    const F8 v_sw = load8c<HALF>(pl.plane, sw_t, C, h), v_se = load8c<HALF>(pl.plane, sw_t + 1u, C, h);
+    const F8 v_l0 = load8c<HALF>(pl.line, l_t, C, h), v_l1 = load8c<HALF>(pl.line, l_t + 1u, C, h);
 #pragma unroll
     for (int q = 0; q < 2; ++q) {
       const float4 nw = q ? v_nw.hi : v_nw.lo, ne = q ? v_ne.hi : v_ne.lo, sw = q ? v_sw.hi : v_sw.lo, se = q ? v_se.hi : v_se.lo;
@@ -179,21 +206,21 @@ __device__ __forceinline__ void pair_sums_thread(const GnrPlane& pl, Tap tx, Tap
 }
 
 // Density feature of one sample, computed by one thread.
-template <int J, int NP>
+template <int J, int NP, bool HALF = false>
 __device__ __forceinline__ float density_thread(const PlaneSet& planes, float x, float y, float z) {
   float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   if (NP == 3) {
     const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
     const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
     const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
-    pair_sums_thread<J>(planes.p[0], tx, ty, tz, part);
-    pair_sums_thread<J>(planes.p[1], tx, tz, ty, part);
-    pair_sums_thread<J>(planes.p[2], ty, tz, tx, part);
+    pair_sums_thread<J, HALF>(planes.p[0], tx, ty, tz, part);
+    pair_sums_thread<J, HALF>(planes.p[1], tx, tz, ty, part);
+    pair_sums_thread<J, HALF>(planes.p[2], ty, tz, tx, part);
   } else {
     for (int pi = 0; pi < planes.n; ++pi) {
       const GnrPlane& pl = planes.p[pi];
       const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-      pair_sums_thread<J>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), part);
+      pair_sums_thread<J, HALF>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L), part);
     }
   }
   return (part[0] + part[1]) + (part[2] + part[3]);
@@ -256,7 +283,7 @@ __device__ __forceinline__ void cta_range(long long total, long long& beg, long 
   end = min(total, beg + per * kStep);
 }
 
-template <int J, int NP>
+template <int J, int NP, bool HALF = false>
 __global__ void __launch_bounds__(kBlock)
 density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, int act, float* __restrict__ sigma_feat,
                float* __restrict__ sigma) {
@@ -274,7 +301,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
     if (active) {
       float x, y, z;
       sample_xyz(p, crd, i, x, y, z);
-      for_each_pair<J, NP>(planes, x, y, z, c4, [&](int, const float4(&prod)[J]) {
+      for_each_pair<J, NP, HALF>(planes, x, y, z, c4, [&](int, const float4(&prod)[J]) {
         float s = 0.0f;
 #pragma unroll
         for (int j = 0; j < J; ++j) s += (prod[j].x + prod[j].y) + (prod[j].z + prod[j].w);
@@ -303,7 +330,7 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
 // weights_kernel.
 constexpr int kMarchBlock = 32;  // one warp per CTA: a finished warp frees its slot at once
 
-template <int J, int NP>
+template <int J, int NP, bool HALF = false>
 __global__ void __launch_bounds__(kMarchBlock, 16)
 march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
              const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
@@ -339,7 +366,7 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
         const float x = gnr_normalize(gnr_point(ox, dx, t), p.lo[0], p.inv[0]);
         const float y = gnr_normalize(gnr_point(oy, dy, t), p.lo[1], p.inv[1]);
         const float z = gnr_normalize(gnr_point(oz, dz, t), p.lo[2], p.inv[2]);
-        const float sg = density_activation(density_thread<J, NP>(planes, x, y, z), shift, act);
+        const float sg = density_activation(density_thread<J, NP, HALF>(planes, x, y, z), shift, act);
         const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
         const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-sg, __fmul_rn(dist, distance_scale))));
         const float w = alpha * T;
@@ -658,6 +685,13 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords&
     else                                                                                                              \
       density_kernel<JJ, 0><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma); \
   } while (0)
+  if (m->cfg.den_storage == 1) {  // fp16 planes: 16 channels (checked at creation)
+    if (standard_vm3(set))
+      density_kernel<1, 3, true><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma);
+    else
+      density_kernel<1, 0, true><<<grid, kBlock, 0, st>>>(p, set, c, m->cfg.density_shift, m->cfg.density_act, sigma_feat, sigma);
+    return (int)cudaGetLastError();
+  }
   switch (J) {
     case 1: GNR_DEN(1); break;
     case 2: GNR_DEN(2); break;
@@ -745,13 +779,16 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
   const int J = m->den[0].C / 16;
   const unsigned grid = (unsigned)((n + kMarchBlock - 1) / kMarchBlock);
   const float t_stop = m->cfg.ert_transmittance > 0.0f ? m->cfg.ert_transmittance : 0.0f;
-#define GNR_MARCH(JJ, NPP)                                                                                        \
-  march_kernel<JJ, NPP><<<grid, kMarchBlock, 0, st>>>(                                                            \
+#define GNR_MARCH(JJ, NPP) GNR_MARCH_H(JJ, NPP, false)
+#define GNR_MARCH_H(JJ, NPP, HH)                                                                                  \
+  march_kernel<JJ, NPP, HH><<<grid, kMarchBlock, 0, st>>>(                                                        \
       p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
       (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)
-  if (J == 1 && standard_vm3(set)) GNR_MARCH(1, 3);
+  if (m->cfg.den_storage == 1 && standard_vm3(set)) GNR_MARCH_H(1, 3, true);
+  else if (m->cfg.den_storage == 1) GNR_MARCH_H(1, 0, true);
+  else if (J == 1 && standard_vm3(set)) GNR_MARCH(1, 3);
   else if (J == 1) GNR_MARCH(1, 0);
   else if (J == 2) GNR_MARCH(2, 0);
   else if (J == 3) GNR_MARCH(3, 0);
@@ -761,5 +798,6 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
     return -1;
   }
 #undef GNR_MARCH
+#undef GNR_MARCH_H
   return (int)cudaGetLastError();
 }

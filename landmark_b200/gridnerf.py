@@ -108,6 +108,7 @@ class B200GridNeRF(torch.nn.Module):
         field_grid=None,
         ert_transmittance: float = 0.0,
         app_plane_fp16: bool = False,
+        density_plane_fp16: bool = False,
         **_ignored,
     ):
         super().__init__()
@@ -157,6 +158,8 @@ class B200GridNeRF(torch.nn.Module):
         # args.half_precision_param is the reference's switch for half planes (inferer_impl.py:263-267).
         self.app_plane_fp16 = bool(app_plane_fp16) or (bool(getattr(args, "half_precision_param", False))
                                                        and int(mlp_mode) == 2)
+        # density planes and lines held as fp16 (GnrConfig.den_storage), the other half of that switch
+        self.density_plane_fp16 = bool(density_plane_fp16) or bool(getattr(args, "half_precision_param", False))
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -290,6 +293,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.sampling_mode = 1 if self.sampling_opt else 0
         cfg.ert_transmittance = self.ert_transmittance
         cfg.app_storage = 1 if self.app_plane_fp16 else 0
+        cfg.den_storage = 1 if self.density_plane_fp16 else 0
         return cfg
 
     def commit(self, release_torch_planes: bool = False):

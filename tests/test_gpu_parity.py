@@ -506,3 +506,27 @@ def test_graph_captured_frame_equals_eager_frames():
             assert not torch.equal(rgba, first)  # another pose, another picture
         else:
             first = rgba.clone()
+
+
+def test_fp16_density_planes_option():
+    """density_plane_fp16 (the other half of the reference's half_precision_param): the valid-sample
+    set cannot change (the sampler does not read the density), sigma moves by ~1e-5 relative, so the
+    image stays within 1e-4 except for rays where a weight crosses the appearance threshold."""
+    spec = scenes.tiny_spec().lit()
+    fx = load_golden("tiny_lit.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    rays = torch.from_numpy(fx["rays"]).cuda()
+    for mode in (0, 2):
+        full = cuda_model(spec, ckpt, mlp_mode=mode)
+        half = cuda_model(spec, ckpt, mlp_mode=mode, density_plane_fp16=True)
+        a, _ = full(rays, N_samples=spec.n_samples)
+        b, _ = half(rays, N_samples=spec.n_samples)
+        assert int(half.last_status[2]) == int(full.last_status[2]) == int(fx["valid_counts"].sum())
+        assert abs(int(half.last_status[3]) - int(full.last_status[3])) <= 20
+        err = (a["rgb_map"] - b["rgb_map"]).abs().max(dim=1).values
+        assert 0.0 < float(err.max()) <= FLIP_RGB_TOL and int((err > 2e-5).sum()) <= 10
+        st = half.run_stages(rays, spec.n_samples, True)  # the list-based density kernel reads fp16 too
+        ref = full.run_stages(rays, spec.n_samples, True)
+        d = (st["sigma_feature"] - ref["sigma_feature"]).abs().max().item()
+        assert 0.0 < d <= 2e-4
+        assert (st["rgb_map"] - b["rgb_map"]).abs().max().item() <= FLIP_RGB_TOL
