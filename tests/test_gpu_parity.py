@@ -530,3 +530,23 @@ def test_fp16_density_planes_option():
         d = (st["sigma_feature"] - ref["sigma_feature"]).abs().max().item()
         assert 0.0 < d <= 2e-4
         assert (st["rgb_map"] - b["rgb_map"]).abs().max().item() <= FLIP_RGB_TOL
+
+
+@pytest.mark.parametrize("mlp_mode", [0, 2])
+def test_ragged_ray_counts_give_the_same_pixels(mlp_mode):
+    """Ray counts that do not fill a warp, a 32-ray group or a 128-sample tile: every ray's pixel is
+    what the same ray gets inside the full chunk (the kernels group rays by 32 and samples by 128,
+    but no result depends on a ray's neighbours)."""
+    spec = scenes.tiny_spec().lit()
+    model = cuda_model(spec, mlp_mode=mlp_mode)
+    rays = tiny_rays(spec).cuda()
+    full, _ = model(rays, N_samples=spec.n_samples)
+    for start, count in ((0, 1), (4321, 31), (77, 33), (5000, 100), (9990, 10), (1234, 257)):
+        part, _ = model(rays[start:start + count].contiguous(), N_samples=spec.n_samples)
+        assert part["rgb_map"].shape == (count, 3)
+        assert torch.equal(part["rgb_map"], full["rgb_map"][start:start + count]), (start, count)
+        assert torch.equal(part["depth_map"], full["depth_map"][start:start + count]), (start, count)
+    # a ray that misses the box entirely, alone
+    miss = torch.tensor([[3.0, 3.0, 3.0, 1.0, 0.0, 0.0]], device="cuda")
+    out, _ = model(miss, N_samples=spec.n_samples)
+    assert torch.equal(out["rgb_map"].cpu(), torch.ones((1, 3))) and float(out["depth_map"][0]) == 0.0
