@@ -76,11 +76,17 @@ class TileSharding:
             dist.all_gather_into_tensor(all_pix, pad, group=group)
             self.keep = all_pix >= 0
             self.all_pixels = all_pix[self.keep]
+            rows = self.keep.nonzero(as_tuple=True)[0]
             self.gathered = torch.empty((world * self.n_pad, 3), dtype=torch.float32, device=device)
         else:
             self.keep = None
             self.all_pixels = self.pixel_ids.to(torch.int64)
+            rows = torch.arange(self.n_local, dtype=torch.int64, device=device)
             self.gathered = None
+        # pixel -> row of the gathered colour buffer: assembling a frame is one gather with
+        # coalesced writes and no host synchronisation
+        self.src_for_pixel = torch.empty((H * W,), dtype=torch.int64, device=device)
+        self.src_for_pixel[self.all_pixels] = rows
 
     def assemble(self, rgb_padded: torch.Tensor, image: torch.Tensor) -> torch.Tensor:
         """``rgb_padded [n_pad, 3]`` of this rank -> ``image [H*W, 3]`` (complete on every rank
@@ -89,9 +95,9 @@ class TileSharding:
 
         if self.world > 1:
             dist.all_gather_into_tensor(self.gathered, rgb_padded, group=self.group)
-            image[self.all_pixels] = self.gathered[self.keep]
+            torch.index_select(self.gathered, 0, self.src_for_pixel, out=image)
         else:
-            image[self.all_pixels] = rgb_padded[: self.n_local]
+            torch.index_select(rgb_padded, 0, self.src_for_pixel, out=image)
         return image
 
 
