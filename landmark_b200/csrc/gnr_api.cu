@@ -248,6 +248,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
   }
   free_dev(m->alpha_bits);
   free_dev(m->alpha_coarse);
+  free_dev(m->alpha_full);
   free_dev(m->hull_near_term);
   free_dev(m->hull_u);
   free_dev(m->mlp.basis_blocked);
@@ -389,6 +390,29 @@ __global__ void coarse_bits_kernel(const uint32_t* __restrict__ bits, int D, int
   if ((threadIdx.x & 31) == 0 && c < (((long long)cD * cH * cW + 31) / 32) * 32) coarse[c >> 5] = word;
 }
 
+// The opposite bound: block (bx, by, bz) is "full" if every mask cell of [4 b, 4 b + 4]^3 exists and
+// is set.  A sample whose lower corner lies in a full block then has that corner occupied.
+__global__ void full_bits_kernel(const uint32_t* __restrict__ bits, int D, int H, int W, int cD, int cH, int cW,
+                                 uint32_t* __restrict__ full) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  bool all = c < (long long)cD * cH * cW;
+  if (all) {
+    const int bx = (int)(c % cW), by = (int)((c / cW) % cH), bz = (int)(c / ((long long)cW * cH));
+    all = 4 * bx + 4 < W && 4 * by + 4 < H && 4 * bz + 4 < D;
+    for (int z = 4 * bz; all && z <= 4 * bz + 4; ++z)
+      for (int y = 4 * by; all && y <= 4 * by + 4; ++y)
+        for (int x = 4 * bx; x <= 4 * bx + 4; ++x) {
+          const uint32_t bit = (uint32_t)(((long long)z * H + y) * W + x);
+          if (!((bits[bit >> 5] >> (bit & 31)) & 1u)) {
+            all = false;
+            break;
+          }
+        }
+  }
+  const uint32_t word = __ballot_sync(0xffffffffu, all);
+  if ((threadIdx.x & 31) == 0 && c < (((long long)cD * cH * cW + 31) / 32) * 32) full[c >> 5] = word;
+}
+
 extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, const float* aabb_h,
                                      const float* inv_size_h, void* stream) {
   if (!m) {
@@ -398,7 +422,8 @@ extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int
   DeviceGuard g(m->device);
   free_dev(m->alpha_bits);
   free_dev(m->alpha_coarse);
-  m->alpha_bits = m->alpha_coarse = nullptr;
+  free_dev(m->alpha_full);
+  m->alpha_bits = m->alpha_coarse = m->alpha_full = nullptr;
   m->aD = m->aH = m->aW = 0;
   if (!vol) return 0;
   if (D < 1 || H < 1 || W < 1 || !aabb_h || !inv_size_h || (long long)D * H * W > 0xffffffffLL) {
@@ -415,6 +440,10 @@ extern "C" int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int
     GNR_CUDA_OK(cudaMalloc(&m->alpha_coarse, (size_t)n_cwords * sizeof(uint32_t)));
     coarse_bits_kernel<<<(unsigned)((n_cwords * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(m->alpha_bits, D, H, W, cD, cH,
                                                                                             cW, m->alpha_coarse);
+    GNR_CUDA_OK(cudaGetLastError());
+    GNR_CUDA_OK(cudaMalloc(&m->alpha_full, (size_t)n_cwords * sizeof(uint32_t)));
+    full_bits_kernel<<<(unsigned)((n_cwords * 32 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(m->alpha_bits, D, H, W, cD, cH, cW,
+                                                                                          m->alpha_full);
     GNR_CUDA_OK(cudaGetLastError());
   }
   m->aD = D;
@@ -558,6 +587,7 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
   p.has_mask = m->alpha_bits != nullptr;
   p.a_bits = m->alpha_bits;
   p.a_coarse = m->alpha_coarse;
+  p.a_full = m->alpha_full;
   p.cD = (m->aD + 3) / 4;
   p.cH = (m->aH + 3) / 4;
   p.cW = (m->aW + 3) / 4;

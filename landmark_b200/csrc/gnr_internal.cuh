@@ -55,6 +55,7 @@ struct GnrModel {
   // occupancy bits
   uint32_t* alpha_bits;
   uint32_t* alpha_coarse;  // one bit per 4x4x4 block of mask cells (see coarse_bits_kernel)
+  uint32_t* alpha_full;    // one bit per block: every cell of the block and of its +1 border is set
   int aD, aH, aW;
   float a_lo[3], a_inv[3];
   GnrMlp mlp;
@@ -85,6 +86,7 @@ struct GnrSampleParams {
   int has_mask;
   const uint32_t* a_bits;
   const uint32_t* a_coarse;  // null, or 1 bit per 4x4x4 block: set if any cell of the block or of its +1 border is set
+  const uint32_t* a_full;    // null, or 1 bit per 4x4x4 block: every cell of the block and its +1 border is set
   int cD, cH, cW;
   int S, words, kbits;
   int mode;                 // 0 dense sampler, 1 hull sampler

@@ -67,8 +67,9 @@ __global__ void raygen_dev_kernel(const float* __restrict__ pose_dev, const floa
 // coarse grid proves that all eight corners are empty (threshold >= 0 then fails), and with a
 // threshold of exactly zero the sum of non-negative weights is positive as soon as one occupied
 // corner has a positive weight, so the loop can stop there.
-// `skip` (optional): when the coarse grid rules the sample out, the number of FOLLOWING samples
-// that provably lie in the same empty coarse block, given the index-space step `di` per sample
+// `skip` (optional): when the coarse grids decide the sample (empty block: invalid; full block and
+// threshold 0: valid), the number of FOLLOWING samples that provably lie in the same block and so
+// get the same answer, given the index-space step `di` per sample
 // (dense sampler: positions advance by d * stepSize).  The bound keeps 1/100 of a mask cell away
 // from the block's faces, far more than the rounding of the index arithmetic (a few 1e-4).
 __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float px, float py, float pz,
@@ -86,7 +87,12 @@ __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float p
   const int x0 = (int)fx0, y0 = (int)fy0, z0 = (int)fz0;
   if (p.a_coarse != nullptr && p.a_thres >= 0.0f && x0 >= 0 && y0 >= 0 && z0 >= 0) {
     const uint32_t cb = (uint32_t)(((z0 >> 2) * p.cH + (y0 >> 2)) * p.cW + (x0 >> 2));
-    if (!((__ldg(p.a_coarse + (cb >> 5)) >> (cb & 31)) & 1u)) {
+    const uint32_t cw = cb >> 5, cs = cb & 31;
+    const bool empty = !((__ldg(p.a_coarse + cw) >> cs) & 1u);
+    // a full block decides the test when the threshold is exactly zero: the lower corner is occupied
+    // and its weight (x0 + 1 - ix)(y0 + 1 - iy)(z0 + 1 - iz) is a product of three positive floats
+    const bool full = !empty && p.a_thres == 0.0f && ((__ldg(p.a_full + cw) >> cs) & 1u);
+    if (empty || full) {
       if (skip) {
         const float idx[3] = {ix, iy, iz};
         const int lo[3] = {x0 & ~3, y0 & ~3, z0 & ~3};
@@ -99,7 +105,7 @@ __device__ __forceinline__ bool occupancy_test(const GnrSampleParams& p, float p
         }
         *skip = n > 0.0f ? (int)n : 0;
       }
-      return false;
+      return full;
     }
   }
   const float fx1 = __fadd_rn(fx0, 1.0f), fy1 = __fadd_rn(fy0, 1.0f), fz1 = __fadd_rn(fz0, 1.0f);
@@ -174,18 +180,39 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
                        d[2] * p.step * p.a_inv[2] * 0.5f * (float)(p.aD - 1)};
   const bool can_skip = p.mode == 0 && p.has_mask;
   constexpr int kMaxSkip = 64;
+  // Samples that are skipped as VALID (full blocks) must also lie inside the box: they do while their
+  // index stays two samples short of the slab exit (the positions are monotone along the ray and the
+  // sample that started the run was tested inside).
+  int k_inside = -1;
+  if (can_skip) {
+    float t_far = INFINITY;
+#pragma unroll
+    for (int a = 0; a < 3; ++a) {
+      if (d[a] != 0.0f) t_far = fminf(t_far, fmaxf((p.hi[a] - o[a]) / d[a], (p.lo[a] - o[a]) / d[a]));
+    }
+    const float ksafe = floorf((t_far - t_min) / p.step) - 2.0f;
+    k_inside = ksafe > 0.0f ? (int)fminf(ksafe, (float)p.S) : -1;
+  }
   bool done = !live;
   uint32_t bits = 0;
   int word = 0, k = 0;
+  int ones_beg = 0, ones_end = 0;  // samples [ones_beg, ones_end) of this ray are valid without a test
+  auto with_ones = [&](uint32_t b, int wd) {
+    const int lo = max(ones_beg, wd * 32), hi = min(ones_end, wd * 32 + 32);
+    if (lo < hi) b |= (hi - lo == 32 ? 0xffffffffu : ((1u << (hi - lo)) - 1u)) << (lo - wd * 32);
+    return b;
+  };
   while (k < p.S) {
     const int w = k >> 5;
     while (word < w) {  // words completed since the last sample (all of them when samples were skipped)
+      bits = with_ones(bits, word);
       if (live) wrow[word] = bits;
       ++word;
       count += __popc(bits);
       bits = 0;
     }
     int skip = kMaxSkip;  // a finished ray never holds the warp back
+    bool run_valid = false;
     if (!done) {
       skip = 0;
       const float t = gnr_sample_t(p, t_min, k);
@@ -193,7 +220,11 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
       const bool lo_out = (p.lo[0] > px) | (p.lo[1] > py) | (p.lo[2] > pz);
       const bool hi_out = (px > p.hi[0]) | (py > p.hi[1]) | (pz > p.hi[2]);
       if (!(lo_out | hi_out)) {
-        if (!p.has_mask || occupancy_test(p, px, py, pz, di, can_skip ? &skip : nullptr)) bits |= 1u << (k & 31);
+        if (!p.has_mask || occupancy_test(p, px, py, pz, di, can_skip ? &skip : nullptr)) {
+          bits |= 1u << (k & 31);
+          run_valid = true;
+          skip = max(0, min(skip, k_inside - k));  // a run of valid samples ends before the box does
+        }
       } else if (p.mode == 0) {
         const bool exited = ((d[0] > 0.0f) & (px > p.hi[0])) | ((d[0] < 0.0f) & (p.lo[0] > px)) |
                             ((d[1] > 0.0f) & (py > p.hi[1])) | ((d[1] < 0.0f) & (p.lo[1] > py)) |
@@ -208,9 +239,16 @@ sample_mask_kernel(GnrSampleParams p, const float* __restrict__ rays, int64_t n_
       }
     }
     if (__all_sync(0xffffffffu, done)) break;
-    k += 1 + __reduce_min_sync(0xffffffffu, min(skip, kMaxSkip));
+    const int jump = __reduce_min_sync(0xffffffffu, min(skip, kMaxSkip));
+    if (run_valid && jump > 0) {  // (jump > 0 implies this lane's own run is at least that long)
+      bits = with_ones(bits, w);  // what an earlier run left in the current word, before the range moves on
+      ones_beg = k + 1;
+      ones_end = min(k + 1 + jump, p.S);
+    }
+    k += 1 + jump;
   }
   while (word < p.words) {
+    bits = with_ones(bits, word);
     if (live) wrow[word] = bits;
     ++word;
     count += __popc(bits);
