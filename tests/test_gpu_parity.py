@@ -12,6 +12,7 @@ import torch
 
 from landmark_b200 import scenes
 from oracle import gridnerf_oracle as orc
+from oracle import sampling_numpy as snp
 from tests._util import cuda_model, load_golden, oracle_field, tiny_rays, valid_bits_from_words
 
 pytestmark = pytest.mark.gpu
@@ -550,3 +551,33 @@ def test_ragged_ray_counts_give_the_same_pixels(mlp_mode):
     miss = torch.tensor([[3.0, 3.0, 3.0, 1.0, 0.0, 0.0]], device="cuda")
     out, _ = model(miss, N_samples=spec.n_samples)
     assert torch.equal(out["rgb_map"].cpu(), torch.ones((1, 3))) and float(out["depth_map"][0]) == 0.0
+
+
+@pytest.mark.parametrize("thres", [0.0, 0.5])
+def test_sampler_runs_and_skips_are_exact_on_many_random_rays(thres):
+    """20,000 random rays (origins inside and outside the box, oblique and axis-parallel directions,
+    some nearly tangent to block faces) through the occupancy mask, 384 samples each: the validity
+    words of the kernel, which jumps over empty blocks and marks runs in full blocks (threshold 0),
+    against the numpy restatement that tests every sample."""
+    spec = scenes.tiny_spec().lit()
+    spec.alpha_filter_thres = thres
+    field, ckpt = oracle_field(spec)
+    model = cuda_model(spec, ckpt)
+    g = torch.Generator().manual_seed(99 + int(thres * 10))
+    n = 20000
+    o = torch.rand((n, 3), generator=g) * 3.2 - 1.6
+    d = torch.randn((n, 3), generator=g)
+    d[::9, 1] = 0.0
+    d[::13, 0] = 0.0
+    d[5::40] *= torch.tensor([1.0, 1e-4, 1.0])  # almost parallel to the x-z planes
+    o[7::50, 2] = torch.round(o[7::50, 2] * 8) / 8  # on lattice planes of the coarse grid
+    rays = torch.cat([o, d], 1).contiguous()
+    S = 384
+    got = model.run_stages(rays.cuda(), S, True, upto="sample")
+    valid, t_min = snp.valid_mask(rays.numpy(), field.aabb.numpy(), field.near, field.far, field.step_size.item(), S,
+                                  field.alpha_volume[0, 0].numpy(), field.alpha_aabb.numpy(), thres)
+    bits = valid_bits_from_words(got["mask_words"], S)
+    assert np.array_equal(bits, valid), f"{int((bits != valid).sum())} validity bits differ"
+    assert np.array_equal(got["t_min"].cpu().numpy(), t_min)
+    assert np.array_equal(got["counts"].cpu().numpy(), valid.sum(1))
+    assert valid.sum() > 100000
