@@ -574,6 +574,53 @@ __device__ __forceinline__ void pair_products_thread48(const GnrPlane& pl, Tap t
   }
 }
 
+// fp16 storage: the 48 channels of a pair in three rounds of 16, six 256-bit loads per round, and
+// the interpolation itself in packed fp16 arithmetic (two channels per instruction, no
+// conversions).  Against fp32 interpolation of the same fp16 texels this adds four more fp16
+// roundings to a product that is rounded to fp16 for the tensor cores anyway; the rounding of
+// the stored texels remains the larger part of the error of the projected features.
+struct H16 {
+  uint32_t v[8];
+};
+__device__ __forceinline__ H16 ldg_h16(const void* base, uint32_t texel, int g) {
+  const unsigned char* ptr = reinterpret_cast<const unsigned char*>(base) + (size_t)texel * 96u + g * 32;
+  H16 r;
+  asm("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
+      : "l"(ptr));
+  return r;
+}
+__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<const __half2*>(&u); }
+__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<const uint32_t*>(&h); }
+
+__device__ __forceinline__ void pair_products_thread48_h2(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, unsigned char* out) {
+  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
+  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
+  const __half2 w_nw = __float2half2_rn(ax0 * ay0), w_ne = __float2half2_rn(ax1 * ay0);
+  const __half2 w_sw = __float2half2_rn(ax0 * ay1), w_se = __float2half2_rn(ax1 * ay1);
+  const __half2 h_l0 = __float2half2_rn(al0), h_l1 = __float2half2_rn(al1);
+  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0, sw = nw + (uint32_t)pl.W;
+  const uint32_t seg = (uint32_t)tl.i0;
+#pragma unroll
+  for (int g = 0; g < 3; ++g) {
+    const H16 a = ldg_h16(pl.plane, nw, g), b = ldg_h16(pl.plane, nw + 1u, g);
+    const H16 c = ldg_h16(pl.plane, sw, g), d = ldg_h16(pl.plane, sw + 1u, g);
+    const H16 l0 = ldg_h16(pl.line, seg, g), l1 = ldg_h16(pl.line, seg + 1u, g);
+    uint32_t q[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      __half2 pv = __hmul2(as_h2(a.v[e]), w_nw);
+      pv = __hfma2(as_h2(b.v[e]), w_ne, pv);
+      pv = __hfma2(as_h2(c.v[e]), w_sw, pv);
+      pv = __hfma2(as_h2(d.v[e]), w_se, pv);
+      const __half2 lv = __hfma2(as_h2(l1.v[e]), h_l1, __hmul2(as_h2(l0.v[e]), h_l0));
+      q[e] = as_u32(__hmul2(pv, lv));
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)(2 * g) * 2048) = make_uint4(q[0], q[1], q[2], q[3]);
+    *reinterpret_cast<uint4*>(out + (size_t)(2 * g + 1) * 2048) = make_uint4(q[4], q[5], q[6], q[7]);
+  }
+}
+
 template <int NP, bool HALF>
 __global__ void __launch_bounds__(kThreadBlock, 4)
 app_products_thread_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned char* __restrict__ prod_hi,
@@ -604,15 +651,22 @@ app_products_thread_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, un
       const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
       const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
       const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
-      pair_products_thread48<HALF>(planes.p[0], tx, ty, tz, row);
-      pair_products_thread48<HALF>(planes.p[1], tx, tz, ty, row + 6 * 2048);
-      pair_products_thread48<HALF>(planes.p[2], ty, tz, tx, row + 12 * 2048);
+      if constexpr (HALF) {
+        pair_products_thread48_h2(planes.p[0], tx, ty, tz, row);
+        pair_products_thread48_h2(planes.p[1], tx, tz, ty, row + 6 * 2048);
+        pair_products_thread48_h2(planes.p[2], ty, tz, tx, row + 12 * 2048);
+      } else {
+        pair_products_thread48<HALF>(planes.p[0], tx, ty, tz, row);
+        pair_products_thread48<HALF>(planes.p[1], tx, tz, ty, row + 6 * 2048);
+        pair_products_thread48<HALF>(planes.p[2], ty, tz, tx, row + 12 * 2048);
+      }
     } else {
       for (int pi = 0; pi < planes.n; ++pi) {
         const GnrPlane& pl = planes.p[pi];
         const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-        pair_products_thread48<HALF>(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L),
-                                     row + (size_t)pi * 6 * 2048);
+        const Tap tu = make_tap(u, pl.fw, pl.W), tv = make_tap(v, pl.fh, pl.H), tl = make_tap(l, pl.fl, pl.L);
+        if constexpr (HALF) pair_products_thread48_h2(pl, tu, tv, tl, row + (size_t)pi * 6 * 2048);
+        else pair_products_thread48<HALF>(pl, tu, tv, tl, row + (size_t)pi * 6 * 2048);
       }
     }
   }
