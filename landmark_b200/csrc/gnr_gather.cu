@@ -6,7 +6,8 @@
 // 8 samples x 64 contiguous bytes.  The ones the frame loop runs (march_kernel,
 // app_products_thread_kernel) give a whole sample to one thread and neighbouring rays to the lanes
 // of a warp, with 256-bit loads; per sample they perform the same operations in the same order as
-// the four-lane kernels, so both families give the same bits.  Interpolation follows
+// the four-lane kernels, so both families give the same bits (except the appearance gather from
+// fp16 planes, which interpolates in packed fp16).  Interpolation follows
 // F.grid_sample(mode="bilinear", padding_mode="zeros", align_corners=True) as called by
 // compute_densityfeature / compute_appfeature (app/models/gridnerf_sequential.py:779-871):
 // index = ((x + 1) / 2) * (size - 1); the weight of a corner is the product of the distances
@@ -518,9 +519,10 @@ app_products_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, unsigned 
 // The same for 48 channels with one thread per sample.  Consecutive list entries are samples of
 // neighbouring rays at the same rank (see the order of the appearance list), so the 32 lanes of a
 // load read a few texels between them, and their rows in the tile are consecutive: every store
-// instruction writes 512 contiguous bytes.  A thread takes the 48 channels of a pair in six rounds
-// of 8: six 256-bit loads (128-bit with fp16 storage), the fp32 interpolation and product of
-// pair_products_tap, and one 16-byte store, which is exactly one k group of its row.
+// instruction writes 512 contiguous bytes.  With fp32 storage a thread takes the 48 channels of a
+// pair in six rounds of 8: six 256-bit loads, the fp32 interpolation and product of
+// pair_products_tap, and one 16-byte store, which is exactly one k group of its row (fp16 storage:
+// pair_products_thread48_h2 below).
 constexpr int kThreadBlock = 128;
 
 template <bool HALF>
