@@ -280,6 +280,19 @@ def test_multires_single_plane_layout():
     assert (got["sigma_feature"].cpu() - sig).abs().max().item() <= 2e-6
     feats = F.linear(torch.cat(prods).T, sd["basis_mat.weight"])
     assert (got["app_features"].cpu() - feats[got["app_index"].cpu()]).abs().max().item() <= 5e-6
+    # the same layout through the tensor-core path, with fp32 and with fp16 appearance planes (the
+    # general-layout branch of the packed-fp16 gather)
+    ref, _ = model(rays.cuda(), N_samples=64)
+    outs = []
+    for half in (False, True):
+        m2 = B200GridNeRF(**kwargs, device="cuda:0", args=args, mlp_mode=2, app_plane_fp16=half)
+        m2.load_state_dict(sd, strict=False)
+        m2.commit()
+        out, _ = m2(rays.cuda(), N_samples=64)
+        assert torch.equal(out["depth_map"], ref["depth_map"])
+        assert (out["rgb_map"] - ref["rgb_map"]).abs().max().item() <= 1e-4
+        outs.append(out["rgb_map"])
+    assert 0.0 < (outs[0] - outs[1]).abs().max().item() <= 5e-5
 
 
 @pytest.mark.parametrize("mlp_mode,tol", [(1, 5e-5), (2, 1e-4)])
