@@ -48,6 +48,7 @@ L1_BYTES_PER_CLOCK_PER_SM = 128
 MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
 BASIS_FLOP_PER_SAMPLE = 7776        # 2 * 144 * 27 (done inside the appearance gather kernel)
 CPU_SAMPLE_RAYS = 65536
+REFERENCE_BUDGET_S = 150.0  # the reference arm sizes its per-step sample so that K steps take about this long
 
 
 def peaks():
@@ -126,7 +127,8 @@ def build_scene(workload, device, frame="1080p"):
 
 def run_reference(a):
     """CPU arm: the oracle port of the reference's torch path, all host threads, one bounded
-    sample (CPU_SAMPLE_RAYS rays starting at image row 536 of the same frame) per step."""
+    sample per step (at most CPU_SAMPLE_RAYS rays starting at image row 536 of the same frame, fewer
+    when K steps of that size would take longer than REFERENCE_BUDGET_S)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
@@ -144,23 +146,30 @@ def run_reference(a):
     pose = torch.from_numpy(scenes.make_pose(spec, vol))
     rays = orc.generate_rays(pose, spec.height, spec.width, spec.focal)
     first = 536 * spec.width
-    sample = rays[first:first + CPU_SAMPLE_RAYS].contiguous()
-    for _ in range(min(a.warmup, 1)):
-        orc.render_chunk(field, sample, spec.n_samples, True)
+    # one untimed pass over a small piece of the sample warms the threads up and gives the rate
+    # that bounds the run: the K timed steps together stay near REFERENCE_BUDGET_S seconds
+    probe = rays[first:first + 8192].contiguous()
+    n_warm = max(a.warmup, 1)
+    for _ in range(n_warm):
+        t0 = time.perf_counter()
+        orc.render_chunk(field, probe, spec.n_samples, True)
+        rate = probe.shape[0] / (time.perf_counter() - t0)
+    n_sample = int(min(CPU_SAMPLE_RAYS, max(8192, rate * REFERENCE_BUDGET_S / max(a.steps, 1))) // 4096 * 4096)
+    sample = rays[first:first + n_sample].contiguous()
     t0 = time.perf_counter()
     for _ in range(a.steps):
         orc.render_chunk(field, sample, spec.n_samples, True)
     dt = (time.perf_counter() - t0) / a.steps
-    value = CPU_SAMPLE_RAYS / dt / 1e6
+    value = n_sample / dt / 1e6
     line = {
         "impl": "reference", "metric": "Mrays/s", "value": value, "unit": "Mrays/s", "n_gpus": a.gpus,
-        "steps": a.steps, "warmup": min(a.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": a.steps, "warmup": n_warm, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{a.workload}: 1920x1080 frame, 512 samples/ray", "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": value, "unit": "Mrays/s", "cores": cores, "kind": "port",
-                         "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-570) per step, torch {torch.__version__} CPU"},
+                         "sample": f"{n_sample} rays (from image row 536 on) per step (warm-up passes: 8192 rays each), torch {torch.__version__} CPU"},
         "e2e": {"value": value, "unit": "Mrays/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "ms_per_frame_extrapolated": dt * 1e3 * spec.height * spec.width / CPU_SAMPLE_RAYS,
+        "ms_per_frame_extrapolated": dt * 1e3 * spec.height * spec.width / n_sample,
     }
     print(json.dumps(line), flush=True)
 
