@@ -143,3 +143,64 @@ def test_engine_single_rank_cpu_fake():
     assert len(eng.latency) == 1
     img = eng.submit(eng.poses[0])
     assert np.array_equal(img, _expected(eng.poses[0], 80.0, 30, 50))
+
+
+def _rank_rows(rank, world):
+    """Deterministic per-rank payload and owners for the routing test."""
+    g = torch.Generator().manual_seed(100 + rank)
+    n = 1000 + 37 * rank
+    owner = torch.randint(0, world, (n,), generator=g)
+    owner[:50] = 0  # an uneven split
+    x = torch.randn((n, 4), generator=g)
+    return owner, x
+
+
+def _route_worker(rank, world, port, out):
+    from landmark_b200.model_parallel import DistComm, _route
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        comm = DistComm()
+        owner, x = _rank_rows(rank, world)
+        order, counts = _route(owner, world)
+        got, rc = comm.all_to_all_rows([x[order]], [counts])
+        # the reply travels the reverse way and is put back in sample order
+        back, _ = comm.all_to_all_rows([got[0] * 2], [rc[0]])
+        restored = torch.empty_like(x)
+        restored[order] = back[0]
+        gathered = comm.all_gather_rows([x[:8]])
+        torch.save({"recv": got[0], "rc": rc[0], "restored": restored, "gathered": gathered[0]}, f"{out}.{rank}")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sample_routing_two_ranks_over_gloo_equals_loopback(tmp_path):
+    """The block-parallel renderer's exchange (group samples by owner, counts first, variable
+    all-to-all, reverse trip) through torch.distributed on two gloo ranks gives what the
+    in-process LoopbackComm, which the GPU tests use, gives for the same rows."""
+    from landmark_b200.model_parallel import LoopbackComm, _route
+
+    world = 2
+    out = str(tmp_path / "route")
+    mp.spawn(_route_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    rows = [_rank_rows(r, world) for r in range(world)]
+    routed = [_route(o, world) for o, _ in rows]
+    lb = LoopbackComm(world)
+    recv, rcs = lb.all_to_all_rows([rows[r][1][routed[r][0]] for r in range(world)], [routed[r][1] for r in range(world)])
+    gathered = lb.all_gather_rows([rows[r][1][:8] for r in range(world)])
+    for r in range(world):
+        got = torch.load(f"{out}.{r}")
+        assert got["rc"] == rcs[r]
+        assert torch.equal(got["recv"], recv[r])
+        assert torch.equal(got["restored"], rows[r][1] * 2)
+        assert torch.equal(got["gathered"], gathered[r])
+        # stable grouping: inside one owner the samples keep their order
+        order, counts = routed[r]
+        assert sum(counts) == rows[r][0].numel()
+        start = 0
+        for d in range(world):
+            seg = order[start:start + counts[d]]
+            assert torch.all(rows[r][0][seg] == d) and torch.all(seg[1:] > seg[:-1])
+            start += counts[d]
