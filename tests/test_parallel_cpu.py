@@ -171,7 +171,10 @@ def _route_worker(rank, world, port, out):
         restored = torch.empty_like(x)
         restored[order] = back[0]
         gathered = comm.all_gather_rows([x[:8]])
-        torch.save({"recv": got[0], "rc": rc[0], "restored": restored, "gathered": gathered[0]}, f"{out}.{rank}")
+        # the channel-parallel renderer's exchange: partial feature rows summed and dealt out by rows
+        part = comm.reduce_scatter_rows([x[:64]])
+        torch.save({"recv": got[0], "rc": rc[0], "restored": restored, "gathered": gathered[0], "part": part[0]},
+                   f"{out}.{rank}")
     finally:
         dist.destroy_process_group()
 
@@ -190,8 +193,10 @@ def test_sample_routing_two_ranks_over_gloo_equals_loopback(tmp_path):
     lb = LoopbackComm(world)
     recv, rcs = lb.all_to_all_rows([rows[r][1][routed[r][0]] for r in range(world)], [routed[r][1] for r in range(world)])
     gathered = lb.all_gather_rows([rows[r][1][:8] for r in range(world)])
+    parts = lb.reduce_scatter_rows([rows[r][1][:64] for r in range(world)])
     for r in range(world):
         got = torch.load(f"{out}.{r}")
+        assert torch.equal(got["part"], parts[r])
         assert got["rc"] == rcs[r]
         assert torch.equal(got["recv"], recv[r])
         assert torch.equal(got["restored"], rows[r][1] * 2)
