@@ -183,8 +183,11 @@ int gnr_sample_bits(int n_samples);
  * holds until the process exits.  The call allocates and frees nothing.
  *
  *  - Limit: 4 * n_rays * ceil(n_samples / 32) + 4 * (n_rays / 1024 + 2), each part rounded up to
- *    256 bytes, must not exceed GNR_SAMPLE_STATIC_SCRATCH_BYTES (e.g. 65536 rays x 512 samples);
+ *    256 bytes, must not exceed GNR_SAMPLE_STATIC_SCRATCH_BYTES (4 MiB of bit words plus one 4 KiB
+ *    page for the block sums: 65536 rays x 512 samples fit, 65536 + 4096 rays x 512 do not);
  *    larger chunks are refused with an error, nothing is enqueued.
+ *  - Preconditions are those of gnr_sample: with sampling_mode 1 the hull tables must have been
+ *    uploaded for exactly ``n_samples`` (gnr_upload_hull_tables); otherwise the call is refused.
  *  - All five outputs are required device buffers owned by the caller: ``t_min[n]``, ``counts[n]``,
  *    ``offsets[n+1]``, ``ids[max_valid]`` and an 8-word ``status`` block (GNR_ST_* indices) that
  *    the call clears first and that reports an ``ids`` overflow.  Results equal gnr_sample's.
@@ -193,7 +196,7 @@ int gnr_sample_bits(int n_samples);
  *  - All calls on one GPU share the array and it keeps the previous call's contents; the call
  *    rewrites every word it reads, so nothing stale leaks in, but two calls that overlap on
  *    the GPU (different streams, no dependency) race on it.  Serialise them. */
-#define GNR_SAMPLE_STATIC_SCRATCH_BYTES (4u << 20)
+#define GNR_SAMPLE_STATIC_SCRATCH_BYTES ((4u << 20) + 4096u)
 int gnr_sample_static(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, int64_t max_valid,
                       float* t_min, int32_t* counts, int32_t* offsets, uint32_t* ids, int32_t* status,
                       void* stream);

@@ -13,7 +13,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_PKG, "libgridnerf_b200.so")
 
 STAGE_NAMES = ("sample", "compact", "density", "weights", "compact_app", "app_gather", "mlp", "composite")
-SAMPLE_STATIC_SCRATCH_BYTES = 4 << 20
+SAMPLE_STATIC_SCRATCH_BYTES = (4 << 20) + 4096
 ST_OVERFLOW_VALID, ST_OVERFLOW_APP, ST_NUM_VALID, ST_NUM_APP, ST_WAIT_EXPIRED, ST_NUM_DENSITY, ST_WORDS = 0, 1, 2, 3, 4, 5, 8
 
 

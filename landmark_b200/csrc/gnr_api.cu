@@ -600,6 +600,23 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
   return p;
 }
 
+int gnr_check_sampler(const GnrModel* m, int S) {
+  if (!m) {
+    gnr_set_error("null model");
+    return -1;
+  }
+  if (S < 1) {
+    gnr_set_error("bad sample count %d", S);
+    return -1;
+  }
+  // the hull sampler reads hull_near_term[k] and hull_u[k] for every k < S
+  if (m->cfg.sampling_mode == 1 && (m->hull_samples != S || !m->hull_u || !m->hull_near_term)) {
+    gnr_set_error("hull sampler: tables for %d samples per ray have not been uploaded (have %d)", S, m->hull_samples);
+    return -1;
+  }
+  return 0;
+}
+
 int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int64_t max_app, const void* ws,
                     size_t ws_bytes) {
   if (!m) {
@@ -631,10 +648,7 @@ int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
     gnr_set_error("MLP weights have not been uploaded");
     return -1;
   }
-  if (m->cfg.sampling_mode == 1 && (m->hull_samples != S || !m->hull_u)) {
-    gnr_set_error("hull sampler: tables for %d samples per ray have not been uploaded (have %d)", S, m->hull_samples);
-    return -1;
-  }
+  if (gnr_check_sampler(m, S)) return -1;
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
   if (!ws || ws_bytes < L.total) {
     gnr_set_error("workspace too small: have %zu bytes, need %zu", ws_bytes, L.total);

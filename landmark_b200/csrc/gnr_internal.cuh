@@ -123,6 +123,9 @@ struct GnrCoords {
 void gnr_set_error(const char* fmt, ...);
 GnrWs gnr_ws_layout(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app);
 GnrSampleParams gnr_sample_params(const GnrModel* m, int S);
+// What every launch of the sampler needs from the model, checked on the host before anything is
+// enqueued: with sampling_mode 1 the hull tables must have been uploaded for exactly S samples.
+int gnr_check_sampler(const GnrModel* m, int S);
 int gnr_check_chunk(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app,
                     const void* ws, size_t ws_bytes);
 

@@ -480,6 +480,8 @@ extern "C" int gnr_sample_static(GnrModel* m, const float* rays, int64_t n_rays,
                   (long long)max_valid);
     return -1;
   }
+  // the same sampler preconditions gnr_sample checks (hull tables present and of this length)
+  if (gnr_check_sampler(m, n_samples)) return -1;
   const int kbits = gnr_sample_bits(n_samples);
   if (kbits > 20 || n_rays > ((int64_t)1 << (32 - kbits)) || n_rays * (int64_t)n_samples > 0x7fffffffLL ||
       max_valid > 0x7fffffffLL) {

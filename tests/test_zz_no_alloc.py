@@ -84,3 +84,46 @@ def test_static_sampler_reports_overflow_and_refuses_oversize():
     msg = _lib.lib.gnr_last_error().decode()
     assert "scratch" in msg and str(_lib.SAMPLE_STATIC_SCRATCH_BYTES) in msg
     assert float(t_min[0]) == -7.0  # untouched
+
+
+def test_static_sampler_size_boundary():
+    """The documented limit: 65,536 rays x 512 samples fit the built-in array, one more scan
+    block of rays (4,096 more) does not, and a refused call enqueues nothing."""
+    from landmark_b200 import _lib
+
+    spec = scenes.tiny_spec().lit()
+    model = cuda_model(spec)
+    rays = tiny_rays(spec).cuda()
+    big = rays[torch.arange(65536 + 4096, device="cuda") % rays.shape[0]].contiguous()
+    rc, _, counts, offsets, _, status = _call_static(model, big[:65536].contiguous(), 512, 1024)
+    assert rc == 0, _lib.lib.gnr_last_error()
+    assert int(status[_lib.ST_NUM_VALID]) == int(counts.sum()) == int(offsets[-1])
+    rc, t_min, *_ = _call_static(model, big, 512, 1024)
+    assert rc != 0 and "scratch" in _lib.lib.gnr_last_error().decode()
+    assert float(t_min[0]) == -7.0
+
+
+def test_static_sampler_refuses_hull_model_without_tables():
+    """A hull-sampler model reads two per-sample tables on the device.  Without them (or with
+    tables for another sample count) the call is refused on the host, exactly as gnr_sample
+    refuses it, and no kernel is launched."""
+    from landmark_b200 import _lib
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    spec = scenes.tiny_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)
+    args = scenes.model_args(spec, "cuda:0")
+    args.sampling_opt, args.n_importance = 1, 64
+    kw = dict(ckpt["kwargs"])
+    kw.update({"device": "cuda:0", "args": args, "is_train": False})
+    model = B200GridNeRF(**kw)
+    model.load(ckpt)  # committed, but no hull tables have been uploaded yet
+    rays = tiny_rays(spec).cuda()[:512].contiguous()
+    rc, t_min, counts, *_ = _call_static(model, rays, 64, 512 * 64)
+    assert rc != 0 and "hull" in _lib.lib.gnr_last_error().decode()
+    assert float(t_min[0]) == -7.0 and int(counts[0]) == -7
+    ref = model.run_stages(rays, -1, True, upto="sample")  # uploads the tables for 64 samples
+    rc, _, counts, *_ = _call_static(model, rays, 64, 512 * 64)
+    assert rc == 0 and torch.equal(counts, ref["counts"])
+    rc, t_min, *_ = _call_static(model, rays, 96, 512 * 96)  # tables are for 64 samples, not 96
+    assert rc != 0 and float(t_min[0]) == -7.0
