@@ -201,6 +201,9 @@ def main():
                     help="hold the appearance planes as fp16 in HBM (mlp_mode 2 only)")
     ap.add_argument("--den-fp16", type=int, default=0, choices=(0, 1),
                     help="hold the density planes and lines as fp16 in HBM as well")
+    ap.add_argument("--den-lattice", type=int, default=1, choices=(0, 1),
+                    help="density from the pre-summed scalar lattice (4 B per grid point of HBM, 8 taps per sample) "
+                         "instead of the 3 x (plane x line) x 16-channel gather")
     ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
@@ -257,7 +260,7 @@ def main():
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
     model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16),
-                         density_plane_fp16=bool(a.den_fp16))
+                         density_plane_fp16=bool(a.den_fp16), density_lattice=bool(a.den_lattice))
     model.load(ckpt)
     if a.reload_test:
         from landmark_b200.dynamic import pin_block
@@ -509,6 +512,7 @@ def main():
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
                    "density_plane_storage": "fp16" if a.den_fp16 else "fp32",
+                   "density_lattice": bool(a.den_lattice),
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,

@@ -112,6 +112,20 @@ int gnr_upload_alpha_mask(GnrModel* m, const uint8_t* vol, int D, int H, int W, 
 int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const float* b1, const float* w2,
                    const float* b2, const float* w3, const float* b3, void* stream);
 
+/* Optional pre-summed density lattice.  For the standard three-pair layout on one grid,
+ * compute_densityfeature (app/models/gridnerf_sequential.py:779-827: per pair, bilinear plane sample x
+ * linear line sample, summed over channels and pairs) is exactly the trilinear interpolation of one
+ * scalar per grid point, V[x][y][z] = sum over pairs and channels of plane texel x line entry.  With
+ * ``enable`` != 0 this builds V on the device from the density planes and lines uploaded so far
+ * (4 bytes x grid points, e.g. 4.3 GB for 2048x2048x256; each value is the correctly rounded sum) and
+ * every later density evaluation of the model (gnr_render_chunk, gnr_march, gnr_density,
+ * gnr_density_points) reads 8 scalars per sample from it instead of 18 texels of 16 channels; the
+ * feature differs from the plane/line evaluation only by floating-point summation order.  Uploading
+ * a density plane or line afterwards makes the lattice stale: launches are refused until it is
+ * rebuilt (same size: no allocation, stream-ordered).  ``enable`` == 0 frees it.  Needs n_pairs == 3
+ * with the planes (x,y), (x,z), (y,z) of one grid; refused otherwise. */
+int gnr_build_density_lattice(GnrModel* m, int enable, void* stream);
+
 /* Tables of the hull sampler for ``n_samples`` (= n_importance) samples per ray:
  * ``u[k] = torch.linspace(0, 1, n_samples)[k]`` and ``near_term[k] = near * (1.0 - u[k])``, both
  * evaluated by torch on the CPU so that ``z = near_term[k] + far * u[k]`` has the reference's bits

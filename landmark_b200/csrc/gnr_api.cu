@@ -58,6 +58,16 @@ struct GnrProfiler {
   }
 };
 
+#define GNR_LAUNCH_OK(call)                                                                  \
+  do {                                                                                       \
+    int _e = (call);                                                                         \
+    if (_e > 0) {                                                                            \
+      gnr_set_error("%s: %s", #call, cudaGetErrorString((cudaError_t)_e));                   \
+      return -2;                                                                             \
+    }                                                                                        \
+    if (_e < 0) return _e;                                                                   \
+  } while (0)
+
 namespace {
 
 struct StageScope {
@@ -246,6 +256,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
     free_dev(m->app_plane_buf[i]);
     free_dev(m->app_line_buf[i]);
   }
+  free_dev(m->den_lattice);
   free_dev(m->alpha_bits);
   free_dev(m->alpha_coarse);
   free_dev(m->alpha_full);
@@ -314,6 +325,7 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
   else
     to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, P);
   GNR_CUDA_OK(cudaGetLastError());
+  if (kind == 0) m->lat_valid = 0;  // a lattice built from the previous planes no longer describes the field
   pl->plane = *buf;
   pl->H = H;
   pl->W = W;
@@ -359,6 +371,7 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
   else
     to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, (long long)Ln);
   GNR_CUDA_OK(cudaGetLastError());
+  if (kind == 0) m->lat_valid = 0;
   pl->line = *buf;
   pl->L = Ln;
   pl->fl = (float)(Ln - 1);
@@ -513,6 +526,39 @@ extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1
   return 0;
 }
 
+extern "C" int gnr_build_density_lattice(GnrModel* m, int enable, void* stream) {
+  if (!m) {
+    gnr_set_error("gnr_build_density_lattice: null model");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  if (!enable) {
+    if (m->den_lattice) {
+      cudaDeviceSynchronize();  // kernels in flight may still read it
+      free_dev(m->den_lattice);
+    }
+    m->den_lattice = nullptr;
+    m->den_lattice_bytes = 0;
+    m->lat_valid = 0;
+    return 0;
+  }
+  int dims[3];
+  if (gnr_lattice_dims(m, dims)) return -1;
+  const size_t need = (size_t)dims[0] * dims[1] * dims[2] * sizeof(float);
+  if (!m->den_lattice || m->den_lattice_bytes != need) {
+    if (m->den_lattice) cudaDeviceSynchronize();
+    free_dev(m->den_lattice);
+    m->den_lattice = nullptr;
+    m->den_lattice_bytes = 0;
+    GNR_CUDA_OK(cudaMalloc(&m->den_lattice, need));
+    m->den_lattice_bytes = need;
+  }
+  for (int a = 0; a < 3; ++a) m->lat_dims[a] = dims[a];
+  GNR_LAUNCH_OK(launch_build_lattice(m, m->den_lattice, (cudaStream_t)stream));
+  m->lat_valid = 1;
+  return 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // workspace
 // ---------------------------------------------------------------------------------------------
@@ -600,6 +646,14 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
   return p;
 }
 
+int gnr_check_lattice(const GnrModel* m) {
+  if (m->den_lattice && !m->lat_valid) {
+    gnr_set_error("density planes or lines were uploaded after the density lattice was built: call gnr_build_density_lattice again");
+    return -1;
+  }
+  return 0;
+}
+
 int gnr_check_sampler(const GnrModel* m, int S) {
   if (!m) {
     gnr_set_error("null model");
@@ -649,6 +703,7 @@ int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
     return -1;
   }
   if (gnr_check_sampler(m, S)) return -1;
+  if (gnr_check_lattice(m)) return -1;
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
   if (!ws || ws_bytes < L.total) {
     gnr_set_error("workspace too small: have %zu bytes, need %zu", ws_bytes, L.total);
@@ -684,16 +739,6 @@ extern "C" int gnr_read_status(const void* workspace, int32_t* status_h, void* s
 // ---------------------------------------------------------------------------------------------
 // stages
 // ---------------------------------------------------------------------------------------------
-#define GNR_LAUNCH_OK(call)                                                                  \
-  do {                                                                                       \
-    int _e = (call);                                                                         \
-    if (_e > 0) {                                                                            \
-      gnr_set_error("%s: %s", #call, cudaGetErrorString((cudaError_t)_e));                   \
-      return -2;                                                                             \
-    }                                                                                        \
-    if (_e < 0) return _e;                                                                   \
-  } while (0)
-
 static int launch_sample(GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
                          int64_t max_valid, cudaStream_t st) {
   int e = launch_sample_mask(m, p, rays, n, ws, L, st);
@@ -1010,6 +1055,7 @@ static int check_points(const GnrModel* m, const char* who, int64_t n, const voi
     gnr_set_error("%s: model parameters have not been uploaded", who);
     return -1;
   }
+  if (gnr_check_lattice(m)) return -1;
   if (scratch_bytes != (size_t)-1) {
     const PointScratch s = point_scratch(m, n);
     if (!scratch || scratch_bytes < s.total || ((uintptr_t)scratch & 255) != 0) {

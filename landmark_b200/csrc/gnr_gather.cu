@@ -227,6 +227,70 @@ __device__ __forceinline__ float density_thread(const PlaneSet& planes, float x,
   return (part[0] + part[1]) + (part[2] + part[3]);
 }
 
+// ---- density from the pre-summed lattice ---------------------------------------------------------
+// For the standard three-pair layout on one grid the density feature
+//   sum_pairs sum_c bilinear(plane_c)(a, b) * linear(line_c)(l)
+// is, term by term, the trilinear interpolation of the products plane_c[j][i] * line_c[k], hence
+// of their sum over channels and pairs: one scalar per lattice point,
+//   V[x][y][z] = sum_c P0_c[y][x] L0_c[z] + P1_c[z][x] L1_c[y] + P2_c[z][y] L2_c[x],
+// interpolated with the same lower indices and fractions (make_tap) the plane/line taps use.  The
+// function is the same; only the order of the floating-point sums differs (a few 1e-8 on the
+// feature).  A sample then costs 8 scalar loads instead of 36 loads of 32 bytes.
+// z is the fastest axis of V: a ray's consecutive samples and the two z taps share sectors.
+__device__ __forceinline__ float lattice_feature(const float* __restrict__ V, uint32_t Gy, uint32_t Gz, Tap tx, Tap ty, Tap tz) {
+  const uint32_t b00 = ((uint32_t)tx.i0 * Gy + (uint32_t)ty.i0) * Gz + (uint32_t)tz.i0;
+  const uint32_t b01 = b00 + Gz, b10 = b00 + Gy * Gz, b11 = b10 + Gz;
+  const float v000 = __ldg(V + b00), v001 = __ldg(V + b00 + 1u), v010 = __ldg(V + b01), v011 = __ldg(V + b01 + 1u);
+  const float v100 = __ldg(V + b10), v101 = __ldg(V + b10 + 1u), v110 = __ldg(V + b11), v111 = __ldg(V + b11 + 1u);
+  const float fz = tz.f1, fy = ty.f1, fx = tx.f1;
+  const float c00 = fmaf(fz, v001 - v000, v000), c01 = fmaf(fz, v011 - v010, v010);
+  const float c10 = fmaf(fz, v101 - v100, v100), c11 = fmaf(fz, v111 - v110, v110);
+  const float c0 = fmaf(fy, c01 - c00, c00), c1 = fmaf(fy, c11 - c10, c10);
+  return fmaf(fx, c1 - c0, c0);
+}
+
+struct LatticeRef {
+  const float* v;  // null: gather from the planes and lines
+  int gx, gy, gz;
+};
+
+__device__ __forceinline__ float lattice_density_feature(const LatticeRef& lat, const PlaneSet& planes, float x, float y, float z) {
+  const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+  const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+  const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+  return lattice_feature(lat.v, (uint32_t)lat.gy, (uint32_t)lat.gz, tx, ty, tz);
+}
+
+// One thread per lattice point, z fastest.  The 48 (3 x C) products are summed in double and
+// rounded once, so every lattice value is the correctly rounded sum.
+template <bool HALF>
+__global__ void __launch_bounds__(256)
+build_lattice_kernel(PlaneSet planes, int C, int gx, int gy, int gz, float* __restrict__ V) {
+  const long long total = (long long)gx * gy * gz;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int z = (int)(i % gz), y = (int)((i / gz) % gy), x = (int)(i / ((long long)gz * gy));
+    // texel (plane) and entry (line) of every pair for this lattice point
+    const size_t pt[3] = {(size_t)y * planes.p[0].W + x, (size_t)z * planes.p[1].W + x, (size_t)z * planes.p[2].W + y};
+    const size_t ln[3] = {(size_t)z, (size_t)y, (size_t)x};
+    double acc = 0.0;
+#pragma unroll
+    for (int pi = 0; pi < 3; ++pi) {
+      for (int c = 0; c < C; ++c) {
+        float pv, lv;
+        if constexpr (HALF) {
+          pv = __half2float(reinterpret_cast<const __half*>(planes.p[pi].plane)[pt[pi] * C + c]);
+          lv = __half2float(reinterpret_cast<const __half*>(planes.p[pi].line)[ln[pi] * C + c]);
+        } else {
+          pv = __ldg(planes.p[pi].plane + pt[pi] * C + c);
+          lv = __ldg(planes.p[pi].line + ln[pi] * C + c);
+        }
+        acc += (double)pv * (double)lv;
+      }
+    }
+    V[i] = (float)acc;
+  }
+}
+
 // Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
 // computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
 // `view` (optional) receives the ray direction of the sample.
@@ -318,6 +382,20 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
   }
 }
 
+// List / point mode density from the lattice: one thread per item.
+__global__ void __launch_bounds__(kBlock)
+density_lattice_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, GnrCoords crd, float shift, int act,
+                       float* __restrict__ sigma_feat, float* __restrict__ sigma) {
+  const long long total = coords_total(crd);
+  for (long long i = (long long)blockIdx.x * kBlock + threadIdx.x; i < total; i += (long long)gridDim.x * kBlock) {
+    float x, y, z;
+    sample_xyz(p, crd, i, x, y, z);
+    const float f = lattice_density_feature(lat, planes, x, y, z);
+    if (sigma_feat) sigma_feat[i] = f;
+    sigma[i] = density_activation(f, shift, act);
+  }
+}
+
 // Fused density + weights pass ("march"): one thread walks one ray's valid samples (the set bits of
 // its validity words; sample j of the ray owns entry offsets[ray] + j of the per-sample arrays): density feature (density_thread), activation, raw2alpha's alpha, the
 // running transmittance product in sample order (as torch.cumprod computes it on the CPU), weight,
@@ -331,9 +409,9 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
 // weights_kernel.
 constexpr int kMarchBlock = 32;  // one warp per CTA: a finished warp frees its slot at once
 
-template <int J, int NP, bool HALF = false>
-__global__ void __launch_bounds__(kMarchBlock, 16)
-march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
+template <int J, int NP, bool HALF = false, bool LAT = false>
+__global__ void __launch_bounds__(kMarchBlock, LAT ? 32 : 16)
+march_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, const float* __restrict__ rays, const float* __restrict__ t_min_arr,
              const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
              float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts,
@@ -367,7 +445,10 @@ march_kernel(GnrSampleParams p, PlaneSet planes, const float* __restrict__ rays,
         const float x = gnr_normalize(gnr_point(ox, dx, t), p.lo[0], p.inv[0]);
         const float y = gnr_normalize(gnr_point(oy, dy, t), p.lo[1], p.inv[1]);
         const float z = gnr_normalize(gnr_point(oz, dz, t), p.lo[2], p.inv[2]);
-        const float sg = density_activation(density_thread<J, NP, HALF>(planes, x, y, z), shift, act);
+        float feat;
+        if constexpr (LAT) feat = lattice_density_feature(lat, planes, x, y, z);
+        else feat = density_thread<J, NP, HALF>(planes, x, y, z);
+        const float sg = density_activation(feat, shift, act);
         const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
         const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-sg, __fmul_rn(dist, distance_scale))));
         const float w = alpha * T;
@@ -729,11 +810,62 @@ GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L) {
   return c;
 }
 
+static LatticeRef lattice_of(const GnrModel* m) {
+  LatticeRef r;
+  r.v = m->den_lattice;
+  r.gx = m->lat_dims[0];
+  r.gy = m->lat_dims[1];
+  r.gz = m->lat_dims[2];
+  return r;
+}
+
+int launch_build_lattice(const GnrModel* m, float* V, cudaStream_t st) {
+  PlaneSet set = make_set(m->den, m->cfg.n_pairs);
+  if (!standard_vm3(set)) {
+    gnr_set_error("the density lattice needs the standard three-pair layout on one grid (xy|z, xz|y, yz|x)");
+    return -1;
+  }
+  const int gx = set.p[0].W, gy = set.p[0].H, gz = set.p[0].L;
+  const int grid = m->sm_count * 16;
+  if (m->cfg.den_storage == 1)
+    build_lattice_kernel<true><<<grid, 256, 0, st>>>(set, set.p[0].C, gx, gy, gz, V);
+  else
+    build_lattice_kernel<false><<<grid, 256, 0, st>>>(set, set.p[0].C, gx, gy, gz, V);
+  return (int)cudaGetLastError();
+}
+
+int gnr_lattice_dims(const GnrModel* m, int* dims) {
+  PlaneSet set = make_set(m->den, m->cfg.n_pairs);
+  for (int i = 0; i < m->cfg.n_pairs; ++i) {
+    if (!m->den[i].plane || !m->den[i].line) {
+      gnr_set_error("density plane/line pair %d has not been uploaded", i);
+      return -1;
+    }
+  }
+  if (!standard_vm3(set)) {
+    gnr_set_error("the density lattice needs the standard three-pair layout on one grid (xy|z, xz|y, yz|x)");
+    return -1;
+  }
+  dims[0] = set.p[0].W;
+  dims[1] = set.p[0].H;
+  dims[2] = set.p[0].L;
+  if ((long long)dims[0] * dims[1] * dims[2] > 0xffffffffLL) {
+    gnr_set_error("density lattice of %dx%dx%d points exceeds 32-bit offsets", dims[0], dims[1], dims[2]);
+    return -1;
+  }
+  return 0;
+}
+
 int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,
                    cudaStream_t st) {
   PlaneSet set = make_set(m->den, m->cfg.n_pairs);
   const int J = m->den[0].C / 16;
   const int grid = m->sm_count * 4;
+  if (m->den_lattice) {
+    density_lattice_kernel<<<m->sm_count * 8, kBlock, 0, st>>>(p, set, lattice_of(m), c, m->cfg.density_shift, m->cfg.density_act,
+                                                              sigma_feat, sigma);
+    return (int)cudaGetLastError();
+  }
 #define GNR_DEN(JJ)                                                                                                   \
   do {                                                                                                                \
     if (standard_vm3(set))                                                                                            \
@@ -835,15 +967,17 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
   const int J = m->den[0].C / 16;
   const unsigned grid = (unsigned)((n + kMarchBlock - 1) / kMarchBlock);
   const float t_stop = m->cfg.ert_transmittance > 0.0f ? m->cfg.ert_transmittance : 0.0f;
-#define GNR_MARCH(JJ, NPP) GNR_MARCH_H(JJ, NPP, false)
-#define GNR_MARCH_H(JJ, NPP, HH)                                                                                  \
-  march_kernel<JJ, NPP, HH><<<grid, kMarchBlock, 0, st>>>(                                                        \
-      p, set, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words), (const int32_t*)(ws + L.offsets), \
+  const LatticeRef lat = lattice_of(m);
+#define GNR_MARCH(JJ, NPP) GNR_MARCH_H(JJ, NPP, false, false)
+#define GNR_MARCH_H(JJ, NPP, HH, LL)                                                                              \
+  march_kernel<JJ, NPP, HH, LL><<<grid, kMarchBlock, 0, st>>>(                                                    \
+      p, set, lat, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
       (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)
-  if (m->cfg.den_storage == 1 && standard_vm3(set)) GNR_MARCH_H(1, 3, true);
-  else if (m->cfg.den_storage == 1) GNR_MARCH_H(1, 0, true);
+  if (m->den_lattice) GNR_MARCH_H(1, 3, false, true);
+  else if (m->cfg.den_storage == 1 && standard_vm3(set)) GNR_MARCH_H(1, 3, true, false);
+  else if (m->cfg.den_storage == 1) GNR_MARCH_H(1, 0, true, false);
   else if (J == 1 && standard_vm3(set)) GNR_MARCH(1, 3);
   else if (J == 1) GNR_MARCH(1, 0);
   else if (J == 2) GNR_MARCH(2, 0);

@@ -52,6 +52,11 @@ struct GnrModel {
   float* app_line_buf[GNR_MAX_PLANES];
   size_t plane_bytes[2][GNR_MAX_PLANES];  // current size of every plane / line buffer: an upload of the
   size_t line_bytes[2][GNR_MAX_PLANES];   // same size reuses it (no cudaFree, hence no device-wide sync)
+  // pre-summed density lattice [gx][gy][gz] (null unless built; see gnr_build_density_lattice)
+  float* den_lattice;
+  size_t den_lattice_bytes;
+  int lat_dims[3];
+  int lat_valid;  // 0 after a density plane or line was uploaded: the lattice must be rebuilt before the next launch
   // occupancy bits
   uint32_t* alpha_bits;
   uint32_t* alpha_coarse;  // one bit per 4x4x4 block of mask cells (see coarse_bits_kernel)
@@ -126,6 +131,7 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S);
 // What every launch of the sampler needs from the model, checked on the host before anything is
 // enqueued: with sampling_mode 1 the hull tables must have been uploaded for exactly S samples.
 int gnr_check_sampler(const GnrModel* m, int S);
+int gnr_check_lattice(const GnrModel* m);  // refuses a lattice that is older than the density planes
 int gnr_check_chunk(const GnrModel* m, int64_t n_rays, int S, int64_t max_valid, int64_t max_app,
                     const void* ws, size_t ws_bytes);
 
@@ -135,6 +141,8 @@ int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float*
 // with_ids == 0: offsets only (the compacted id list is needed by the list-based density kernel and the stage API)
 int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, int with_ids, cudaStream_t st);
+int launch_build_lattice(const GnrModel* m, float* V, cudaStream_t st);
+int gnr_lattice_dims(const GnrModel* m, int* dims);  // grid of the density field if it has the standard VM3 layout, else -1
 GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L);
 GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L);
 int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,

@@ -100,6 +100,8 @@ class GraphedFrameRenderer:
             self.model.render_rays(self.rays, self.n_samples, self.white_bg, chunk=self.chunk, rgb_out=self.rgb,
                                    depth_out=self.depth, overlap=self.streams)
             self._status = self.model._pending_status
+            # the captured launches carry these buffers' addresses: hold them for the graph's lifetime
+            self._workspaces = list(self.model._last_workspaces)
             check(lib.gnr_rgba8(C.c_void_p(self.rgb.data_ptr()), self.n, C.c_void_p(self.rgba.data_ptr()),
                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gnr_rgba8")
 

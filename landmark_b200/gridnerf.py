@@ -109,6 +109,7 @@ class B200GridNeRF(torch.nn.Module):
         ert_transmittance: float = 0.0,
         app_plane_fp16: bool = False,
         density_plane_fp16: bool = False,
+        density_lattice: bool = False,
         **_ignored,
     ):
         super().__init__()
@@ -154,12 +155,19 @@ class B200GridNeRF(torch.nn.Module):
         self.mlp_mode = int(mlp_mode)
         # early ray termination of the density pass (see GnrConfig.ert_transmittance); 0 = exact
         self.ert_transmittance = float(ert_transmittance)
-        # appearance planes and lines held as fp16 in the library (GnrConfig.app_storage); mlp_mode 2 only.
-        # args.half_precision_param is the reference's switch for half planes (inferer_impl.py:263-267).
+        # Appearance planes and lines held as fp16 in the library (GnrConfig.app_storage); mlp_mode 2 only.
+        # args.half_precision_param is the reference's switch for half planes (inferer_impl.py:251,263-267:
+        # density_plane and app_plane become fp16, the lines stay fp32).  Here it selects fp16 appearance
+        # storage when the tensor-core MLP is in use (planes AND lines: the gather interpolates in packed
+        # fp16) and leaves the density field in fp32: fp16 density moves weights across the w > 1e-3
+        # appearance threshold, so it is only ever switched on explicitly (density_plane_fp16=True).
         self.app_plane_fp16 = bool(app_plane_fp16) or (bool(getattr(args, "half_precision_param", False))
                                                        and int(mlp_mode) == 2)
-        # density planes and lines held as fp16 (GnrConfig.den_storage), the other half of that switch
-        self.density_plane_fp16 = bool(density_plane_fp16) or bool(getattr(args, "half_precision_param", False))
+        self.density_plane_fp16 = bool(density_plane_fp16)
+        # Density from the pre-summed lattice (gnr_build_density_lattice): one fp32 scalar per grid point,
+        # built on the device from the planes and lines at commit(); the same function of position, 8
+        # scalar taps per sample instead of 18 texels x 16 channels.  Costs 4 bytes per grid point of HBM.
+        self.density_lattice = bool(density_lattice)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -191,7 +199,9 @@ class B200GridNeRF(torch.nn.Module):
         self._handle = C.c_void_p(0)
         self._committed = False
         self._hull_tables_for = -1
-        self._ws: Dict[tuple, torch.Tensor] = {}
+        self._ws: Dict[int, torch.Tensor] = {}        # chunk slot -> scratch buffer (grows, never shrinks)
+        self._ws_bytes: Dict[tuple, int] = {}          # chunk shape -> bytes the library asks for
+        self._last_workspaces: list = []               # buffers the last render_rays call used
         # capacities of the two compacted sample lists, per ray of a chunk
         self.valid_capacity_per_ray: Optional[int] = None  # None = n_samples (can never overflow)
         self.app_capacity_per_ray = 192
@@ -318,6 +328,8 @@ class B200GridNeRF(torch.nn.Module):
                                                self.matMode[dim][0], self.matMode[dim][1], st), "gnr_upload_plane")
                     check(lib.gnr_upload_line(h, kind, idx, _ptr(l_), l_.shape[1], l_.shape[2], self.vecMode[dim], st),
                           "gnr_upload_line")
+            if self.density_lattice:
+                check(lib.gnr_build_density_lattice(h, 1, st), "gnr_build_density_lattice")
             self._upload_alpha_mask(st)
             self._upload_mlp(st)
             torch.cuda.current_stream().synchronize()
@@ -442,6 +454,8 @@ class B200GridNeRF(torch.nn.Module):
                                                self.matMode[dim][0], self.matMode[dim][1], raw), "gnr_upload_plane")
                     check(lib.gnr_upload_line(self._handle, kind, idx, _ptr(l_), l_.shape[1], l_.shape[2], self.vecMode[dim], raw),
                           "gnr_upload_line")
+            if self.density_lattice:  # same size as before: rebuilt in place, stream-ordered
+                check(lib.gnr_build_density_lattice(self._handle, 1, raw), "gnr_build_density_lattice")
 
     def release_torch_planes(self):
         """Drop the torch (NCHW) copies of the planes once the library holds its own
@@ -469,17 +483,31 @@ class B200GridNeRF(torch.nn.Module):
         return max(1, n_rays * per_valid), max(1, n_rays * per_app)
 
     def workspace(self, n_rays: int, n_samples: int, slot: int = 0):
+        """Scratch buffer of chunk slot ``slot`` (one per stream that renders chunks concurrently).
+
+        A slot keeps ONE buffer and only ever replaces it by a larger one: the library derives the
+        layout from the call's arguments, so a larger buffer serves every smaller shape.  Before a
+        buffer is replaced the device is synchronised, because kernels on a side stream may still
+        be using it and the caching allocator would hand its memory out again at once.  Callers
+        that bake the pointer into a CUDA graph keep their own reference to the returned tensor
+        (``GraphedFrameRenderer`` does), which keeps that memory out of the allocator for as long
+        as the graph lives."""
         max_valid, max_app = self.capacities(n_rays, n_samples)
-        key = (n_rays, n_samples, max_valid, max_app, slot)
-        buf = self._ws.get(key)
-        if buf is None:
+        key = (n_rays, n_samples, max_valid, max_app)
+        need = self._ws_bytes.get(key)
+        if need is None:
             nbytes = C.c_size_t(0)
             check(lib.gnr_workspace_bytes(self._handle, n_rays, n_samples, max_valid, max_app, C.byref(nbytes)),
                   "gnr_workspace_bytes")
-            if len(self._ws) > 6:
-                self._ws.clear()
-            buf = torch.empty(nbytes.value + 256, dtype=torch.uint8, device=self.device)
-            self._ws[key] = buf
+            if len(self._ws_bytes) > 256:
+                self._ws_bytes.clear()
+            need = self._ws_bytes[key] = int(nbytes.value)
+        buf = self._ws.get(slot)
+        if buf is None or buf.numel() < need + 256:
+            if buf is not None:
+                torch.cuda.synchronize(self.device)
+            buf = torch.empty(need + 256, dtype=torch.uint8, device=self.device)
+            self._ws[slot] = buf
         off = (-buf.data_ptr()) % 256
         return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off, max_valid, max_app
 
@@ -643,10 +671,12 @@ class B200GridNeRF(torch.nn.Module):
                     self._side_streams = [torch.cuda.Stream(device=self.device) for _ in range(n_side)]
                 for st_ in self._side_streams[:n_side]:
                     st_.wait_stream(main)
+            used = {}
             for ci, first in enumerate(range(0, n, chunk)):
                 m = min(chunk, n - first)
                 slot = ci % n_side if use_side else 0
                 keep, ws_ptr, ws_bytes, max_valid, max_app = self.workspace(chunk, s, slot)
+                used[slot] = keep
                 stream = self._side_streams[slot] if use_side else main
                 with torch.cuda.stream(stream):
                     check(lib.gnr_render_chunk(self._handle, C.c_void_p(rays.data_ptr() + first * 24), m, s,
@@ -659,6 +689,7 @@ class B200GridNeRF(torch.nn.Module):
                 for st_ in self._side_streams[:n_side]:
                     main.wait_stream(st_)
         self._pending_status = status
+        self._last_workspaces = list(used.values())
         return rgb_out, depth_out
 
     def check_pending_status(self):

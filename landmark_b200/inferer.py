@@ -16,31 +16,53 @@ import torch
 from .gridnerf import B200GridNeRF
 
 
+def _rgb_of(result) -> torch.Tensor:
+    """``rgb_map`` of a forward's result: the models return ``({"rgb_map": ...}, extra)``, some
+    forwards return the dict alone (both shapes are accepted by inferer_impl.py:112-118)."""
+    maps = result[0] if isinstance(result, tuple) else result
+    try:
+        return maps["rgb_map"]
+    except (KeyError, TypeError, IndexError):
+        raise Exception("cannot find correct key for ret") from None
+
+
 def renderer_fn(forward: Callable, rays: torch.Tensor, chunk_size: int, **kwargs) -> torch.Tensor:
-    """The chunk loop of inferer_impl.py:95-120, including its handling of the two return
-    shapes a forward may have and its error for a result without ``rgb_map``."""
-    all_ret = []
-    n_all = rays.shape[0]
-    for chunk_idx in range(n_all // chunk_size + int(n_all % chunk_size > 0)):
-        rays_chunk = rays[chunk_idx * chunk_size:(chunk_idx + 1) * chunk_size]
-        with torch.inference_mode():
-            ret = forward(rays_chunk, **kwargs)
-        if isinstance(ret, tuple) and "rgb_map" in ret[0]:
-            all_ret.append(ret[0]["rgb_map"])
-        elif "rgb_map" in ret:
-            all_ret.append(ret["rgb_map"])
-        else:
-            raise Exception("cannot find correct key for ret")
-    if not all_ret:
+    """The chunk loop of inferer_impl.py:95-120: ``forward`` on consecutive slices of
+    ``chunk_size`` rays, colours concatenated; a result without ``rgb_map`` is an error."""
+    if rays.shape[0] == 0:
         return rays.new_zeros((0, 3))
-    return torch.cat(all_ret, 0)
+    with torch.inference_mode():
+        parts = [_rgb_of(forward(piece, **kwargs)) for piece in torch.split(rays, chunk_size)]
+    return parts[0] if len(parts) == 1 else torch.cat(parts, 0)
+
+
+# Precision presets of the drop-in inferer.  "exact": fp32 everywhere, no termination (what the
+# reference's torch path computes; about 11x slower than "fast" on a city frame).  "fast": the
+# configuration the benchmark measures: tcgen05 MLP with fp16 operands, fp16 appearance planes,
+# rays stop at transmittance 2e-5, density from the pre-summed lattice; rgb stays within 1e-4 of
+# "exact" on the tested scenes.
+PRESETS = {
+    "exact": {"mlp_mode": 0, "ert_transmittance": 0.0, "app_plane_fp16": False, "density_lattice": False},
+    "fast": {"mlp_mode": 2, "ert_transmittance": 2e-5, "app_plane_fp16": True, "density_lattice": True},
+}
 
 
 class B200NerfDDPInfererImpl:
     """Drop-in for ``TorchNerfDDPInfererImpl``: same constructor argument (a context with
     ``args_nerf`` and ``model_path``), same methods and properties."""
 
-    def __init__(self, context, profile_stages: bool = False, mlp_mode: int = 0) -> None:
+    def __init__(self, context, profile_stages: bool = False, mlp_mode: Optional[int] = None, preset: str = "exact",
+                 **model_options) -> None:
+        """``preset`` picks a row of ``PRESETS`` ("exact" is the default so that a drop-in run first
+        reproduces the reference's numbers; "fast" is the benchmarked configuration);
+        ``mlp_mode`` and any further ``B200GridNeRF`` option (``ert_transmittance``,
+        ``app_plane_fp16``, ``density_plane_fp16``, ...) override single entries of it."""
+        if preset not in PRESETS:
+            raise ValueError(f"preset {preset!r} (one of {sorted(PRESETS)})")
+        self._model_options = dict(PRESETS[preset])
+        if mlp_mode is not None:
+            self._model_options["mlp_mode"] = int(mlp_mode)
+        self._model_options.update(model_options)
         self._chunk_size = context.args_nerf.render_batch_size
         self._args = context.args_nerf
         self._tensor_parallel = False
@@ -49,7 +71,6 @@ class B200NerfDDPInfererImpl:
         self._model = None
         self._model_path = getattr(context, "model_path", None)
         self._ckpt = getattr(context, "checkpoint", None)  # an already loaded checkpoint dict
-        self._mlp_mode = mlp_mode
 
     @property
     def args(self):
@@ -92,7 +113,7 @@ class B200NerfDDPInfererImpl:
         kwargs = dict(ckpt["kwargs"])
         kwargs.update({"device": device, "args": self._args, "is_train": False})
         kwargs = self.remove_old_kwargs(kwargs)
-        self._model = B200GridNeRF(**kwargs, mlp_mode=self._mlp_mode)
+        self._model = B200GridNeRF(**kwargs, **self._model_options)
         self._model.load(ckpt)
         self.set_forward_func(self._model)
 

@@ -594,3 +594,67 @@ def test_sampler_runs_and_skips_are_exact_on_many_random_rays(thres):
     assert np.array_equal(got["t_min"].cpu().numpy(), t_min)
     assert np.array_equal(got["counts"].cpu().numpy(), valid.sum(1))
     assert valid.sum() > 100000
+
+
+def test_density_lattice_is_the_same_function(tiny):
+    """density_lattice=True: the density feature comes from the pre-summed scalar lattice (trilinear,
+    8 taps) instead of 3 x (bilinear plane x linear line) over 16 channels.  Same function of the
+    position; only the order of the fp32 sums differs.  Sample sets stay bit-exact, the feature stays
+    within the bar of the plane path, flips of the w > 1e-3 appearance threshold are counted, and the
+    image stays within 1e-4 of the reference's."""
+    from landmark_b200 import _lib
+    from landmark_b200.model_parallel import density_points
+
+    spec, field, model, rays, ref, got = tiny
+    lat = cuda_model(spec, density_lattice=True)
+    out = lat.run_stages(rays.cuda(), spec.n_samples, True)
+    assert torch.equal(out["mask_words"], got["mask_words"]) and torch.equal(out["offsets"], got["offsets"])
+    d_plane = (out["sigma_feature"] - got["sigma_feature"]).abs().max().item()
+    d_ref = (out["sigma_feature"].cpu() - ref["sigma_feature"]).abs().max().item()
+    assert d_plane <= 5e-7 and d_ref <= 2e-6, (d_plane, d_ref)
+    assert (out["weight"].cpu() - ref["weight"][ref["ray_valid"]]).abs().max().item() <= 1e-6
+    app_ref = ref["app_mask"][ref["ray_valid"]]
+    app_got = torch.zeros_like(app_ref)
+    app_got[out["app_index"].cpu()] = True
+    assert int((app_got != app_ref).sum()) <= 3
+    fx = load_golden("tiny_lit.npz")
+    flipped = torch.unique(out["ray_index"].cpu()[app_got != app_ref])
+    _check_image(out["rgb_map"].cpu(), out["depth_map"].cpu(), torch.from_numpy(fx["rgb_map"]),
+                 torch.from_numpy(fx["depth_map"]), flipped)
+    # fused pass (march kernel) == stage-wise kernels, bit for bit, with the lattice as well
+    fwd, _ = lat(rays.cuda(), white_bg=True, N_samples=spec.n_samples)
+    assert torch.equal(fwd["rgb_map"], out["rgb_map"]) and torch.equal(fwd["depth_map"], out["depth_map"])
+    # point mode reads the lattice too
+    xyz = (torch.rand((5000, 3), generator=torch.Generator().manual_seed(3)) * 2 - 1).cuda()
+    assert (density_points(lat, xyz) - density_points(model, xyz)).abs().max().item() <= 5e-7
+    # points exactly on the faces of the box use the clamped taps of the plane path
+    faces = torch.tensor([[-1.0, -1.0, -1.0], [1.0, 1.0, 1.0], [1.0, -1.0, 0.3], [0.0, 1.0, -1.0]]).cuda()
+    assert (density_points(lat, faces) - density_points(model, faces)).abs().max().item() <= 5e-7
+    # a density upload makes the lattice stale: launches are refused until it is rebuilt
+    import ctypes as C
+
+    p0 = lat.density_plane[0].detach().float().contiguous()
+    _lib.check(_lib.lib.gnr_upload_plane(lat._handle, 0, 0, C.c_void_p(p0.data_ptr()), p0.shape[1], p0.shape[2], p0.shape[3],
+                                         0, 1, C.c_void_p(0)), "gnr_upload_plane")
+    with pytest.raises(_lib.GnrError, match="lattice"):
+        lat(rays.cuda()[:64], N_samples=spec.n_samples)
+    _lib.check(_lib.lib.gnr_build_density_lattice(lat._handle, 1, C.c_void_p(0)), "gnr_build_density_lattice")
+    again, _ = lat(rays.cuda(), white_bg=True, N_samples=spec.n_samples)
+    assert torch.equal(again["rgb_map"], fwd["rgb_map"])
+
+
+def test_density_lattice_needs_the_standard_layout():
+    """Multi-resolution fields (nine pairs on three grids) have no single lattice: refused."""
+    from landmark_b200 import _lib
+
+    spec = scenes.tiny_spec(height=8, width=8, n_samples=32, grid=32).lit()
+    args = scenes.model_args(spec, "cuda:0")
+    args.ndims, args.resMode = 1, [1, 2, 4]
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    ckpt = scenes.make_checkpoint(spec)
+    kw = dict(ckpt["kwargs"])
+    kw.update({"device": "cuda:0", "args": args, "is_train": False})
+    m = B200GridNeRF(**kw, density_lattice=True)
+    with pytest.raises(_lib.GnrError, match="lattice"):
+        m.commit()
