@@ -204,6 +204,8 @@ def main():
     ap.add_argument("--den-lattice", type=int, default=1, choices=(0, 1),
                     help="density from the pre-summed scalar lattice (4 B per grid point of HBM, 8 taps per sample) "
                          "instead of the 3 x (plane x line) x 16-channel gather")
+    ap.add_argument("--app-fusion", type=int, default=1, choices=(0, 1),
+                    help="appearance gather + basis projection + MLP as one kernel (needs --mlp-mode 2 --app-fp16 1)")
     ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
@@ -260,7 +262,8 @@ def main():
     kwargs = dict(ckpt["kwargs"])
     kwargs.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
     model = B200GridNeRF(**kwargs, mlp_mode=a.mlp_mode, ert_transmittance=a.ert, app_plane_fp16=bool(a.app_fp16),
-                         density_plane_fp16=bool(a.den_fp16), density_lattice=bool(a.den_lattice))
+                         density_plane_fp16=bool(a.den_fp16), density_lattice=bool(a.den_lattice),
+                         fused_appearance=bool(a.app_fusion))
     model.load(ckpt)
     if a.reload_test:
         from landmark_b200.dynamic import pin_block
@@ -481,10 +484,17 @@ def main():
                                      "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["app_gather"],
                                      "l1_to_register": l1_roof(app_l1_bytes, n_app, per_launch["app_gather"])}
     if per_launch["mlp"] > 0 and n_app > 0:
-        ach = n_app * MLP_FLOP_PER_SAMPLE / (per_launch["mlp"] * 1e-3) / 1e12
+        fused_app = per_launch["app_gather"] == 0 and a.mlp_mode == 2  # gather + basis + MLP in one kernel
+        flop = MLP_FLOP_PER_SAMPLE + (BASIS_FLOP_PER_SAMPLE if a.mlp_mode else 0)
+        ach = n_app * flop / (per_launch["mlp"] * 1e-3) / 1e12
         roof["mlp_kernel"] = {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                               "frac": ach / pk["bf16_tflops"], "ms_per_frame": per_launch["mlp"],
-                              "note": "fp32 CUDA-core kernel" if a.mlp_mode == 0 else "tcgen05 kernel"}
+                              "flop_per_sample": flop,
+                              "note": "fp32 CUDA-core kernel" if a.mlp_mode == 0 else
+                                      ("tcgen05 kernel with the appearance gather inside (app_mlp_fused_kernel)" if fused_app
+                                       else "tcgen05 kernel (basis + MLP)")}
+        if fused_app:
+            roof["mlp_kernel"]["l1_to_register"] = l1_roof(app_l1_bytes, n_app, per_launch["mlp"])
     dominant = max(roof, key=lambda k: roof[k]["ms_per_frame"]) if roof else None
     traffic = None
     tpath = os.path.join(ROOT, "profiles", "dram_traffic.txt")
@@ -512,7 +522,7 @@ def main():
                    "chunk_rays": a.chunk, "mlp_mode": a.mlp_mode, "chunk_overlap": f"{a.streams} streams" if not a.no_overlap else "none",
                    "ert_transmittance": a.ert, "app_plane_storage": "fp16" if a.app_fp16 else "fp32",
                    "density_plane_storage": "fp16" if a.den_fp16 else "fp32",
-                   "density_lattice": bool(a.den_lattice),
+                   "density_lattice": bool(a.den_lattice), "fused_appearance": bool(a.app_fusion),
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,

@@ -68,7 +68,11 @@ typedef struct GnrConfig {
   int32_t den_storage;      /* the same for the density planes and lines (the other half of the
                                reference's half_precision_param); any mlp_mode; 16 (padded) density
                                channels.  Sample sets do not depend on it; rgb moves by a few 1e-6. */
-  int32_t reserved[4];
+  int32_t unfused_appearance; /* 0 = gnr_render_chunk runs appearance gather, basis projection and MLP as ONE
+                               kernel whenever the model allows it (mlp_mode 2, app_storage 1, 48 padded
+                               appearance channels, at most 160 products per sample); 1 = always the separate
+                               gather and MLP kernels (what the stage-wise entries run).                  */
+  int32_t reserved[3];
 } GnrConfig;
 
 /* Indices into the 8 x int32 status block (first 32 bytes of every workspace). */
@@ -315,6 +319,15 @@ enum {
 };
 int gnr_profile_enable(GnrModel* m, int on);
 int gnr_profile_collect(GnrModel* m, float* stage_ms_h, int64_t* launches_h);
+
+/* Test hook for the bounded device-side waits of the tensor-core kernels.  ``wait_limit`` > 0 replaces
+ * the number of polls a wait may take (default 2^20); with ``expire`` != 0 one group of one CTA of every
+ * following tensor-core launch leaves out the step its next wait depends on (the bulk copy of its first
+ * tile in the MLP kernel, the commit of its first projection in the fused kernel), so that this wait
+ * runs out: the group raises status[GNR_ST_WAIT_EXPIRED] and stops, the kernel frees its tensor memory
+ * and returns, and the context stays usable.  ``expire`` = 0, ``wait_limit`` = 0 restores normal
+ * operation.  Nothing in this hook faults, traps or spins without bound. */
+int gnr_debug_wait(GnrModel* m, int expire, int wait_limit);
 
 /* Copy the 8-word status block of a workspace to the host (synchronises the stream). */
 int gnr_read_status(const void* workspace, int32_t* status_h, void* stream);

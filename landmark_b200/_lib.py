@@ -43,7 +43,8 @@ class GnrConfig(C.Structure):
         ("ert_transmittance", C.c_float),
         ("app_storage", C.c_int32),
         ("den_storage", C.c_int32),
-        ("reserved", C.c_int32 * 4),
+        ("unfused_appearance", C.c_int32),
+        ("reserved", C.c_int32 * 3),
     ]
 
 
@@ -88,6 +89,7 @@ SIGNATURES = {
     "gnr_composite_rgb": (_INT, [_P, _I64, _INT, _P, _SZ, _I64, _I64, _INT, _P, _I64, _P, _P, _P]),
     "gnr_profile_enable": (_INT, [_P, _INT]),
     "gnr_profile_collect": (_INT, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
+    "gnr_debug_wait": (_INT, [_P, _INT, _INT]),
     "gnr_read_status": (_INT, [_P, C.POINTER(C.c_int32), _P]),
 }
 

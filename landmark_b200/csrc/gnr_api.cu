@@ -726,6 +726,16 @@ extern "C" int gnr_workspace_bytes(const GnrModel* m, int64_t n_rays, int n_samp
   return 0;
 }
 
+extern "C" int gnr_debug_wait(GnrModel* m, int expire, int wait_limit) {
+  if (!m || wait_limit < 0) {
+    gnr_set_error("gnr_debug_wait: bad argument");
+    return -1;
+  }
+  m->debug_expire_wait = expire ? 1 : 0;
+  m->debug_wait_limit = wait_limit;
+  return 0;
+}
+
 extern "C" int gnr_read_status(const void* workspace, int32_t* status_h, void* stream) {
   if (!workspace || !status_h) {
     gnr_set_error("gnr_read_status: null argument");
@@ -937,13 +947,19 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
     StageScope sc(m, GNR_STAGE_COMPACT_APP, 4, st);
     GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st));
   }
-  {
-    StageScope sc(m, GNR_STAGE_APP_GATHER, 1, st);
-    GNR_LAUNCH_OK(run_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
-  }
-  {
+  if (gnr_app_fusable(m)) {
+    // gather + basis projection + MLP as one kernel: no operand of a sample leaves the SM
     StageScope sc(m, GNR_STAGE_MLP, 1, st);
-    GNR_LAUNCH_OK(run_mlp(m, p, rays, ws, L, /*write_features=*/0, st));
+    GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, gnr_coords_app(rays, ws, L), (float*)(ws + L.app_rgb), (int32_t*)(ws + L.status), st));
+  } else {
+    {
+      StageScope sc(m, GNR_STAGE_APP_GATHER, 1, st);
+      GNR_LAUNCH_OK(run_app_gather(m, p, rays, n, ws, L, max_valid, max_app, st));
+    }
+    {
+      StageScope sc(m, GNR_STAGE_MLP, 1, st);
+      GNR_LAUNCH_OK(run_mlp(m, p, rays, ws, L, /*write_features=*/0, st));
+    }
   }
   {
     StageScope sc(m, GNR_STAGE_COMPOSITE, 1, st);

@@ -14,19 +14,13 @@
 // to the opposite corner; taps outside the grid contribute zero.
 #include <cuda_fp16.h>
 
-#include "gnr_internal.cuh"
+#include "gnr_gather.cuh"
 
 namespace {
 
 constexpr int kBlock = 256;
 constexpr int kFeat = 28;  // accumulators per sample for the basis projection (app_dim <= 28)
 
-struct PlaneSet {
-  GnrPlane p[GNR_MAX_PLANES];
-  int n;
-};
-
-__device__ __forceinline__ float pick(float x, float y, float z, int a) { return a == 0 ? x : (a == 1 ? y : z); }
 
 // float4 arithmetic as two packed fp32x2 instructions each (sm_100 has paired FP32 pipes)
 __device__ __forceinline__ float4 f4_scale(float4 a, float s) {
@@ -51,19 +45,6 @@ __device__ __forceinline__ float4 f4_mul(float4 a, float4 b) {
 // and the lower corner to size - 2: no tap can fall outside and no bounds test is needed (a
 // point exactly on the upper face then takes the last texel with weight 1, which is what
 // zero padding gives as well).  All offsets are 32-bit float4 indices.
-// Lower grid index and fractional offset of one normalised coordinate on an axis of `size` points.
-struct Tap {
-  int i0;
-  float f1;
-};
-__device__ __forceinline__ Tap make_tap(float u, float fsize, int size) {
-  const float ix = fminf(fmaxf((u + 1.0f) * 0.5f * fsize, 0.0f), fsize);
-  Tap t;
-  t.i0 = min((int)ix, size - 2);
-  t.f1 = ix - (float)t.i0;
-  return t;
-}
-
 // The four channels 16 j + 4 c4 .. + 3 of texel `texel` (C channels per texel) from an fp32 or an
 // fp16 array.
 template <bool HALF>
@@ -289,42 +270,6 @@ build_lattice_kernel(PlaneSet planes, int C, int gx, int gy, int gz, float* __re
     }
     V[i] = (float)acc;
   }
-}
-
-// Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
-// computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
-// `view` (optional) receives the ray direction of the sample.
-__device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCoords& c, long long i, float& x, float& y,
-                                           float& z, float* view = nullptr) {
-  if (c.xyz_direct) {
-    x = __ldg(c.xyz_direct + i * 3 + 0);
-    y = __ldg(c.xyz_direct + i * 3 + 1);
-    z = __ldg(c.xyz_direct + i * 3 + 2);
-    if (view) {
-#pragma unroll
-      for (int a = 0; a < 3; ++a) view[a] = c.view_direct ? __ldg(c.view_direct + i * 3 + a) : 0.0f;
-    }
-    return;
-  }
-  const uint32_t id = __ldg(c.ids + (c.index ? (long long)__ldg(c.index + i) : i));
-  const uint32_t ray = id >> p.kbits;
-  const int k = (int)(id & ((1u << p.kbits) - 1u));
-  const float* r = c.rays + (size_t)ray * 6;
-  const float t = gnr_sample_t(p, __ldg(c.t_min + ray), k);
-  const float dx = __ldg(r + 3), dy = __ldg(r + 4), dz = __ldg(r + 5);
-  x = gnr_normalize(gnr_point(__ldg(r + 0), dx, t), p.lo[0], p.inv[0]);
-  y = gnr_normalize(gnr_point(__ldg(r + 1), dy, t), p.lo[1], p.inv[1]);
-  z = gnr_normalize(gnr_point(__ldg(r + 2), dz, t), p.lo[2], p.inv[2]);
-  if (view) {
-    view[0] = dx;
-    view[1] = dy;
-    view[2] = dz;
-  }
-}
-
-__device__ __forceinline__ long long coords_total(const GnrCoords& c) {
-  const long long t = c.total_ptr ? (long long)*c.total_ptr : c.total_direct;
-  return min(t, c.capacity);
 }
 
 __device__ __forceinline__ float density_activation(float f, float shift, int act) {
@@ -657,48 +602,12 @@ __device__ __forceinline__ void pair_products_thread48(const GnrPlane& pl, Tap t
   }
 }
 
-// fp16 storage: the 48 channels of a pair in three rounds of 16, six 256-bit loads per round, and
-// the interpolation itself in packed fp16 arithmetic (two channels per instruction, no
-// conversions).  Against fp32 interpolation of the same fp16 texels this adds four more fp16
-// roundings to a product that is rounded to fp16 for the tensor cores anyway; the rounding of
-// the stored texels remains the larger part of the error of the projected features.
-struct H16 {
-  uint32_t v[8];
-};
-__device__ __forceinline__ H16 ldg_h16(const void* base, uint32_t texel, int g) {
-  const unsigned char* ptr = reinterpret_cast<const unsigned char*>(base) + (size_t)texel * 96u + g * 32;
-  H16 r;
-  asm("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-      : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]), "=r"(r.v[7])
-      : "l"(ptr));
-  return r;
-}
-__device__ __forceinline__ __half2 as_h2(uint32_t u) { return *reinterpret_cast<const __half2*>(&u); }
-__device__ __forceinline__ uint32_t as_u32(__half2 h) { return *reinterpret_cast<const uint32_t*>(&h); }
-
 __device__ __forceinline__ void pair_products_thread48_h2(const GnrPlane& pl, Tap tx, Tap ty, Tap tl, unsigned char* out) {
-  const float ax1 = tx.f1, ay1 = ty.f1, al1 = tl.f1;
-  const float ax0 = 1.0f - ax1, ay0 = 1.0f - ay1, al0 = 1.0f - al1;
-  const __half2 w_nw = __float2half2_rn(ax0 * ay0), w_ne = __float2half2_rn(ax1 * ay0);
-  const __half2 w_sw = __float2half2_rn(ax0 * ay1), w_se = __float2half2_rn(ax1 * ay1);
-  const __half2 h_l0 = __float2half2_rn(al0), h_l1 = __float2half2_rn(al1);
-  const uint32_t nw = (uint32_t)ty.i0 * (uint32_t)pl.W + (uint32_t)tx.i0, sw = nw + (uint32_t)pl.W;
-  const uint32_t seg = (uint32_t)tl.i0;
+  const PairTapsH2 t = make_pair_taps_h2(pl, tx, ty, tl);
 #pragma unroll
   for (int g = 0; g < 3; ++g) {
-    const H16 a = ldg_h16(pl.plane, nw, g), b = ldg_h16(pl.plane, nw + 1u, g);
-    const H16 c = ldg_h16(pl.plane, sw, g), d = ldg_h16(pl.plane, sw + 1u, g);
-    const H16 l0 = ldg_h16(pl.line, seg, g), l1 = ldg_h16(pl.line, seg + 1u, g);
     uint32_t q[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      __half2 pv = __hmul2(as_h2(a.v[e]), w_nw);
-      pv = __hfma2(as_h2(b.v[e]), w_ne, pv);
-      pv = __hfma2(as_h2(c.v[e]), w_sw, pv);
-      pv = __hfma2(as_h2(d.v[e]), w_se, pv);
-      const __half2 lv = __hfma2(as_h2(l1.v[e]), h_l1, __hmul2(as_h2(l0.v[e]), h_l0));
-      q[e] = as_u32(__hmul2(pv, lv));
-    }
+    pair_round_h2(pl, t, g, q);
     *reinterpret_cast<uint4*>(out + (size_t)(2 * g) * 2048) = make_uint4(q[0], q[1], q[2], q[3]);
     *reinterpret_cast<uint4*>(out + (size_t)(2 * g + 1) * 2048) = make_uint4(q[4], q[5], q[6], q[7]);
   }
@@ -767,23 +676,6 @@ __global__ void positions_kernel(GnrSampleParams p, GnrCoords crd, float* __rest
     xyz[i * 3 + 2] = z;
     if (ray_index) ray_index[i] = (int32_t)(__ldg(crd.ids + i) >> p.kbits);
   }
-}
-
-// True if the three pairs are the standard VM layout on one grid: (x,y|z), (x,z|y), (y,z|x).
-bool standard_vm3(const PlaneSet& s) {
-  if (s.n != 3) return false;
-  const GnrPlane &a = s.p[0], &b = s.p[1], &c = s.p[2];
-  const bool modes = a.mat0 == 0 && a.mat1 == 1 && a.vec == 2 && b.mat0 == 0 && b.mat1 == 2 && b.vec == 1 &&
-                     c.mat0 == 1 && c.mat1 == 2 && c.vec == 0;
-  const bool sizes = b.W == a.W && b.H == a.L && b.L == a.H && c.W == a.H && c.H == a.L && c.L == a.W;
-  return modes && sizes;
-}
-
-PlaneSet make_set(const GnrPlane* src, int n) {
-  PlaneSet s;
-  s.n = n;
-  for (int i = 0; i < n; ++i) s.p[i] = src[i];
-  return s;
 }
 
 }  // namespace

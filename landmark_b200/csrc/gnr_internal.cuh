@@ -64,6 +64,8 @@ struct GnrModel {
   int aD, aH, aW;
   float a_lo[3], a_inv[3];
   GnrMlp mlp;
+  int debug_expire_wait;  // test hook (gnr_debug_wait): make one bounded wait of the tensor-core kernels run out
+  int debug_wait_limit;   // polls a bounded wait may take; 0 = the default
   // hull sampler tables (sampling_mode 1)
   float* hull_near_term;
   float* hull_u;
@@ -158,6 +160,10 @@ int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoor
                       cudaStream_t st);
 int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* prod_hi,
                         unsigned char* prod_lo, int tile_bytes, int terms, cudaStream_t st);
+// gather + basis + MLP in one kernel (gnr_app_fused.cu): 1 if this model can run it
+int gnr_app_fusable(const GnrModel* m);
+int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
+                         cudaStream_t st);
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,

@@ -110,6 +110,7 @@ class B200GridNeRF(torch.nn.Module):
         app_plane_fp16: bool = False,
         density_plane_fp16: bool = False,
         density_lattice: bool = False,
+        fused_appearance: bool = True,
         **_ignored,
     ):
         super().__init__()
@@ -168,6 +169,9 @@ class B200GridNeRF(torch.nn.Module):
         # built on the device from the planes and lines at commit(); the same function of position, 8
         # scalar taps per sample instead of 18 texels x 16 channels.  Costs 4 bytes per grid point of HBM.
         self.density_lattice = bool(density_lattice)
+        # forward() runs appearance gather + basis projection + MLP as one kernel when the library can
+        # (mlp_mode 2 with fp16 appearance planes); False keeps the separate kernels (GnrConfig.unfused_appearance)
+        self.fused_appearance = bool(fused_appearance)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -304,6 +308,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.ert_transmittance = self.ert_transmittance
         cfg.app_storage = 1 if self.app_plane_fp16 else 0
         cfg.den_storage = 1 if self.density_plane_fp16 else 0
+        cfg.unfused_appearance = 0 if self.fused_appearance else 1
         return cfg
 
     def commit(self, release_torch_planes: bool = False):
@@ -632,6 +637,11 @@ class B200GridNeRF(torch.nn.Module):
                 out.update({"rgb_map": rgb, "depth_map": depth})
             torch.cuda.current_stream().synchronize()
         return out
+
+    def debug_wait(self, expire: bool = False, wait_limit: int = 0):
+        """Test hook (gnr_debug_wait): make one bounded device-side wait of the next tensor-core launches
+        run out, with ``wait_limit`` polls per wait; ``debug_wait()`` restores normal operation."""
+        check(lib.gnr_debug_wait(self._handle, int(bool(expire)), int(wait_limit)), "gnr_debug_wait")
 
     def profile_enable(self, on: bool = True):
         check(lib.gnr_profile_enable(self._handle, int(on)), "gnr_profile_enable")

@@ -546,13 +546,16 @@ def test_fp16_density_planes_option():
         assert (st["rgb_map"] - b["rgb_map"]).abs().max().item() <= FLIP_RGB_TOL
 
 
-@pytest.mark.parametrize("mlp_mode", [0, 2])
+@pytest.mark.parametrize("mlp_mode", [0, 2, "fused"])
 def test_ragged_ray_counts_give_the_same_pixels(mlp_mode):
     """Ray counts that do not fill a warp, a 32-ray group or a 128-sample tile: every ray's pixel is
     what the same ray gets inside the full chunk (the kernels group rays by 32 and samples by 128,
     but no result depends on a ray's neighbours)."""
     spec = scenes.tiny_spec().lit()
-    model = cuda_model(spec, mlp_mode=mlp_mode)
+    if mlp_mode == "fused":  # gather + basis + MLP as one kernel (fp16 appearance planes)
+        model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True)
+    else:
+        model = cuda_model(spec, mlp_mode=mlp_mode)
     rays = tiny_rays(spec).cuda()
     full, _ = model(rays, N_samples=spec.n_samples)
     for start, count in ((0, 1), (4321, 31), (77, 33), (5000, 100), (9990, 10), (1234, 257)):
@@ -658,3 +661,91 @@ def test_density_lattice_needs_the_standard_layout():
     m = B200GridNeRF(**kw, density_lattice=True)
     with pytest.raises(_lib.GnrError, match="lattice"):
         m.commit()
+
+
+def _fused_pair(spec, ckpt=None, args=None, sd=None, kwargs=None):
+    """The same scene as two models: appearance as one kernel, and as the separate gather and MLP kernels."""
+    from landmark_b200.gridnerf import B200GridNeRF
+
+    out = []
+    for fused in (True, False):
+        if sd is None:
+            out.append(cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused))
+        else:
+            m = B200GridNeRF(**kwargs, device="cuda:0", args=args, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused)
+            m.load_state_dict(sd, strict=False)
+            m.commit()
+            out.append(m)
+    return out
+
+
+def test_fused_appearance_kernel_equals_separate_kernels():
+    """gather + basis projection + MLP in one kernel (operands in tensor memory) against the separate
+    gather and MLP kernels: the same products, the same GEMMs in the same K order, so the colours agree
+    to the last few bits (the view direction reaches the fused kernel as fp32 instead of fp16 hi + lo);
+    both stay within 1e-4 of the reference fixture.  Also with a black background, on the nine-tap
+    general layout, and on a chunk whose appearance list does not fill a tile."""
+    spec = scenes.tiny_spec().lit()
+    fx = load_golden("tiny_lit.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    rays = torch.from_numpy(fx["rays"]).cuda()
+    fused, split = _fused_pair(spec, ckpt)
+    for white in (True, False):
+        a, _ = fused(rays, white_bg=white, N_samples=spec.n_samples)
+        b, _ = split(rays, white_bg=white, N_samples=spec.n_samples)
+        assert int(fused.last_status[3]) == int(split.last_status[3]) > 10000
+        assert torch.equal(a["depth_map"], b["depth_map"])
+        assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+    a, _ = fused(rays, N_samples=spec.n_samples)
+    err = (a["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+    few = rays[5000:5003].contiguous()  # a handful of appearance samples: one partial tile
+    a, _ = fused(few, N_samples=spec.n_samples)
+    b, _ = split(few, N_samples=spec.n_samples)
+    assert 0 < int(fused.last_status[3]) < 128 * 3
+    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+    # three pairs that are not the standard VM layout (general branch of the fused gather)
+    spec2 = scenes.tiny_spec(grid=32).lit()
+    args = scenes.model_args(spec2)
+    args.ndims, args.resMode = 1, [1, 2, 4]
+    g = torch.Generator().manual_seed(11)
+    sd = {}
+    for j, r in enumerate([1, 2, 4]):
+        sd[f"density_plane.{j}"] = 0.1 * torch.randn((1, 16, 32 * r, 32 * r), generator=g)
+        sd[f"density_line.{j}"] = 0.1 * torch.randn((1, 16, 32 * r, 1), generator=g)
+        sd[f"app_plane.{j}"] = 0.1 * torch.randn((1, 48, 32 * r, 32 * r), generator=g)
+        sd[f"app_line.{j}"] = 0.1 * torch.randn((1, 48, 32 * r, 1), generator=g)
+    base = scenes.make_state_dict(spec2)
+    sd.update({k: v for k, v in base.items() if k.startswith(("renderModule", "basis_mat"))})
+    kwargs = scenes.model_kwargs(spec2)
+    kwargs["density_shift"] = 0.0
+    fused2, split2 = _fused_pair(spec2, args=args, sd=sd, kwargs=kwargs)
+    r2 = tiny_rays(scenes.tiny_spec(height=40, width=40)).cuda()
+    a, _ = fused2(r2, N_samples=64)
+    b, _ = split2(r2, N_samples=64)
+    assert int(fused2.last_status[3]) > 1000
+    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_bounded_wait_expires_and_the_context_survives(fused):
+    """The tensor-core kernels bound every wait on an mbarrier.  The test hook makes one group skip the
+    step its next wait depends on, with a short poll limit: the wait runs out, the kernel reports it in
+    the status block, frees its tensor memory and returns; the same context then renders correctly."""
+    spec = scenes.tiny_spec().lit()
+    model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused)
+    rays = tiny_rays(spec).cuda()
+    good, _ = model(rays, N_samples=spec.n_samples)
+    model.debug_wait(expire=True, wait_limit=2000)
+    model.check_status_every_call = False
+    model(rays, N_samples=spec.n_samples)
+    torch.cuda.synchronize()
+    keep, ws_ptr, *_ = model.workspace(rays.shape[0], spec.n_samples)
+    status = model.read_status(ws_ptr)
+    assert status[4] == 1  # GNR_ST_WAIT_EXPIRED
+    with pytest.raises(RuntimeError, match="wait expired"):
+        model.raise_on_status(status)
+    model.debug_wait()
+    model.check_status_every_call = True
+    again, _ = model(rays, N_samples=spec.n_samples)
+    assert torch.equal(again["rgb_map"], good["rgb_map"]) and int(model.last_status[4]) == 0
