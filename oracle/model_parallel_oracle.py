@@ -5,8 +5,11 @@ blocks is rendered: global sampling and occupancy filter as in the sequential mo
 ``assign_blocks_to_samples`` (app/models/gridnerf_parallel.py:296-327) gives every valid sample a
 block and block-local coordinates, each block's own field supplies sigma and colour for its
 samples (:765-859), and weights / compositing run over the merged values
-(app/models/gridnerf_sequential.py:477-504).  A sample with x or y exactly 1 is given to the last
-block (the reference's CUDA kernel drops such a sample, its torch path would index past the list).
+(app/models/gridnerf_sequential.py:477-504).  ``assign_blocks`` is pinned: tests/golden/make_golden.py
+runs the reference's own method on seeded points (including points on block borders) and asserts
+equality bit for bit (tests/golden/assign_blocks.npz).  The one intended difference lies outside that
+set: a sample with x or y exactly 1 is given to the last block here (the reference's CUDA kernel drops
+such a sample, its torch path gives it an index past the last block).
 
 The channel-parallel layout needs no oracle of its own: the sum of the ranks' partial basis
 projections is the projection of the unsplit model, so ``gridnerf_oracle.render_chunk`` on the

@@ -208,6 +208,44 @@ def pin_merged_stack():
     print(f"merged_stack_tiny.npz: merge_ckpts of {len(blocks)} blocks pinned, size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
 
 
+def pin_assign_blocks():
+    """Run the reference's own assign_blocks_to_samples (app/models/gridnerf_parallel.py:279-338) with a
+    stand-in ``self`` on seeded points and keep block ids and block-local coordinates; the oracle's
+    restatement (oracle/model_parallel_oracle.py) must reproduce both bit for bit.  The one intended
+    difference is outside the compared set: a point with x or y exactly 1 gets the block index
+    ``px * py + ...`` from the reference (past the last block, so none of its masks selects it), while
+    the restatement clamps it into the last block; the points here lie in [-1, 1)."""
+    from app.models.gridnerf_parallel import GridBaseParallel
+    from oracle import model_parallel_oracle as mpo
+
+    g = torch.Generator().manual_seed(4242)
+    xyz = torch.rand((4096, 3), generator=g) * 2 - 1
+    xyz[:64, 0] = -1.0                      # on the lower faces
+    xyz[64:128, 1] = -1.0
+    xyz[128:192, 0] = torch.linspace(-1, 1, 65)[:-1]  # on interior block borders for every division below
+    xyz[192:256, 1] = torch.linspace(-1, 1, 65)[:-1]
+    xyz[:, :2] = xyz[:, :2].clamp(max=float(np.nextafter(np.float32(1.0), np.float32(0.0))))
+    fx = {"xyz": xyz.numpy()}
+    for division in ((2, 1), (2, 2), (4, 2), (3, 5)):
+        fake = types.SimpleNamespace(args=types.SimpleNamespace(plane_division=list(division), ckpt_type="sub"), device="cpu")
+        masks, xyzb = GridBaseParallel.assign_blocks_to_samples(fake, xyz, None, False)
+        block = torch.full((xyz.shape[0],), -1, dtype=torch.int64)
+        for b, m in enumerate(masks):
+            assert not (block[m] >= 0).any()
+            block[m] = b
+        assert (block >= 0).all()
+        mine_block, mine_local = mpo.assign_blocks(xyz, division)
+        assert torch.equal(mine_block, block), division
+        assert torch.equal(mine_local, xyzb[:, :3]), division
+        tag = f"{division[0]}x{division[1]}"
+        fx[f"block_{tag}"] = block.numpy().astype(np.int32)
+        fx[f"local_{tag}"] = xyzb[:, :3].numpy()
+    path = os.path.join(HERE, "assign_blocks.npz")
+    np.savez_compressed(path, **fx)
+    print(f"assign_blocks.npz: assign_blocks_to_samples pinned for 4 divisions on {xyz.shape[0]} points, "
+          f"size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
+
+
 def pin_update_alpha_mask(GridNeRF, grid=(40, 36, 28)):
     """updateAlphaMask of the reference (gridnerf_sequential.py:321-384) on the tiny lit scene, with
     and without an existing mask; the oracle's restatement must give the same volume and box."""
@@ -282,6 +320,7 @@ def main():
                  "config[0] lit, encode_app=1, app_code=1234, every 5th ray", app_code=torch.tensor(1234))
 
     pin_merged_stack()
+    pin_assign_blocks()
     pin_update_alpha_mask(GridNeRF)
 
     if not a.skip_city:

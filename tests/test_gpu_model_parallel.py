@@ -111,6 +111,21 @@ def test_assign_blocks_matches_oracle_restatement():
         assert int(b0.max()) == division[0] * division[1] - 1 and int(b0.min()) == 0
 
 
+def test_assign_blocks_matches_the_reference_fixture():
+    """Block ids and block-local coordinates the reference's own assign_blocks_to_samples produced
+    (tests/golden/assign_blocks.npz, written by make_golden.py), against the device arithmetic."""
+    from landmark_b200.model_parallel import assign_blocks
+    from tests._util import load_golden
+
+    fx = load_golden("assign_blocks.npz")
+    xyz = torch.from_numpy(fx["xyz"]).cuda()
+    for division in ((2, 1), (2, 2), (4, 2), (3, 5)):
+        tag = f"{division[0]}x{division[1]}"
+        b, local = assign_blocks(xyz, division)
+        assert np.array_equal(b.cpu().numpy(), fx[f"block_{tag}"].astype(np.int64)), tag
+        assert np.array_equal(local.cpu().numpy(), fx[f"local_{tag}"]), tag
+
+
 def test_point_mode_entries_match_list_mode():
     """gnr_density_points / gnr_appearance_points on explicit coordinates give what the list-mode
     stages give for the same samples."""

@@ -151,3 +151,17 @@ def test_update_alpha_mask_fixture():
         assert np.array_equal(np.packbits(vol.numpy().reshape(-1)), fx[f"{tag}_volume_bits"])
         assert np.array_equal(box.numpy(), fx[f"{tag}_aabb"])
         assert 0 < int(vol.sum()) == int(fx[f"{tag}_occupied"]) < n
+
+
+def test_assign_blocks_fixture():
+    """The block assignment of the block-parallel oracle against what the reference's own
+    assign_blocks_to_samples returned for the same points (pinned by make_golden.py)."""
+    from oracle import model_parallel_oracle as mpo
+
+    fx = load_golden("assign_blocks.npz")
+    xyz = torch.from_numpy(fx["xyz"])
+    for division in ((2, 1), (2, 2), (4, 2), (3, 5)):
+        tag = f"{division[0]}x{division[1]}"
+        b, local = mpo.assign_blocks(xyz, division)
+        assert np.array_equal(b.numpy(), fx[f"block_{tag}"].astype(np.int64))
+        assert np.array_equal(local.numpy(), fx[f"local_{tag}"])
