@@ -250,6 +250,24 @@ def model_args(spec: SceneSpec, device: str = "cpu"):
     )
 
 
+def multires_state_dict(spec: SceneSpec, res_mode=(1, 2, 4), seed: int = 11) -> Dict[str, torch.Tensor]:
+    """State dict of the single-dimension multi-resolution layout the reference's city configs use
+    (``ndims=1``, ``resMode=[1,2,4]``: pair ``j`` is an xy plane and a z line at ``resMode[j]`` times the
+    grid, app/models/gridnerf_sequential.py:684-718), seeded; basis_mat and the MLP are those of
+    ``make_state_dict(spec)``."""
+    g = torch.Generator().manual_seed(seed)
+    gx, gy, gz = spec.grid
+    sd = {}
+    for j, r in enumerate(res_mode):
+        sd[f"density_plane.{j}"] = 0.1 * torch.randn((1, spec.density_n_comp[0], gy * r, gx * r), generator=g)
+        sd[f"density_line.{j}"] = 0.1 * torch.randn((1, spec.density_n_comp[0], gz * r, 1), generator=g)
+        sd[f"app_plane.{j}"] = 0.1 * torch.randn((1, spec.app_n_comp[0], gy * r, gx * r), generator=g)
+        sd[f"app_line.{j}"] = 0.1 * torch.randn((1, spec.app_n_comp[0], gz * r, 1), generator=g)
+    base = make_state_dict(spec)
+    sd.update({k: v for k, v in base.items() if k.startswith(("renderModule", "basis_mat"))})
+    return sd
+
+
 def make_checkpoint(spec: SceneSpec, seed: int = FIELD_SEED, mask_seed: int = MASK_SEED, device: str = "cpu"):
     """A dict in the reference's on-disk checkpoint format
     (app/models/gridnerf_sequential.py:209-223): kwargs, state_dict, bit-packed alpha mask."""

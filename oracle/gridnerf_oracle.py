@@ -35,12 +35,16 @@ class Field:
 
     def __init__(self, state_dict: Dict[str, torch.Tensor], kwargs: Dict[str, object],
                  alpha_volume: Optional[torch.Tensor], alpha_aabb: Optional[torch.Tensor],
-                 alpha_filter_thres: float = 0.0):
+                 alpha_filter_thres: float = 0.0, ndims: int = 3, res_mode=(1,)):
         sd = state_dict
-        self.density_plane = [sd[f"density_plane.{i}"].float() for i in range(3)]
-        self.density_line = [sd[f"density_line.{i}"].float() for i in range(3)]
-        self.app_plane = [sd[f"app_plane.{i}"].float() for i in range(3)]
-        self.app_line = [sd[f"app_line.{i}"].float() for i in range(3)]
+        # args.ndims dimensions x len(args.resMode) resolutions: pair idx belongs to dimension
+        # idx // len(resMode) (app/models/gridnerf_sequential.py:106-110,698-718,801-802)
+        self.ndims, self.n_res = int(ndims), len(res_mode)
+        n_pairs = self.ndims * self.n_res
+        self.density_plane = [sd[f"density_plane.{i}"].float() for i in range(n_pairs)]
+        self.density_line = [sd[f"density_line.{i}"].float() for i in range(n_pairs)]
+        self.app_plane = [sd[f"app_plane.{i}"].float() for i in range(n_pairs)]
+        self.app_line = [sd[f"app_line.{i}"].float() for i in range(n_pairs)]
         self.basis_w = sd["basis_mat.weight"].float()
         self.mlp_w = [sd[f"renderModule.mlp.{j}.weight"].float() for j in (0, 2, 4)]
         self.mlp_b = [sd.get(f"renderModule.mlp.{j}.bias") for j in (0, 2, 4)]
@@ -123,20 +127,21 @@ def sample_alpha(f: Field, pts):
     return F.grid_sample(f.alpha_volume, q.view(1, -1, 1, 1, 3), align_corners=True).view(-1)
 
 
-def _coords(xyz):
-    plane = torch.stack([xyz[..., list(MAT_MODE[i])] for i in range(3)]).view(3, -1, 1, 2)
-    line = torch.stack([xyz[..., VEC_MODE[i]] for i in range(3)])
-    line = torch.stack((torch.zeros_like(line), line), dim=-1).view(3, -1, 1, 2)
+def _coords(xyz, n: int = 3):
+    plane = torch.stack([xyz[..., list(MAT_MODE[i])] for i in range(n)]).view(n, -1, 1, 2)
+    line = torch.stack([xyz[..., VEC_MODE[i]] for i in range(n)])
+    line = torch.stack((torch.zeros_like(line), line), dim=-1).view(n, -1, 1, 2)
     return plane, line
 
 
 def density_feature(f: Field, xyz):
     """Sum over planes and channels of plane x line.  app/models/gridnerf_sequential.py:779-827."""
-    cp, cl = _coords(xyz)
+    cp, cl = _coords(xyz, f.ndims)
     sigma = torch.zeros((xyz.shape[0],))
-    for i in range(3):
-        p = F.grid_sample(f.density_plane[i], cp[[i]], align_corners=True).view(-1, xyz.shape[0])
-        l = F.grid_sample(f.density_line[i], cl[[i]], align_corners=True).view(-1, xyz.shape[0])
+    for i in range(len(f.density_plane)):
+        d = i // f.n_res
+        p = F.grid_sample(f.density_plane[i], cp[[d]], align_corners=True).view(-1, xyz.shape[0])
+        l = F.grid_sample(f.density_line[i], cl[[d]], align_corners=True).view(-1, xyz.shape[0])
         sigma = sigma + torch.sum(p * l, dim=0)
     return sigma
 
@@ -151,11 +156,12 @@ def feature2density(f: Field, feat):
 def app_feature(f: Field, xyz):
     """Plane x line products, concatenated and projected by ``basis_mat``.
     app/models/gridnerf_sequential.py:829-871."""
-    cp, cl = _coords(xyz)
+    cp, cl = _coords(xyz, f.ndims)
     ps, ls = [], []
-    for i in range(3):
-        ps.append(F.grid_sample(f.app_plane[i], cp[[i]], align_corners=True).view(-1, xyz.shape[0]))
-        ls.append(F.grid_sample(f.app_line[i], cl[[i]], align_corners=True).view(-1, xyz.shape[0]))
+    for i in range(len(f.app_plane)):
+        d = i // f.n_res
+        ps.append(F.grid_sample(f.app_plane[i], cp[[d]], align_corners=True).view(-1, xyz.shape[0]))
+        ls.append(F.grid_sample(f.app_line[i], cl[[d]], align_corners=True).view(-1, xyz.shape[0]))
     prod = (torch.cat(ps) * torch.cat(ls)).T
     return F.linear(prod, f.basis_w)
 
@@ -293,7 +299,7 @@ def update_alpha_mask(f: Field, grid_size, alpha_mask_thres: float = 1e-3, incre
     return volume, torch.stack((valid_xyz.amin(0), valid_xyz.amax(0)))
 
 
-def field_from_checkpoint(ckpt: Dict[str, object], alpha_filter_thres: float = 0.0) -> Field:
+def field_from_checkpoint(ckpt: Dict[str, object], alpha_filter_thres: float = 0.0, ndims: int = 3, res_mode=(1,)) -> Field:
     """Unpack a checkpoint dict the way ``GridBaseSequential.load`` does
     (app/models/gridnerf_sequential.py:225-242)."""
     import numpy as np
@@ -305,4 +311,4 @@ def field_from_checkpoint(ckpt: Dict[str, object], alpha_filter_thres: float = 0
         vol = torch.from_numpy(np.unpackbits(ckpt["alphaMask.mask"])[:n].reshape(shape))
         aabb = ckpt["alphaMask.aabb"]
     sd = {k: v.detach().cpu() for k, v in ckpt["state_dict"].items()}
-    return Field(sd, ckpt["kwargs"], vol, aabb, alpha_filter_thres)
+    return Field(sd, ckpt["kwargs"], vol, aabb, alpha_filter_thres, ndims, res_mode)

@@ -246,6 +246,47 @@ def pin_assign_blocks():
           f"size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
 
 
+def pin_multires(GridNeRF, raw2alpha):
+    """The multi-resolution single-dimension layout of the reference's city configs (``ndims=1``,
+    ``resMode=[1,2,4]``: three xy planes at 1x/2x/4x the grid with z lines) rendered by the reference
+    class itself, every stage compared with the oracle, through rgb_map."""
+    spec = scenes.tiny_spec(height=40, width=40, n_samples=64, grid=32).lit()
+    spec.name = "tiny_multires"
+    res_mode = [1, 2, 4]
+    ckpt = scenes.make_checkpoint(spec)
+    ckpt["state_dict"] = scenes.multires_state_dict(spec, res_mode)
+    args = scenes.model_args(spec)
+    args.ndims, args.resMode = 1, res_mode
+    kwargs = dict(ckpt["kwargs"])
+    kwargs.update({"device": "cpu", "args": args, "is_train": False})
+    pose = torch.from_numpy(scenes.make_pose(spec))
+    rays = orc.generate_rays(pose, spec.height, spec.width, spec.focal)
+    with torch.no_grad():
+        model = GridNeRF(**kwargs)
+        model.load(ckpt)
+        assert len(model.density_plane) == 3 and tuple(model.app_plane[2].shape[-2:]) == (128, 128)
+        ref = reference_stages(model, raw2alpha, rays, spec.n_samples)
+        ref_out, _ = model(rays, white_bg=True, is_train=False, N_samples=spec.n_samples)
+    field = orc.field_from_checkpoint(ckpt, 0.0, ndims=1, res_mode=res_mode)
+    mine = orc.render_chunk(field, rays, spec.n_samples, True, keep_stages=True)
+    for k in ("in_box", "ray_valid", "sigma_feature", "sigma", "weight", "app_mask", "app_features", "z_vals"):
+        check_equal(k, mine[k], ref[k])
+    check_equal("rgb_samples", mine["rgb"][mine["app_mask"]], ref["rgb_samples"])
+    check_equal("rgb_map", mine["rgb_map"], ref_out["rgb_map"])
+    check_equal("depth_map", mine["depth_map"], ref_out["depth_map"])
+    valid, app = ref["ray_valid"].numpy(), ref["app_mask"].numpy()
+    fx = {"note": np.array("ndims=1, resMode=[1,2,4], grid 32, 40x40 rays, 64 samples; rendered by the reference's GridNeRF"),
+          "state_dict_digest": np.array(scenes.state_dict_digest(ckpt["state_dict"])), "n_samples": np.array(spec.n_samples),
+          "rays": rays.numpy(), "valid_bits": np.packbits(valid, axis=1), "valid_counts": valid.sum(1).astype(np.int32),
+          "app_counts": app.sum(1).astype(np.int32), "sigma_feature": ref["sigma_feature"].numpy(),
+          "app_features_sub": ref["app_features"].numpy()[::7], "rgb_map": ref_out["rgb_map"].numpy(),
+          "depth_map": ref_out["depth_map"].numpy()}
+    path = os.path.join(HERE, "tiny_multires.npz")
+    np.savez_compressed(path, **fx)
+    print(f"tiny_multires.npz: rays {rays.shape[0]} valid {int(valid.sum())} app {int(app.sum())} "
+          f"rgb_mean {float(ref_out['rgb_map'].mean()):.4f} size {os.path.getsize(path) / 1e3:.0f} kB", flush=True)
+
+
 def pin_update_alpha_mask(GridNeRF, grid=(40, 36, 28)):
     """updateAlphaMask of the reference (gridnerf_sequential.py:321-384) on the tiny lit scene, with
     and without an existing mask; the oracle's restatement must give the same volume and box."""
@@ -321,6 +362,7 @@ def main():
 
     pin_merged_stack()
     pin_assign_blocks()
+    pin_multires(GridNeRF, raw2alpha)
     pin_update_alpha_mask(GridNeRF)
 
     if not a.skip_city:

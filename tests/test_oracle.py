@@ -165,3 +165,17 @@ def test_assign_blocks_fixture():
         b, local = mpo.assign_blocks(xyz, division)
         assert np.array_equal(b.numpy(), fx[f"block_{tag}"].astype(np.int64))
         assert np.array_equal(local.numpy(), fx[f"local_{tag}"])
+
+
+def test_multires_fixture():
+    """ndims=1, resMode=[1,2,4]: the oracle against the fixture the reference's GridNeRF class rendered."""
+    fx = load_golden("tiny_multires.npz")
+    spec = scenes.tiny_spec(height=40, width=40, n_samples=64, grid=32).lit()
+    ckpt = scenes.make_checkpoint(spec)
+    ckpt["state_dict"] = scenes.multires_state_dict(spec)
+    assert scenes.state_dict_digest(ckpt["state_dict"]) == str(fx["state_dict_digest"])
+    field = orc.field_from_checkpoint(ckpt, 0.0, ndims=1, res_mode=[1, 2, 4])
+    out = orc.render_chunk(field, torch.from_numpy(fx["rays"]), int(fx["n_samples"]), True, keep_stages=True)
+    assert np.array_equal(np.packbits(out["ray_valid"].numpy(), axis=1), fx["valid_bits"])
+    assert np.array_equal(out["sigma_feature"].numpy(), fx["sigma_feature"])
+    assert np.array_equal(out["rgb_map"].numpy(), fx["rgb_map"]) and np.array_equal(out["depth_map"].numpy(), fx["depth_map"])
