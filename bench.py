@@ -209,6 +209,7 @@ def main():
     ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
+    ap.add_argument("--no-variants", action="store_true", help="skip the extra configurations (literal scene, T < 1e-3, mlp_mode 1, ...)")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
     ap.add_argument("--streams", type=int, default=2, help="streams the chunks of a frame rotate over")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
@@ -365,7 +366,45 @@ def main():
     model.profile_enable(False)
     model.check_pending_status()
 
-    # ---- end to end: host rays in, host rgb/depth out, through the C ABI ---------------------
+    # ---- end to end through the runner API: pose on the host in, uint8 [H, W, 4] image on rank 0's host out.
+    # Inside the timed region, every frame: pose broadcast to the ranks, ray generation, the chunk loop,
+    # the NCCL all-gather of the tiles, frame assembly, RGBA8 conversion, the device->host copy of the
+    # image into pinned memory and the status read (dist_render/runner/ddp_runner/nerf_ddp_runner.py:25-42,
+    # dist_render/ddp_infer/nerf_inferer.py:345-378). -------------------------------------------------
+    from landmark_b200.engine import FrameRenderer, NerfDDPRunner
+
+    runner = NerfDDPRunner(FrameRenderer(model, S, True, chunk=a.chunk, streams=(1 if a.no_overlap else a.streams)),
+                           H, W, focal=spec.focal, rank=rank, world=world)
+    n_e2e_warm = 2
+
+    def e2e_frames(k):
+        if rank == 0:
+            for _ in range(k):
+                img = runner.run_batch(pose)
+            return img
+        runner.serve(max_frames=k)
+        return None
+
+    e2e_frames(n_e2e_warm)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    img_host = e2e_frames(a.steps)
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / a.steps
+    t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_s = float(t.item())
+    e2e_same = None
+    if rank == 0:
+        want = (image.clamp(0, 1) * 255).to(torch.uint8).view(H, W, 3).cpu().numpy()
+        e2e_same = bool(np.array_equal(img_host[..., :3], want))
+    del runner
+
+    # ---- the previous end-to-end figure, kept as an extra key: host rays in, host rgb/depth out through
+    # gnr_render_host (this rank's rays only, no gather) --------------------------------------------------
     rays_h = rays.cpu().pin_memory()
     rgb_h = torch.empty((n_local, 3), dtype=torch.float32).pin_memory()
     depth_h = torch.empty((n_local,), dtype=torch.float32).pin_memory()
@@ -377,12 +416,13 @@ def main():
     t0 = time.perf_counter()
     for _ in range(a.steps):
         model.render_host(rays_h, S, True, chunk=a.chunk, rgb_out=rgb_h, depth_out=depth_h)
-    e2e_s = (time.perf_counter() - t0) / a.steps
-    t = torch.tensor([e2e_s], device=device, dtype=torch.float64)
+    rays_e2e_s = (time.perf_counter() - t0) / a.steps
+    t = torch.tensor([rays_e2e_s], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_s = float(t.item())
+    rays_e2e_s = float(t.item())
     same = bool(torch.equal(rgb_h, rgb[:n_local].cpu()))
+    del rays_h, rgb_h, depth_h
 
     # ---- the frame as one replayed CUDA graph: pose in, RGBA8 pixels out (device) -----------------
     graphed = None
@@ -447,6 +487,71 @@ def main():
         del m2, rgb2, depth2
         torch.cuda.empty_cache()
 
+    # ---- other configurations of the same frame, a few frames each (N = 1): the literal density_shift = -10
+    # scene, the coarser termination the scene description names (T < 1e-3), the split-precision
+    # tensor-core mode, and the defaults with one optimisation switched off at a time ---------------------
+    variants = None
+    if world == 1 and not a.no_variants:
+        variants = {}
+
+        def measure(label, what, workload=None, **opts):
+            _, ck, _ = build_scene(workload or a.workload, device, a.frame)
+            kw = dict(ck["kwargs"])
+            kw.update({"device": device, "args": scenes.model_args(spec, device), "is_train": False})
+            base = {"mlp_mode": a.mlp_mode, "ert_transmittance": a.ert, "app_plane_fp16": bool(a.app_fp16),
+                    "density_plane_fp16": bool(a.den_fp16), "density_lattice": bool(a.den_lattice),
+                    "fused_appearance": bool(a.app_fusion)}
+            base.update(opts)
+            mv = B200GridNeRF(**kw, **base)
+            mv.load(ck)
+            mv.release_torch_planes()
+            del ck
+            torch.cuda.empty_cache()
+            out_rgb, out_depth = torch.zeros_like(rgb), torch.zeros_like(depth)
+
+            def one():
+                mv.render_rays(rays, S, True, chunk=a.chunk, rgb_out=out_rgb[:n_local], depth_out=out_depth[:n_local],
+                               overlap=(0 if a.no_overlap else a.streams))
+
+            for _ in range(3):
+                one()
+            mv.check_pending_status()
+            torch.cuda.synchronize()
+            v0, v1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            v0.record()
+            for _ in range(3):
+                one()
+            v1.record()
+            torch.cuda.synchronize()
+            stv = mv.check_pending_status()
+            ms_v = v0.elapsed_time(v1) / 3
+            diff = (out_rgb[:n_local] - rgb[:n_local]).abs().max(dim=1).values
+            variants[label] = {"what": what, "ms_per_frame": ms_v, "Mrays_per_s": H * W / (ms_v * 1e-3) / 1e6,
+                               "appearance_samples": float(stv[3]), "density_evaluated": float(stv[5]),
+                               "max_abs_rgb_diff_vs_headline": float(diff.max()), "rays_above_1e-4_vs_headline": int((diff > 1e-4).sum())}
+            del mv, out_rgb, out_depth
+            torch.cuda.empty_cache()
+
+        if a.workload == "city_lit":
+            measure("city_literal", "the scene with its literal density_shift = -10: no sample passes the appearance "
+                    "threshold, only sampling, density and compositing run (rgb is not comparable with the headline)", workload="city")
+        measure("ert_1e-3", "rays stop at transmittance < 1e-3 (the scene description's own termination)", ert_transmittance=1e-3)
+        measure("mlp_mode_1", "tcgen05 MLP with activations and products as fp16 hi + lo, fp32 appearance planes, separate kernels",
+                mlp_mode=1, app_plane_fp16=False)
+        measure("separate_appearance_kernels", "appearance gather and MLP as two kernels (product tiles through HBM)",
+                fused_appearance=False)
+        measure("density_from_planes", "density from the three plane x line pairs instead of the pre-summed lattice",
+                density_lattice=False)
+
+    l1_measured = None
+    if world == 1:
+        from landmark_b200._lib import check as _check, lib as _glib
+        import ctypes as _C
+
+        val = _C.c_float(0.0)
+        _check(_glib.gnr_measure_l1_bandwidth(local_rank, 4000, _C.byref(val)), "gnr_measure_l1_bandwidth")
+        l1_measured = float(val.value)
+
     tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local), float(stats[5])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
@@ -461,55 +566,65 @@ def main():
     per_launch = {k: (stage_ms[k] / a.steps) for k in stage_ms}  # ms per frame per stage (all chunks)
     roof = {}
     sm_mhz = float((clocks or {}).get("sm_mhz") or 1965.0)
-    l1_peak = L1_BYTES_PER_CLOCK_PER_SM * torch.cuda.get_device_properties(device).multi_processor_count * sm_mhz * 1e6 / 1e9
+    l1_nominal = L1_BYTES_PER_CLOCK_PER_SM * torch.cuda.get_device_properties(device).multi_processor_count * sm_mhz * 1e6 / 1e9
+    l1_peak = l1_measured if l1_measured else l1_nominal
+    l1_peak_is = ("measured on this GPU in this run: L1-resident 256-bit loads into registers (gnr_measure_l1_bandwidth)"
+                  if l1_measured else "128 B/clk/SM x SMs x median SM clock (nominal)")
+    dram = {}
+    tpath = os.path.join(ROOT, "profiles", "dram_traffic.txt")
+    if os.path.exists(tpath):
+        with open(tpath) as fh:
+            dram = json.load(fh)
 
     def l1_roof(bytes_per_sample, samples, ms):
         ach_l1 = samples * bytes_per_sample / (ms * 1e-3) / 1e9
-        return {"achieved": ach_l1, "peak": l1_peak, "unit": "GB/s", "frac": ach_l1 / l1_peak,
-                "peak_is": "128 B/clk/SM x SMs x median SM clock (nominal L1 width, not measured)"}
+        return {"achieved": ach_l1, "peak": l1_peak, "unit": "GB/s", "frac": ach_l1 / l1_peak, "peak_is": l1_peak_is,
+                "bytes_per_sample": bytes_per_sample}
 
-    app_bytes = APP_BYTES_PER_SAMPLE if not a.app_fp16 else 1164
+    def hbm_part(key, samples, ms):
+        """DRAM traffic of the kernel (ncu, per sample, scaled to this frame) against the measured copy bandwidth."""
+        if key not in dram:
+            return None
+        tb = dram[key]["dram_bytes_per_sample"] * samples
+        ach_d = tb / (ms * 1e-3) / 1e9
+        return {"traffic_bytes": tb, "achieved": ach_d, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach_d / pk["hbm_gbs"],
+                "source": dram[key].get("source")}
+
     app_l1_bytes = APP_L1_BYTES_PER_SAMPLE // (2 if a.app_fp16 else 1)
     if per_launch["density"] > 0:
-        den_bytes = DENSITY_BYTES_PER_SAMPLE if not a.den_fp16 else 400  # 3 x 4 x 16 ch x 2 B + 12 B + 4 B
-        ach = n_density * den_bytes / (per_launch["density"] * 1e-3) / 1e9
-        roof["density_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                  "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["density"],
-                                  "samples_gathered": n_density,
-                                  "l1_to_register": l1_roof(DENSITY_L1_BYTES_PER_SAMPLE // (2 if a.den_fp16 else 1), n_density, per_launch["density"]),
-                                  "note": "fused density gather + transmittance product (march_kernel)" if a.ert >= 0 else "density_kernel"}
+        if a.den_lattice:
+            key, l1b = "march_lattice_kernel", 8 * 4  # eight scalar taps of the pre-summed lattice
+            note = "fused density (8-tap lattice) + transmittance product + termination (march_kernel, LAT)"
+        else:
+            key, l1b = "density_kernel", DENSITY_L1_BYTES_PER_SAMPLE // (2 if a.den_fp16 else 1)
+            note = "fused density gather (18 taps x 16 ch) + transmittance product (march_kernel)"
+        r = l1_roof(l1b, n_density, per_launch["density"])
+        roof["density_kernel"] = {"bound": "l1", **r, "ms_per_frame": per_launch["density"], "samples_gathered": n_density,
+                                  "hbm": hbm_part(key, n_density, per_launch["density"]), "note": note}
     if per_launch["app_gather"] > 0 and n_app > 0:
-        ach = n_app * app_bytes / (per_launch["app_gather"] * 1e-3) / 1e9
-        roof["app_gather_kernel"] = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                     "frac": ach / pk["hbm_gbs"], "ms_per_frame": per_launch["app_gather"],
-                                     "l1_to_register": l1_roof(app_l1_bytes, n_app, per_launch["app_gather"])}
+        r = l1_roof(app_l1_bytes, n_app, per_launch["app_gather"])
+        roof["app_gather_kernel"] = {"bound": "l1", **r, "ms_per_frame": per_launch["app_gather"],
+                                     "hbm": hbm_part("app_gather_kernel", n_app, per_launch["app_gather"])}
     if per_launch["mlp"] > 0 and n_app > 0:
         fused_app = per_launch["app_gather"] == 0 and a.mlp_mode == 2  # gather + basis + MLP in one kernel
         flop = MLP_FLOP_PER_SAMPLE + (BASIS_FLOP_PER_SAMPLE if a.mlp_mode else 0)
         ach = n_app * flop / (per_launch["mlp"] * 1e-3) / 1e12
+        key = "app_mlp_fused_kernel" if fused_app else "mlp_kernel"
         roof["mlp_kernel"] = {"bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
-                              "frac": ach / pk["bf16_tflops"], "ms_per_frame": per_launch["mlp"],
-                              "flop_per_sample": flop,
+                              "frac": ach / pk["bf16_tflops"], "ms_per_frame": per_launch["mlp"], "flop_per_sample": flop,
+                              "hbm": hbm_part(key, n_app, per_launch["mlp"]),
                               "note": "fp32 CUDA-core kernel" if a.mlp_mode == 0 else
                                       ("tcgen05 kernel with the appearance gather inside (app_mlp_fused_kernel)" if fused_app
                                        else "tcgen05 kernel (basis + MLP)")}
         if fused_app:
             roof["mlp_kernel"]["l1_to_register"] = l1_roof(app_l1_bytes, n_app, per_launch["mlp"])
     dominant = max(roof, key=lambda k: roof[k]["ms_per_frame"]) if roof else None
-    traffic = None
-    tpath = os.path.join(ROOT, "profiles", "dram_traffic.txt")
-    if dominant and os.path.exists(tpath):
-        with open(tpath) as fh:
-            tj = json.load(fh)
-        if dominant in tj:
-            units = n_density if dominant == "density_kernel" else n_app
-            traffic = tj[dominant]["dram_bytes_per_sample"] * units
     roofline = None
     if dominant:
         roofline = dict(roof[dominant])
         roofline["kernel"] = dominant
-        roofline["peak_source"] = f"of {pk['source']}"
-        roofline["traffic"] = traffic
+        roofline["peak_source"] = f"of {pk['source']}" if roofline["bound"] == "tensor" else roofline.get("peak_is")
+        roofline["traffic"] = (roofline.get("hbm") or {}).get("traffic_bytes")
         roofline["per"] = "frame (sum over the chunk launches of this kernel)"
         roofline["timing"] = "CUDA events around the kernel on its stream, single-stream pass of the same K frames"
 
@@ -527,8 +642,14 @@ def main():
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,
         "e2e": {"value": H * W / e2e_s / 1e6, "unit": "Mrays/s", "ms_per_frame": e2e_s * 1e3,
-                "h2d_bytes_per_step": int(n_local * 24), "d2h_bytes_per_step": int(n_local * 16),
-                "matches_device_path": same},
+                "h2d_bytes_per_step": 56, "d2h_bytes_per_step": int(H * W * 4),
+                "api": "NerfDDPRunner.run_batch(pose) -> uint8 [H, W, 4] on rank 0's host: pose broadcast, ray generation, "
+                       "chunk loop, tile all-gather, frame assembly, RGBA8, pinned device->host copy, status read",
+                "same_pixels_as_device_path": e2e_same},
+        "e2e_ray_buffers": {"value": H * W / rays_e2e_s / 1e6, "unit": "Mrays/s", "ms_per_frame": rays_e2e_s * 1e3,
+                            "h2d_bytes_per_step": int(n_local * 24), "d2h_bytes_per_step": int(n_local * 16),
+                            "api": "gnr_render_host: this rank's host rays in, host rgb + depth out (no gather)",
+                            "matches_device_path": same},
         "gpu_launches": int(sum(stage_launches.values())),
         "clocks": clocks,
         "roofline": roofline,
@@ -541,6 +662,8 @@ def main():
         line["graph_replay"] = graphed
     if strict is not None:
         line["strict_fp32"] = strict
+    if variants is not None:
+        line["variants"] = variants
     if cpu_sd is not None:
         from oracle import gridnerf_oracle as orc
 
@@ -558,6 +681,30 @@ def main():
         line["cpu_baseline"] = {"value": CPU_SAMPLE_RAYS / dt / 1e6, "unit": "Mrays/s", "cores": cores, "kind": "port",
                                 "sample": f"{CPU_SAMPLE_RAYS} rays (image rows 536-570), one pass, torch {torch.__version__} CPU",
                                 "rays_above_1e-4_vs_gpu": int((err > 1e-4).sum()), "max_abs_rgb_diff": float(err.max())}
+        # the same torch port on this GPU (the reference's torch path with device="cuda"): a same-hardware
+        # reference point between the CPU baseline and the CUDA path
+        try:
+            gfield = orc.Field(cpu_sd, scenes.model_kwargs(spec), vol, torch.tensor(spec.aabb), 0.0).to(device)
+            gs = sample.to(device)
+            chunk_t = 8192  # the reference's render_batch_size
+            orc.render_rays(gfield, gs[:chunk_t], S, True, chunk=chunk_t)
+            torch.cuda.synchronize()
+            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            c0.record()
+            g_rgb, _ = orc.render_rays(gfield, gs, S, True, chunk=chunk_t)
+            c1.record()
+            torch.cuda.synchronize()
+            ms_t = c0.elapsed_time(c1)
+            errg = (got["rgb_map"] - g_rgb).abs().max(dim=1).values
+            line["torch_cuda_baseline"] = {"value": CPU_SAMPLE_RAYS / (ms_t * 1e-3) / 1e6, "unit": "Mrays/s",
+                                           "ms_per_frame_extrapolated": ms_t * H * W / CPU_SAMPLE_RAYS,
+                                           "what": f"the same torch port with every tensor on {torch.cuda.get_device_name(device)} "
+                                                   f"(grid_sample, cumprod, linear: stock torch {torch.__version__} kernels), "
+                                                   f"{CPU_SAMPLE_RAYS} rays in chunks of {chunk_t}",
+                                           "rays_above_1e-4_vs_cuda_path": int((errg > 1e-4).sum())}
+            del gfield, gs, g_rgb
+        except RuntimeError as exc:  # e.g. out of memory on a smaller GPU: report, do not fail the bench
+            line["torch_cuda_baseline"] = {"unavailable": str(exc).splitlines()[0][:200]}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -320,6 +320,13 @@ enum {
 int gnr_profile_enable(GnrModel* m, int on);
 int gnr_profile_collect(GnrModel* m, float* stage_ms_h, int64_t* launches_h);
 
+/* Measurement helper for roofline figures: the rate (GB/s, whole GPU) at which the L1 caches deliver
+ * 256-bit loads that hit in L1 into registers, measured with a small kernel that re-reads a per-CTA
+ * buffer ``iters`` times (CUDA events around one launch).  The feature gathers of this library are bound
+ * by that path, not by HBM, so their roofline fractions are quoted against this number.  Host call;
+ * allocates and frees its own few megabytes; synchronises the device. */
+int gnr_measure_l1_bandwidth(int device, int iters, float* gb_per_s_h);
+
 /* Test hook for the bounded device-side waits of the tensor-core kernels.  ``wait_limit`` > 0 replaces
  * the number of polls a wait may take (default 2^20); with ``expire`` != 0 one group of one CTA of every
  * following tensor-core launch leaves out the step its next wait depends on (the bulk copy of its first

@@ -702,6 +702,63 @@ GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L) {
   return c;
 }
 
+// ---- measurement helper: rate of L1-resident 256-bit loads ------------------------------------------
+// Every warp re-reads its own 8 KB window (1 KB per instruction, lanes 32 bytes apart) of a per-CTA
+// buffer that stays in L1: what the kernel moves is exactly the L1 -> register traffic the gathers are
+// bound by, with no misses, no address arithmetic to speak of and eight loads in flight per thread.
+namespace {
+__global__ void __launch_bounds__(256) l1_read_kernel(const float* __restrict__ buf, int iters, float* __restrict__ sink) {
+  const float* base = buf + (size_t)blockIdx.x * 16384 + (threadIdx.x >> 5) * 2048 + (threadIdx.x & 31) * 8;
+  float acc = 0.0f;
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      // volatile: every iteration really loads (the window is re-read, it never changes)
+      float a0, a1, a2, a3, a4, a5, a6, a7;
+      asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                   : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
+                   : "l"(base + u * 256));
+      acc += (a0 + a1) + (a2 + a3) + (a4 + a5) + (a6 + a7);
+    }
+  }
+  if (acc == 123.456f) sink[0] = acc;  // never true for the zero-filled buffer; keeps the sums alive
+}
+}  // namespace
+
+extern "C" int gnr_measure_l1_bandwidth(int device, int iters, float* gb_per_s_h) {
+  if (!gb_per_s_h || iters < 1 || iters > (1 << 20)) {
+    gnr_set_error("gnr_measure_l1_bandwidth: bad argument");
+    return -1;
+  }
+  int prev = 0;
+  cudaGetDevice(&prev);
+  GNR_CUDA_OK(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  GNR_CUDA_OK(cudaGetDeviceProperties(&prop, device));
+  const int ctas = prop.multiProcessorCount * 4;
+  float *buf = nullptr, *sink = nullptr;
+  cudaEvent_t e0, e1;
+  GNR_CUDA_OK(cudaMalloc(&buf, (size_t)ctas * 16384 * sizeof(float)));
+  GNR_CUDA_OK(cudaMalloc(&sink, 256));
+  GNR_CUDA_OK(cudaMemset(buf, 0, (size_t)ctas * 16384 * sizeof(float)));
+  GNR_CUDA_OK(cudaEventCreate(&e0));
+  GNR_CUDA_OK(cudaEventCreate(&e1));
+  l1_read_kernel<<<ctas, 256>>>(buf, 16, sink);  // warm-up
+  GNR_CUDA_OK(cudaEventRecord(e0));
+  l1_read_kernel<<<ctas, 256>>>(buf, iters, sink);
+  GNR_CUDA_OK(cudaEventRecord(e1));
+  GNR_CUDA_OK(cudaEventSynchronize(e1));
+  float ms = 0.0f;
+  GNR_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+  *gb_per_s_h = (float)((double)ctas * 256 * iters * 8 * 32 / (ms * 1e-3) / 1e9);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(buf);
+  cudaFree(sink);
+  cudaSetDevice(prev);
+  return 0;
+}
+
 static LatticeRef lattice_of(const GnrModel* m) {
   LatticeRef r;
   r.v = m->den_lattice;

@@ -34,8 +34,9 @@ class FrameRenderer:
     """Renders the pixels a rank owns.  The default implementation drives ``B200GridNeRF``; tests
     substitute a CPU fake with the same two methods to exercise the multi-rank protocol."""
 
-    def __init__(self, model, n_samples: int = -1, white_bg: bool = True, chunk: int = 131072):
+    def __init__(self, model, n_samples: int = -1, white_bg: bool = True, chunk: int = 131072, streams: int = 2):
         self.model, self.n_samples, self.white_bg, self.chunk = model, n_samples, white_bg, chunk
+        self.streams = streams  # consecutive chunks of a frame rotate over this many streams
         self.device = model.device
 
     def render_pixels(self, pose: np.ndarray, H: int, W: int, focal: float, pixel_ids: torch.Tensor,
@@ -43,7 +44,8 @@ class FrameRenderer:
         from .rays import generate_rays
 
         rays = generate_rays(pose, H, W, focal, device=self.device, pixel_ids=pixel_ids)
-        self.model.render_rays(rays, self.n_samples, self.white_bg, chunk=self.chunk, rgb_out=rgb_out)
+        self.model.render_rays(rays, self.n_samples, self.white_bg, chunk=self.chunk, rgb_out=rgb_out,
+                               overlap=self.streams if self.streams > 1 else False)
 
     def finish(self):
         self.model.check_pending_status()
@@ -59,9 +61,9 @@ class FrameRenderer:
 class GraphedFrameRenderer:
     """One frame of a fixed shape as a replayable CUDA graph.
 
-    Pose upload, ray generation for this rank's pixels, the chunk loop of ``render_rays`` on its
-    streams, and the RGBA8 conversion are captured once; ``render(pose)`` writes the 12 pose floats
-    into a pinned host buffer and replays the graph, so a frame costs one launch on the host instead
+    Ray generation for this rank's pixels (from a pose in device memory), the chunk loop of
+    ``render_rays`` on its streams, and the RGBA8 conversion are captured once; ``render(pose)`` copies
+    the 12 pose floats through a pinned slot into that device buffer and replays the graph, so a frame costs one launch on the host instead
     of some 400 (the three-stage overlap of dist_render/runner/pipe_runner/nerf_pipe_runner.py:102-140
     then needs no host thread per stage).  Every buffer the graph touches is allocated before the
     capture and kept alive here.  List overflow / expired waits are read from the status blocks
@@ -79,12 +81,21 @@ class GraphedFrameRenderer:
         n = self.n = self.H * self.W if pixel_ids is None else int(self.pixel_ids.numel())
         dx, dy = direction_tables(self.H, self.W, self.focal)
         self.dir_x, self.dir_y = dx.to(dev), dy.to(dev)
-        self.pose_host = torch.zeros(12, dtype=torch.float32).pin_memory()
+        # pinned pose slots: a frame's pose copy reads its slot when the stream gets there, so frames
+        # submitted before earlier ones have run each need their own (8 frames may be in flight)
+        self.pose_ring = torch.zeros((8, 12), dtype=torch.float32).pin_memory()
+        self._pose_slot = 0
         self.pose_dev = torch.zeros(12, dtype=torch.float32, device=dev)
         self.rays = torch.empty((n, 6), dtype=torch.float32, device=dev)
         self.rgb = torch.empty((n, 3), dtype=torch.float32, device=dev)
         self.depth = torch.empty((n,), dtype=torch.float32, device=dev)
         self.rgba = torch.empty((n, 4), dtype=torch.uint8, device=dev)
+        # with a pixel list that covers the whole frame (e.g. tile order, which the kernels prefer) the graph
+        # also scatters the pixels back into row-major order: ``rgba_frame`` is the image
+        self.rgba_frame = None
+        if self.pixel_ids is not None and n == self.H * self.W:
+            self._pixel_ids64 = self.pixel_ids.to(torch.int64)
+            self.rgba_frame = torch.zeros((n, 4), dtype=torch.uint8, device=dev)
         self.graph = None
 
     def _enqueue(self):
@@ -92,7 +103,6 @@ class GraphedFrameRenderer:
 
         with torch.cuda.device(self.device):
             st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
-            self.pose_dev.copy_(self.pose_host, non_blocking=True)
             check(lib.gnr_generate_rays_dev(C.c_void_p(self.pose_dev.data_ptr()), C.c_void_p(self.dir_x.data_ptr()),
                                             C.c_void_p(self.dir_y.data_ptr()), self.H, self.W,
                                             C.c_void_p(self.pixel_ids.data_ptr() if self.pixel_ids is not None else 0),
@@ -104,6 +114,8 @@ class GraphedFrameRenderer:
             self._workspaces = list(self.model._last_workspaces)
             check(lib.gnr_rgba8(C.c_void_p(self.rgb.data_ptr()), self.n, C.c_void_p(self.rgba.data_ptr()),
                                 C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gnr_rgba8")
+            if self.rgba_frame is not None:
+                self.rgba_frame.view(torch.int32).view(-1).index_copy_(0, self._pixel_ids64, self.rgba.view(torch.int32).view(-1))
 
     def capture(self, pose: np.ndarray):
         """Warm up (creates workspaces and side streams) and capture the frame."""
@@ -124,8 +136,14 @@ class GraphedFrameRenderer:
         return self
 
     def _set_pose(self, pose):
+        """Pose -> next pinned slot -> device pose buffer (an asynchronous copy on the current stream,
+        in front of the graph, which reads the pose from device memory)."""
         p = np.asarray(pose.cpu() if isinstance(pose, torch.Tensor) else pose, dtype=np.float32)[:3, :4].reshape(-1)
-        self.pose_host.copy_(torch.from_numpy(np.ascontiguousarray(p)))
+        slot = self.pose_ring[self._pose_slot]
+        self._pose_slot = (self._pose_slot + 1) % self.pose_ring.shape[0]
+        slot.copy_(torch.from_numpy(np.ascontiguousarray(p)))
+        with torch.cuda.device(self.device):
+            self.pose_dev.copy_(slot, non_blocking=True)
 
     def render(self, pose) -> torch.Tensor:
         """Replay for ``pose``; returns the RGBA8 pixels ``[n, 4]`` (device, valid after the stream
@@ -139,6 +157,23 @@ class GraphedFrameRenderer:
     def finish(self):
         self.model._pending_status = self._status
         return self.model.check_pending_status()
+
+    # frame backend of pipe_engine.PipeRunner (single process)
+    def enqueue(self, pose, host_image: torch.Tensor):
+        """Replay for ``pose`` and copy the RGBA8 frame into ``host_image`` (``uint8 [H, W, 4]``, pinned;
+        needs a graph over the whole image in row-major pixel order).  Returns an event behind the copy."""
+        if self.pixel_ids is not None and self.rgba_frame is None:
+            raise RuntimeError("enqueue needs a renderer over the whole frame (no pixel list, or one that covers it)")
+        self.render(pose)
+        frame = self.rgba_frame if self.rgba_frame is not None else self.rgba
+        with torch.cuda.device(self.device):
+            host_image.copy_(frame.view(self.H, self.W, 4), non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        return ev
+
+    def stop(self):
+        return None
 
 
 class NerfDDPRunner:
@@ -188,18 +223,33 @@ class NerfDDPRunner:
         self.shard.assemble(self.rgb, self.image)
         self.renderer.finish()
 
-    def run_batch(self, single_pose) -> np.ndarray:
+    def enqueue(self, single_pose, host_image: torch.Tensor):
+        """Everything ``run_batch`` does for one frame except waiting for it: broadcast, render, gather,
+        RGBA8, and the copy of the image into ``host_image`` (``uint8 [H, W, 4]``, pinned for an
+        asynchronous copy).  Returns an event recorded behind that copy; frames enqueued one after the
+        other share this runner's device buffers and are ordered by the stream."""
         if self.rank != 0:
-            raise RuntimeError("run_batch is the main rank's call; other ranks run serve()")
+            raise RuntimeError("enqueue / run_batch is the main rank's call; other ranks run serve()")
         pose = np.asarray(single_pose.cpu() if isinstance(single_pose, torch.Tensor) else single_pose, dtype=np.float32)
         focal = self._focal_of(pose)
         pose, focal, _ = self._broadcast(pose[:3, :4], focal, False)
-        self._render_and_gather(pose, focal)
+        self.renderer.render_pixels(pose, self.H, self.W, focal, self.shard.pixel_ids, self.rgb[: self.shard.n_local])
+        self.shard.assemble(self.rgb, self.image)
         # postprocess (nerf_inferer.py:345-378)
         self.renderer.to_rgba8(self.image, self.rgba)
-        self.img_cpu.copy_(self.rgba.view(self.H, self.W, 4), non_blocking=True)
-        if torch.device(self.renderer.device).type == "cuda":
-            torch.cuda.current_stream(self.renderer.device).synchronize()
+        host_image.copy_(self.rgba.view(self.H, self.W, 4), non_blocking=True)
+        if torch.device(self.renderer.device).type != "cuda":
+            return None
+        with torch.cuda.device(self.renderer.device):
+            ev = torch.cuda.Event()
+            ev.record()
+        return ev
+
+    def run_batch(self, single_pose) -> np.ndarray:
+        ev = self.enqueue(single_pose, self.img_cpu)
+        if ev is not None:
+            ev.synchronize()
+        self.renderer.finish()
         return self.img_cpu.numpy().copy()
 
     def serve(self, max_frames: int = -1) -> int:

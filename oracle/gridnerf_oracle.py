@@ -74,6 +74,16 @@ class Field:
         else:
             self.alpha_volume = None
 
+    def to(self, device):
+        """Move every tensor of the field (the same torch operators then run on that device: the
+        benchmark times this port on the GPU as a same-hardware reference point)."""
+        for k, v in list(vars(self).items()):
+            if isinstance(v, torch.Tensor):
+                setattr(self, k, v.to(device))
+            elif isinstance(v, list) and v and all(isinstance(t, torch.Tensor) or t is None for t in v):
+                setattr(self, k, [t.to(device) if t is not None else None for t in v])
+        return self
+
 
 def generate_rays(pose: torch.Tensor, height: int, width: int, focal: float) -> torch.Tensor:
     """Pinhole rays ``[H*W, 6]`` (origin, un-normalised direction) for a ``[3, 4]`` pose.
@@ -98,7 +108,7 @@ def sample_ray(f: Field, rays_o, rays_d, n_samples: int):
     rate_a = (f.aabb[1] - rays_o) / vec
     rate_b = (f.aabb[0] - rays_o) / vec
     t_min = torch.minimum(rate_a, rate_b).amax(-1).clamp(min=f.near, max=f.far)
-    rng = torch.arange(n_samples)[None].float()
+    rng = torch.arange(n_samples, device=rays_o.device)[None].float()
     step = f.step_size * rng
     interpx = t_min[..., None] + step
     pts = rays_o[..., None, :] + rays_d[..., None, :] * interpx[..., None]
@@ -114,7 +124,7 @@ def sample_ray_within_hull(f: Field, rays_o, rays_d, n_samples: int):
     d_z = rays_d[:, -1:]
     far = -(o_z / d_z)
     far[rays_d[:, 2] >= 0] = f.far
-    t_vals = torch.linspace(0.0, 1.0, steps=n_samples)
+    t_vals = torch.linspace(0.0, 1.0, steps=n_samples, device=rays_o.device)
     z_vals = near * (1.0 - t_vals) + far * (t_vals)
     pts = rays_o[..., None, :] + rays_d[..., None, :] * z_vals[..., :, None]
     outside = ((f.aabb[0] > pts) | (pts > f.aabb[1])).any(dim=-1)
@@ -137,7 +147,7 @@ def _coords(xyz, n: int = 3):
 def density_feature(f: Field, xyz):
     """Sum over planes and channels of plane x line.  app/models/gridnerf_sequential.py:779-827."""
     cp, cl = _coords(xyz, f.ndims)
-    sigma = torch.zeros((xyz.shape[0],))
+    sigma = torch.zeros((xyz.shape[0],), device=xyz.device)
     for i in range(len(f.density_plane)):
         d = i // f.n_res
         p = F.grid_sample(f.density_plane[i], cp[[d]], align_corners=True).view(-1, xyz.shape[0])
@@ -168,7 +178,7 @@ def app_feature(f: Field, xyz):
 
 def positional_encoding(x, freqs: int):
     """app/tools/utils.py:42-48."""
-    bands = 2 ** torch.arange(freqs, dtype=torch.float)
+    bands = 2 ** torch.arange(freqs, dtype=torch.float, device=x.device)
     pts = (x[..., None] * bands).reshape(x.shape[:-1] + (freqs * x.shape[-1],))
     return torch.cat([torch.sin(pts), torch.cos(pts)], dim=-1)
 
@@ -192,7 +202,7 @@ def mlp_render(f: Field, viewdirs, feats, latent=None):
 def raw2alpha(sigma, dist):
     """app/tools/utils.py:51-64."""
     alpha = 1.0 - torch.exp(-sigma * dist)
-    trans = torch.cumprod(torch.cat([torch.ones(alpha.shape[0], 1), 1.0 - alpha + 1e-10], -1), -1)
+    trans = torch.cumprod(torch.cat([torch.ones(alpha.shape[0], 1, device=alpha.device), 1.0 - alpha + 1e-10], -1), -1)
     return alpha, alpha * trans[:, :-1], trans[:, -1:]
 
 
@@ -219,8 +229,8 @@ def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bo
         ray_invalid = ~ray_valid
         ray_invalid[ray_valid] |= ~alpha_mask
         ray_valid = ~ray_invalid
-    sigma = torch.zeros(pts.shape[:-1])
-    rgb = torch.zeros((*pts.shape[:2], 3))
+    sigma = torch.zeros(pts.shape[:-1], device=pts.device)
+    rgb = torch.zeros((*pts.shape[:2], 3), device=pts.device)
     xyz = pts
     sigma_feat = None
     if ray_valid.any():
@@ -235,7 +245,7 @@ def render_chunk(f: Field, rays: torch.Tensor, n_samples: int = -1, white_bg: bo
         latent = None
         if f.embedding_app is not None:
             # compute_app_latent, app/models/gridnerf_sequential.py:429-437: the same row for every sample
-            idx = torch.ones(pts.shape[:-1], dtype=torch.long) * torch.as_tensor(app_code).long()
+            idx = torch.ones(pts.shape[:-1], dtype=torch.long, device=pts.device) * torch.as_tensor(app_code).long().to(pts.device)
             latent = F.embedding(idx[app_mask], f.embedding_app)
         rgb[app_mask] = mlp_render(f, view_exp[app_mask], feats, latent)
     acc = torch.sum(weight, -1)

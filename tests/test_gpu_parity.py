@@ -746,3 +746,31 @@ def test_bounded_wait_expires_and_the_context_survives(fused):
     model.check_status_every_call = True
     again, _ = model(rays, N_samples=spec.n_samples)
     assert torch.equal(again["rgb_map"], good["rgb_map"]) and int(model.last_status[4]) == 0
+
+
+@pytest.mark.parametrize("scale", [10.0, 30.0])
+def test_large_appearance_values_stress(scale):
+    """Every synthetic field is 0.1 * randn; a trained field can carry larger features.  Appearance planes
+    scaled by 10 and 30 (features up to several units, so sin/cos of 2 f see real phase): the
+    split-precision tensor-core mode (mlp_mode 1: fp16 hi + lo operands, fp32 planes) must stay inside the
+    1e-4 bar against the oracle; the single-fp16 mode (mode 2, with fp32 and with fp16 planes through the
+    fused kernel) is allowed to leave it, within the bound asserted here, which documents where it does."""
+    spec = scenes.tiny_spec().lit()
+    ckpt = scenes.make_checkpoint(spec)
+    for i in range(3):
+        ckpt["state_dict"][f"app_plane.{i}"] = ckpt["state_dict"][f"app_plane.{i}"] * scale
+    field = orc.field_from_checkpoint(ckpt)
+    rays = tiny_rays(spec)[1000:5096].contiguous()
+    ref = orc.render_chunk(field, rays, spec.n_samples, True, keep_stages=True)
+    feat_max = float(ref["app_features"].abs().max())
+    errs = {}
+    for label, extra in (("fp32", {"mlp_mode": 0}), ("mode1", {"mlp_mode": 1}), ("mode2", {"mlp_mode": 2}),
+                         ("mode2+fp16 planes", {"mlp_mode": 2, "app_plane_fp16": True})):
+        m = cuda_model(spec, ckpt, **extra)
+        out, _ = m(rays.cuda(), N_samples=spec.n_samples)
+        err = (out["rgb_map"].cpu() - ref["rgb_map"]).abs().max(dim=1).values
+        errs[label] = (float(err.max()), int((err > RGB_TOL).sum()))
+    print(f"scale {scale}: |feature| max {feat_max:.2f}; (max |rgb - oracle|, rays above 1e-4 of {rays.shape[0]}): {errs}")
+    assert errs["fp32"][1] <= 3 and errs["fp32"][0] <= FLIP_RGB_TOL
+    assert errs["mode1"][1] <= 3 and errs["mode1"][0] <= FLIP_RGB_TOL, errs
+    assert errs["mode2"][0] <= 2e-2 and errs["mode2+fp16 planes"][0] <= 2e-2, errs

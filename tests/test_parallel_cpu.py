@@ -4,6 +4,7 @@ import os
 import socket
 
 import numpy as np
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -209,3 +210,43 @@ def test_sample_routing_two_ranks_over_gloo_equals_loopback(tmp_path):
             seg = order[start:start + counts[d]]
             assert torch.all(rows[r][0][seg] == d) and torch.all(seg[1:] > seg[:-1])
             start += counts[d]
+
+
+def test_pipe_engine_submit_get_result_wait_stop_cpu():
+    """The asynchronous engine interface (submit -> uid, get_result in submission order, wait(uid) in any
+    order, more frames submitted than slots, stop) with a CPU frame backend, and through NerfDDPRunner's
+    enqueue with the fake renderer."""
+    from queue import Empty
+
+    from landmark_b200.engine import NerfDDPRunner
+    from landmark_b200.pipe_engine import CpuFrameBackend, MainRankPipeRenderEngine, PipeRunner, RunnerFrameBackend
+
+    H, W = 24, 40
+    poses = [np.eye(4, dtype=np.float32)[:3] * (k + 1) for k in range(7)]
+    frame = lambda pose: _expected(pose, 100.0, H, W)  # noqa: E731
+
+    eng = MainRankPipeRenderEngine(lambda: PipeRunner(CpuFrameBackend(frame, H, W), depth=2), poses=poses, async_=True)
+    eng.start()
+    uids = [eng.submit(p) for p in poses]          # 7 frames through 2 slots
+    assert len(set(uids)) == 7
+    for k in (3, 0, 6):                            # by uid, any order
+        assert np.array_equal(eng.wait(uids[k]), frame(poses[k]))
+    assert np.array_equal(eng.get_result(), frame(poses[1]))   # the rest in submission order
+    assert np.array_equal(eng.get_result(), frame(poses[2]))
+    with pytest.raises(KeyError):
+        eng.wait(uids[3])                          # handed out already
+    assert np.array_equal(eng.get_result(), frame(poses[4])) and np.array_equal(eng.get_result(), frame(poses[5]))
+    with pytest.raises(Empty):
+        eng.runner.get_result_task(block=False)
+    eng.run_for_latency()
+    eng.run_for_throughput()
+    assert len(eng.latency) == 7 and eng.throughput > 0
+    eng.stop()
+    with pytest.raises(RuntimeError):
+        eng.submit(poses[0])
+
+    # the same interface over the tile-sharded runner (single rank, fake renderer)
+    eng2 = MainRankPipeRenderEngine(
+        lambda: PipeRunner(RunnerFrameBackend(NerfDDPRunner(_FakeRenderer(), H, W, focal=100.0)), depth=3), poses=poses[:3])
+    eng2.start(test=True)  # warm-up, latency run, stop
+    assert len(eng2.latency) == 3
