@@ -336,6 +336,12 @@ int gnr_measure_l1_bandwidth(int device, int iters, float* gb_per_s_h);
  * operation.  Nothing in this hook faults, traps or spins without bound. */
 int gnr_debug_wait(GnrModel* m, int expire, int wait_limit);
 
+/* Measurement aid for the fused appearance kernel: with ``on`` != 0 the following launches let one thread
+ * per group of the middle CTA sum the clock cycles it spends in each phase of a tile (store A0, projection,
+ * gather behind it, wait, encoding, layer 1, ...); ``on`` == 0 synchronises, copies the last launch's sums
+ * to ``cycles_h[64]`` ([group][16 phases], unused entries zero) and switches the timer off. */
+int gnr_debug_phase_cycles(GnrModel* m, int on, long long* cycles_h);
+
 /* Copy the 8-word status block of a workspace to the host (synchronises the stream). */
 int gnr_read_status(const void* workspace, int32_t* status_h, void* stream);
 

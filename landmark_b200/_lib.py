@@ -90,6 +90,7 @@ SIGNATURES = {
     "gnr_profile_enable": (_INT, [_P, _INT]),
     "gnr_profile_collect": (_INT, [_P, C.POINTER(C.c_float), C.POINTER(C.c_int64)]),
     "gnr_measure_l1_bandwidth": (_INT, [_INT, _INT, C.POINTER(C.c_float)]),
+    "gnr_debug_phase_cycles": (_INT, [_P, _INT, C.POINTER(C.c_longlong)]),
     "gnr_debug_wait": (_INT, [_P, _INT, _INT]),
     "gnr_read_status": (_INT, [_P, C.POINTER(C.c_int32), _P]),
 }

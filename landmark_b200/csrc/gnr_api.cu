@@ -257,6 +257,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
     free_dev(m->app_line_buf[i]);
   }
   free_dev(m->den_lattice);
+  free_dev(m->debug_prof);
   free_dev(m->alpha_bits);
   free_dev(m->alpha_coarse);
   free_dev(m->alpha_full);
@@ -733,6 +734,26 @@ extern "C" int gnr_debug_wait(GnrModel* m, int expire, int wait_limit) {
   }
   m->debug_expire_wait = expire ? 1 : 0;
   m->debug_wait_limit = wait_limit;
+  return 0;
+}
+
+extern "C" int gnr_debug_phase_cycles(GnrModel* m, int on, long long* cycles_h) {
+  if (!m) {
+    gnr_set_error("gnr_debug_phase_cycles: null model");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  if (on) {
+    if (!m->debug_prof) GNR_CUDA_OK(cudaMalloc(&m->debug_prof, 64 * sizeof(long long)));
+    GNR_CUDA_OK(cudaMemset(m->debug_prof, 0, 64 * sizeof(long long)));
+    return 0;
+  }
+  if (m->debug_prof) {
+    GNR_CUDA_OK(cudaDeviceSynchronize());
+    if (cycles_h) GNR_CUDA_OK(cudaMemcpy(cycles_h, m->debug_prof, 64 * sizeof(long long), cudaMemcpyDeviceToHost));
+    cudaFree(m->debug_prof);
+    m->debug_prof = nullptr;
+  }
   return 0;
 }
 

@@ -27,6 +27,8 @@
 // Every wait on an mbarrier is bounded; when one expires the group raises
 // status[GNR_ST_WAIT_EXPIRED] and stops taking tiles; before the CTA frees its tensor memory a
 // group that stopped commits once more and waits (bounded) so that none of its MMAs is in flight.
+#include <type_traits>
+
 #include "gnr_gather.cuh"
 #include "gnr_tc.cuh"
 
@@ -47,9 +49,10 @@ struct FusedArgs {
   int k0;                        // products per sample (n_pairs * 48)
   uint32_t wait_limit;           // iterations a bounded wait may take
   int debug_skip_commit;         // test hook: group 0 of CTA 0 leaves out the commit of its first basis GEMM
+  long long* prof;               // null, or [FG][16] cycle sums per phase of the middle CTA (measurement aid)
 };
 
-template <int NP>
+template <int NP, bool PROF>
 __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
@@ -64,7 +67,8 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   const int tid = threadIdx.x, warp = tid >> 5;
   const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int slot = warp_u >> 2, row = tid & 127;
-  const bool lead_warp = (warp_u & 3) == 0;
+  const int warp_in_group = warp_u & 3;  // GEMM i of a tile is issued by warp i of the group: the ~50-90 cycles an MMA
+                                         // takes to issue are then spread over the four warps instead of adding up in one
 
   {
     const uint4* src = reinterpret_cast<const uint4*>(a.w_image);
@@ -114,51 +118,106 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   }                                                                      \
   parity ^= 1
 
-  for (long long tile = t_beg + slot; tile < t_end; tile += FG) {
-    const long long j_raw = tile * ROWS + row;
-    const bool live = j_raw < total;
-    const long long j = live ? j_raw : total - 1;  // rows past the end repeat the last entry (no divergence around
-                                                   // the warp-wide tensor-memory instructions) and write nothing
-    // ---- gather: products -> tensor memory ------------------------------------------------------------
-    float view[3];
-    {
-      float x, y, z;
-      sample_xyz(p, a.crd, j, x, y, z, view);
-      if (NP == 3) {
-        const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
-        const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
-        const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+  // ---- software pipeline: the products of a group's NEXT tile are gathered into registers (72 packed fp16
+  // pairs per thread) in the shadows of the current tile's MMAs: positions and L1 prefetches behind the
+  // projection, one plane/line pair behind each of the three layers, so the L1 port works while the tensor
+  // pipe does and a tile starts with its A0 ready
+  uint32_t nq[3 * PAIR_COLS];
+  float nx = 0.0f, ny = 0.0f, nz = 0.0f, nview[3] = {0.0f, 0.0f, 0.0f};
+  auto fetch_pos = [&](long long t) {
+    const long long jr = t * ROWS + row;
+    // rows past the end repeat the last entry (no divergence around the warp-wide tensor-memory
+    // instructions) and write nothing
+    sample_xyz(p, a.crd, jr < total ? jr : total - 1, nx, ny, nz, nview);
+  };
+  auto gather_pair = [&](auto pair_c) {
+    constexpr int pi = decltype(pair_c)::value;
+    if (pi >= planes.n) {  // fewer than three pairs: the columns stay zero
 #pragma unroll
-        for (int pi = 0; pi < 3; ++pi) {
-          const PairTapsH2 t = pi == 0 ? make_pair_taps_h2(planes.p[0], tx, ty, tz)
-                                       : (pi == 1 ? make_pair_taps_h2(planes.p[1], tx, tz, ty) : make_pair_taps_h2(planes.p[2], ty, tz, tx));
+      for (int e = 0; e < PAIR_COLS; ++e) nq[pi * PAIR_COLS + e] = 0u;
+      return;
+    }
+    const GnrPlane& pl = planes.p[pi];
+    PairTapsH2 t;
+    if (NP == 3) {
+      const Tap tx = make_tap(nx, planes.p[0].fw, planes.p[0].W);
+      const Tap ty = make_tap(ny, planes.p[0].fh, planes.p[0].H);
+      const Tap tz = make_tap(nz, planes.p[0].fl, planes.p[0].L);
+      t = pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
+    } else {
+      const float u = pick(nx, ny, nz, pl.mat0), v = pick(nx, ny, nz, pl.mat1), l = pick(nx, ny, nz, pl.vec);
+      t = make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
+    }
 #pragma unroll
-          for (int g = 0; g < 3; ++g) {
-            uint32_t q[8];
-            pair_round_h2(planes.p[pi], t, g, q);
-            tmem_st8(a_tmem + lane_off + pi * PAIR_COLS + g * 8, q);
-          }
-        }
-      } else {
-        for (int pi = 0; pi < planes.n; ++pi) {
-          const GnrPlane& pl = planes.p[pi];
-          const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-          const PairTapsH2 t = make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
+    for (int g = 0; g < 3; ++g) {
+      uint32_t q[8];
+      pair_round_h2(pl, t, g, q);
 #pragma unroll
-          for (int g = 0; g < 3; ++g) {
-            uint32_t q[8];
-            pair_round_h2(pl, t, g, q);
-            tmem_st8(a_tmem + lane_off + pi * PAIR_COLS + g * 8, q);
-          }
+      for (int e = 0; e < 8; ++e) nq[pi * PAIR_COLS + g * 8 + e] = q[e];
+    }
+  };
+  // Brings the lines of the next tile's texels into L1 well before the gather reads them: per pair the
+  // two upper corners, the two lower corners and the two line entries are 192 contiguous bytes each.
+  auto prefetch_next = [&]() {
+#pragma unroll
+    for (int pi = 0; pi < 3; ++pi) {
+      if (pi < planes.n) {
+        const GnrPlane& pl = planes.p[pi];
+        const float u = pick(nx, ny, nz, pl.mat0), v = pick(nx, ny, nz, pl.mat1), l = pick(nx, ny, nz, pl.vec);
+        const Tap tu = make_tap(u, pl.fw, pl.W), tv = make_tap(v, pl.fh, pl.H), tl = make_tap(l, pl.fl, pl.L);
+        const uint32_t nw = (uint32_t)tv.i0 * (uint32_t)pl.W + (uint32_t)tu.i0;
+        const unsigned char* r0 = reinterpret_cast<const unsigned char*>(pl.plane) + (size_t)nw * 96u;
+        const unsigned char* r1 = r0 + (size_t)pl.W * 96u;
+        const unsigned char* r2 = reinterpret_cast<const unsigned char*>(pl.line) + (size_t)tl.i0 * 96u;
+        const unsigned char* rs[3] = {r0, r1, r2};
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k]));
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k] + 128));
+          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k] + 191));
         }
       }
     }
+  };
+  using P0 = std::integral_constant<int, 0>;
+  using P1 = std::integral_constant<int, 1>;
+  using P2 = std::integral_constant<int, 2>;
+  if (t_beg + slot < t_end) {
+    fetch_pos(t_beg + slot);
+    gather_pair(P0{});
+    gather_pair(P1{});
+    gather_pair(P2{});
+  }
+
+  // phase timer of one thread per group of one CTA (only when a buffer was passed)
+  const bool prof_on = PROF && a.prof != nullptr && row == 0 && blockIdx.x == gridDim.x / 2;
+  long long pacc[16], plast = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) pacc[i] = 0;
+#define PROF_MARK(k)               \
+  if (PROF && prof_on) {           \
+    const long long now = clock64(); \
+    pacc[k] += now - plast;        \
+    plast = now;                   \
+  }
+  if (PROF && prof_on) plast = clock64();
+
+  for (long long tile = t_beg + slot; tile < t_end; tile += FG) {
+    const long long j = tile * ROWS + row;
+    const bool live = j < total;
+    const bool has_next = tile + FG < t_end;  // (the same for every thread of the group)
+    // ---- this tile's products: registers -> tensor memory ------------------------------------------------
+    const float view[3] = {nview[0], nview[1], nview[2]};
+    tmem_st32(a_tmem + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&nq[0]));
+    tmem_st32(a_tmem + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&nq[32]));
+    tmem_st8(a_tmem + lane_off + 64, *reinterpret_cast<uint32_t(*)[8]>(&nq[64]));
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
+    PROF_MARK(0);
 
     // ---- F = A0 * Wb^T ---------------------------------------------------------------------------------
-    if (lead_warp) {
+    if (warp_in_group == 0) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -170,7 +229,14 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, skip ? 0u : leader);
       __syncwarp();
     }
+    PROF_MARK(1);
+    if (has_next) {  // behind the projection: the next tile's positions, and its texels on their way into L1
+      fetch_pos(tile + FG);
+      prefetch_next();
+    }
+    PROF_MARK(2);
     WAIT_OR_STOP();
+    PROF_MARK(3);
     float f[32];
     {
       uint32_t v[32];
@@ -218,9 +284,10 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
+    PROF_MARK(4);
 
     // ---- D = A1 * W1^T ---------------------------------------------------------------------------------------
-    if (lead_warp) {
+    if (warp_in_group == 1) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -229,7 +296,11 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
+    PROF_MARK(5);
+    if (has_next) gather_pair(P0{});  // behind layer 1
+    PROF_MARK(6);
     WAIT_OR_STOP();
+    PROF_MARK(7);
 
     // ---- A2 = relu(D) (D already holds b1), the constant-1 column of b2, padding ------------------------------
 #pragma unroll
@@ -250,9 +321,10 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
+    PROF_MARK(8);
 
     // ---- D = A2 * W2^T ---------------------------------------------------------------------------------------
-    if (lead_warp) {
+    if (warp_in_group == 2) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -261,7 +333,11 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
+    PROF_MARK(9);
+    if (has_next) gather_pair(P1{});  // behind layer 2
+    PROF_MARK(10);
     WAIT_OR_STOP();
+    PROF_MARK(11);
 
     // ---- A3 = relu(D), rgb = sigmoid(A3 * W3^T + b3) ---------------------------------------------------------
 #pragma unroll
@@ -278,7 +354,8 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
-    if (lead_warp) {
+    PROF_MARK(12);
+    if (warp_in_group == 3) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -287,7 +364,9 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
+    if (has_next) gather_pair(P2{});  // behind layer 3
     WAIT_OR_STOP();
+    PROF_MARK(13);
     {
       uint32_t r[4];
       tmem_ld4(f_tmem + lane_off, r);
@@ -300,14 +379,20 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       }
     }
     tc_fence_before();  // this tile's tensor-memory reads come before the next tile's writes
+    PROF_MARK(14);
   }
 #undef WAIT_OR_STOP
+#undef PROF_MARK
+  if (PROF && prof_on) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) a.prof[slot * 16 + i] = pacc[i];
+  }
 
   // ---- teardown ---------------------------------------------------------------------------------------------
   if (expired) {
     // MMAs of this group may still be running: commit once more and wait for them, so that nothing
     // writes tensor memory after it has been freed
-    if (lead_warp) {
+    if (warp_in_group == 0) {
       const uint32_t leader = elect_one();
       mma_commit(mbar, leader);
       __syncwarp();
@@ -350,15 +435,16 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.k0 = m->mlp.n_prod;
   a.wait_limit = m->debug_wait_limit > 0 ? (uint32_t)m->debug_wait_limit : kWaitLimit;
   a.debug_skip_commit = m->debug_expire_wait;
-  cudaError_t e;
-  if (standard_vm3(set)) {
-    e = cudaFuncSetAttribute(app_mlp_fused_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
+  a.prof = m->debug_prof;
+  auto launch = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
     if (e != cudaSuccess) return (int)e;
-    app_mlp_fused_kernel<3><<<m->sm_count, FG * 128, kFusedSmem, st>>>(p, set, a);
-  } else {
-    e = cudaFuncSetAttribute(app_mlp_fused_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
-    if (e != cudaSuccess) return (int)e;
-    app_mlp_fused_kernel<0><<<m->sm_count, FG * 128, kFusedSmem, st>>>(p, set, a);
-  }
+    kernel<<<m->sm_count, FG * 128, kFusedSmem, st>>>(p, set, a);
+    return 0;
+  };
+  int rc;
+  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true>) : launch(app_mlp_fused_kernel<0, true>);
+  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false>) : launch(app_mlp_fused_kernel<0, false>);
+  if (rc) return rc;
   return (int)cudaGetLastError();
 }

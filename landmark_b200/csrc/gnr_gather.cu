@@ -717,7 +717,7 @@ __global__ void __launch_bounds__(256) l1_read_kernel(const float* __restrict__ 
       float a0, a1, a2, a3, a4, a5, a6, a7;
       asm volatile("ld.global.nc.v8.f32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
                    : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
-                   : "l"(base + u * 256));
+                   : "l"(base + ((u + it) & 7) * 256));  // the address depends on `it`: nothing can be hoisted
       acc += (a0 + a1) + (a2 + a3) + (a4 + a5) + (a6 + a7);
     }
   }

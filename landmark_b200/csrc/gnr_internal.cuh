@@ -66,6 +66,7 @@ struct GnrModel {
   GnrMlp mlp;
   int debug_expire_wait;  // test hook (gnr_debug_wait): make one bounded wait of the tensor-core kernels run out
   int debug_wait_limit;   // polls a bounded wait may take; 0 = the default
+  long long* debug_prof;  // device buffer of phase cycle sums (gnr_debug_phase_cycles), null when off
   // hull sampler tables (sampling_mode 1)
   float* hull_near_term;
   float* hull_u;
