@@ -346,7 +346,11 @@ def main():
     ms_total = e0.elapsed_time(e1)
     clocks = sampler.stop() if sampler else None
     t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+    per_rank_ms = [ms_total / a.steps]
     if world > 1:
+        allt = torch.zeros(world, device=device, dtype=torch.float64)
+        dist.all_gather_into_tensor(allt, t)
+        per_rank_ms = [float(v) / a.steps for v in allt.tolist()]
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms_step = float(t.item()) / a.steps
     model.check_pending_status()
@@ -552,6 +556,14 @@ def main():
         _check(_glib.gnr_measure_l1_bandwidth(local_rank, 4000, _C.byref(val)), "gnr_measure_l1_bandwidth")
         l1_measured = float(val.value)
 
+    # what every rank did: its share of the samples and the time its kernels took on one stream (separates an
+    # uneven split of the work from kernels that lose efficiency on small chunks)
+    mine = torch.tensor([float(stats[2]), float(stats[3]), float(stats[5]), float(n_local), ms_step_single] +
+                        [stage_ms[k] / a.steps for k in sorted(stage_ms)], device=device, dtype=torch.float64)
+    rank_table = mine[None]
+    if world > 1:
+        rank_table = torch.zeros((world, mine.numel()), device=device, dtype=torch.float64)
+        dist.all_gather_into_tensor(rank_table, mine)
     tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local), float(stats[5])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
@@ -641,6 +653,9 @@ def main():
                    "l2": "inputs larger than L2 (1.34 GB of planes, >0.5 GB of per-frame sample lists)"},
         "ms_per_frame": ms_step, "fps": 1e3 / ms_step,
         "ms_per_frame_single_stream": ms_step_single,
+        "per_rank": {"ms_per_frame": per_rank_ms,
+                     "columns": ["valid", "appearance", "density_evaluated", "rays", "ms_single_stream"] + [f"ms_{k}" for k in sorted(stage_ms)],
+                     "rows": [[round(float(v), 3) for v in r] for r in rank_table.tolist()]},
         "e2e": {"value": H * W / e2e_s / 1e6, "unit": "Mrays/s", "ms_per_frame": e2e_s * 1e3,
                 "h2d_bytes_per_step": 56, "d2h_bytes_per_step": int(H * W * 4),
                 "api": "NerfDDPRunner.run_batch(pose) -> uint8 [H, W, 4] on rank 0's host: pose broadcast, ray generation, "

@@ -6,19 +6,30 @@
 // encoding and the GEMMs in one pass (dist_render/kernel/cuda_kernel/dal/pe_concate_mlp) behind a
 // separate gather kernel; here the gather is in the same kernel too.
 //
-// One persistent CTA per SM, two groups of 128 threads; thread = appearance sample = row of a
-// 128-row tile = lane of tensor memory.  Per tile a group
-//   1. gathers: each thread interpolates the 144 plane x line products of its sample (packed fp16,
-//      256-bit loads, the arithmetic of the stand-alone gather) and writes them with tcgen05.st into
-//      tensor memory, where they ARE the A operand of the basis projection (72 columns of fp16 pairs);
+// One persistent CTA per SM, two groups of 256 threads; a group works on one 128-sample tile at a
+// time.  Row r of the tile (= lane r of tensor memory) belongs to TWO threads of the group, one in
+// each half of it (warps 0-3 and 4-7; warp w of either half owns lanes 32 (w % 4) ..): every per-row
+// phase is split between them by columns, so each phase takes half as long and the SM holds 16 warps
+// whose loads hide each other's latency.  Per tile a group
+//   1. gathers: the 144 plane x line products of a sample as nine rounds of 16 channels (packed fp16,
+//      256-bit loads, the arithmetic of the stand-alone gather); half 0 takes rounds 0-4, half 1
+//      rounds 5-8, and each round goes with one tcgen05.st straight into tensor memory, where the
+//      products ARE the A operand of the basis projection;
 //   2. F  = A0 * Wb^T                 tcgen05.mma, A from tensor memory, B (basis) from shared memory
-//   3. A1 = [F, view, sin/cos ...]    registers -> tensor memory (80 columns)
+//   3. A1 = [F, view, sin/cos ...]    registers -> tensor memory: half 0 encodes features 0-13, half 1
+//                                     features 14-26 and the view direction, 40 columns each (the K
+//                                     order of layer 1 is permuted to make the halves contiguous;
+//                                     the W1 image carries the same permutation)
 //   4. D  = A1 * W1^T, A2 = relu(D), D = A2 * W2^T, A3 = relu(D), rgb = sigmoid(A3 * W3^T + b3)
-//      every activation goes registers -> tensor memory -> MMA; biases ride in the MMAs.
+//      every activation goes registers -> tensor memory -> MMA (half h converts columns 64 h .. of D);
+//      biases ride in the MMAs.
 // Shared memory holds only the four weight images (90 KB): no operand of a sample is ever written
 // to shared or global memory, so the L1/shared-memory port carries the gather's loads and the
 // weight fetches of the MMAs and nothing else, and the rest of the 256 KB array stays L1 cache for
-// the texels.  While one group gathers (L1 port) the other group's MMAs run (tensor pipe).
+// the texels.  While one group gathers (L1 port) the other group's MMAs run (tensor pipe).  GEMM i of
+// a tile is issued by warp i of the group, so the issue time of the MMAs is spread over four warps.
+// The (ray, sample) of a row is fetched two tiles ahead and the ray itself one tile ahead, so the
+// dependent loads behind a list entry are never waited for.
 //
 // Tensor memory, 256 columns per group: R0 = [0, 128) accumulator D of layers 1 and 2;
 // R1 = [128, 256): columns 0..79 the current A operand (A0, then A1, A2, A3: each is dead when the
@@ -35,14 +46,18 @@
 namespace {
 
 constexpr int FG = 2;               // groups per CTA
+constexpr int GT = 256;             // threads per group (two per row)
 constexpr int GROUP_COLS = 256;     // tensor-memory columns per group
 constexpr int A_COL = HID;          // R1: A operand
 constexpr int F_COL = HID + 96;     // R1: 32 fp32 columns (features, then the layer-3 result)
-constexpr int PAIR_COLS = 24;       // 48 channels of a pair as fp16 pairs
 
 struct FusedArgs {
-  GnrCoords crd;
-  const unsigned char* w_image;  // [basis][W1][W2][W3] fp16 operand images (gnr_mlp_tc_prepare)
+  const float* rays;             // [n][6]
+  const float* t_min;            // [n]
+  const uint32_t* ids;           // appearance list: ray << kbits | sample
+  const int32_t* total_ptr;      // length of the list (device)
+  long long capacity;
+  const unsigned char* w_image;  // [basis][W1][W2][W3][W1 with permuted K] fp16 operand images
   const float* b3;
   float* rgb_out;
   int32_t* status;
@@ -52,11 +67,16 @@ struct FusedArgs {
   long long* prof;               // null, or [FG][16] cycle sums per phase of the middle CTA (measurement aid)
 };
 
-template <int NP, bool PROF>
-__global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
+struct RaySample {  // what a row needs of its list entry
+  float o[3], d[3], t_min;
+  int k;
+};
+
+template <int NP, bool PROF, bool PIPE>
+__global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
-  unsigned char* s_w1 = s_wb + WB_BYTES;
+  unsigned char* s_w1 = s_wb + WB_BYTES;  // layer 1, K permuted (see the header of this file)
   unsigned char* s_w2 = s_w1 + W1_BYTES;
   unsigned char* s_w3h = s_w2 + W2_BYTES;
   float* s_b3 = reinterpret_cast<float*>(s_w3h + W3_BYTES);
@@ -65,15 +85,20 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   volatile uint32_t* s_flag = s_tmem + 1;                    // [FG] outcome of a group's last wait
 
   const int tid = threadIdx.x, warp = tid >> 5;
-  const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);
-  const int slot = warp_u >> 2, row = tid & 127;
-  const int warp_in_group = warp_u & 3;  // GEMM i of a tile is issued by warp i of the group: the ~50-90 cycles an MMA
-                                         // takes to issue are then spread over the four warps instead of adding up in one
+  const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same number, known to be warp-uniform
+  const int slot = warp_u >> 3;                              // group
+  const int wg = warp_u & 7;                                 // warp in group
+  const int half = wg >> 2;                                  // which half of every row's columns this thread takes
+  const int row = tid & 127;
+  const int tg = tid & (GT - 1);                             // thread in group
 
   {
+    // weights -> shared memory: basis, W1 (the permuted image, stored last in global memory), W2, W3
     const uint4* src = reinterpret_cast<const uint4*>(a.w_image);
+    const uint4* src_w1p = reinterpret_cast<const uint4*>(a.w_image + WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES);
     uint4* dst = reinterpret_cast<uint4*>(s_wb);
-    for (int i = tid; i < (WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES) / 16; i += FG * 128) dst[i] = src[i];
+    constexpr int kAll = (WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES) / 16, kW1Beg = WB_BYTES / 16, kW1End = (WB_BYTES + W1_BYTES) / 16;
+    for (int i = tid; i < kAll; i += FG * GT) dst[i] = (i >= kW1Beg && i < kW1End) ? src_w1p[i - kW1Beg] : src[i];
     if (tid < 4) s_b3[tid] = a.b3[tid];
     if (tid == 0) {
       for (int s = 0; s < FG; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_mbar[s])));
@@ -93,7 +118,7 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   const uint32_t d_tmem = tmem_base + (uint32_t)(slot * GROUP_COLS);  // R0
   const uint32_t a_tmem = d_tmem + A_COL;                             // R1, A operand
   const uint32_t f_tmem = d_tmem + F_COL;                             // R1, fp32 result columns
-  const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;
+  const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;        // the lane quarter this warp may touch
   const uint32_t wb_addr = smem_u32(s_wb), w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2), w3_addr = smem_u32(s_w3h);
   const uint32_t mbar = smem_u32(&s_mbar[slot]);
   const int bar_id = 1 + slot;
@@ -101,123 +126,146 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   uint32_t parity = 0;
   bool expired = false;
 
-  const long long total = min(a.crd.total_ptr ? (long long)*a.crd.total_ptr : a.crd.total_direct, a.crd.capacity);
+  const long long total = min((long long)*a.total_ptr, a.capacity);
   const long long n_tiles = (total + ROWS - 1) / ROWS;
   // a contiguous share of the list per CTA (neighbouring tiles are neighbouring rays: their texels
   // are still in this SM's L1), the two groups taking alternate tiles of it
   const long long per = (n_tiles + gridDim.x - 1) / gridDim.x;
   const long long t_beg = min(n_tiles, (long long)blockIdx.x * per), t_end = min(n_tiles, t_beg + per);
   const int ksteps0 = a.k0 >> 4;
+  const uint32_t kmask = (1u << p.kbits) - 1u;
 
-#define GROUP_SYNC() asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory")
-#define WAIT_OR_STOP()                                                   \
-  if (!group_wait(mbar, parity, bar_id, row, s_flag, a.wait_limit)) {    \
-    if (row == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);         \
-    expired = true;                                                      \
-    break;                                                               \
-  }                                                                      \
+#define GROUP_SYNC() asm volatile("bar.sync %0, 256;" ::"r"(bar_id) : "memory")
+#define WAIT_OR_STOP()                                                          \
+  if (!group_wait(mbar, parity, bar_id, tg, s_flag, a.wait_limit, GT)) {        \
+    if (tg == 0) atomicExch(a.status + GNR_ST_WAIT_EXPIRED, 1);                 \
+    expired = true;                                                             \
+    break;                                                                      \
+  }                                                                             \
   parity ^= 1
-
-  // ---- software pipeline: the products of a group's NEXT tile are gathered into registers (72 packed fp16
-  // pairs per thread) in the shadows of the current tile's MMAs: positions and L1 prefetches behind the
-  // projection, one plane/line pair behind each of the three layers, so the L1 port works while the tensor
-  // pipe does and a tile starts with its A0 ready
-  uint32_t nq[3 * PAIR_COLS];
-  float nx = 0.0f, ny = 0.0f, nz = 0.0f, nview[3] = {0.0f, 0.0f, 0.0f};
-  auto fetch_pos = [&](long long t) {
-    const long long jr = t * ROWS + row;
-    // rows past the end repeat the last entry (no divergence around the warp-wide tensor-memory
-    // instructions) and write nothing
-    sample_xyz(p, a.crd, jr < total ? jr : total - 1, nx, ny, nz, nview);
-  };
-  auto gather_pair = [&](auto pair_c) {
-    constexpr int pi = decltype(pair_c)::value;
-    if (pi >= planes.n) {  // fewer than three pairs: the columns stay zero
-#pragma unroll
-      for (int e = 0; e < PAIR_COLS; ++e) nq[pi * PAIR_COLS + e] = 0u;
-      return;
-    }
-    const GnrPlane& pl = planes.p[pi];
-    PairTapsH2 t;
-    if (NP == 3) {
-      const Tap tx = make_tap(nx, planes.p[0].fw, planes.p[0].W);
-      const Tap ty = make_tap(ny, planes.p[0].fh, planes.p[0].H);
-      const Tap tz = make_tap(nz, planes.p[0].fl, planes.p[0].L);
-      t = pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
-    } else {
-      const float u = pick(nx, ny, nz, pl.mat0), v = pick(nx, ny, nz, pl.mat1), l = pick(nx, ny, nz, pl.vec);
-      t = make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
-    }
-#pragma unroll
-    for (int g = 0; g < 3; ++g) {
-      uint32_t q[8];
-      pair_round_h2(pl, t, g, q);
-#pragma unroll
-      for (int e = 0; e < 8; ++e) nq[pi * PAIR_COLS + g * 8 + e] = q[e];
-    }
-  };
-  // Brings the lines of the next tile's texels into L1 well before the gather reads them: per pair the
-  // two upper corners, the two lower corners and the two line entries are 192 contiguous bytes each.
-  auto prefetch_next = [&]() {
-#pragma unroll
-    for (int pi = 0; pi < 3; ++pi) {
-      if (pi < planes.n) {
-        const GnrPlane& pl = planes.p[pi];
-        const float u = pick(nx, ny, nz, pl.mat0), v = pick(nx, ny, nz, pl.mat1), l = pick(nx, ny, nz, pl.vec);
-        const Tap tu = make_tap(u, pl.fw, pl.W), tv = make_tap(v, pl.fh, pl.H), tl = make_tap(l, pl.fl, pl.L);
-        const uint32_t nw = (uint32_t)tv.i0 * (uint32_t)pl.W + (uint32_t)tu.i0;
-        const unsigned char* r0 = reinterpret_cast<const unsigned char*>(pl.plane) + (size_t)nw * 96u;
-        const unsigned char* r1 = r0 + (size_t)pl.W * 96u;
-        const unsigned char* r2 = reinterpret_cast<const unsigned char*>(pl.line) + (size_t)tl.i0 * 96u;
-        const unsigned char* rs[3] = {r0, r1, r2};
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k]));
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k] + 128));
-          asm volatile("prefetch.global.L1 [%0];" ::"l"(rs[k] + 191));
-        }
-      }
-    }
-  };
-  using P0 = std::integral_constant<int, 0>;
-  using P1 = std::integral_constant<int, 1>;
-  using P2 = std::integral_constant<int, 2>;
-  if (t_beg + slot < t_end) {
-    fetch_pos(t_beg + slot);
-    gather_pair(P0{});
-    gather_pair(P1{});
-    gather_pair(P2{});
-  }
-
   // phase timer of one thread per group of one CTA (only when a buffer was passed)
-  const bool prof_on = PROF && a.prof != nullptr && row == 0 && blockIdx.x == gridDim.x / 2;
+  const bool prof_on = PROF && a.prof != nullptr && tg == 0 && blockIdx.x == gridDim.x / 2;
   long long pacc[16], plast = 0;
 #pragma unroll
   for (int i = 0; i < 16; ++i) pacc[i] = 0;
-#define PROF_MARK(k)               \
-  if (PROF && prof_on) {           \
+#define PROF_MARK(k)                 \
+  if (PROF && prof_on) {             \
     const long long now = clock64(); \
-    pacc[k] += now - plast;        \
-    plast = now;                   \
+    pacc[k] += now - plast;          \
+    plast = now;                     \
+  }
+
+  // ---- list entry -> ray, two tiles ahead; ray -> registers, one tile ahead ----------------------------------
+  // rows past the end of the list repeat its last entry (no divergence around the warp-wide tensor-memory
+  // instructions) and write nothing
+  auto entry_of = [&](long long t) -> uint32_t {
+    const long long jr = t * ROWS + row;
+    return __ldg(a.ids + (jr < total ? jr : total - 1));
+  };
+  auto load_ray = [&](uint32_t id) -> RaySample {
+    RaySample r;
+    const uint32_t ray = id >> p.kbits;
+    const float* src = a.rays + (size_t)ray * 6;
+    r.o[0] = __ldg(src + 0);
+    r.o[1] = __ldg(src + 1);
+    r.o[2] = __ldg(src + 2);
+    r.d[0] = __ldg(src + 3);
+    r.d[1] = __ldg(src + 4);
+    r.d[2] = __ldg(src + 5);
+    r.t_min = __ldg(a.t_min + ray);
+    r.k = (int)(id & kmask);
+    return r;
+  };
+  uint32_t id_ahead = 0;  // entry of this group's tile after the next
+  RaySample next_ray = {};
+  if (t_beg + slot < t_end) {
+    next_ray = load_ray(entry_of(t_beg + slot));
+    if (t_beg + slot + FG < t_end) id_ahead = entry_of(t_beg + slot + FG);
   }
   if (PROF && prof_on) plast = clock64();
+
+  // ---- gather ----------------------------------------------------------------------------------------------
+  // PIPE == false (what runs): a tile starts with its gather; the five rounds of a thread are independent,
+  // so their loads overlap.  PIPE == true: the rounds of a group's NEXT tile are gathered into registers
+  // in the shadows of the current tile's MMAs (one round behind the projection, two behind each hidden
+  // layer) and a tile starts by storing them; measured slower (19.6 against 17.6 ms per frame): spread
+  // out like that a round has only its own six loads in flight.
+  uint32_t nq[5][8];  // half 0 holds rounds 0..4, half 1 rounds 5..8 (index = round - 5 half)
+  RaySample gs = {};  // the sample being gathered
+  float gx = 0.0f, gy = 0.0f, gz = 0.0f;
+  auto position_of = [&](const RaySample& r) {
+    // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
+    const float t = gnr_sample_t(p, r.t_min, r.k);
+    gx = gnr_normalize(gnr_point(r.o[0], r.d[0], t), p.lo[0], p.inv[0]);
+    gy = gnr_normalize(gnr_point(r.o[1], r.d[1], t), p.lo[1], p.inv[1]);
+    gz = gnr_normalize(gnr_point(r.o[2], r.d[2], t), p.lo[2], p.inv[2]);
+  };
+  auto taps_of = [&](int pi) -> PairTapsH2 {
+    const GnrPlane& pl = planes.p[pi];
+    if (NP == 3) {
+      const Tap tx = make_tap(gx, planes.p[0].fw, planes.p[0].W);
+      const Tap ty = make_tap(gy, planes.p[0].fh, planes.p[0].H);
+      const Tap tz = make_tap(gz, planes.p[0].fl, planes.p[0].L);
+      return pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
+    }
+    const float u = pick(gx, gy, gz, pl.mat0), v = pick(gx, gy, gz, pl.mat1), l = pick(gx, gy, gz, pl.vec);
+    return make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
+  };
+  // local round i of this half: global round r = i + 5 half = 3 pair + g, columns 8 r .. 8 r + 7 of A0
+  auto gather_local = [&](auto idx_c) {
+    constexpr int i = decltype(idx_c)::value;
+    const int r = i + 5 * half, pi = r / 3, g = r - 3 * pi;  // (warp-uniform)
+    if (r >= 9) return;
+    if (pi < planes.n) {
+      const PairTapsH2 t_pair = taps_of(pi);
+      pair_round_h2(planes.p[pi], t_pair, g, nq[i]);
+    } else {  // fewer than three pairs: these columns are zero
+#pragma unroll
+      for (int e = 0; e < 8; ++e) nq[i][e] = 0u;
+    }
+  };
+  using I0 = std::integral_constant<int, 0>;
+  using I1 = std::integral_constant<int, 1>;
+  using I2 = std::integral_constant<int, 2>;
+  using I3 = std::integral_constant<int, 3>;
+  using I4 = std::integral_constant<int, 4>;
+  if (PIPE && t_beg + slot < t_end) {  // prologue: the first tile's rounds
+    position_of(next_ray);
+    gather_local(I0{});
+    gather_local(I1{});
+    gather_local(I2{});
+    gather_local(I3{});
+    gather_local(I4{});
+  }
 
   for (long long tile = t_beg + slot; tile < t_end; tile += FG) {
     const long long j = tile * ROWS + row;
     const bool live = j < total;
     const bool has_next = tile + FG < t_end;  // (the same for every thread of the group)
-    // ---- this tile's products: registers -> tensor memory ------------------------------------------------
-    const float view[3] = {nview[0], nview[1], nview[2]};
-    tmem_st32(a_tmem + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&nq[0]));
-    tmem_st32(a_tmem + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&nq[32]));
-    tmem_st8(a_tmem + lane_off + 64, *reinterpret_cast<uint32_t(*)[8]>(&nq[64]));
+    const RaySample cur = next_ray;
+    if (has_next) next_ray = load_ray(id_ahead);              // (not needed before the gather slots below)
+    if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
+
+    // ---- this tile's products: (gather,) registers -> tensor memory ---------------------------------------
+    if (!PIPE) {
+      position_of(cur);
+      gather_local(I0{});
+      gather_local(I1{});
+      gather_local(I2{});
+      gather_local(I3{});
+      gather_local(I4{});
+    }
+#pragma unroll
+    for (int i = 0; i < 5; ++i) {
+      if (i + 5 * half < 9) tmem_st8(a_tmem + lane_off + (i + 5 * half) * 8, nq[i]);
+    }
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
     PROF_MARK(0);
 
-    // ---- F = A0 * Wb^T ---------------------------------------------------------------------------------
-    if (warp_in_group == 0) {
+    // ---- F = A0 * Wb^T (issued by warp 0 of the group) -----------------------------------------------------
+    if (wg == 0) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -230,64 +278,68 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       __syncwarp();
     }
     PROF_MARK(1);
-    if (has_next) {  // behind the projection: the next tile's positions, and its texels on their way into L1
-      fetch_pos(tile + FG);
-      prefetch_next();
+    if (PIPE && has_next) {  // gather slot behind the projection
+      position_of(next_ray);
+      gather_local(I0{});
     }
-    PROF_MARK(2);
     WAIT_OR_STOP();
-    PROF_MARK(3);
-    float f[32];
+    PROF_MARK(2);
+
+    // ---- A1: this half's 40 columns of the layer-1 input (K order of the permuted W1 image) -----------------
     {
-      uint32_t v[32];
+      uint32_t v[32];  // the 27 projected features of this row (accumulator columns 27..31 are zero padding)
       tmem_ld32(f_tmem + lane_off, v);
       tmem_ld_wait();
+      uint32_t h[40];
+      if (half == 0) {
+        // columns 0..6: f0..f13; 7: the constant 1 that multiplies b1; 8..21: (sin f, sin 2f); 22..35: (cos f, cos 2f); 36..39: 0
 #pragma unroll
-      for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-    }
-
-    // ---- A1: features, view direction and their positional encodings ----------------------------------------
-    {
-      float x[K1];
+        for (int c = 0; c < 7; ++c) h[c] = pack_h2(__uint_as_float(v[2 * c]), __uint_as_float(v[2 * c + 1]));
+        h[7] = pack_h2(1.0f, 0.0f);
 #pragma unroll
-      for (int i = 0; i < APP; ++i) x[i] = f[i];
+        for (int i = 0; i < 14; ++i) {  // sin/cos of f and 2 f: one sincos, then the double-angle identities
+          float s, c;
+          sincos_reduced(__uint_as_float(v[i]), s, c);
+          h[8 + i] = pack_h2(s, 2.0f * s * c);
+          h[22 + i] = pack_h2(c, 1.0f - 2.0f * s * s);
+        }
 #pragma unroll
-      for (int i = 0; i < 3; ++i) x[APP + i] = view[i];
+        for (int c = 36; c < 40; ++c) h[c] = 0u;
+      } else {
+        // columns 40..47: f14..f26, view; 48..60: sin pairs of f14..f26; 61..73: cos pairs; 74..76 / 77..79: view sin / cos pairs
+        float val[16];
 #pragma unroll
-      for (int i = 0; i < APP; ++i) {  // sin/cos of v and 2 v: one sincos, then the double-angle identities
-        float s, c;
-        sincos_reduced(f[i], s, c);
-        x[APP + 3 + 2 * i] = s;
-        x[APP + 3 + 2 * i + 1] = 2.0f * s * c;
-        x[APP + 3 + 2 * APP + 2 * i] = c;
-        x[APP + 3 + 2 * APP + 2 * i + 1] = 1.0f - 2.0f * s * s;
+        for (int i = 0; i < 13; ++i) val[i] = __uint_as_float(v[14 + i]);
+        val[13] = cur.d[0];
+        val[14] = cur.d[1];
+        val[15] = cur.d[2];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) h[c] = pack_h2(val[2 * c], val[2 * c + 1]);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float s, c;
+          sincos_reduced(val[i], s, c);
+          const uint32_t sp = pack_h2(s, 2.0f * s * c), cp = pack_h2(c, 1.0f - 2.0f * s * s);
+          if (i < 13) {
+            h[8 + i] = sp;
+            h[21 + i] = cp;
+          } else {
+            h[34 + (i - 13)] = sp;
+            h[37 + (i - 13)] = cp;
+          }
+        }
       }
-#pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        float s, c;
-        sincos_reduced(view[i], s, c);
-        x[APP + 3 + 4 * APP + 2 * i] = s;
-        x[APP + 3 + 4 * APP + 2 * i + 1] = 2.0f * s * c;
-        x[APP + 3 + 4 * APP + 6 + 2 * i] = c;
-        x[APP + 3 + 4 * APP + 6 + 2 * i + 1] = 1.0f - 2.0f * s * s;
-      }
-      x[BIAS_COL1] = 1.0f;  // multiplies the b1 column of the W1 image
-#pragma unroll
-      for (int i = IN_DIM + 1; i < K1; ++i) x[i] = 0.0f;
-      uint32_t h[K1 / 2];
-#pragma unroll
-      for (int i = 0; i < K1 / 2; ++i) h[i] = pack_h2(x[2 * i], x[2 * i + 1]);
-      tmem_st32(a_tmem + lane_off, *reinterpret_cast<uint32_t(*)[32]>(&h[0]));
-      tmem_st32(a_tmem + lane_off + 32, *reinterpret_cast<uint32_t(*)[32]>(&h[32]));
-      tmem_st16(a_tmem + lane_off + 64, *reinterpret_cast<uint32_t(*)[16]>(&h[64]));
+      const uint32_t at = a_tmem + lane_off + (half ? 40u : 0u);
+      tmem_st32(at, *reinterpret_cast<uint32_t(*)[32]>(&h[0]));
+      tmem_st8(at + 32, *reinterpret_cast<uint32_t(*)[8]>(&h[32]));
     }
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
-    PROF_MARK(4);
+    PROF_MARK(3);
 
-    // ---- D = A1 * W1^T ---------------------------------------------------------------------------------------
-    if (warp_in_group == 1) {
+    // ---- D = A1 * W1^T (warp 1) ------------------------------------------------------------------------------
+    if (wg == 1) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -296,35 +348,36 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
-    PROF_MARK(5);
-    if (has_next) gather_pair(P0{});  // behind layer 1
-    PROF_MARK(6);
-    WAIT_OR_STOP();
-    PROF_MARK(7);
-
-    // ---- A2 = relu(D) (D already holds b1), the constant-1 column of b2, padding ------------------------------
-#pragma unroll
-    for (int cb = 0; cb < HID / 64; ++cb) {
-      uint32_t v[64];
-      tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-      tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-      tmem_ld_wait();
-      uint32_t h[32];
-#pragma unroll
-      for (int e = 0; e < 32; ++e) h[e] = pack_h2_relu(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-      tmem_st32(a_tmem + lane_off + cb * 32, h);
+    PROF_MARK(4);
+    if (PIPE && has_next) {  // gather slot behind layer 1
+      gather_local(I1{});
+      gather_local(I2{});
     }
-    {
+    WAIT_OR_STOP();
+    PROF_MARK(5);
+
+    // ---- A2 = relu(D) (D already holds b1): half h converts columns 64 h .. 64 h + 63 --------------------------
+#pragma unroll
+    for (int cb = 0; cb < 2; ++cb) {
+      uint32_t v[32];
+      tmem_ld32(d_tmem + lane_off + half * 64 + cb * 32, v);
+      tmem_ld_wait();
+      uint32_t h[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) h[e] = pack_h2_relu(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+      tmem_st16(a_tmem + lane_off + half * 32 + cb * 16, h);
+    }
+    if (half == 1) {
       const uint32_t tail[8] = {pack_h2(1.0f, 0.0f), 0u, 0u, 0u, 0u, 0u, 0u, 0u};  // k = 128 is the bias input, 129..143 padding
       tmem_st8(a_tmem + lane_off + HID / 2, tail);
     }
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
-    PROF_MARK(8);
+    PROF_MARK(6);
 
-    // ---- D = A2 * W2^T ---------------------------------------------------------------------------------------
-    if (warp_in_group == 2) {
+    // ---- D = A2 * W2^T (warp 2) ------------------------------------------------------------------------------
+    if (wg == 2) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -333,29 +386,30 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
-    PROF_MARK(9);
-    if (has_next) gather_pair(P1{});  // behind layer 2
-    PROF_MARK(10);
+    PROF_MARK(7);
+    if (PIPE && has_next) {  // gather slot behind layer 2
+      gather_local(I3{});
+      gather_local(I4{});
+    }
     WAIT_OR_STOP();
-    PROF_MARK(11);
+    PROF_MARK(8);
 
-    // ---- A3 = relu(D), rgb = sigmoid(A3 * W3^T + b3) ---------------------------------------------------------
+    // ---- A3 = relu(D), rgb = sigmoid(A3 * W3^T + b3) (warp 3) ---------------------------------------------------
 #pragma unroll
-    for (int cb = 0; cb < HID / 64; ++cb) {
-      uint32_t v[64];
-      tmem_ld32(d_tmem + lane_off + cb * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-      tmem_ld32(d_tmem + lane_off + cb * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+    for (int cb = 0; cb < 2; ++cb) {
+      uint32_t v[32];
+      tmem_ld32(d_tmem + lane_off + half * 64 + cb * 32, v);
       tmem_ld_wait();
-      uint32_t h[32];
+      uint32_t h[16];
 #pragma unroll
-      for (int e = 0; e < 32; ++e) h[e] = pack_h2_relu(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
-      tmem_st32(a_tmem + lane_off + cb * 32, h);
+      for (int e = 0; e < 16; ++e) h[e] = pack_h2_relu(__uint_as_float(v[2 * e]), __uint_as_float(v[2 * e + 1]));
+      tmem_st16(a_tmem + lane_off + half * 32 + cb * 16, h);
     }
     tmem_st_wait();
     tc_fence_before();
     GROUP_SYNC();
-    PROF_MARK(12);
-    if (warp_in_group == 3) {
+    PROF_MARK(9);
+    if (wg == 3) {
       tc_fence_after();
       const uint32_t leader = elect_one();
 #pragma unroll
@@ -364,22 +418,22 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
       mma_commit(mbar, leader);
       __syncwarp();
     }
-    if (has_next) gather_pair(P2{});  // behind layer 3
+    PROF_MARK(10);
     WAIT_OR_STOP();
-    PROF_MARK(13);
-    {
+    PROF_MARK(11);
+    if (half == 0) {
       uint32_t r[4];
       tmem_ld4(f_tmem + lane_off, r);
       tmem_ld_wait();
       if (live) {
         float* out = a.rgb_out + (size_t)j * 3;
-        out[0] = 1.0f / (1.0f + expf(-(s_b3[0] + __uint_as_float(r[0]))));
-        out[1] = 1.0f / (1.0f + expf(-(s_b3[1] + __uint_as_float(r[1]))));
-        out[2] = 1.0f / (1.0f + expf(-(s_b3[2] + __uint_as_float(r[2]))));
+        out[0] = 1.0f / (1.0f + __expf(-(s_b3[0] + __uint_as_float(r[0]))));
+        out[1] = 1.0f / (1.0f + __expf(-(s_b3[1] + __uint_as_float(r[1]))));
+        out[2] = 1.0f / (1.0f + __expf(-(s_b3[2] + __uint_as_float(r[2]))));
       }
     }
     tc_fence_before();  // this tile's tensor-memory reads come before the next tile's writes
-    PROF_MARK(14);
+    PROF_MARK(12);
   }
 #undef WAIT_OR_STOP
 #undef PROF_MARK
@@ -392,12 +446,12 @@ __global__ void __launch_bounds__(FG * 128, 1) app_mlp_fused_kernel(GnrSamplePar
   if (expired) {
     // MMAs of this group may still be running: commit once more and wait for them, so that nothing
     // writes tensor memory after it has been freed
-    if (warp_in_group == 0) {
+    if (wg == 0) {
       const uint32_t leader = elect_one();
       mma_commit(mbar, leader);
       __syncwarp();
     }
-    group_wait(mbar, parity, bar_id, row, s_flag, a.wait_limit);
+    group_wait(mbar, parity, bar_id, tg, s_flag, a.wait_limit, GT);
   }
 #undef GROUP_SYNC
   tc_fence_before();
@@ -412,6 +466,33 @@ constexpr size_t kFusedSmem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES 
 
 }  // namespace
 
+// Input column of MLP layer 1 that sits at position k of the fused kernel's A1 operand
+// (0..149 = an input of the layer, -2 = the constant 1 that multiplies b1, -1 = zero padding).
+void gnr_fused_k1_order(int* map) {
+  for (int k = 0; k < K1; ++k) map[k] = -1;
+  const int sin0 = APP + 3, cos0 = sin0 + 2 * APP, vsin0 = cos0 + 2 * APP, vcos0 = vsin0 + 6;
+  // half 0: columns 0..39
+  for (int i = 0; i < 14; ++i) map[i] = i;                       // f0..f13
+  map[14] = -2;                                                  // bias input
+  for (int i = 0; i < 14; ++i)
+    for (int o = 0; o < 2; ++o) {
+      map[16 + 2 * i + o] = sin0 + 2 * i + o;
+      map[44 + 2 * i + o] = cos0 + 2 * i + o;
+    }
+  // half 1: columns 40..79
+  for (int m = 0; m < 16; ++m) map[80 + m] = m < 13 ? 14 + m : APP + (m - 13);  // f14..f26, view
+  for (int i = 14; i < APP; ++i)
+    for (int o = 0; o < 2; ++o) {
+      map[96 + 2 * (i - 14) + o] = sin0 + 2 * i + o;
+      map[122 + 2 * (i - 14) + o] = cos0 + 2 * i + o;
+    }
+  for (int i = 0; i < 3; ++i)
+    for (int o = 0; o < 2; ++o) {
+      map[148 + 2 * i + o] = vsin0 + 2 * i + o;
+      map[154 + 2 * i + o] = vcos0 + 2 * i + o;
+    }
+}
+
 int gnr_app_fusable(const GnrModel* m) {
   // fp16 appearance planes of 48 (padded) channels, the single-fp16 tensor-core mode, and a product count
   // that fits the 80 operand columns
@@ -425,9 +506,17 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
   }
+  if (!c.ids || c.index || c.xyz_direct || !c.total_ptr) {
+    gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count)");
+    return -1;
+  }
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
   FusedArgs a;
-  a.crd = c;
+  a.rays = c.rays;
+  a.t_min = c.t_min;
+  a.ids = c.ids;
+  a.total_ptr = c.total_ptr;
+  a.capacity = c.capacity;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
   a.b3 = m->mlp.b3;
   a.rgb_out = rgb;
@@ -439,12 +528,12 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   auto launch = [&](auto kernel) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
     if (e != cudaSuccess) return (int)e;
-    kernel<<<m->sm_count, FG * 128, kFusedSmem, st>>>(p, set, a);
+    kernel<<<m->sm_count, FG * GT, kFusedSmem, st>>>(p, set, a);
     return 0;
   };
   int rc;
-  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true>) : launch(app_mlp_fused_kernel<0, true>);
-  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false>) : launch(app_mlp_fused_kernel<0, false>);
+  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false>) : launch(app_mlp_fused_kernel<0, true, false>);
+  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false>) : launch(app_mlp_fused_kernel<0, false, false>);
   if (rc) return rc;
   return (int)cudaGetLastError();
 }

@@ -165,6 +165,7 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
 int gnr_app_fusable(const GnrModel* m);
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
                          cudaStream_t st);
+void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,

@@ -471,6 +471,26 @@ __global__ void pack_weight_image_kernel(const float* __restrict__ w, __half* __
   }
 }
 
+// The same image with the K positions taken from a table: map[k] = column of w, -2 = bias, -1 = zero.
+__global__ void pack_weight_image_mapped_kernel(const float* __restrict__ w, __half* __restrict__ img, int n_out, int n_rows,
+                                                int k_real, int k_groups, const int* __restrict__ map,
+                                                const float* __restrict__ bias) {
+  int i = blockIdx.x * blockDim.x + threadIdx.x;  // one thread per (kg, n)
+  if (i >= k_groups * n_rows) return;
+  int kg = i / n_rows, n = i - kg * n_rows;
+  __half* dst = img + (size_t)i * 8;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int col = map[kg * 8 + e];
+    float v = 0.0f;
+    if (n < n_out) {
+      if (col >= 0 && col < k_real) v = w[(size_t)n * k_real + col];
+      else if (col == -2 && bias != nullptr) v = bias[n];
+    }
+    dst[e] = __float2half_rn(v);
+  }
+}
+
 template <int TA, int NSLOT, bool BASIS>
 int launch_variant(const GnrModel* m, const TcArgs& args, cudaStream_t st) {
   const size_t smem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES + (size_t)NSLOT * TA * A_BYTES +
@@ -499,7 +519,8 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
   }
   if (m->mlp.tc_image) cudaFree(m->mlp.tc_image);
   m->mlp.tc_image = nullptr;
-  m->mlp.tc_image_bytes = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES;
+  // [basis][W1][W2][W3] and, for the fused appearance kernel, W1 once more with its K order permuted
+  m->mlp.tc_image_bytes = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES + W1_BYTES + K1 * sizeof(int);
   GNR_CUDA_OK(cudaMalloc(&m->mlp.tc_image, m->mlp.tc_image_bytes));
   GNR_CUDA_OK(cudaMemsetAsync(m->mlp.tc_image, 0, m->mlp.tc_image_bytes, st));
   __half* img = reinterpret_cast<__half*>(m->mlp.tc_image);
@@ -515,6 +536,15 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
                                                                    0, 0, m->mlp.b2, BIAS_COL2);
   pack_weight_image_kernel<<<((HID / 8) * N3 + 255) / 256, 256, 0, st>>>(w3, img + (WB_BYTES + W1_BYTES + W2_BYTES) / 2, 3, N3,
                                                                         HID, HID / 8, 0, 0, nullptr, -1);
+  {
+    int map_h[K1];
+    gnr_fused_k1_order(map_h);
+    int* map_d = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(m->mlp.tc_image) + WB_BYTES + 2 * W1_BYTES + W2_BYTES + W3_BYTES);
+    GNR_CUDA_OK(cudaMemcpyAsync(map_d, map_h, sizeof(map_h), cudaMemcpyHostToDevice, st));
+    GNR_CUDA_OK(cudaStreamSynchronize(st));  // map_h is a stack array
+    pack_weight_image_mapped_kernel<<<(KG1 * HID + 255) / 256, 256, 0, st>>>(
+        w1, img + (WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES) / 2, HID, HID, IN_DIM, KG1, map_d, m->mlp.b1);
+  }
   GNR_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -124,9 +124,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
 // One thread of the group waits (bounded) and publishes the outcome; the whole group leaves
 // with the same answer, so a group either continues or stops as one.
 __device__ __forceinline__ bool group_wait(uint32_t mbar, uint32_t parity, int bar_id, int row, volatile uint32_t* flag,
-                                           uint32_t limit = kWaitLimit) {
+                                           uint32_t limit = kWaitLimit, int group_threads = 128) {
   if (row == 0) *flag = mbar_wait_bounded(mbar, parity, limit) ? 1u : 0u;
-  asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+  asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(group_threads) : "memory");
   const bool ok = *flag != 0;
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   return ok;

@@ -679,7 +679,7 @@ def _fused_pair(spec, ckpt=None, args=None, sd=None, kwargs=None):
 def test_fused_appearance_kernel_equals_separate_kernels():
     """gather + basis projection + MLP in one kernel (operands in tensor memory) against the separate
     gather and MLP kernels: the same products, the same GEMMs in the same K order, so the colours agree
-    to the last few bits (the view direction reaches the fused kernel as fp32 instead of fp16 hi + lo);
+    to a few 1e-6 (the fused kernel sums layer 1 in another K order and takes the view direction as fp32);
     both stay within 1e-4 of the reference fixture.  Also with a black background, on the nine-tap
     general layout, and on a chunk whose appearance list does not fill a tile."""
     spec = scenes.tiny_spec().lit()
@@ -692,7 +692,7 @@ def test_fused_appearance_kernel_equals_separate_kernels():
         b, _ = split(rays, white_bg=white, N_samples=spec.n_samples)
         assert int(fused.last_status[3]) == int(split.last_status[3]) > 10000
         assert torch.equal(a["depth_map"], b["depth_map"])
-        assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+        assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
     a, _ = fused(rays, N_samples=spec.n_samples)
     err = (a["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
     assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
@@ -700,7 +700,7 @@ def test_fused_appearance_kernel_equals_separate_kernels():
     a, _ = fused(few, N_samples=spec.n_samples)
     b, _ = split(few, N_samples=spec.n_samples)
     assert 0 < int(fused.last_status[3]) < 128 * 3
-    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
     # three pairs that are not the standard VM layout (general branch of the fused gather)
     spec2 = scenes.tiny_spec(grid=32).lit()
     args = scenes.model_args(spec2)
@@ -721,7 +721,7 @@ def test_fused_appearance_kernel_equals_separate_kernels():
     a, _ = fused2(r2, N_samples=64)
     b, _ = split2(r2, N_samples=64)
     assert int(fused2.last_status[3]) > 1000
-    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 2e-6
+    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
 
 
 @pytest.mark.parametrize("fused", [True, False])
