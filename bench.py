@@ -237,7 +237,7 @@ def main():
 
         sampler = ClockSampler(local_rank) if rank == 0 else None
         res = run_model_parallel(a.workload, a.steps, max(a.warmup, 3), a.chunk, a.mlp_mode, rank, world, device,
-                                 a.grid_scale, a.check, ert=a.ert, app_fp16=bool(a.app_fp16))
+                                 a.grid_scale, a.check, ert=a.ert, app_fp16=bool(a.app_fp16), den_lattice=bool(a.den_lattice))
         clocks = sampler.stop() if sampler else None
         if rank == 0:
             line = {"metric": "Mrays/s", "value": res["rays"] / (res["ms_per_frame"] * 1e-3) / 1e6, "unit": "Mrays/s",

@@ -267,6 +267,21 @@ int gnr_composite(GnrModel* m, int64_t n_rays, int white_bg, void* workspace, si
  * number of every valid sample of the last gnr_sample on this workspace. */
 int gnr_valid_positions(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
                         size_t workspace_bytes, int64_t max_valid, float* xyz, int32_t* ray_index, void* stream);
+/* Block routing: assign_blocks_to_samples (app/models/gridnerf_parallel.py:279-338; kernel version
+ * dist_render/kernel/cuda_kernel/sampleray_gridsample/compute_assign_blocks_to_samples_norm_cuda_kernel.cu:19-74)
+ * for a field cut into ``px x py`` blocks (block b = bx * py + by, at most 32), applied to the valid list
+ * (``which_list`` 0, after gnr_sample) or the appearance list (1, after gnr_weights / gnr_weights_from_sigma
+ * / gnr_march) of the workspace, fused with the grouping an all-to-all needs.  ``send_points`` receives the
+ * block-local points grouped by block, block 0 first and list order inside a block (a stable partition):
+ * rows of 3 floats (x, y local to the block, z) for the valid list, 6 floats (point, view direction) for the
+ * appearance list; capacity = the list's capacity.  ``dest_row[i]`` = row of list entry i in that buffer (use
+ * it to bring the owners' answers back into list order), ``counts[px*py]`` = rows per block (device int32),
+ * ``block_of[i]`` (optional) = block of entry i.  Block indices and local coordinates have the bits of the
+ * reference's torch arithmetic, except that x or y == 1 belongs to the last block instead of one past it.
+ * Three launches on ``stream``, no host synchronisation; the first call on a model allocates 150 KB. */
+int gnr_route_blocks(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
+                     int64_t max_valid, int64_t max_app, int which_list, int px, int py, float* send_points,
+                     int32_t* dest_row, int32_t* counts, int32_t* block_of, void* stream);
 /* compute_densityfeature + feature2density at explicit normalised points (block owner side of
  * gridnerf_parallel.py:765-790).  ``sigma_feature`` may be NULL. */
 int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_feature, float* sigma, void* stream);
@@ -291,6 +306,12 @@ int gnr_points_scratch_bytes(const GnrModel* m, int64_t n, size_t* bytes_h);
  * gridnerf_parallel.py:801-859. */
 int gnr_appearance_points(GnrModel* m, const float* xyz, const float* view, int64_t n, void* scratch,
                           size_t scratch_bytes, float* features, float* rgb, void* stream);
+/* compute_appfeature alone at explicit points: ``features[n][app_dim]`` = basis_mat(plane x line products) of
+ * this model's appearance channels.  With a channel slice of the planes and the matching columns of basis_mat
+ * these are the partial sums a tensor-parallel rank contributes for points that any rank sampled
+ * (gridnerf_tensor_parallel.py:284-300).  Same scratch as gnr_appearance_points. */
+int gnr_app_features_points(GnrModel* m, const float* xyz, int64_t n, void* scratch, size_t scratch_bytes,
+                            float* features, void* stream);
 /* MLPRender_Fea alone on explicit ``features[n][app_dim]`` and ``view[n][3]`` (the sample slice a
  * tensor-parallel rank owns after the reduction, gridnerf_tensor_parallel.py:301-325). */
 int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,

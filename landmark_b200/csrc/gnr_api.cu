@@ -258,6 +258,7 @@ extern "C" int gnr_destroy(GnrModel* m) {
   }
   free_dev(m->den_lattice);
   free_dev(m->debug_prof);
+  free_dev(m->route_scratch);
   free_dev(m->alpha_bits);
   free_dev(m->alpha_coarse);
   free_dev(m->alpha_full);
@@ -1169,6 +1170,37 @@ extern "C" int gnr_appearance_points(GnrModel* m, const float* xyz, const float*
   return mlp_points(m, p, c, sc, S, fused, features, rgb, st);
 }
 
+extern "C" int gnr_app_features_points(GnrModel* m, const float* xyz, int64_t n, void* scratch, size_t scratch_bytes,
+                                       float* features, void* stream) {
+  int rc = check_points(m, "gnr_app_features_points", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!xyz || !features) {
+    gnr_set_error("gnr_app_features_points: null xyz or features");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = (char*)scratch;
+  const PointScratch S = point_scratch(m, n);
+  GnrSampleParams p = gnr_sample_params(m, 1);
+  const GnrCoords c = coords_points(xyz, nullptr, n);
+  float* feat = (float*)(sc + S.feat);
+  if (m->cfg.mlp_mode != 0 && gnr_tc_basis_fused(m)) {
+    // product tiles, then the projection alone on the tensor cores (fp32 accumulate)
+    GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+    unsigned char* hi = (unsigned char*)(sc + S.prod);
+    GNR_LAUNCH_OK(launch_app_products(m, p, c, hi, hi + S.prod_image, S.tile_bytes, S.terms, st));
+    GNR_LAUNCH_OK(launch_mlp_tc(m, p, c, 28, nullptr, feat, hi, hi + S.prod_image, S.tile_bytes, nullptr, (int32_t*)(sc + S.status), 0, st,
+                                /*basis_only=*/1));
+  } else {
+    GNR_LAUNCH_OK(launch_app_gather(m, p, c, 28, feat, st));
+  }
+  GNR_CUDA_OK(cudaMemcpy2DAsync(features, (size_t)m->cfg.app_dim * 4, feat, 28 * 4, (size_t)m->cfg.app_dim * 4, (size_t)n,
+                                cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
 extern "C" int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,
                                 size_t scratch_bytes, float* rgb, void* stream) {
   int rc = check_points(m, "gnr_mlp_features", n, scratch, scratch_bytes);
@@ -1203,6 +1235,24 @@ extern "C" int gnr_valid_positions(GnrModel* m, const float* rays, int64_t n, in
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, 0);
   GnrSampleParams p = gnr_sample_params(m, S);
   GNR_LAUNCH_OK(launch_positions(m, p, gnr_coords_valid(rays, ws, L), xyz, ray_index, (cudaStream_t)stream));
+  return 0;
+}
+
+extern "C" int gnr_route_blocks(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                                int64_t max_valid, int64_t max_app, int which_list, int px, int py, float* send_points,
+                                int32_t* dest_row, int32_t* counts, int32_t* block_of, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays || !send_points || !dest_row || !counts || (which_list != 0 && which_list != 1)) {
+    gnr_set_error("gnr_route_blocks: null rays / send_points / dest_row / counts, or which_list not 0 (valid) / 1 (appearance)");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  const GnrCoords c = which_list == 0 ? gnr_coords_valid(rays, ws, L) : gnr_coords_app(rays, ws, L);
+  GNR_LAUNCH_OK(launch_route_blocks(m, p, c, px, py, which_list == 1, send_points, dest_row, counts, block_of, (cudaStream_t)stream));
   return 0;
 }
 

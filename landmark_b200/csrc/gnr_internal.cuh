@@ -66,6 +66,8 @@ struct GnrModel {
   GnrMlp mlp;
   int debug_expire_wait;  // test hook (gnr_debug_wait): make one bounded wait of the tensor-core kernels run out
   int debug_wait_limit;   // polls a bounded wait may take; 0 = the default
+  int32_t* route_scratch;  // per-CTA block counts and start rows of gnr_route_blocks
+  size_t route_scratch_bytes;
   long long* debug_prof;  // device buffer of phase cycle sums (gnr_debug_phase_cycles), null when off
   // hull sampler tables (sampling_mode 1)
   float* hull_near_term;
@@ -168,6 +170,8 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
 void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
+int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int px, int py, int with_view, float* send,
+                        int32_t* dest, int32_t* counts, int32_t* block_of, cudaStream_t st);
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
                      cudaStream_t st);
 int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat,

@@ -121,8 +121,9 @@ class _Chunk:
         self.num_valid = self.num_app = 0
         self.ids = self.app_index = None
 
-    def sample(self):
-        self.ids = torch.empty(self.max_valid, dtype=torch.int32, device=self.m.device)
+    def sample(self, keep_ids: bool = True):
+        """``keep_ids``: also copy the compacted id list out of the workspace (callers that index it with torch)."""
+        self.ids = torch.empty(self.max_valid, dtype=torch.int32, device=self.m.device) if keep_ids else None
         check(lib.gnr_sample(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
                              None, None, None, None, _ptr(self.ids), _stream()), "gnr_sample")
         st = self.m.read_status(self.ws)
@@ -150,9 +151,34 @@ class _Chunk:
                                       self.max_valid, _ptr(xyz), _ptr(ray), _stream()), "gnr_valid_positions")
         return xyz[: self.num_valid], ray[: self.num_valid].to(torch.int64)
 
-    def weights(self, sigma: Optional[torch.Tensor] = None):
+    def route(self, which_list: int, division: Tuple[int, int]):
+        """Block assignment + grouping by owner of the valid list (``which_list`` 0) or the appearance list
+        (1) in one library call (gnr_route_blocks).  Returns the send buffer (block-local points, with view
+        directions for the appearance list, grouped by block), the row every list entry went to, and the
+        per-block counts (the only host read of the exchange)."""
+        n_items = self.num_valid if which_list == 0 else self.num_app
+        dev = self.m.device
+        send = torch.empty((max(n_items, 1), 3 if which_list == 0 else 6), dtype=torch.float32, device=dev)
+        dest = torch.empty((max(n_items, 1),), dtype=torch.int32, device=dev)
+        counts = torch.zeros((division[0] * division[1],), dtype=torch.int32, device=dev)
+        if n_items:
+            check(lib.gnr_route_blocks(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                       self.max_app, which_list, division[0], division[1], _ptr(send), _ptr(dest),
+                                       _ptr(counts), None, _stream()), "gnr_route_blocks")
+        return send[:n_items], dest[:n_items], [int(v) for v in counts.cpu().tolist()]
+
+    def weights(self, sigma: Optional[torch.Tensor] = None, sigma_rows: Optional[torch.Tensor] = None):
+        """``sigma``: one value per valid sample in list order, or, with ``sigma_rows``, the owners' answers
+        in send-buffer order plus the row of every list entry (gathered here, no intermediate copy)."""
         self.app_index = torch.empty(self.max_app, dtype=torch.int32, device=self.m.device)
-        if sigma is None:
+        if sigma is not None and sigma_rows is not None:
+            full = torch.empty(self.max_valid, dtype=torch.float32, device=self.m.device)  # entries past num_valid are never read
+            if self.num_valid:
+                torch.index_select(sigma, 0, sigma_rows, out=full[: self.num_valid])
+            check(lib.gnr_weights_from_sigma(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                             self.max_app, _ptr(full), _ptr(self.app_index), _stream()),
+                  "gnr_weights_from_sigma")
+        elif sigma is None:
             check(lib.gnr_weights(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
                                   self.max_app, None, None, None, None, None, _ptr(self.app_index), _stream()),
                   "gnr_weights")
@@ -189,9 +215,16 @@ class _Chunk:
 
 
 def _scratch(model: B200GridNeRF, n: int):
+    """Scratch of the point-mode entries, kept on the model and only ever grown: calls on one stream reuse
+    it in order, so no call has to wait for the previous one."""
     nb = C.c_size_t(0)
     check(lib.gnr_points_scratch_bytes(model._handle, n, C.byref(nb)), "gnr_points_scratch_bytes")
-    buf = torch.empty(nb.value + 256, dtype=torch.uint8, device=model.device)
+    buf = getattr(model, "_point_scratch", None)
+    if buf is None or buf.numel() < nb.value + 256:
+        if buf is not None:
+            torch.cuda.synchronize(model.device)  # kernels may still be using the smaller buffer
+        buf = torch.empty(int(nb.value * 1.25) + 256, dtype=torch.uint8, device=model.device)
+        model._point_scratch = buf
     off = (-buf.data_ptr()) % 256
     return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off
 
@@ -205,8 +238,20 @@ def mlp_features(model: B200GridNeRF, feats: torch.Tensor, view: torch.Tensor) -
     feats, view = feats.contiguous(), view.contiguous()
     with torch.cuda.device(model.device):
         check(lib.gnr_mlp_features(model._handle, _ptr(feats), _ptr(view), n, sc, nb, _ptr(rgb), _stream()), "gnr_mlp_features")
-        torch.cuda.current_stream().synchronize()  # `keep` must outlive the kernels
     return rgb
+
+
+def app_features_points(model: B200GridNeRF, xyz: torch.Tensor) -> torch.Tensor:
+    """Partial (or complete) basis projection of this model's appearance channels at explicit points."""
+    n = xyz.shape[0]
+    feat = torch.empty((n, model.app_dim), dtype=torch.float32, device=model.device)
+    if n == 0:
+        return feat
+    keep, sc, nb = _scratch(model, n)
+    xyz = xyz.contiguous()
+    with torch.cuda.device(model.device):
+        check(lib.gnr_app_features_points(model._handle, _ptr(xyz), n, sc, nb, _ptr(feat), _stream()), "gnr_app_features_points")
+    return feat
 
 
 def density_points(model: B200GridNeRF, xyz: torch.Tensor) -> torch.Tensor:
@@ -229,7 +274,6 @@ def appearance_points(model: B200GridNeRF, xyz: torch.Tensor, view: torch.Tensor
     with torch.cuda.device(model.device):
         check(lib.gnr_appearance_points(model._handle, _ptr(xyz), _ptr(view), n, sc, nb, None, _ptr(rgb), _stream()),
               "gnr_appearance_points")
-        torch.cuda.current_stream().synchronize()
     return rgb
 
 
@@ -266,47 +310,85 @@ class ChannelParallelRenderer:
         assert len(models) == len(comm.local_ranks)
         self.models, self.comm = list(models), comm
 
+    RAY_GROUP = 1024  # rays are dealt to the ranks in groups of this many consecutive rays
+
+    def _ray_share(self, n: int, rank: int, device) -> torch.Tensor:
+        """Indices of the rays of a chunk that ``rank`` samples: groups of RAY_GROUP consecutive rays dealt
+        round-robin (consecutive rays are neighbouring pixels: a group keeps the kernels' locality, the
+        round-robin balances sky against ground)."""
+        idx = torch.arange(n, device=device)
+        return idx[(idx // self.RAY_GROUP) % self.comm.world == rank]
+
     @torch.no_grad()
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the same chunk on each local rank's device.  Returns per local rank
-        ``(rgb_map, depth_map)``; all ranks end up with the full result."""
+        ``(rgb_map, depth_map)``; all ranks end up with the full result.
+
+        Work split (app/models/gridnerf_tensor_parallel.py:198-217,284-330 divides the density work and the
+        samples over the group as well): every rank samples and marches only ITS share of the rays; the
+        appearance points of all ranks are all-gathered (24 bytes each); every rank projects all of them
+        through its channel slice; the reduce-scatter hands each rank the complete features of its OWN
+        points, on which it runs the MLP and composites its own rays; the pixels are all-gathered."""
         W = self.comm.world
-        chunks = []
-        for m, r in zip(self.models, rays):
+        chunks, shares, points = [], [], []
+        for m, r, rank in zip(self.models, rays, self.comm.local_ranks):
             with torch.cuda.device(m.device):
-                ch = _Chunk(m, r, n_samples)
-                ch.sample()
+                share = self._ray_share(r.shape[0], rank, m.device)
+                mine = r[share] if share.numel() else r[:1]  # a rank without rays still takes part in the collectives
+                ch = _Chunk(m, mine, n_samples)
+                ch.sample(keep_ids=False)
                 if m.ert_transmittance >= 0.0:
-                    ch.march()  # density is replicated: the fused pass of the single-GPU renderer
+                    ch.march()  # the fused pass of the single-GPU renderer
                 else:
                     ch.density()
                     ch.weights()
+                pts, _, _ = ch.route(1, (1, 1))  # one block: the appearance list as (point, view) rows in list order
                 chunks.append(ch)
-        m_a = chunks[0].num_app
-        if any(ch.num_app != m_a for ch in chunks):
-            raise RuntimeError("tensor-parallel ranks disagree on the appearance list (sampling must be replicated)")
-        per = -(-max(m_a, 1) // W)
-        m_pad = per * W
-        partial, views = [], []
-        for ch in chunks:
+                shares.append(share)
+                points.append(pts)
+        counts = self.comm.all_gather_rows([torch.tensor([ch.num_app], dtype=torch.int64, device=ch.m.device) for ch in chunks])
+        per = max(1, int(counts[0].max().item()))  # rows per rank in the gathered list (padded to the largest)
+        padded = []
+        for ch, pts in zip(chunks, points):
             with torch.cuda.device(ch.m.device):
-                f = torch.zeros((m_pad, ch.m.app_dim), dtype=torch.float32, device=ch.m.device)
-                if m_a:
-                    f[:m_a] = ch.app_features()
-                partial.append(f)
-                v = torch.zeros((m_pad, 3), dtype=torch.float32, device=ch.m.device)
-                if m_a:
-                    v[:m_a] = ch.rays[ch.app_ray_index(), 3:6]
-                views.append(v)
-        feats = self.comm.reduce_scatter_rows(partial)  # complete features of this rank's sample slice
-        rgb_slices = []
-        for ch, f, v, rank in zip(chunks, feats, views, self.comm.local_ranks):
-            rgb_slices.append(mlp_features(ch.m, f, v[rank * per:(rank + 1) * per]))
-        rgb_all = self.comm.all_gather_rows(rgb_slices)
+                buf = torch.zeros((per, 6), dtype=torch.float32, device=ch.m.device)
+                buf[: ch.num_app] = pts
+                padded.append(buf)
+        everyone = self.comm.all_gather_rows(padded)  # [W * per, 6], rank r's points in rows r * per ..
+        partial = []
+        for ch, allp in zip(chunks, everyone):
+            with torch.cuda.device(ch.m.device):
+                partial.append(app_features_points(ch.m, allp[:, :3].contiguous()))
+        feats = self.comm.reduce_scatter_rows(partial)  # [per, app_dim]: the complete features of this rank's own points
+        pix = []
+        for ch, share, f, pts in zip(chunks, shares, feats, points):
+            with torch.cuda.device(ch.m.device):
+                rgb_s = mlp_features(ch.m, f[: ch.num_app], pts[:, 3:6].contiguous())
+                rgb, depth = ch.composite(rgb_s, white_bg)
+                pix.append((rgb, depth))
+        # pixels of every rank -> every rank (padded to the largest share)
+        n = rays[0].shape[0]
+        per_rays = max(1, max(int(self._ray_share(n, r, "cpu").numel()) for r in range(W)))
+        packed = []
+        for ch, share, (rgb, depth) in zip(chunks, shares, pix):
+            with torch.cuda.device(ch.m.device):
+                buf = torch.zeros((per_rays, 4), dtype=torch.float32, device=ch.m.device)
+                k = share.numel()
+                buf[:k, :3] = rgb[:k]
+                buf[:k, 3] = depth[:k]
+                packed.append(buf)
+        gathered = self.comm.all_gather_rows(packed)
         out = []
-        for ch, rgb in zip(chunks, rgb_all):
+        for ch, g in zip(chunks, gathered):
             with torch.cuda.device(ch.m.device):
-                out.append(ch.composite(rgb[:m_a], white_bg))
+                rgb = torch.empty((n, 3), dtype=torch.float32, device=ch.m.device)
+                depth = torch.empty((n,), dtype=torch.float32, device=ch.m.device)
+                for r in range(W):
+                    share = self._ray_share(n, r, ch.m.device)
+                    k = share.numel()
+                    rgb[share] = g[r * per_rays:r * per_rays + k, :3]
+                    depth[share] = g[r * per_rays:r * per_rays + k, 3]
+                out.append((rgb, depth))
         return out
 
 
@@ -357,47 +439,36 @@ class BlockParallelRenderer:
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
         Returns per local rank ``(rgb_map, depth_map)`` of its own rays."""
-        W = self.comm.world
-        chunks, locals_, rays_idx, orders, counts = [], [], [], [], []
-        # ---- sample globally, assign blocks, route positions to the owners ----------------------
-        for s, r in zip(self.samplers, rays):
-            with torch.cuda.device(s.device):
-                ch = _Chunk(s, r, n_samples)
-                ch.sample()
-                xyz, ray = ch.positions()
-                b, loc = assign_blocks(xyz, self.division)
-                order, cnt = _route(b, W)
+        chunks, sends, dests, counts = [], [], [], []
+        # ---- sample globally; block assignment + grouping by owner on the device; points travel to the owners
+        for s_, r in zip(self.samplers, rays):
+            with torch.cuda.device(s_.device):
+                ch = _Chunk(s_, r, n_samples)
+                ch.sample(keep_ids=False)
+                send, dest, cnt = ch.route(0, self.division)
                 chunks.append(ch)
-                locals_.append((b, loc))
-                rays_idx.append(ray)
-                orders.append(order)
+                sends.append(send)
+                dests.append(dest)
                 counts.append(cnt)
-        send = [loc[o] for (b, loc), o in zip(locals_, orders)]
-        recv, rcounts = self.comm.all_to_all_rows(send, counts)
+        recv, rcounts = self.comm.all_to_all_rows(sends, counts)
         # ---- owners: density at the received points, values travel back -------------------------
         sig = [density_points(o, x) for o, x in zip(self.owners, recv)]
         back, _ = self.comm.all_to_all_rows(sig, rcounts)
-        app_send, app_counts, app_orders = [], [], []
-        for ch, (b, loc), order, ray, sg in zip(chunks, locals_, orders, rays_idx, back):
+        app_send, app_counts, app_dests = [], [], []
+        for ch, dest, sg in zip(chunks, dests, back):
             with torch.cuda.device(ch.m.device):
-                sigma = torch.empty_like(sg)
-                sigma[order] = sg
-                ch.weights(sigma)
-                ai = ch.app_index
-                ob = b[ai]
-                o2, c2 = _route(ob, W)
-                payload = torch.cat([loc[ai], ch.rays[ray[ai], 3:6]], dim=1)[o2]
-                app_send.append(payload)
-                app_counts.append(c2)
-                app_orders.append(o2)
+                ch.weights(sg, dest)  # answers -> list order, weights, appearance list
+                send, dest_a, cnt = ch.route(1, self.division)
+                app_send.append(send)
+                app_dests.append(dest_a)
+                app_counts.append(cnt)
         # ---- owners: colour at the received (position, view) pairs, values travel back ----------
         arecv, arcounts = self.comm.all_to_all_rows(app_send, app_counts)
         rgb_o = [appearance_points(o, x[:, :3], x[:, 3:6]) for o, x in zip(self.owners, arecv)]
         rgb_back, _ = self.comm.all_to_all_rows(rgb_o, arcounts)
         out = []
-        for ch, o2, rb in zip(chunks, app_orders, rgb_back):
+        for ch, dest_a, rb in zip(chunks, app_dests, rgb_back):
             with torch.cuda.device(ch.m.device):
-                rgb_s = torch.empty_like(rb)
-                rgb_s[o2] = rb
+                rgb_s = torch.index_select(rb, 0, dest_a) if ch.num_app else rb[:0]
                 out.append(ch.composite(rgb_s, white_bg))
         return out

@@ -9,7 +9,8 @@ NCCL).  Both build seeded synthetic scenes on the fly:
   heightfield.  The 1080p frame's rays are tile-sharded over the ranks; samples are routed to
   block owners by all-to-all.
 * ``city_channels``: one city block whose appearance planes have ``48 x world`` channels, 48 per
-  rank; every rank samples all rays of its chunk, partial projections are reduce-scattered.
+  rank; every rank samples its share of the rays of a chunk, the appearance points are all-gathered,
+  partial projections are reduce-scattered back to the rank that owns the points.
 """
 
 from __future__ import annotations
@@ -87,21 +88,22 @@ def build_channels(world: int, rank_list, device: str, mlp_mode: int, grid_scale
 
 
 def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank: int, world: int, device: str,
-        grid_scale: int = 1, check: bool = False, ert: float = 0.0, app_fp16: bool = False) -> Dict:
+        grid_scale: int = 1, check: bool = False, ert: float = 0.0, app_fp16: bool = False, den_lattice: bool = True) -> Dict:
     """Render ``steps`` frames; returns timing and sample statistics (rank 0's view)."""
     import torch.distributed as dist
 
     comm = DistComm() if world > 1 else LoopbackComm(1)
     H, W = 1080, 1920
     if workload == "city_blocks":
-        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2)}
+        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2), "density_lattice": bool(den_lattice)}
         spec, pose, samplers, owners, division = build_blocks(world, [rank], device, mlp_mode, grid_scale, **extra)
         ren = BlockParallelRenderer(samplers, owners, comm, division)
         shard = TileSharding(H, W, rank, world, device)
         rays = generate_rays(pose, H, W, spec.focal, device=device, pixel_ids=shard.pixel_ids)
         parallelism = f"blocks {division[0]}x{division[1]} (all-to-all sample routing) + ray tiles x{world}"
     elif workload == "city_channels":
-        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2), "ert_transmittance": float(ert)}
+        extra = {"app_plane_fp16": bool(app_fp16 and mlp_mode == 2), "ert_transmittance": float(ert),
+                 "density_lattice": bool(den_lattice)}
         spec, pose, models = build_channels(world, [rank], device, mlp_mode, grid_scale, **extra)
         ren = ChannelParallelRenderer(models, comm)
         shard = TileSharding(H, W, 0, 1, device)  # every rank walks the whole frame
@@ -155,8 +157,7 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
     tot = torch.tensor([float(stats["valid"]), float(stats["app"])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        if workload == "city_blocks":
-            dist.all_reduce(tot)
+        dist.all_reduce(tot)  # every rank sampled its own share of the rays (both layouts)
     res = {"ms_per_frame": float(ms.item()), "wall_ms_per_frame": (time.perf_counter() - t0) * 1e3 / steps,
            "valid": float(tot[0].item()), "appearance": float(tot[1].item()), "parallelism": parallelism,
            "image_mean": float(image.mean().item()), "rays": H * W}

@@ -126,6 +126,43 @@ def test_assign_blocks_matches_the_reference_fixture():
         assert np.array_equal(local.cpu().numpy(), fx[f"local_{tag}"]), tag
 
 
+@pytest.mark.parametrize("division", [(2, 1), (2, 2), (4, 2), (3, 5)])
+def test_route_blocks_kernel_equals_torch_assignment_and_stable_grouping(division):
+    """gnr_route_blocks (block assignment + grouping by owner in one pass on the device) against the torch
+    arithmetic (pinned to the reference's method by the fixture test above) followed by a stable per-owner
+    grouping: same rows in the same order, same counts, for the valid list and for the appearance list."""
+    from landmark_b200.model_parallel import _Chunk, _route, assign_blocks
+
+    spec = scenes.tiny_spec().lit()
+    model = cuda_model(spec)
+    rays = tiny_rays(spec).cuda()[2000:6000].contiguous()
+    ch = _Chunk(model, rays, spec.n_samples)
+    ch.sample()
+    xyz, ray = ch.positions()
+    b, loc = assign_blocks(xyz, division)
+    order, cnt = _route(b, division[0] * division[1])
+    send, dest, counts = ch.route(0, division)
+    assert counts == cnt and sum(counts) == ch.num_valid > 50000
+    assert torch.equal(send, loc[order])
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device)
+    assert torch.equal(dest.to(torch.int64), inv)
+    # appearance list: rows carry the view direction as well
+    ch.density()
+    ch.weights()
+    ids = ch.ids[: ch.num_valid].to(torch.int64) & 0xFFFFFFFF
+    ai = ch.app_index
+    b_a, loc_a = b[ai], loc[ai]
+    view = rays[ids[ai] >> ch.kbits, 3:6]
+    order_a, cnt_a = _route(b_a, division[0] * division[1])
+    send_a, dest_a, counts_a = ch.route(1, division)
+    assert counts_a == cnt_a and sum(counts_a) == ch.num_app > 10000
+    assert torch.equal(send_a, torch.cat([loc_a, view], dim=1)[order_a])
+    inv_a = torch.empty_like(order_a)
+    inv_a[order_a] = torch.arange(order_a.numel(), device=order_a.device)
+    assert torch.equal(dest_a.to(torch.int64), inv_a)
+
+
 def test_point_mode_entries_match_list_mode():
     """gnr_density_points / gnr_appearance_points on explicit coordinates give what the list-mode
     stages give for the same samples."""
