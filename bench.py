@@ -209,6 +209,9 @@ def main():
     ap.add_argument("--ert", type=float, default=2e-5,
                     help="early ray termination threshold of the density pass (rgb error bound); 0 = exact, "
                          "-1 = separate density and weights kernels")
+    ap.add_argument("--no-model-parallel", action="store_true",
+                    help="N > 1: skip the block-partitioned and channel-parallel renders of the same frame")
+    ap.add_argument("--chunk-model-parallel", type=int, default=65536, help="rays per exchange of the model-parallel renderers")
     ap.add_argument("--no-variants", action="store_true", help="skip the extra configurations (literal scene, T < 1e-3, mlp_mode 1, ...)")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
     ap.add_argument("--streams", type=int, default=2, help="streams the chunks of a frame rotate over")
@@ -567,6 +570,26 @@ def main():
     tot = torch.tensor([float(stats[2]), float(stats[3]), float(n_local), float(stats[5])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(tot)
+    # ---- the two model-parallel layouts of the same frame on these N GPUs, a few frames each: the field cut
+    # into N spatial blocks (samples routed to their owners by all-to-all) and the appearance channels split
+    # N ways (partial projections reduce-scattered).  Every rank takes part. ----------------------------------
+    model_parallel = None
+    if world > 1 and not a.no_model_parallel:
+        from landmark_b200.model_parallel_run import run as run_model_parallel
+
+        del model, shard, rays, rgb, depth, image
+        torch.cuda.empty_cache()
+        model_parallel = {}
+        for wl in ("city_blocks", "city_channels"):
+            try:
+                res = run_model_parallel(wl, 3, 1, a.chunk_model_parallel, a.mlp_mode, rank, world, device, 1, False, ert=a.ert,
+                                         app_fp16=bool(a.app_fp16), den_lattice=bool(a.den_lattice))
+                model_parallel[wl] = {"ms_per_frame": res["ms_per_frame"], "Mrays_per_s": res["rays"] / (res["ms_per_frame"] * 1e-3) / 1e6,
+                                      "parallelism": res["parallelism"], "valid_samples": res["valid"],
+                                      "appearance_samples": res["appearance"], "steps": 3, "warmup": 1}
+            except RuntimeError as exc:  # reported, never fatal for the headline line
+                model_parallel[wl] = {"failed": str(exc).splitlines()[0][:300]}
+            torch.cuda.empty_cache()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -679,6 +702,8 @@ def main():
         line["strict_fp32"] = strict
     if variants is not None:
         line["variants"] = variants
+    if model_parallel is not None:
+        line["model_parallel"] = model_parallel
     if cpu_sd is not None:
         from oracle import gridnerf_oracle as orc
 

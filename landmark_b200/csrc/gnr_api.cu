@@ -972,7 +972,10 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   if (gnr_app_fusable(m)) {
     // gather + basis projection + MLP as one kernel: no operand of a sample leaves the SM
     StageScope sc(m, GNR_STAGE_MLP, 1, st);
-    GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, gnr_coords_app(rays, ws, L), (float*)(ws + L.app_rgb), (int32_t*)(ws + L.status), st));
+    if (m->cfg.unfused_appearance == 2 && !m->debug_prof)
+      GNR_LAUNCH_OK(launch_app_mlp_stream(m, p, gnr_coords_app(rays, ws, L), (float*)(ws + L.app_rgb), (int32_t*)(ws + L.status), st));
+    else
+      GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, gnr_coords_app(rays, ws, L), (float*)(ws + L.app_rgb), (int32_t*)(ws + L.status), st));
   } else {
     {
       StageScope sc(m, GNR_STAGE_APP_GATHER, 1, st);

@@ -496,7 +496,7 @@ void gnr_fused_k1_order(int* map) {
 int gnr_app_fusable(const GnrModel* m) {
   // fp16 appearance planes of 48 (padded) channels, the single-fp16 tensor-core mode, and a product count
   // that fits the 80 operand columns
-  return m->cfg.mlp_mode == 2 && m->cfg.app_storage == 1 && m->cfg.unfused_appearance == 0 && gnr_tc_basis_fused(m) &&
+  return m->cfg.mlp_mode == 2 && m->cfg.app_storage == 1 && m->cfg.unfused_appearance != 1 && gnr_tc_basis_fused(m) &&
          m->app[0].C == 48 && m->mlp.n_prod == m->cfg.n_pairs * 48 && m->mlp.n_prod <= MAX_K0;
 }
 

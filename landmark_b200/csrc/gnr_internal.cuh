@@ -165,6 +165,9 @@ int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCo
                         unsigned char* prod_lo, int tile_bytes, int terms, cudaStream_t st);
 // gather + basis + MLP in one kernel (gnr_app_fused.cu): 1 if this model can run it
 int gnr_app_fusable(const GnrModel* m);
+// the same work with dedicated gather warps feeding the MLP warps through tensor memory (gnr_app_stream.cu)
+int launch_app_mlp_stream(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
+                          cudaStream_t st);
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
                          cudaStream_t st);
 void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)

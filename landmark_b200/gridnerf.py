@@ -171,7 +171,7 @@ class B200GridNeRF(torch.nn.Module):
         self.density_lattice = bool(density_lattice)
         # forward() runs appearance gather + basis projection + MLP as one kernel when the library can
         # (mlp_mode 2 with fp16 appearance planes); False keeps the separate kernels (GnrConfig.unfused_appearance)
-        self.fused_appearance = bool(fused_appearance)
+        self.fused_appearance = fused_appearance if fused_appearance in ("stream", "groups") else bool(fused_appearance)
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -308,7 +308,9 @@ class B200GridNeRF(torch.nn.Module):
         cfg.ert_transmittance = self.ert_transmittance
         cfg.app_storage = 1 if self.app_plane_fp16 else 0
         cfg.den_storage = 1 if self.density_plane_fp16 else 0
-        cfg.unfused_appearance = 0 if self.fused_appearance else 1
+        # True / "groups": two groups of warps that each gather and run the MLP of their tile; "stream": gather warps
+        # feed MLP warps through tensor memory; False: separate kernels
+        cfg.unfused_appearance = {True: 0, "groups": 0, "stream": 2, False: 1}[self.fused_appearance]
         return cfg
 
     def commit(self, release_torch_planes: bool = False):

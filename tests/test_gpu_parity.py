@@ -660,12 +660,13 @@ def test_density_lattice_needs_the_standard_layout():
         m.commit()
 
 
-def _fused_pair(spec, ckpt=None, args=None, sd=None, kwargs=None):
-    """The same scene as two models: appearance as one kernel, and as the separate gather and MLP kernels."""
+def _fused_models(spec, ckpt=None, args=None, sd=None, kwargs=None):
+    """The same scene as three models: appearance as one kernel in its two forms (gather warps feeding MLP
+    warps; two groups that each gather and run the MLP), and as the separate gather and MLP kernels."""
     from landmark_b200.gridnerf import B200GridNeRF
 
     out = []
-    for fused in (True, False):
+    for fused in ("stream", "groups", False):
         if sd is None:
             out.append(cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused))
         else:
@@ -677,54 +678,52 @@ def _fused_pair(spec, ckpt=None, args=None, sd=None, kwargs=None):
 
 
 def test_fused_appearance_kernel_equals_separate_kernels():
-    """gather + basis projection + MLP in one kernel (operands in tensor memory) against the separate
-    gather and MLP kernels: the same products, the same GEMMs in the same K order, so the colours agree
-    to a few 1e-6 (the fused kernel sums layer 1 in another K order and takes the view direction as fp32);
-    both stay within 1e-4 of the reference fixture.  Also with a black background, on the nine-tap
-    general layout, and on a chunk whose appearance list does not fill a tile."""
+    """gather + basis projection + MLP in one kernel (operands in tensor memory), in both of its forms,
+    against the separate gather and MLP kernels: the same products and the same GEMMs, so the colours agree
+    to a few 1e-6 (the fused kernels sum layer 1 in another K order and take the view direction as fp32);
+    all stay within 1e-4 of the reference fixture.  Also with a black background, on the general pair
+    layout, on a chunk whose appearance list does not fill a tile, and on lists of 1..7 tiles (the
+    producer / consumer form rotates three operand buffers and two accumulator slots)."""
     spec = scenes.tiny_spec().lit()
     fx = load_golden("tiny_lit.npz")
     ckpt = scenes.make_checkpoint(spec)
     rays = torch.from_numpy(fx["rays"]).cuda()
-    fused, split = _fused_pair(spec, ckpt)
-    for white in (True, False):
-        a, _ = fused(rays, white_bg=white, N_samples=spec.n_samples)
-        b, _ = split(rays, white_bg=white, N_samples=spec.n_samples)
-        assert int(fused.last_status[3]) == int(split.last_status[3]) > 10000
-        assert torch.equal(a["depth_map"], b["depth_map"])
-        assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
-    a, _ = fused(rays, N_samples=spec.n_samples)
-    err = (a["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
-    assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
-    few = rays[5000:5003].contiguous()  # a handful of appearance samples: one partial tile
-    a, _ = fused(few, N_samples=spec.n_samples)
-    b, _ = split(few, N_samples=spec.n_samples)
-    assert 0 < int(fused.last_status[3]) < 128 * 3
-    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
+    stream, groups, split = _fused_models(spec, ckpt)
+    for fused in (stream, groups):
+        for white in (True, False):
+            a, _ = fused(rays, white_bg=white, N_samples=spec.n_samples)
+            b, _ = split(rays, white_bg=white, N_samples=spec.n_samples)
+            assert int(fused.last_status[3]) == int(split.last_status[3]) > 10000
+            assert torch.equal(a["depth_map"], b["depth_map"])
+            assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
+        a, _ = fused(rays, N_samples=spec.n_samples)
+        err = (a["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+        assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL
+        for lo, hi in ((5000, 5003), (5000, 5010), (5000, 5030), (4000, 4100)):  # a few tiles per CTA at most
+            few = rays[lo:hi].contiguous()
+            a, _ = fused(few, N_samples=spec.n_samples)
+            b, _ = split(few, N_samples=spec.n_samples)
+            assert int(fused.last_status[3]) > 0
+            assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5, (lo, hi)
+    a, _ = stream(rays, N_samples=spec.n_samples)
+    b, _ = groups(rays, N_samples=spec.n_samples)
+    assert torch.equal(a["rgb_map"], b["rgb_map"])  # the two fused forms run the same arithmetic in the same order
     # three pairs that are not the standard VM layout (general branch of the fused gather)
-    spec2 = scenes.tiny_spec(grid=32).lit()
+    spec2 = scenes.tiny_spec(height=40, width=40, n_samples=64, grid=32).lit()
+    sd = scenes.multires_state_dict(spec2)
     args = scenes.model_args(spec2)
     args.ndims, args.resMode = 1, [1, 2, 4]
-    g = torch.Generator().manual_seed(11)
-    sd = {}
-    for j, r in enumerate([1, 2, 4]):
-        sd[f"density_plane.{j}"] = 0.1 * torch.randn((1, 16, 32 * r, 32 * r), generator=g)
-        sd[f"density_line.{j}"] = 0.1 * torch.randn((1, 16, 32 * r, 1), generator=g)
-        sd[f"app_plane.{j}"] = 0.1 * torch.randn((1, 48, 32 * r, 32 * r), generator=g)
-        sd[f"app_line.{j}"] = 0.1 * torch.randn((1, 48, 32 * r, 1), generator=g)
-    base = scenes.make_state_dict(spec2)
-    sd.update({k: v for k, v in base.items() if k.startswith(("renderModule", "basis_mat"))})
     kwargs = scenes.model_kwargs(spec2)
-    kwargs["density_shift"] = 0.0
-    fused2, split2 = _fused_pair(spec2, args=args, sd=sd, kwargs=kwargs)
-    r2 = tiny_rays(scenes.tiny_spec(height=40, width=40)).cuda()
-    a, _ = fused2(r2, N_samples=64)
+    stream2, groups2, split2 = _fused_models(spec2, args=args, sd=sd, kwargs=kwargs)
+    r2 = tiny_rays(spec2).cuda()
     b, _ = split2(r2, N_samples=64)
-    assert int(fused2.last_status[3]) > 1000
-    assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
+    for fused in (stream2, groups2):
+        a, _ = fused(r2, N_samples=64)
+        assert int(fused.last_status[3]) > 1000
+        assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
 
 
-@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("fused", ["stream", "groups", False])
 def test_bounded_wait_expires_and_the_context_survives(fused):
     """The tensor-core kernels bound every wait on an mbarrier.  The test hook makes one group skip the
     step its next wait depends on, with a short poll limit: the wait runs out, the kernel reports it in
