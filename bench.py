@@ -729,12 +729,14 @@ def main():
             chunk_t = 8192  # the reference's render_batch_size
             orc.render_rays(gfield, gs[:chunk_t], S, True, chunk=chunk_t)
             torch.cuda.synchronize()
-            c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            c0.record()
-            g_rgb, _ = orc.render_rays(gfield, gs, S, True, chunk=chunk_t)
-            c1.record()
-            torch.cuda.synchronize()
-            ms_t = c0.elapsed_time(c1)
+            ms_t = float("inf")
+            for _ in range(2):  # best of two passes (the first still grows torch's allocator pools)
+                c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                c0.record()
+                g_rgb, _ = orc.render_rays(gfield, gs, S, True, chunk=chunk_t)
+                c1.record()
+                torch.cuda.synchronize()
+                ms_t = min(ms_t, c0.elapsed_time(c1))
             errg = (got["rgb_map"] - g_rgb).abs().max(dim=1).values
             line["torch_cuda_baseline"] = {"value": CPU_SAMPLE_RAYS / (ms_t * 1e-3) / 1e6, "unit": "Mrays/s",
                                            "ms_per_frame_extrapolated": ms_t * H * W / CPU_SAMPLE_RAYS,

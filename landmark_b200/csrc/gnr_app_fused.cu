@@ -38,8 +38,6 @@
 // Every wait on an mbarrier is bounded; when one expires the group raises
 // status[GNR_ST_WAIT_EXPIRED] and stops taking tiles; before the CTA frees its tensor memory a
 // group that stopped commits once more and waits (bounded) so that none of its MMAs is in flight.
-#include <type_traits>
-
 #include "gnr_gather.cuh"
 #include "gnr_tc.cuh"
 
@@ -72,7 +70,7 @@ struct RaySample {  // what a row needs of its list entry
   int k;
 };
 
-template <int NP, bool PROF, bool PIPE>
+template <int NP, bool PROF>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
@@ -184,80 +182,62 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   }
   if (PROF && prof_on) plast = clock64();
 
-  // ---- gather ----------------------------------------------------------------------------------------------
-  // PIPE == false (what runs): a tile starts with its gather; the five rounds of a thread are independent,
-  // so their loads overlap.  PIPE == true: the rounds of a group's NEXT tile are gathered into registers
-  // in the shadows of the current tile's MMAs (one round behind the projection, two behind each hidden
-  // layer) and a tile starts by storing them; measured slower (19.6 against 17.6 ms per frame): spread
-  // out like that a round has only its own six loads in flight.
-  uint32_t nq[5][8];  // half 0 holds rounds 0..4, half 1 rounds 5..8 (index = round - 5 half)
-  RaySample gs = {};  // the sample being gathered
-  float gx = 0.0f, gy = 0.0f, gz = 0.0f;
-  auto position_of = [&](const RaySample& r) {
-    // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
-    const float t = gnr_sample_t(p, r.t_min, r.k);
-    gx = gnr_normalize(gnr_point(r.o[0], r.d[0], t), p.lo[0], p.inv[0]);
-    gy = gnr_normalize(gnr_point(r.o[1], r.d[1], t), p.lo[1], p.inv[1]);
-    gz = gnr_normalize(gnr_point(r.o[2], r.d[2], t), p.lo[2], p.inv[2]);
-  };
-  auto taps_of = [&](int pi) -> PairTapsH2 {
-    const GnrPlane& pl = planes.p[pi];
-    if (NP == 3) {
-      const Tap tx = make_tap(gx, planes.p[0].fw, planes.p[0].W);
-      const Tap ty = make_tap(gy, planes.p[0].fh, planes.p[0].H);
-      const Tap tz = make_tap(gz, planes.p[0].fl, planes.p[0].L);
-      return pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
-    }
-    const float u = pick(gx, gy, gz, pl.mat0), v = pick(gx, gy, gz, pl.mat1), l = pick(gx, gy, gz, pl.vec);
-    return make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
-  };
-  // local round i of this half: global round r = i + 5 half = 3 pair + g, columns 8 r .. 8 r + 7 of A0
-  auto gather_local = [&](auto idx_c) {
-    constexpr int i = decltype(idx_c)::value;
-    const int r = i + 5 * half, pi = r / 3, g = r - 3 * pi;  // (warp-uniform)
-    if (r >= 9) return;
-    if (pi < planes.n) {
-      const PairTapsH2 t_pair = taps_of(pi);
-      pair_round_h2(planes.p[pi], t_pair, g, nq[i]);
-    } else {  // fewer than three pairs: these columns are zero
-#pragma unroll
-      for (int e = 0; e < 8; ++e) nq[i][e] = 0u;
-    }
-  };
-  using I0 = std::integral_constant<int, 0>;
-  using I1 = std::integral_constant<int, 1>;
-  using I2 = std::integral_constant<int, 2>;
-  using I3 = std::integral_constant<int, 3>;
-  using I4 = std::integral_constant<int, 4>;
-  if (PIPE && t_beg + slot < t_end) {  // prologue: the first tile's rounds
-    position_of(next_ray);
-    gather_local(I0{});
-    gather_local(I1{});
-    gather_local(I2{});
-    gather_local(I3{});
-    gather_local(I4{});
-  }
-
   for (long long tile = t_beg + slot; tile < t_end; tile += FG) {
     const long long j = tile * ROWS + row;
     const bool live = j < total;
-    const bool has_next = tile + FG < t_end;  // (the same for every thread of the group)
     const RaySample cur = next_ray;
-    if (has_next) next_ray = load_ray(id_ahead);              // (not needed before the gather slots below)
+    if (tile + FG < t_end) next_ray = load_ray(id_ahead);              // (not needed before the next iteration)
     if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
 
-    // ---- this tile's products: (gather,) registers -> tensor memory ---------------------------------------
-    if (!PIPE) {
-      position_of(cur);
-      gather_local(I0{});
-      gather_local(I1{});
-      gather_local(I2{});
-      gather_local(I3{});
-      gather_local(I4{});
-    }
+    // ---- gather: this half's rounds of products -> tensor memory ------------------------------------------
+    // (Gathering a group's NEXT tile into registers in the shadows of the current tile's GEMMs instead was
+    // measured slower, 19.6 against 17.6 ms per frame: the GEMMs fetch their weights through the same
+    // L1 / shared-memory port the gather saturates, so the two do not overlap.)
+    {
+      // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
+      const float t = gnr_sample_t(p, cur.t_min, cur.k);
+      const float x = gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
+      const float y = gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
+      const float z = gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
+      auto taps_of = [&](int pi) -> PairTapsH2 {
+        const GnrPlane& pl = planes.p[pi];
+        if (NP == 3) {
+          const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+          const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+          const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+          return pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
+        }
+        const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+        return make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
+      };
+      auto do_round = [&](int r, const PairTapsH2& t_pair) {  // r is a compile-time constant after inlining
+        const int pi = r / 3, g = r - 3 * pi;
+        uint32_t q[8];
+        if (pi < planes.n) {
+          pair_round_h2(planes.p[pi], t_pair, g, q);
+        } else {  // fewer than three pairs: these columns are zero
 #pragma unroll
-    for (int i = 0; i < 5; ++i) {
-      if (i + 5 * half < 9) tmem_st8(a_tmem + lane_off + (i + 5 * half) * 8, nq[i]);
+          for (int e = 0; e < 8; ++e) q[e] = 0u;
+        }
+        tmem_st8(a_tmem + lane_off + r * 8, q);
+      };
+      // round r = 3 pair + g fills columns 8 r .. 8 r + 7; half 0 takes rounds 0..4, half 1 rounds 5..8
+      if (half == 0) {  // (warp-uniform)
+        const PairTapsH2 t0 = taps_of(0);
+        do_round(0, t0);
+        do_round(1, t0);
+        do_round(2, t0);
+        const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
+        do_round(3, t1);
+        do_round(4, t1);
+      } else {
+        const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
+        do_round(5, t1);
+        const PairTapsH2 t2 = taps_of(planes.n > 2 ? 2 : 0);
+        do_round(6, t2);
+        do_round(7, t2);
+        do_round(8, t2);
+      }
     }
     tmem_st_wait();
     tc_fence_before();
@@ -278,10 +258,6 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       __syncwarp();
     }
     PROF_MARK(1);
-    if (PIPE && has_next) {  // gather slot behind the projection
-      position_of(next_ray);
-      gather_local(I0{});
-    }
     WAIT_OR_STOP();
     PROF_MARK(2);
 
@@ -349,10 +325,6 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       __syncwarp();
     }
     PROF_MARK(4);
-    if (PIPE && has_next) {  // gather slot behind layer 1
-      gather_local(I1{});
-      gather_local(I2{});
-    }
     WAIT_OR_STOP();
     PROF_MARK(5);
 
@@ -387,10 +359,6 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       __syncwarp();
     }
     PROF_MARK(7);
-    if (PIPE && has_next) {  // gather slot behind layer 2
-      gather_local(I3{});
-      gather_local(I4{});
-    }
     WAIT_OR_STOP();
     PROF_MARK(8);
 
@@ -532,8 +500,8 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     return 0;
   };
   int rc;
-  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false>) : launch(app_mlp_fused_kernel<0, true, false>);
-  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false>) : launch(app_mlp_fused_kernel<0, false, false>);
+  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true>) : launch(app_mlp_fused_kernel<0, true>);
+  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false>) : launch(app_mlp_fused_kernel<0, false>);
   if (rc) return rc;
   return (int)cudaGetLastError();
 }
