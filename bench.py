@@ -211,7 +211,7 @@ def main():
                          "-1 = separate density and weights kernels")
     ap.add_argument("--no-model-parallel", action="store_true",
                     help="N > 1: skip the block-partitioned and channel-parallel renders of the same frame")
-    ap.add_argument("--chunk-model-parallel", type=int, default=65536, help="rays per exchange of the model-parallel renderers")
+    ap.add_argument("--chunk-model-parallel", type=int, default=262144, help="rays per exchange of the model-parallel renderers")
     ap.add_argument("--no-variants", action="store_true", help="skip the extra configurations (literal scene, T < 1e-3, mlp_mode 1, ...)")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
     ap.add_argument("--streams", type=int, default=2, help="streams the chunks of a frame rotate over")
@@ -586,7 +586,8 @@ def main():
                                          app_fp16=bool(a.app_fp16), den_lattice=bool(a.den_lattice))
                 model_parallel[wl] = {"ms_per_frame": res["ms_per_frame"], "Mrays_per_s": res["rays"] / (res["ms_per_frame"] * 1e-3) / 1e6,
                                       "parallelism": res["parallelism"], "valid_samples": res["valid"],
-                                      "appearance_samples": res["appearance"], "steps": 3, "warmup": 1}
+                                      "appearance_samples": res["appearance"], "steps": 3, "warmup": 1,
+                                      "chunks_per_rank": res["chunks_per_rank"], "sections_ms_rank0": res["sections_ms"]}
             except RuntimeError as exc:  # reported, never fatal for the headline line
                 model_parallel[wl] = {"failed": str(exc).splitlines()[0][:300]}
             torch.cuda.empty_cache()

@@ -1163,6 +1163,11 @@ extern "C" int gnr_appearance_points(GnrModel* m, const float* xyz, const float*
   GnrSampleParams p = gnr_sample_params(m, 1);
   const GnrCoords c = coords_points(xyz, view, n);
   GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+  if (!features && gnr_app_fusable(m)) {
+    // gather + basis projection + MLP as one kernel, the points' operands never leaving the SM
+    GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, c, rgb, (int32_t*)(sc + S.status), st));
+    return 0;
+  }
   const int fused = m->cfg.mlp_mode != 0 && gnr_tc_basis_fused(m);
   if (fused) {
     unsigned char* hi = (unsigned char*)(sc + S.prod);

@@ -53,8 +53,11 @@ struct FusedArgs {
   const float* rays;             // [n][6]
   const float* t_min;            // [n]
   const uint32_t* ids;           // appearance list: ray << kbits | sample
-  const int32_t* total_ptr;      // length of the list (device)
+  const int32_t* total_ptr;      // length of the list (device), or null ...
+  long long total_direct;        // ... then this host count (point mode)
   long long capacity;
+  const float* xyz_direct;       // point mode: [n][3] normalised positions
+  const float* view_direct;      // point mode: [n][3] view directions
   const unsigned char* w_image;  // [basis][W1][W2][W3][W1 with permuted K] fp16 operand images
   const float* b3;
   float* rgb_out;
@@ -70,7 +73,7 @@ struct RaySample {  // what a row needs of its list entry
   int k;
 };
 
-template <int NP, bool PROF>
+template <int NP, bool PROF, bool POINTS>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
@@ -124,7 +127,7 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   uint32_t parity = 0;
   bool expired = false;
 
-  const long long total = min((long long)*a.total_ptr, a.capacity);
+  const long long total = min(a.total_ptr ? (long long)*a.total_ptr : a.total_direct, a.capacity);
   const long long n_tiles = (total + ROWS - 1) / ROWS;
   // a contiguous share of the list per CTA (neighbouring tiles are neighbouring rays: their texels
   // are still in this SM's L1), the two groups taking alternate tiles of it
@@ -158,10 +161,25 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   // instructions) and write nothing
   auto entry_of = [&](long long t) -> uint32_t {
     const long long jr = t * ROWS + row;
-    return __ldg(a.ids + (jr < total ? jr : total - 1));
+    const long long at = jr < total ? jr : total - 1;
+    if (POINTS) return (uint32_t)at;  // point mode: the "entry" is the point's own number
+    return __ldg(a.ids + at);
   };
   auto load_ray = [&](uint32_t id) -> RaySample {
     RaySample r;
+    if (POINTS) {  // o = the normalised position itself, d = the view direction
+      const float* px = a.xyz_direct + (size_t)id * 3;
+      const float* pv = a.view_direct + (size_t)id * 3;
+      r.o[0] = __ldg(px + 0);
+      r.o[1] = __ldg(px + 1);
+      r.o[2] = __ldg(px + 2);
+      r.d[0] = __ldg(pv + 0);
+      r.d[1] = __ldg(pv + 1);
+      r.d[2] = __ldg(pv + 2);
+      r.t_min = 0.0f;
+      r.k = 0;
+      return r;
+    }
     const uint32_t ray = id >> p.kbits;
     const float* src = a.rays + (size_t)ray * 6;
     r.o[0] = __ldg(src + 0);
@@ -195,10 +213,10 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     // L1 / shared-memory port the gather saturates, so the two do not overlap.)
     {
       // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
-      const float t = gnr_sample_t(p, cur.t_min, cur.k);
-      const float x = gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
-      const float y = gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
-      const float z = gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
+      const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
+      const float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
+      const float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
+      const float z = POINTS ? cur.o[2] : gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
       auto taps_of = [&](int pi) -> PairTapsH2 {
         const GnrPlane& pl = planes.p[pi];
         if (NP == 3) {
@@ -474,8 +492,9 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
   }
-  if (!c.ids || c.index || c.xyz_direct || !c.total_ptr) {
-    gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count)");
+  const bool points = c.xyz_direct != nullptr;
+  if (points ? (!c.view_direct) : (!c.ids || c.index || !c.total_ptr)) {
+    gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count) or explicit points with view directions");
     return -1;
   }
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
@@ -484,7 +503,10 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.t_min = c.t_min;
   a.ids = c.ids;
   a.total_ptr = c.total_ptr;
+  a.total_direct = c.total_direct;
   a.capacity = c.capacity;
+  a.xyz_direct = c.xyz_direct;
+  a.view_direct = c.view_direct;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
   a.b3 = m->mlp.b3;
   a.rgb_out = rgb;
@@ -500,8 +522,9 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     return 0;
   };
   int rc;
-  if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true>) : launch(app_mlp_fused_kernel<0, true>);
-  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false>) : launch(app_mlp_fused_kernel<0, false>);
+  if (points) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true>) : launch(app_mlp_fused_kernel<0, false, true>);
+  else if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false>) : launch(app_mlp_fused_kernel<0, true, false>);
+  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false>) : launch(app_mlp_fused_kernel<0, false, false>);
   if (rc) return rc;
   return (int)cudaGetLastError();
 }

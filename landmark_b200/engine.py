@@ -192,7 +192,8 @@ class NerfDDPRunner:
         self.img_cpu = torch.zeros((self.H, self.W, 4), dtype=torch.uint8)
         if torch.device(dev).type == "cuda":
             self.img_cpu = self.img_cpu.pin_memory()
-        self._msg = torch.zeros(14, dtype=torch.float32, device=dev)  # pose (12), focal, stop flag
+        # pose (12), focal, stop flag; float64 so that a double focal length reaches the other ranks unrounded
+        self._msg = torch.zeros(14, dtype=torch.float64, device=dev)
 
     # -- rank 0 <-> other ranks -------------------------------------------------------------------
     def _broadcast(self, pose: Optional[np.ndarray], focal: float, stop: bool):
@@ -201,14 +202,14 @@ class NerfDDPRunner:
         if self.world == 1:
             return pose, focal, stop
         if self.rank == 0:
-            m = np.zeros(14, dtype=np.float32)
+            m = np.zeros(14, dtype=np.float64)
             if pose is not None:
                 m[:12] = np.asarray(pose, dtype=np.float32)[:3, :4].reshape(-1)
             m[12], m[13] = focal, 1.0 if stop else 0.0
             self._msg.copy_(torch.from_numpy(m))
         dist.broadcast(self._msg, src=0, group=self.group)
         m = self._msg.cpu().numpy()
-        return m[:12].reshape(3, 4).copy(), float(m[12]), bool(m[13] > 0.5)
+        return m[:12].astype(np.float32).reshape(3, 4).copy(), float(m[12]), bool(m[13] > 0.5)
 
     def _focal_of(self, pose) -> float:
         pose = np.asarray(pose)

@@ -105,6 +105,35 @@ class LoopbackComm:
         return outs, rcs
 
 
+class SectionTimer:
+    """CUDA-event stopwatch for the sections of a model-parallel frame (off unless ``enabled``): ``mark(name)``
+    closes the section that started at the previous mark; ``collect()`` returns milliseconds per name."""
+
+    def __init__(self, enabled: bool = False):
+        self.enabled, self._events, self._last = enabled, [], None
+
+    def start(self):
+        if self.enabled:
+            self._last = torch.cuda.Event(enable_timing=True)
+            self._last.record()
+
+    def mark(self, name: str):
+        if self.enabled and self._last is not None:
+            e = torch.cuda.Event(enable_timing=True)
+            e.record()
+            self._events.append((name, self._last, e))
+            self._last = e
+
+    def collect(self) -> Dict[str, float]:
+        out: Dict[str, float] = {}
+        if self.enabled:
+            torch.cuda.synchronize()
+            for name, a, b in self._events:
+                out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+            self._events = []
+        return out
+
+
 # ----------------------------------------------------------------------------------------------
 # thin stage wrappers (no output copies, no host syncs except where a count is needed)
 # ----------------------------------------------------------------------------------------------
@@ -309,6 +338,7 @@ class ChannelParallelRenderer:
     def __init__(self, models: Sequence[B200GridNeRF], comm):
         assert len(models) == len(comm.local_ranks)
         self.models, self.comm = list(models), comm
+        self.timer = SectionTimer(False)
 
     RAY_GROUP = 1024  # rays are dealt to the ranks in groups of this many consecutive rays
 
@@ -331,6 +361,8 @@ class ChannelParallelRenderer:
         points, on which it runs the MLP and composites its own rays; the pixels are all-gathered."""
         W = self.comm.world
         chunks, shares, points = [], [], []
+        tm = self.timer
+        tm.start()
         for m, r, rank in zip(self.models, rays, self.comm.local_ranks):
             with torch.cuda.device(m.device):
                 share = self._ray_share(r.shape[0], rank, m.device)
@@ -342,7 +374,9 @@ class ChannelParallelRenderer:
                 else:
                     ch.density()
                     ch.weights()
+                tm.mark("sample + march (own rays)")
                 pts, _, _ = ch.route(1, (1, 1))  # one block: the appearance list as (point, view) rows in list order
+                tm.mark("appearance points")
                 chunks.append(ch)
                 shares.append(share)
                 points.append(pts)
@@ -355,17 +389,21 @@ class ChannelParallelRenderer:
                 buf[: ch.num_app] = pts
                 padded.append(buf)
         everyone = self.comm.all_gather_rows(padded)  # [W * per, 6], rank r's points in rows r * per ..
+        tm.mark("all-gather points")
         partial = []
         for ch, allp in zip(chunks, everyone):
             with torch.cuda.device(ch.m.device):
                 partial.append(app_features_points(ch.m, allp[:, :3].contiguous()))
+        tm.mark("partial projection (all points)")
         feats = self.comm.reduce_scatter_rows(partial)  # [per, app_dim]: the complete features of this rank's own points
+        tm.mark("reduce-scatter features")
         pix = []
         for ch, share, f, pts in zip(chunks, shares, feats, points):
             with torch.cuda.device(ch.m.device):
                 rgb_s = mlp_features(ch.m, f[: ch.num_app], pts[:, 3:6].contiguous())
                 rgb, depth = ch.composite(rgb_s, white_bg)
                 pix.append((rgb, depth))
+        tm.mark("MLP + composite (own rays)")
         # pixels of every rank -> every rank (padded to the largest share)
         n = rays[0].shape[0]
         per_rays = max(1, max(int(self._ray_share(n, r, "cpu").numel()) for r in range(W)))
@@ -389,6 +427,7 @@ class ChannelParallelRenderer:
                     rgb[share] = g[r * per_rays:r * per_rays + k, :3]
                     depth[share] = g[r * per_rays:r * per_rays + k, 3]
                 out.append((rgb, depth))
+        tm.mark("all-gather pixels")
         return out
 
 
@@ -434,41 +473,55 @@ class BlockParallelRenderer:
         if division[0] * division[1] != comm.world:
             raise ValueError(f"{division[0]}x{division[1]} blocks need {division[0] * division[1]} ranks, have {comm.world}")
         self.samplers, self.owners, self.comm, self.division = list(samplers), list(owners), comm, division
+        self.timer = SectionTimer(False)  # set ``timer.enabled`` to get a per-section breakdown of a frame
 
     @torch.no_grad()
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
         Returns per local rank ``(rgb_map, depth_map)`` of its own rays."""
         chunks, sends, dests, counts = [], [], [], []
+        tm = self.timer
+        tm.start()
         # ---- sample globally; block assignment + grouping by owner on the device; points travel to the owners
         for s_, r in zip(self.samplers, rays):
             with torch.cuda.device(s_.device):
                 ch = _Chunk(s_, r, n_samples)
                 ch.sample(keep_ids=False)
+                tm.mark("sample")
                 send, dest, cnt = ch.route(0, self.division)
+                tm.mark("route valid")
                 chunks.append(ch)
                 sends.append(send)
                 dests.append(dest)
                 counts.append(cnt)
         recv, rcounts = self.comm.all_to_all_rows(sends, counts)
+        tm.mark("all-to-all points")
         # ---- owners: density at the received points, values travel back -------------------------
         sig = [density_points(o, x) for o, x in zip(self.owners, recv)]
+        tm.mark("density at owners")
         back, _ = self.comm.all_to_all_rows(sig, rcounts)
+        tm.mark("all-to-all sigma")
         app_send, app_counts, app_dests = [], [], []
         for ch, dest, sg in zip(chunks, dests, back):
             with torch.cuda.device(ch.m.device):
                 ch.weights(sg, dest)  # answers -> list order, weights, appearance list
+                tm.mark("weights")
                 send, dest_a, cnt = ch.route(1, self.division)
+                tm.mark("route appearance")
                 app_send.append(send)
                 app_dests.append(dest_a)
                 app_counts.append(cnt)
         # ---- owners: colour at the received (position, view) pairs, values travel back ----------
         arecv, arcounts = self.comm.all_to_all_rows(app_send, app_counts)
+        tm.mark("all-to-all appearance points")
         rgb_o = [appearance_points(o, x[:, :3], x[:, 3:6]) for o, x in zip(self.owners, arecv)]
+        tm.mark("appearance at owners")
         rgb_back, _ = self.comm.all_to_all_rows(rgb_o, arcounts)
+        tm.mark("all-to-all rgb")
         out = []
         for ch, dest_a, rb in zip(chunks, app_dests, rgb_back):
             with torch.cuda.device(ch.m.device):
                 rgb_s = torch.index_select(rb, 0, dest_a) if ch.num_app else rb[:0]
                 out.append(ch.composite(rgb_s, white_bg))
+        tm.mark("composite")
         return out

@@ -154,13 +154,19 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
     if world > 1:
         dist.barrier()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=device, dtype=torch.float64)
+    # one more frame with a CUDA-event stopwatch around every section (rank 0's view; its extra events and the
+    # synchronisation at the end are why this frame is not part of the timed ones)
+    ren.timer.enabled = True
+    frame()
+    sections = {k: round(v, 3) for k, v in ren.timer.collect().items()}
+    ren.timer.enabled = False
     tot = torch.tensor([float(stats["valid"]), float(stats["app"])], device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         dist.all_reduce(tot)  # every rank sampled its own share of the rays (both layouts)
     res = {"ms_per_frame": float(ms.item()), "wall_ms_per_frame": (time.perf_counter() - t0) * 1e3 / steps,
            "valid": float(tot[0].item()), "appearance": float(tot[1].item()), "parallelism": parallelism,
-           "image_mean": float(image.mean().item()), "rays": H * W}
+           "image_mean": float(image.mean().item()), "rays": H * W, "sections_ms": sections, "chunks_per_rank": n_chunks}
     if check and workload == "city_blocks" and rank == 0 and world > 1:
         # rank 0 re-renders its own rays with every block held locally (loopback); the bits must agree
         _, _, s_all, o_all, division = build_blocks(world, list(range(world)), device, mlp_mode, grid_scale, **extra)

@@ -62,7 +62,7 @@ def _block_scene(division, grid=32, seed0=100):
     return gspec, gck, blocks
 
 
-@pytest.mark.parametrize("division,mlp_mode", [((2, 1), 0), ((2, 2), 2)])
+@pytest.mark.parametrize("division,mlp_mode", [((2, 1), 0), ((2, 2), 2), ((2, 2), "bench")])
 def test_block_parallel_matches_oracle(division, mlp_mode):
     from landmark_b200.gridnerf import B200GridNeRF
     from landmark_b200.model_parallel import BlockParallelRenderer, LoopbackComm
@@ -84,7 +84,10 @@ def test_block_parallel_matches_oracle(division, mlp_mode):
         s = B200GridNeRF(**kw, mlp_mode=0, field_grid=(2, 2, 2))
         s.load({k: v for k, v in gck.items() if k != "state_dict"} | {"state_dict": {}})
         samplers.append(s)
-        owners.append(cuda_model(blocks[r][0], blocks[r][1], mlp_mode=mlp_mode))
+        if mlp_mode == "bench":  # what the benchmark's owners run: density lattice, fused appearance kernel in point mode
+            owners.append(cuda_model(blocks[r][0], blocks[r][1], mlp_mode=2, app_plane_fp16=True, density_lattice=True))
+        else:
+            owners.append(cuda_model(blocks[r][0], blocks[r][1], mlp_mode=mlp_mode))
     ren = BlockParallelRenderer(samplers, owners, LoopbackComm(world), division)
     # data parallel over rays: rank r renders rows r, r + world, ...
     parts = [torch.arange(r, rays.shape[0], world) for r in range(world)]
@@ -182,6 +185,13 @@ def test_point_mode_entries_match_list_mode():
         ai = got["app_index"]
         rgb = appearance_points(model, xyz[ai], rays[ray[ai], 3:6])
         assert torch.equal(rgb, got["rgb_samples"])
+    # fp16 appearance planes: point mode runs the one-kernel form (gather + basis + MLP), list-mode stages the
+    # separate kernels; same products and GEMMs, another K order in layer 1
+    model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True)
+    got = model.run_stages(rays, spec.n_samples, True)
+    ai = got["app_index"]
+    rgb = appearance_points(model, xyz[ai], rays[ray[ai], 3:6])
+    assert (rgb - got["rgb_samples"]).abs().max().item() <= 1e-5
 
 
 def test_block_renderer_from_merged_stack_checkpoint():
