@@ -549,6 +549,16 @@ def main():
                 fused_appearance=False)
         measure("density_from_planes", "density from the three plane x line pairs instead of the pre-summed lattice",
                 density_lattice=False)
+        # the baked appearance lattice takes 69 GB next to its own chunk scratch: the headline model's scratch
+        # buffers go back to the allocator first (they are made again when that model renders next)
+        model.release_workspaces()
+        free_b, _ = torch.cuda.mem_get_info(device)
+        if free_b > 125e9:
+            measure("appearance_lattice", "appearance features from a baked lattice (27 projected features as 32 fp16 channels per "
+                    "grid point, 69 GB): 8 taps per sample, no plane gather, no projection GEMM; a trade of memory for time, opt-in",
+                    appearance_lattice=True)
+        else:
+            variants["appearance_lattice"] = {"skipped": f"{free_b / 1e9:.0f} GB of device memory free, 125 GB needed"}
 
     l1_measured = None
     if world == 1:

@@ -133,6 +133,20 @@ int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1, const flo
  * with the planes (x,y), (x,z), (y,z) of one grid; refused otherwise. */
 int gnr_build_density_lattice(GnrModel* m, int enable, void* stream);
 
+/* Optional projected-feature lattice of the appearance field ("baked" appearance).  compute_appfeature
+ * (app/models/gridnerf_sequential.py:829-871) is basis_mat applied to the plane x line products, and every
+ * product is trilinear in the position, so the 27 projected features are the trilinear interpolation of
+ * their values at the eight surrounding grid points.  With ``enable`` != 0 this builds those values on the
+ * device (32 fp16 channels = 64 bytes per grid point: 69 GB for 2048x2048x256, refused if the device has
+ * not that much free) from the appearance planes, lines and basis matrix uploaded so far, and
+ * gnr_render_chunk / gnr_appearance_points then run the one-kernel appearance path without a plane
+ * gather and without the projection GEMM: a sample reads 8 x 64 bytes.  Against the plane path the
+ * features carry one fp16 rounding per lattice value instead of one per product.  An upload of an
+ * appearance plane or line, or of the MLP, makes the lattice stale (launches refused until rebuilt).
+ * Needs mlp_mode 2, three pairs in the standard layout, 33..48 appearance channels.  A trade of memory
+ * for time, off by default; the stage-wise entries keep reading the planes. */
+int gnr_build_appearance_lattice(GnrModel* m, int enable, void* stream);
+
 /* Tables of the hull sampler for ``n_samples`` (= n_importance) samples per ray:
  * ``u[k] = torch.linspace(0, 1, n_samples)[k]`` and ``near_term[k] = near * (1.0 - u[k])``, both
  * evaluated by torch on the CPU so that ``z = near_term[k] + far * u[k]`` has the reference's bits

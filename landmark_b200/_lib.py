@@ -64,6 +64,7 @@ SIGNATURES = {
     "gnr_upload_alpha_mask": (_INT, [_P, _P, _INT, _INT, _INT, C.POINTER(C.c_float), C.POINTER(C.c_float), _P]),
     "gnr_upload_mlp": (_INT, [_P, _P, _P, _P, _P, _P, _P, _P, _P]),
     "gnr_build_density_lattice": (_INT, [_P, _INT, _P]),
+    "gnr_build_appearance_lattice": (_INT, [_P, _INT, _P]),
     "gnr_upload_hull_tables": (_INT, [_P, _INT, _P, _P, _P]),
     "gnr_generate_rays": (_INT, [C.POINTER(C.c_float), _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),
     "gnr_generate_rays_dev": (_INT, [_P, _P, _P, _INT, _INT, _P, _I64, _I64, _P, _P]),

@@ -257,6 +257,8 @@ extern "C" int gnr_destroy(GnrModel* m) {
     free_dev(m->app_line_buf[i]);
   }
   free_dev(m->den_lattice);
+  free_dev(m->app_lattice);
+  free_dev(m->mlp.basis_raw);
   free_dev(m->debug_prof);
   free_dev(m->route_scratch);
   free_dev(m->alpha_bits);
@@ -328,6 +330,7 @@ extern "C" int gnr_upload_plane(GnrModel* m, int kind, int idx, const float* src
     to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, P);
   GNR_CUDA_OK(cudaGetLastError());
   if (kind == 0) m->lat_valid = 0;  // a lattice built from the previous planes no longer describes the field
+  if (kind == 1) m->app_lat_valid = 0;
   pl->plane = *buf;
   pl->H = H;
   pl->W = W;
@@ -374,6 +377,7 @@ extern "C" int gnr_upload_line(GnrModel* m, int kind, int idx, const float* src,
     to_channel_last_kernel<<<grid, block, 0, (cudaStream_t)stream>>>(src, *buf, C, Cp, (long long)Ln);
   GNR_CUDA_OK(cudaGetLastError());
   if (kind == 0) m->lat_valid = 0;
+  if (kind == 1) m->app_lat_valid = 0;
   pl->line = *buf;
   pl->L = Ln;
   pl->fl = (float)(Ln - 1);
@@ -500,6 +504,9 @@ extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1
   GnrMlp& q = m->mlp;
   const int Hd = m->cfg.hidden, J = padded_channels(m->cfg.n_app) / 16;
   const int n_basis = m->cfg.n_pairs * 4 * (4 * J * 28 + 8);
+  free_dev(q.basis_raw);
+  q.basis_raw = nullptr;
+  m->app_lat_valid = 0;  // the lattice bakes the basis matrix in
   free_dev(q.basis_blocked);
   free_dev(q.w1t);
   free_dev(q.w2t);
@@ -508,6 +515,11 @@ extern "C" int gnr_upload_mlp(GnrModel* m, const float* basis_w, const float* w1
   free_dev(q.b2);
   free_dev(q.b3);
   q.basis_blocked = q.w1t = q.w2t = q.w3 = q.b1 = q.b2 = q.b3 = nullptr;
+  {
+    const size_t raw = (size_t)m->cfg.app_dim * m->cfg.n_pairs * m->cfg.n_app * sizeof(float);
+    GNR_CUDA_OK(cudaMalloc(&q.basis_raw, raw));
+    GNR_CUDA_OK(cudaMemcpyAsync(q.basis_raw, basis_w, raw, cudaMemcpyDeviceToDevice, st));
+  }
   GNR_CUDA_OK(cudaMalloc(&q.basis_blocked, (size_t)n_basis * sizeof(float)));
   GNR_CUDA_OK(cudaMalloc(&q.w1t, (size_t)q.k1_pad * Hd * sizeof(float)));
   GNR_CUDA_OK(cudaMalloc(&q.w2t, (size_t)Hd * Hd * sizeof(float)));
@@ -558,6 +570,51 @@ extern "C" int gnr_build_density_lattice(GnrModel* m, int enable, void* stream) 
   for (int a = 0; a < 3; ++a) m->lat_dims[a] = dims[a];
   GNR_LAUNCH_OK(launch_build_lattice(m, m->den_lattice, (cudaStream_t)stream));
   m->lat_valid = 1;
+  return 0;
+}
+
+extern "C" int gnr_build_appearance_lattice(GnrModel* m, int enable, void* stream) {
+  if (!m) {
+    gnr_set_error("gnr_build_appearance_lattice: null model");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  if (!enable) {
+    if (m->app_lattice) {
+      cudaDeviceSynchronize();  // kernels in flight may still read it
+      free_dev(m->app_lattice);
+    }
+    m->app_lattice = nullptr;
+    m->app_lattice_bytes = 0;
+    m->app_lat_valid = 0;
+    return 0;
+  }
+  if (m->cfg.mlp_mode != 2 || m->cfg.n_pairs != 3) {
+    gnr_set_error("gnr_build_appearance_lattice: needs mlp_mode 2 and three plane/line pairs (got mode %d, %d pairs)",
+                  m->cfg.mlp_mode, m->cfg.n_pairs);
+    return -1;
+  }
+  int dims[3];
+  if (gnr_app_lattice_dims(m, dims)) return -1;
+  const size_t need = (size_t)dims[0] * dims[1] * dims[2] * 32 * sizeof(__half);
+  if (!m->app_lattice || m->app_lattice_bytes != need) {
+    if (m->app_lattice) cudaDeviceSynchronize();
+    free_dev(m->app_lattice);
+    m->app_lattice = nullptr;
+    m->app_lattice_bytes = 0;
+    size_t free_b = 0, total_b = 0;
+    GNR_CUDA_OK(cudaMemGetInfo(&free_b, &total_b));
+    if (need + ((size_t)1 << 30) > free_b) {
+      gnr_set_error("gnr_build_appearance_lattice: the lattice of %dx%dx%d points needs %.1f GB, %.1f GB are free",
+                    dims[0], dims[1], dims[2], need / 1e9, free_b / 1e9);
+      return -1;
+    }
+    GNR_CUDA_OK(cudaMalloc(&m->app_lattice, need));
+    m->app_lattice_bytes = need;
+  }
+  for (int a = 0; a < 3; ++a) m->app_lat_dims[a] = dims[a];
+  GNR_LAUNCH_OK(launch_build_app_lattice(m, m->app_lattice, (cudaStream_t)stream));
+  m->app_lat_valid = 1;
   return 0;
 }
 
@@ -649,6 +706,11 @@ GnrSampleParams gnr_sample_params(const GnrModel* m, int S) {
 }
 
 int gnr_check_lattice(const GnrModel* m) {
+  if (m->app_lattice && !m->app_lat_valid) {
+    gnr_set_error("appearance planes, lines or MLP weights were uploaded after the appearance lattice was built: "
+                  "call gnr_build_appearance_lattice again");
+    return -1;
+  }
   if (m->den_lattice && !m->lat_valid) {
     gnr_set_error("density planes or lines were uploaded after the density lattice was built: call gnr_build_density_lattice again");
     return -1;

@@ -35,6 +35,11 @@
 // R1 = [128, 256): columns 0..79 the current A operand (A0, then A1, A2, A3: each is dead when the
 // next is written), columns 96..127 the fp32 result of the basis projection and later of layer 3.
 //
+// LAT variant (gnr_build_appearance_lattice): the 27 projected features are themselves trilinear in the
+// position (sum over pairs and channels of basis weight x plane texel x line entry at the eight surrounding
+// grid points), so they can be baked into one lattice of 32 fp16 channels per grid point; a sample then
+// reads 8 x 64 bytes instead of 18 x 96, and steps 1 and 2 disappear (the tile starts at step 3).
+//
 // Every wait on an mbarrier is bounded; when one expires the group raises
 // status[GNR_ST_WAIT_EXPIRED] and stops taking tiles; before the CTA frees its tensor memory a
 // group that stopped commits once more and waits (bounded) so that none of its MMAs is in flight.
@@ -66,6 +71,8 @@ struct FusedArgs {
   uint32_t wait_limit;           // iterations a bounded wait may take
   int debug_skip_commit;         // test hook: group 0 of CTA 0 leaves out the commit of its first basis GEMM
   long long* prof;               // null, or [FG][16] cycle sums per phase of the middle CTA (measurement aid)
+  const unsigned char* lat;      // LAT: projected-feature lattice [gx][gy][gz][32] fp16 (gnr_build_appearance_lattice)
+  int lat_g[3];                  // its grid
 };
 
 struct RaySample {  // what a row needs of its list entry
@@ -73,7 +80,7 @@ struct RaySample {  // what a row needs of its list entry
   int k;
 };
 
-template <int NP, bool PROF, bool POINTS>
+template <int NP, bool PROF, bool POINTS, bool LAT>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
@@ -207,83 +214,130 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     if (tile + FG < t_end) next_ray = load_ray(id_ahead);              // (not needed before the next iteration)
     if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
 
-    // ---- gather: this half's rounds of products -> tensor memory ------------------------------------------
-    // (Gathering a group's NEXT tile into registers in the shadows of the current tile's GEMMs instead was
-    // measured slower, 19.6 against 17.6 ms per frame: the GEMMs fetch their weights through the same
-    // L1 / shared-memory port the gather saturates, so the two do not overlap.)
-    {
-      // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
+    uint32_t v[32];  // the 27 projected features of this row as fp32 bits (half 0 reads v[0..13], half 1 v[14..26])
+    if constexpr (LAT) {
+      // ---- features straight from the projected-feature lattice: trilinear interpolation of this half's 16
+      // channels (8 taps x 32 bytes, fp32 accumulation); no products, no projection GEMM -------------------
       const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
       const float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
       const float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
       const float z = POINTS ? cur.o[2] : gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
-      auto taps_of = [&](int pi) -> PairTapsH2 {
-        const GnrPlane& pl = planes.p[pi];
-        if (NP == 3) {
-          const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
-          const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
-          const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
-          return pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
-        }
-        const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
-        return make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
-      };
-      auto do_round = [&](int r, const PairTapsH2& t_pair) {  // r is a compile-time constant after inlining
-        const int pi = r / 3, g = r - 3 * pi;
-        uint32_t q[8];
-        if (pi < planes.n) {
-          pair_round_h2(planes.p[pi], t_pair, g, q);
-        } else {  // fewer than three pairs: these columns are zero
+      const Tap tx = make_tap(x, (float)(a.lat_g[0] - 1), a.lat_g[0]);
+      const Tap ty = make_tap(y, (float)(a.lat_g[1] - 1), a.lat_g[1]);
+      const Tap tz = make_tap(z, (float)(a.lat_g[2] - 1), a.lat_g[2]);
+      const size_t gz = (size_t)a.lat_g[2], gyz = (size_t)a.lat_g[1] * gz;
+      const size_t p000 = ((size_t)tx.i0 * (size_t)a.lat_g[1] + (size_t)ty.i0) * gz + (size_t)tz.i0;
+      const unsigned char* base = a.lat + half * 32;
+      const float wx[2] = {1.0f - tx.f1, tx.f1}, wy[2] = {1.0f - ty.f1, ty.f1}, wz[2] = {1.0f - tz.f1, tz.f1};
+      H16 tap[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) q[e] = 0u;
+      for (int c = 0; c < 8; ++c) {
+        const size_t pt = p000 + (c & 4 ? gyz : 0) + (c & 2 ? gz : 0) + (c & 1);
+        const unsigned char* src = base + pt * 64;
+        asm("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+            : "=r"(tap[c].v[0]), "=r"(tap[c].v[1]), "=r"(tap[c].v[2]), "=r"(tap[c].v[3]), "=r"(tap[c].v[4]), "=r"(tap[c].v[5]),
+              "=r"(tap[c].v[6]), "=r"(tap[c].v[7])
+            : "l"(src));
+      }
+      float acc[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const float w = wx[(c >> 2) & 1] * wy[(c >> 1) & 1] * wz[c & 1];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float2 f = __half22float2(as_h2(tap[c].v[e]));
+          acc[2 * e] = fmaf(w, f.x, acc[2 * e]);
+          acc[2 * e + 1] = fmaf(w, f.y, acc[2 * e + 1]);
         }
-        tmem_st8(a_tmem + lane_off + r * 8, q);
-      };
-      // round r = 3 pair + g fills columns 8 r .. 8 r + 7; half 0 takes rounds 0..4, half 1 rounds 5..8
-      if (half == 0) {  // (warp-uniform)
-        const PairTapsH2 t0 = taps_of(0);
-        do_round(0, t0);
-        do_round(1, t0);
-        do_round(2, t0);
-        const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
-        do_round(3, t1);
-        do_round(4, t1);
+      }
+      if (half == 0) {  // (compile-time indices on either side of a warp-uniform branch: v stays in registers)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) v[e] = __float_as_uint(acc[e]);
       } else {
-        const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
-        do_round(5, t1);
-        const PairTapsH2 t2 = taps_of(planes.n > 2 ? 2 : 0);
-        do_round(6, t2);
-        do_round(7, t2);
-        do_round(8, t2);
-      }
-    }
-    tmem_st_wait();
-    tc_fence_before();
-    GROUP_SYNC();
-    PROF_MARK(0);
-
-    // ---- F = A0 * Wb^T (issued by warp 0 of the group) -----------------------------------------------------
-    if (wg == 0) {
-      tc_fence_after();
-      const uint32_t leader = elect_one();
 #pragma unroll
-      for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
-        if (ks < ksteps0)
-          mma_f16_ts(f_tmem, a_tmem + ks * 8, make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES), kIdescBasis, ks > 0 ? 1u : 0u, leader);
+        for (int e = 0; e < 16; ++e) v[14 + e] = __float_as_uint(acc[e]);
       }
-      const bool skip = a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
-      mma_commit(mbar, skip ? 0u : leader);
-      __syncwarp();
+      PROF_MARK(0);
+    } else {
+    // ---- gather: this half's rounds of products -> tensor memory ------------------------------------------
+      // (Gathering a group's NEXT tile into registers in the shadows of the current tile's GEMMs instead was
+      // measured slower, 19.6 against 17.6 ms per frame: the GEMMs fetch their weights through the same
+      // L1 / shared-memory port the gather saturates, so the two do not overlap.)
+      {
+        // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
+        const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
+        const float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
+        const float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
+        const float z = POINTS ? cur.o[2] : gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
+        auto taps_of = [&](int pi) -> PairTapsH2 {
+          const GnrPlane& pl = planes.p[pi];
+          if (NP == 3) {
+            const Tap tx = make_tap(x, planes.p[0].fw, planes.p[0].W);
+            const Tap ty = make_tap(y, planes.p[0].fh, planes.p[0].H);
+            const Tap tz = make_tap(z, planes.p[0].fl, planes.p[0].L);
+            return pi == 0 ? make_pair_taps_h2(pl, tx, ty, tz) : (pi == 1 ? make_pair_taps_h2(pl, tx, tz, ty) : make_pair_taps_h2(pl, ty, tz, tx));
+          }
+          const float u = pick(x, y, z, pl.mat0), v = pick(x, y, z, pl.mat1), l = pick(x, y, z, pl.vec);
+          return make_pair_taps_h2(pl, make_tap(u, pl.fw, pl.W), make_tap(v, pl.fh, pl.H), make_tap(l, pl.fl, pl.L));
+        };
+        auto do_round = [&](int r, const PairTapsH2& t_pair) {  // r is a compile-time constant after inlining
+          const int pi = r / 3, g = r - 3 * pi;
+          uint32_t q[8];
+          if (pi < planes.n) {
+            pair_round_h2(planes.p[pi], t_pair, g, q);
+          } else {  // fewer than three pairs: these columns are zero
+  #pragma unroll
+            for (int e = 0; e < 8; ++e) q[e] = 0u;
+          }
+          tmem_st8(a_tmem + lane_off + r * 8, q);
+        };
+        // round r = 3 pair + g fills columns 8 r .. 8 r + 7; half 0 takes rounds 0..4, half 1 rounds 5..8
+        if (half == 0) {  // (warp-uniform)
+          const PairTapsH2 t0 = taps_of(0);
+          do_round(0, t0);
+          do_round(1, t0);
+          do_round(2, t0);
+          const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
+          do_round(3, t1);
+          do_round(4, t1);
+        } else {
+          const PairTapsH2 t1 = taps_of(planes.n > 1 ? 1 : 0);
+          do_round(5, t1);
+          const PairTapsH2 t2 = taps_of(planes.n > 2 ? 2 : 0);
+          do_round(6, t2);
+          do_round(7, t2);
+          do_round(8, t2);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      GROUP_SYNC();
+      PROF_MARK(0);
+  
+      // ---- F = A0 * Wb^T (issued by warp 0 of the group) -----------------------------------------------------
+      if (wg == 0) {
+        tc_fence_after();
+        const uint32_t leader = elect_one();
+  #pragma unroll
+        for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
+          if (ks < ksteps0)
+            mma_f16_ts(f_tmem, a_tmem + ks * 8, make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES), kIdescBasis, ks > 0 ? 1u : 0u, leader);
+        }
+        const bool skip = a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
+        mma_commit(mbar, skip ? 0u : leader);
+        __syncwarp();
+      }
+      PROF_MARK(1);
+      WAIT_OR_STOP();
+      PROF_MARK(2);
+      tmem_ld32(f_tmem + lane_off, v);
+      tmem_ld_wait();
     }
-    PROF_MARK(1);
-    WAIT_OR_STOP();
-    PROF_MARK(2);
 
     // ---- A1: this half's 40 columns of the layer-1 input (K order of the permuted W1 image) -----------------
     {
-      uint32_t v[32];  // the 27 projected features of this row (accumulator columns 27..31 are zero padding)
-      tmem_ld32(f_tmem + lane_off, v);
-      tmem_ld_wait();
       uint32_t h[40];
       if (half == 0) {
         // columns 0..6: f0..f13; 7: the constant 1 that multiplies b1; 8..21: (sin f, sin 2f); 22..35: (cos f, cos 2f); 36..39: 0
@@ -339,7 +393,9 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
 #pragma unroll
       for (int ks = 0; ks < K1 / 16; ++ks)
         mma_f16_ts(d_tmem, a_tmem + ks * 8, make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES), kIdescHid, ks > 0 ? 1u : 0u, leader);
-      mma_commit(mbar, leader);
+      // (test hook of the lattice form, which has no projection GEMM to leave uncommitted)
+      const bool skip1 = LAT && a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
+      mma_commit(mbar, skip1 ? 0u : leader);
       __syncwarp();
     }
     PROF_MARK(4);
@@ -480,6 +536,8 @@ void gnr_fused_k1_order(int* map) {
 }
 
 int gnr_app_fusable(const GnrModel* m) {
+  // with the appearance lattice the planes' storage type does not matter: they are not read
+  if (m->app_lattice && m->cfg.mlp_mode == 2 && m->cfg.unfused_appearance == 0) return 1;
   // fp16 appearance planes of 48 (padded) channels, the single-fp16 tensor-core mode, and a product count
   // that fits the 80 operand columns
   return m->cfg.mlp_mode == 2 && m->cfg.app_storage == 1 && m->cfg.unfused_appearance != 1 && gnr_tc_basis_fused(m) &&
@@ -522,9 +580,17 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     return 0;
   };
   int rc;
-  if (points) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true>) : launch(app_mlp_fused_kernel<0, false, true>);
-  else if (a.prof) rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false>) : launch(app_mlp_fused_kernel<0, true, false>);
-  else rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false>) : launch(app_mlp_fused_kernel<0, false, false>);
+  a.lat = (const unsigned char*)m->app_lattice;
+  for (int i = 0; i < 3; ++i) a.lat_g[i] = m->app_lat_dims[i];
+  if (m->app_lattice) {  // features from the projected-feature lattice: no gather of planes, no projection GEMM
+    rc = points ? launch(app_mlp_fused_kernel<3, false, true, true>) : launch(app_mlp_fused_kernel<3, false, false, true>);
+  } else if (points) {
+    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true, false>) : launch(app_mlp_fused_kernel<0, false, true, false>);
+  } else if (a.prof) {
+    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false, false>) : launch(app_mlp_fused_kernel<0, true, false, false>);
+  } else {
+    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false, false>) : launch(app_mlp_fused_kernel<0, false, false, false>);
+  }
   if (rc) return rc;
   return (int)cudaGetLastError();
 }

@@ -327,6 +327,68 @@ density_kernel(GnrSampleParams p, PlaneSet planes, GnrCoords crd, float shift, i
   }
 }
 
+// Appearance lattice: the 27 projected features at every grid point,
+//   A_o[x][y][z] = sum over pairs p and channels c of basis[o][p][c] * plane_p,c(texel) * line_p,c(entry),
+// stored as 32 fp16 channels per point in the order the one-kernel appearance path reads them: channels
+// 0..13 = features 0..13, 14..15 = 0, 16..28 = features 14..26, 29..31 = 0 (each of the two threads of a
+// row loads its own 32 bytes per tap).  One thread per grid point; the basis matrix sits in shared memory
+// as [pair * 48 + c][28] so that a warp reads it as broadcasts; sums in fp32, one rounding to fp16.
+template <bool HALF>
+__global__ void __launch_bounds__(128)
+build_app_lattice_kernel(PlaneSet planes, const float* __restrict__ basis, int app_dim, int n_app, int gx, int gy, int gz,
+                         __half* __restrict__ V) {
+  extern __shared__ float s_basis[];  // [3 * 48][28]
+  for (int i = threadIdx.x; i < 3 * 48 * 28; i += blockDim.x) {
+    const int k = i / 28, o = i - k * 28, pi = k / 48, c = k - pi * 48;
+    s_basis[i] = (o < app_dim && c < n_app) ? basis[(size_t)o * (3 * n_app) + pi * n_app + c] : 0.0f;
+  }
+  __syncthreads();
+  const long long total = (long long)gx * gy * gz;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int z = (int)(i % gz), y = (int)((i / gz) % gy), x = (int)(i / ((long long)gz * gy));
+    const size_t pt[3] = {(size_t)y * planes.p[0].W + x, (size_t)z * planes.p[1].W + x, (size_t)z * planes.p[2].W + y};
+    const size_t ln[3] = {(size_t)z, (size_t)y, (size_t)x};
+    float acc[28];
+#pragma unroll
+    for (int o = 0; o < 28; ++o) acc[o] = 0.0f;
+#pragma unroll 1
+    for (int pi = 0; pi < 3; ++pi) {
+#pragma unroll 4
+      for (int c = 0; c < 48; ++c) {
+        float pv, lv;
+        if constexpr (HALF) {
+          pv = __half2float(reinterpret_cast<const __half*>(planes.p[pi].plane)[pt[pi] * 48 + c]);
+          lv = __half2float(reinterpret_cast<const __half*>(planes.p[pi].line)[ln[pi] * 48 + c]);
+        } else {
+          pv = __ldg(planes.p[pi].plane + pt[pi] * 48 + c);
+          lv = __ldg(planes.p[pi].line + ln[pi] * 48 + c);
+        }
+        const float prod = pv * lv;
+        const float4* w = reinterpret_cast<const float4*>(s_basis + (pi * 48 + c) * 28);
+#pragma unroll
+        for (int q = 0; q < 7; ++q) {
+          const float4 wq = w[q];
+          acc[4 * q + 0] = fmaf(prod, wq.x, acc[4 * q + 0]);
+          acc[4 * q + 1] = fmaf(prod, wq.y, acc[4 * q + 1]);
+          acc[4 * q + 2] = fmaf(prod, wq.z, acc[4 * q + 2]);
+          acc[4 * q + 3] = fmaf(prod, wq.w, acc[4 * q + 3]);
+        }
+      }
+    }
+    __half out[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) out[e] = __float2half_rn(0.0f);
+#pragma unroll
+    for (int o = 0; o < 14; ++o) out[o] = __float2half_rn(acc[o]);
+#pragma unroll
+    for (int o = 14; o < 27; ++o) out[16 + (o - 14)] = __float2half_rn(acc[o]);
+    uint4* dst = reinterpret_cast<uint4*>(V + (size_t)i * 32);
+    const uint4* src = reinterpret_cast<const uint4*>(out);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) dst[q] = src[q];
+  }
+}
+
 // List / point mode density from the lattice: one thread per item.
 __global__ void __launch_bounds__(kBlock)
 density_lattice_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, GnrCoords crd, float shift, int act,
@@ -780,6 +842,37 @@ int launch_build_lattice(const GnrModel* m, float* V, cudaStream_t st) {
     build_lattice_kernel<true><<<grid, 256, 0, st>>>(set, set.p[0].C, gx, gy, gz, V);
   else
     build_lattice_kernel<false><<<grid, 256, 0, st>>>(set, set.p[0].C, gx, gy, gz, V);
+  return (int)cudaGetLastError();
+}
+
+int gnr_app_lattice_dims(const GnrModel* m, int* dims) {
+  PlaneSet set = make_set(m->app, m->cfg.n_pairs);
+  for (int i = 0; i < m->cfg.n_pairs; ++i) {
+    if (!m->app[i].plane || !m->app[i].line) {
+      gnr_set_error("appearance plane/line pair %d has not been uploaded", i);
+      return -1;
+    }
+  }
+  if (!standard_vm3(set) || set.p[0].C != 48 || m->cfg.app_dim > 27 || !m->mlp.basis_raw) {
+    gnr_set_error("the appearance lattice needs the standard three-pair layout on one grid, 33..48 appearance channels, "
+                  "app_dim <= 27 and uploaded MLP weights");
+    return -1;
+  }
+  dims[0] = set.p[0].W;
+  dims[1] = set.p[0].H;
+  dims[2] = set.p[0].L;
+  return 0;
+}
+
+int launch_build_app_lattice(const GnrModel* m, void* V, cudaStream_t st) {
+  PlaneSet set = make_set(m->app, m->cfg.n_pairs);
+  const int gx = set.p[0].W, gy = set.p[0].H, gz = set.p[0].L;
+  const size_t smem = 3 * 48 * 28 * sizeof(float);
+  const int grid = m->sm_count * 16;
+  if (m->cfg.app_storage == 1)
+    build_app_lattice_kernel<true><<<grid, 128, smem, st>>>(set, m->mlp.basis_raw, m->cfg.app_dim, m->cfg.n_app, gx, gy, gz, (__half*)V);
+  else
+    build_app_lattice_kernel<false><<<grid, 128, smem, st>>>(set, m->mlp.basis_raw, m->cfg.app_dim, m->cfg.n_app, gx, gy, gz, (__half*)V);
   return (int)cudaGetLastError();
 }
 

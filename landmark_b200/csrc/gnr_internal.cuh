@@ -22,6 +22,7 @@ struct GnrPlane {
 
 struct GnrMlp {
   // fp32 images for the CUDA-core kernels
+  float* basis_raw;      // [app_dim][n_pairs * n_app] as uploaded (source of the appearance lattice)
   float* basis_blocked;  // [4 lanes][36(+pad)][28] blocked basis weights for the gather kernel
   float* w1t;            // [K1p][hidden]  (transposed, K padded)
   float* w2t;            // [hidden][hidden]
@@ -52,6 +53,11 @@ struct GnrModel {
   float* app_line_buf[GNR_MAX_PLANES];
   size_t plane_bytes[2][GNR_MAX_PLANES];  // current size of every plane / line buffer: an upload of the
   size_t line_bytes[2][GNR_MAX_PLANES];   // same size reuses it (no cudaFree, hence no device-wide sync)
+  // projected-feature lattice of the appearance field [gx][gy][gz][32] fp16 (null unless built)
+  void* app_lattice;
+  size_t app_lattice_bytes;
+  int app_lat_dims[3];
+  int app_lat_valid;
   // pre-summed density lattice [gx][gy][gz] (null unless built; see gnr_build_density_lattice)
   float* den_lattice;
   size_t den_lattice_bytes;
@@ -147,6 +153,8 @@ int launch_sample_mask(const GnrModel* m, const GnrSampleParams& p, const float*
 int launch_sample_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                           int64_t max_valid, int with_ids, cudaStream_t st);
 int launch_build_lattice(const GnrModel* m, float* V, cudaStream_t st);
+int launch_build_app_lattice(const GnrModel* m, void* V, cudaStream_t st);
+int gnr_app_lattice_dims(const GnrModel* m, int* dims);
 int gnr_lattice_dims(const GnrModel* m, int* dims);  // grid of the density field if it has the standard VM3 layout, else -1
 GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L);
 GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L);

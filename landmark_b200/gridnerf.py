@@ -111,6 +111,7 @@ class B200GridNeRF(torch.nn.Module):
         density_plane_fp16: bool = False,
         density_lattice: bool = False,
         fused_appearance: bool = True,
+        appearance_lattice: bool = False,
         **_ignored,
     ):
         super().__init__()
@@ -169,6 +170,9 @@ class B200GridNeRF(torch.nn.Module):
         # built on the device from the planes and lines at commit(); the same function of position, 8
         # scalar taps per sample instead of 18 texels x 16 channels.  Costs 4 bytes per grid point of HBM.
         self.density_lattice = bool(density_lattice)
+        # Appearance features from a baked lattice (gnr_build_appearance_lattice): 64 bytes per grid point of HBM
+        # (69 GB for the city block), 8 taps per sample, no plane gather and no projection GEMM; mlp_mode 2 only
+        self.appearance_lattice = bool(appearance_lattice)
         # forward() runs appearance gather + basis projection + MLP as one kernel when the library can
         # (mlp_mode 2 with fp16 appearance planes); False keeps the separate kernels (GnrConfig.unfused_appearance)
         self.fused_appearance = fused_appearance if fused_appearance in ("stream", "groups") else bool(fused_appearance)
@@ -339,6 +343,8 @@ class B200GridNeRF(torch.nn.Module):
                 check(lib.gnr_build_density_lattice(h, 1, st), "gnr_build_density_lattice")
             self._upload_alpha_mask(st)
             self._upload_mlp(st)
+            if self.appearance_lattice:
+                check(lib.gnr_build_appearance_lattice(h, 1, st), "gnr_build_appearance_lattice")
             torch.cuda.current_stream().synchronize()
         self._committed = True
         if release_torch_planes:
@@ -390,6 +396,8 @@ class B200GridNeRF(torch.nn.Module):
             self._app_code = code
             with torch.cuda.device(self.device):
                 self._upload_mlp()
+                if self.appearance_lattice:  # (the latent only moves the layer-1 bias, but an MLP upload marks the lattice stale)
+                    check(lib.gnr_build_appearance_lattice(self._handle, 1, _stream()), "gnr_build_appearance_lattice")
 
     @torch.no_grad()
     def updateAlphaMask(self, gridSize=(200, 200, 200), increase_alpha_thresh=0):
@@ -517,6 +525,14 @@ class B200GridNeRF(torch.nn.Module):
             self._ws[slot] = buf
         off = (-buf.data_ptr()) % 256
         return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off, max_valid, max_app
+
+    def release_workspaces(self):
+        """Give the chunk scratch buffers back to the allocator (they are made again on the next render).
+        Synchronises the device first: kernels on a side stream may still be using them."""
+        torch.cuda.synchronize(self.device)
+        self._ws.clear()
+        self._last_workspaces = []
+        torch.cuda.empty_cache()
 
     def _samples(self, N_samples: int) -> int:
         if self.sampling_opt:

@@ -723,13 +723,16 @@ def test_fused_appearance_kernel_equals_separate_kernels():
         assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
 
 
-@pytest.mark.parametrize("fused", ["stream", "groups", False])
+@pytest.mark.parametrize("fused", ["stream", "groups", False, "lattice"])
 def test_bounded_wait_expires_and_the_context_survives(fused):
     """The tensor-core kernels bound every wait on an mbarrier.  The test hook makes one group skip the
     step its next wait depends on, with a short poll limit: the wait runs out, the kernel reports it in
     the status block, frees its tensor memory and returns; the same context then renders correctly."""
     spec = scenes.tiny_spec().lit()
-    model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused)
+    if fused == "lattice":
+        model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True, appearance_lattice=True)
+    else:
+        model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True, fused_appearance=fused)
     rays = tiny_rays(spec).cuda()
     good, _ = model(rays, N_samples=spec.n_samples)
     model.debug_wait(expire=True, wait_limit=2000)
@@ -773,3 +776,50 @@ def test_large_appearance_values_stress(scale):
     assert errs["fp32"][1] <= 3 and errs["fp32"][0] <= FLIP_RGB_TOL
     assert errs["mode1"][1] <= 3 and errs["mode1"][0] <= FLIP_RGB_TOL, errs
     assert errs["mode2"][0] <= 2e-2 and errs["mode2+fp16 planes"][0] <= 2e-2, errs
+
+
+def test_appearance_lattice_stays_inside_the_bar(tiny):
+    """appearance_lattice=True: the 27 projected features baked into a lattice of 32 fp16 channels per grid
+    point and interpolated trilinearly (8 taps) by the one-kernel appearance path, instead of 18 plane / line
+    taps of 48 channels and the projection GEMM.  Same function of the position; one fp16 rounding per
+    lattice value instead of one per product.  The image stays within 1e-4 of the reference fixture, within
+    5e-5 of the plane path of the same mode, list mode and point mode agree, and the staleness rule holds."""
+    from landmark_b200 import _lib
+    from landmark_b200.model_parallel import _Chunk, appearance_points
+
+    spec, field, model, rays, ref, got = tiny
+    fx = load_golden("tiny_lit.npz")
+    ckpt = scenes.make_checkpoint(spec)
+    planes = cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True)
+    for half_planes in (False, True):  # lattice built from fp32 or from fp16 planes
+        lat = cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=half_planes, appearance_lattice=True, density_lattice=True)
+        a, _ = lat(rays.cuda(), N_samples=spec.n_samples)
+        b, _ = planes(rays.cuda(), N_samples=spec.n_samples)
+        assert abs(int(lat.last_status[3]) - int(planes.last_status[3])) <= 2 and int(lat.last_status[3]) > 10000
+        err = (a["rgb_map"].cpu() - torch.from_numpy(fx["rgb_map"])).abs().max(dim=1).values
+        assert (err > RGB_TOL).sum().item() <= 2 and err.max().item() <= FLIP_RGB_TOL, (half_planes, float(err.max()))
+        d = (a["rgb_map"] - b["rgb_map"]).abs().max(dim=1).values
+        assert (d > 5e-5).sum().item() <= 2, float(d.max())
+    # point mode (block owners) reads the lattice as well
+    ch = _Chunk(lat, rays.cuda()[3000:5000].contiguous(), spec.n_samples)
+    ch.sample()
+    xyz, ray = ch.positions()
+    st = lat.run_stages(rays.cuda()[3000:5000].contiguous(), spec.n_samples, True)
+    ai = st["app_index"]
+    rgb_pts = appearance_points(lat, xyz[ai], rays.cuda()[3000:5000][ray[ai], 3:6])
+    assert (rgb_pts - st["rgb_samples"]).abs().max().item() <= 1e-4  # (the stage API reads the planes)
+    # ragged counts give the same pixels
+    full, _ = lat(rays.cuda(), N_samples=spec.n_samples)
+    part, _ = lat(rays.cuda()[777:777 + 257].contiguous(), N_samples=spec.n_samples)
+    assert torch.equal(part["rgb_map"], full["rgb_map"][777:777 + 257])
+    # an appearance upload makes the lattice stale
+    import ctypes as C
+
+    l0 = lat.app_line[0].detach().float().contiguous()
+    _lib.check(_lib.lib.gnr_upload_line(lat._handle, 1, 0, C.c_void_p(l0.data_ptr()), l0.shape[1], l0.shape[2], 2, C.c_void_p(0)),
+               "gnr_upload_line")
+    with pytest.raises(_lib.GnrError, match="lattice"):
+        lat(rays.cuda()[:64], N_samples=spec.n_samples)
+    _lib.check(_lib.lib.gnr_build_appearance_lattice(lat._handle, 1, C.c_void_p(0)), "gnr_build_appearance_lattice")
+    again, _ = lat(rays.cuda(), N_samples=spec.n_samples)
+    assert torch.equal(again["rgb_map"], full["rgb_map"])
