@@ -70,11 +70,13 @@ typedef struct GnrConfig {
                                channels.  Sample sets do not depend on it; rgb moves by a few 1e-6. */
   int32_t unfused_appearance; /* 0 = gnr_render_chunk runs appearance gather, basis projection and MLP as ONE
                                kernel whenever the model allows it (mlp_mode 2, app_storage 1, 48 padded
-                               appearance channels, at most 160 products per sample): two groups of warps
-                               each gather and then run the MLP of their own tile; 1 = always the separate
-                               gather and MLP kernels (what the stage-wise entries run); 2 = the one-kernel
-                               form with dedicated gather warps feeding the MLP warps through tensor memory
-                               (same results; measured slower on the city frame).                         */
+                               appearance channels, at most 160 products per sample): three groups of warps
+                               each gather and then run the MLP of their own tile, the three tiles sharing two
+                               accumulators in tensor memory; 1 = always the separate gather and MLP kernels
+                               (what the stage-wise entries run); 2 = the one-kernel form with dedicated gather
+                               warps feeding the MLP warps through tensor memory; 3 = the one-kernel form with
+                               two groups, one accumulator each (2 and 3: same results, kept as measured
+                               alternatives).                                                             */
   int32_t reserved[3];
 } GnrConfig;
 

@@ -43,16 +43,18 @@
 // Every wait on an mbarrier is bounded; when one expires the group raises
 // status[GNR_ST_WAIT_EXPIRED] and stops taking tiles; before the CTA frees its tensor memory a
 // group that stopped commits once more and waits (bounded) so that none of its MMAs is in flight.
+#include <type_traits>
+
 #include "gnr_gather.cuh"
 #include "gnr_tc.cuh"
 
 namespace {
 
-constexpr int FG = 2;               // groups per CTA
+constexpr int MAX_FG = 3;           // groups per CTA: 3 (default) or 2
 constexpr int GT = 256;             // threads per group (two per row)
-constexpr int GROUP_COLS = 256;     // tensor-memory columns per group
-constexpr int A_COL = HID;          // R1: A operand
-constexpr int F_COL = HID + 96;     // R1: 32 fp32 columns (features, then the layer-3 result)
+constexpr int TMEM_COLS = 512;      // the whole tensor memory of the SM
+constexpr int A_COLS = 80;          // operand columns of a group, at [80 g, 80 g + 80)
+constexpr int D_COL = 256;          // the two accumulators: [256, 384) and [384, 512)
 
 struct FusedArgs {
   const float* rays;             // [n][6]
@@ -70,7 +72,7 @@ struct FusedArgs {
   int k0;                        // products per sample (n_pairs * 48)
   uint32_t wait_limit;           // iterations a bounded wait may take
   int debug_skip_commit;         // test hook: group 0 of CTA 0 leaves out the commit of its first basis GEMM
-  long long* prof;               // null, or [FG][16] cycle sums per phase of the middle CTA (measurement aid)
+  long long* prof;               // null, or [groups][16] cycle sums per phase of the middle CTA (measurement aid)
   const unsigned char* lat;      // LAT: projected-feature lattice [gx][gy][gz][32] fp16 (gnr_build_appearance_lattice)
   int lat_g[3];                  // its grid
 };
@@ -80,7 +82,7 @@ struct RaySample {  // what a row needs of its list entry
   int k;
 };
 
-template <int NP, bool PROF, bool POINTS, bool LAT>
+template <int NP, bool PROF, bool POINTS, bool LAT, int FG>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
@@ -91,6 +93,7 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   uint64_t* s_mbar = reinterpret_cast<uint64_t*>(s_b3 + 4);  // [FG] MMA completion
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_mbar + FG);
   volatile uint32_t* s_flag = s_tmem + 1;                    // [FG] outcome of a group's last wait
+  uint32_t* s_rel = s_tmem + 1 + MAX_FG;                     // [2] releases of each accumulator so far (4 per tile)
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const int warp_u = __shfl_sync(0xffffffffu, tid >> 5, 0);  // the same number, known to be warp-uniform
@@ -110,11 +113,13 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     if (tid < 4) s_b3[tid] = a.b3[tid];
     if (tid == 0) {
       for (int s = 0; s < FG; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&s_mbar[s])));
+      s_rel[0] = 0u;
+      s_rel[1] = 0u;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
       asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(s_tmem)),
-                   "r"((uint32_t)(FG * GROUP_COLS)));
+                   "r"((uint32_t)TMEM_COLS));
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     proxy_fence();
@@ -123,9 +128,8 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     tc_fence_after();
   }
   const uint32_t tmem_base = __shfl_sync(0xffffffffu, *s_tmem, 0);
-  const uint32_t d_tmem = tmem_base + (uint32_t)(slot * GROUP_COLS);  // R0
-  const uint32_t a_tmem = d_tmem + A_COL;                             // R1, A operand
-  const uint32_t f_tmem = d_tmem + F_COL;                             // R1, fp32 result columns
+  const uint32_t a_tmem = tmem_base + (uint32_t)(slot * A_COLS);      // this group's A operand
+  const uint32_t rel0 = smem_u32(&s_rel[0]);
   const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;        // the lane quarter this warp may touch
   const uint32_t wb_addr = smem_u32(s_wb), w1_addr = smem_u32(s_w1), w2_addr = smem_u32(s_w2), w3_addr = smem_u32(s_w3h);
   const uint32_t mbar = smem_u32(&s_mbar[slot]);
@@ -210,6 +214,34 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   for (long long tile = t_beg + slot; tile < t_end; tile += FG) {
     const long long j = tile * ROWS + row;
     const bool live = j < total;
+    // The n-th tile of this CTA (counted over all groups) accumulates in D[n & 1]: its own group's for two
+    // groups; with three groups the accumulator of the tile two before it, which that tile's group hands on
+    // when it has read its last result.  f_tmem: the 32 fp32 columns of the projection and, later, of layer 3,
+    // at the start of the same accumulator (each is read before the next MMA that writes there is issued).
+    const uint32_t n_cta = (uint32_t)(tile - t_beg);
+    const uint32_t d_tmem = tmem_base + (uint32_t)D_COL + (n_cta & 1u) * (uint32_t)HID;
+    const uint32_t f_tmem = d_tmem;
+    // Releases are COUNTED (one per warp that read the tile's last result, four per tile), not phases of an
+    // mbarrier: a group meets an accumulator only every other tile of its own, so it would skip phases, and a
+    // phase bit cannot tell "not yet" from "twice since".
+    const uint32_t rel = rel0 + (n_cta & 1u) * 4u;
+    auto acquire_d = [&]() -> bool {  // by every lane of the warp that issues the tile's first MMA
+      if (FG == 2 || n_cta < 2u) return true;
+      const uint32_t want = 4u * (n_cta >> 1);  // every earlier tile on this accumulator has been read out
+      bool ok = false;
+      for (uint32_t it = 0; it < a.wait_limit; ++it) {
+        uint32_t seen;
+        asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(seen) : "r"(rel) : "memory");
+        if (seen >= want) {
+          ok = true;
+          break;
+        }
+        if (it > 64) __nanosleep(64);
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      return ok;
+    };
     const RaySample cur = next_ray;
     if (tile + FG < t_end) next_ray = load_ray(id_ahead);              // (not needed before the next iteration)
     if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
@@ -319,7 +351,8 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       // ---- F = A0 * Wb^T (issued by warp 0 of the group) -----------------------------------------------------
       if (wg == 0) {
         tc_fence_after();
-        const uint32_t leader = elect_one();
+        // (no accumulator within the wait limit: nothing is issued or committed, and the group's own wait expires)
+        const uint32_t leader = acquire_d() ? elect_one() : 0u;
   #pragma unroll
         for (int ks = 0; ks < MAX_K0 / 16; ++ks) {
           if (ks < ksteps0)
@@ -389,7 +422,7 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     // ---- D = A1 * W1^T (warp 1) ------------------------------------------------------------------------------
     if (wg == 1) {
       tc_fence_after();
-      const uint32_t leader = elect_one();
+      const uint32_t leader = (!LAT || acquire_d()) ? elect_one() : 0u;  // (the lattice form has no projection before it)
 #pragma unroll
       for (int ks = 0; ks < K1 / 16; ++ks)
         mma_f16_ts(d_tmem, a_tmem + ks * 8, make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES), kIdescHid, ks > 0 ? 1u : 0u, leader);
@@ -475,6 +508,7 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       }
     }
     tc_fence_before();  // this tile's tensor-memory reads come before the next tile's writes
+    if (FG > 2 && half == 0 && (tid & 31) == 0) asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(rel) : "memory");
     PROF_MARK(12);
   }
 #undef WAIT_OR_STOP
@@ -500,11 +534,11 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   __syncthreads();
   if (warp == 0) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(FG * GROUP_COLS)));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TMEM_COLS));
   }
 }
 
-constexpr size_t kFusedSmem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES + 4 * sizeof(float) + FG * sizeof(uint64_t) + 64;
+constexpr size_t kFusedSmem = (size_t)WB_BYTES + W1_BYTES + W2_BYTES + W3_BYTES + 4 * sizeof(float) + MAX_FG * sizeof(uint64_t) + 64;
 
 }  // namespace
 
@@ -573,24 +607,29 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.wait_limit = m->debug_wait_limit > 0 ? (uint32_t)m->debug_wait_limit : kWaitLimit;
   a.debug_skip_commit = m->debug_expire_wait;
   a.prof = m->debug_prof;
-  auto launch = [&](auto kernel) -> int {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
-    if (e != cudaSuccess) return (int)e;
-    kernel<<<m->sm_count, FG * GT, kFusedSmem, st>>>(p, set, a);
-    return 0;
-  };
-  int rc;
   a.lat = (const unsigned char*)m->app_lattice;
   for (int i = 0; i < 3; ++i) a.lat_g[i] = m->app_lat_dims[i];
-  if (m->app_lattice) {  // features from the projected-feature lattice: no gather of planes, no projection GEMM
-    rc = points ? launch(app_mlp_fused_kernel<3, false, true, true>) : launch(app_mlp_fused_kernel<3, false, false, true>);
-  } else if (points) {
-    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true, false>) : launch(app_mlp_fused_kernel<0, false, true, false>);
-  } else if (a.prof) {
-    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false, false>) : launch(app_mlp_fused_kernel<0, true, false, false>);
-  } else {
-    rc = standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false, false>) : launch(app_mlp_fused_kernel<0, false, false, false>);
-  }
+  auto launch = [&](auto kernel, int groups) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
+    if (e != cudaSuccess) return (int)e;
+    kernel<<<m->sm_count, groups * GT, kFusedSmem, st>>>(p, set, a);
+    return 0;
+  };
+  auto pick_variant = [&](auto groups_tag) -> int {
+    constexpr int G = decltype(groups_tag)::value;
+    if (m->app_lattice)  // features from the projected-feature lattice: no gather of planes, no projection GEMM
+      return points ? launch(app_mlp_fused_kernel<3, false, true, true, G>, G) : launch(app_mlp_fused_kernel<3, false, false, true, G>, G);
+    if (points)
+      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true, false, G>, G)
+                               : launch(app_mlp_fused_kernel<0, false, true, false, G>, G);
+    if (a.prof)
+      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false, false, G>, G)
+                               : launch(app_mlp_fused_kernel<0, true, false, false, G>, G);
+    return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false, false, G>, G)
+                             : launch(app_mlp_fused_kernel<0, false, false, false, G>, G);
+  };
+  const int rc = m->cfg.unfused_appearance == 3 ? pick_variant(std::integral_constant<int, 2>{})
+                                                : pick_variant(std::integral_constant<int, 3>{});
   if (rc) return rc;
   return (int)cudaGetLastError();
 }

@@ -175,7 +175,10 @@ class B200GridNeRF(torch.nn.Module):
         self.appearance_lattice = bool(appearance_lattice)
         # forward() runs appearance gather + basis projection + MLP as one kernel when the library can
         # (mlp_mode 2 with fp16 appearance planes); False keeps the separate kernels (GnrConfig.unfused_appearance)
-        self.fused_appearance = fused_appearance if fused_appearance in ("stream", "groups") else bool(fused_appearance)
+        # ("groups" = True: three groups of warps share two accumulators; "two_groups": two groups, one accumulator
+        # each; "stream": dedicated gather warps)
+        self.fused_appearance = (fused_appearance if fused_appearance in ("stream", "groups", "two_groups")
+                                 else bool(fused_appearance))
         self.update_stepSize(gridSize)
 
         # learnable tensors, reference layout and names (gridnerf_sequential.py:669-747)
@@ -314,7 +317,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.den_storage = 1 if self.density_plane_fp16 else 0
         # True / "groups": two groups of warps that each gather and run the MLP of their tile; "stream": gather warps
         # feed MLP warps through tensor memory; False: separate kernels
-        cfg.unfused_appearance = {True: 0, "groups": 0, "stream": 2, False: 1}[self.fused_appearance]
+        cfg.unfused_appearance = {True: 0, "groups": 0, "stream": 2, "two_groups": 3, False: 1}[self.fused_appearance]
         return cfg
 
     def commit(self, release_torch_planes: bool = False):

@@ -707,7 +707,12 @@ def test_fused_appearance_kernel_equals_separate_kernels():
             assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5, (lo, hi)
     a, _ = stream(rays, N_samples=spec.n_samples)
     b, _ = groups(rays, N_samples=spec.n_samples)
-    assert torch.equal(a["rgb_map"], b["rgb_map"])  # the two fused forms run the same arithmetic in the same order
+    assert torch.equal(a["rgb_map"], b["rgb_map"])  # the fused forms run the same arithmetic in the same order
+    pairs = cuda_model(spec, ckpt, mlp_mode=2, app_plane_fp16=True, fused_appearance="two_groups")
+    for lo, hi in ((0, rays.shape[0]), (5000, 5003), (5000, 5030), (4000, 4100)):
+        a, _ = pairs(rays[lo:hi].contiguous(), N_samples=spec.n_samples)
+        b, _ = groups(rays[lo:hi].contiguous(), N_samples=spec.n_samples)
+        assert torch.equal(a["rgb_map"], b["rgb_map"]), (lo, hi)
     # three pairs that are not the standard VM layout (general branch of the fused gather)
     spec2 = scenes.tiny_spec(height=40, width=40, n_samples=64, grid=32).lit()
     sd = scenes.multires_state_dict(spec2)
@@ -723,7 +728,7 @@ def test_fused_appearance_kernel_equals_separate_kernels():
         assert (a["rgb_map"] - b["rgb_map"]).abs().max().item() <= 1e-5
 
 
-@pytest.mark.parametrize("fused", ["stream", "groups", False, "lattice"])
+@pytest.mark.parametrize("fused", ["stream", "groups", "two_groups", False, "lattice"])
 def test_bounded_wait_expires_and_the_context_survives(fused):
     """The tensor-core kernels bound every wait on an mbarrier.  The test hook makes one group skip the
     step its next wait depends on, with a short poll limit: the wait runs out, the kernel reports it in
