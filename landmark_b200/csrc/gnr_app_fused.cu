@@ -6,10 +6,10 @@
 // encoding and the GEMMs in one pass (dist_render/kernel/cuda_kernel/dal/pe_concate_mlp) behind a
 // separate gather kernel; here the gather is in the same kernel too.
 //
-// One persistent CTA per SM, two groups of 256 threads; a group works on one 128-sample tile at a
-// time.  Row r of the tile (= lane r of tensor memory) belongs to TWO threads of the group, one in
-// each half of it (warps 0-3 and 4-7; warp w of either half owns lanes 32 (w % 4) ..): every per-row
-// phase is split between them by columns, so each phase takes half as long and the SM holds 16 warps
+// One persistent CTA per SM, three groups of 256 threads (768 threads, 80 registers each); a group works on
+// one 128-sample tile at a time.  Row r of the tile (= lane r of tensor memory) belongs to TWO threads of the
+// group, one in each half of it (warps 0-3 and 4-7; warp w of either half owns lanes 32 (w % 4) ..): every
+// per-row phase is split between them by columns, so each phase takes half as long and the SM holds 24 warps
 // whose loads hide each other's latency.  Per tile a group
 //   1. gathers: the 144 plane x line products of a sample as nine rounds of 16 channels (packed fp16,
 //      256-bit loads, the arithmetic of the stand-alone gather); half 0 takes rounds 0-4, half 1
@@ -26,14 +26,20 @@
 // Shared memory holds only the four weight images (90 KB): no operand of a sample is ever written
 // to shared or global memory, so the L1/shared-memory port carries the gather's loads and the
 // weight fetches of the MMAs and nothing else, and the rest of the 256 KB array stays L1 cache for
-// the texels.  While one group gathers (L1 port) the other group's MMAs run (tensor pipe).  GEMM i of
+// the texels.  While one group gathers (L1 port) the other groups' MMAs run (tensor pipe).  GEMM i of
 // a tile is issued by warp i of the group, so the issue time of the MMAs is spread over four warps.
 // The (ray, sample) of a row is fetched two tiles ahead and the ray itself one tile ahead, so the
 // dependent loads behind a list entry are never waited for.
 //
-// Tensor memory, 256 columns per group: R0 = [0, 128) accumulator D of layers 1 and 2;
-// R1 = [128, 256): columns 0..79 the current A operand (A0, then A1, A2, A3: each is dead when the
-// next is written), columns 96..127 the fp32 result of the basis projection and later of layer 3.
+// Tensor memory (512 columns): a tile needs an 80-column operand buffer for its whole life (A0, then A1,
+// A2, A3: each is dead when the next is written) but its 128-column fp32 accumulator only from the
+// projection on, about 60 % of it.  So the three groups own the operand buffers [80 g, 80 g + 80) and SHARE
+// two accumulators, [256, 384) and [384, 512): the n-th tile of the CTA (group n % 3) accumulates in D[n & 1]
+// and takes it over from tile n - 2, whose group counts a release in shared memory as soon as that tile's
+// last result is in registers; the warp that issues a tile's first MMA waits (bounded) for that count.  The
+// 32 fp32 columns of the projection, and later the layer-3 result, sit at the start of the same accumulator.
+// With two groups (GnrConfig.unfused_appearance = 3) tile n - 2 is the group's own previous tile and nothing
+// is waited for; three tiles in flight measured 14.4 against 17.5 ms per city frame.
 //
 // LAT variant (gnr_build_appearance_lattice): the 27 projected features are themselves trilinear in the
 // position (sum over pairs and channels of basis weight x plane texel x line entry at the eight surrounding
@@ -500,6 +506,9 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       uint32_t r[4];
       tmem_ld4(f_tmem + lane_off, r);
       tmem_ld_wait();
+      // the accumulator goes to the tile after the next as soon as its last result is in registers
+      tc_fence_before();
+      if (FG > 2 && (tid & 31) == 0) asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(rel) : "memory");
       if (live) {
         float* out = a.rgb_out + (size_t)j * 3;
         out[0] = 1.0f / (1.0f + __expf(-(s_b3[0] + __uint_as_float(r[0]))));
@@ -508,7 +517,6 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       }
     }
     tc_fence_before();  // this tile's tensor-memory reads come before the next tile's writes
-    if (FG > 2 && half == 0 && (tid & 31) == 0) asm volatile("red.release.cta.shared::cta.add.u32 [%0], 1;" ::"r"(rel) : "memory");
     PROF_MARK(12);
   }
 #undef WAIT_OR_STOP
