@@ -325,6 +325,10 @@ int gnr_points_scratch_bytes(const GnrModel* m, int64_t n, size_t* bytes_h);
  * gridnerf_parallel.py:801-859. */
 int gnr_appearance_points(GnrModel* m, const float* xyz, const float* view, int64_t n, void* scratch,
                           size_t scratch_bytes, float* features, float* rgb, void* stream);
+/* The same with the points as the rows gnr_route_blocks writes for an appearance list, ``rows[n][6]`` =
+ * (x, y, z, view x, view y, view z): what a block owner receives from the all-to-all, read in place. */
+int gnr_appearance_rows(GnrModel* m, const float* rows, int64_t n, void* scratch, size_t scratch_bytes, float* rgb,
+                        void* stream);
 /* compute_appfeature alone at explicit points: ``features[n][app_dim]`` = basis_mat(plane x line products) of
  * this model's appearance channels.  With a channel slice of the planes and the matching columns of basis_mat
  * these are the partial sums a tensor-parallel rank contributes for points that any rank sampled

@@ -1111,11 +1111,12 @@ extern "C" int gnr_render_chunk(GnrModel* m, const float* rays, int64_t n, int S
 // ---------------------------------------------------------------------------------------------
 // split-stage and point-mode entries (model-parallel renderers compose these with collectives)
 // ---------------------------------------------------------------------------------------------
-static GnrCoords coords_points(const float* xyz, const float* view, int64_t n) {
+static GnrCoords coords_points(const float* xyz, const float* view, int64_t n, int stride = 3) {
   GnrCoords c;
   memset(&c, 0, sizeof(c));
   c.xyz_direct = xyz;
   c.view_direct = view;
+  c.point_stride = stride;
   c.total_direct = n;
   c.capacity = n;
   return c;
@@ -1209,6 +1210,9 @@ static int mlp_points(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c,
   return 0;
 }
 
+static int appearance_points_impl(GnrModel* m, const GnrCoords& c, int64_t n, void* scratch, float* features, float* rgb,
+                                  void* stream);
+
 extern "C" int gnr_appearance_points(GnrModel* m, const float* xyz, const float* view, int64_t n, void* scratch,
                                      size_t scratch_bytes, float* features, float* rgb, void* stream) {
   int rc = check_points(m, "gnr_appearance_points", n, scratch, scratch_bytes);
@@ -1218,12 +1222,28 @@ extern "C" int gnr_appearance_points(GnrModel* m, const float* xyz, const float*
     gnr_set_error("gnr_appearance_points: null xyz, view or rgb");
     return -1;
   }
+  return appearance_points_impl(m, coords_points(xyz, view, n), n, scratch, features, rgb, stream);
+}
+
+extern "C" int gnr_appearance_rows(GnrModel* m, const float* rows, int64_t n, void* scratch, size_t scratch_bytes, float* rgb,
+                                   void* stream) {
+  int rc = check_points(m, "gnr_appearance_rows", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!rows || !rgb) {
+    gnr_set_error("gnr_appearance_rows: null rows or rgb");
+    return -1;
+  }
+  return appearance_points_impl(m, coords_points(rows, rows + 3, n, 6), n, scratch, nullptr, rgb, stream);
+}
+
+static int appearance_points_impl(GnrModel* m, const GnrCoords& c, int64_t n, void* scratch, float* features, float* rgb,
+                                  void* stream) {
   DeviceGuard g(m->device);
   cudaStream_t st = (cudaStream_t)stream;
   char* sc = (char*)scratch;
   const PointScratch S = point_scratch(m, n);
   GnrSampleParams p = gnr_sample_params(m, 1);
-  const GnrCoords c = coords_points(xyz, view, n);
   GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
   if (!features && gnr_app_fusable(m)) {
     // gather + basis projection + MLP as one kernel, the points' operands never leaving the SM

@@ -71,6 +71,7 @@ struct FusedArgs {
   long long capacity;
   const float* xyz_direct;       // point mode: [n][3] normalised positions
   const float* view_direct;      // point mode: [n][3] view directions
+  int point_stride;              // floats between the rows of consecutive points in either array
   const unsigned char* w_image;  // [basis][W1][W2][W3][W1 with permuted K] fp16 operand images
   const float* b3;
   float* rgb_out;
@@ -185,8 +186,8 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
   auto load_ray = [&](uint32_t id) -> RaySample {
     RaySample r;
     if (POINTS) {  // o = the normalised position itself, d = the view direction
-      const float* px = a.xyz_direct + (size_t)id * 3;
-      const float* pv = a.view_direct + (size_t)id * 3;
+      const float* px = a.xyz_direct + (size_t)id * a.point_stride;
+      const float* pv = a.view_direct + (size_t)id * a.point_stride;
       r.o[0] = __ldg(px + 0);
       r.o[1] = __ldg(px + 1);
       r.o[2] = __ldg(px + 2);
@@ -607,6 +608,7 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.capacity = c.capacity;
   a.xyz_direct = c.xyz_direct;
   a.view_direct = c.view_direct;
+  a.point_stride = c.point_stride;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
   a.b3 = m->mlp.b3;
   a.rgb_out = rgb;

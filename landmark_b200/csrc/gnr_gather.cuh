@@ -34,12 +34,13 @@ __device__ __forceinline__ Tap make_tap(float u, float fsize, int size) {
 __device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCoords& c, long long i, float& x, float& y,
                                            float& z, float* view = nullptr) {
   if (c.xyz_direct) {
-    x = __ldg(c.xyz_direct + i * 3 + 0);
-    y = __ldg(c.xyz_direct + i * 3 + 1);
-    z = __ldg(c.xyz_direct + i * 3 + 2);
+    const long long at = i * c.point_stride;
+    x = __ldg(c.xyz_direct + at + 0);
+    y = __ldg(c.xyz_direct + at + 1);
+    z = __ldg(c.xyz_direct + at + 2);
     if (view) {
 #pragma unroll
-      for (int a = 0; a < 3; ++a) view[a] = c.view_direct ? __ldg(c.view_direct + i * 3 + a) : 0.0f;
+      for (int a = 0; a < 3; ++a) view[a] = c.view_direct ? __ldg(c.view_direct + at + a) : 0.0f;
     }
     return;
   }

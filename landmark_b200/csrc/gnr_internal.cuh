@@ -131,6 +131,7 @@ struct GnrCoords {
   const int32_t* index;       // optional indirection (appearance list -> valid list)
   const float* xyz_direct;    // [n][3] normalised positions (point mode)
   const float* view_direct;   // [n][3] view directions (point mode)
+  int point_stride;           // floats from one point's row to the next in xyz_direct / view_direct (3 when each is its own array)
   const int32_t* total_ptr;   // device count of items, or null ...
   long long total_direct;     // ... then this host count
   long long capacity;

@@ -95,7 +95,7 @@ mlp_simt_kernel(MlpDims d, int kbits, GnrCoords crd, const float* __restrict__ f
       if (live) {
         const float* vsrc;
         if (crd.view_direct) {
-          vsrc = crd.view_direct + (size_t)j * 3;
+          vsrc = crd.view_direct + (size_t)j * crd.point_stride;
         } else {
           const uint32_t ray = __ldg(crd.ids + (crd.index ? (long long)__ldg(crd.index + j) : j)) >> kbits;
           vsrc = crd.rays + (size_t)ray * 6 + 3;

@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(NSLOT * 128, 1) mlp_tc_kernel(TcArgs a) {
       } else if (live) {
         const float* vsrc;
         if (a.crd.view_direct) {
-          vsrc = a.crd.view_direct + (size_t)j * 3;
+          vsrc = a.crd.view_direct + (size_t)j * a.crd.point_stride;
         } else {
           const uint32_t ray = __ldg(a.crd.ids + (a.crd.index ? (long long)__ldg(a.crd.index + j) : j)) >> a.kbits;
           vsrc = a.crd.rays + (size_t)ray * 6 + 3;

@@ -77,6 +77,25 @@ class DistComm:
         return [out], [rc]
 
 
+    def gather_counts(self, cs: List[torch.Tensor]) -> np.ndarray:
+        """``cs[0]``: this rank's per-destination counts on the device.  Returns the whole [source, destination]
+        matrix on the host; the one host read of an exchange (the device counts are never read on their own)."""
+        c = cs[0].to(torch.int64)
+        out = torch.empty((self.world * c.numel(),), dtype=torch.int64, device=c.device)
+        self.dist.all_gather_into_tensor(out, c.contiguous(), group=self.group)
+        return out.view(self.world, c.numel()).cpu().numpy()
+
+    def all_to_all_known(self, xs: List[torch.Tensor], matrix: np.ndarray, outs: List[torch.Tensor]) -> List[torch.Tensor]:
+        """Counted all-to-all with the [source, destination] matrix known on every rank: the first
+        ``matrix[r].sum()`` rows of ``xs[0]`` go out grouped by destination, the rows for this rank (grouped by
+        source) land in the front of ``outs[0]``, whose used part is returned."""
+        r = self.local_ranks[0]
+        sc, rc = [int(v) for v in matrix[r]], [int(v) for v in matrix[:, r]]
+        x, out = xs[0][: sum(sc)], outs[0][: sum(rc)]
+        self.dist.all_to_all_single(out, x, output_split_sizes=rc, input_split_sizes=sc, group=self.group)
+        return [out]
+
+
 class LoopbackComm:
     """All ranks of the group live in this process; element ``r`` of every list is rank ``r``'s."""
 
@@ -103,6 +122,22 @@ class LoopbackComm:
             outs.append(torch.cat(parts, 0))
             rcs.append([int(send_counts[s][d]) for s in range(self.world)])
         return outs, rcs
+
+
+    def gather_counts(self, cs):
+        return torch.stack([c.to(torch.int64) for c in cs], 0).cpu().numpy()
+
+    def all_to_all_known(self, xs, matrix, outs):
+        starts = np.concatenate([np.zeros((self.world, 1), dtype=np.int64), np.cumsum(matrix, axis=1)], axis=1)
+        res = []
+        for d in range(self.world):
+            at = 0
+            for src in range(self.world):
+                n = int(matrix[src, d])
+                outs[d][at:at + n] = xs[src][int(starts[src, d]):int(starts[src, d]) + n]
+                at += n
+            res.append(outs[d][:at])
+        return res
 
 
 class SectionTimer:
@@ -140,12 +175,12 @@ class SectionTimer:
 class _Chunk:
     """One model's view of one chunk of rays: workspace + the list sizes read back so far."""
 
-    def __init__(self, model: B200GridNeRF, rays: torch.Tensor, n_samples: int):
+    def __init__(self, model: B200GridNeRF, rays: torch.Tensor, n_samples: int, slot: int = 0):
         self.m = model
         self.rays = model._prepare(rays)
         self.n = self.rays.shape[0]
         self.s = model._samples(n_samples)
-        self.keep, self.ws, self.ws_bytes, self.max_valid, self.max_app = model.workspace(self.n, self.s)
+        self.keep, self.ws, self.ws_bytes, self.max_valid, self.max_app = model.workspace(self.n, self.s, slot)
         self.kbits = lib.gnr_sample_bits(self.s)
         self.num_valid = self.num_app = 0
         self.ids = self.app_index = None
@@ -158,6 +193,32 @@ class _Chunk:
         st = self.m.read_status(self.ws)
         self.m.raise_on_status(st)
         self.num_valid = int(st[_lib.ST_NUM_VALID])
+
+    # -- launch-only forms (no host read: the caller reads status and counts together, once per exchange) --
+    def launch_sample(self):
+        check(lib.gnr_sample(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                             None, None, None, None, None, _stream()), "gnr_sample")
+
+    def launch_route(self, which_list: int, division: Tuple[int, int], send: torch.Tensor, dest: torch.Tensor,
+                     counts: torch.Tensor):
+        """gnr_route_blocks into caller-held buffers of list capacity; the list length is read on the device."""
+        counts.zero_()
+        check(lib.gnr_route_blocks(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                   self.max_app, which_list, division[0], division[1], _ptr(send), _ptr(dest),
+                                   _ptr(counts), None, _stream()), "gnr_route_blocks")
+
+    def launch_weights(self, sigma_back: torch.Tensor, dest: torch.Tensor, full: torch.Tensor):
+        """The owners' answers (send-buffer order) gathered into list order, then weights and the appearance list."""
+        if self.num_valid:
+            torch.index_select(sigma_back, 0, dest[: self.num_valid], out=full[: self.num_valid])
+        check(lib.gnr_weights_from_sigma(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                         self.max_app, _ptr(full), None, _stream()), "gnr_weights_from_sigma")
+
+    def checked_status(self):
+        st = self.m.read_status(self.ws)
+        self.m.raise_on_status(st)
+        self.num_valid, self.num_app = int(st[_lib.ST_NUM_VALID]), int(st[_lib.ST_NUM_APP])
+        return st
 
     def density(self):
         check(lib.gnr_density(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
@@ -243,17 +304,19 @@ class _Chunk:
         return rgb, depth
 
 
-def _scratch(model: B200GridNeRF, n: int):
-    """Scratch of the point-mode entries, kept on the model and only ever grown: calls on one stream reuse
-    it in order, so no call has to wait for the previous one."""
+def _scratch(model: B200GridNeRF, n: int, lane: int = 0):
+    """Scratch of the point-mode entries, kept on the model (one per lane: calls of different lanes may be in
+    flight on different streams) and only ever grown: calls on one stream reuse it in order, so no call has
+    to wait for the previous one."""
     nb = C.c_size_t(0)
     check(lib.gnr_points_scratch_bytes(model._handle, n, C.byref(nb)), "gnr_points_scratch_bytes")
-    buf = getattr(model, "_point_scratch", None)
+    store = model.__dict__.setdefault("_point_scratch", {})
+    buf = store.get(lane)
     if buf is None or buf.numel() < nb.value + 256:
         if buf is not None:
             torch.cuda.synchronize(model.device)  # kernels may still be using the smaller buffer
         buf = torch.empty(int(nb.value * 1.25) + 256, dtype=torch.uint8, device=model.device)
-        model._point_scratch = buf
+        store[lane] = buf
     off = (-buf.data_ptr()) % 256
     return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off
 
@@ -467,61 +530,194 @@ def _route(owner: torch.Tensor, world: int):
 class BlockParallelRenderer:
     """``samplers[i]``: a model carrying the global box, step size and occupancy mask (its planes
     are never read); ``owners[i]``: the field of the block that ``comm.local_ranks[i]`` owns.
-    Block ``b`` lives on rank ``b``; ``division[0] * division[1]`` must equal the world size."""
+    Block ``b`` lives on rank ``b``; ``division[0] * division[1]`` must equal the world size.
+
+    A chunk goes through four steps, two of which end in the only host reads of the chunk (status + the
+    [source, destination] count matrix of an exchange, one synchronisation each):
+
+      1. sample, route the valid list by owner (``gnr_route_blocks``), gather the counts             [host read]
+      2. all-to-all of the points, density at the owners, all-to-all of sigma back                      [no read]
+      3. weights + appearance list, route it by owner, gather the counts                             [host read]
+      4. all-to-all of (point, view) rows, colour at the owners, all-to-all back, composite            [no read]
+
+    ``render_frame`` keeps two chunks in flight on two streams (lanes), alternating (1, 2) of one with (3, 4)
+    of the other: while the host waits for one lane's counts, the GPU runs the other lane's exchange and
+    owner-side kernels, and a lane's all-to-all (NCCL's stream) overlaps the other lane's kernels.  Every
+    buffer of a lane is kept and only grown, so a frame allocates nothing after the first."""
 
     def __init__(self, samplers: Sequence[B200GridNeRF], owners: Sequence[B200GridNeRF], comm, division: Tuple[int, int]):
         if division[0] * division[1] != comm.world:
             raise ValueError(f"{division[0]}x{division[1]} blocks need {division[0] * division[1]} ranks, have {comm.world}")
         self.samplers, self.owners, self.comm, self.division = list(samplers), list(owners), comm, division
         self.timer = SectionTimer(False)  # set ``timer.enabled`` to get a per-section breakdown of a frame
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+        self._streams: Dict[tuple, torch.cuda.Stream] = {}
+        self.samples = {"valid": 0, "app": 0}  # list lengths of the local ranks' chunks since the last render_frame began
+
+    def _buf(self, lane: int, i: int, name: str, rows: int, cols: int, dtype, device) -> torch.Tensor:
+        """Grow-only buffer ``name`` of lane ``lane`` and local rank ``i``, at least [rows, cols] (flat when cols == 0)."""
+        key = (lane, i, name)
+        need = max(rows, 1) * max(cols, 1)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < need:
+            if buf is not None:
+                torch.cuda.synchronize(device)  # kernels of this lane may still be using the smaller one
+            buf = torch.empty(int(need * 1.25) + 16, dtype=dtype, device=device)
+            self._bufs[key] = buf
+        return buf[:need].view(max(rows, 1), cols) if cols else buf[:need]
+
+    def _steps(self, rays: Sequence[torch.Tensor], n_samples: int, white_bg: bool, lane: int, result: list):
+        """Generator over the four steps of one chunk; ``result`` receives per local rank ``(rgb_map, depth_map)``."""
+        tm, div, nb = self.timer, self.division, self.comm.world
+        chunks, sends, dests, cnts = [], [], [], []
+        # ---- 1: sample globally; block assignment + grouping by owner on the device ---------------------------------
+        for i, (s_, r) in enumerate(zip(self.samplers, rays)):
+            with torch.cuda.device(s_.device):
+                ch = _Chunk(s_, r, n_samples, slot=lane)
+                ch.launch_sample()
+                tm.mark("sample")
+                send = self._buf(lane, i, "send", ch.max_valid, 3, torch.float32, s_.device)
+                dest = self._buf(lane, i, "dest", ch.max_valid, 0, torch.int32, s_.device)
+                cnt = self._buf(lane, i, "cnt", nb, 0, torch.int32, s_.device)
+                ch.launch_route(0, div, send, dest, cnt)
+                tm.mark("route valid")
+                chunks.append(ch)
+                sends.append(send)
+                dests.append(dest)
+                cnts.append(cnt)
+        matrix = self.comm.gather_counts(cnts)
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                ch.checked_status()
+        tm.mark("counts of the valid lists")
+        yield
+        # ---- 2: points travel to the owners, density there, values travel back --------------------------------------
+        n_in = [int(matrix[:, r].sum()) for r in self.comm.local_ranks]
+        recv = self.comm.all_to_all_known(sends, matrix, [self._buf(lane, i, "recv", n, 3, torch.float32, o.device)
+                                                          for i, (o, n) in enumerate(zip(self.owners, n_in))])
+        tm.mark("all-to-all points")
+        sig = []
+        for i, (o, x) in enumerate(zip(self.owners, recv)):
+            out = self._buf(lane, i, "sigma", x.shape[0], 0, torch.float32, o.device)
+            if x.shape[0]:
+                with torch.cuda.device(o.device):
+                    check(lib.gnr_density_points(o._handle, _ptr(x), x.shape[0], None, _ptr(out), _stream()), "gnr_density_points")
+            sig.append(out)
+        tm.mark("density at owners")
+        back = self.comm.all_to_all_known(sig, matrix.T, [self._buf(lane, i, "sigma_back", ch.max_valid, 0, torch.float32, ch.m.device)
+                                                          for i, ch in enumerate(chunks)])
+        tm.mark("all-to-all sigma")
+        yield
+        # ---- 3: weights and the appearance list at the ray's rank; route it by owner ----------------------------------
+        app_sends, app_dests = [], []
+        for i, (ch, dest, sg) in enumerate(zip(chunks, dests, back)):
+            with torch.cuda.device(ch.m.device):
+                full = self._buf(lane, i, "sigma_list", ch.max_valid, 0, torch.float32, ch.m.device)
+                ch.launch_weights(sg, dest, full)
+                tm.mark("weights")
+                send = self._buf(lane, i, "app_send", ch.max_app, 6, torch.float32, ch.m.device)
+                dest_a = self._buf(lane, i, "app_dest", ch.max_app, 0, torch.int32, ch.m.device)
+                ch.launch_route(1, div, send, dest_a, cnts[i])
+                tm.mark("route appearance")
+                app_sends.append(send)
+                app_dests.append(dest_a)
+        amatrix = self.comm.gather_counts(cnts)
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                ch.checked_status()
+        tm.mark("counts of the appearance lists")
+        self.samples["valid"] += sum(ch.num_valid for ch in chunks)
+        self.samples["app"] += sum(ch.num_app for ch in chunks)
+        yield
+        # ---- 4: (point, view) rows travel to the owners, colour there, values travel back, composite -----------------
+        n_in = [int(amatrix[:, r].sum()) for r in self.comm.local_ranks]
+        arecv = self.comm.all_to_all_known(app_sends, amatrix, [self._buf(lane, i, "app_recv", n, 6, torch.float32, o.device)
+                                                                for i, (o, n) in enumerate(zip(self.owners, n_in))])
+        tm.mark("all-to-all appearance points")
+        rgb_o = []
+        for i, (o, x) in enumerate(zip(self.owners, arecv)):
+            out = self._buf(lane, i, "rgb_owner", x.shape[0], 3, torch.float32, o.device)[: x.shape[0]]
+            if x.shape[0]:
+                keep, sc, nbytes = _scratch(o, x.shape[0], lane)
+                with torch.cuda.device(o.device):
+                    check(lib.gnr_appearance_rows(o._handle, _ptr(x), x.shape[0], sc, nbytes, _ptr(out), _stream()),
+                          "gnr_appearance_rows")
+            rgb_o.append(out)
+        tm.mark("appearance at owners")
+        rgb_back = self.comm.all_to_all_known(rgb_o, amatrix.T, [self._buf(lane, i, "rgb_back", ch.max_app, 3, torch.float32, ch.m.device)
+                                                                 for i, ch in enumerate(chunks)])
+        tm.mark("all-to-all rgb")
+        for i, (ch, dest_a, rb) in enumerate(zip(chunks, app_dests, rgb_back)):
+            with torch.cuda.device(ch.m.device):
+                rgb_s = self._buf(lane, i, "rgb_list", ch.num_app, 3, torch.float32, ch.m.device)[: ch.num_app]
+                if ch.num_app:
+                    torch.index_select(rb, 0, dest_a[: ch.num_app], out=rgb_s)
+                result.append(ch.composite(rgb_s, white_bg))
+        tm.mark("composite")
+
+    def _lane_stream(self, lane: int, device) -> torch.cuda.Stream:
+        key = (lane, str(device))
+        if key not in self._streams:
+            self._streams[key] = torch.cuda.Stream(device=device)
+        return self._streams[key]
 
     @torch.no_grad()
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
         Returns per local rank ``(rgb_map, depth_map)`` of its own rays."""
-        chunks, sends, dests, counts = [], [], [], []
-        tm = self.timer
-        tm.start()
-        # ---- sample globally; block assignment + grouping by owner on the device; points travel to the owners
-        for s_, r in zip(self.samplers, rays):
-            with torch.cuda.device(s_.device):
-                ch = _Chunk(s_, r, n_samples)
-                ch.sample(keep_ids=False)
-                tm.mark("sample")
-                send, dest, cnt = ch.route(0, self.division)
-                tm.mark("route valid")
-                chunks.append(ch)
-                sends.append(send)
-                dests.append(dest)
-                counts.append(cnt)
-        recv, rcounts = self.comm.all_to_all_rows(sends, counts)
-        tm.mark("all-to-all points")
-        # ---- owners: density at the received points, values travel back -------------------------
-        sig = [density_points(o, x) for o, x in zip(self.owners, recv)]
-        tm.mark("density at owners")
-        back, _ = self.comm.all_to_all_rows(sig, rcounts)
-        tm.mark("all-to-all sigma")
-        app_send, app_counts, app_dests = [], [], []
-        for ch, dest, sg in zip(chunks, dests, back):
-            with torch.cuda.device(ch.m.device):
-                ch.weights(sg, dest)  # answers -> list order, weights, appearance list
-                tm.mark("weights")
-                send, dest_a, cnt = ch.route(1, self.division)
-                tm.mark("route appearance")
-                app_send.append(send)
-                app_dests.append(dest_a)
-                app_counts.append(cnt)
-        # ---- owners: colour at the received (position, view) pairs, values travel back ----------
-        arecv, arcounts = self.comm.all_to_all_rows(app_send, app_counts)
-        tm.mark("all-to-all appearance points")
-        rgb_o = [appearance_points(o, x[:, :3], x[:, 3:6]) for o, x in zip(self.owners, arecv)]
-        tm.mark("appearance at owners")
-        rgb_back, _ = self.comm.all_to_all_rows(rgb_o, arcounts)
-        tm.mark("all-to-all rgb")
-        out = []
-        for ch, dest_a, rb in zip(chunks, app_dests, rgb_back):
-            with torch.cuda.device(ch.m.device):
-                rgb_s = torch.index_select(rb, 0, dest_a) if ch.num_app else rb[:0]
-                out.append(ch.composite(rgb_s, white_bg))
-        tm.mark("composite")
+        self.timer.start()
+        out: list = []
+        for _ in self._steps(rays, n_samples, white_bg, 0, out):
+            pass
         return out
+
+    @torch.no_grad()
+    def render_frame(self, chunk_list: Sequence[Sequence[torch.Tensor]], n_samples: int = -1, white_bg: bool = True,
+                     lanes: int = 2):
+        """``chunk_list[c][i]``: chunk c of local rank i (every rank of the group passes the same number of
+        chunks).  Two chunks are in flight, each on its own stream; returns per chunk what ``render_chunk``
+        returns.  Only the single-process-per-rank form overlaps; with several local ranks (loopback) the
+        lanes still alternate but share the current device's streams."""
+        n = len(chunk_list)
+        results = [[] for _ in range(n)]
+        self.samples = {"valid": 0, "app": 0}
+        if n == 0:
+            return results
+        dev = self.samplers[0].device
+        cur = torch.cuda.current_stream(dev)
+        lanes = max(1, min(lanes, n))
+        streams = [self._lane_stream(l, dev) for l in range(lanes)]
+        for st in streams:
+            st.wait_stream(cur)
+        self.timer.start()
+        gens = [None] * lanes
+        nxt = 0
+
+        def advance(l, steps):
+            with torch.cuda.stream(streams[l]):
+                for _ in range(steps):
+                    try:
+                        next(gens[l])
+                    except StopIteration:
+                        gens[l] = None
+                        return
+
+        # every lane takes chunks in turn; a turn is two steps (one that ends in a host read, one that does not)
+        active = True
+        while active:
+            active = False
+            for l in range(lanes):
+                if gens[l] is None and nxt < n:
+                    gens[l] = self._steps(chunk_list[nxt], n_samples, white_bg, l, results[nxt])
+                    nxt += 1
+                if gens[l] is not None:
+                    advance(l, 2)
+                    active = True
+            active = active or nxt < n
+        for st in streams:
+            cur.wait_stream(st)
+        for per_chunk in results:  # made on a lane's stream, read by the caller on the current one
+            for rgb, depth in per_chunk:
+                rgb.record_stream(cur)
+                depth.record_stream(cur)
+        return results

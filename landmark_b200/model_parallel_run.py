@@ -27,7 +27,9 @@ from .model_parallel import BlockParallelRenderer, ChannelParallelRenderer, Dist
 from .parallel import TileSharding
 from .rays import generate_rays
 
-DIVISIONS = {1: (1, 1), 2: (2, 1), 4: (2, 2), 8: (4, 2)}
+# (the camera of the block scene looks along +x across the y = 0 plane: every division here cuts y, so that at
+# least two owners carry visible samples)
+DIVISIONS = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (4, 2)}
 
 
 def _model(spec, ckpt, device, mlp_mode, **extra):
@@ -123,7 +125,26 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
     image = torch.zeros((H * W, 3), dtype=torch.float32, device=device)
     stats = {"valid": 0, "app": 0}
 
+    def parts_of_frame():
+        out = []
+        for c in range(n_chunks):
+            lo, hi = min(c * chunk, n_local), min((c + 1) * chunk, n_local)
+            out.append((lo, hi, rays[lo:hi] if hi > lo else rays[:1]))  # an idle rank still takes part in the exchange
+        return out
+
+    def frame_blocks(lanes=2):
+        """Block layout: the chunks of the frame go through the renderer's two-lane pipeline."""
+        parts = parts_of_frame()
+        res = ren.render_frame([[p[2]] for p in parts], S, True, lanes=lanes)
+        for (lo, hi, _), per_chunk in zip(parts, res):
+            if hi > lo:
+                rgb[lo:hi] = per_chunk[0][0]
+        shard.assemble(rgb, image)
+        stats["valid"], stats["app"] = ren.samples["valid"], ren.samples["app"]
+
     def frame():
+        if workload == "city_blocks":
+            return frame_blocks()
         stats["valid"] = stats["app"] = 0
         for c in range(n_chunks):
             lo, hi = min(c * chunk, n_local), min((c + 1) * chunk, n_local)
@@ -157,7 +178,10 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
     # one more frame with a CUDA-event stopwatch around every section (rank 0's view; its extra events and the
     # synchronisation at the end are why this frame is not part of the timed ones)
     ren.timer.enabled = True
-    frame()
+    if workload == "city_blocks":
+        frame_blocks(lanes=1)  # one lane: the sections of a chunk follow each other on one stream
+    else:
+        frame()
     sections = {k: round(v, 3) for k, v in ren.timer.collect().items()}
     ren.timer.enabled = False
     tot = torch.tensor([float(stats["valid"]), float(stats["app"])], device=device, dtype=torch.float64)

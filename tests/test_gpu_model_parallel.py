@@ -97,6 +97,16 @@ def test_block_parallel_matches_oracle(division, mlp_mode):
     for p, (c, d) in zip(parts, outs):
         rgb[p], depth[p] = c.cpu(), d.cpu()
     _check(rgb, depth, ref)
+    # the frame form: three chunks per rank through the two-lane pipeline give the bits of chunk-by-chunk calls
+    cuts = [0, 200, 520, 10 ** 9]
+    chunk_list = [[rays[p][lo:hi].cuda() for p in parts] for lo, hi in zip(cuts[:-1], cuts[1:])]
+    for lanes in (1, 2):
+        res = ren.render_frame(chunk_list, 160, True, lanes=lanes)
+        torch.cuda.synchronize()
+        for r in range(world):
+            assert torch.equal(torch.cat([res[c][r][0] for c in range(3)]), outs[r][0]), (lanes, r)
+            assert torch.equal(torch.cat([res[c][r][1] for c in range(3)]), outs[r][1]), (lanes, r)
+    assert ren.samples["valid"] > 0 and ren.samples["app"] > 2000
 
 
 def test_assign_blocks_matches_oracle_restatement():

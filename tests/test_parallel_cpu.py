@@ -174,7 +174,15 @@ def _route_worker(rank, world, port, out):
         gathered = comm.all_gather_rows([x[:8]])
         # the channel-parallel renderer's exchange: partial feature rows summed and dealt out by rows
         part = comm.reduce_scatter_rows([x[:64]])
-        torch.save({"recv": got[0], "rc": rc[0], "restored": restored, "gathered": gathered[0], "part": part[0]},
+        # the pipelined block renderer's form: device-side counts gathered into one [source, destination] matrix,
+        # exchanges into caller-held buffers of list capacity, return trip with the transposed matrix
+        matrix = comm.gather_counts([torch.tensor(counts, dtype=torch.int32)])
+        known = comm.all_to_all_known([x[order]], matrix, [torch.zeros((4000, 4))])
+        known_back = comm.all_to_all_known([known[0] * 2], matrix.T, [torch.zeros((4000, 4))])
+        restored2 = torch.empty_like(x)
+        restored2[order] = known_back[0]
+        torch.save({"recv": got[0], "rc": rc[0], "restored": restored, "gathered": gathered[0], "part": part[0],
+                    "matrix": torch.from_numpy(matrix.copy()), "known": known[0].clone(), "restored2": restored2},
                    f"{out}.{rank}")
     finally:
         dist.destroy_process_group()
@@ -195,8 +203,14 @@ def test_sample_routing_two_ranks_over_gloo_equals_loopback(tmp_path):
     recv, rcs = lb.all_to_all_rows([rows[r][1][routed[r][0]] for r in range(world)], [routed[r][1] for r in range(world)])
     gathered = lb.all_gather_rows([rows[r][1][:8] for r in range(world)])
     parts = lb.reduce_scatter_rows([rows[r][1][:64] for r in range(world)])
+    matrix = lb.gather_counts([torch.tensor(routed[r][1], dtype=torch.int32) for r in range(world)])
+    known = lb.all_to_all_known([rows[r][1][routed[r][0]] for r in range(world)], matrix,
+                                [torch.zeros((4000, 4)) for _ in range(world)])
     for r in range(world):
         got = torch.load(f"{out}.{r}")
+        assert np.array_equal(got["matrix"].numpy(), matrix) and matrix[r].tolist() == routed[r][1]
+        assert torch.equal(got["known"], known[r]) and torch.equal(known[r], recv[r])
+        assert torch.equal(got["restored2"], rows[r][1] * 2)
         assert torch.equal(got["part"], parts[r])
         assert got["rc"] == rcs[r]
         assert torch.equal(got["recv"], recv[r])
