@@ -15,6 +15,7 @@ NCCL).  Both build seeded synthetic scenes on the fly:
 
 from __future__ import annotations
 
+import os
 import time
 from typing import Dict, Tuple
 
@@ -132,7 +133,7 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
             out.append((lo, hi, rays[lo:hi] if hi > lo else rays[:1]))  # an idle rank still takes part in the exchange
         return out
 
-    def frame_blocks(lanes=2):
+    def frame_blocks(lanes=int(os.environ.get('GNR_LANES', '2'))):
         """Block layout: the chunks of the frame go through the renderer's two-lane pipeline."""
         parts = parts_of_frame()
         res = ren.render_frame([[p[2]] for p in parts], S, True, lanes=lanes)
