@@ -1306,6 +1306,12 @@ extern "C" int gnr_mlp_features(GnrModel* m, const float* features, const float*
   const PointScratch S = point_scratch(m, n);
   GnrSampleParams p = gnr_sample_params(m, 1);
   GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+  if (m->cfg.mlp_mode == 2 && m->cfg.unfused_appearance != 1 && m->mlp.tc_image) {
+    // positional encoding + the three layers in the one-kernel form, features read in place
+    GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, coords_points(nullptr, view, n), rgb, (int32_t*)(sc + S.status), st, features,
+                                       m->cfg.app_dim));
+    return 0;
+  }
   GNR_CUDA_OK(cudaMemsetAsync(sc + S.feat, 0, (size_t)n * 28 * 4, st));
   GNR_CUDA_OK(cudaMemcpy2DAsync(sc + S.feat, 28 * 4, features, (size_t)m->cfg.app_dim * 4, (size_t)m->cfg.app_dim * 4, (size_t)n,
                                 cudaMemcpyDeviceToDevice, st));

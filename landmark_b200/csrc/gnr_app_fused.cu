@@ -82,6 +82,8 @@ struct FusedArgs {
   long long* prof;               // null, or [groups][16] cycle sums per phase of the middle CTA (measurement aid)
   const unsigned char* lat;      // LAT: projected-feature lattice [gx][gy][gz][32] fp16 (gnr_build_appearance_lattice)
   int lat_g[3];                  // its grid
+  const float* feat;             // SRC 2: [n][feat_stride] fp32 projected features of the points
+  int feat_stride;
 };
 
 struct RaySample {  // what a row needs of its list entry
@@ -89,8 +91,12 @@ struct RaySample {  // what a row needs of its list entry
   int k;
 };
 
-template <int NP, bool PROF, bool POINTS, bool LAT, int FG>
+// SRC: where a tile's 27 projected features come from: 0 = gathered from the planes and lines and projected
+// here, 1 = the projected-feature lattice, 2 = given per point (features computed elsewhere, e.g. summed over
+// the channel slices of a tensor-parallel group); 1 and 2 start a tile at step 3.
+template <int NP, bool PROF, bool POINTS, int SRC, int FG>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
+  constexpr bool LAT = SRC == 1, FEAT = SRC == 2;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
   unsigned char* s_w1 = s_wb + WB_BYTES;  // layer 1, K permuted (see the header of this file)
@@ -254,7 +260,18 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
 
     uint32_t v[32];  // the 27 projected features of this row as fp32 bits (half 0 reads v[0..13], half 1 v[14..26])
-    if constexpr (LAT) {
+    if constexpr (FEAT) {
+      // ---- features given per point: this half's 14 / 13 values of the row --------------------------------------
+      const float* src = a.feat + (size_t)(j < total ? j : total - 1) * a.feat_stride + (half ? 14 : 0);
+      if (half == 0) {
+#pragma unroll
+        for (int e = 0; e < 14; ++e) v[e] = __float_as_uint(__ldg(src + e));
+      } else {
+#pragma unroll
+        for (int e = 0; e < 13; ++e) v[14 + e] = __float_as_uint(__ldg(src + e));
+      }
+      PROF_MARK(0);
+    } else if constexpr (LAT) {
       // ---- features straight from the projected-feature lattice: trilinear interpolation of this half's 16
       // channels (8 taps x 32 bytes, fp32 accumulation); no products, no projection GEMM -------------------
       const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
@@ -429,12 +446,12 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     // ---- D = A1 * W1^T (warp 1) ------------------------------------------------------------------------------
     if (wg == 1) {
       tc_fence_after();
-      const uint32_t leader = (!LAT || acquire_d()) ? elect_one() : 0u;  // (the lattice form has no projection before it)
+      const uint32_t leader = (SRC == 0 || acquire_d()) ? elect_one() : 0u;  // (without a projection this is the tile's first MMA)
 #pragma unroll
       for (int ks = 0; ks < K1 / 16; ++ks)
         mma_f16_ts(d_tmem, a_tmem + ks * 8, make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES), kIdescHid, ks > 0 ? 1u : 0u, leader);
       // (test hook of the lattice form, which has no projection GEMM to leave uncommitted)
-      const bool skip1 = LAT && a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
+      const bool skip1 = SRC != 0 && a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
       mma_commit(mbar, skip1 ? 0u : leader);
       __syncwarp();
     }
@@ -588,14 +605,15 @@ int gnr_app_fusable(const GnrModel* m) {
 }
 
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
-                         cudaStream_t st) {
+                         cudaStream_t st, const float* features, int feat_stride) {
   if (!m->mlp.tc_image) {
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
   }
-  const bool points = c.xyz_direct != nullptr;
-  if (points ? (!c.view_direct) : (!c.ids || c.index || !c.total_ptr)) {
-    gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count) or explicit points with view directions");
+  const bool points = c.xyz_direct != nullptr || features != nullptr;
+  if (features ? (!c.view_direct) : (c.xyz_direct ? (!c.view_direct) : (!c.ids || c.index || !c.total_ptr))) {
+    gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count), explicit points with view "
+                  "directions, or explicit features with view directions");
     return -1;
   }
   PlaneSet set = make_set(m->app, m->cfg.n_pairs);
@@ -606,7 +624,7 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.total_ptr = c.total_ptr;
   a.total_direct = c.total_direct;
   a.capacity = c.capacity;
-  a.xyz_direct = c.xyz_direct;
+  a.xyz_direct = c.xyz_direct ? c.xyz_direct : c.view_direct;  // (with given features the position is never read)
   a.view_direct = c.view_direct;
   a.point_stride = c.point_stride;
   a.w_image = (const unsigned char*)m->mlp.tc_image;
@@ -619,6 +637,8 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   a.prof = m->debug_prof;
   a.lat = (const unsigned char*)m->app_lattice;
   for (int i = 0; i < 3; ++i) a.lat_g[i] = m->app_lat_dims[i];
+  a.feat = features;
+  a.feat_stride = feat_stride;
   auto launch = [&](auto kernel, int groups) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
     if (e != cudaSuccess) return (int)e;
@@ -627,16 +647,17 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   };
   auto pick_variant = [&](auto groups_tag) -> int {
     constexpr int G = decltype(groups_tag)::value;
+    if (features) return launch(app_mlp_fused_kernel<3, false, true, 2, G>, G);
     if (m->app_lattice)  // features from the projected-feature lattice: no gather of planes, no projection GEMM
-      return points ? launch(app_mlp_fused_kernel<3, false, true, true, G>, G) : launch(app_mlp_fused_kernel<3, false, false, true, G>, G);
+      return points ? launch(app_mlp_fused_kernel<3, false, true, 1, G>, G) : launch(app_mlp_fused_kernel<3, false, false, 1, G>, G);
     if (points)
-      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true, false, G>, G)
-                               : launch(app_mlp_fused_kernel<0, false, true, false, G>, G);
+      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, true, 0, G>, G)
+                               : launch(app_mlp_fused_kernel<0, false, true, 0, G>, G);
     if (a.prof)
-      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false, false, G>, G)
-                               : launch(app_mlp_fused_kernel<0, true, false, false, G>, G);
-    return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false, false, G>, G)
-                             : launch(app_mlp_fused_kernel<0, false, false, false, G>, G);
+      return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, true, false, 0, G>, G)
+                               : launch(app_mlp_fused_kernel<0, true, false, 0, G>, G);
+    return standard_vm3(set) ? launch(app_mlp_fused_kernel<3, false, false, 0, G>, G)
+                             : launch(app_mlp_fused_kernel<0, false, false, 0, G>, G);
   };
   const int rc = m->cfg.unfused_appearance == 3 ? pick_variant(std::integral_constant<int, 2>{})
                                                 : pick_variant(std::integral_constant<int, 3>{});

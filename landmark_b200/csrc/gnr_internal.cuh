@@ -177,8 +177,9 @@ int gnr_app_fusable(const GnrModel* m);
 // the same work with dedicated gather warps feeding the MLP warps through tensor memory (gnr_app_stream.cu)
 int launch_app_mlp_stream(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
                           cudaStream_t st);
+// (`features` non-null: MLP alone on given projected features [n][feat_stride] and c.view_direct)
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
-                         cudaStream_t st);
+                         cudaStream_t st, const float* features = nullptr, int feat_stride = 0);
 void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
