@@ -335,6 +335,17 @@ int gnr_appearance_rows(GnrModel* m, const float* rows, int64_t n, void* scratch
  * (gridnerf_tensor_parallel.py:284-300).  Same scratch as gnr_appearance_points. */
 int gnr_app_features_points(GnrModel* m, const float* xyz, int64_t n, void* scratch, size_t scratch_bytes,
                             float* features, void* stream);
+/* Tensor-parallel exchange in fp16: ``features_h[n][32]`` (fp16, 64-byte rows, columns >= app_dim zero) = the partial
+ * projection of this model's channel slice at ``xyz`` (rows of ``point_stride`` floats), on the tensor cores; needs
+ * mlp_mode 2 and app_storage 1 with 16 / 32 / 48 padded channels per plane.  ``status``: 8 device words (zeroed here;
+ * word GNR_ST_WAIT_EXPIRED is raised if a bounded wait of the kernel ran out).  No reference counterpart as a separate
+ * entry: the reference sums fp32 products after an all-gather (gridnerf_tensor_parallel.py:284-300). */
+int gnr_project_slice_points(GnrModel* m, const float* xyz, int point_stride, int64_t n, void* features_h, int32_t* status,
+                             void* stream);
+/* ``features[rows][app_dim]`` (fp32) = sum over ``n_parts`` buffers of fp16 rows of 32 (part w starts
+ * ``w * part_stride_rows`` rows into ``parts_h``): the receiver's side of that exchange. */
+int gnr_sum_partials(GnrModel* m, const void* parts_h, int n_parts, int64_t rows, int64_t part_stride_rows, float* features,
+                     void* stream);
 /* MLPRender_Fea alone on explicit ``features[n][app_dim]`` and ``view[n][3]`` (the sample slice a
  * tensor-parallel rank owns after the reduction, gridnerf_tensor_parallel.py:301-325). */
 int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,

@@ -203,8 +203,9 @@ extern "C" int gnr_create(const GnrConfig* cfg, int device, GnrModel** out) {
     return -1;
   }
   if (cfg->app_storage != 0 &&
-      (cfg->app_storage != 1 || cfg->mlp_mode != 2 || cfg->n_app <= 32 || cfg->n_app > 48 || cfg->app_dim > 27)) {
-    gnr_set_error("gnr_create: app_storage %d: fp16 appearance planes need mlp_mode 2 (got %d) and 33..48 appearance channels (got %d)",
+      (cfg->app_storage != 1 || cfg->mlp_mode != 2 || cfg->n_app > 48 || cfg->app_dim > 27)) {
+    // (33..48 channels: every appearance path; fewer, a channel slice: gnr_project_slice_points only)
+    gnr_set_error("gnr_create: app_storage %d: fp16 appearance planes need mlp_mode 2 (got %d) and at most 48 appearance channels (got %d)",
                   cfg->app_storage, cfg->mlp_mode, cfg->n_app);
     return -1;
   }
@@ -1288,6 +1289,35 @@ extern "C" int gnr_app_features_points(GnrModel* m, const float* xyz, int64_t n,
   }
   GNR_CUDA_OK(cudaMemcpy2DAsync(features, (size_t)m->cfg.app_dim * 4, feat, 28 * 4, (size_t)m->cfg.app_dim * 4, (size_t)n,
                                 cudaMemcpyDeviceToDevice, st));
+  return 0;
+}
+
+extern "C" int gnr_project_slice_points(GnrModel* m, const float* xyz, int point_stride, int64_t n, void* features_h,
+                                        int32_t* status, void* stream) {
+  int rc = check_points(m, "gnr_project_slice_points", n, nullptr, (size_t)-1);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!xyz || !features_h || !status || point_stride < 3) {
+    gnr_set_error("gnr_project_slice_points: null xyz, features or status, or a point stride below 3");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  GNR_CUDA_OK(cudaMemsetAsync(status, 0, GNR_ST_WORDS * 4, st));
+  GNR_LAUNCH_OK(launch_app_slice_project(m, xyz, point_stride, n, features_h, status, st));
+  return 0;
+}
+
+extern "C" int gnr_sum_partials(GnrModel* m, const void* parts_h, int n_parts, int64_t rows, int64_t part_stride_rows,
+                                float* features, void* stream) {
+  if (!m || !parts_h || !features || n_parts < 1 || rows < 0 || part_stride_rows < rows) {
+    gnr_set_error("gnr_sum_partials: null model, parts or features, or bad sizes (%d parts, %lld rows, stride %lld)", n_parts,
+                  (long long)rows, (long long)part_stride_rows);
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  GNR_LAUNCH_OK(launch_sum_partials(parts_h, n_parts, rows, part_stride_rows, m->cfg.app_dim, m->cfg.app_dim, features,
+                                    (cudaStream_t)stream));
   return 0;
 }
 

@@ -180,6 +180,11 @@ int launch_app_mlp_stream(const GnrModel* m, const GnrSampleParams& p, const Gnr
 // (`features` non-null: MLP alone on given projected features [n][feat_stride] and c.view_direct)
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
                          cudaStream_t st, const float* features = nullptr, int feat_stride = 0);
+// partial projection of a channel slice at explicit points, fp16 rows of 32 (gnr_app_slice.cu), and the fp32 sum of such parts
+int launch_app_slice_project(const GnrModel* m, const float* xyz, int stride, int64_t n, void* features_h, int32_t* status,
+                             cudaStream_t st);
+int launch_sum_partials(const void* parts_h, int n_parts, int64_t rows, int64_t part_stride_rows, int n_out, int out_stride,
+                        float* out, cudaStream_t st);
 void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)

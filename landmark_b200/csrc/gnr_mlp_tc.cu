@@ -524,8 +524,10 @@ int gnr_mlp_tc_prepare(GnrModel* m, const float* basis_w, const float* w1, const
   GNR_CUDA_OK(cudaMalloc(&m->mlp.tc_image, m->mlp.tc_image_bytes));
   GNR_CUDA_OK(cudaMemsetAsync(m->mlp.tc_image, 0, m->mlp.tc_image_bytes, st));
   __half* img = reinterpret_cast<__half*>(m->mlp.tc_image);
-  if (gnr_tc_basis_fused(m)) {
-    const int cp = (c.n_app + 15) / 16 * 16, kgb = m->mlp.n_prod / 8;
+  // the basis over PADDED channels (k = pair * cp + channel): what the fused paths multiply the products by, and, for a
+  // channel slice of any width, what the slice projection does
+  const int cp = (c.n_app + 15) / 16 * 16, kgb = c.n_pairs * cp / 8;
+  if (c.app_dim <= NB && c.n_pairs * cp <= MAX_K0) {
     pack_weight_image_kernel<<<(kgb * NB + 255) / 256, 256, 0, st>>>(basis_w, img, c.app_dim, NB, c.n_pairs * c.n_app, kgb,
                                                                     c.n_app, cp, nullptr, -1);
   }

@@ -77,6 +77,17 @@ class DistComm:
         return [out], [rc]
 
 
+    def all_gather_into(self, xs: List[torch.Tensor], outs: List[torch.Tensor]) -> List[torch.Tensor]:
+        """``outs[0]`` (world x the rows of ``xs[0]``) receives every rank's rows, rank r's first row at r * rows."""
+        self.dist.all_gather_into_tensor(outs[0], xs[0], group=self.group)
+        return outs
+
+    def all_to_all_equal(self, xs: List[torch.Tensor], outs: List[torch.Tensor]) -> List[torch.Tensor]:
+        """Equal split: part d of ``xs[0]`` (world equal parts) goes to rank d; ``outs[0]`` holds the parts received,
+        by source."""
+        self.dist.all_to_all_single(outs[0], xs[0], group=self.group)
+        return outs
+
     def gather_counts(self, cs: List[torch.Tensor]) -> np.ndarray:
         """``cs[0]``: this rank's per-destination counts on the device.  Returns the whole [source, destination]
         matrix on the host; the one host read of an exchange (the device counts are never read on their own)."""
@@ -123,6 +134,20 @@ class LoopbackComm:
             rcs.append([int(send_counts[s][d]) for s in range(self.world)])
         return outs, rcs
 
+
+    def all_gather_into(self, xs, outs):
+        n = xs[0].shape[0]
+        for out in outs:
+            for r, x in enumerate(xs):
+                out[r * n:(r + 1) * n] = x
+        return outs
+
+    def all_to_all_equal(self, xs, outs):
+        n = xs[0].shape[0] // self.world
+        for d, out in enumerate(outs):
+            for src, x in enumerate(xs):
+                out[src * n:(src + 1) * n] = x[d * n:(d + 1) * n]
+        return outs
 
     def gather_counts(self, cs):
         return torch.stack([c.to(torch.int64) for c in cs], 0).cpu().numpy()
@@ -213,6 +238,10 @@ class _Chunk:
             torch.index_select(sigma_back, 0, dest[: self.num_valid], out=full[: self.num_valid])
         check(lib.gnr_weights_from_sigma(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
                                          self.max_app, _ptr(full), None, _stream()), "gnr_weights_from_sigma")
+
+    def launch_march(self):
+        check(lib.gnr_march(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                            self.max_app, None, None, None, None, None, None, _stream()), "gnr_march")
 
     def checked_status(self):
         st = self.m.read_status(self.ws)
@@ -409,13 +438,139 @@ class ChannelParallelRenderer:
         """Indices of the rays of a chunk that ``rank`` samples: groups of RAY_GROUP consecutive rays dealt
         round-robin (consecutive rays are neighbouring pixels: a group keeps the kernels' locality, the
         round-robin balances sky against ground)."""
-        idx = torch.arange(n, device=device)
-        return idx[(idx // self.RAY_GROUP) % self.comm.world == rank]
+        key = (n, rank, str(device))
+        cache = self.__dict__.setdefault("_shares", {})
+        if key not in cache:  # (boolean indexing reads a count back: once per chunk size, not once per chunk)
+            if len(cache) > 64:
+                cache.clear()
+            idx = torch.arange(n, device=device)
+            cache[key] = idx[(idx // self.RAY_GROUP) % self.comm.world == rank]
+        return cache[key]
+
+    def _buf(self, i: int, name: str, rows: int, cols: int, dtype, device) -> torch.Tensor:
+        """Grow-only buffer ``name`` of local rank ``i``, at least [rows, cols] (flat when cols == 0)."""
+        key = (i, name)
+        need = max(rows, 1) * max(cols, 1)
+        store = self.__dict__.setdefault("_bufs", {})
+        buf = store.get(key)
+        if buf is None or buf.numel() < need:
+            if buf is not None:
+                torch.cuda.synchronize(device)
+            buf = torch.zeros(int(need * 1.25) + 16, dtype=dtype, device=device)
+            store[key] = buf
+        return buf[:need].view(max(rows, 1), cols) if cols else buf[:need]
+
+    def _fp16_exchange(self) -> bool:
+        """The tensor-core form of the exchange: fp16 appearance planes and the single-fp16 MLP on every rank."""
+        return all(m.mlp_mode == 2 and m.app_plane_fp16 and m.ert_transmittance >= 0.0 for m in self.models)
 
     @torch.no_grad()
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
-        """``rays[i]``: the same chunk on each local rank's device.  Returns per local rank
-        ``(rgb_map, depth_map)``; all ranks end up with the full result.
+        """``rays[i]``: the same chunk on each local rank's device.  Returns per local rank ``(rgb_map, depth_map)``;
+        all ranks end up with the full result.  With fp16 appearance planes and mlp_mode 2 on every rank the
+        partial projections are computed on the tensor cores and travel as fp16 (``_render_chunk_fp16``); otherwise
+        they are fp32 rows summed by a reduce-scatter (``_render_chunk_fp32``)."""
+        if self._fp16_exchange():
+            return self._render_chunk_fp16(rays, n_samples, white_bg)
+        return self._render_chunk_fp32(rays, n_samples, white_bg)
+
+    def _render_chunk_fp16(self, rays, n_samples, white_bg):
+        """Every rank samples and marches ITS share of the rays (one host read: the list lengths); the positions of
+        all appearance samples are all-gathered (12 bytes each); every rank projects all of them through its channel
+        slice on the tensor cores (``gnr_project_slice_points``: products from registers into tensor memory, one
+        small GEMM, fp16 rows of 64 bytes); an all-to-all hands every rank the W partial rows of its OWN samples,
+        which it sums in fp32 (``gnr_sum_partials``), runs through the MLP (``gnr_mlp_features``, the one-kernel
+        form on given features) and composites; the pixels are all-gathered.  Against the fp32 form: half the
+        bytes on the wire, no fp32 feature rows in memory, and the sum over the ranks in fp32 at the receiver."""
+        W = self.comm.world
+        tm = self.timer
+        tm.start()
+        chunks, shares, rows6 = [], [], []
+        for i, (m, r, rank) in enumerate(zip(self.models, rays, self.comm.local_ranks)):
+            with torch.cuda.device(m.device):
+                share = self._ray_share(r.shape[0], rank, m.device)
+                mine = r[share] if share.numel() else r[:1]  # a rank without rays still takes part in the collectives
+                ch = _Chunk(m, mine, n_samples)
+                ch.launch_sample()
+                ch.launch_march()
+                tm.mark("sample + march (own rays)")
+                pts = self._buf(i, "rows6", ch.max_app, 6, torch.float32, m.device)
+                dest = self._buf(i, "dest", ch.max_app, 0, torch.int32, m.device)
+                cnt = self._buf(i, "cnt", 1, 0, torch.int32, m.device)
+                ch.launch_route(1, (1, 1), pts, dest, cnt)  # one block: the appearance list as (point, view) rows in list order
+                tm.mark("appearance points")
+                chunks.append(ch)
+                shares.append(share)
+                rows6.append(pts)
+        counts = self.comm.gather_counts([self._buf(i, "cnt", 1, 0, torch.int32, ch.m.device) for i, ch in enumerate(chunks)])
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                ch.checked_status()
+        per = max(1, int(counts.max()))  # rows per rank in the gathered list (padded to the largest)
+        tm.mark("counts")
+        own_xyz, all_xyz = [], []
+        for i, (ch, pts) in enumerate(zip(chunks, rows6)):
+            with torch.cuda.device(ch.m.device):
+                x = self._buf(i, "xyz_own", per, 3, torch.float32, ch.m.device)
+                x[: ch.num_app] = pts[: ch.num_app, :3]  # (rows past the list keep older positions: any point will do)
+                own_xyz.append(x)
+                all_xyz.append(self._buf(i, "xyz_all", W * per, 3, torch.float32, ch.m.device))
+        self.comm.all_gather_into(own_xyz, all_xyz)
+        tm.mark("all-gather points")
+        parts = []
+        for i, (ch, allp) in enumerate(zip(chunks, all_xyz)):
+            with torch.cuda.device(ch.m.device):
+                part = self._buf(i, "part_h", W * per, 32, torch.float16, ch.m.device)
+                st = self._buf(i, "slice_status", 8, 0, torch.int32, ch.m.device)
+                check(lib.gnr_project_slice_points(ch.m._handle, _ptr(allp), 3, W * per, _ptr(part), _ptr(st), _stream()),
+                      "gnr_project_slice_points")
+                parts.append(part)
+        tm.mark("partial projection (all points)")
+        recvs = [self._buf(i, "recv_h", W * per, 32, torch.float16, ch.m.device) for i, ch in enumerate(chunks)]
+        self.comm.all_to_all_equal(parts, recvs)
+        tm.mark("all-to-all of fp16 partial rows")
+        pix = []
+        for i, (ch, recv, pts) in enumerate(zip(chunks, recvs, rows6)):
+            with torch.cuda.device(ch.m.device):
+                na = ch.num_app
+                feats = self._buf(i, "feats", na, ch.m.app_dim, torch.float32, ch.m.device)
+                if na:
+                    check(lib.gnr_sum_partials(ch.m._handle, _ptr(recv), W, na, per, _ptr(feats), _stream()), "gnr_sum_partials")
+                rgb_s = mlp_features(ch.m, feats[:na], pts[:na, 3:6].contiguous())
+                pix.append(ch.composite(rgb_s, white_bg))
+        tm.mark("sum + MLP + composite (own rays)")
+        return self._gather_pixels(rays, chunks, shares, pix)
+
+    def _gather_pixels(self, rays, chunks, shares, pix):
+        """Pixels of every rank -> every rank (padded to the largest share)."""
+        W = self.comm.world
+        n = rays[0].shape[0]
+        per_rays = max(1, max(int(self._ray_share(n, r, "cpu").numel()) for r in range(W)))
+        packed = []
+        for ch, share, (rgb, depth) in zip(chunks, shares, pix):
+            with torch.cuda.device(ch.m.device):
+                buf = torch.zeros((per_rays, 4), dtype=torch.float32, device=ch.m.device)
+                k = share.numel()
+                buf[:k, :3] = rgb[:k]
+                buf[:k, 3] = depth[:k]
+                packed.append(buf)
+        gathered = self.comm.all_gather_rows(packed)
+        out = []
+        for ch, g in zip(chunks, gathered):
+            with torch.cuda.device(ch.m.device):
+                rgb = torch.empty((n, 3), dtype=torch.float32, device=ch.m.device)
+                depth = torch.empty((n,), dtype=torch.float32, device=ch.m.device)
+                for r in range(W):
+                    share = self._ray_share(n, r, ch.m.device)
+                    k = share.numel()
+                    rgb[share] = g[r * per_rays:r * per_rays + k, :3]
+                    depth[share] = g[r * per_rays:r * per_rays + k, 3]
+                out.append((rgb, depth))
+        self.timer.mark("all-gather pixels")
+        return out
+
+    def _render_chunk_fp32(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
+        """The fp32 form of the exchange (any precision mode of the models).
 
         Work split (app/models/gridnerf_tensor_parallel.py:198-217,284-330 divides the density work and the
         samples over the group as well): every rank samples and marches only ITS share of the rays; the
@@ -467,31 +622,7 @@ class ChannelParallelRenderer:
                 rgb, depth = ch.composite(rgb_s, white_bg)
                 pix.append((rgb, depth))
         tm.mark("MLP + composite (own rays)")
-        # pixels of every rank -> every rank (padded to the largest share)
-        n = rays[0].shape[0]
-        per_rays = max(1, max(int(self._ray_share(n, r, "cpu").numel()) for r in range(W)))
-        packed = []
-        for ch, share, (rgb, depth) in zip(chunks, shares, pix):
-            with torch.cuda.device(ch.m.device):
-                buf = torch.zeros((per_rays, 4), dtype=torch.float32, device=ch.m.device)
-                k = share.numel()
-                buf[:k, :3] = rgb[:k]
-                buf[:k, 3] = depth[:k]
-                packed.append(buf)
-        gathered = self.comm.all_gather_rows(packed)
-        out = []
-        for ch, g in zip(chunks, gathered):
-            with torch.cuda.device(ch.m.device):
-                rgb = torch.empty((n, 3), dtype=torch.float32, device=ch.m.device)
-                depth = torch.empty((n,), dtype=torch.float32, device=ch.m.device)
-                for r in range(W):
-                    share = self._ray_share(n, r, ch.m.device)
-                    k = share.numel()
-                    rgb[share] = g[r * per_rays:r * per_rays + k, :3]
-                    depth[share] = g[r * per_rays:r * per_rays + k, 3]
-                out.append((rgb, depth))
-        tm.mark("all-gather pixels")
-        return out
+        return self._gather_pixels(rays, chunks, shares, pix)
 
 
 # ----------------------------------------------------------------------------------------------

@@ -20,9 +20,15 @@ def _check(rgb, depth, ref, max_flips=3):
     assert (depth.cpu() - ref["depth_map"]).abs().max().item() <= 2e-4
 
 
-@pytest.mark.parametrize("world,mlp_mode", [(2, 0), (3, 2), (1, 2)])
+@pytest.mark.parametrize("world,mlp_mode", [(2, 0), (3, 2), (1, 2), (1, "fp16"), (2, "fp16"), (3, "fp16")])
 def test_channel_parallel_matches_unsplit_oracle(world, mlp_mode):
+    """``"fp16"``: fp16 appearance planes + mlp_mode 2 on every rank, which selects the tensor-core form of the
+    exchange (slices of 48, 24 and 16 channels: three, two and one round of 16 per pair)."""
     from landmark_b200.model_parallel import ChannelParallelRenderer, LoopbackComm, slice_checkpoint_channels
+
+    extra = {}
+    if mlp_mode == "fp16":
+        mlp_mode, extra = 2, {"app_plane_fp16": True, "ert_transmittance": 0.0}
 
     spec = scenes.tiny_spec(grid=64).lit()
     field, ckpt = oracle_field(spec)
@@ -34,8 +40,9 @@ def test_channel_parallel_matches_unsplit_oracle(world, mlp_mode):
         assert sl["state_dict"]["app_plane.0"].shape[1] == 48 // world
         sspec = scenes.tiny_spec(grid=64).lit()
         sspec.app_n_comp = (48 // world,) * 3
-        models.append(cuda_model(sspec, sl, mlp_mode=mlp_mode))
+        models.append(cuda_model(sspec, sl, mlp_mode=mlp_mode, **extra))
     ren = ChannelParallelRenderer(models, LoopbackComm(world))
+    assert ren._fp16_exchange() == bool(extra)
     outs = ren.render_chunk([rays.cuda()] * world, spec.n_samples, True)
     assert len(outs) == world
     for rgb, depth in outs:
