@@ -350,12 +350,12 @@ def _scratch(model: B200GridNeRF, n: int, lane: int = 0):
     return buf, C.c_void_p(buf.data_ptr() + off), buf.numel() - off
 
 
-def mlp_features(model: B200GridNeRF, feats: torch.Tensor, view: torch.Tensor) -> torch.Tensor:
+def mlp_features(model: B200GridNeRF, feats: torch.Tensor, view: torch.Tensor, lane: int = 0) -> torch.Tensor:
     n = feats.shape[0]
     rgb = torch.empty((n, 3), dtype=torch.float32, device=model.device)
     if n == 0:
         return rgb
-    keep, sc, nb = _scratch(model, n)
+    keep, sc, nb = _scratch(model, n, lane)
     feats, view = feats.contiguous(), view.contiguous()
     with torch.cuda.device(model.device):
         check(lib.gnr_mlp_features(model._handle, _ptr(feats), _ptr(view), n, sc, nb, _ptr(rgb), _stream()), "gnr_mlp_features")
@@ -424,6 +424,53 @@ def slice_checkpoint_channels(ckpt: Dict, rank: int, world: int) -> Dict:
     return out
 
 
+def _run_lanes(make_steps, n_chunks: int, lanes: int, device, streams: Dict[tuple, "torch.cuda.Stream"], steps_per_turn: int):
+    """Drive ``n_chunks`` step generators (``make_steps(chunk, lane, result_list)``) with up to ``lanes`` of them in
+    flight, each on its own CUDA stream; a lane's turn is ``steps_per_turn`` steps (one that ends in a host read and
+    the launches that follow it), then the next lane's turn: while the host waits for one lane's read the GPU has
+    the other lanes' queued work, and a lane's collectives (NCCL's stream) run beside the other lanes' kernels.
+    Every rank of a group must call this with the same ``n_chunks`` and ``lanes`` (the collectives interleave in
+    the same order).  Returns the result list of every chunk."""
+    results = [[] for _ in range(n_chunks)]
+    if n_chunks == 0:
+        return results
+    cur = torch.cuda.current_stream(device)
+    lanes = max(1, min(lanes, n_chunks))
+    lane_streams = []
+    for l in range(lanes):
+        key = (l, str(device))
+        if key not in streams:
+            streams[key] = torch.cuda.Stream(device=device)
+        streams[key].wait_stream(cur)
+        lane_streams.append(streams[key])
+    gens = [None] * lanes
+    nxt = 0
+    active = True
+    while active:
+        active = False
+        for l in range(lanes):
+            if gens[l] is None and nxt < n_chunks:
+                gens[l] = make_steps(nxt, l, results[nxt])
+                nxt += 1
+            if gens[l] is not None:
+                with torch.cuda.stream(lane_streams[l]):
+                    for _ in range(steps_per_turn):
+                        try:
+                            next(gens[l])
+                        except StopIteration:
+                            gens[l] = None
+                            break
+                active = True
+        active = active or nxt < n_chunks
+    for st in lane_streams:
+        cur.wait_stream(st)
+    for per_chunk in results:  # made on a lane's stream, read by the caller on the current one
+        for rgb, depth in per_chunk:
+            rgb.record_stream(cur)
+            depth.record_stream(cur)
+    return results
+
+
 class ChannelParallelRenderer:
     """``models[i]`` is the channel-sliced model of ``comm.local_ranks[i]``."""
 
@@ -447,8 +494,8 @@ class ChannelParallelRenderer:
             cache[key] = idx[(idx // self.RAY_GROUP) % self.comm.world == rank]
         return cache[key]
 
-    def _buf(self, i: int, name: str, rows: int, cols: int, dtype, device) -> torch.Tensor:
-        """Grow-only buffer ``name`` of local rank ``i``, at least [rows, cols] (flat when cols == 0)."""
+    def _buf(self, i, name: str, rows: int, cols: int, dtype, device) -> torch.Tensor:
+        """Grow-only buffer ``name`` of (lane, local rank) ``i``, at least [rows, cols] (flat when cols == 0)."""
         key = (i, name)
         need = max(rows, 1) * max(cols, 1)
         store = self.__dict__.setdefault("_bufs", {})
@@ -471,10 +518,28 @@ class ChannelParallelRenderer:
         partial projections are computed on the tensor cores and travel as fp16 (``_render_chunk_fp16``); otherwise
         they are fp32 rows summed by a reduce-scatter (``_render_chunk_fp32``)."""
         if self._fp16_exchange():
-            return self._render_chunk_fp16(rays, n_samples, white_bg)
+            self.timer.start()
+            out: list = []
+            for _ in self._steps_fp16(rays, n_samples, white_bg, 0, out):
+                pass
+            return out
         return self._render_chunk_fp32(rays, n_samples, white_bg)
 
-    def _render_chunk_fp16(self, rays, n_samples, white_bg):
+    @torch.no_grad()
+    def render_frame(self, chunk_list: Sequence[Sequence[torch.Tensor]], n_samples: int = -1, white_bg: bool = True,
+                     lanes: int = 2):
+        """``chunk_list[c][i]``: chunk c on local rank i's device.  With the fp16 exchange two chunks are in flight on two
+        streams (a chunk has one host read, the list lengths, then only launches and collectives); returns per chunk
+        what ``render_chunk`` returns."""
+        if not self._fp16_exchange():
+            return [self.render_chunk(c, n_samples, white_bg) for c in chunk_list]
+        self.timer.start()
+        self.samples = {"valid": 0, "app": 0}  # list lengths of the local ranks' shares since this call began
+        streams = self.__dict__.setdefault("_streams", {})
+        return _run_lanes(lambda c, lane, out: self._steps_fp16(chunk_list[c], n_samples, white_bg, lane, out), len(chunk_list),
+                          lanes, self.models[0].device, streams, 2)
+
+    def _steps_fp16(self, rays, n_samples, white_bg, lane, result):
         """Every rank samples and marches ITS share of the rays (one host read: the list lengths); the positions of
         all appearance samples are all-gathered (12 bytes each); every rank projects all of them through its channel
         slice on the tensor cores (``gnr_project_slice_points``: products from registers into tensor memory, one
@@ -490,56 +555,60 @@ class ChannelParallelRenderer:
             with torch.cuda.device(m.device):
                 share = self._ray_share(r.shape[0], rank, m.device)
                 mine = r[share] if share.numel() else r[:1]  # a rank without rays still takes part in the collectives
-                ch = _Chunk(m, mine, n_samples)
+                ch = _Chunk(m, mine, n_samples, slot=lane)
                 ch.launch_sample()
                 ch.launch_march()
                 tm.mark("sample + march (own rays)")
-                pts = self._buf(i, "rows6", ch.max_app, 6, torch.float32, m.device)
-                dest = self._buf(i, "dest", ch.max_app, 0, torch.int32, m.device)
-                cnt = self._buf(i, "cnt", 1, 0, torch.int32, m.device)
+                pts = self._buf((lane, i), "rows6", ch.max_app, 6, torch.float32, m.device)
+                dest = self._buf((lane, i), "dest", ch.max_app, 0, torch.int32, m.device)
+                cnt = self._buf((lane, i), "cnt", 1, 0, torch.int32, m.device)
                 ch.launch_route(1, (1, 1), pts, dest, cnt)  # one block: the appearance list as (point, view) rows in list order
                 tm.mark("appearance points")
                 chunks.append(ch)
                 shares.append(share)
                 rows6.append(pts)
-        counts = self.comm.gather_counts([self._buf(i, "cnt", 1, 0, torch.int32, ch.m.device) for i, ch in enumerate(chunks)])
+        counts = self.comm.gather_counts([self._buf((lane, i), "cnt", 1, 0, torch.int32, ch.m.device) for i, ch in enumerate(chunks)])
         for ch in chunks:
             with torch.cuda.device(ch.m.device):
                 ch.checked_status()
         per = max(1, int(counts.max()))  # rows per rank in the gathered list (padded to the largest)
         tm.mark("counts")
+        tally = self.__dict__.setdefault("samples", {"valid": 0, "app": 0})
+        tally["valid"] += sum(ch.num_valid for ch in chunks)
+        tally["app"] += sum(ch.num_app for ch in chunks)
+        yield
         own_xyz, all_xyz = [], []
         for i, (ch, pts) in enumerate(zip(chunks, rows6)):
             with torch.cuda.device(ch.m.device):
-                x = self._buf(i, "xyz_own", per, 3, torch.float32, ch.m.device)
+                x = self._buf((lane, i), "xyz_own", per, 3, torch.float32, ch.m.device)
                 x[: ch.num_app] = pts[: ch.num_app, :3]  # (rows past the list keep older positions: any point will do)
                 own_xyz.append(x)
-                all_xyz.append(self._buf(i, "xyz_all", W * per, 3, torch.float32, ch.m.device))
+                all_xyz.append(self._buf((lane, i), "xyz_all", W * per, 3, torch.float32, ch.m.device))
         self.comm.all_gather_into(own_xyz, all_xyz)
         tm.mark("all-gather points")
         parts = []
         for i, (ch, allp) in enumerate(zip(chunks, all_xyz)):
             with torch.cuda.device(ch.m.device):
-                part = self._buf(i, "part_h", W * per, 32, torch.float16, ch.m.device)
-                st = self._buf(i, "slice_status", 8, 0, torch.int32, ch.m.device)
+                part = self._buf((lane, i), "part_h", W * per, 32, torch.float16, ch.m.device)
+                st = self._buf((lane, i), "slice_status", 8, 0, torch.int32, ch.m.device)
                 check(lib.gnr_project_slice_points(ch.m._handle, _ptr(allp), 3, W * per, _ptr(part), _ptr(st), _stream()),
                       "gnr_project_slice_points")
                 parts.append(part)
         tm.mark("partial projection (all points)")
-        recvs = [self._buf(i, "recv_h", W * per, 32, torch.float16, ch.m.device) for i, ch in enumerate(chunks)]
+        recvs = [self._buf((lane, i), "recv_h", W * per, 32, torch.float16, ch.m.device) for i, ch in enumerate(chunks)]
         self.comm.all_to_all_equal(parts, recvs)
         tm.mark("all-to-all of fp16 partial rows")
         pix = []
         for i, (ch, recv, pts) in enumerate(zip(chunks, recvs, rows6)):
             with torch.cuda.device(ch.m.device):
                 na = ch.num_app
-                feats = self._buf(i, "feats", na, ch.m.app_dim, torch.float32, ch.m.device)
+                feats = self._buf((lane, i), "feats", na, ch.m.app_dim, torch.float32, ch.m.device)
                 if na:
                     check(lib.gnr_sum_partials(ch.m._handle, _ptr(recv), W, na, per, _ptr(feats), _stream()), "gnr_sum_partials")
-                rgb_s = mlp_features(ch.m, feats[:na], pts[:na, 3:6].contiguous())
+                rgb_s = mlp_features(ch.m, feats[:na], pts[:na, 3:6].contiguous(), lane)
                 pix.append(ch.composite(rgb_s, white_bg))
         tm.mark("sum + MLP + composite (own rays)")
-        return self._gather_pixels(rays, chunks, shares, pix)
+        result.extend(self._gather_pixels(rays, chunks, shares, pix))
 
     def _gather_pixels(self, rays, chunks, shares, pix):
         """Pixels of every rank -> every rank (padded to the largest share)."""
@@ -786,12 +855,6 @@ class BlockParallelRenderer:
                 result.append(ch.composite(rgb_s, white_bg))
         tm.mark("composite")
 
-    def _lane_stream(self, lane: int, device) -> torch.cuda.Stream:
-        key = (lane, str(device))
-        if key not in self._streams:
-            self._streams[key] = torch.cuda.Stream(device=device)
-        return self._streams[key]
-
     @torch.no_grad()
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
@@ -809,46 +872,7 @@ class BlockParallelRenderer:
         chunks).  Two chunks are in flight, each on its own stream; returns per chunk what ``render_chunk``
         returns.  Only the single-process-per-rank form overlaps; with several local ranks (loopback) the
         lanes still alternate but share the current device's streams."""
-        n = len(chunk_list)
-        results = [[] for _ in range(n)]
         self.samples = {"valid": 0, "app": 0}
-        if n == 0:
-            return results
-        dev = self.samplers[0].device
-        cur = torch.cuda.current_stream(dev)
-        lanes = max(1, min(lanes, n))
-        streams = [self._lane_stream(l, dev) for l in range(lanes)]
-        for st in streams:
-            st.wait_stream(cur)
         self.timer.start()
-        gens = [None] * lanes
-        nxt = 0
-
-        def advance(l, steps):
-            with torch.cuda.stream(streams[l]):
-                for _ in range(steps):
-                    try:
-                        next(gens[l])
-                    except StopIteration:
-                        gens[l] = None
-                        return
-
-        # every lane takes chunks in turn; a turn is two steps (one that ends in a host read, one that does not)
-        active = True
-        while active:
-            active = False
-            for l in range(lanes):
-                if gens[l] is None and nxt < n:
-                    gens[l] = self._steps(chunk_list[nxt], n_samples, white_bg, l, results[nxt])
-                    nxt += 1
-                if gens[l] is not None:
-                    advance(l, 2)
-                    active = True
-            active = active or nxt < n
-        for st in streams:
-            cur.wait_stream(st)
-        for per_chunk in results:  # made on a lane's stream, read by the caller on the current one
-            for rgb, depth in per_chunk:
-                rgb.record_stream(cur)
-                depth.record_stream(cur)
-        return results
+        return _run_lanes(lambda c, lane, out: self._steps(chunk_list[c], n_samples, white_bg, lane, out), len(chunk_list),
+                          lanes, self.samplers[0].device, self._streams, 2)

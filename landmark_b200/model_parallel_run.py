@@ -143,9 +143,21 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
         shard.assemble(rgb, image)
         stats["valid"], stats["app"] = ren.samples["valid"], ren.samples["app"]
 
+    def frame_channels(lanes=int(os.environ.get('GNR_LANES', '2'))):
+        """Channel layout: every rank walks the whole frame; the chunks go through the renderer's two-lane pipeline."""
+        parts = parts_of_frame()
+        res = ren.render_frame([[p[2]] for p in parts], S, True, lanes=lanes)
+        stats["valid"], stats["app"] = ren.samples["valid"], ren.samples["app"]
+        for (lo, hi, _), per_chunk in zip(parts, res):
+            if hi > lo:
+                rgb[lo:hi] = per_chunk[0][0]
+        image[shard.all_pixels] = rgb
+
     def frame():
         if workload == "city_blocks":
             return frame_blocks()
+        if ren._fp16_exchange():
+            return frame_channels()
         stats["valid"] = stats["app"] = 0
         for c in range(n_chunks):
             lo, hi = min(c * chunk, n_local), min((c + 1) * chunk, n_local)
@@ -181,6 +193,8 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
     ren.timer.enabled = True
     if workload == "city_blocks":
         frame_blocks(lanes=1)  # one lane: the sections of a chunk follow each other on one stream
+    elif ren._fp16_exchange():
+        frame_channels(lanes=1)
     else:
         frame()
     sections = {k: round(v, 3) for k, v in ren.timer.collect().items()}

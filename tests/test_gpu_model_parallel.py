@@ -49,6 +49,15 @@ def test_channel_parallel_matches_unsplit_oracle(world, mlp_mode):
         _check(rgb, depth, ref)
     for rgb, depth in outs[1:]:
         assert torch.equal(rgb, outs[0][0])  # every rank ends with the same image
+    # the frame form (two chunks in flight with the fp16 exchange) gives the bits of chunk-by-chunk calls
+    cuts = [0, 1500, 2600, rays.shape[0]]
+    chunk_list = [[rays[lo:hi].cuda()] * world for lo, hi in zip(cuts[:-1], cuts[1:])]
+    want = [ren.render_chunk(c, spec.n_samples, True) for c in chunk_list]
+    res = ren.render_frame(chunk_list, spec.n_samples, True, lanes=2)
+    torch.cuda.synchronize()
+    for w_c, r_c in zip(want, res):
+        for (a, b), (c, d) in zip(w_c, r_c):
+            assert torch.equal(a, c) and torch.equal(b, d)
 
 
 def _block_scene(division, grid=32, seed0=100):
