@@ -44,6 +44,8 @@ APP_BYTES_PER_SAMPLE = 2316         # 3 planes x 4 corners x 48 ch x 4 B + 12 B 
 # 128 B per clock to its register files.
 DENSITY_L1_BYTES_PER_SAMPLE = 18 * 16 * 4   # (4 plane + 2 line taps) x 3 pairs x 16 ch x 4 B
 APP_L1_BYTES_PER_SAMPLE = 18 * 48 * 4       # halved by fp16 storage
+# fp16 weight operands a 128-sample tile's GEMMs read from shared memory: basis 144x32, W1 160x128, W2 144x128, W3 128x16
+FUSED_WEIGHT_OPERAND_BYTES_PER_TILE = 2 * (144 * 32 + 160 * 128 + 144 * 128 + 128 * 16)
 L1_BYTES_PER_CLOCK_PER_SM = 128
 MLP_FLOP_PER_SAMPLE = 71936         # 2 * (150*128 + 128*128 + 128*3)
 BASIS_FLOP_PER_SAMPLE = 7776        # 2 * 144 * 27 (done inside the appearance gather kernel)
@@ -234,6 +236,11 @@ def main():
     import torch.distributed as dist
 
     if world > 1:
+        # The model-parallel layouts move their samples with counted all-to-alls (point-to-point copies between
+        # GPU pairs).  NCCL's default channel count gave 317 GB/s per direction between two B200s; 64 channels gave
+        # 532 GB/s (456 MB per rank, measured).  Set before the communicator is made; an outer setting wins.
+        for key in ("NCCL_MIN_P2P_NCHANNELS", "NCCL_MAX_P2P_NCHANNELS", "NCCL_MAX_NCHANNELS"):
+            os.environ.setdefault(key, "64")
         dist.init_process_group("nccl", device_id=torch.device(device))
     if a.workload in ("city_blocks", "city_channels"):
         from landmark_b200.model_parallel_run import run as run_model_parallel
@@ -664,6 +671,12 @@ def main():
                                        else "tcgen05 kernel (basis + MLP)")}
         if fused_app:
             roof["mlp_kernel"]["l1_to_register"] = l1_roof(app_l1_bytes, n_app, per_launch["mlp"])
+            # everything the SM's L1 / shared-memory port moves for a sample: its texels into registers plus its share
+            # (1/128) of the 91 KB of weight operands the four GEMMs of a 128-sample tile fetch from shared memory
+            port = l1_roof(app_l1_bytes + FUSED_WEIGHT_OPERAND_BYTES_PER_TILE // 128, n_app, per_launch["mlp"])
+            port["what"] = ("texel bytes into registers + weight-operand bytes of the tile's MMAs out of shared memory, against "
+                            "the measured L1->register rate (the operand fetch shares that port; its own ceiling is not measured)")
+            roof["mlp_kernel"]["l1_port"] = port
     dominant = max(roof, key=lambda k: roof[k]["ms_per_frame"]) if roof else None
     roofline = None
     if dominant:

@@ -608,33 +608,46 @@ class ChannelParallelRenderer:
                 rgb_s = mlp_features(ch.m, feats[:na], pts[:na, 3:6].contiguous(), lane)
                 pix.append(ch.composite(rgb_s, white_bg))
         tm.mark("sum + MLP + composite (own rays)")
-        result.extend(self._gather_pixels(rays, chunks, shares, pix))
+        result.extend(self._gather_pixels(rays, chunks, shares, pix, lane))
 
-    def _gather_pixels(self, rays, chunks, shares, pix):
-        """Pixels of every rank -> every rank (padded to the largest share)."""
+    def _pixel_source(self, n: int, device):
+        """For a chunk of ``n`` rays: rows per rank in the gathered pixel list, and for every ray the row that holds
+        it (rank r's share starts at row r * per_rays; inside a share the rays keep their order)."""
+        key = ("pix", n, str(device))
+        cache = self.__dict__.setdefault("_shares", {})
+        if key not in cache:
+            W, G = self.comm.world, self.RAY_GROUP
+            j = torch.arange(n, device=device)
+            group = j // G
+            n_groups = -(-n // G)
+            # a rank's share: its full groups, and the last (possibly short) group if that one is its own
+            sizes = [sum(min(G, n - g * G) for g in range(r, n_groups, W)) for r in range(W)]
+            per_rays = max(1, max(sizes))
+            cache[key] = (per_rays, (group % W) * per_rays + (group // W) * G + j % G)
+        return cache[key]
+
+    def _gather_pixels(self, rays, chunks, shares, pix, lane: int = 0):
+        """Pixels of every rank -> every rank: one all-gather of (rgb, depth) rows padded to the largest share, one
+        indexed read that puts them back in ray order."""
         W = self.comm.world
         n = rays[0].shape[0]
-        per_rays = max(1, max(int(self._ray_share(n, r, "cpu").numel()) for r in range(W)))
-        packed = []
-        for ch, share, (rgb, depth) in zip(chunks, shares, pix):
+        packed, gathered, sources = [], [], []
+        for i, (ch, share, (rgb, depth)) in enumerate(zip(chunks, shares, pix)):
             with torch.cuda.device(ch.m.device):
-                buf = torch.zeros((per_rays, 4), dtype=torch.float32, device=ch.m.device)
+                per_rays, src = self._pixel_source(n, ch.m.device)
+                buf = self._buf((lane, i), "pix_own", per_rays, 4, torch.float32, ch.m.device)
                 k = share.numel()
                 buf[:k, :3] = rgb[:k]
                 buf[:k, 3] = depth[:k]
                 packed.append(buf)
-        gathered = self.comm.all_gather_rows(packed)
+                gathered.append(self._buf((lane, i), "pix_all", W * per_rays, 4, torch.float32, ch.m.device))
+                sources.append(src)
+        self.comm.all_gather_into(packed, gathered)
         out = []
-        for ch, g in zip(chunks, gathered):
+        for ch, g, src in zip(chunks, gathered, sources):
             with torch.cuda.device(ch.m.device):
-                rgb = torch.empty((n, 3), dtype=torch.float32, device=ch.m.device)
-                depth = torch.empty((n,), dtype=torch.float32, device=ch.m.device)
-                for r in range(W):
-                    share = self._ray_share(n, r, ch.m.device)
-                    k = share.numel()
-                    rgb[share] = g[r * per_rays:r * per_rays + k, :3]
-                    depth[share] = g[r * per_rays:r * per_rays + k, 3]
-                out.append((rgb, depth))
+                sel = torch.index_select(g, 0, src)
+                out.append((sel[:, :3].contiguous(), sel[:, 3].contiguous()))
         self.timer.mark("all-gather pixels")
         return out
 
