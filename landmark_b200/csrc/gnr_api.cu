@@ -1017,7 +1017,7 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   if (m->cfg.ert_transmittance >= 0.0f) {
     // fused density + weights pass (with early ray termination when the threshold is > 0)
     StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
-    GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st));
+    GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st, /*list_only=*/1));
   } else {
     {
       StageScope sc(m, GNR_STAGE_DENSITY, 1, st);
@@ -1030,7 +1030,7 @@ static int render_chunk_impl(GnrModel* m, const float* rays, int64_t n, int S, i
   }
   {
     StageScope sc(m, GNR_STAGE_COMPACT_APP, 4, st);
-    GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st));
+    GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st, /*packed=*/m->cfg.ert_transmittance >= 0.0f ? 1 : 0));
   }
   if (gnr_app_fusable(m)) {
     // gather + basis projection + MLP as one kernel: no operand of a sample leaves the SM

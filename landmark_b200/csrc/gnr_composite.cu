@@ -109,6 +109,38 @@ expand_app_kernel(const float* __restrict__ weight, const uint32_t* __restrict__
   }
 }
 
+// The same list from the packed output of the march (list_only): ray r's j-th appearance sample is the pair
+// (weight, sample number) at packed[offsets[r] + j]; no walk over weights or validity bits.
+// (app_index, the valid-list index of an entry, is not produced: nothing in the frame loop reads it.)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+expand_app_packed_kernel(const float2* __restrict__ packed, int kbits,
+                         const int32_t* __restrict__ offsets, const int32_t* __restrict__ app_counts,
+                         const int32_t* __restrict__ app_offsets, int64_t n_rays, long long capacity, long long app_capacity,
+                         uint32_t* __restrict__ app_ids, float* __restrict__ app_weight) {
+  const int lane = threadIdx.x & 31;
+  const int64_t group = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (group * 32 >= n_rays) return;
+  const int64_t ray = group * 32 + lane;
+  const bool has_ray = ray < n_rays;
+  int left = has_ray ? app_counts[ray] : 0;
+  long long i = has_ray ? offsets[ray] : 0;
+  const long long end = has_ray ? min((long long)offsets[ray + 1], capacity) : 0;
+  AppGroupWalk walk;
+  walk.pos = app_offsets[group * 32];
+  long long at;
+  while (walk.step(lane, left > 0, at)) {
+    if (left > 0) {
+      if (i < end && at < app_capacity) {
+        const float2 wk = __ldg(packed + i);
+        app_ids[at] = ((uint32_t)ray << kbits) | (uint32_t)__float_as_int(wk.y);
+        app_weight[at] = wk.x;
+      }
+      ++i;
+      --left;
+    }
+  }
+}
+
 // rgb_map = sum_j w_j rgb_j (+ 1 - acc), clamp to [0,1]; depth_map = sum w t
 // (app/models/gridnerf_sequential.py:493-501).  One thread per ray, ranks in order.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -161,13 +193,20 @@ int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, 
 }
 
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                       int64_t max_valid, int64_t max_app, cudaStream_t st) {
+                       int64_t max_valid, int64_t max_app, cudaStream_t st, int packed) {
   int32_t* app_offsets = (int32_t*)(ws + L.app_offsets);
   int e = launch_exclusive_scan((const int32_t*)(ws + L.app_counts), app_offsets, (int32_t*)(ws + L.block_sums), n,
                                 (int32_t*)(ws + L.status), GNR_ST_NUM_APP, GNR_ST_OVERFLOW_APP, max_app, st);
   if (e) return e;
   const int64_t groups = (n + 31) / 32;
   unsigned blocks = (unsigned)((groups + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  if (packed) {
+    expand_app_packed_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+        (const float2*)(ws + L.sigma), p.kbits, (const int32_t*)(ws + L.offsets),
+        (const int32_t*)(ws + L.app_counts), app_offsets, n, (long long)max_valid, (long long)max_app,
+        (uint32_t*)(ws + L.app_ids), (float*)(ws + L.app_weight));
+    return (int)cudaGetLastError();
+  }
   expand_app_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>((const float*)(ws + L.weight), (const uint32_t*)(ws + L.words),
                                                            p.words, p.kbits, m->cfg.ray_weight_thres,
                                                            (const int32_t*)(ws + L.offsets),

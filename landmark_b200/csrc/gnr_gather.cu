@@ -422,7 +422,7 @@ march_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, const float* __
              const uint32_t* __restrict__ words, const int32_t* __restrict__ offsets, long long n_rays, long long capacity,
              float shift, int act, float distance_scale, float thres, float t_stop, float* __restrict__ weight,
              float* __restrict__ acc_out, float* __restrict__ depth_out, int32_t* __restrict__ app_counts,
-             int32_t* __restrict__ evaluated_total) {
+             int32_t* __restrict__ evaluated_total, int list_only, float2* __restrict__ packed) {
   __shared__ int s_evaluated;
   if (threadIdx.x == 0) s_evaluated = 0;
   __syncthreads();
@@ -459,7 +459,13 @@ march_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, const float* __
         const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
         const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-sg, __fmul_rn(dist, distance_scale))));
         const float w = alpha * T;
-        weight[i] = w;
+        if (list_only) {
+          // the frame loop reads nothing but the samples that pass the appearance threshold: they go, as (weight,
+          // sample number) pairs of 8 bytes, to the front of the ray's own range of the pair array, in order
+          if (w > thres) packed[beg + n_app] = make_float2(w, __int_as_float(k));
+        } else {
+          weight[i] = w;
+        }
         acc += w;
         dep = fmaf(w, t, dep);
         n_app += (w > thres) ? 1 : 0;
@@ -468,7 +474,9 @@ march_kernel(GnrSampleParams p, PlaneSet planes, LatticeRef lat, const float* __
         if (T < t_stop) break;
       }
       evaluated = (int)(i - beg);
-      for (; i < end; ++i) weight[i] = 0.0f;
+      // Weights behind the stop are zero (written for callers that look at the weight array itself).
+      if (!list_only)
+        for (; i < end; ++i) weight[i] = 0.0f;
     }
     acc_out[ray] = acc;
     depth_out[ray] = dep;
@@ -1004,7 +1012,7 @@ int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoord
 }
 
 int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
-                 cudaStream_t st) {
+                 cudaStream_t st, int list_only) {
   PlaneSet set = make_set(m->den, m->cfg.n_pairs);
   const int J = m->den[0].C / 16;
   const unsigned grid = (unsigned)((n + kMarchBlock - 1) / kMarchBlock);
@@ -1016,7 +1024,7 @@ int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays,
       p, set, lat, rays, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words), (const int32_t*)(ws + L.offsets), \
       (long long)n, L.max_valid, m->cfg.density_shift, m->cfg.density_act, m->cfg.distance_scale,                 \
       m->cfg.ray_weight_thres, t_stop, (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth),     \
-      (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY)
+      (int32_t*)(ws + L.app_counts), (int32_t*)(ws + L.status) + GNR_ST_NUM_DENSITY, list_only, (float2*)(ws + L.sigma))
   if (m->den_lattice) GNR_MARCH_H(1, 3, false, true);
   else if (m->cfg.den_storage == 1 && standard_vm3(set)) GNR_MARCH_H(1, 3, true, false);
   else if (m->cfg.den_storage == 1) GNR_MARCH_H(1, 0, true, false);

@@ -163,11 +163,16 @@ int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords&
                    cudaStream_t st);
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                         int64_t max_valid, cudaStream_t st);
+// (`packed`: the march ran with list_only)
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                       int64_t max_valid, int64_t max_app, cudaStream_t st);
+                       int64_t max_valid, int64_t max_app, cudaStream_t st, int packed = 0);
 // Fused density gather + transmittance scan + early termination, one warp per ray.
+// (`list_only`: instead of one weight per valid sample, write only the samples above the appearance threshold, packed
+// at the front of every ray's range as 8-byte (weight, sample number) pairs in the sigma + weight arrays, which lie
+// back to back in the workspace; what
+// launch_app_compact(..., packed = 1) reads)
 int launch_march(const GnrModel* m, const GnrSampleParams& p, const float* rays, int64_t n, char* ws, const GnrWs& L,
-                 cudaStream_t st);
+                 cudaStream_t st, int list_only = 0);
 int launch_app_gather(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, float* feat,
                       cudaStream_t st);
 int launch_app_products(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, unsigned char* prod_hi,
