@@ -309,6 +309,12 @@ int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_fe
  * ``app_index[max_app]`` (optional) receives the appearance list. */
 int gnr_weights_from_sigma(GnrModel* m, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
                            int64_t max_valid, int64_t max_app, const float* sigma, int32_t* app_index, void* stream);
+/* gnr_weights_from_sigma for a caller whose sigma values still lie in the order they came back from the block owners:
+ * the sigma of valid-list entry i is ``sigma_rows[rows[i]]`` (``rows`` = the dest_row output of gnr_route_blocks), read in
+ * place.  Leaves the appearance list (ids, weights, counts, offsets) in the workspace for gnr_route_blocks /
+ * gnr_composite_rgb; the per-sample weight array and the valid-list index of the entries are not produced. */
+int gnr_weights_from_rows(GnrModel* m, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
+                          int64_t max_valid, int64_t max_app, const float* sigma_rows, const int32_t* rows, void* stream);
 /* compute_appfeature only (gather + basis projection; on the tensor cores with mlp_mode 1/2, in fp32
  * on the CUDA cores with mode 0) for the appearance list of the workspace: with a channel slice of
  * the planes and the matching columns of basis_mat these are the partial sums a tensor-parallel

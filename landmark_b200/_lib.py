@@ -88,6 +88,7 @@ SIGNATURES = {
     "gnr_points_scratch_bytes": (_INT, [_P, _I64, C.POINTER(_SZ)]),
     "gnr_appearance_points": (_INT, [_P, _P, _P, _I64, _P, _SZ, _P, _P, _P]),
     "gnr_appearance_rows": (_INT, [_P, _P, _I64, _P, _SZ, _P, _P]),
+    "gnr_weights_from_rows": (_INT, [_P, _I64, C.c_int, _P, _SZ, _I64, _I64, _P, _P, _P]),
     "gnr_project_slice_points": (_INT, [_P, _P, C.c_int, _I64, _P, _P, _P]),
     "gnr_sum_partials": (_INT, [_P, _P, C.c_int, _I64, _I64, _P, _P]),
     "gnr_app_features_points": (_INT, [_P, _P, _I64, _P, _SZ, _P, _P]),

@@ -1401,6 +1401,24 @@ extern "C" int gnr_weights_from_sigma(GnrModel* m, int64_t n, int S, void* works
   return 0;
 }
 
+extern "C" int gnr_weights_from_rows(GnrModel* m, int64_t n, int S, void* workspace, size_t ws_bytes, int64_t max_valid,
+                                     int64_t max_app, const float* sigma_rows, const int32_t* rows, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!sigma_rows || !rows) {
+    gnr_set_error("gnr_weights_from_rows: null sigma_rows or rows");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  GNR_LAUNCH_OK(launch_weights_only(m, p, n, ws, L, max_valid, st, sigma_rows, rows));
+  GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st, /*packed=*/1));
+  return 0;
+}
+
 extern "C" int gnr_app_features(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
                                 int64_t max_valid, int64_t max_app, float* features, int64_t n_features, void* stream) {
   int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);

@@ -17,7 +17,11 @@ __global__ void __launch_bounds__(128)
 weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float* __restrict__ t_min_arr,
                const uint32_t* __restrict__ ids, const float* __restrict__ sigma, const int32_t* __restrict__ offsets,
                int64_t n_rays, long long capacity, float* __restrict__ weight, float* __restrict__ acc_out,
-               float* __restrict__ depth_out, int32_t* __restrict__ app_counts) {
+               float* __restrict__ depth_out, int32_t* __restrict__ app_counts, const int32_t* __restrict__ rows,
+               float2* __restrict__ packed) {
+  // `rows`: sigma of list entry i is sigma[rows[i]] (answers of block owners, still in the order they were sent).
+  // `packed`: write only the samples above the appearance threshold, as (weight, sample) pairs at the front of the
+  // ray's range (the form expand_app_packed_kernel reads); sigma must then not live in the workspace's own arrays.
   const int64_t ray = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (ray >= n_rays) return;
   const long long beg = offsets[ray], end = min((long long)offsets[ray + 1], capacity);
@@ -32,9 +36,14 @@ weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float
       const float t = gnr_sample_t(p, t_min, k);
       // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
       const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
-      const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-__ldg(sigma + i), __fmul_rn(dist, distance_scale))));
+      const float sg = __ldg(sigma + (rows ? (long long)__ldg(rows + i) : i));
+      const float alpha = __fsub_rn(1.0f, expf(__fmul_rn(-sg, __fmul_rn(dist, distance_scale))));
       const float w = alpha * T;
-      weight[i] = w;
+      if (packed) {
+        if (w > thres) packed[beg + n_app] = make_float2(w, __int_as_float(k));
+      } else {
+        weight[i] = w;
+      }
       acc += w;
       dep = fmaf(w, t, dep);
       n_app += (w > thres) ? 1 : 0;
@@ -183,12 +192,14 @@ composite_kernel(const float* __restrict__ app_weight, const int32_t* __restrict
 }  // namespace
 
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                        int64_t max_valid, cudaStream_t st) {
+                        int64_t max_valid, cudaStream_t st, const float* sigma_rows, const int32_t* rows) {
   unsigned blocks = (unsigned)((n + 127) / 128);
+  const bool ext = sigma_rows != nullptr;  // owners' answers read in place through `rows`, packed output
   weights_kernel<<<blocks, 128, 0, st>>>(
       p, m->cfg.distance_scale, m->cfg.ray_weight_thres, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids),
-      (const float*)(ws + L.sigma), (const int32_t*)(ws + L.offsets), n, (long long)max_valid, (float*)(ws + L.weight),
-      (float*)(ws + L.acc), (float*)(ws + L.depth), (int32_t*)(ws + L.app_counts));
+      ext ? sigma_rows : (const float*)(ws + L.sigma), (const int32_t*)(ws + L.offsets), n, (long long)max_valid,
+      (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth), (int32_t*)(ws + L.app_counts),
+      ext ? rows : nullptr, ext ? (float2*)(ws + L.sigma) : nullptr);
   return (int)cudaGetLastError();
 }
 

@@ -161,8 +161,10 @@ GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L);
 GnrCoords gnr_coords_app(const float* rays, char* ws, const GnrWs& L);
 int launch_density(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* sigma_feat, float* sigma,
                    cudaStream_t st);
+// (`sigma_rows` + `rows`: sigma of list entry i is sigma_rows[rows[i]], read in place; the output is then the packed
+// form launch_app_compact(..., packed = 1) reads)
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
-                        int64_t max_valid, cudaStream_t st);
+                        int64_t max_valid, cudaStream_t st, const float* sigma_rows = nullptr, const int32_t* rows = nullptr);
 // (`packed`: the march ran with list_only)
 int launch_app_compact(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                        int64_t max_valid, int64_t max_app, cudaStream_t st, int packed = 0);

@@ -232,12 +232,13 @@ class _Chunk:
                                    self.max_app, which_list, division[0], division[1], _ptr(send), _ptr(dest),
                                    _ptr(counts), None, _stream()), "gnr_route_blocks")
 
-    def launch_weights(self, sigma_back: torch.Tensor, dest: torch.Tensor, full: torch.Tensor):
-        """The owners' answers (send-buffer order) gathered into list order, then weights and the appearance list."""
-        if self.num_valid:
-            torch.index_select(sigma_back, 0, dest[: self.num_valid], out=full[: self.num_valid])
-        check(lib.gnr_weights_from_sigma(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
-                                         self.max_app, _ptr(full), None, _stream()), "gnr_weights_from_sigma")
+    def launch_weights(self, sigma_back: torch.Tensor, dest: torch.Tensor):
+        """Weights and the appearance list from the owners' answers, read in place (send-buffer order) through the row
+        every list entry went to."""
+        if sigma_back.numel() == 0:  # no valid sample in this chunk (an empty view has no address): nothing will be read
+            sigma_back = torch.zeros(1, dtype=torch.float32, device=self.m.device)
+        check(lib.gnr_weights_from_rows(self.m._handle, self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                        self.max_app, _ptr(sigma_back), _ptr(dest), _stream()), "gnr_weights_from_rows")
 
     def launch_march(self):
         check(lib.gnr_march(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
@@ -825,8 +826,7 @@ class BlockParallelRenderer:
         app_sends, app_dests = [], []
         for i, (ch, dest, sg) in enumerate(zip(chunks, dests, back)):
             with torch.cuda.device(ch.m.device):
-                full = self._buf(lane, i, "sigma_list", ch.max_valid, 0, torch.float32, ch.m.device)
-                ch.launch_weights(sg, dest, full)
+                ch.launch_weights(sg, dest)
                 tm.mark("weights")
                 send = self._buf(lane, i, "app_send", ch.max_app, 6, torch.float32, ch.m.device)
                 dest_a = self._buf(lane, i, "app_dest", ch.max_app, 0, torch.int32, ch.m.device)
