@@ -678,12 +678,16 @@ class B200GridNeRF(torch.nn.Module):
     @torch.no_grad()
     def render_rays(self, rays: torch.Tensor, N_samples=-1, white_bg=True, chunk: int = 262144,
                     rgb_out: Optional[torch.Tensor] = None, depth_out: Optional[torch.Tensor] = None,
-                    overlap=False):
+                    overlap=False, after: Optional["torch.cuda.Event"] = None):
         """Device-resident chunk loop: ``rays [N, 6]`` on the GPU -> ``rgb [N, 3]``, ``depth [N]``
-        written in place, one status check at the end instead of one per chunk.  With
+        written in place, one status check at the end instead of one per chunk.
         With ``overlap`` consecutive chunks rotate over that many side streams (``True`` = 2), each
         with its own workspace, so that one chunk's kernels run beside the other's: the stages are
-        bound by different units (issue slots, L1, tensor pipe)."""
+        bound by different units (issue slots, L1, tensor pipe).
+        ``after`` (with ``overlap``): the side streams wait for this event instead of for everything queued on the
+        current stream.  A caller that keeps several frames in flight passes the event that marks its output
+        buffers free (and makes sure the rays were ready before it): the next frame's first chunks then run
+        beside the previous frame's last chunk and its assembly instead of behind them."""
         rays = self._prepare(rays)
         n, s = rays.shape[0], self._samples(N_samples)
         if rgb_out is None:
@@ -701,7 +705,10 @@ class B200GridNeRF(torch.nn.Module):
                 if len(getattr(self, "_side_streams", None) or ()) < n_side:
                     self._side_streams = [torch.cuda.Stream(device=self.device) for _ in range(n_side)]
                 for st_ in self._side_streams[:n_side]:
-                    st_.wait_stream(main)
+                    if after is not None:
+                        st_.wait_event(after)
+                    else:
+                        st_.wait_stream(main)
             used = {}
             for ci, first in enumerate(range(0, n, chunk)):
                 m = min(chunk, n - first)
