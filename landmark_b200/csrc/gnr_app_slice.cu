@@ -33,6 +33,7 @@ struct SliceArgs {
   unsigned char* out;           // [n][32] fp16
   int32_t* status;
   uint32_t wait_limit;
+  int debug_skip_commit;        // test hook: group 0 of CTA 0 leaves out the commit of its first GEMM
 };
 
 template <int RP>
@@ -150,7 +151,8 @@ __global__ void __launch_bounds__(SliceGeom<RP>::kGroups * ST, 1) app_slice_proj
 #pragma unroll
       for (int ks = 0; ks < G::kSteps; ++ks)
         mma_f16_ts(f_tmem, a_tmem + ks * 8, make_desc(wb_addr + ks * 2 * KGB_BYTES, KGB_BYTES), kIdescBasis, ks > 0 ? 1u : 0u, leader);
-      mma_commit(mbar, leader);
+      const bool skip = a.debug_skip_commit != 0 && blockIdx.x == 0 && slot == 0 && tile == t_beg;
+      mma_commit(mbar, skip ? 0u : leader);
       __syncwarp();
     }
     if (!group_wait(mbar, parity, bar_id, row, s_flag, a.wait_limit)) {
@@ -248,6 +250,7 @@ int launch_app_slice_project(const GnrModel* m, const float* xyz, int stride, in
   a.out = (unsigned char*)features_h;
   a.status = status;
   a.wait_limit = m->debug_wait_limit > 0 ? (uint32_t)m->debug_wait_limit : kWaitLimit;
+  a.debug_skip_commit = m->debug_expire_wait;
   return cp == 16 ? launch_slice<1>(m, set, a, st) : (cp == 32 ? launch_slice<2>(m, set, a, st) : launch_slice<3>(m, set, a, st));
 }
 

@@ -335,3 +335,33 @@ def test_dynamic_block_window_follows_the_camera():
     full4, _ = everything.render_rays(rays4, 200, True)
     part4, _ = small.render_rays(rays4, 200, True)
     assert not torch.equal(full4, part4)
+
+
+def test_slice_projection_bounded_wait_expires_and_the_context_survives():
+    """The slice-projection kernel bounds its waits like the other tensor-core kernels: with the test hook one group
+    skips the commit its wait depends on, the status word reports the expired wait, the kernel frees its tensor
+    memory and returns, and the same call then gives the same rows as before."""
+    from landmark_b200._lib import check, lib
+    from landmark_b200.gridnerf import _ptr, _stream
+
+    spec = scenes.tiny_spec(grid=64).lit()
+    model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True)
+    g = torch.Generator().manual_seed(3)
+    xyz = (torch.rand((5000, 3), generator=g) * 1.8 - 0.9).cuda()
+
+    def project():
+        out = torch.zeros((xyz.shape[0], 32), dtype=torch.float16, device="cuda:0")
+        st = torch.zeros(8, dtype=torch.int32, device="cuda:0")
+        check(lib.gnr_project_slice_points(model._handle, _ptr(xyz), 3, xyz.shape[0], _ptr(out), _ptr(st), _stream()),
+              "gnr_project_slice_points")
+        torch.cuda.synchronize()
+        return out, st.cpu().tolist()
+
+    good, st = project()
+    assert st[4] == 0 and good.abs().max().item() > 0
+    model.debug_wait(expire=True, wait_limit=2000)
+    _, st = project()
+    assert st[4] == 1  # GNR_ST_WAIT_EXPIRED
+    model.debug_wait()
+    again, st = project()
+    assert st[4] == 0 and torch.equal(again, good)
