@@ -622,7 +622,10 @@ def main():
         model_parallel = {}
         for wl in ("city_blocks", "city_channels"):
             try:
-                res = run_model_parallel(wl, 3, 1, a.chunk_model_parallel, a.mlp_mode, rank, world, device, 1, False, ert=a.ert,
+                chunk_mp = a.chunk_model_parallel
+                if wl == "city_blocks":  # rays are tile-sharded there: at least four chunks per rank for the two-lane pipeline
+                    chunk_mp = min(chunk_mp, max(65536, -(-(H * W // world) // 4 // 4096) * 4096))
+                res = run_model_parallel(wl, 3, 1, chunk_mp, a.mlp_mode, rank, world, device, 1, False, ert=a.ert,
                                          app_fp16=bool(a.app_fp16), den_lattice=bool(a.den_lattice))
                 model_parallel[wl] = {"ms_per_frame": res["ms_per_frame"], "Mrays_per_s": res["rays"] / (res["ms_per_frame"] * 1e-3) / 1e6,
                                       "parallelism": res["parallelism"], "valid_samples": res["valid"],
