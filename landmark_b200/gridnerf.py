@@ -315,7 +315,7 @@ class B200GridNeRF(torch.nn.Module):
         cfg.ert_transmittance = self.ert_transmittance
         cfg.app_storage = 1 if self.app_plane_fp16 else 0
         cfg.den_storage = 1 if self.density_plane_fp16 else 0
-        # True / "groups": two groups of warps that each gather and run the MLP of their tile; "stream": gather warps
+        # True / "groups": three groups of warps that each gather and run the MLP of their tile; "stream": gather warps
         # feed MLP warps through tensor memory; False: separate kernels
         cfg.unfused_appearance = {True: 0, "groups": 0, "stream": 2, "two_groups": 3, False: 1}[self.fused_appearance]
         return cfg
