@@ -309,6 +309,24 @@ int gnr_density_points(GnrModel* m, const float* xyz, int64_t n, float* sigma_fe
  * ``app_index[max_app]`` (optional) receives the appearance list. */
 int gnr_weights_from_sigma(GnrModel* m, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
                            int64_t max_valid, int64_t max_app, const float* sigma, int32_t* app_index, void* stream);
+/* Block routing that ships ids instead of positions.  gnr_route_block_ids is gnr_route_blocks with one 32-bit id per row,
+ * ``(ray_base + ray) << gnr_sample_bits(n_samples) | sample``, in place of the block-local point (and view direction):
+ * a third (a sixth) of the bytes of a valid (appearance) sample on the wire.  The owner holds the rays and t_min of
+ * every rank of the chunk in one table (rank r's first ray at its ray_base) and recomputes each position from its ray
+ * with the SAMPLER's parametrisation and global box (``sampler``: the model the chunk was sampled with, on the same
+ * device), then expresses it in the coordinates of its own block with the arithmetic of assign_blocks_to_samples
+ * (app/models/gridnerf_parallel.py:296-327): gnr_density_list (sigma per id) and gnr_appearance_list (rgb per id; the
+ * one-kernel appearance path in list mode, view direction = the ray's) give the bits of gnr_density_points /
+ * gnr_appearance_rows on the rows gnr_route_blocks would have sent. */
+int gnr_query_one_kernel_appearance(const GnrModel* m); /* 1 if gnr_render_chunk / gnr_appearance_list run the one-kernel path */
+int gnr_route_block_ids(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace, size_t workspace_bytes,
+                        int64_t max_valid, int64_t max_app, int which_list, int px, int py, uint32_t ray_base,
+                        uint32_t* send_ids, int32_t* dest_row, int32_t* counts, void* stream);
+int gnr_density_list(GnrModel* owner, const GnrModel* sampler, const float* rays_all, const float* t_min_all,
+                     const uint32_t* ids, int64_t n, int n_samples, int px, int py, int block, float* sigma, void* stream);
+int gnr_appearance_list(GnrModel* owner, const GnrModel* sampler, const float* rays_all, const float* t_min_all,
+                        const uint32_t* ids, int64_t n, int n_samples, int px, int py, int block, void* scratch,
+                        size_t scratch_bytes, float* rgb, void* stream);
 /* gnr_weights_from_sigma for a caller whose sigma values still lie in the order they came back from the block owners:
  * the sigma of valid-list entry i is ``sigma_rows[rows[i]]`` (``rows`` = the dest_row output of gnr_route_blocks), read in
  * place.  Leaves the appearance list (ids, weights, counts, offsets) in the workspace for gnr_route_blocks /

@@ -89,6 +89,11 @@ SIGNATURES = {
     "gnr_appearance_points": (_INT, [_P, _P, _P, _I64, _P, _SZ, _P, _P, _P]),
     "gnr_appearance_rows": (_INT, [_P, _P, _I64, _P, _SZ, _P, _P]),
     "gnr_weights_from_rows": (_INT, [_P, _I64, C.c_int, _P, _SZ, _I64, _I64, _P, _P, _P]),
+    "gnr_route_block_ids": (_INT, [_P, _P, _I64, C.c_int, _P, _SZ, _I64, _I64, C.c_int, C.c_int, C.c_int, C.c_uint32,
+                                   _P, _P, _P, _P]),
+    "gnr_query_one_kernel_appearance": (_INT, [_P]),
+    "gnr_density_list": (_INT, [_P, _P, _P, _P, _P, _I64, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
+    "gnr_appearance_list": (_INT, [_P, _P, _P, _P, _P, _I64, C.c_int, C.c_int, C.c_int, C.c_int, _P, _SZ, _P, _P]),
     "gnr_project_slice_points": (_INT, [_P, _P, C.c_int, _I64, _P, _P, _P]),
     "gnr_sum_partials": (_INT, [_P, _P, C.c_int, _I64, _I64, _P, _P]),
     "gnr_app_features_points": (_INT, [_P, _P, _I64, _P, _SZ, _P, _P]),

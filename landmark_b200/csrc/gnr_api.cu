@@ -1382,6 +1382,109 @@ extern "C" int gnr_route_blocks(GnrModel* m, const float* rays, int64_t n, int S
   return 0;
 }
 
+extern "C" int gnr_query_one_kernel_appearance(const GnrModel* m) { return m ? gnr_app_fusable(m) : 0; }
+
+extern "C" int gnr_route_block_ids(GnrModel* m, const float* rays, int64_t n, int S, void* workspace, size_t ws_bytes,
+                                   int64_t max_valid, int64_t max_app, int which_list, int px, int py, uint32_t ray_base,
+                                   uint32_t* send_ids, int32_t* dest_row, int32_t* counts, void* stream) {
+  int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);
+  if (rc) return rc;
+  if (!rays || !send_ids || !dest_row || !counts || (which_list != 0 && which_list != 1)) {
+    gnr_set_error("gnr_route_block_ids: null rays / send_ids / dest_row / counts, or which_list not 0 (valid) / 1 (appearance)");
+    return -1;
+  }
+  const int kbits = gnr_sample_bits(S);
+  if (((uint64_t)ray_base + (uint64_t)n) >> (32 - kbits)) {
+    gnr_set_error("gnr_route_block_ids: ray number %llu does not fit the %d bits an id leaves for it",
+                  (unsigned long long)ray_base + (unsigned long long)n, 32 - kbits);
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  char* ws = (char*)workspace;
+  GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
+  GnrSampleParams p = gnr_sample_params(m, S);
+  const GnrCoords c = which_list == 0 ? gnr_coords_valid(rays, ws, L) : gnr_coords_app(rays, ws, L);
+  GNR_LAUNCH_OK(launch_route_blocks(m, p, c, px, py, 2, (float*)send_ids, dest_row, counts, nullptr, (cudaStream_t)stream, ray_base));
+  return 0;
+}
+
+// list-mode coordinates at a block owner: ids that carry ray numbers of the gathered ray table, the sampler's global
+// box in `p`, positions expressed in block `block` of a px x py division
+static int coords_owner_list(const char* who, const GnrModel* owner, const GnrModel* sampler, const float* rays_all,
+                             const float* t_min_all, const uint32_t* ids, int64_t n, int px, int py, int block, GnrCoords* c) {
+  if (!owner || !sampler || !rays_all || !t_min_all || !ids || n < 0 || n > 0x7fffffffLL) {
+    gnr_set_error("%s: null model, rays, t_min or ids, or a bad count", who);
+    return -1;
+  }
+  if (px < 1 || py < 1 || block < 0 || block >= px * py) {
+    gnr_set_error("%s: block %d is not one of %d x %d", who, block, px, py);
+    return -1;
+  }
+  if (owner->device != sampler->device) {
+    gnr_set_error("%s: sampler and owner live on different devices", who);
+    return -1;
+  }
+  memset(c, 0, sizeof(*c));
+  c->rays = rays_all;
+  c->t_min = t_min_all;
+  c->ids = ids;
+  c->point_stride = 3;
+  c->total_direct = n;
+  c->capacity = n;
+  c->blk_px = px;
+  c->blk_py = py;
+  c->blk_bx = block / py;
+  c->blk_by = block % py;
+  c->blk_pw = (float)(2.0 / px);
+  c->blk_ph = (float)(2.0 / py);
+  return 0;
+}
+
+extern "C" int gnr_density_list(GnrModel* owner, const GnrModel* sampler, const float* rays_all, const float* t_min_all,
+                                const uint32_t* ids, int64_t n, int S, int px, int py, int block, float* sigma, void* stream) {
+  GnrCoords c;
+  int rc = coords_owner_list("gnr_density_list", owner, sampler, rays_all, t_min_all, ids, n, px, py, block, &c);
+  if (rc) return rc;
+  rc = check_points(owner, "gnr_density_list", n, nullptr, (size_t)-1);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!sigma) {
+    gnr_set_error("gnr_density_list: null sigma");
+    return -1;
+  }
+  DeviceGuard g(owner->device);
+  const GnrSampleParams p = gnr_sample_params(sampler, S);  // the ray parametrisation and the global box are the sampler's
+  GNR_LAUNCH_OK(launch_density(owner, p, c, nullptr, sigma, (cudaStream_t)stream));
+  return 0;
+}
+
+extern "C" int gnr_appearance_list(GnrModel* owner, const GnrModel* sampler, const float* rays_all, const float* t_min_all,
+                                   const uint32_t* ids, int64_t n, int S, int px, int py, int block, void* scratch,
+                                   size_t scratch_bytes, float* rgb, void* stream) {
+  GnrCoords c;
+  int rc = coords_owner_list("gnr_appearance_list", owner, sampler, rays_all, t_min_all, ids, n, px, py, block, &c);
+  if (rc) return rc;
+  rc = check_points(owner, "gnr_appearance_list", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!rgb) {
+    gnr_set_error("gnr_appearance_list: null rgb");
+    return -1;
+  }
+  if (!gnr_app_fusable(owner)) {
+    gnr_set_error("gnr_appearance_list: needs the one-kernel appearance path (mlp_mode 2, fp16 appearance planes of 48 channels)");
+    return -1;
+  }
+  DeviceGuard g(owner->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = (char*)scratch;
+  const PointScratch Sc = point_scratch(owner, n);
+  const GnrSampleParams p = gnr_sample_params(sampler, S);
+  GNR_CUDA_OK(cudaMemsetAsync(sc + Sc.status, 0, GNR_ST_WORDS * 4, st));
+  GNR_LAUNCH_OK(launch_app_mlp_fused(owner, p, c, rgb, (int32_t*)(sc + Sc.status), st));
+  return 0;
+}
+
 extern "C" int gnr_weights_from_sigma(GnrModel* m, int64_t n, int S, void* workspace, size_t ws_bytes, int64_t max_valid,
                                       int64_t max_app, const float* sigma_in, int32_t* app_index, void* stream) {
   int rc = gnr_check_chunk(m, n, S, max_valid, max_app, workspace, ws_bytes);

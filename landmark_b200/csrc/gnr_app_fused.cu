@@ -84,6 +84,8 @@ struct FusedArgs {
   int lat_g[3];                  // its grid
   const float* feat;             // SRC 2: [n][feat_stride] fp32 projected features of the points
   int feat_stride;
+  int blk_px, blk_bx, blk_by;    // list mode at a block owner (blk_px > 0): positions, computed in the sampler's global
+  float blk_pw, blk_ph;          // box, are then expressed in the coordinates of block (blk_bx, blk_by)
 };
 
 struct RaySample {  // what a row needs of its list entry
@@ -275,9 +277,10 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       // ---- features straight from the projected-feature lattice: trilinear interpolation of this half's 16
       // channels (8 taps x 32 bytes, fp32 accumulation); no products, no projection GEMM -------------------
       const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
-      const float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
-      const float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
+      float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
+      float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
       const float z = POINTS ? cur.o[2] : gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
+      if (!POINTS && a.blk_px > 0) block_local((float)a.blk_bx, (float)a.blk_by, a.blk_pw, a.blk_ph, x, y, x, y);
       const Tap tx = make_tap(x, (float)(a.lat_g[0] - 1), a.lat_g[0]);
       const Tap ty = make_tap(y, (float)(a.lat_g[1] - 1), a.lat_g[1]);
       const Tap tz = make_tap(z, (float)(a.lat_g[2] - 1), a.lat_g[2]);
@@ -324,9 +327,10 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
       {
         // the sampler's own arithmetic for the position (gnr_sample_t, gnr_point), then normalize_coord
         const float t = POINTS ? 0.0f : gnr_sample_t(p, cur.t_min, cur.k);
-        const float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
-        const float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
+        float x = POINTS ? cur.o[0] : gnr_normalize(gnr_point(cur.o[0], cur.d[0], t), p.lo[0], p.inv[0]);
+        float y = POINTS ? cur.o[1] : gnr_normalize(gnr_point(cur.o[1], cur.d[1], t), p.lo[1], p.inv[1]);
         const float z = POINTS ? cur.o[2] : gnr_normalize(gnr_point(cur.o[2], cur.d[2], t), p.lo[2], p.inv[2]);
+        if (!POINTS && a.blk_px > 0) block_local((float)a.blk_bx, (float)a.blk_by, a.blk_pw, a.blk_ph, x, y, x, y);
         auto taps_of = [&](int pi) -> PairTapsH2 {
           const GnrPlane& pl = planes.p[pi];
           if (NP == 3) {
@@ -611,7 +615,7 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
     return -1;
   }
   const bool points = c.xyz_direct != nullptr || features != nullptr;
-  if (features ? (!c.view_direct) : (c.xyz_direct ? (!c.view_direct) : (!c.ids || c.index || !c.total_ptr))) {
+  if (features ? (!c.view_direct) : (c.xyz_direct ? (!c.view_direct) : (!c.ids || c.index || (!c.total_ptr && c.total_direct <= 0)))) {
     gnr_set_error("the fused appearance kernel walks an appearance list (ids + device count), explicit points with view "
                   "directions, or explicit features with view directions");
     return -1;
@@ -639,6 +643,11 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   for (int i = 0; i < 3; ++i) a.lat_g[i] = m->app_lat_dims[i];
   a.feat = features;
   a.feat_stride = feat_stride;
+  a.blk_px = points ? 0 : c.blk_px;
+  a.blk_bx = c.blk_bx;
+  a.blk_by = c.blk_by;
+  a.blk_pw = c.blk_pw;
+  a.blk_ph = c.blk_ph;
   auto launch = [&](auto kernel, int groups) -> int {
     cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFusedSmem);
     if (e != cudaSuccess) return (int)e;

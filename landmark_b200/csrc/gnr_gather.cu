@@ -758,6 +758,9 @@ GnrCoords gnr_coords_valid(const float* rays, char* ws, const GnrWs& L) {
   c.index = nullptr;
   c.xyz_direct = nullptr;
   c.view_direct = nullptr;
+  c.point_stride = 3;
+  c.blk_px = c.blk_py = c.blk_bx = c.blk_by = 0;
+  c.blk_pw = c.blk_ph = 0.0f;
   c.total_ptr = (const int32_t*)(ws + L.offsets) + L.n_rays;
   c.total_direct = 0;
   c.capacity = L.max_valid;

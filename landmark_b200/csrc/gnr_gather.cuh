@@ -28,6 +28,17 @@ __device__ __forceinline__ Tap make_tap(float u, float fsize, int size) {
   return t;
 }
 
+// Coordinates of a normalised position inside block (bx, by) of a division into blocks of width pw x ph: the
+// arithmetic of assign_blocks_to_samples (app/models/gridnerf_parallel.py:296-327), one rounded fp32 operation per
+// step in torch's order: coord_min = -1 + b * width, coord_max = -1 + (b + 1) * width,
+// local = (p - min) * 2 / (max - min) - 1.
+__device__ __forceinline__ void block_local(float bx, float by, float pw, float ph, float x, float y, float& lx, float& ly) {
+  const float x0 = __fadd_rn(-1.0f, __fmul_rn(bx, pw)), x1 = __fadd_rn(-1.0f, __fmul_rn(__fadd_rn(bx, 1.0f), pw));
+  const float y0 = __fadd_rn(-1.0f, __fmul_rn(by, ph)), y1 = __fadd_rn(-1.0f, __fmul_rn(__fadd_rn(by, 1.0f), ph));
+  lx = __fsub_rn(__fdiv_rn(__fmul_rn(__fsub_rn(x, x0), 2.0f), __fsub_rn(x1, x0)), 1.0f);
+  ly = __fsub_rn(__fdiv_rn(__fmul_rn(__fsub_rn(y, y0), 2.0f), __fsub_rn(y1, y0)), 1.0f);
+}
+
 // Normalised position of item i.  List mode: recomputed from the ray exactly as the sampler
 // computed it, then normalised as normalize_coord does (app/models/gridnerf_sequential.py:203-204).
 // `view` (optional) receives the ray direction of the sample.
@@ -53,6 +64,7 @@ __device__ __forceinline__ void sample_xyz(const GnrSampleParams& p, const GnrCo
   x = gnr_normalize(gnr_point(__ldg(r + 0), dx, t), p.lo[0], p.inv[0]);
   y = gnr_normalize(gnr_point(__ldg(r + 1), dy, t), p.lo[1], p.inv[1]);
   z = gnr_normalize(gnr_point(__ldg(r + 2), dz, t), p.lo[2], p.inv[2]);
+  if (c.blk_px > 0) block_local((float)c.blk_bx, (float)c.blk_by, c.blk_pw, c.blk_ph, x, y, x, y);
   if (view) {
     view[0] = dx;
     view[1] = dy;

@@ -132,6 +132,10 @@ struct GnrCoords {
   const float* xyz_direct;    // [n][3] normalised positions (point mode)
   const float* view_direct;   // [n][3] view directions (point mode)
   int point_stride;           // floats from one point's row to the next in xyz_direct / view_direct (3 when each is its own array)
+  // List mode at a block owner: the position, computed in the GLOBAL box of the sampler, is then expressed in the
+  // coordinates of block (blk_bx, blk_by) of a blk_px x blk_py division (blk_px == 0: no blocks).
+  int blk_px, blk_py, blk_bx, blk_by;
+  float blk_pw, blk_ph;       // 2 / px, 2 / py as fp32
   const int32_t* total_ptr;   // device count of items, or null ...
   long long total_direct;     // ... then this host count
   long long capacity;
@@ -195,8 +199,9 @@ int launch_sum_partials(const void* parts_h, int n_parts, int64_t rows, int64_t 
 void gnr_fused_k1_order(int* map);  // K order of the fused kernel's layer-1 operand (160 entries)
 int gnr_tc_basis_fused(const GnrModel* m);  // 1 if the tensor-core path also runs the basis projection
 int gnr_tc_tile_bytes(const GnrModel* m);   // bytes of one 128-sample product tile (products + the view group)
-int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int px, int py, int with_view, float* send,
-                        int32_t* dest, int32_t* counts, int32_t* block_of, cudaStream_t st);
+// (`mode` 0: rows of block-local points; 1: points + view directions; 2: 32-bit ids, (ray_base + ray) << kbits | sample)
+int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int px, int py, int mode, float* send,
+                        int32_t* dest, int32_t* counts, int32_t* block_of, cudaStream_t st, uint32_t ray_base = 0);
 int launch_positions(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* xyz, int32_t* ray_index,
                      cudaStream_t st);
 int launch_mlp_simt(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int feat_stride, const float* feat,

@@ -36,11 +36,7 @@ struct BlockGrid {
 __device__ __forceinline__ int assign_block(const BlockGrid& g, float x, float y, float& lx, float& ly) {
   const float u = __fdiv_rn(__fadd_rn(x, 1.0f), g.pw), v = __fdiv_rn(__fadd_rn(y, 1.0f), g.ph);
   const float bx = fminf(fmaxf(floorf(u), 0.0f), (float)(g.px - 1)), by = fminf(fmaxf(floorf(v), 0.0f), (float)(g.py - 1));
-  // coord_min = -1 + b * width, coord_max = -1 + (b + 1) * width; local = (p - min) * 2 / (max - min) - 1
-  const float x0 = __fadd_rn(-1.0f, __fmul_rn(bx, g.pw)), x1 = __fadd_rn(-1.0f, __fmul_rn(__fadd_rn(bx, 1.0f), g.pw));
-  const float y0 = __fadd_rn(-1.0f, __fmul_rn(by, g.ph)), y1 = __fadd_rn(-1.0f, __fmul_rn(__fadd_rn(by, 1.0f), g.ph));
-  lx = __fsub_rn(__fdiv_rn(__fmul_rn(__fsub_rn(x, x0), 2.0f), __fsub_rn(x1, x0)), 1.0f);
-  ly = __fsub_rn(__fdiv_rn(__fmul_rn(__fsub_rn(y, y0), 2.0f), __fsub_rn(y1, y0)), 1.0f);
+  block_local(bx, by, g.pw, g.ph, x, y, lx, ly);
   return (int)bx * g.py + (int)by;
 }
 
@@ -98,10 +94,15 @@ __global__ void __launch_bounds__(kMaxBlocks) route_scan_kernel(const int32_t* _
   }
 }
 
-template <bool WITH_VIEW>
+// MODE 0: rows of (block-local x, y, z); 1: the same plus the view direction; 2: one 32-bit id per row,
+// (ray_base + ray) << kbits | sample: the owner recomputes the position from the ray itself (it holds the rays of
+// every rank of the chunk, rank r's first ray at its ray_base), a third of the bytes on the wire for a valid sample
+// and a sixth for an appearance sample.
+template <int MODE>
 __global__ void __launch_bounds__(kRouteBlock)
 route_scatter_kernel(GnrSampleParams p, GnrCoords crd, BlockGrid g, int n_blocks, const int32_t* __restrict__ cta_base,
-                     float* __restrict__ send, int32_t* __restrict__ dest, int32_t* __restrict__ block_of) {
+                     float* __restrict__ send, int32_t* __restrict__ dest, int32_t* __restrict__ block_of, uint32_t ray_base) {
+  constexpr bool WITH_VIEW = MODE == 1;
   __shared__ int s_run[kMaxBlocks];                 // next free row of every block for this CTA
   __shared__ int s_warp[kRouteWarps][kMaxBlocks];   // entries of a block per warp in the current step
   if (threadIdx.x < kMaxBlocks)
@@ -132,14 +133,19 @@ route_scatter_kernel(GnrSampleParams p, GnrCoords crd, BlockGrid g, int n_blocks
     if (b >= 0) {
       int row = s_run[b] + rank_in_warp;
       for (int w = 0; w < warp; ++w) row += s_warp[w][b];
-      float* out = send + (size_t)row * kStride;
-      out[0] = lx;
-      out[1] = ly;
-      out[2] = z;
-      if (WITH_VIEW) {
-        out[3] = view[0];
-        out[4] = view[1];
-        out[5] = view[2];
+      if (MODE == 2) {
+        const uint32_t id = __ldg(crd.ids + i);
+        reinterpret_cast<uint32_t*>(send)[row] = id + (ray_base << p.kbits);
+      } else {
+        float* out = send + (size_t)row * kStride;
+        out[0] = lx;
+        out[1] = ly;
+        out[2] = z;
+        if (WITH_VIEW) {
+          out[3] = view[0];
+          out[4] = view[1];
+          out[5] = view[2];
+        }
       }
       dest[i] = row;
       if (block_of) block_of[i] = b;
@@ -157,8 +163,8 @@ route_scatter_kernel(GnrSampleParams p, GnrCoords crd, BlockGrid g, int n_blocks
 
 }  // namespace
 
-int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int px, int py, int with_view, float* send,
-                        int32_t* dest, int32_t* counts, int32_t* block_of, cudaStream_t st) {
+int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, int px, int py, int mode, float* send,
+                        int32_t* dest, int32_t* counts, int32_t* block_of, cudaStream_t st, uint32_t ray_base) {
   const int n_blocks = px * py;
   if (px < 1 || py < 1 || n_blocks > kMaxBlocks) {
     gnr_set_error("block routing supports 1..%d blocks (got %d x %d)", kMaxBlocks, px, py);
@@ -185,9 +191,11 @@ int launch_route_blocks(GnrModel* m, const GnrSampleParams& p, const GnrCoords& 
   g.ph = (float)(2.0 / py);
   route_count_kernel<<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_counts);
   route_scan_kernel<<<1, kMaxBlocks, 0, st>>>(cta_counts, n_ctas, n_blocks, cta_base, counts);
-  if (with_view)
-    route_scatter_kernel<true><<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_base, send, dest, block_of);
+  if (mode == 2)
+    route_scatter_kernel<2><<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_base, send, dest, block_of, ray_base);
+  else if (mode == 1)
+    route_scatter_kernel<1><<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_base, send, dest, block_of, 0u);
   else
-    route_scatter_kernel<false><<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_base, send, dest, block_of);
+    route_scatter_kernel<0><<<n_ctas, kRouteBlock, 0, st>>>(p, c, g, n_blocks, cta_base, send, dest, block_of, 0u);
   return (int)cudaGetLastError();
 }

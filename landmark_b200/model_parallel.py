@@ -220,9 +220,18 @@ class _Chunk:
         self.num_valid = int(st[_lib.ST_NUM_VALID])
 
     # -- launch-only forms (no host read: the caller reads status and counts together, once per exchange) --
-    def launch_sample(self):
+    def launch_sample(self, t_min: Optional[torch.Tensor] = None):
+        """``t_min``: also copy the rays' entry distances out (``[n]``; a block owner recomputes positions from them)."""
         check(lib.gnr_sample(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
-                             None, None, None, None, None, _stream()), "gnr_sample")
+                             _ptr(t_min), None, None, None, None, _stream()), "gnr_sample")
+
+    def launch_route_ids(self, which_list: int, division: Tuple[int, int], ray_base: int, send_ids: torch.Tensor,
+                         dest: torch.Tensor, counts: torch.Tensor):
+        """gnr_route_block_ids: like ``launch_route`` with one 32-bit id per row instead of the point."""
+        counts.zero_()
+        check(lib.gnr_route_block_ids(self.m._handle, _ptr(self.rays), self.n, self.s, self.ws, self.ws_bytes, self.max_valid,
+                                      self.max_app, which_list, division[0], division[1], int(ray_base), _ptr(send_ids),
+                                      _ptr(dest), _ptr(counts), _stream()), "gnr_route_block_ids")
 
     def launch_route(self, which_list: int, division: Tuple[int, int], send: torch.Tensor, dest: torch.Tensor,
                      counts: torch.Tensor):
@@ -767,6 +776,8 @@ class BlockParallelRenderer:
         self._bufs: Dict[tuple, torch.Tensor] = {}
         self._streams: Dict[tuple, torch.cuda.Stream] = {}
         self.samples = {"valid": 0, "app": 0}  # list lengths of the local ranks' chunks since the last render_frame began
+        # ids instead of points on the wire whenever the owners can evaluate colour from the ray (set False to force points)
+        self.ship_ids = self.ships_ids()
 
     def _buf(self, lane: int, i: int, name: str, rows: int, cols: int, dtype, device) -> torch.Tensor:
         """Grow-only buffer ``name`` of lane ``lane`` and local rank ``i``, at least [rows, cols] (flat when cols == 0)."""
@@ -779,6 +790,122 @@ class BlockParallelRenderer:
             buf = torch.empty(int(need * 1.25) + 16, dtype=dtype, device=device)
             self._bufs[key] = buf
         return buf[:need].view(max(rows, 1), cols) if cols else buf[:need]
+
+    def ships_ids(self) -> bool:
+        """True if the exchange can ship ids instead of points: every local owner runs the one-kernel appearance path
+        (it evaluates colour in list mode, from the ray) -- all ranks of a group must be configured alike."""
+        return all(bool(lib.gnr_query_one_kernel_appearance(o._handle)) for o in self.owners)
+
+    def _agree_ray_capacity(self, n_local_max: int) -> int:
+        """Rows per rank in the chunk's table of rays (the largest chunk of any rank), agreed once per call."""
+        dev = self.samplers[0].device
+        m = self.comm.gather_counts([torch.tensor([n_local_max], dtype=torch.int32, device=s_.device) for s_ in self.samplers])
+        return max(1, int(m.max()))
+
+    def _steps_ids(self, rays: Sequence[torch.Tensor], n_samples: int, white_bg: bool, lane: int, result: list, cap: int):
+        """The four steps with ids on the wire: a valid sample travels as 4 bytes (ray << bits | sample) instead of 12,
+        an appearance sample as 4 instead of 24; every rank's rays and entry distances of the chunk are all-gathered
+        (28 bytes per ray) and the owners recompute the positions (``gnr_density_list`` / ``gnr_appearance_list``)."""
+        tm, div, nb, W = self.timer, self.division, self.comm.world, self.comm.world
+        chunks, sends, dests, cnts, rays_pad, tmins = [], [], [], [], [], []
+        for i, (s_, r, rank) in enumerate(zip(self.samplers, rays, self.comm.local_ranks)):
+            with torch.cuda.device(s_.device):
+                ch = _Chunk(s_, r, n_samples, slot=lane)
+                if ch.n > cap:
+                    raise ValueError(f"a chunk of {ch.n} rays exceeds the agreed ray capacity {cap}")
+                rp = self._buf(lane, i, "rays_pad", cap, 6, torch.float32, s_.device)
+                rp[: ch.n] = ch.rays
+                tmn = self._buf(lane, i, "tmin_own", cap, 0, torch.float32, s_.device)
+                ch.launch_sample(tmn)
+                tm.mark("sample")
+                send = self._buf(lane, i, "send_ids", ch.max_valid, 0, torch.int32, s_.device)
+                dest = self._buf(lane, i, "dest", ch.max_valid, 0, torch.int32, s_.device)
+                cnt = self._buf(lane, i, "cnt", nb, 0, torch.int32, s_.device)
+                ch.launch_route_ids(0, div, rank * cap, send, dest, cnt)
+                tm.mark("route valid")
+                chunks.append(ch)
+                sends.append(send)
+                dests.append(dest)
+                cnts.append(cnt)
+                rays_pad.append(rp)
+                tmins.append(tmn)
+        matrix = self.comm.gather_counts(cnts)
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                ch.checked_status()
+        tm.mark("counts of the valid lists")
+        yield
+        rays_all = self.comm.all_gather_into(rays_pad, [self._buf(lane, i, "rays_all", W * cap, 6, torch.float32, o.device)
+                                                        for i, o in enumerate(self.owners)])
+        tmin_all = self.comm.all_gather_into(tmins, [self._buf(lane, i, "tmin_all", W * cap, 0, torch.float32, o.device)
+                                                     for i, o in enumerate(self.owners)])
+        tm.mark("all-gather rays")
+        n_in = [int(matrix[:, r].sum()) for r in self.comm.local_ranks]
+        recv = self.comm.all_to_all_known(sends, matrix, [self._buf(lane, i, "recv_ids", n, 0, torch.int32, o.device)
+                                                          for i, (o, n) in enumerate(zip(self.owners, n_in))])
+        tm.mark("all-to-all ids")
+        sig = []
+        for i, (o, s_, x, rank) in enumerate(zip(self.owners, self.samplers, recv, self.comm.local_ranks)):
+            out = self._buf(lane, i, "sigma", x.shape[0], 0, torch.float32, o.device)
+            if x.shape[0]:
+                with torch.cuda.device(o.device):
+                    check(lib.gnr_density_list(o._handle, s_._handle, _ptr(rays_all[i]), _ptr(tmin_all[i]), _ptr(x), x.shape[0],
+                                               chunks[i].s, div[0], div[1], rank, _ptr(out), _stream()), "gnr_density_list")
+            sig.append(out)
+        tm.mark("density at owners")
+        back = self.comm.all_to_all_known(sig, matrix.T, [self._buf(lane, i, "sigma_back", ch.max_valid, 0, torch.float32, ch.m.device)
+                                                          for i, ch in enumerate(chunks)])
+        tm.mark("all-to-all sigma")
+        yield
+        app_sends, app_dests = [], []
+        for i, (ch, dest, sg, rank) in enumerate(zip(chunks, dests, back, self.comm.local_ranks)):
+            with torch.cuda.device(ch.m.device):
+                ch.launch_weights(sg, dest)
+                tm.mark("weights")
+                send = self._buf(lane, i, "app_send_ids", ch.max_app, 0, torch.int32, ch.m.device)
+                dest_a = self._buf(lane, i, "app_dest", ch.max_app, 0, torch.int32, ch.m.device)
+                ch.launch_route_ids(1, div, rank * cap, send, dest_a, cnts[i])
+                tm.mark("route appearance")
+                app_sends.append(send)
+                app_dests.append(dest_a)
+        amatrix = self.comm.gather_counts(cnts)
+        for ch in chunks:
+            with torch.cuda.device(ch.m.device):
+                ch.checked_status()
+        tm.mark("counts of the appearance lists")
+        self.samples["valid"] += sum(ch.num_valid for ch in chunks)
+        self.samples["app"] += sum(ch.num_app for ch in chunks)
+        yield
+        n_in = [int(amatrix[:, r].sum()) for r in self.comm.local_ranks]
+        arecv = self.comm.all_to_all_known(app_sends, amatrix, [self._buf(lane, i, "app_recv_ids", n, 0, torch.int32, o.device)
+                                                                for i, (o, n) in enumerate(zip(self.owners, n_in))])
+        tm.mark("all-to-all appearance ids")
+        rgb_o = []
+        for i, (o, s_, x, rank) in enumerate(zip(self.owners, self.samplers, arecv, self.comm.local_ranks)):
+            out = self._buf(lane, i, "rgb_owner", x.shape[0], 3, torch.float32, o.device)[: x.shape[0]]
+            if x.shape[0]:
+                keep, sc, nbytes = _scratch(o, x.shape[0], lane)
+                with torch.cuda.device(o.device):
+                    check(lib.gnr_appearance_list(o._handle, s_._handle, _ptr(rays_all[i]), _ptr(tmin_all[i]), _ptr(x), x.shape[0],
+                                                  chunks[i].s, div[0], div[1], rank, sc, nbytes, _ptr(out), _stream()),
+                          "gnr_appearance_list")
+            rgb_o.append(out)
+        tm.mark("appearance at owners")
+        rgb_back = self.comm.all_to_all_known(rgb_o, amatrix.T, [self._buf(lane, i, "rgb_back", ch.max_app, 3, torch.float32, ch.m.device)
+                                                                 for i, ch in enumerate(chunks)])
+        tm.mark("all-to-all rgb")
+        for i, (ch, dest_a, rb) in enumerate(zip(chunks, app_dests, rgb_back)):
+            with torch.cuda.device(ch.m.device):
+                rgb_s = self._buf(lane, i, "rgb_list", ch.num_app, 3, torch.float32, ch.m.device)[: ch.num_app]
+                if ch.num_app:
+                    torch.index_select(rb, 0, dest_a[: ch.num_app], out=rgb_s)
+                result.append(ch.composite(rgb_s, white_bg))
+        tm.mark("composite")
+
+    def _chunk_steps(self, rays, n_samples, white_bg, lane, result, cap):
+        if cap:
+            return self._steps_ids(rays, n_samples, white_bg, lane, result, cap)
+        return self._steps(rays, n_samples, white_bg, lane, result)
 
     def _steps(self, rays: Sequence[torch.Tensor], n_samples: int, white_bg: bool, lane: int, result: list):
         """Generator over the four steps of one chunk; ``result`` receives per local rank ``(rgb_map, depth_map)``."""
@@ -872,9 +999,10 @@ class BlockParallelRenderer:
     def render_chunk(self, rays: Sequence[torch.Tensor], n_samples: int = -1, white_bg: bool = True):
         """``rays[i]``: the chunk of rays local rank i is responsible for (they differ per rank).
         Returns per local rank ``(rgb_map, depth_map)`` of its own rays."""
+        cap = self._agree_ray_capacity(max(r.shape[0] for r in rays)) if self.ship_ids else 0
         self.timer.start()
         out: list = []
-        for _ in self._steps(rays, n_samples, white_bg, 0, out):
+        for _ in self._chunk_steps(rays, n_samples, white_bg, 0, out, cap):
             pass
         return out
 
@@ -886,6 +1014,9 @@ class BlockParallelRenderer:
         returns.  Only the single-process-per-rank form overlaps; with several local ranks (loopback) the
         lanes still alternate but share the current device's streams."""
         self.samples = {"valid": 0, "app": 0}
+        cap = 0
+        if self.ship_ids and len(chunk_list):
+            cap = self._agree_ray_capacity(max(r.shape[0] for c in chunk_list for r in c))
         self.timer.start()
-        return _run_lanes(lambda c, lane, out: self._steps(chunk_list[c], n_samples, white_bg, lane, out), len(chunk_list),
-                          lanes, self.samplers[0].device, self._streams, 2)
+        return _run_lanes(lambda c, lane, out: self._chunk_steps(chunk_list[c], n_samples, white_bg, lane, out, cap),
+                          len(chunk_list), lanes, self.samplers[0].device, self._streams, 2)
