@@ -13,9 +13,9 @@ constexpr int kWarpsPerBlock = 8;
 
 // One thread per ray, samples in order: the same operations in the same order as the fused
 // march kernel, so both give the same bits.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32)  // one warp per CTA: a finished warp frees its slot at once
 weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float* __restrict__ t_min_arr,
-               const uint32_t* __restrict__ ids, const float* __restrict__ sigma, const int32_t* __restrict__ offsets,
+               const uint32_t* __restrict__ words, const float* __restrict__ sigma, const int32_t* __restrict__ offsets,
                int64_t n_rays, long long capacity, float* __restrict__ weight, float* __restrict__ acc_out,
                float* __restrict__ depth_out, int32_t* __restrict__ app_counts, const int32_t* __restrict__ rows,
                float2* __restrict__ packed) {
@@ -29,10 +29,15 @@ weights_kernel(GnrSampleParams p, float distance_scale, float thres, const float
   int n_app = 0;
   if (beg < end) {
     const float t_min = t_min_arr[ray];
-    const uint32_t kmask = (1u << p.kbits) - 1u;
     float T = 1.0f;  // transmittance before the current sample
+    // entry i of the valid list is the (i - beg)-th set bit of the ray's validity words, in order
+    const uint32_t* wrow = words + (size_t)ray * p.words;
+    int word = 0;
+    uint32_t bits = __ldg(wrow);
     for (long long i = beg; i < end; ++i) {
-      const int k = (int)(__ldg(ids + i) & kmask);
+      while (bits == 0u && word + 1 < p.words) bits = __ldg(wrow + ++word);
+      const int k = word * 32 + (__ffs(bits) - 1);
+      bits &= bits - 1u;
       const float t = gnr_sample_t(p, t_min, k);
       // dists = z[k+1] - z[k], 0 for the last sample (gridnerf_sequential.py:457)
       const float dist = (k == p.S - 1) ? 0.0f : __fsub_rn(gnr_sample_t(p, t_min, k + 1), t);
@@ -193,10 +198,10 @@ composite_kernel(const float* __restrict__ app_weight, const int32_t* __restrict
 
 int launch_weights_only(const GnrModel* m, const GnrSampleParams& p, int64_t n, char* ws, const GnrWs& L,
                         int64_t max_valid, cudaStream_t st, const float* sigma_rows, const int32_t* rows) {
-  unsigned blocks = (unsigned)((n + 127) / 128);
+  unsigned blocks = (unsigned)((n + 31) / 32);
   const bool ext = sigma_rows != nullptr;  // owners' answers read in place through `rows`, packed output
-  weights_kernel<<<blocks, 128, 0, st>>>(
-      p, m->cfg.distance_scale, m->cfg.ray_weight_thres, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.ids),
+  weights_kernel<<<blocks, 32, 0, st>>>(
+      p, m->cfg.distance_scale, m->cfg.ray_weight_thres, (const float*)(ws + L.t_min), (const uint32_t*)(ws + L.words),
       ext ? sigma_rows : (const float*)(ws + L.sigma), (const int32_t*)(ws + L.offsets), n, (long long)max_valid,
       (float*)(ws + L.weight), (float*)(ws + L.acc), (float*)(ws + L.depth), (int32_t*)(ws + L.app_counts),
       ext ? rows : nullptr, ext ? (float2*)(ws + L.sigma) : nullptr);
