@@ -258,7 +258,10 @@ int gnr_weights(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, v
 /* Stages 2 + 3 in one pass (what gnr_render_chunk runs): density of the valid samples of the
  * last gnr_sample on this workspace, raw2alpha with the transmittance product in sample order,
  * early ray termination at GnrConfig.ert_transmittance (0 = none), and the appearance compaction.
- * Outputs as gnr_weights (samples after a ray's termination have weight 0); no sigma is kept. */
+ * Outputs as gnr_weights (samples after a ray's termination have weight 0); no sigma is kept.
+ * With ``weights`` and ``app_index`` both null the pass writes only the samples above the appearance
+ * threshold (what gnr_render_chunk does): the appearance list, counts, offsets, acc and depth are the same,
+ * the workspace's per-sample weight array is then not filled. */
 int gnr_march(GnrModel* m, const float* rays, int64_t n_rays, int n_samples, void* workspace,
               size_t workspace_bytes, int64_t max_valid, int64_t max_app, float* weights, float* acc,
               float* depth, int32_t* app_counts, int32_t* app_offsets, int32_t* app_index, void* stream);

@@ -938,8 +938,11 @@ extern "C" int gnr_march(GnrModel* m, const float* rays, int64_t n, int S, void*
   char* ws = (char*)workspace;
   GnrWs L = gnr_ws_layout(m, n, S, max_valid, max_app);
   GnrSampleParams p = gnr_sample_params(m, S);
-  GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st));
-  GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st));
+  // a caller that takes neither the per-sample weights nor the valid-list index of the entries gets the frame loop's
+  // form: only the samples above the appearance threshold are written (the list, counts and offsets are the same)
+  const int list_only = (weights == nullptr && app_index == nullptr) ? 1 : 0;
+  GNR_LAUNCH_OK(launch_march(m, p, rays, n, ws, L, st, list_only));
+  GNR_LAUNCH_OK(launch_app_compact(m, p, n, ws, L, max_valid, max_app, st, list_only));
   if (copy_out(weights, ws + L.weight, (size_t)max_valid * 4, st)) return -2;
   if (copy_out(acc, ws + L.acc, (size_t)n * 4, st)) return -2;
   if (copy_out(depth, ws + L.depth, (size_t)n * 4, st)) return -2;
