@@ -373,6 +373,11 @@ int gnr_project_slice_points(GnrModel* m, const float* xyz, int point_stride, in
  * ``w * part_stride_rows`` rows into ``parts_h``): the receiver's side of that exchange. */
 int gnr_sum_partials(GnrModel* m, const void* parts_h, int n_parts, int64_t rows, int64_t part_stride_rows, float* features,
                      void* stream);
+/* gnr_sum_partials + gnr_mlp_features in one kernel: rgb[n][3] of the points whose W partial rows lie in ``parts_h``
+ * (summed in fp32, parts in order, inside the one-kernel appearance path) and whose view directions are columns 3..5
+ * of ``rows6[n][6]`` (the rows gnr_route_blocks writes for an appearance list).  mlp_mode 2 only. */
+int gnr_mlp_partial_rows(GnrModel* m, const void* parts_h, int n_parts, int64_t part_stride_rows, const float* rows6,
+                         int64_t n, void* scratch, size_t scratch_bytes, float* rgb, void* stream);
 /* MLPRender_Fea alone on explicit ``features[n][app_dim]`` and ``view[n][3]`` (the sample slice a
  * tensor-parallel rank owns after the reduction, gridnerf_tensor_parallel.py:301-325). */
 int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,

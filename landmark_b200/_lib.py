@@ -95,6 +95,7 @@ SIGNATURES = {
     "gnr_density_list": (_INT, [_P, _P, _P, _P, _P, _I64, C.c_int, C.c_int, C.c_int, C.c_int, _P, _P]),
     "gnr_appearance_list": (_INT, [_P, _P, _P, _P, _P, _I64, C.c_int, C.c_int, C.c_int, C.c_int, _P, _SZ, _P, _P]),
     "gnr_project_slice_points": (_INT, [_P, _P, C.c_int, _I64, _P, _P, _P]),
+    "gnr_mlp_partial_rows": (_INT, [_P, _P, C.c_int, _I64, _P, _I64, _P, _SZ, _P, _P]),
     "gnr_sum_partials": (_INT, [_P, _P, C.c_int, _I64, _I64, _P, _P]),
     "gnr_app_features_points": (_INT, [_P, _P, _I64, _P, _SZ, _P, _P]),
     "gnr_mlp_features": (_INT, [_P, _P, _P, _I64, _P, _SZ, _P, _P]),

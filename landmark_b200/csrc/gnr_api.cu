@@ -1324,6 +1324,33 @@ extern "C" int gnr_sum_partials(GnrModel* m, const void* parts_h, int n_parts, i
   return 0;
 }
 
+extern "C" int gnr_mlp_partial_rows(GnrModel* m, const void* parts_h, int n_parts, int64_t part_stride_rows,
+                                    const float* rows6, int64_t n, void* scratch, size_t scratch_bytes, float* rgb,
+                                    void* stream) {
+  int rc = check_points(m, "gnr_mlp_partial_rows", n, scratch, scratch_bytes);
+  if (rc) return rc;
+  if (n == 0) return 0;
+  if (!parts_h || !rows6 || !rgb || n_parts < 1 || part_stride_rows < n) {
+    gnr_set_error("gnr_mlp_partial_rows: null parts, rows or rgb, or bad sizes (%d parts, stride %lld, %lld rows)", n_parts,
+                  (long long)part_stride_rows, (long long)n);
+    return -1;
+  }
+  if (m->cfg.mlp_mode != 2 || m->cfg.unfused_appearance == 1 || !m->mlp.tc_image) {
+    gnr_set_error("gnr_mlp_partial_rows: needs mlp_mode 2 and the one-kernel appearance path");
+    return -1;
+  }
+  DeviceGuard g(m->device);
+  cudaStream_t st = (cudaStream_t)stream;
+  char* sc = (char*)scratch;
+  const PointScratch S = point_scratch(m, n);
+  GnrSampleParams p = gnr_sample_params(m, 1);
+  GNR_CUDA_OK(cudaMemsetAsync(sc + S.status, 0, GNR_ST_WORDS * 4, st));
+  // view directions are columns 3..5 of the (point, view) rows the appearance list was routed as
+  GNR_LAUNCH_OK(launch_app_mlp_fused(m, p, coords_points(nullptr, rows6 + 3, n, 6), rgb, (int32_t*)(sc + S.status), st, nullptr, 0,
+                                     parts_h, n_parts, part_stride_rows));
+  return 0;
+}
+
 extern "C" int gnr_mlp_features(GnrModel* m, const float* features, const float* view, int64_t n, void* scratch,
                                 size_t scratch_bytes, float* rgb, void* stream) {
   int rc = check_points(m, "gnr_mlp_features", n, scratch, scratch_bytes);

@@ -84,6 +84,9 @@ struct FusedArgs {
   int lat_g[3];                  // its grid
   const float* feat;             // SRC 2: [n][feat_stride] fp32 projected features of the points
   int feat_stride;
+  const unsigned char* parts;    // SRC 3: n_parts buffers of fp16 rows of 32 (64 bytes), part w starting part_stride rows in
+  int n_parts;
+  long long part_stride;
   int blk_px, blk_bx, blk_by;    // list mode at a block owner (blk_px > 0): positions, computed in the sampler's global
   float blk_pw, blk_ph;          // box, are then expressed in the coordinates of block (blk_bx, blk_by)
 };
@@ -95,10 +98,11 @@ struct RaySample {  // what a row needs of its list entry
 
 // SRC: where a tile's 27 projected features come from: 0 = gathered from the planes and lines and projected
 // here, 1 = the projected-feature lattice, 2 = given per point (features computed elsewhere, e.g. summed over
-// the channel slices of a tensor-parallel group); 1 and 2 start a tile at step 3.
+// the channel slices of a tensor-parallel group), 3 = given per point as n_parts partial rows of 32 fp16 (the rows a
+// tensor-parallel rank received from its peers), summed here in fp32; 1, 2 and 3 start a tile at step 3.
 template <int NP, bool PROF, bool POINTS, int SRC, int FG>
 __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSampleParams p, PlaneSet planes, FusedArgs a) {
-  constexpr bool LAT = SRC == 1, FEAT = SRC == 2;
+  constexpr bool LAT = SRC == 1, FEAT = SRC == 2, PARTS = SRC == 3;
   extern __shared__ __align__(128) unsigned char smem[];
   unsigned char* s_wb = smem;
   unsigned char* s_w1 = s_wb + WB_BYTES;  // layer 1, K permuted (see the header of this file)
@@ -262,7 +266,44 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     if (tile + 2 * FG < t_end) id_ahead = entry_of(tile + 2 * FG);
 
     uint32_t v[32];  // the 27 projected features of this row as fp32 bits (half 0 reads v[0..13], half 1 v[14..26])
-    if constexpr (FEAT) {
+    if constexpr (PARTS) {
+      // ---- features as the fp32 sum of n_parts fp16 rows (part w of row r at (w * part_stride + r) * 64 bytes): this
+      // half's columns, parts added in order -----------------------------------------------------------------------
+      const size_t r = (size_t)(j < total ? j : total - 1);
+      float acc[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) acc[e] = 0.0f;
+      for (int w = 0; w < a.n_parts; ++w) {
+        // half 0: columns 0..15 (uses 0..13); half 1: columns 8..31 are loaded, 14..26 used -> acc[e] = column 14 + e
+        const uint4* src = reinterpret_cast<const uint4*>(a.parts + ((size_t)w * a.part_stride + r) * 64);
+        if (half == 0) {
+          const uint4 c0 = __ldg(src), c1 = __ldg(src + 1);
+          const uint32_t u[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+          for (int e = 0; e < 7; ++e) {
+            const float2 f = __half22float2(as_h2(u[e]));
+            acc[2 * e] += f.x;
+            acc[2 * e + 1] += f.y;
+          }
+        } else {
+          const uint4 c1 = __ldg(src + 1), c2 = __ldg(src + 2), c3 = __ldg(src + 3);
+          const uint32_t u[12] = {c1.x, c1.y, c1.z, c1.w, c2.x, c2.y, c2.z, c2.w, c3.x, c3.y, c3.z, c3.w};  // columns 8..31
+#pragma unroll
+          for (int e = 0; e < 13; ++e) {  // column 14 + e = element (6 + e) of the 24 loaded
+            const float2 f = __half22float2(as_h2(u[(6 + e) >> 1]));
+            acc[e] += ((6 + e) & 1) ? f.y : f.x;
+          }
+        }
+      }
+      if (half == 0) {
+#pragma unroll
+        for (int e = 0; e < 14; ++e) v[e] = __float_as_uint(acc[e]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 13; ++e) v[14 + e] = __float_as_uint(acc[e]);
+      }
+      PROF_MARK(0);
+    } else if constexpr (FEAT) {
       // ---- features given per point: this half's 14 / 13 values of the row --------------------------------------
       const float* src = a.feat + (size_t)(j < total ? j : total - 1) * a.feat_stride + (half ? 14 : 0);
       if (half == 0) {
@@ -450,7 +491,7 @@ __global__ void __launch_bounds__(FG * GT, 1) app_mlp_fused_kernel(GnrSamplePara
     // ---- D = A1 * W1^T (warp 1) ------------------------------------------------------------------------------
     if (wg == 1) {
       tc_fence_after();
-      const uint32_t leader = (SRC == 0 || acquire_d()) ? elect_one() : 0u;  // (without a projection this is the tile's first MMA)
+      const uint32_t leader = (SRC == 0 || acquire_d()) ? elect_one() : 0u;  // SRC != 0: no projection came before  // (without a projection this is the tile's first MMA)
 #pragma unroll
       for (int ks = 0; ks < K1 / 16; ++ks)
         mma_f16_ts(d_tmem, a_tmem + ks * 8, make_desc(w1_addr + ks * 2 * KG_BYTES, KG_BYTES), kIdescHid, ks > 0 ? 1u : 0u, leader);
@@ -609,7 +650,9 @@ int gnr_app_fusable(const GnrModel* m) {
 }
 
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
-                         cudaStream_t st, const float* features, int feat_stride) {
+                         cudaStream_t st, const float* features, int feat_stride, const void* parts_h, int n_parts,
+                         int64_t part_stride_rows) {
+  if (parts_h) features = reinterpret_cast<const float*>(parts_h);  // (marks the features-given family below)
   if (!m->mlp.tc_image) {
     gnr_set_error("tensor-core MLP weights were not prepared");
     return -1;
@@ -643,6 +686,9 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   for (int i = 0; i < 3; ++i) a.lat_g[i] = m->app_lat_dims[i];
   a.feat = features;
   a.feat_stride = feat_stride;
+  a.parts = (const unsigned char*)parts_h;
+  a.n_parts = n_parts;
+  a.part_stride = part_stride_rows;
   a.blk_px = points ? 0 : c.blk_px;
   a.blk_bx = c.blk_bx;
   a.blk_by = c.blk_by;
@@ -656,6 +702,7 @@ int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrC
   };
   auto pick_variant = [&](auto groups_tag) -> int {
     constexpr int G = decltype(groups_tag)::value;
+    if (parts_h) return launch(app_mlp_fused_kernel<3, false, true, 3, G>, G);
     if (features) return launch(app_mlp_fused_kernel<3, false, true, 2, G>, G);
     if (m->app_lattice)  // features from the projected-feature lattice: no gather of planes, no projection GEMM
       return points ? launch(app_mlp_fused_kernel<3, false, true, 1, G>, G) : launch(app_mlp_fused_kernel<3, false, false, 1, G>, G);

@@ -190,7 +190,8 @@ int launch_app_mlp_stream(const GnrModel* m, const GnrSampleParams& p, const Gnr
                           cudaStream_t st);
 // (`features` non-null: MLP alone on given projected features [n][feat_stride] and c.view_direct)
 int launch_app_mlp_fused(const GnrModel* m, const GnrSampleParams& p, const GnrCoords& c, float* rgb, int32_t* status,
-                         cudaStream_t st, const float* features = nullptr, int feat_stride = 0);
+                         cudaStream_t st, const float* features = nullptr, int feat_stride = 0,
+                         const void* parts_h = nullptr, int n_parts = 0, int64_t part_stride_rows = 0);
 // partial projection of a channel slice at explicit points, fp16 rows of 32 (gnr_app_slice.cu), and the fp32 sum of such parts
 int launch_app_slice_project(const GnrModel* m, const float* xyz, int stride, int64_t n, void* features_h, int32_t* status,
                              cudaStream_t st);

@@ -612,10 +612,11 @@ class ChannelParallelRenderer:
         for i, (ch, recv, pts) in enumerate(zip(chunks, recvs, rows6)):
             with torch.cuda.device(ch.m.device):
                 na = ch.num_app
-                feats = self._buf((lane, i), "feats", na, ch.m.app_dim, torch.float32, ch.m.device)
-                if na:
-                    check(lib.gnr_sum_partials(ch.m._handle, _ptr(recv), W, na, per, _ptr(feats), _stream()), "gnr_sum_partials")
-                rgb_s = mlp_features(ch.m, feats[:na], pts[:na, 3:6].contiguous(), lane)
+                rgb_s = self._buf((lane, i), "rgb_list", na, 3, torch.float32, ch.m.device)[:na]
+                if na:  # the W partial rows of every own sample are summed inside the MLP kernel
+                    keep, sc, nbytes = _scratch(ch.m, na, lane)
+                    check(lib.gnr_mlp_partial_rows(ch.m._handle, _ptr(recv), W, per, _ptr(pts), na, sc, nbytes, _ptr(rgb_s),
+                                                   _stream()), "gnr_mlp_partial_rows")
                 pix.append(ch.composite(rgb_s, white_bg))
         tm.mark("sum + MLP + composite (own rays)")
         result.extend(self._gather_pixels(rays, chunks, shares, pix, lane))

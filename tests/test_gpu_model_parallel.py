@@ -365,3 +365,32 @@ def test_slice_projection_bounded_wait_expires_and_the_context_survives():
     model.debug_wait()
     again, st = project()
     assert st[4] == 0 and torch.equal(again, good)
+
+
+def test_partial_rows_summed_inside_the_mlp_kernel_equal_sum_then_mlp():
+    """gnr_mlp_partial_rows (the W fp16 partial rows of a sample summed in fp32 inside the one-kernel appearance path)
+    against gnr_sum_partials followed by gnr_mlp_features on the same rows: the same additions in the same order and the
+    same network, so the colours agree bit for bit."""
+    from landmark_b200._lib import check, lib
+    from landmark_b200.gridnerf import _ptr, _stream
+    from landmark_b200.model_parallel import _scratch, mlp_features
+
+    spec = scenes.tiny_spec(grid=64).lit()
+    model = cuda_model(spec, mlp_mode=2, app_plane_fp16=True)
+    n, W, per = 3001, 3, 3200
+    g = torch.Generator().manual_seed(5)
+    parts = (torch.randn((W * per, 32), generator=g) * 0.3).to(torch.float16).cuda()
+    parts[:, 27:] = 0
+    rows6 = torch.randn((n, 6), generator=g).cuda()
+    rows6[:, 3:6] = torch.nn.functional.normalize(rows6[:, 3:6], dim=1)
+    feats = torch.empty((n, model.app_dim), dtype=torch.float32, device="cuda:0")
+    check(lib.gnr_sum_partials(model._handle, _ptr(parts), W, n, per, _ptr(feats), _stream()), "gnr_sum_partials")
+    want_f = parts.view(W, per, 32)[:, :n, :27].float().sum(0)
+    assert torch.allclose(feats, want_f, atol=1e-6)
+    want = mlp_features(model, feats, rows6[:, 3:6].contiguous())
+    got = torch.empty((n, 3), dtype=torch.float32, device="cuda:0")
+    keep, sc, nbytes = _scratch(model, n)
+    check(lib.gnr_mlp_partial_rows(model._handle, _ptr(parts), W, per, _ptr(rows6), n, sc, nbytes, _ptr(got), _stream()),
+          "gnr_mlp_partial_rows")
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
