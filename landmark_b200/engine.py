@@ -246,12 +246,27 @@ class NerfDDPRunner:
             ev.record()
         return ev
 
+    HOST_RING = 4  # pinned host images run_batch rotates over
+
     def run_batch(self, single_pose) -> np.ndarray:
-        ev = self.enqueue(single_pose, self.img_cpu)
+        """One frame, synchronously.  The returned array is a view of one of ``HOST_RING`` pinned host images that
+        take turns: it stays untouched until ``HOST_RING - 1`` further frames have been rendered (copy it to keep it
+        longer).  Handing out the pinned image itself saves an 8 MB host copy per frame."""
+        ring = self.__dict__.get("_host_ring")
+        if ring is None:  # pinned once, on the first frame
+            ring = [self.img_cpu]
+            for _ in range(self.HOST_RING - 1):
+                img = torch.zeros((self.H, self.W, 4), dtype=torch.uint8)
+                ring.append(img.pin_memory() if torch.device(self.renderer.device).type == "cuda" else img)
+            self._host_ring = ring
+        turn = self.__dict__.get("_host_turn", 0)
+        host = ring[turn]
+        self._host_turn = (turn + 1) % self.HOST_RING
+        ev = self.enqueue(single_pose, host)
         if ev is not None:
             ev.synchronize()
         self.renderer.finish()
-        return self.img_cpu.numpy().copy()
+        return host.numpy()
 
     def serve(self, max_frames: int = -1) -> int:
         """Loop of a non-main rank: render every broadcast pose until the stop message (or
