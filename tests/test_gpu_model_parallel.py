@@ -78,7 +78,7 @@ def _block_scene(division, grid=32, seed0=100):
     return gspec, gck, blocks
 
 
-@pytest.mark.parametrize("division,mlp_mode", [((2, 1), 0), ((2, 2), 2), ((2, 2), "bench")])
+@pytest.mark.parametrize("division,mlp_mode", [((2, 1), 0), ((2, 2), 2), ((2, 2), "bench"), ((4, 2), "bench")])
 def test_block_parallel_matches_oracle(division, mlp_mode):
     from landmark_b200.gridnerf import B200GridNeRF
     from landmark_b200.model_parallel import BlockParallelRenderer, LoopbackComm
@@ -91,7 +91,8 @@ def test_block_parallel_matches_oracle(division, mlp_mode):
     pose = scenes.pitched_pose((0.1, -0.2, 2.5), yaw_deg=20.0, pitch_deg=-65.0)
     rays = orc.generate_rays(torch.from_numpy(pose), 48, 64, 40.0)
     ref = mpo.render_chunk_blocks(gfield, bfields, division, rays, 160, True)
-    assert len(torch.unique(ref["block"])) == world and int(ref["app_mask"].sum()) > 2000
+    # (the 4 x 2 scene is wider than the camera's view: six of its eight blocks hold samples, the other owners idle)
+    assert len(torch.unique(ref["block"])) >= min(world, 6) and int(ref["app_mask"].sum()) > 2000
     # samplers: global box / step / mask, planes never read -> keep them 2x2
     samplers, owners = [], []
     for r in range(world):
@@ -114,7 +115,8 @@ def test_block_parallel_matches_oracle(division, mlp_mode):
         rgb[p], depth[p] = c.cpu(), d.cpu()
     _check(rgb, depth, ref)
     # the frame form: three chunks per rank through the two-lane pipeline give the bits of chunk-by-chunk calls
-    cuts = [0, 200, 520, 10 ** 9]
+    n_min = min(p.numel() for p in parts)
+    cuts = [0, n_min // 4, (5 * n_min) // 8, 10 ** 9]  # three uneven, non-empty chunks per rank
     chunk_list = [[rays[p][lo:hi].cuda() for p in parts] for lo, hi in zip(cuts[:-1], cuts[1:])]
     for lanes in (1, 2):
         res = ren.render_frame(chunk_list, 160, True, lanes=lanes)
