@@ -742,8 +742,8 @@ int gnr_check_chunk(const GnrModel* m, int64_t n, int S, int64_t max_valid, int6
     gnr_set_error("null model");
     return -1;
   }
-  if (n < 0 || S < 1 || max_valid < 0 || max_app < 0) {
-    gnr_set_error("bad chunk arguments: n_rays %lld n_samples %d max_valid %lld max_app %lld", (long long)n, S,
+  if (n < 1 || S < 1 || max_valid < 0 || max_app < 0) {
+    gnr_set_error("bad chunk arguments: n_rays %lld (at least 1) n_samples %d max_valid %lld max_app %lld", (long long)n, S,
                   (long long)max_valid, (long long)max_app);
     return -1;
   }
