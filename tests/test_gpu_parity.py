@@ -755,7 +755,7 @@ def test_bounded_wait_expires_and_the_context_survives(fused):
     assert torch.equal(again["rgb_map"], good["rgb_map"]) and int(model.last_status[4]) == 0
 
 
-@pytest.mark.parametrize("scale", [10.0, 30.0])
+@pytest.mark.parametrize("scale", [10.0, 30.0, 100.0])
 def test_large_appearance_values_stress(scale):
     """Every synthetic field is 0.1 * randn; a trained field can carry larger features.  Appearance planes
     scaled by 10 and 30 (features up to several units, so sin/cos of 2 f see real phase): the
