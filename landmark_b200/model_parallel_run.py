@@ -15,7 +15,6 @@ NCCL).  Both build seeded synthetic scenes on the fly:
 
 from __future__ import annotations
 
-import os
 import time
 from typing import Dict, Tuple
 
@@ -91,8 +90,9 @@ def build_channels(world: int, rank_list, device: str, mlp_mode: int, grid_scale
 
 
 def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank: int, world: int, device: str,
-        grid_scale: int = 1, check: bool = False, ert: float = 0.0, app_fp16: bool = False, den_lattice: bool = True) -> Dict:
-    """Render ``steps`` frames; returns timing and sample statistics (rank 0's view)."""
+        grid_scale: int = 1, check: bool = False, ert: float = 0.0, app_fp16: bool = False, den_lattice: bool = True,
+        lanes: int = 2) -> Dict:
+    """Render ``steps`` frames; returns timing and sample statistics (rank 0's view).  ``lanes``: chunks in flight."""
     import torch.distributed as dist
 
     comm = DistComm() if world > 1 else LoopbackComm(1)
@@ -133,7 +133,7 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
             out.append((lo, hi, rays[lo:hi] if hi > lo else rays[:1]))  # an idle rank still takes part in the exchange
         return out
 
-    def frame_blocks(lanes=int(os.environ.get('GNR_LANES', '2'))):
+    def frame_blocks(lanes=lanes):
         """Block layout: the chunks of the frame go through the renderer's two-lane pipeline."""
         parts = parts_of_frame()
         res = ren.render_frame([[p[2]] for p in parts], S, True, lanes=lanes)
@@ -143,7 +143,7 @@ def run(workload: str, steps: int, warmup: int, chunk: int, mlp_mode: int, rank:
         shard.assemble(rgb, image)
         stats["valid"], stats["app"] = ren.samples["valid"], ren.samples["app"]
 
-    def frame_channels(lanes=int(os.environ.get('GNR_LANES', '2'))):
+    def frame_channels(lanes=lanes):
         """Channel layout: every rank walks the whole frame; the chunks go through the renderer's two-lane pipeline."""
         parts = parts_of_frame()
         res = ren.render_frame([[p[2]] for p in parts], S, True, lanes=lanes)
