@@ -217,11 +217,12 @@ def main():
     ap.add_argument("--no-variants", action="store_true", help="skip the extra configurations (literal scene, T < 1e-3, mlp_mode 1, ...)")
     ap.add_argument("--no-overlap", action="store_true", help="render the chunks of a frame on one stream only")
     ap.add_argument("--streams", type=int, default=2, help="streams the chunks of a frame rotate over")
-    ap.add_argument("--frames-in-flight", type=int, default=1, choices=(1, 2),
-                    help="2: a frame's chunks may start while the previous frame's last chunk and tile gather still run "
-                         "(two output buffer sets; measured 19.50 against 19.63 ms on one GPU, 9.95 against 9.99 on two: "
-                         "the persistent appearance kernel leaves no room beside it); 1 (default): every frame waits for "
-                         "the one before it")
+    ap.add_argument("--frames-in-flight", type=int, default=2, choices=(1, 2),
+                    help="2 (default): a frame's first chunks may start while the previous frame's last chunk, assembly and "
+                         "tile gather still run (two output buffer sets; the throughput form of the reference's pipe engine; "
+                         "about 0.1 ms per frame at any N: 19.51 against 19.64 ms on one GPU, 2.65 against 2.74 ms for one "
+                         "rank's eighth of the frame); 1: every frame waits for the one before it.  `e2e` is always one "
+                         "frame at a time")
     ap.add_argument("--order", default="tiles", choices=["tiles", "rows"], help="ray order at N=1")
     ap.add_argument("--profile-case", type=int, default=0, metavar="RAYS",
                     help="render one chunk of RAYS rays from the middle of the frame twice and exit "
