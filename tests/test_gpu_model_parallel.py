@@ -125,6 +125,15 @@ def test_block_parallel_matches_oracle(division, mlp_mode):
             assert torch.equal(torch.cat([res[c][r][0] for c in range(3)]), outs[r][0]), (lanes, r)
             assert torch.equal(torch.cat([res[c][r][1] for c in range(3)]), outs[r][1]), (lanes, r)
     assert ren.samples["valid"] > 0 and ren.samples["app"] > 2000
+    if mlp_mode == "bench":
+        # ids on the wire (owners recompute the positions from the gathered rays) against points on the wire: same bits
+        assert ren.ship_ids
+        ren.ship_ids = False
+        pts = ren.render_chunk([rays[p].cuda() for p in parts], 160, True)
+        for (a, b), (c, d) in zip(outs, pts):
+            assert torch.equal(a, c) and torch.equal(b, d)
+    else:
+        assert not ren.ship_ids
 
 
 def test_assign_blocks_matches_oracle_restatement():
